@@ -1,0 +1,121 @@
+"""ctypes binding of ``libbobcat_cuda.so`` (declared in ``include/bobcat_cuda.h``).
+
+The library is the product; this module only declares its signatures. There is no fallback: if the
+shared library is missing, importing anything that needs it raises with the build command.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libbobcat_cuda.so")
+
+vp, u32, i32, u64, sz, f32 = C.c_void_p, C.c_uint32, C.c_int32, C.c_uint64, C.c_size_t, C.c_float
+
+
+class Hparams(C.Structure):
+    _fields_ = [(n, i32 if n == "architecture" else u32) for n in (
+        "architecture", "n_layers", "n_attention_layers", "n_conv_layers", "n_delta_layers", "n_embd", "n_ff", "n_vocab",
+        "n_heads", "n_kv_heads", "head_dim", "n_rot", "conv_kernel", "n_experts", "n_experts_used", "n_ff_expert",
+        "n_k_heads", "n_v_heads", "k_head_dim", "v_head_dim")] + [("rope_theta", f32), ("norm_eps", f32)]
+
+
+class Trace(C.Structure):
+    _fields_ = [("embedding", C.POINTER(f32)), ("layers", C.POINTER(f32)), ("final_norm", C.POINTER(f32)), ("n_tokens", u32)]
+
+
+class ProfileEntry(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("n_rows", u32), ("n_cols", u32), ("calls", u64), ("seconds", C.c_double), ("bytes", u64)]
+
+
+EMIT_FN = C.CFUNCTYPE(i32, u32, vp)
+
+# name -> (restype, argtypes). `None` restype means void; the default restype is the status code.
+_VIEW = [vp, sz]
+SIGNATURES = {
+    "bc_last_error": (C.c_char_p, []),
+    "bc_version": (C.c_char_p, []),
+    "bc_backend_open": (i32, [i32, vp, C.POINTER(vp)]),
+    "bc_backend_close": (None, [vp]),
+    "bc_backend_stream": (vp, [vp]),
+    "bc_buffer_new": (i32, [vp, sz, C.POINTER(vp)]),
+    "bc_buffer_free": (None, [vp]),
+    "bc_buffer_len": (sz, [vp]),
+    "bc_buffer_device_ptr": (vp, [vp]),
+    "bc_buffer_write": (i32, [vp, sz, vp, sz]),
+    "bc_buffer_read": (i32, [vp, sz, vp, sz]),
+    "bc_matrix_upload": (i32, [vp, i32, vp, u32, u32, C.POINTER(vp)]),
+    "bc_begin": (i32, [vp]),
+    "bc_barrier": (i32, [vp]),
+    "bc_commit": (i32, [vp, C.POINTER(u64)]),
+    "bc_wait": (i32, [vp, u64, C.POINTER(C.c_double)]),
+    "bc_end": (i32, [vp, C.POINTER(C.c_double)]),
+    "bc_discard": (None, [vp]),
+    "bc_set_profiling": (i32, [vp, i32]),
+    "bc_profile": (i32, [vp, C.POINTER(ProfileEntry), sz, C.POINTER(sz)]),
+    "bc_op_matvec": (i32, [vp, i32] + _VIEW + [u32, u32] + _VIEW + _VIEW + _VIEW + [f32, i32]),
+    "bc_op_matvec_swiglu": (i32, [vp, i32] + _VIEW + _VIEW + [u32, u32] + _VIEW + _VIEW + [f32] + _VIEW),
+    "bc_op_matvec_conv": (i32, [vp, i32] + _VIEW + [u32] + _VIEW + _VIEW + [f32] + _VIEW + _VIEW + _VIEW + [u32, u32]),
+    "bc_op_short_conv": (i32, [vp] + _VIEW + _VIEW + _VIEW + _VIEW + [u32, u32, u32]),
+    "bc_op_matmul": (i32, [vp, i32] + _VIEW + [u32, u32] + _VIEW + _VIEW + [u32, i32]),
+    "bc_op_expand": (i32, [vp, i32] + _VIEW + _VIEW + [u32, u32, i32]),
+    "bc_op_embed": (i32, [vp, i32] + _VIEW + [u32] + _VIEW + _VIEW + [u32, u32]),
+    "bc_op_rms_norm": (i32, [vp] + _VIEW + _VIEW + _VIEW + [u32, u32, f32]),
+    "bc_op_norm_rope": (i32, [vp] + _VIEW + _VIEW + [i32] + _VIEW + [u32] * 8 + [f32, f32]),
+    "bc_op_convert_half": (i32, [vp] + _VIEW + _VIEW + [u32]),
+    "bc_op_copy": (i32, [vp] + _VIEW + _VIEW + [u32]),
+    "bc_op_attention": (i32, [vp] + _VIEW + _VIEW + _VIEW + [i32] + _VIEW + _VIEW + [u32] * 6),
+    "bc_attention_scratch_floats": (sz, [u32, u32, u32, u32]),
+    "bc_op_argmax": (i32, [vp] + _VIEW + _VIEW + [u32]),
+    "bc_op_silu_mul": (i32, [vp] + _VIEW + _VIEW + [u32]),
+    "bc_model_load": (i32, [C.c_char_p, C.POINTER(vp)]),
+    "bc_model_free": (None, [vp]),
+    "bc_model_hparams": (i32, [vp, C.POINTER(Hparams)]),
+    "bc_model_attention_layers": (i32, [vp, vp, sz]),
+    "bc_model_decode_bytes": (u64, [vp]),
+    "bc_seq_new": (i32, [vp, vp, u32, i32, C.POINTER(vp)]),
+    "bc_seq_free": (None, [vp]),
+    "bc_seq_n_past": (u32, [vp]),
+    "bc_seq_step": (i32, [vp, u32, vp, sz, C.POINTER(Trace)]),
+    "bc_seq_prefill": (i32, [vp, vp, sz, vp, sz, vp, sz, C.POINTER(Trace)]),
+    "bc_seq_greedy_token": (i32, [vp, C.POINTER(u32)]),
+    "bc_seq_generate": (i32, [vp, vp, sz]),
+    "bc_seq_generate_next": (i32, [vp, vp, sz]),
+    "bc_seq_generate_stream": (i32, [vp, u32, EMIT_FN, vp, vp, sz, C.POINTER(sz)]),
+    "bc_seq_reset": (i32, [vp]),
+    "bc_seq_checkpoint": (i32, [vp, C.POINTER(vp)]),
+    "bc_seq_restore": (i32, [vp, vp]),
+    "bc_checkpoint_free": (None, [vp]),
+    "bc_seq_timings": (i32, [vp, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "bc_seq_read_state": (i32, [vp, i32, u32, vp, sz, C.POINTER(sz)]),
+    "bc_seq_launches": (u64, [vp]),
+    "bc_gguf_writer_new": (i32, [C.c_char_p, u64, C.POINTER(vp)]),
+    "bc_gguf_writer_kv_u32": (i32, [vp, C.c_char_p, u32]),
+    "bc_gguf_writer_kv_f32": (i32, [vp, C.c_char_p, f32]),
+    "bc_gguf_writer_kv_str": (i32, [vp, C.c_char_p, C.c_char_p]),
+    "bc_gguf_writer_kv_u32_array": (i32, [vp, C.c_char_p, C.POINTER(u32), u64]),
+    "bc_gguf_writer_tensor": (i32, [vp, C.c_char_p, i32, C.POINTER(u64), u32, i32, f32]),
+    "bc_gguf_writer_finish": (i32, [vp]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the shared library, declaring every signature. Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            "bobcat_b200: %s is missing. Build it with `python -m bobcat_b200.build` "
+            "(nvcc, sm_100a). There is no CPU fallback." % LIB_PATH)
+    L = C.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(L, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = L
+    return L

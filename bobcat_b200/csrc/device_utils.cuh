@@ -1,0 +1,83 @@
+// Device helpers shared by the kernels: warp/block reductions, the shared-memory layout of an
+// input vector, and the register-level Q4_0 unpack.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace bc {
+namespace k {
+
+constexpr int kWarpSize = 32;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the whole CTA; every thread receives the result. `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = lane < n_warps ? scratch[lane] : 0.f;
+    return warp_sum(total);
+}
+
+// An input vector lives in shared memory as float4 chunks. Chunk c (elements 4c..4c+3) of 32-element
+// block b sits at slot (b * 8) + ((c + b) & 7): rotating the eight chunks of a block by the block
+// index lets 8 lanes that each own a different block read the same chunk number without bank
+// conflicts, and lanes that walk consecutive chunks stay conflict-free too.
+__device__ __forceinline__ int x_slot(int block, int chunk) { return (block << 3) | ((chunk + block) & 7); }
+
+// The eight 4-bit quants of one 32-bit word of a Q4_0 block, minus 8, as floats: lo[i] is the low
+// nibble of byte i (element 4k+i of the block for word k), hi[i] the high nibble (element
+// 16+4k+i). The nibbles are masked in place into fp16 mantissas (0x6400 is 1024.0), so two
+// quants convert per logic op and the subtraction is exact.
+__device__ __forceinline__ void unpack_q4_word(uint32_t w, float (&lo)[4], float (&hi)[4]) {
+    const uint32_t magic = 0x64006400u;
+    uint32_t lo02 = (w & 0x000f000fu) | magic;   // 1024 + n        for bytes 0 and 2
+    uint32_t hi02 = (w & 0x00f000f0u) | magic;   // 1024 + 16 n     for bytes 0 and 2
+    uint32_t w8 = w >> 8;
+    uint32_t lo13 = (w8 & 0x000f000fu) | magic;  // bytes 1 and 3
+    uint32_t hi13 = (w8 & 0x00f000f0u) | magic;
+    const __half2 bias_lo = __floats2half2_rn(1032.f, 1032.f);
+    const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
+    const __half2 bias_hi = __floats2half2_rn(-72.f, -72.f);  // (1024 + 16 n) / 16 - 72 = n - 8
+    float2 a = __half22float2(__hsub2(*reinterpret_cast<__half2*>(&lo02), bias_lo));
+    float2 b = __half22float2(__hsub2(*reinterpret_cast<__half2*>(&lo13), bias_lo));
+    float2 c = __half22float2(__hfma2(*reinterpret_cast<__half2*>(&hi02), sixteenth, bias_hi));
+    float2 d = __half22float2(__hfma2(*reinterpret_cast<__half2*>(&hi13), sixteenth, bias_hi));
+    lo[0] = a.x; lo[2] = a.y; lo[1] = b.x; lo[3] = b.y;
+    hi[0] = c.x; hi[2] = c.y; hi[1] = d.x; hi[3] = d.y;
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float4 ldg_stream(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+}  // namespace k
+}  // namespace bc

@@ -1,0 +1,87 @@
+// Launch functions of every CUDA kernel in the library. All pointers are device pointers; all
+// launches go to `stream` and return the launch status without synchronising.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace bc {
+namespace k {
+
+// A matrix in the device layout.
+//  F32 / F16: `data` holds n_rows contiguous rows.
+//  Q4_0: `data` holds n_rows * (n_cols / 32) 16-byte quant groups, row-major, with the byte and
+//  nibble order of the GGUF block (low nibbles are elements 0..15, high nibbles 16..31); `scales`
+//  holds the matching fp16 scales. The split keeps every quant group 16-byte aligned so one lane
+//  reads a block with one 128-bit load and a warp reads 512 contiguous bytes.
+struct Mat {
+    int32_t format = 0;
+    const void* data = nullptr;
+    const __half* scales = nullptr;
+    uint32_t n_rows = 0, n_cols = 0;
+    // Rows [first, first + rows) of this matrix.
+    Mat rows(uint32_t first, uint32_t count) const;
+    uint64_t bytes() const;  // bytes a full pass over the matrix reads
+};
+
+struct Norm {
+    const float* weight = nullptr;  // null: no normalisation
+    float eps = 0.f;
+};
+
+// Up to three matrices that share an input vector, multiplied in one launch.
+struct MatvecSegment {
+    Mat w;
+    float* y = nullptr;
+};
+
+// Raise `kernel`'s dynamic shared-memory limit to `smem` bytes on the current device if needed.
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t smem);
+// Number of SMs of the current device.
+int sm_count();
+
+// Repack GGUF Q4_0 bytes (18-byte blocks) already on the device into the split layout.
+cudaError_t repack_q4_0(cudaStream_t stream, const uint8_t* raw, uint64_t n_blocks, void* quants, __half* scales);
+
+cudaError_t matvec(cudaStream_t stream, const MatvecSegment* segments, int n_segments, const float* x, Norm norm,
+                   bool accumulate);
+cudaError_t matvec_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, const float* x, Norm norm, float* y);
+cudaError_t matvec_conv(cudaStream_t stream, const Mat& in_proj, const float* x, Norm norm, const float* taps,
+                        float* history, float* out, uint32_t n_embd, uint32_t kernel);
+cudaError_t short_conv(cudaStream_t stream, const float* bcx, const float* taps, float* history, float* out,
+                       uint32_t n_embd, uint32_t kernel, uint32_t n_tokens);
+cudaError_t expand(cudaStream_t stream, const Mat& w, void* out, bool out_half);
+cudaError_t embed(cudaStream_t stream, const Mat& w, const uint32_t* tokens, float* out, uint32_t n_tokens);
+cudaError_t rms_norm(cudaStream_t stream, const float* x, const float* weight, float* out, uint32_t n_cols,
+                     uint32_t n_rows, float eps);
+cudaError_t norm_rope(cudaStream_t stream, const float* src, void* dst, bool dst_half, const float* weight,
+                      uint32_t n_heads, uint32_t head_dim, uint32_t head_stride, uint32_t n_rot, uint32_t first_pos,
+                      uint32_t n_tokens, uint32_t src_stride, uint32_t dst_stride, float theta, float eps);
+cudaError_t convert_half(cudaStream_t stream, const float* src, __half* dst, uint64_t n);
+cudaError_t copy_floats(cudaStream_t stream, const float* src, float* dst, uint64_t n);
+cudaError_t silu_mul(cudaStream_t stream, float* x, const float* gate, uint64_t n);
+
+// Causal grouped-query attention of n_queries tokens at positions first_pos.. over the cache.
+// q and out are [n_queries][n_heads * head_dim]; caches are [n_ctx][n_kv_heads * head_dim].
+// q_stride is the element stride between tokens of q (Qwen interleaves q and gate per head, so
+// q_head_stride is the element stride between heads).
+struct AttentionShape {
+    uint32_t n_heads, n_kv_heads, head_dim, first_pos, n_queries, n_ctx;
+    uint32_t q_stride, q_head_stride;
+};
+uint64_t attention_scratch_floats(uint32_t n_heads, uint32_t head_dim, uint32_t n_ctx, uint32_t n_queries);
+cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, const void* v_cache, bool kv_half,
+                      float* scratch, float* out, const AttentionShape& shape);
+
+// argmax over n floats, ties to the lowest index. `out` is a device word; `readback` (nullable) is
+// a host-mapped word that receives the same value.
+cudaError_t argmax(cudaStream_t stream, const float* x, uint32_t n, uint32_t* out, uint32_t* readback);
+
+// Y[t][r] (store) sum_c W[r][c] X[t][c]. X is [n_tokens][n_cols] f32, Y is [n_tokens][y_stride].
+cudaError_t matmul(cudaStream_t stream, const Mat& w, const float* x, float* y, uint32_t n_tokens, uint32_t y_stride,
+                   int32_t store);
+
+}  // namespace k
+}  // namespace bc

@@ -1,0 +1,203 @@
+// Causal grouped-query attention over a contiguous KV cache, split over 64-position chunks with a
+// combine pass (the structure of attention_chunk / attention_wide / attention_combine in
+// crates/bobcat-metal/src/attention.metal:26-265, :496-540; host side backend.rs:2150-2320).
+//
+// Chunk pass: one CTA per (KV head, chunk, query). The query heads of the group that shares the KV
+// head are scored together, so each key and value row is read from the cache once per group.
+// Each CTA writes, per query head, the chunk's score maximum, the sum of exponentials and the
+// unnormalised weighted value sum. Combine pass: one CTA per (query head, query) rescales the
+// chunk partials by exp(max_c - max) and divides.
+
+#include "device_utils.cuh"
+#include "kernels.h"
+
+namespace bc {
+namespace k {
+
+namespace {
+
+constexpr int kChunk = 64;         // positions per chunk
+constexpr int kMaxGroup = 8;       // query heads per KV head
+constexpr int kQueryBatch = 64;    // queries per launch, which bounds the scratch
+constexpr int kChunkThreads = 256;
+
+template <typename T>
+__device__ __forceinline__ float load_kv(const T* p);
+template <>
+__device__ __forceinline__ float load_kv<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float load_kv<__half>(const __half* p) { return __half2float(*p); }
+
+struct ChunkParams {
+    const float* q;
+    const void* k_cache;
+    const void* v_cache;
+    float* scratch;
+    uint32_t n_heads, n_kv_heads, head_dim, first_pos, n_ctx, q_stride, q_head_stride;
+    uint32_t query0;      // first query of this launch
+    uint32_t max_chunks;  // chunks the scratch holds per (query, head)
+};
+
+// Scratch layout: [query in batch][head][chunk][head_dim + 2] = (max, sum, acc[head_dim]).
+template <typename T>
+__global__ void __launch_bounds__(kChunkThreads) attention_chunk_kernel(ChunkParams p) {
+    const uint32_t kv_head = blockIdx.x, chunk = blockIdx.y, qi = blockIdx.z;
+    const uint32_t query = p.query0 + qi;
+    const uint32_t pos = p.first_pos + query;  // the query attends to positions 0..pos
+    const uint32_t start = chunk * kChunk;
+    if (start > pos) return;
+    const uint32_t count = min((uint32_t)kChunk, pos + 1 - start);
+    const uint32_t hd = p.head_dim, group = p.n_heads / p.n_kv_heads;
+    const uint32_t kv_dim = p.n_kv_heads * hd;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = kChunkThreads / 32;
+
+    extern __shared__ float smem[];
+    float* qs = smem;                         // [group][hd], pre-scaled
+    float* scores = qs + group * hd;          // [group][kChunk]
+    float* partial = scores + group * kChunk; // [slices][group][hd]
+    __shared__ float head_max[kMaxGroup], head_sum[kMaxGroup];
+
+    const float scale = 1.0f / sqrtf((float)hd);
+    for (uint32_t i = tid; i < group * hd; i += kChunkThreads) {
+        uint32_t g = i / hd, d = i % hd;
+        uint32_t head = kv_head * group + g;
+        qs[i] = p.q[(uint64_t)query * p.q_stride + (uint64_t)head * p.q_head_stride + d] * scale;
+    }
+    __syncthreads();
+
+    const T* kc = static_cast<const T*>(p.k_cache) + (uint64_t)start * kv_dim + (uint64_t)kv_head * hd;
+    const T* vc = static_cast<const T*>(p.v_cache) + (uint64_t)start * kv_dim + (uint64_t)kv_head * hd;
+
+    // Scores: a warp per position, lanes across the head.
+    for (uint32_t t = warp; t < count; t += n_warps) {
+        float dot[kMaxGroup];
+#pragma unroll
+        for (int g = 0; g < kMaxGroup; ++g) dot[g] = 0.f;
+        for (uint32_t d = lane; d < hd; d += 32) {
+            float kv = load_kv<T>(kc + (uint64_t)t * kv_dim + d);
+#pragma unroll
+            for (int g = 0; g < kMaxGroup; ++g)
+                if (g < group) dot[g] += kv * qs[g * hd + d];
+        }
+#pragma unroll
+        for (int g = 0; g < kMaxGroup; ++g) {
+            if (g < group) {
+                float s = warp_sum(dot[g]);
+                if (lane == 0) scores[g * kChunk + t] = s;
+            }
+        }
+    }
+    __syncthreads();
+
+    // Per head: chunk maximum, exponentials, their sum. A warp per head.
+    for (uint32_t g = warp; g < group; g += n_warps) {
+        float m = -INFINITY;
+        for (uint32_t t = lane; t < count; t += 32) m = fmaxf(m, scores[g * kChunk + t]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (uint32_t t = lane; t < count; t += 32) {
+            float e = expf(scores[g * kChunk + t] - m);
+            scores[g * kChunk + t] = e;
+            sum += e;
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) {
+            head_max[g] = m;
+            head_sum[g] = sum;
+        }
+    }
+    __syncthreads();
+
+    // Weighted value sums: thread (slice, d) walks every n_slices-th position of the chunk.
+    const uint32_t n_slices = kChunkThreads / hd;  // hd <= 256 and divides 256
+    const uint32_t d = tid % hd, slice = tid / hd;
+    float acc[kMaxGroup];
+#pragma unroll
+    for (int g = 0; g < kMaxGroup; ++g) acc[g] = 0.f;
+    if (slice < n_slices) {
+        for (uint32_t t = slice; t < count; t += n_slices) {
+            float v = load_kv<T>(vc + (uint64_t)t * kv_dim + d);
+#pragma unroll
+            for (int g = 0; g < kMaxGroup; ++g)
+                if (g < group) acc[g] += scores[g * kChunk + t] * v;
+        }
+#pragma unroll
+        for (int g = 0; g < kMaxGroup; ++g)
+            if (g < group) partial[(slice * group + g) * hd + d] = acc[g];
+    }
+    __syncthreads();
+    for (uint32_t i = tid; i < group * hd; i += kChunkThreads) {
+        uint32_t g = i / hd, dd = i % hd;
+        float total = 0.f;
+        for (uint32_t s = 0; s < n_slices; ++s) total += partial[(s * group + g) * hd + dd];
+        uint32_t head = kv_head * group + g;
+        float* out = p.scratch + (((uint64_t)qi * p.n_heads + head) * p.max_chunks + chunk) * (hd + 2);
+        out[2 + dd] = total;
+        if (dd == 0) {
+            out[0] = head_max[g];
+            out[1] = head_sum[g];
+        }
+    }
+}
+
+struct CombineParams {
+    const float* scratch;
+    float* out;
+    uint32_t n_heads, head_dim, first_pos, query0, max_chunks;
+};
+
+// grid (n_heads, queries in batch), head_dim threads.
+__global__ void attention_combine_kernel(CombineParams p) {
+    const uint32_t head = blockIdx.x, qi = blockIdx.y, d = threadIdx.x;
+    const uint32_t query = p.query0 + qi, pos = p.first_pos + query;
+    const uint32_t n_chunks = pos / kChunk + 1, hd = p.head_dim;
+    const float* base = p.scratch + ((uint64_t)qi * p.n_heads + head) * p.max_chunks * (hd + 2);
+    float m = -INFINITY;
+    for (uint32_t c = 0; c < n_chunks; ++c) m = fmaxf(m, base[(uint64_t)c * (hd + 2)]);
+    float sum = 0.f, acc = 0.f;
+    for (uint32_t c = 0; c < n_chunks; ++c) {
+        const float* part = base + (uint64_t)c * (hd + 2);
+        float w = expf(part[0] - m);
+        sum += w * part[1];
+        acc += w * part[2 + d];
+    }
+    p.out[(uint64_t)query * p.n_heads * hd + (uint64_t)head * hd + d] = acc / sum;
+}
+
+}  // namespace
+
+uint64_t attention_scratch_floats(uint32_t n_heads, uint32_t head_dim, uint32_t n_ctx, uint32_t n_queries) {
+    uint64_t queries = n_queries < (uint32_t)kQueryBatch ? n_queries : (uint32_t)kQueryBatch;
+    uint64_t chunks = ((uint64_t)n_ctx + kChunk - 1) / kChunk;
+    return queries * n_heads * chunks * (head_dim + 2);
+}
+
+cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, const void* v_cache, bool kv_half,
+                      float* scratch, float* out, const AttentionShape& s) {
+    if (s.n_queries == 0) return cudaSuccess;
+    const uint32_t group = s.n_heads / s.n_kv_heads;
+    const uint32_t max_chunks = (s.n_ctx + kChunk - 1) / kChunk;
+    const uint32_t n_slices = kChunkThreads / s.head_dim;
+    size_t smem = ((size_t)group * s.head_dim + (size_t)group * kChunk + (size_t)n_slices * group * s.head_dim) * sizeof(float);
+    cudaError_t e;
+    if (kv_half) e = ensure_dynamic_smem(reinterpret_cast<const void*>(attention_chunk_kernel<__half>), smem);
+    else e = ensure_dynamic_smem(reinterpret_cast<const void*>(attention_chunk_kernel<float>), smem);
+    if (e != cudaSuccess) return e;
+    for (uint32_t q0 = 0; q0 < s.n_queries; q0 += kQueryBatch) {
+        uint32_t nq = s.n_queries - q0 < (uint32_t)kQueryBatch ? s.n_queries - q0 : (uint32_t)kQueryBatch;
+        uint32_t last_pos = s.first_pos + q0 + nq - 1;
+        ChunkParams cp{q, k_cache, v_cache, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.first_pos, s.n_ctx,
+                       s.q_stride, s.q_head_stride, q0, max_chunks};
+        dim3 grid(s.n_kv_heads, last_pos / kChunk + 1, nq);
+        if (kv_half) attention_chunk_kernel<__half><<<grid, kChunkThreads, smem, stream>>>(cp);
+        else attention_chunk_kernel<float><<<grid, kChunkThreads, smem, stream>>>(cp);
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        CombineParams mp{scratch, out, s.n_heads, s.head_dim, s.first_pos, q0, max_chunks};
+        attention_combine_kernel<<<dim3(s.n_heads, nq), s.head_dim, 0, stream>>>(mp);
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+}  // namespace k
+}  // namespace bc

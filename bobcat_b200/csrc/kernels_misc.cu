@@ -1,0 +1,331 @@
+// The small kernels of the decode and prefill graphs: weight repack and expansion, embedding
+// gather, RMSNorm, per-head norm + rotary embedding + cache store, conversions, the batched short
+// convolution, and argmax. Counterparts: crates/bobcat-metal/src/norm.metal, conv.metal,
+// quant.metal:279-330 (expand).
+
+#include "device_utils.cuh"
+#include "kernels.h"
+#include "../../include/bobcat_cuda.h"
+
+namespace bc {
+namespace k {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline int blocks_for(uint64_t n, int per_block = kThreads) {
+    uint64_t b = (n + per_block - 1) / per_block;
+    return (int)(b < 1 ? 1 : b);
+}
+
+// GGUF Q4_0 block = 2 bytes of fp16 scale + 16 bytes of quants, 18 bytes, so blocks are only
+// 2-byte aligned. One thread moves one block.
+__global__ void repack_q4_0_kernel(const uint8_t* __restrict__ raw, uint64_t n_blocks, uint4* __restrict__ quants,
+                                   __half* __restrict__ scales) {
+    uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(raw + 18 * b);
+    uint16_t h[9];
+#pragma unroll
+    for (int i = 0; i < 9; ++i) h[i] = p[i];
+    scales[b] = __ushort_as_half(h[0]);
+    uint4 q;
+    q.x = h[1] | ((uint32_t)h[2] << 16);
+    q.y = h[3] | ((uint32_t)h[4] << 16);
+    q.z = h[5] | ((uint32_t)h[6] << 16);
+    q.w = h[7] | ((uint32_t)h[8] << 16);
+    quants[b] = q;
+}
+
+// One thread per Q4_0 block: value = f32(q - 8) * f32(d), the single multiply of
+// scalar::dequantize_q4_0 (crates/bobcat/src/scalar.rs:98-105), so the f32 output is bit-identical.
+template <typename Out>
+__global__ void expand_q4_0_kernel(const uint4* __restrict__ quants, const __half* __restrict__ scales,
+                                   uint64_t n_blocks, Out* __restrict__ out) {
+    uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    uint4 q = quants[b];
+    float d = __half2float(scales[b]);
+    uint32_t words[4] = {q.x, q.y, q.z, q.w};
+    Out* o = out + 32 * b;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t byte = (words[w] >> (8 * i)) & 0xffu;
+            float lo = (float)((int)(byte & 0xfu) - 8) * d;
+            float hi = (float)((int)(byte >> 4) - 8) * d;
+            o[4 * w + i] = (Out)lo;
+            o[16 + 4 * w + i] = (Out)hi;
+        }
+    }
+}
+
+template <typename In, typename Out>
+__global__ void convert_kernel(const In* __restrict__ src, Out* __restrict__ dst, uint64_t n) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = (Out)(float)src[i];
+}
+
+__global__ void silu_mul_kernel(float* __restrict__ x, const float* __restrict__ gate, uint64_t n) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        float g = gate[i];
+        x[i] = g / (1.f + expf(-g)) * x[i];
+    }
+}
+
+// grid (ceil(n_embd / threads), n_tokens)
+__global__ void embed_kernel(Mat w, const uint32_t* __restrict__ tokens, float* __restrict__ out) {
+    uint32_t token = tokens[blockIdx.y];
+    uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= w.n_cols) return;
+    float v;
+    if (w.format == BC_Q4_0) {
+        uint64_t block = (uint64_t)token * (w.n_cols >> 5) + (c >> 5);
+        const uint8_t* q = reinterpret_cast<const uint8_t*>(static_cast<const uint4*>(w.data) + block);
+        uint32_t i = c & 31;
+        uint8_t byte = q[i & 15];
+        int n = i < 16 ? (byte & 0xf) : (byte >> 4);
+        v = (float)(n - 8) * __half2float(w.scales[block]);
+    } else if (w.format == BC_F16) {
+        v = __half2float(static_cast<const __half*>(w.data)[(uint64_t)token * w.n_cols + c]);
+    } else {
+        v = static_cast<const float*>(w.data)[(uint64_t)token * w.n_cols + c];
+    }
+    out[(uint64_t)blockIdx.y * w.n_cols + c] = v;
+}
+
+// One CTA per row: out = w * (x * rsqrt(mean(x^2) + eps)), the order of scalar::rms_norm
+// (crates/bobcat/src/scalar.rs:224-229).
+__global__ void __launch_bounds__(kThreads) rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                                                             float* __restrict__ out, uint32_t n_cols, float eps) {
+    __shared__ float scratch[32];
+    const float* row = x + (uint64_t)blockIdx.x * n_cols;
+    float* o = out + (uint64_t)blockIdx.x * n_cols;
+    float sumsq = 0.f;
+    for (uint32_t c = threadIdx.x; c < n_cols; c += blockDim.x) sumsq += row[c] * row[c];
+    float total = block_sum(sumsq, scratch);
+    float scale = rsqrtf(total / (float)n_cols + eps);
+    for (uint32_t c = threadIdx.x; c < n_cols; c += blockDim.x) o[c] = weight[c] * (row[c] * scale);
+}
+
+struct NormRopeParams {
+    const float* src;
+    void* dst;
+    const float* weight;
+    uint32_t n_heads, head_dim, head_stride, n_rot, first_pos, src_stride, dst_stride;
+    float theta, eps;
+    int dst_half;
+};
+
+// One warp per (head, token): RMSNorm over head_dim with the shared weight, then the NeoX rotation
+// of the first n_rot elements (pairs i, i + n_rot / 2; inverse frequency 1 / theta^(2i / n_rot)
+// and angle in f32, as scalar::rope_neox does, crates/bobcat/src/scalar.rs:253-266), then the
+// store as f32 or half. grid (n_heads, n_tokens), 32 threads.
+__global__ void norm_rope_kernel(NormRopeParams p) {
+    const int lane = threadIdx.x;
+    const uint32_t head = blockIdx.x, token = blockIdx.y;
+    const float* src = p.src + (uint64_t)token * p.src_stride + (uint64_t)head * p.head_stride;
+    const uint64_t dst_index = (uint64_t)token * p.dst_stride + (uint64_t)head * p.head_dim;
+    // head_dim <= 256: each lane holds up to 8 elements, element e = lane + 32 j.
+    float v[8];
+    float sumsq = 0.f;
+    const int per_lane = p.head_dim / 32;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        v[j] = 0.f;
+        if (j < per_lane) {
+            v[j] = src[lane + 32 * j];
+            sumsq += v[j] * v[j];
+        }
+    }
+    sumsq = warp_sum(sumsq);
+    float scale = rsqrtf(sumsq / (float)p.head_dim + p.eps);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if (j < per_lane) v[j] = p.weight[lane + 32 * j] * (v[j] * scale);
+    // Rotation: element e < n_rot / 2 pairs with e + n_rot / 2. n_rot / 2 is a multiple of 16 here
+    // only when n_rot is a multiple of 32; handle any even n_rot through shared memory.
+    __shared__ float head_values[256];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if (j < per_lane) head_values[lane + 32 * j] = v[j];
+    __syncwarp();
+    const uint32_t half_rot = p.n_rot / 2;
+    const float pos = (float)(p.first_pos + token);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (j >= per_lane) continue;
+        uint32_t e = lane + 32 * j;
+        float result = v[j];
+        if (e < p.n_rot) {
+            uint32_t i = e < half_rot ? e : e - half_rot;
+            float inv_freq = 1.0f / powf(p.theta, (float)(2 * i) / (float)p.n_rot);
+            float angle = pos * inv_freq;
+            float s, c;
+            sincosf(angle, &s, &c);
+            float a = head_values[i], b = head_values[i + half_rot];
+            result = e < half_rot ? a * c - b * s : b * c + a * s;
+        }
+        if (p.dst_half) static_cast<__half*>(p.dst)[dst_index + e] = __float2half_rn(result);
+        else static_cast<float*>(p.dst)[dst_index + e] = result;
+    }
+}
+
+// One thread per channel, serial over tokens: bx = B * X, the taps over bx and the history, the
+// history shift (crates/bobcat/src/lfm2.rs:456-475). bcx is [n_tokens][3 n_embd], out is
+// [n_tokens][n_embd], history is [kernel - 1][n_embd]. kernel <= 9.
+__global__ void short_conv_kernel(const float* __restrict__ bcx, const float* __restrict__ taps,
+                                  float* __restrict__ history, float* __restrict__ out, uint32_t n_embd,
+                                  uint32_t kernel, uint32_t n_tokens) {
+    uint32_t ch = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ch >= n_embd) return;
+    float tap[9], hist[8];
+    for (uint32_t kk = 0; kk < kernel; ++kk) tap[kk] = taps[(uint64_t)ch * kernel + kk];
+    for (uint32_t kk = 0; kk + 1 < kernel; ++kk) hist[kk] = history[(uint64_t)kk * n_embd + ch];
+    for (uint32_t t = 0; t < n_tokens; ++t) {
+        const float* row = bcx + (uint64_t)t * 3 * n_embd;
+        float b = row[ch], c = row[n_embd + ch], x = row[2 * n_embd + ch];
+        float bx = b * x;
+        float sum = tap[kernel - 1] * bx;
+        for (uint32_t kk = 0; kk + 1 < kernel; ++kk) sum += tap[kk] * hist[kk];
+        for (uint32_t kk = 0; kk + 2 < kernel; ++kk) hist[kk] = hist[kk + 1];
+        hist[kernel - 2] = bx;
+        out[(uint64_t)t * n_embd + ch] = c * sum;
+    }
+    for (uint32_t kk = 0; kk + 1 < kernel; ++kk) history[(uint64_t)kk * n_embd + ch] = hist[kk];
+}
+
+// One CTA of 1024 threads scans the vocabulary; ties go to the lowest index.
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ x, uint32_t n, uint32_t* out,
+                                                       uint32_t* readback) {
+    __shared__ float best_value[32];
+    __shared__ uint32_t best_index[32];
+    float value = -INFINITY;
+    uint32_t index = 0xffffffffu;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = x[i];
+        if (v > value || index == 0xffffffffu) {
+            value = v;
+            index = i;
+        }
+    }
+    auto better = [](float v, uint32_t i, float bv, uint32_t bi) { return i != 0xffffffffu && (bi == 0xffffffffu || v > bv || (v == bv && i < bi)); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, value, o);
+        uint32_t oi = __shfl_xor_sync(0xffffffffu, index, o);
+        if (better(ov, oi, value, index)) {
+            value = ov;
+            index = oi;
+        }
+    }
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) {
+        best_value[warp] = value;
+        best_index[warp] = index;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        value = best_value[lane];
+        index = best_index[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, value, o);
+            uint32_t oi = __shfl_xor_sync(0xffffffffu, index, o);
+            if (better(ov, oi, value, index)) {
+                value = ov;
+                index = oi;
+            }
+        }
+        if (lane == 0) {
+            *out = index;
+            if (readback) *readback = index;
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t repack_q4_0(cudaStream_t stream, const uint8_t* raw, uint64_t n_blocks, void* quants, __half* scales) {
+    if (n_blocks == 0) return cudaSuccess;
+    repack_q4_0_kernel<<<blocks_for(n_blocks), kThreads, 0, stream>>>(raw, n_blocks, static_cast<uint4*>(quants), scales);
+    return cudaGetLastError();
+}
+
+cudaError_t expand(cudaStream_t stream, const Mat& w, void* out, bool out_half) {
+    uint64_t n = (uint64_t)w.n_rows * w.n_cols;
+    if (n == 0) return cudaSuccess;
+    if (w.format == BC_Q4_0) {
+        uint64_t nb = n / 32;
+        if (out_half)
+            expand_q4_0_kernel<__half><<<blocks_for(nb), kThreads, 0, stream>>>(static_cast<const uint4*>(w.data), w.scales, nb, static_cast<__half*>(out));
+        else
+            expand_q4_0_kernel<float><<<blocks_for(nb), kThreads, 0, stream>>>(static_cast<const uint4*>(w.data), w.scales, nb, static_cast<float*>(out));
+    } else if (w.format == BC_F16) {
+        if (out_half) convert_kernel<__half, __half><<<blocks_for(n), kThreads, 0, stream>>>(static_cast<const __half*>(w.data), static_cast<__half*>(out), n);
+        else convert_kernel<__half, float><<<blocks_for(n), kThreads, 0, stream>>>(static_cast<const __half*>(w.data), static_cast<float*>(out), n);
+    } else {
+        if (out_half) convert_kernel<float, __half><<<blocks_for(n), kThreads, 0, stream>>>(static_cast<const float*>(w.data), static_cast<__half*>(out), n);
+        else convert_kernel<float, float><<<blocks_for(n), kThreads, 0, stream>>>(static_cast<const float*>(w.data), static_cast<float*>(out), n);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t embed(cudaStream_t stream, const Mat& w, const uint32_t* tokens, float* out, uint32_t n_tokens) {
+    if (n_tokens == 0) return cudaSuccess;
+    dim3 grid(blocks_for(w.n_cols), n_tokens);
+    embed_kernel<<<grid, kThreads, 0, stream>>>(w, tokens, out);
+    return cudaGetLastError();
+}
+
+cudaError_t rms_norm(cudaStream_t stream, const float* x, const float* weight, float* out, uint32_t n_cols, uint32_t n_rows,
+                     float eps) {
+    if (n_rows == 0) return cudaSuccess;
+    rms_norm_kernel<<<n_rows, kThreads, 0, stream>>>(x, weight, out, n_cols, eps);
+    return cudaGetLastError();
+}
+
+cudaError_t norm_rope(cudaStream_t stream, const float* src, void* dst, bool dst_half, const float* weight, uint32_t n_heads,
+                      uint32_t head_dim, uint32_t head_stride, uint32_t n_rot, uint32_t first_pos, uint32_t n_tokens,
+                      uint32_t src_stride, uint32_t dst_stride, float theta, float eps) {
+    if (n_tokens == 0 || n_heads == 0) return cudaSuccess;
+    NormRopeParams p{src, dst, weight, n_heads, head_dim, head_stride, n_rot, first_pos, src_stride, dst_stride, theta, eps, dst_half ? 1 : 0};
+    dim3 grid(n_heads, n_tokens);
+    norm_rope_kernel<<<grid, 32, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t convert_half(cudaStream_t stream, const float* src, __half* dst, uint64_t n) {
+    if (n == 0) return cudaSuccess;
+    convert_kernel<float, __half><<<blocks_for(n), kThreads, 0, stream>>>(src, dst, n);
+    return cudaGetLastError();
+}
+
+cudaError_t copy_floats(cudaStream_t stream, const float* src, float* dst, uint64_t n) {
+    if (n == 0) return cudaSuccess;
+    return cudaMemcpyAsync(dst, src, n * sizeof(float), cudaMemcpyDeviceToDevice, stream);
+}
+
+cudaError_t silu_mul(cudaStream_t stream, float* x, const float* gate, uint64_t n) {
+    if (n == 0) return cudaSuccess;
+    silu_mul_kernel<<<blocks_for(n), kThreads, 0, stream>>>(x, gate, n);
+    return cudaGetLastError();
+}
+
+cudaError_t short_conv(cudaStream_t stream, const float* bcx, const float* taps, float* history, float* out, uint32_t n_embd,
+                       uint32_t kernel, uint32_t n_tokens) {
+    if (n_tokens == 0) return cudaSuccess;
+    short_conv_kernel<<<blocks_for(n_embd, 128), 128, 0, stream>>>(bcx, taps, history, out, n_embd, kernel, n_tokens);
+    return cudaGetLastError();
+}
+
+cudaError_t argmax(cudaStream_t stream, const float* x, uint32_t n, uint32_t* out, uint32_t* readback) {
+    argmax_kernel<<<1, 1024, 0, stream>>>(x, n, out, readback);
+    return cudaGetLastError();
+}
+
+}  // namespace k
+}  // namespace bc

@@ -1,0 +1,53 @@
+// The device state of one decode and the recording of its forward passes. Stands in for
+// `Lfm2Metal` (crates/bobcat/src/lfm2_metal.rs) and `Qwen35Metal` (crates/bobcat/src/qwen35_metal.rs).
+#pragma once
+
+#include <chrono>
+#include <memory>
+#include <vector>
+
+#include "model.h"
+
+// Generation keeps up to this many steps submitted ahead of the device
+// (GENERATE_IN_FLIGHT, crates/bobcat/src/lfm2_metal.rs:29-31).
+constexpr int kGenerateInFlight = 3;
+// Prefill runs the prompt this many tokens at a time (PREFILL_BATCH, lfm2_metal.rs:33-34).
+constexpr uint32_t kPrefillBatch = 512;
+
+struct bc_checkpoint {
+    const bc_seq* owner = nullptr;
+    uint64_t resets = 0;
+    uint32_t n_past = 0;
+    std::vector<float> conv_state;   // LFM2 conv history, or Qwen conv history of every DeltaNet layer
+    std::vector<float> delta_state;  // Qwen DeltaNet state matrices
+    std::vector<float> logits;
+};
+
+struct bc_seq {
+    bc_model* model = nullptr;
+    bc_backend* backend = nullptr;
+    std::shared_ptr<bc::DeviceModel> weights;
+    uint32_t n_ctx = 0, n_past = 0, batch = 0;
+    uint64_t resets = 0;
+    bool kv_half = false;
+    double last_encode_seconds = 0, last_gpu_seconds = 0;
+    uint64_t launches = 0;
+
+    // One device allocation carved into the buffers below.
+    void* arena = nullptr;
+    size_t arena_bytes = 0;
+    void *k_cache = nullptr, *v_cache = nullptr;
+    float *k = nullptr, *v = nullptr, *conv_state = nullptr, *hidden = nullptr, *normed = nullptr, *bcx = nullptr;
+    float *conv_out = nullptr, *q = nullptr, *attn = nullptr, *scores = nullptr, *ffn = nullptr, *logits = nullptr;
+    float *trace_embedding = nullptr, *trace_layers = nullptr, *trace_final = nullptr;
+    uint32_t* tokens = nullptr;        // n_ctx + 1 ids; the extra slot takes the pick at the last position
+    uint32_t* greedy_token = nullptr;
+    size_t conv_floats = 0;
+    uint32_t trace_rows = 0;
+    // Host-mapped words the device writes picked tokens into, one per step in flight.
+    uint32_t* readback = nullptr;
+    cudaEvent_t slot_done[kGenerateInFlight] = {};
+    cudaEvent_t timing_start = nullptr, timing_end = nullptr;
+
+    ~bc_seq();
+};

@@ -1,0 +1,194 @@
+"""``Model``, ``Lfm2Cuda`` and ``Qwen35Cuda``: the sequence API, with the method names of the
+reference's ``lfm2::Model`` / ``Lfm2Metal`` (crates/bobcat/src/lfm2.rs:186, lfm2_metal.rs:103-762)
+and ``Qwen35Metal`` (crates/bobcat/src/qwen35_metal.rs:112-676). All work happens in the C ABI."""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib, errors
+from .backend import Cuda
+
+
+class Trace:
+    """Activations of a run of tokens (``lfm2::Trace``, lfm2.rs:630-675)."""
+
+    def __init__(self, n_embd: int, n_layers: int, n_tokens: int):
+        self.embedding = np.zeros((n_tokens, n_embd), dtype=np.float32)
+        self.layers = np.zeros((n_layers, n_tokens, n_embd), dtype=np.float32)
+        self.final_norm = np.zeros((n_tokens, n_embd), dtype=np.float32)
+        self.n_tokens = n_tokens
+
+    def _c(self) -> _lib.Trace:
+        fp = C.POINTER(C.c_float)
+        return _lib.Trace(self.embedding.ctypes.data_as(fp), self.layers.ctypes.data_as(fp), self.final_norm.ctypes.data_as(fp), self.n_tokens)
+
+
+class Model:
+    """A GGUF model on the host (``Model::load``)."""
+
+    def __init__(self, path: str):
+        self._L = _lib.load()
+        h = C.c_void_p()
+        errors.check(self._L.bc_model_load(str(path).encode(), C.byref(h)), self._L)
+        self._h = h
+        hp = _lib.Hparams()
+        errors.check(self._L.bc_model_hparams(self._h, C.byref(hp)), self._L)
+        self.hp = hp
+
+    @classmethod
+    def load(cls, path: str) -> "Model":
+        return cls(path)
+
+    def hyperparameters(self) -> _lib.Hparams:
+        return self.hp
+
+    def attention_layers(self) -> list[bool]:
+        out = np.zeros(self.hp.n_layers, dtype=np.uint8)
+        errors.check(self._L.bc_model_attention_layers(self._h, out.ctypes.data_as(C.c_void_p), out.size), self._L)
+        return [bool(v) for v in out]
+
+    def decode_bytes(self) -> int:
+        return int(self._L.bc_model_decode_bytes(self._h))
+
+    def trace(self, n_tokens: int) -> Trace:
+        return Trace(self.hp.n_embd, self.hp.n_layers, n_tokens)
+
+    def close(self) -> None:
+        if self._h:
+            self._L.bc_model_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Checkpoint:
+    def __init__(self, lib, handle):
+        self._L, self._h = lib, handle
+
+    def __del__(self):
+        try:
+            if self._h:
+                self._L.bc_checkpoint_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+class SeqCuda:
+    """The device state of one decode. ``Lfm2Cuda`` and ``Qwen35Cuda`` are this class."""
+
+    def __init__(self, model: Model, cuda: Cuda, n_ctx: int, kv_half: bool):
+        self._L = _lib.load()
+        self.model, self.cuda = model, cuda
+        h = C.c_void_p()
+        errors.check(self._L.bc_seq_new(model._h, cuda._h, n_ctx, int(kv_half), C.byref(h)), self._L)
+        self._h = h
+        self.n_ctx = n_ctx
+
+    def _check(self, status: int) -> None:
+        errors.check(status, self._L)
+
+    def n_past(self) -> int:
+        return int(self._L.bc_seq_n_past(self._h))
+
+    def launches(self) -> int:
+        return int(self._L.bc_seq_launches(self._h))
+
+    def step(self, token: int, logits: np.ndarray | None = None, trace: Trace | None = None) -> None:
+        t = trace._c() if trace is not None else None
+        self._check(self._L.bc_seq_step(self._h, token, logits.ctypes.data_as(C.c_void_p) if logits is not None else None,
+                                        logits.size if logits is not None else 0, C.byref(t) if t is not None else None))
+
+    def prefill(self, tokens, logits: np.ndarray | None = None, final_norm: np.ndarray | None = None, trace: Trace | None = None) -> None:
+        tokens = np.ascontiguousarray(tokens, dtype=np.uint32)
+        t = trace._c() if trace is not None else None
+        p = lambda a: a.ctypes.data_as(C.c_void_p) if a is not None else None
+        n = lambda a: a.size if a is not None else 0
+        self._check(self._L.bc_seq_prefill(self._h, p(tokens), tokens.size, p(logits), n(logits), p(final_norm), n(final_norm),
+                                           C.byref(t) if t is not None else None))
+
+    def greedy_token(self) -> int:
+        tok = C.c_uint32()
+        self._check(self._L.bc_seq_greedy_token(self._h, C.byref(tok)))
+        return int(tok.value)
+
+    def generate(self, n: int) -> np.ndarray:
+        out = np.zeros(n, dtype=np.uint32)
+        self._check(self._L.bc_seq_generate(self._h, out.ctypes.data_as(C.c_void_p), n))
+        return out
+
+    def generate_next(self, n: int) -> np.ndarray:
+        out = np.zeros(n, dtype=np.uint32)
+        self._check(self._L.bc_seq_generate_next(self._h, out.ctypes.data_as(C.c_void_p), n))
+        return out
+
+    def generate_stream(self, max_tokens: int, emit) -> np.ndarray:
+        """``emit(token) -> bool``; returns the tokens the sequence gained."""
+        failure = []
+
+        def trampoline(token, _user):
+            try:
+                return 1 if emit(int(token)) else 0
+            except Exception as e:  # an exception must not cross the C boundary
+                failure.append(e)
+                return 0
+
+        cb = _lib.EMIT_FN(trampoline)
+        gained = np.zeros(max(1, max_tokens), dtype=np.uint32)
+        n = C.c_size_t()
+        self._check(self._L.bc_seq_generate_stream(self._h, max_tokens, cb, None, gained.ctypes.data_as(C.c_void_p), gained.size, C.byref(n)))
+        if failure:
+            raise failure[0]
+        return gained[: n.value].copy()
+
+    def reset(self) -> None:
+        self._check(self._L.bc_seq_reset(self._h))
+
+    def checkpoint(self) -> Checkpoint:
+        h = C.c_void_p()
+        self._check(self._L.bc_seq_checkpoint(self._h, C.byref(h)))
+        return Checkpoint(self._L, h)
+
+    def restore(self, checkpoint: Checkpoint) -> None:
+        self._check(self._L.bc_seq_restore(self._h, checkpoint._h))
+
+    def timings(self) -> tuple[float, float]:
+        e, g = C.c_double(), C.c_double()
+        self._check(self._L.bc_seq_timings(self._h, C.byref(e), C.byref(g)))
+        return float(e.value), float(g.value)
+
+    def last_encode_seconds(self) -> float:
+        return self.timings()[0]
+
+    def last_gpu_seconds(self) -> float:
+        return self.timings()[1]
+
+    def read_state(self, which: int, layer: int = 0) -> np.ndarray:
+        n = C.c_size_t()
+        self._check(self._L.bc_seq_read_state(self._h, which, layer, None, 0, C.byref(n)))
+        out = np.zeros(n.value, dtype=np.float32)
+        if n.value:
+            self._check(self._L.bc_seq_read_state(self._h, which, layer, out.ctypes.data_as(C.c_void_p), out.size, C.byref(n)))
+        return out
+
+    def close(self) -> None:
+        if self._h:
+            self._L.bc_seq_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+Lfm2Cuda = SeqCuda
+Qwen35Cuda = SeqCuda

@@ -1,0 +1,309 @@
+/* bobcat-cuda: the C ABI of the B200 (sm_100a) decode / prefill path for bobcat.
+ *
+ * Every entry point is plain C: opaque handles, pointers and sizes. Nothing here allocates with or
+ * depends on any Python or tensor library. Each group names the reference interface it stands in
+ * for (paths are relative to the bobcat repository root).
+ *
+ * Conventions
+ *  - Every call returns a bc_status. On failure bc_last_error() holds a message for the calling
+ *    thread. The library never prints, aborts or throws across this boundary
+ *    (the reference's rule: AGENTS.md "library code never prints, panics or exits").
+ *  - Arguments are validated before any device work; sequence positions advance only on success
+ *    (crates/bobcat/src/lfm2_metal.rs:314-332, :363).
+ *  - Handles are not thread-safe; distinct handles are independent
+ *    (crates/bobcat/tests/metal_commands.rs:12-59).
+ *  - There is no CPU fallback. Opening a backend without a CUDA device fails with BC_ERR_NO_DEVICE.
+ */
+#ifndef BOBCAT_CUDA_H
+#define BOBCAT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes: crates/bobcat/src/error.rs:10-97 and crates/bobcat-metal/src/backend.rs:163-298 */
+typedef int32_t bc_status;
+enum {
+    BC_OK = 0,
+    BC_ERR_IO = 1,               /* Error::Io */
+    BC_ERR_GGUF = 2,             /* Error::Gguf (any bobcat_gguf::Error) */
+    BC_ERR_METADATA = 3,         /* Error::Metadata */
+    BC_ERR_ARCHITECTURE = 4,     /* Error::Architecture */
+    BC_ERR_HYPERPARAMETERS = 5,  /* Error::Hyperparameters */
+    BC_ERR_ODD_HEAD_DIM = 6,     /* Error::OddHeadDim */
+    BC_ERR_MISSING_TENSOR = 7,   /* Error::MissingTensor */
+    BC_ERR_TENSOR_SHAPE = 8,     /* Error::TensorShape */
+    BC_ERR_TENSOR_TYPE = 9,      /* Error::TensorType */
+    BC_ERR_KV_HEADS = 10,        /* Error::KvHeads */
+    BC_ERR_TOKEN = 11,           /* Error::Token */
+    BC_ERR_CONTEXT_FULL = 12,    /* Error::ContextFull */
+    BC_ERR_ARGUMENT = 13,        /* Error::Argument */
+    BC_ERR_UNSUPPORTED = 14,     /* Error::MetalUnsupported */
+    BC_ERR_NO_DEVICE = 20,       /* bobcat_metal::Error::NoDevice */
+    BC_ERR_ALLOCATION = 21,      /* ::Allocation */
+    BC_ERR_NOT_RECORDING = 22,   /* ::NotRecording */
+    BC_ERR_ALREADY_RECORDING = 23, /* ::AlreadyRecording */
+    BC_ERR_OUT_OF_BOUNDS = 24,   /* ::OutOfBounds and ::Access */
+    BC_ERR_FOREIGN_BUFFER = 25,  /* ::ForeignBuffer */
+    BC_ERR_BUSY = 26,            /* ::Busy */
+    BC_ERR_ATTENTION_LIMITS = 27, /* ::AttentionLimits */
+    BC_ERR_GATE_SHAPE = 28,      /* ::GateShape */
+    BC_ERR_NO_FUSED_CONV = 29,   /* ::NoFusedConv */
+    BC_ERR_NO_EXPANSION = 30,    /* ::NoExpansion */
+    BC_ERR_NO_EXPERTS = 31,      /* ::NoExperts */
+    BC_ERR_DELTANET_LIMITS = 32, /* ::DeltaNetLimits */
+    BC_ERR_EXPERT_LIMITS = 33,   /* ::ExpertLimits */
+    BC_ERR_EXECUTION = 34        /* ::Execution (a CUDA error while running recorded work) */
+};
+
+/* The message of the calling thread's latest failure ("" when none). */
+const char* bc_last_error(void);
+/* The library's version string. */
+const char* bc_version(void);
+
+/* ---- weight formats: bobcat_metal::Format (crates/bobcat-metal/src/backend.rs:408-449).
+ * The numeric values are the ggml type ids (crates/bobcat-gguf/src/lib.rs:126-152). */
+enum { BC_F32 = 0, BC_F16 = 1, BC_Q4_0 = 2, BC_Q8_0 = 8 };
+
+/* ---- how a batched multiply combines with its output: bobcat_metal::Store (backend.rs:361-370) */
+enum { BC_STORE_OVERWRITE = 0, BC_STORE_ACCUMULATE = 1, BC_STORE_SWIGLU = 2 };
+
+/* ============================================================================================
+ * Backend: one CUDA device + one stream + the buffers allocated on it.
+ * Stands in for `bobcat_metal::Metal` (crates/bobcat-metal/src/backend.rs:1027-1340).
+ * ============================================================================================ */
+typedef struct bc_backend bc_backend;
+typedef struct bc_buffer bc_buffer;
+
+/* Metal::open (backend.rs:1083). `stream` may be an existing cudaStream_t the caller owns (work is
+ * then ordered with the caller's other work on it) or NULL for a stream the backend creates. */
+bc_status bc_backend_open(int32_t device, void* stream, bc_backend** out);
+void bc_backend_close(bc_backend* backend);
+/* The cudaStream_t every launch of this backend goes to. */
+void* bc_backend_stream(bc_backend* backend);
+
+/* Metal::new_buffer (backend.rs:1124): `len` zeroed bytes of device memory. */
+bc_status bc_buffer_new(bc_backend* backend, size_t len, bc_buffer** out);
+void bc_buffer_free(bc_buffer* buffer);
+size_t bc_buffer_len(const bc_buffer* buffer);
+/* The device address, for callers that share the buffer with their own CUDA code. */
+void* bc_buffer_device_ptr(bc_buffer* buffer);
+/* Metal::write / Metal::read (backend.rs:1180-1205): host <-> device copies, complete on return.
+ * Fail with BC_ERR_BUSY while a recording is open, BC_ERR_OUT_OF_BOUNDS past the end. */
+bc_status bc_buffer_write(bc_buffer* buffer, size_t offset, const void* data, size_t len);
+bc_status bc_buffer_read(bc_buffer* buffer, size_t offset, void* out, size_t len);
+
+/* Convert a matrix of `format` from its GGUF byte layout (`data`, n_rows * row_bytes) into the
+ * device layout the kernels read, in a new buffer. F32/F16 are copied unchanged. Q4_0 is split
+ * into 16-byte quant groups followed by the fp16 scales; values are unchanged bit for bit.
+ * No reference counterpart by name: the reference reads the mapped file in place
+ * (crates/bobcat/src/lfm2_metal.rs:137-146); a discrete GPU uploads once instead. */
+bc_status bc_matrix_upload(bc_backend* backend, int32_t format, const void* data, uint32_t n_rows,
+                           uint32_t n_cols, bc_buffer** out);
+
+/* Metal::begin / barrier / commit / wait / end / discard (backend.rs:1244-1279). Launches are
+ * legal only between begin and commit/end. `barrier` orders later launches after earlier ones;
+ * on a CUDA stream that order already holds, so it records nothing. A ticket is complete once
+ * bc_wait returns; `seconds` (nullable) receives the GPU time of the recorded work. */
+typedef uint64_t bc_ticket;
+bc_status bc_begin(bc_backend* backend);
+bc_status bc_barrier(bc_backend* backend);
+bc_status bc_commit(bc_backend* backend, bc_ticket* ticket);
+bc_status bc_wait(bc_backend* backend, bc_ticket ticket, double* seconds);
+bc_status bc_end(bc_backend* backend, double* seconds);
+void bc_discard(bc_backend* backend);
+
+/* Metal::set_profiling / profile (backend.rs:1285-1340): per (kernel, n_rows, n_cols) totals. */
+typedef struct bc_profile_entry {
+    const char* name;
+    uint32_t n_rows, n_cols;
+    uint64_t calls;
+    double seconds;
+    uint64_t bytes; /* weight bytes the launches read, for GB/s */
+} bc_profile_entry;
+bc_status bc_set_profiling(bc_backend* backend, int32_t enabled);
+/* Copies up to `capacity` entries; `count` receives the number available. */
+bc_status bc_profile(bc_backend* backend, bc_profile_entry* out, size_t capacity, size_t* count);
+
+/* ---- ops. A (buffer, byte offset) pair is the reference's `View` (backend.rs:337-341). Every
+ * op checks its ranges before launching (check_range, backend.rs:2772-2790). */
+
+/* Metal::matvec (backend.rs:1344-1380): y[r] (+)= sum_c W[r,c] * x^[c], with x^ = RMSNorm(x) *
+ * norm_weight when `norm` is non-null. `weights` must come from bc_matrix_upload. */
+bc_status bc_op_matvec(bc_backend* b, int32_t format, bc_buffer* weights, size_t w_off, uint32_t n_rows,
+                       uint32_t n_cols, bc_buffer* x, size_t x_off, bc_buffer* y, size_t y_off,
+                       bc_buffer* norm, size_t norm_off, float eps, int32_t accumulate);
+/* Metal::matvec_swiglu (backend.rs:1385-1417): y = silu(gate x^) * (up x^). */
+bc_status bc_op_matvec_swiglu(bc_backend* b, int32_t format, bc_buffer* gate, size_t gate_off, bc_buffer* up,
+                              size_t up_off, uint32_t n_rows, uint32_t n_cols, bc_buffer* x, size_t x_off,
+                              bc_buffer* norm, size_t norm_off, float eps, bc_buffer* y, size_t y_off);
+/* Metal::matvec_conv (backend.rs:2329-2382): LFM2 decode conv block up to the output projection:
+ * RMSNorm, in_proj rows (ch, n_embd+ch, 2 n_embd+ch) -> B, C, X, bx = B*X, taps over bx and the
+ * history, history shift, out = C * conv. */
+bc_status bc_op_matvec_conv(bc_backend* b, int32_t format, bc_buffer* in_proj, size_t w_off, uint32_t n_cols,
+                            bc_buffer* x, size_t x_off, bc_buffer* norm, size_t norm_off, float eps,
+                            bc_buffer* taps, size_t taps_off, bc_buffer* history, size_t hist_off,
+                            bc_buffer* out, size_t out_off, uint32_t n_embd, uint32_t kernel);
+/* Metal::short_conv / short_conv_batch (backend.rs:2384-2468): the same conv over `n_tokens` rows
+ * of a [n_tokens][3 n_embd] B|C|X projection. */
+bc_status bc_op_short_conv(bc_backend* b, bc_buffer* bcx, size_t bcx_off, bc_buffer* taps, size_t taps_off,
+                           bc_buffer* history, size_t hist_off, bc_buffer* out, size_t out_off,
+                           uint32_t n_embd, uint32_t kernel, uint32_t n_tokens);
+/* Metal::matmul (backend.rs:2470-2517): Y[t,r] = sum_c W[r,c] X[t,c] for n_tokens rows, combined
+ * with Y as `store` says. Q4_0 weights are multiplied on the tensor cores in half precision with
+ * f32 accumulation, inputs rounded to half, as the reference's Q4_0 path does
+ * (crates/bobcat-metal/src/matmul.metal:519-521). */
+bc_status bc_op_matmul(bc_backend* b, int32_t format, bc_buffer* weights, size_t w_off, uint32_t n_rows,
+                       uint32_t n_cols, bc_buffer* x, size_t x_off, bc_buffer* y, size_t y_off,
+                       uint32_t n_tokens, int32_t store);
+/* Metal::expand (backend.rs:2519-2550), widened: dequantise a whole uploaded matrix to contiguous
+ * rows of f32 (out_half = 0) or half (out_half = 1). The f32 result is bit-identical to
+ * scalar::dequantize (crates/bobcat/src/scalar.rs:59-105). */
+bc_status bc_op_expand(bc_backend* b, int32_t format, bc_buffer* weights, size_t w_off, bc_buffer* out,
+                       size_t out_off, uint32_t n_rows, uint32_t n_cols, int32_t out_half);
+/* Metal::embed (backend.rs:2570-2610): rows of the embedding matrix picked by `n_tokens` ids. */
+bc_status bc_op_embed(bc_backend* b, int32_t format, bc_buffer* weights, size_t w_off, uint32_t n_vocab,
+                      bc_buffer* tokens, size_t tok_off, bc_buffer* out, size_t out_off, uint32_t n_embd,
+                      uint32_t n_tokens);
+/* Metal::rms_norm (backend.rs:2034-2068). */
+bc_status bc_op_rms_norm(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* weight, size_t w_off,
+                         bc_buffer* out, size_t out_off, uint32_t n_cols, uint32_t n_rows, float eps);
+/* Metal::norm_rope (backend.rs:2070-2123): per-head RMSNorm, NeoX rotation of the first n_rot
+ * elements at positions first_pos.., store as f32 or half. Strides are in elements per token. */
+bc_status bc_op_norm_rope(bc_backend* b, bc_buffer* src, size_t src_off, bc_buffer* dst, size_t dst_off,
+                          int32_t dst_half, bc_buffer* weight, size_t w_off, uint32_t n_heads, uint32_t head_dim,
+                          uint32_t head_stride, uint32_t n_rot, uint32_t first_pos, uint32_t n_tokens,
+                          uint32_t src_stride, uint32_t dst_stride, float theta, float eps);
+/* Metal::convert_half / copy (backend.rs:2126-2148, :2552-2568). */
+bc_status bc_op_convert_half(bc_backend* b, bc_buffer* src, size_t src_off, bc_buffer* dst, size_t dst_off, uint32_t n);
+bc_status bc_op_copy(bc_backend* b, bc_buffer* src, size_t src_off, bc_buffer* dst, size_t dst_off, uint32_t n);
+/* Metal::attention (backend.rs:2150-2320): causal grouped-query attention of n_queries tokens at
+ * positions first_pos.. over cache rows [0, first_pos + i]. The caches are [n_ctx][n_kv_heads *
+ * head_dim] f32 or half. `scratch` needs bc_attention_scratch_floats floats. */
+bc_status bc_op_attention(bc_backend* b, bc_buffer* q, size_t q_off, bc_buffer* k_cache, size_t k_off,
+                          bc_buffer* v_cache, size_t v_off, int32_t kv_half, bc_buffer* scratch, size_t s_off,
+                          bc_buffer* out, size_t out_off, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                          uint32_t first_pos, uint32_t n_queries, uint32_t n_ctx);
+/* attention_scratch_floats (backend.rs:2739-2748). */
+size_t bc_attention_scratch_floats(uint32_t n_heads, uint32_t head_dim, uint32_t n_ctx, uint32_t n_queries);
+/* Metal::argmax (backend.rs:2612-2617): index of the largest of n floats, ties to the lowest. */
+bc_status bc_op_argmax(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* out, size_t out_off, uint32_t n);
+/* Metal::silu_mul (backend.rs:1983-1999): x = silu(gate) * x, elementwise. */
+bc_status bc_op_silu_mul(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* gate, size_t g_off, uint32_t n);
+
+/* ============================================================================================
+ * Model: a parsed GGUF file + its hyperparameters (host side).
+ * Stands in for lfm2::Model::load (crates/bobcat/src/lfm2.rs:186-233) and
+ * qwen35::Model::load (crates/bobcat/src/qwen35.rs:179-229); the architecture is read from
+ * `general.architecture` and may be "lfm2", "lfm2moe" or "qwen35".
+ * ============================================================================================ */
+typedef struct bc_model bc_model;
+
+enum { BC_ARCH_LFM2 = 0, BC_ARCH_LFM2MOE = 1, BC_ARCH_QWEN35 = 2 };
+
+/* lfm2::Hyperparameters (lfm2.rs:18-49) and qwen35::Hyperparameters (qwen35.rs:33-68) in one
+ * record; fields a family lacks are zero. */
+typedef struct bc_hparams {
+    int32_t architecture;
+    uint32_t n_layers, n_attention_layers, n_conv_layers, n_delta_layers;
+    uint32_t n_embd, n_ff, n_vocab;
+    uint32_t n_heads, n_kv_heads, head_dim, n_rot;
+    uint32_t conv_kernel;
+    uint32_t n_experts, n_experts_used, n_ff_expert;
+    uint32_t n_k_heads, n_v_heads, k_head_dim, v_head_dim;
+    float rope_theta, norm_eps;
+} bc_hparams;
+
+bc_status bc_model_load(const char* path, bc_model** out);
+void bc_model_free(bc_model* model);
+bc_status bc_model_hparams(const bc_model* model, bc_hparams* out);
+/* Writes 1 for each attention layer and 0 for each other layer (Model::attention_layers,
+ * lfm2.rs:241-245). `out` holds n_layers bytes. */
+bc_status bc_model_attention_layers(const bc_model* model, uint8_t* out, size_t len);
+/* Bytes of weights one decoded token reads (every matrix once, active experts only), the figure
+ * the decode roofline divides by (docs/design.md:15-34). */
+uint64_t bc_model_decode_bytes(const bc_model* model);
+
+/* ============================================================================================
+ * Sequence: the device state of one decode.
+ * Stands in for `Lfm2Metal` (crates/bobcat/src/lfm2_metal.rs:103-762) and `Qwen35Metal`
+ * (crates/bobcat/src/qwen35_metal.rs:112-676).
+ * ============================================================================================ */
+typedef struct bc_seq bc_seq;
+typedef struct bc_checkpoint bc_checkpoint;
+
+/* Buffers that receive activations: lfm2::Trace (lfm2.rs:630-675). Each pointer is nullable as a
+ * group (all three or none); `n_tokens` is the token count the caller sized them for. */
+typedef struct bc_trace {
+    float* embedding;  /* [n_tokens][n_embd] */
+    float* layers;     /* [n_layers][n_tokens][n_embd] */
+    float* final_norm; /* [n_tokens][n_embd] */
+    uint32_t n_tokens;
+} bc_trace;
+
+/* Lfm2Metal::new / Qwen35Metal::new (lfm2_metal.rs:125, qwen35_metal.rs:112). Uploads the model's
+ * weights to the backend's device on first use and shares them between sequences. */
+bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32_t kv_half, bc_seq** out);
+void bc_seq_free(bc_seq* seq);
+/* Qwen35Metal::n_past (qwen35_metal.rs:231). */
+uint32_t bc_seq_n_past(const bc_seq* seq);
+/* step (lfm2_metal.rs:308): `logits` (n_vocab floats) and `trace` (one token) are nullable. */
+bc_status bc_seq_step(bc_seq* seq, uint32_t token, float* logits, size_t logits_len, bc_trace* trace);
+/* prefill (lfm2_metal.rs:662; qwen35_metal.rs:557): `final_norm` (n_embd floats of the last token,
+ * Qwen's extra output) is nullable. */
+bc_status bc_seq_prefill(bc_seq* seq, const uint32_t* tokens, size_t n_tokens, float* logits, size_t logits_len,
+                         float* final_norm, size_t final_norm_len, bc_trace* trace);
+/* greedy_token (lfm2_metal.rs:372). */
+bc_status bc_seq_greedy_token(bc_seq* seq, uint32_t* token);
+/* generate / generate_next (lfm2_metal.rs:401, :411). */
+bc_status bc_seq_generate(bc_seq* seq, uint32_t* out, size_t n);
+bc_status bc_seq_generate_next(bc_seq* seq, uint32_t* out, size_t n);
+/* generate_stream (lfm2_metal.rs:425): `emit` runs on the calling thread and returns nonzero to
+ * continue. `gained` (capacity `gained_cap`) receives the tokens the sequence gained. */
+typedef int32_t (*bc_emit_fn)(uint32_t token, void* user);
+bc_status bc_seq_generate_stream(bc_seq* seq, uint32_t max_tokens, bc_emit_fn emit, void* user, uint32_t* gained,
+                                 size_t gained_cap, size_t* n_gained);
+/* reset / checkpoint / restore (lfm2_metal.rs:238-288; qwen35_metal.rs:238-297). */
+bc_status bc_seq_reset(bc_seq* seq);
+bc_status bc_seq_checkpoint(bc_seq* seq, bc_checkpoint** out);
+bc_status bc_seq_restore(bc_seq* seq, const bc_checkpoint* checkpoint);
+void bc_checkpoint_free(bc_checkpoint* checkpoint);
+/* last_encode_seconds / last_gpu_seconds (lfm2_metal.rs:223-230). */
+bc_status bc_seq_timings(const bc_seq* seq, double* encode_seconds, double* gpu_seconds);
+/* Read back sequence state for tests: which = 0 conv / DeltaNet conv history, 1 K cache, 2 V cache
+ * (as f32), 3 DeltaNet state. `layer` indexes layers of that kind. Returns the float count in
+ * `n` and fills `out` (capacity `cap` floats) when non-null. */
+bc_status bc_seq_read_state(bc_seq* seq, int32_t which, uint32_t layer, float* out, size_t cap, size_t* n);
+/* How many kernels this sequence has launched so far (its own kernels, not library calls). */
+uint64_t bc_seq_launches(const bc_seq* seq);
+
+/* ============================================================================================
+ * GGUF writing, for synthetic model files. No reference counterpart: the reference only reads
+ * GGUF (crates/bobcat-gguf/src/lib.rs); files written here follow the layout that parser checks
+ * (magic, version 3, general.alignment, aligned tensor offsets, whole quant blocks per row).
+ * ============================================================================================ */
+typedef struct bc_gguf_writer bc_gguf_writer;
+/* How a tensor's values are drawn: a normal distribution N(0, std^2) from a counter-based
+ * generator keyed by (seed, tensor order, row) so the bytes do not depend on thread count; a
+ * constant; or -exp(N(0, std^2)) (the stored form of a DeltaNet decay, always negative). */
+enum { BC_INIT_NORMAL = 0, BC_INIT_CONSTANT = 1, BC_INIT_NEG_EXP_NORMAL = 2 };
+
+bc_status bc_gguf_writer_new(const char* path, uint64_t seed, bc_gguf_writer** out);
+bc_status bc_gguf_writer_kv_u32(bc_gguf_writer* w, const char* key, uint32_t value);
+bc_status bc_gguf_writer_kv_f32(bc_gguf_writer* w, const char* key, float value);
+bc_status bc_gguf_writer_kv_str(bc_gguf_writer* w, const char* key, const char* value);
+bc_status bc_gguf_writer_kv_u32_array(bc_gguf_writer* w, const char* key, const uint32_t* values, uint64_t n);
+/* `dims` is innermost-first (ne0 = columns). `type` is BC_F32 or BC_Q4_0 (quantised from the
+ * drawn f32 values with ggml's reference Q4_0 rounding). */
+bc_status bc_gguf_writer_tensor(bc_gguf_writer* w, const char* name, int32_t type, const uint64_t* dims,
+                                uint32_t n_dims, int32_t init, float value);
+/* Draws every tensor (in parallel over rows) and writes the file. Frees the writer. */
+bc_status bc_gguf_writer_finish(bc_gguf_writer* w);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BOBCAT_CUDA_H */
