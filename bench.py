@@ -1,0 +1,309 @@
+"""Benchmark of the decode / prefill path: one JSON line on stdout.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config NAME]
+
+A step is one request in the shape of the reference's own benchmark (crates/bobcat-bench/src/bin/
+bobcat_bench.rs:125-147): reset, prefill a 512-token prompt in one call, then decode 128 tokens
+greedily in one pipelined call. The model is the LFM2.5-2.6B-shaped synthetic Q4_0 file
+(``bobcat_b200.synth``), written to a scratch directory on first use. ``value`` is decode tokens
+per second from CUDA events; prefill tokens per second rides along under ``prefill``.
+
+With N > 1 (launched under torchrun, one rank per GPU) every rank serves its own request replica
+with a distinct prompt; there is no collective on the data path.
+
+``--impl reference`` times the CPU restatement of the reference's scalar path (``oracle/``, all
+host threads) on a bounded sample of the same workload; no GPU work happens on that arm.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PROMPT_TOKENS, DECODE_TOKENS = 512, 128
+METRIC = "decode tok/s, Q4_0 LFM2.5-2.6B-shape, batch 1"
+
+
+def measured_peaks() -> tuple[float, str]:
+    """HBM GB/s to divide by: the measured copy bandwidth of this pool, else the stated fallback."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device = device
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 9:
+                self.rows.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        clocks = [float(r[1]) for r in self.rows if r[1].replace(".", "").isdigit()]
+        max_clock = [float(r[2]) for r in self.rows if r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(clocks)) if clocks else None, "sm_max_mhz": max(max_clock) if max_clock else None,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def rank_info():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+
+
+def prompt_for(n_vocab: int, seed: int) -> np.ndarray:
+    return np.random.default_rng(seed).integers(0, n_vocab, size=PROMPT_TOKENS).astype(np.uint32)
+
+
+def model_file(config: str) -> str:
+    from bobcat_b200 import synth
+    return synth.cached_model(config, seed=0, directory=os.environ.get("BOBCAT_SYNTH_DIR", os.path.join(tempfile.gettempdir(), "bobcat_synth")))
+
+
+def cpu_sample(path: str, n_vocab: int, threads: int, n_prompt: int, n_decode: int) -> tuple[float, float]:
+    """Run the CPU restatement on a short request. Returns (decode tok/s, seconds)."""
+    from oracle import oracle
+    model = oracle.Model(path, threads=threads)
+    state = model.state(n_prompt + n_decode + 1)
+    prompt = prompt_for(n_vocab, 1)[:n_prompt]
+    logits = None
+    for i, tok in enumerate(prompt):
+        logits = state.step(int(tok), want_logits=(i == n_prompt - 1)).get("logits")
+    start = time.perf_counter()
+    for _ in range(n_decode):
+        logits = state.step(int(np.argmax(logits)))["logits"]
+    seconds = time.perf_counter() - start
+    return n_decode / seconds, seconds
+
+
+def run_reference(args) -> None:
+    rank, _, world = rank_info()
+    if rank != 0:
+        return
+    from bobcat_b200 import Model
+    path = model_file(args.config)
+    n_vocab = Model.load(path).hyperparameters().n_vocab
+    threads = len(os.sched_getaffinity(0))
+    n_prompt, n_decode = 4, 4
+    times = []
+    for i in range(args.warmup + args.steps):
+        rate, seconds = cpu_sample(path, n_vocab, threads, n_prompt, n_decode)
+        if i >= args.warmup:
+            times.append(seconds)
+    ms_per_step = 1e3 * float(np.mean(times))
+    value = n_decode / (ms_per_step * 1e-3)
+    sample = "%d-token prompt then %d greedy decode steps of the scalar restatement per step, %d threads over matrix rows" % (n_prompt, n_decode, threads)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (f64 sums)", "data": "synthetic",
+        "config": {"workload": "%s Q4_0, batch 1, decode after a short prompt (bounded sample of the 512+128 request)" % args.config},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def dominant_kernel(cuda, seq, prompt) -> dict:
+    """Time every launch of one more decode pass with CUDA events (profiling mode serialises the
+    launches) and report the kernel with the largest share of the time."""
+    seq.reset()
+    seq.prefill(prompt)
+    cuda.set_profiling(True)
+    seq.generate(16)
+    cuda.set_profiling(False)
+    entries = cuda.profile()
+    total = sum(e["seconds"] for e in entries) or 1.0
+    top = max(entries, key=lambda e: e["seconds"])
+    per_launch_s = top["seconds"] / top["calls"]
+    per_launch_bytes = top["bytes"] / top["calls"]
+    table = sorted(entries, key=lambda e: -e["seconds"])[:8]
+    return {"top": top, "share": top["seconds"] / total, "seconds": per_launch_s, "bytes": per_launch_bytes,
+            "table": [{"kernel": e["name"], "rows": e["n_rows"], "cols": e["n_cols"], "calls": e["calls"], "us": 1e6 * e["seconds"] / e["calls"],
+                       "gbs": (e["bytes"] / e["seconds"] / 1e9) if e["seconds"] else 0.0, "share": e["seconds"] / total} for e in table]}
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from bobcat_b200 import Cuda, Lfm2Cuda, Model
+
+    rank, local_rank, world = rank_info()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    # Rank 0 writes the model file; the others wait for it.
+    if rank == 0:
+        path = model_file(args.config)
+    if world > 1:
+        dist.barrier()
+    path = model_file(args.config)
+
+    model = Model.load(path)
+    hp = model.hyperparameters()
+    # Launch on torch's current stream so torch's events and barriers order with our kernels.
+    stream = torch.cuda.current_stream().cuda_stream
+    cuda = Cuda.open(local_rank, stream if stream else None)
+    n_ctx = PROMPT_TOKENS + DECODE_TOKENS
+    seq = Lfm2Cuda(model, cuda, n_ctx, kv_half=True)
+    prompt = prompt_for(hp.n_vocab, 1 + rank)
+    pinned_prompt = torch.from_numpy(prompt.view(np.int32).copy()).pin_memory()  # the prompt's ids in pinned host memory
+
+    def request():
+        """One request through the public API with host buffers. Returns device and wall seconds."""
+        seq.reset()
+        t0 = time.perf_counter()
+        seq.prefill(pinned_prompt.numpy().view(np.uint32))
+        t1 = time.perf_counter()
+        prefill_gpu = seq.last_gpu_seconds()
+        tokens = seq.generate(DECODE_TOKENS)
+        t2 = time.perf_counter()
+        return prefill_gpu, seq.last_gpu_seconds(), t1 - t0, t2 - t1, tokens
+
+    for _ in range(args.warmup):
+        request()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    launches_before = seq.launches()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    sync_all()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    rows = [request() for _ in range(args.steps)]
+    end.record()
+    sync_all()
+    clocks = sampler.stop() if rank == 0 else None
+    launches = seq.launches() - launches_before
+    total_ms = start.elapsed_time(end)
+
+    prefill_gpu = float(np.mean([r[0] for r in rows]))
+    decode_gpu = float(np.mean([r[1] for r in rows]))
+    prefill_wall = float(np.mean([r[2] for r in rows]))
+    decode_wall = float(np.mean([r[3] for r in rows]))
+    stats = torch.tensor([decode_gpu, prefill_gpu, decode_wall, prefill_wall, total_ms / args.steps], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        launch_count = torch.tensor([launches], dtype=torch.int64, device="cuda")
+        dist.all_reduce(launch_count)
+        launches = int(launch_count.item())
+    decode_gpu, prefill_gpu, decode_wall, prefill_wall, ms_per_step = [float(v) for v in stats.tolist()]
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        weight_bytes = model.decode_bytes()
+        # KV traffic: f16 K and V rows of every attention layer at the mean decode position.
+        kv_bytes = hp.n_attention_layers * 2 * hp.n_kv_heads * hp.head_dim * 2 * (PROMPT_TOKENS + DECODE_TOKENS / 2)
+        token_bytes = weight_bytes + kv_bytes
+        decode_tok_s = world * DECODE_TOKENS / decode_gpu
+        prefill_tok_s = world * PROMPT_TOKENS / prefill_gpu
+        token_hash = 0
+        for tok in rows[-1][4].tolist():
+            token_hash = (token_hash * 1000003 + tok) & 0xFFFFFFFFFFFFFFFF
+        dom = dominant_kernel(cuda, seq, prompt)
+        achieved = dom["bytes"] / dom["seconds"] / 1e9
+        cpu_rate, cpu_seconds = cpu_sample(path, hp.n_vocab, 1, 2, 4) if world == 1 and not args.no_cpu_baseline else (None, None)
+        line = {
+            "metric": METRIC, "value": decode_tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations, Q4_0 weights, f16 KV",
+            "data": "synthetic",
+            "config": {"workload": "%s Q4_0 (random init N(0,0.02), seed 0), batch 1 per GPU, %d-token uniform-random prompt then %d greedy tokens; "
+                                   "%d request replica(s), one per GPU" % (args.config, PROMPT_TOKENS, DECODE_TOKENS, world),
+                       "l2": "every token streams %.2f GB of weights, far larger than the 126 MB L2" % (weight_bytes / 1e9),
+                       "n_ctx": n_ctx, "kv_cache": "f16"},
+            "decode": {"tok_s": decode_tok_s, "tpot_ms": 1e3 * decode_gpu / DECODE_TOKENS, "bytes_per_token": token_bytes,
+                       "hbm_gbs": token_bytes * DECODE_TOKENS / decode_gpu / 1e9, "hbm_frac": token_bytes * DECODE_TOKENS / decode_gpu / 1e9 / peak,
+                       "hbm_frac_of_nominal_8tbs": token_bytes * DECODE_TOKENS / decode_gpu / 8e12, "token_hash": token_hash},
+            "prefill": {"tok_s": prefill_tok_s, "ttft_ms": 1e3 * prefill_gpu, "tokens": PROMPT_TOKENS},
+            "roofline": {"bound": "hbm", "kernel": "%s %dx%d" % (dom["top"]["name"], dom["top"]["n_rows"], dom["top"]["n_cols"]),
+                         "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "share_of_decode": dom["share"], "launch_us": 1e6 * dom["seconds"], "bytes_per_launch": dom["bytes"], "kernels": dom["table"]},
+            "e2e": {"value": world * DECODE_TOKENS / decode_wall, "unit": "tok/s", "h2d_bytes_per_step": PROMPT_TOKENS * 4,
+                    "d2h_bytes_per_step": DECODE_TOKENS * 4, "prefill_tok_s": world * PROMPT_TOKENS / prefill_wall},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        if cpu_rate is not None:
+            line["cpu_baseline"] = {"value": cpu_rate, "unit": "tok/s", "cores": 1, "kind": "port",
+                                    "sample": "2-token prompt then 4 greedy decode steps of the scalar restatement, single thread (%.1f s)" % cpu_seconds}
+        print(json.dumps(line))
+    seq.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=5)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--config", default="lfm2-2.6b")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
