@@ -68,6 +68,7 @@ SIGNATURES = {
     "bc_op_copy": (i32, [vp] + _VIEW + _VIEW + [u32]),
     "bc_op_attention": (i32, [vp] + _VIEW + _VIEW + _VIEW + [i32] + _VIEW + _VIEW + [u32] * 6),
     "bc_attention_scratch_floats": (sz, [u32, u32, u32, u32]),
+    "bc_attention_static": (i32, [vp, vp, vp, vp, i32, vp] + [u32] * 6),
     "bc_op_argmax": (i32, [vp] + _VIEW + _VIEW + [u32]),
     "bc_op_silu_mul": (i32, [vp] + _VIEW + _VIEW + [u32]),
     "bc_model_load": (i32, [C.c_char_p, C.POINTER(vp)]),

@@ -8,6 +8,7 @@
 // unnormalised weighted value sum. Combine pass: one CTA per (query head, query) rescales the
 // chunk partials by exp(max_c - max) and divides.
 
+#include "common.h"
 #include "device_utils.cuh"
 #include "kernels.h"
 
@@ -201,3 +202,55 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
 
 }  // namespace k
 }  // namespace bc
+
+// ------------------------------------------------------------------------------------------------
+// Attention without any allocation.
+//
+// Some embedders may not allocate device memory at all while they decode: an engine whose device
+// memory is one pool planned up front and owned by its own allocator hands a plugin only the
+// tensors of the call, and a serving loop that must not stall cannot afford cudaMalloc, which
+// synchronises the whole device. For them the chunk partials live in the fixed array below, which
+// every GPU that loads this library holds from load until exit.
+// ------------------------------------------------------------------------------------------------
+
+// 2 Mi floats = 8 MiB: enough for one query over 32 heads of 64 elements at 63 000 positions, or a
+// 64-query batch of the same heads at 980 positions.
+#define BC_STATIC_ATTENTION_SCRATCH_FLOATS (2u << 20)
+static __device__ __align__(256) float bc_static_attention_scratch[BC_STATIC_ATTENTION_SCRATCH_FLOATS];
+
+extern "C" bc_status bc_attention_static(void* stream, const float* q, const void* k_cache, const void* v_cache, int32_t kv_half,
+                                         float* out, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t first_pos,
+                                         uint32_t n_queries, uint32_t n_ctx) {
+    using namespace bc;
+    if (!q || !k_cache || !v_cache || !out) return fail(BC_ERR_ARGUMENT, "q, the caches and out must be non-null");
+    if (n_kv_heads == 0 || n_heads % n_kv_heads != 0 || n_heads / n_kv_heads > 8 || head_dim == 0 || head_dim % 32 != 0 || head_dim > 256 ||
+        n_queries == 0 || (uint64_t)first_pos + n_queries > n_ctx)
+        return fail(BC_ERR_ATTENTION_LIMITS,
+                    "attention needs heads of a multiple of 32 up to 256 elements, at most 8 query heads per KV head and queries inside the "
+                    "context, got head_dim %u, %u/%u heads, positions %u..%u of %u",
+                    head_dim, n_heads, n_kv_heads, first_pos, first_pos + n_queries, n_ctx);
+    uint64_t need = k::attention_scratch_floats(n_heads, head_dim, n_ctx, n_queries);
+    if (need > BC_STATIC_ATTENTION_SCRATCH_FLOATS)
+        return fail(BC_ERR_ARGUMENT,
+                    "this shape needs %llu floats of chunk partials and the built-in scratch holds %u; use bc_op_attention with a scratch "
+                    "buffer of your own, or a smaller n_ctx",
+                    (unsigned long long)need, (unsigned)BC_STATIC_ATTENTION_SCRATCH_FLOATS);
+    // The array's name is only a host-side handle; the kernels need its address on the current
+    // device, looked up once per device.
+    static float* address_on_device[64] = {};
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (device < 0 || device >= 64) return fail(BC_ERR_ARGUMENT, "device index %d is outside the table of 64", device);
+    float* scratch = address_on_device[device];
+    if (!scratch) {
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), bc_static_attention_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(bc_static_attention_scratch)");
+        address_on_device[device] = scratch;
+    }
+    k::AttentionShape shape{n_heads, n_kv_heads, head_dim, first_pos, n_queries, n_ctx, n_heads * head_dim, head_dim};
+    e = k::attention(static_cast<cudaStream_t>(stream), q, k_cache, v_cache, kv_half != 0, scratch, out, shape);
+    if (e != cudaSuccess) return cuda_fail(e, "attention");
+    return BC_OK;
+}
+

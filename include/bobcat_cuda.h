@@ -189,6 +189,28 @@ bc_status bc_op_attention(bc_backend* b, bc_buffer* q, size_t q_off, bc_buffer* 
                           uint32_t first_pos, uint32_t n_queries, uint32_t n_ctx);
 /* attention_scratch_floats (backend.rs:2739-2748). */
 size_t bc_attention_scratch_floats(uint32_t n_heads, uint32_t head_dim, uint32_t n_ctx, uint32_t n_queries);
+/* Attention for callers that may not allocate device memory. No counterpart in the reference.
+ *
+ * Who needs it: an embedding engine that plans one device pool up front and gives a plugin only
+ * the tensors of the call, or a serving loop that cannot take the device-wide synchronisation of
+ * cudaMalloc in the middle of a decode. bc_op_attention wants a scratch buffer for its chunk
+ * partials; this variant keeps them in an 8 MiB array built into the library (2 Mi floats, held by
+ * every GPU that loads the library until the process exits) and calls no cudaMalloc, cudaFree or
+ * other allocating routine. Same kernels, same results as bc_op_attention.
+ *
+ * All pointers are device pointers on the current device; `stream` is a cudaStream_t (NULL for the
+ * default stream). q and out are [n_queries][n_heads * head_dim] f32; the caches are
+ * [n_ctx][n_kv_heads * head_dim] f32 or half. Shapes whose partials do not fit
+ * (bc_attention_scratch_floats(...) > 2 Mi) fail with BC_ERR_ARGUMENT and launch nothing.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ * that call with the device current and before starting any stream capture. Every call shares the
+ * one array, which keeps the previous call's contents: the kernels write every partial before they
+ * read it, so nothing needs clearing, but two calls that overlap on the GPU (different streams, or
+ * different threads) race on it. Serialise them. */
+bc_status bc_attention_static(void* stream, const float* q, const void* k_cache, const void* v_cache, int32_t kv_half,
+                              float* out, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t first_pos,
+                              uint32_t n_queries, uint32_t n_ctx);
 /* Metal::argmax (backend.rs:2612-2617): index of the largest of n floats, ties to the lowest. */
 bc_status bc_op_argmax(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* out, size_t out_off, uint32_t n);
 /* Metal::silu_mul (backend.rs:1983-1999): x = silu(gate) * x, elementwise. */
