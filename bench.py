@@ -156,7 +156,7 @@ def dominant_kernel(cuda, seq, prompt) -> dict:
     seq.reset()
     seq.prefill(prompt)
     cuda.set_profiling(True)
-    seq.generate(16)
+    seq.generate(min(16, DECODE_TOKENS))
     cuda.set_profiling(False)
     entries = cuda.profile()
     total = sum(e["seconds"] for e in entries) or 1.0
@@ -193,8 +193,9 @@ def run_ours(args) -> None:
     model = Model.load(path)
     hp = model.hyperparameters()
     # Launch on torch's current stream so torch's events and barriers order with our kernels.
+    torch.cuda.set_stream(torch.cuda.Stream())
     stream = torch.cuda.current_stream().cuda_stream
-    cuda = Cuda.open(local_rank, stream if stream else None)
+    cuda = Cuda.open(local_rank, stream)
     n_ctx = PROMPT_TOKENS + DECODE_TOKENS
     seq = Lfm2Cuda(model, cuda, n_ctx, kv_half=True)
     prompt = prompt_for(hp.n_vocab, 1 + rank)
@@ -290,6 +291,7 @@ def run_ours(args) -> None:
 
 
 def main() -> None:
+    global PROMPT_TOKENS, DECODE_TOKENS
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=5)
@@ -297,7 +299,10 @@ def main() -> None:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--config", default="lfm2-2.6b")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--prompt-tokens", type=int, default=PROMPT_TOKENS, help="shorter requests, for profiler captures only")
+    parser.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS)
     args = parser.parse_args()
+    PROMPT_TOKENS, DECODE_TOKENS = args.prompt_tokens, args.decode_tokens
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

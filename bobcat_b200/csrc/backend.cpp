@@ -188,8 +188,11 @@ bc_status bc_matrix_upload(bc_backend* b, int32_t format, const void* data, uint
     if (n_rows == 0 || n_cols == 0 || n_cols % 32 != 0) return fail(BC_ERR_ARGUMENT, "a matrix has rows of a multiple of 32 columns");
     BC_TRY(b->activate());
     uint64_t raw_bytes = (uint64_t)n_rows * type_row_bytes((uint32_t)format, n_cols);
+    // Q4_0 matrices also get the tile layout of the tensor-core decode kernel, after the split one.
+    const bool tiled = format == BC_Q4_0 && k::tiles_supported(n_cols);
+    const uint64_t split_bytes = round_up(raw_bytes, 256);
     bc_buffer* buffer = nullptr;
-    BC_TRY(bc_buffer_new(b, raw_bytes, &buffer));
+    BC_TRY(bc_buffer_new(b, tiled ? split_bytes + k::tiles_bytes(n_rows, n_cols) : raw_bytes, &buffer));
     buffer->is_matrix = true;
     buffer->matrix.format = format;
     buffer->matrix.n_rows = n_rows;
@@ -206,6 +209,11 @@ bc_status bc_matrix_upload(bc_backend* b, int32_t format, const void* data, uint
         if (status == BC_OK && (e = k::repack_q4_0(b->stream, static_cast<const uint8_t*>(raw), n_blocks, buffer->ptr,
                                                     const_cast<__half*>(buffer->matrix.scales))) != cudaSuccess)
             status = cuda_fail(e, "repack_q4_0");
+        if (status == BC_OK && tiled) {
+            buffer->matrix.tiles = static_cast<char*>(buffer->ptr) + split_bytes;
+            if ((e = k::repack_tiles(b->stream, buffer->ptr, buffer->matrix.scales, n_rows, n_cols, const_cast<void*>(buffer->matrix.tiles))) != cudaSuccess)
+                status = cuda_fail(e, "repack_tiles");
+        }
         if (status == BC_OK && (e = cudaStreamSynchronize(b->stream)) != cudaSuccess) status = cuda_fail(e, "repack_q4_0");
         if (raw) cudaFree(raw);
     } else {
@@ -427,7 +435,7 @@ bc_status bc_op_embed(bc_backend* b, int32_t format, bc_buffer* weights, size_t 
     BC_TRY(check_range(b, tokens, tok_off, (size_t)n_tokens * 4, "embed"));
     BC_TRY(check_range(b, out, out_off, (size_t)n_tokens * n_embd * 4, "embed"));
     return b->run("embed", n_tokens, n_embd, 0, 1, [&] {
-        return k::embed(b->stream, w, reinterpret_cast<const uint32_t*>(at(tokens, tok_off)), reinterpret_cast<float*>(at(out, out_off)),
+        return k::embed(b->stream, w, reinterpret_cast<const uint32_t*>(at(tokens, tok_off)), k::Pos{}, reinterpret_cast<float*>(at(out, out_off)),
                         n_tokens);
     });
 }

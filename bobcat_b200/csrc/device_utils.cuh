@@ -12,6 +12,14 @@ namespace k {
 
 constexpr int kWarpSize = 32;
 
+// Programmatic dependent launch. `pdl_launch_dependents` lets the next launch of the stream begin
+// while this grid still runs; `pdl_wait` blocks until every launch before this one has finished
+// and its writes are visible. Both do nothing in a launch made without the attribute. A kernel
+// launched with the attribute must call pdl_wait before it touches anything an earlier launch
+// wrote or will read, which is what keeps a chain of such launches ordered.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -20,6 +20,9 @@ struct Mat {
     int32_t format = 0;
     const void* data = nullptr;
     const __half* scales = nullptr;
+    // Q4_0 only, optional: the same values in the 16-row tile layout the tensor-core decode kernel
+    // streams (see kernels_matvec_mma.cu). Null when the matrix has no such copy.
+    const void* tiles = nullptr;
     uint32_t n_rows = 0, n_cols = 0;
     // Rows [first, first + rows) of this matrix.
     Mat rows(uint32_t first, uint32_t count) const;
@@ -37,6 +40,11 @@ struct MatvecSegment {
     float* y = nullptr;
 };
 
+// Launch `kernel` with the programmatic-dependent-launch attribute (unless BOBCAT_NO_PDL=1), so it
+// may start while the launch before it still runs. Only for kernels that call pdl_wait() before
+// touching memory other launches write. `args` is the usual array of pointers to the arguments.
+cudaError_t launch_kernel(const void* kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, void** args);
+bool pdl_enabled();
 // Raise `kernel`'s dynamic shared-memory limit to `smem` bytes on the current device if needed.
 cudaError_t ensure_dynamic_smem(const void* kernel, size_t smem);
 // Number of SMs of the current device.
@@ -45,6 +53,22 @@ int sm_count();
 // Repack GGUF Q4_0 bytes (18-byte blocks) already on the device into the split layout.
 cudaError_t repack_q4_0(cudaStream_t stream, const uint8_t* raw, uint64_t n_blocks, void* quants, __half* scales);
 
+// The tile layout of a Q4_0 matrix: its size, whether this width has one, and the conversion from
+// the split layout (both already on the device).
+uint64_t tiles_bytes(uint32_t n_rows, uint32_t n_cols);
+bool tiles_supported(uint32_t n_cols);
+cudaError_t repack_tiles(cudaStream_t stream, const void* quants, const __half* scales, uint32_t n_rows, uint32_t n_cols, void* tiles);
+// The tensor-core decode kernels; every matrix must carry `tiles`. matvec / matvec_swiglu /
+// matvec_conv below pick them when they can.
+cudaError_t matvec_mma(cudaStream_t stream, const MatvecSegment* segments, int n_segments, const float* x, Norm norm, bool accumulate);
+cudaError_t matvec_swiglu_mma(cudaStream_t stream, const Mat& gate, const Mat& up, const float* x, Norm norm, float* y);
+cudaError_t matvec_conv_mma(cudaStream_t stream, const Mat& in_proj, const float* x, Norm norm, const float* taps, float* history,
+                            float* out, uint32_t n_embd, uint32_t kernel);
+cudaError_t matvec_mma_prepare(uint32_t widest_cols);
+// Nonzero once a bounded wait inside a kernel gave up (1: a ring slot never freed, 2: a chunk never arrived).
+int matvec_error_flag();
+// Raise the shared-memory limit of every matvec kernel for input vectors of up to `widest_cols`.
+cudaError_t matvec_prepare(uint32_t widest_cols);
 cudaError_t matvec(cudaStream_t stream, const MatvecSegment* segments, int n_segments, const float* x, Norm norm,
                    bool accumulate);
 cudaError_t matvec_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, const float* x, Norm norm, float* y);
@@ -53,7 +77,36 @@ cudaError_t matvec_conv(cudaStream_t stream, const Mat& in_proj, const float* x,
 cudaError_t short_conv(cudaStream_t stream, const float* bcx, const float* taps, float* history, float* out,
                        uint32_t n_embd, uint32_t kernel, uint32_t n_tokens);
 cudaError_t expand(cudaStream_t stream, const Mat& w, void* out, bool out_half);
-cudaError_t embed(cudaStream_t stream, const Mat& w, const uint32_t* tokens, float* out, uint32_t n_tokens);
+// A position that is either immediate or read from device memory at run time (`*ptr + value`), so
+// one captured launch sequence can be replayed at every position of a decode.
+struct Pos {
+    const uint32_t* ptr = nullptr;
+    uint32_t value = 0;
+};
+// `tokens + pos` names the first token id.
+cudaError_t embed(cudaStream_t stream, const Mat& w, const uint32_t* tokens, Pos pos, float* out, uint32_t n_tokens);
+// Decode-time fusion of the three per-token stores of an attention layer: per-head RMSNorm and
+// rotation of q in place; the same for k, stored into the cache row of `pos`; v copied (or rounded
+// to half) into its cache row. Caches point at the layer's first row.
+struct RopeStore {
+    float* q;
+    const float* k;
+    const float* v;
+    void* k_cache;
+    void* v_cache;
+    const float* q_norm;
+    const float* k_norm;
+    uint32_t n_heads, n_kv_heads, head_dim, q_head_stride, n_rot;
+    float theta, eps;
+    bool kv_half;
+};
+cudaError_t rope_store(cudaStream_t stream, const RopeStore& p, Pos pos);
+// One thread: *counter += 1.
+cudaError_t advance(cudaStream_t stream, uint32_t* counter);
+// argmax for a replayed decode: pos = *counter (after adding 1 to it when `advance`), then
+// tokens[pos + offset] = argmax(x) and, when `ring` is non-null, ring[pos % ring_slots] too.
+cudaError_t argmax_step(cudaStream_t stream, const float* x, uint32_t n, uint32_t* counter, bool advance, uint32_t* tokens,
+                        uint32_t offset, uint32_t* ring, uint32_t ring_slots);
 cudaError_t rms_norm(cudaStream_t stream, const float* x, const float* weight, float* out, uint32_t n_cols,
                      uint32_t n_rows, float eps);
 cudaError_t norm_rope(cudaStream_t stream, const float* src, void* dst, bool dst_half, const float* weight,
@@ -70,6 +123,7 @@ cudaError_t silu_mul(cudaStream_t stream, float* x, const float* gate, uint64_t 
 struct AttentionShape {
     uint32_t n_heads, n_kv_heads, head_dim, first_pos, n_queries, n_ctx;
     uint32_t q_stride, q_head_stride;
+    const uint32_t* pos_ptr = nullptr;  // when set, first_pos is *pos_ptr + first_pos and the grid covers n_ctx
 };
 uint64_t attention_scratch_floats(uint32_t n_heads, uint32_t head_dim, uint32_t n_ctx, uint32_t n_queries);
 cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, const void* v_cache, bool kv_half,

@@ -37,14 +37,17 @@ struct ChunkParams {
     uint32_t n_heads, n_kv_heads, head_dim, first_pos, n_ctx, q_stride, q_head_stride;
     uint32_t query0;      // first query of this launch
     uint32_t max_chunks;  // chunks the scratch holds per (query, head)
+    const uint32_t* pos_ptr;  // when set, added to first_pos at run time
 };
 
 // Scratch layout: [query in batch][head][chunk][head_dim + 2] = (max, sum, acc[head_dim]).
 template <typename T>
 __global__ void __launch_bounds__(kChunkThreads) attention_chunk_kernel(ChunkParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t kv_head = blockIdx.x, chunk = blockIdx.y, qi = blockIdx.z;
     const uint32_t query = p.query0 + qi;
-    const uint32_t pos = p.first_pos + query;  // the query attends to positions 0..pos
+    const uint32_t pos = p.first_pos + (p.pos_ptr ? *p.pos_ptr : 0u) + query;  // the query attends to positions 0..pos
     const uint32_t start = chunk * kChunk;
     if (start > pos) return;
     const uint32_t count = min((uint32_t)kChunk, pos + 1 - start);
@@ -145,12 +148,15 @@ struct CombineParams {
     const float* scratch;
     float* out;
     uint32_t n_heads, head_dim, first_pos, query0, max_chunks;
+    const uint32_t* pos_ptr;
 };
 
 // grid (n_heads, queries in batch), head_dim threads.
 __global__ void attention_combine_kernel(CombineParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t head = blockIdx.x, qi = blockIdx.y, d = threadIdx.x;
-    const uint32_t query = p.query0 + qi, pos = p.first_pos + query;
+    const uint32_t query = p.query0 + qi, pos = p.first_pos + (p.pos_ptr ? *p.pos_ptr : 0u) + query;
     const uint32_t n_chunks = pos / kChunk + 1, hd = p.head_dim;
     const float* base = p.scratch + ((uint64_t)qi * p.n_heads + head) * p.max_chunks * (hd + 2);
     float m = -INFINITY;
@@ -188,14 +194,15 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
         uint32_t nq = s.n_queries - q0 < (uint32_t)kQueryBatch ? s.n_queries - q0 : (uint32_t)kQueryBatch;
         uint32_t last_pos = s.first_pos + q0 + nq - 1;
         ChunkParams cp{q, k_cache, v_cache, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.first_pos, s.n_ctx,
-                       s.q_stride, s.q_head_stride, q0, max_chunks};
-        dim3 grid(s.n_kv_heads, last_pos / kChunk + 1, nq);
-        if (kv_half) attention_chunk_kernel<__half><<<grid, kChunkThreads, smem, stream>>>(cp);
-        else attention_chunk_kernel<float><<<grid, kChunkThreads, smem, stream>>>(cp);
-        if ((e = cudaGetLastError()) != cudaSuccess) return e;
-        CombineParams mp{scratch, out, s.n_heads, s.head_dim, s.first_pos, q0, max_chunks};
-        attention_combine_kernel<<<dim3(s.n_heads, nq), s.head_dim, 0, stream>>>(mp);
-        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+                       s.q_stride, s.q_head_stride, q0, max_chunks, s.pos_ptr};
+        // With a run-time position the grid covers every chunk of the context; CTAs past the position exit at once.
+        dim3 grid(s.n_kv_heads, s.pos_ptr ? max_chunks : last_pos / kChunk + 1, nq);
+        void* chunk_args[] = {&cp};
+        const void* chunk_kernel = kv_half ? (const void*)attention_chunk_kernel<__half> : (const void*)attention_chunk_kernel<float>;
+        if ((e = launch_kernel(chunk_kernel, grid, dim3(kChunkThreads), smem, stream, chunk_args)) != cudaSuccess) return e;
+        CombineParams mp{scratch, out, s.n_heads, s.head_dim, s.first_pos, q0, max_chunks, s.pos_ptr};
+        void* combine_args[] = {&mp};
+        if ((e = launch_kernel((const void*)attention_combine_kernel, dim3(s.n_heads, nq), dim3(s.head_dim), 0, stream, combine_args)) != cudaSuccess) return e;
     }
     return cudaSuccess;
 }

@@ -1,16 +1,25 @@
 // Decode-time matrix-vector kernels: y = W x with optional fused RMSNorm of x, residual
 // accumulate, SwiGLU of a gate/up pair, and the LFM2 gated short convolution.
 //
-// Shape of every kernel here: a CTA stages the input vector once in shared memory (multiplied by
-// the norm weight when a norm is fused, with the sum of squares reduced on the way), then its warps
-// walk rows. A lane owns whole 32-weight blocks: one 128-bit load brings a block's quants, the
-// block's 32 inputs come from shared memory once and are reused for every row the warp has in
-// flight, and the block's scale multiplies the finished block sum. A warp's loads are contiguous
-// 512-byte runs of the weight stream, which is the only HBM traffic that matters here.
+// One kernel template serves all of them. A CTA stages the input vector once in shared memory
+// (multiplied by the norm weight when a norm is fused, with the sum of squares reduced on the
+// way), then its warps walk "units" of two or three rows that share the staged input. A lane owns
+// whole 32-weight blocks: one 128-bit load brings a block's quants, the block's 32 inputs come from
+// shared memory once and are reused for every row of the unit, and the block's scale multiplies the
+// finished block sum. A warp's loads are contiguous 512-byte runs of the weight stream. Rows too
+// wide for one warp to finish quickly are split across 2, 4 or 8 warps whose partial sums meet in
+// shared memory.
+//
+// A decode step is a chain of such launches, each depending on the one before through a few
+// kilobytes of activations, while the weights - the only real HBM traffic - depend on nothing. So
+// every kernel here is written for programmatic dependent launch: it first lets its successor
+// start, then asks the L2 to fetch the weights its CTA will read, and only then waits for its
+// predecessor's results. The weight stream of launch N+1 overlaps the tail of launch N.
 //
 // Counterparts in the reference: matvec_k / matvec_q / swiglu_rows / matvec_conv in
 // crates/bobcat-metal/src/matvec.metal:151-585, lane layout q4_0_lanes in quant.metal:587-656.
 
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <utility>
@@ -26,6 +35,10 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
+// Bytes of weights one CTA asks the L2 to fetch ahead of its dependency wait.
+constexpr uint32_t kPrefetchCap = 96 * 1024;
+
+enum Mode { kPlain = 0, kSwiglu = 1, kConv = 2 };
 
 struct RowPtr {
     const void* data;      // first byte of the row's weights
@@ -46,6 +59,22 @@ __device__ __forceinline__ RowPtr row_of(const Mat& m, uint32_t row) {
         p.scales = nullptr;
     }
     return p;
+}
+
+// Ask the L2 to fetch [p, p + bytes); both must be multiples of 16.
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+template <int FORMAT>
+__device__ __forceinline__ void prefetch_row(const RowPtr& r, uint32_t n_cols) {
+    if (FORMAT == BC_Q4_0) {
+        uint32_t nb = n_cols >> 5;
+        prefetch_l2(r.data, nb * 16);
+        if ((reinterpret_cast<uintptr_t>(r.scales) & 15) == 0 && (nb & 7) == 0) prefetch_l2(r.scales, nb * 2);
+    } else {
+        prefetch_l2(r.data, n_cols * (FORMAT == BC_F16 ? 2u : 4u));
+    }
 }
 
 // Stage x into shared memory in the rotated chunk layout, times the norm weight when given.
@@ -74,16 +103,18 @@ __device__ float stage_input(const float* __restrict__ x, const float* __restric
     return scale;
 }
 
-// Partial dot products of R rows with the staged input, for this lane's share of the columns.
+// Partial dot products of R rows with the staged input over this warp's share of the columns:
+// part `kpart` of `ksplit` interleaved parts, each a stride of 32 lanes.
 template <int FORMAT, int R>
 __device__ __forceinline__ void dot_rows(const RowPtr (&rows)[R], uint32_t n_cols, const float4* __restrict__ xs, int lane,
-                                         float (&acc)[R]) {
+                                         int kpart, int ksplit, float (&acc)[R]) {
 #pragma unroll
     for (int r = 0; r < R; ++r) acc[r] = 0.f;
+    const int step = 32 * ksplit;
     if (FORMAT == BC_Q4_0) {
         const int nb = n_cols >> 5;
 #pragma unroll 2
-        for (int b0 = 0; b0 < nb; b0 += 32) {
+        for (int b0 = kpart * 32; b0 < nb; b0 += step) {
             int b = b0 + lane;
             bool live = b < nb;
             int bc_ = live ? b : nb - 1;
@@ -116,7 +147,7 @@ __device__ __forceinline__ void dot_rows(const RowPtr (&rows)[R], uint32_t n_col
     } else if (FORMAT == BC_F32) {
         const int nc = n_cols >> 2;
 #pragma unroll 4
-        for (int c0 = 0; c0 < nc; c0 += 32) {
+        for (int c0 = kpart * 32; c0 < nc; c0 += step) {
             int c = c0 + lane;
             bool live = c < nc;
             int cc = live ? c : nc - 1;
@@ -131,7 +162,7 @@ __device__ __forceinline__ void dot_rows(const RowPtr (&rows)[R], uint32_t n_col
     } else {  // BC_F16
         const int nc = n_cols >> 3;
 #pragma unroll 2
-        for (int c0 = 0; c0 < nc; c0 += 32) {
+        for (int c0 = kpart * 32; c0 < nc; c0 += step) {
             int c = c0 + lane;
             bool live = c < nc;
             int cc = live ? c : nc - 1;
@@ -154,32 +185,35 @@ __device__ __forceinline__ void dot_rows(const RowPtr (&rows)[R], uint32_t n_col
     for (int r = 0; r < R; ++r) acc[r] = warp_sum(acc[r]);
 }
 
-struct MatvecParams {
+struct Params {
+    // kPlain: up to three matrices that share x; kSwiglu: seg[0] = gate, seg[1] = up;
+    // kConv: seg[0] = in_proj.
     MatvecSegment seg[3];
     int n_segments;
-    uint32_t total_rows;
+    uint32_t total_rows;  // kPlain: rows over all segments
+    uint32_t units;       // kPlain: row pairs; kSwiglu: rows; kConv: channels
+    int ksplit;           // warps that share one unit: 1, 2, 4 or 8
+    uint32_t prefetch_bytes;  // weight bytes each CTA asks the L2 for ahead of its dependency wait
     const float* x;
     const float* norm_weight;
     float eps;
     int accumulate;
+    // kConv
+    const float* taps;
+    float* history;
+    uint32_t n_embd, conv_kernel;
 };
 
-template <int FORMAT>
-__global__ void __launch_bounds__(kThreads) matvec_kernel(MatvecParams p) {
-    extern __shared__ float4 xs[];
-    __shared__ float reduce_scratch[32];
-    const uint32_t n_cols = p.seg[0].w.n_cols;
-    float scale = stage_input(p.x, p.norm_weight, p.eps, n_cols, xs, reduce_scratch);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    constexpr int R = 2;
-    // Row pairs are dealt round-robin to warps across the grid.
-    const uint32_t n_pairs = (p.total_rows + R - 1) / R;
-    for (uint32_t pair = blockIdx.x * kWarps + warp; pair < n_pairs; pair += gridDim.x * kWarps) {
-        RowPtr rows[R];
-        float* out[R];
+template <int MODE>
+__device__ __forceinline__ constexpr int rows_per_unit() { return MODE == kConv ? 3 : 2; }
+
+// The rows of unit `unit` (clamped into range by the caller) and, for kPlain, where each result goes.
+template <int MODE>
+__device__ __forceinline__ void unit_rows(const Params& p, uint32_t unit, RowPtr (&rows)[rows_per_unit<MODE>()], float* (&out)[rows_per_unit<MODE>()]) {
+    if (MODE == kPlain) {
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            uint32_t row = pair * R + r;
+        for (int r = 0; r < 2; ++r) {
+            uint32_t row = unit * 2 + r;
             bool valid = row < p.total_rows;
             if (!valid) row = p.total_rows - 1;
             int s = 0;
@@ -191,81 +225,104 @@ __global__ void __launch_bounds__(kThreads) matvec_kernel(MatvecParams p) {
             rows[r] = row_of(p.seg[s].w, local);
             out[r] = valid ? p.seg[s].y + local : nullptr;
         }
+    } else if (MODE == kSwiglu) {
+        rows[0] = row_of(p.seg[0].w, unit);
+        rows[1] = row_of(p.seg[1].w, unit);
+        out[0] = p.seg[0].y + unit;
+        out[1] = nullptr;
+    } else {
+        rows[0] = row_of(p.seg[0].w, unit);
+        rows[1] = row_of(p.seg[0].w, p.n_embd + unit);
+        rows[2] = row_of(p.seg[0].w, 2 * p.n_embd + unit);
+        out[0] = p.seg[0].y + unit;
+        out[1] = out[2] = nullptr;
+    }
+}
+
+template <int FORMAT, int MODE>
+__global__ void __launch_bounds__(kThreads) matvec_kernel(Params p) {
+    constexpr int R = rows_per_unit<MODE>();
+    extern __shared__ float4 xs[];
+    __shared__ float reduce_scratch[32];
+    __shared__ float partial[2][kWarps][3];
+    const uint32_t n_cols = p.seg[0].w.n_cols;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ksplit = p.ksplit, units_per_pass = kWarps / ksplit;
+    const int kpart = warp % ksplit, slot = warp / ksplit;
+
+    // Let the next launch of the stream start, fetch this CTA's weights toward the L2, and only
+    // then wait for the launches before this one: their results (x, and y when accumulating) are
+    // first touched below the wait.
+    pdl_launch_dependents();
+    {
+        const uint32_t row_bytes = FORMAT == BC_Q4_0 ? (n_cols >> 5) * 18 : n_cols * (FORMAT == BC_F16 ? 2u : 4u);
+        const uint32_t rows_per_pass = (uint32_t)units_per_pass * R;
+        uint32_t max_rows = p.prefetch_bytes / (row_bytes ? row_bytes : 1);
+        for (uint32_t t = threadIdx.x; t < max_rows; t += blockDim.x) {
+            uint32_t pass = t / rows_per_pass, within = t % rows_per_pass;
+            uint64_t unit = ((uint64_t)blockIdx.x + (uint64_t)pass * gridDim.x) * units_per_pass + within / R;
+            if (unit >= p.units) break;
+            RowPtr rows[R];
+            float* out[R];
+            unit_rows<MODE>(p, (uint32_t)unit, rows, out);
+            prefetch_row<FORMAT>(rows[within % R], n_cols);
+        }
+    }
+    pdl_wait();
+
+    const float scale = stage_input(p.x, p.norm_weight, p.eps, n_cols, xs, reduce_scratch);
+    int parity = 0;
+    for (uint64_t first = (uint64_t)blockIdx.x * units_per_pass; first < p.units; first += (uint64_t)gridDim.x * units_per_pass) {
+        uint64_t wanted = first + slot;
+        const bool valid = wanted < p.units;
+        const uint32_t unit = valid ? (uint32_t)wanted : p.units - 1;
+        RowPtr rows[R];
+        float* out[R];
+        unit_rows<MODE>(p, unit, rows, out);
         float acc[R];
-        dot_rows<FORMAT, R>(rows, n_cols, xs, lane, acc);
-        if (lane == 0) {
+        dot_rows<FORMAT, R>(rows, n_cols, xs, lane, kpart, ksplit, acc);
+        if (ksplit > 1) {
+            if (lane == 0) {
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                if (out[r]) {
-                    float v = acc[r] * scale;
-                    *out[r] = p.accumulate ? *out[r] + v : v;
+                for (int r = 0; r < R; ++r) partial[parity][warp][r] = acc[r];
+            }
+            __syncthreads();
+            if (kpart == 0) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    float total = 0.f;
+                    for (int kk = 0; kk < ksplit; ++kk) total += partial[parity][warp + kk][r];
+                    acc[r] = total;
                 }
             }
+            parity ^= 1;
         }
-    }
-}
-
-struct SwigluParams {
-    Mat gate, up;
-    const float* x;
-    const float* norm_weight;
-    float eps;
-    float* y;
-};
-
-template <int FORMAT>
-__global__ void __launch_bounds__(kThreads) matvec_swiglu_kernel(SwigluParams p) {
-    extern __shared__ float4 xs[];
-    __shared__ float reduce_scratch[32];
-    const uint32_t n_cols = p.gate.n_cols, n_rows = p.gate.n_rows;
-    float scale = stage_input(p.x, p.norm_weight, p.eps, n_cols, xs, reduce_scratch);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (uint32_t row = blockIdx.x * kWarps + warp; row < n_rows; row += gridDim.x * kWarps) {
-        RowPtr rows[2] = {row_of(p.gate, row), row_of(p.up, row)};
-        float acc[2];
-        dot_rows<FORMAT, 2>(rows, n_cols, xs, lane, acc);
-        if (lane == 0) {
-            float g = acc[0] * scale, u = acc[1] * scale;
-            p.y[row] = g / (1.f + expf(-g)) * u;
-        }
-    }
-}
-
-struct ConvParams {
-    Mat in_proj;
-    const float* x;
-    const float* norm_weight;
-    float eps;
-    const float* taps;
-    float* history;
-    float* out;
-    uint32_t n_embd, kernel;
-};
-
-// One warp per channel: rows ch, n_embd + ch and 2 n_embd + ch of in_proj give B, C and X; lane 0
-// then runs the taps over B*X and the channel's history, shifts the history and writes C * conv
-// (the arithmetic of crates/bobcat/src/lfm2.rs:456-475 with f32 sums).
-template <int FORMAT>
-__global__ void __launch_bounds__(kThreads) matvec_conv_kernel(ConvParams p) {
-    extern __shared__ float4 xs[];
-    __shared__ float reduce_scratch[32];
-    const uint32_t n_cols = p.in_proj.n_cols;
-    float scale = stage_input(p.x, p.norm_weight, p.eps, n_cols, xs, reduce_scratch);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (uint32_t ch = blockIdx.x * kWarps + warp; ch < p.n_embd; ch += gridDim.x * kWarps) {
-        RowPtr rows[3] = {row_of(p.in_proj, ch), row_of(p.in_proj, p.n_embd + ch), row_of(p.in_proj, 2 * p.n_embd + ch)};
-        float acc[3];
-        dot_rows<FORMAT, 3>(rows, n_cols, xs, lane, acc);
-        if (lane == 0) {
-            float b = acc[0] * scale, c = acc[1] * scale, xv = acc[2] * scale;
-            float bx = b * xv;
-            const float* taps = p.taps + (uint64_t)ch * p.kernel;
-            float sum = taps[p.kernel - 1] * bx;
-            for (uint32_t kk = 0; kk + 1 < p.kernel; ++kk) sum += taps[kk] * p.history[(uint64_t)kk * p.n_embd + ch];
-            for (uint32_t kk = 0; kk + 2 < p.kernel; ++kk)
-                p.history[(uint64_t)kk * p.n_embd + ch] = p.history[(uint64_t)(kk + 1) * p.n_embd + ch];
-            p.history[(uint64_t)(p.kernel - 2) * p.n_embd + ch] = bx;
-            p.out[ch] = c * sum;
+        if (lane == 0 && kpart == 0 && valid) {
+            if (MODE == kPlain) {
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    if (out[r]) {
+                        float v = acc[r] * scale;
+                        *out[r] = p.accumulate ? *out[r] + v : v;
+                    }
+                }
+            } else if (MODE == kSwiglu) {
+                float g = acc[0] * scale, u = acc[1] * scale;
+                *out[0] = g / (1.f + expf(-g)) * u;
+            } else {
+                // Rows ch, n_embd + ch and 2 n_embd + ch of in_proj gave B, C and X; run the taps over
+                // B*X and the channel's history, shift the history, write C * conv (the arithmetic
+                // of crates/bobcat/src/lfm2.rs:456-475 with f32 sums).
+                float b = acc[0] * scale, c = acc[1] * scale, xv = acc[2] * scale;
+                float bx = b * xv;
+                const uint32_t ch = unit, K = p.conv_kernel;
+                const float* taps = p.taps + (uint64_t)ch * K;
+                float sum = taps[K - 1] * bx;
+                for (uint32_t kk = 0; kk + 1 < K; ++kk) sum += taps[kk] * p.history[(uint64_t)kk * p.n_embd + ch];
+                for (uint32_t kk = 0; kk + 2 < K; ++kk) p.history[(uint64_t)kk * p.n_embd + ch] = p.history[(uint64_t)(kk + 1) * p.n_embd + ch];
+                p.history[(uint64_t)(K - 2) * p.n_embd + ch] = bx;
+                *out[0] = c * sum;
+            }
         }
     }
 }
@@ -281,7 +338,65 @@ int sm_count_impl() {
     return count;
 }
 
+// How many warps share a unit: split rows that would take one warp more than three trips when the
+// launch has too few units to fill the machine anyway.
+int choose_ksplit(int format, uint32_t n_cols, uint64_t units) {
+    uint32_t per_trip = format == BC_Q4_0 ? 1024 : format == BC_F16 ? 256 : 128;
+    uint32_t trips = (n_cols + per_trip - 1) / per_trip;
+    if (units >= (uint64_t)sm_count_impl() * kWarps * 2) return 1;
+    int ksplit = 1;
+    while (ksplit < kWarps && (trips + ksplit - 1) / ksplit > 3) ksplit *= 2;
+    return ksplit;
+}
+
+template <int MODE>
+const void* kernel_for(int format) {
+    switch (format) {
+        case BC_Q4_0: return (const void*)matvec_kernel<BC_Q4_0, MODE>;
+        case BC_F16: return (const void*)matvec_kernel<BC_F16, MODE>;
+        default: return (const void*)matvec_kernel<BC_F32, MODE>;
+    }
+}
+
+cudaError_t launch(const void* kernel, cudaStream_t stream, Params& p) {
+    size_t smem = (size_t)p.seg[0].w.n_cols * 4;
+    cudaError_t e = ensure_dynamic_smem(kernel, smem);
+    if (e != cudaSuccess) return e;
+    p.ksplit = choose_ksplit(p.seg[0].w.format, p.seg[0].w.n_cols, p.units);
+    uint64_t per_cta = (uint64_t)(kWarps / p.ksplit);
+    uint64_t ctas = (p.units + per_cta - 1) / per_cta;
+    uint64_t cap = (uint64_t)sm_count_impl() * 8;
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
+    // Keep the whole launch's prefetch well inside the L2.
+    uint64_t budget = (48ull << 20) / ctas;
+    p.prefetch_bytes = (uint32_t)(budget < kPrefetchCap ? budget : kPrefetchCap);
+    void* args[] = {&p};
+    return launch_kernel(kernel, dim3((unsigned)ctas), dim3(kThreads), smem, stream, args);
+}
+
+bool g_pdl = [] {
+    const char* v = getenv("BOBCAT_NO_PDL");
+    return !(v && v[0] == '1');
+}();
+
 }  // namespace
+
+bool pdl_enabled() { return g_pdl; }
+
+cudaError_t launch_kernel(const void* kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, void** args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = g_pdl ? 1 : 0;
+    return cudaLaunchKernelExC(&config, kernel, args);
+}
 
 // Raise a kernel's dynamic shared-memory limit when a launch needs more than the 48 KB default.
 // The setting is per device and per function; remember what was granted so steady-state launches
@@ -300,25 +415,6 @@ cudaError_t ensure_dynamic_smem(const void* kernel, size_t smem) {
     return e;
 }
 
-namespace {
-
-template <typename Kernel>
-cudaError_t prepare(Kernel kernel, size_t smem) {
-    return ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
-}
-
-// CTAs for `units` warp-sized pieces of work: enough to fill the machine a few times over, never
-// more than the work.
-int grid_for(uint64_t units) {
-    uint64_t ctas = (units + kWarps - 1) / kWarps;
-    uint64_t cap = (uint64_t)sm_count_impl() * 8;
-    if (ctas > cap) ctas = cap;
-    if (ctas < 1) ctas = 1;
-    return (int)ctas;
-}
-
-}  // namespace
-
 int sm_count() { return sm_count_impl(); }
 
 Mat Mat::rows(uint32_t first, uint32_t count) const {
@@ -328,6 +424,8 @@ Mat Mat::rows(uint32_t first, uint32_t count) const {
         uint64_t nb = n_cols >> 5;
         m.data = static_cast<const uint4*>(data) + first * nb;
         m.scales = scales + first * nb;
+        // Tiles hold 16 rows each, so only a tile-aligned row range keeps its tile copy.
+        m.tiles = (tiles && first % 16 == 0) ? static_cast<const uint8_t*>(tiles) + (uint64_t)(first / 16) * nb * 288 : nullptr;
     } else if (format == BC_F16) {
         m.data = static_cast<const __half*>(data) + (uint64_t)first * n_cols;
     } else {
@@ -343,82 +441,68 @@ uint64_t Mat::bytes() const {
     return n * 4;
 }
 
+cudaError_t matvec_prepare(uint32_t widest_cols) {
+    size_t smem = (size_t)widest_cols * 4;
+    cudaError_t prepared = matvec_mma_prepare(widest_cols);
+    if (prepared != cudaSuccess) return prepared;
+    for (int format : {BC_Q4_0, BC_F16, BC_F32}) {
+        for (const void* kernel : {kernel_for<kPlain>(format), kernel_for<kSwiglu>(format), kernel_for<kConv>(format)}) {
+            cudaError_t e = ensure_dynamic_smem(kernel, smem);
+            if (e != cudaSuccess) return e;
+        }
+    }
+    return cudaSuccess;
+}
+
 cudaError_t matvec(cudaStream_t stream, const MatvecSegment* segments, int n_segments, const float* x, Norm norm,
                    bool accumulate) {
-    MatvecParams p{};
+    bool tiled = segments[0].w.format == BC_Q4_0;
+    for (int i = 0; i < n_segments; ++i) tiled = tiled && segments[i].w.tiles != nullptr;
+    if (tiled) return matvec_mma(stream, segments, n_segments, x, norm, accumulate);
+    Params p{};
     p.n_segments = n_segments;
-    p.total_rows = 0;
     for (int i = 0; i < n_segments; ++i) {
         p.seg[i] = segments[i];
         p.total_rows += segments[i].w.n_rows;
     }
+    p.units = (p.total_rows + 1) / 2;
     p.x = x;
     p.norm_weight = norm.weight;
     p.eps = norm.eps;
     p.accumulate = accumulate;
-    size_t smem = (size_t)segments[0].w.n_cols * 4;
-    int grid = grid_for((p.total_rows + 1) / 2);
-    cudaError_t e;
-    switch (segments[0].w.format) {
-        case BC_Q4_0:
-            if ((e = prepare(matvec_kernel<BC_Q4_0>, smem)) != cudaSuccess) return e;
-            matvec_kernel<BC_Q4_0><<<grid, kThreads, smem, stream>>>(p);
-            break;
-        case BC_F16:
-            if ((e = prepare(matvec_kernel<BC_F16>, smem)) != cudaSuccess) return e;
-            matvec_kernel<BC_F16><<<grid, kThreads, smem, stream>>>(p);
-            break;
-        default:
-            if ((e = prepare(matvec_kernel<BC_F32>, smem)) != cudaSuccess) return e;
-            matvec_kernel<BC_F32><<<grid, kThreads, smem, stream>>>(p);
-            break;
-    }
-    return cudaGetLastError();
+    return launch(kernel_for<kPlain>(segments[0].w.format), stream, p);
 }
 
 cudaError_t matvec_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, const float* x, Norm norm, float* y) {
-    SwigluParams p{gate, up, x, norm.weight, norm.eps, y};
-    size_t smem = (size_t)gate.n_cols * 4;
-    int grid = grid_for(gate.n_rows);
-    cudaError_t e;
-    switch (gate.format) {
-        case BC_Q4_0:
-            if ((e = prepare(matvec_swiglu_kernel<BC_Q4_0>, smem)) != cudaSuccess) return e;
-            matvec_swiglu_kernel<BC_Q4_0><<<grid, kThreads, smem, stream>>>(p);
-            break;
-        case BC_F16:
-            if ((e = prepare(matvec_swiglu_kernel<BC_F16>, smem)) != cudaSuccess) return e;
-            matvec_swiglu_kernel<BC_F16><<<grid, kThreads, smem, stream>>>(p);
-            break;
-        default:
-            if ((e = prepare(matvec_swiglu_kernel<BC_F32>, smem)) != cudaSuccess) return e;
-            matvec_swiglu_kernel<BC_F32><<<grid, kThreads, smem, stream>>>(p);
-            break;
-    }
-    return cudaGetLastError();
+    if (gate.format == BC_Q4_0 && gate.tiles && up.tiles) return matvec_swiglu_mma(stream, gate, up, x, norm, y);
+    Params p{};
+    p.n_segments = 2;
+    p.seg[0] = MatvecSegment{gate, y};
+    p.seg[1] = MatvecSegment{up, nullptr};
+    p.total_rows = gate.n_rows;
+    p.units = gate.n_rows;
+    p.x = x;
+    p.norm_weight = norm.weight;
+    p.eps = norm.eps;
+    return launch(kernel_for<kSwiglu>(gate.format), stream, p);
 }
 
 cudaError_t matvec_conv(cudaStream_t stream, const Mat& in_proj, const float* x, Norm norm, const float* taps,
                         float* history, float* out, uint32_t n_embd, uint32_t kernel) {
-    ConvParams p{in_proj, x, norm.weight, norm.eps, taps, history, out, n_embd, kernel};
-    size_t smem = (size_t)in_proj.n_cols * 4;
-    int grid = grid_for(n_embd);
-    cudaError_t e;
-    switch (in_proj.format) {
-        case BC_Q4_0:
-            if ((e = prepare(matvec_conv_kernel<BC_Q4_0>, smem)) != cudaSuccess) return e;
-            matvec_conv_kernel<BC_Q4_0><<<grid, kThreads, smem, stream>>>(p);
-            break;
-        case BC_F16:
-            if ((e = prepare(matvec_conv_kernel<BC_F16>, smem)) != cudaSuccess) return e;
-            matvec_conv_kernel<BC_F16><<<grid, kThreads, smem, stream>>>(p);
-            break;
-        default:
-            if ((e = prepare(matvec_conv_kernel<BC_F32>, smem)) != cudaSuccess) return e;
-            matvec_conv_kernel<BC_F32><<<grid, kThreads, smem, stream>>>(p);
-            break;
-    }
-    return cudaGetLastError();
+    if (in_proj.format == BC_Q4_0 && in_proj.tiles && n_embd % 16 == 0) return matvec_conv_mma(stream, in_proj, x, norm, taps, history, out, n_embd, kernel);
+    Params p{};
+    p.n_segments = 1;
+    p.seg[0] = MatvecSegment{in_proj, out};
+    p.total_rows = in_proj.n_rows;
+    p.units = n_embd;
+    p.x = x;
+    p.norm_weight = norm.weight;
+    p.eps = norm.eps;
+    p.taps = taps;
+    p.history = history;
+    p.n_embd = n_embd;
+    p.conv_kernel = kernel;
+    return launch(kernel_for<kConv>(in_proj.format), stream, p);
 }
 
 }  // namespace k

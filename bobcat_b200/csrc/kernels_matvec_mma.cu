@@ -1,0 +1,507 @@
+// The decode Q4_0 matrix-vector kernel: a persistent, TMA-fed weight stream with the dot products
+// on the tensor cores.
+//
+// Why it looks like this. At batch 1 a Q4_0 multiply moves 18 bytes per 32 weights and nothing
+// else of size, so the only goal is to keep HBM streaming. Two things stand in the way. (1) A lane
+// that turns nibbles into floats and multiplies them one by one spends about 3.5 instructions per
+// weight, more than an SM can issue at the rate HBM delivers weights (40 per clock per SM). Here
+// the nibbles become exact fp16 integers with one logic op per pair, and an mma.m16n8k16 does the
+// multiply-adds: the 16-row weight tile is the A operand, the input vector is the B operand, split
+// into a high and a low fp16 half in two of its eight columns so no input precision is lost; the
+// fp16 block scale multiplies the per-block f32 result. That is about 1.6 instructions per weight.
+// (2) A decode step is a chain of small dependent launches, and a launch that starts its loads
+// only after its input exists idles HBM for microseconds at every link. Here one thread per CTA
+// streams the CTA's share of the matrix into a shared-memory ring with bulk async copies, starting
+// before the kernel waits for its predecessor (programmatic dependent launch): the weights depend
+// on nothing, only the few kilobytes of activations do.
+//
+// Layout ("tiles"): rows in tiles of 16, columns in chunks of 16 blocks. A chunk of a tile is
+// contiguous: for each pair of blocks 512 bytes ordered by lane - lane (g, t) = (lane / 4, lane % 4)
+// holds word t of the quants of rows g and g + 8 for both blocks, exactly its A-fragment share -
+// then the chunk's fp16 scales, 16 per block. A tile's chunks follow one another, 288 bytes per
+// block, so a tile is one contiguous run and the matrix is the tiles in order. Values are the GGUF
+// values bit for bit.
+//
+// Reference counterpart: matvec_k<q4_0_lanes> (crates/bobcat-metal/src/matvec.metal:298-365,
+// quant.metal:587-656) and its swiglu / conv variants (:386-585).
+
+#include <cstdlib>
+
+#include "device_utils.cuh"
+#include "kernels.h"
+#include "../../include/bobcat_cuda.h"
+
+namespace bc {
+namespace k {
+
+namespace {
+
+constexpr int kConsumers = 8;                    // consumer warps per CTA
+constexpr int kThreads = (kConsumers + 1) * 32;  // plus the producer warp
+constexpr int kDepth = 2;                        // ring slots per consumer warp
+constexpr int kStages = kConsumers * kDepth;
+constexpr int kChunkBlocks = 16;                 // blocks of 32 weights per chunk of a tile
+constexpr int kBlockBytes = 288;                 // 16 rows x 18 bytes
+constexpr int kStageBytes = kChunkBlocks * kBlockBytes;
+constexpr uint32_t kSpinLimit = 1u << 22;        // bounded waits: give up rather than hang
+
+__device__ int g_error_flag;
+
+// ---- mbarrier and bulk-copy wrappers (shared::cta addresses as 32-bit integers)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Returns false when the wait ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+                 "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The eight 4-bit quants of a word, minus 8, as four half2 registers of exact integers:
+// h[0] = elements (4t, 4t+2), h[1] = (4t+1, 4t+3), h[2] = (16+4t, 16+4t+2), h[3] = (16+4t+1, 16+4t+3)
+// of the block, for word t.
+__device__ __forceinline__ void unpack_word_half2(uint32_t w, uint32_t (&h)[4]) {
+    const uint32_t magic = 0x64006400u;  // half2(1024, 1024)
+    uint32_t lo02 = (w & 0x000f000fu) | magic;
+    uint32_t hi02 = (w & 0x00f000f0u) | magic;
+    uint32_t w8 = w >> 8;
+    uint32_t lo13 = (w8 & 0x000f000fu) | magic;
+    uint32_t hi13 = (w8 & 0x00f000f0u) | magic;
+    const __half2 bias_lo = __floats2half2_rn(1032.f, 1032.f);
+    const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
+    const __half2 bias_hi = __floats2half2_rn(-72.f, -72.f);
+    __half2 a = __hsub2(*reinterpret_cast<__half2*>(&lo02), bias_lo);
+    __half2 b = __hsub2(*reinterpret_cast<__half2*>(&lo13), bias_lo);
+    __half2 c = __hfma2(*reinterpret_cast<__half2*>(&hi02), sixteenth, bias_hi);
+    __half2 d = __hfma2(*reinterpret_cast<__half2*>(&hi13), sixteenth, bias_hi);
+    h[0] = *reinterpret_cast<uint32_t*>(&a);
+    h[1] = *reinterpret_cast<uint32_t*>(&b);
+    h[2] = *reinterpret_cast<uint32_t*>(&c);
+    h[3] = *reinterpret_cast<uint32_t*>(&d);
+}
+
+enum Mode { kPlain = 0, kSwiglu = 1, kConv = 2 };
+
+struct Params {
+    // Tile streams. kPlain: up to three matrices sharing x, one job per tile of their
+    // concatenation. kSwiglu: gate, up; one job per tile pair. kConv: in_proj; a job is the tiles
+    // of 16 channels' B, C and X rows.
+    const uint8_t* tiles[3];
+    float* y[3];
+    uint32_t seg_tiles[3];  // tiles per segment
+    uint32_t seg_rows[3];   // rows per segment (the last tile may be padded)
+    int n_segments;
+    uint32_t n_jobs, n_blocks;  // blocks per row
+    const float* x;
+    const float* norm_weight;
+    float eps;
+    int accumulate;
+    const float* taps;
+    float* history;
+    uint32_t n_embd, conv_kernel;
+};
+
+template <int MODE>
+__device__ __forceinline__ constexpr int segments_per_job() { return MODE == kPlain ? 1 : MODE == kSwiglu ? 2 : 3; }
+
+// The tile stream of segment `s` of job `job`.
+template <int MODE>
+__device__ __forceinline__ const uint8_t* job_tiles(const Params& p, uint32_t job, int s, uint32_t tile_bytes) {
+    if (MODE == kPlain) {
+        int seg = 0;
+        uint32_t local = job;
+        while (seg + 1 < p.n_segments && local >= p.seg_tiles[seg]) {
+            local -= p.seg_tiles[seg];
+            ++seg;
+        }
+        return p.tiles[seg] + (uint64_t)local * tile_bytes;
+    }
+    if (MODE == kSwiglu) return p.tiles[s] + (uint64_t)job * tile_bytes;
+    return p.tiles[0] + ((uint64_t)s * (p.n_embd / 16) + job) * tile_bytes;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1) matvec_mma_kernel(Params p) {
+    constexpr int S = segments_per_job<MODE>();
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* ring = smem;                                                   // kStages * kStageBytes
+    uint4* xs = reinterpret_cast<uint4*>(smem + kStages * kStageBytes);     // [block][hi | lo][t]: 8 x 16 bytes per block
+    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
+    __shared__ float reduce_scratch[64];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t nb = p.n_blocks;
+    const uint32_t tile_bytes = nb * kBlockBytes;
+    const uint32_t chunks = (nb + kChunkBlocks - 1) / kChunkBlocks;  // per tile
+    const uint32_t q_per_job = S * chunks;
+    // Jobs of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ... dealt round-robin to its warps.
+    const uint32_t my_jobs = p.n_jobs > blockIdx.x ? (p.n_jobs - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t rounds = (my_jobs + kConsumers - 1) / kConsumers;
+
+    if (tid == 0) {
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(smem_u32(&full_bar[i]), 1);
+            mbar_init(smem_u32(&empty_bar[i]), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == kConsumers) {
+        // ---- producer: one thread streams this CTA's chunks into the ring, in the order the
+        // consumers take them: round by round, chunk position by chunk position, warp by warp.
+        if (lane == 0) {
+            bool ok = true;
+            for (uint32_t r = 0; r < rounds && ok; ++r) {
+                uint32_t in_round = min((uint32_t)kConsumers, my_jobs - r * kConsumers);
+                for (uint32_t q = 0; q < q_per_job && ok; ++q) {
+                    uint32_t seg = q / chunks, chunk = q % chunks;
+                    uint32_t cb = min((uint32_t)kChunkBlocks, nb - chunk * kChunkBlocks);
+                    // Warp w's n-th chunk goes to slot n % kDepth of that warp's own slots, so each
+                    // slot is filled and drained by one pair of threads in strict order.
+                    const uint32_t n = r * q_per_job + q;
+                    for (uint32_t w = 0; w < in_round; ++w) {
+                        uint32_t stage = w * kDepth + n % kDepth, use = n / kDepth;
+                        if (use > 0 && !mbar_wait(smem_u32(&empty_bar[stage]), (use - 1) & 1)) {
+                            atomicExch(&g_error_flag, 1);
+                            ok = false;
+                            break;
+                        }
+                        uint32_t job = blockIdx.x + gridDim.x * (r * kConsumers + w);
+                        const uint8_t* src = job_tiles<MODE>(p, job, (int)seg, tile_bytes) + (uint64_t)chunk * kStageBytes;
+                        uint32_t bytes = cb * kBlockBytes;
+                        mbar_arrive_expect(smem_u32(&full_bar[stage]), bytes);
+                        bulk_load(smem_u32(ring + stage * kStageBytes), src, bytes, smem_u32(&full_bar[stage]));
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- consumers. Everything above touched only weights; the input vector (and y, the conv
+    // history) belong to earlier launches.
+    pdl_wait();
+
+    // Stage x: the rotation-free layout the B fragments want. For block b and word index t the 16
+    // bytes at xs[b * 8 + part * 4 + t] hold half2(x[4t], x[4t+2]), half2(x[4t+1], x[4t+3]),
+    // half2(x[16+4t], x[16+4t+2]), half2(x[16+4t+1], x[16+4t+3]) of the block, as the high fp16
+    // part (part 0) or the low part (part 1) of x * 2^shift. The shift brings the largest |x| to
+    // [2^13, 2^14), so neither part loses bits to fp16's narrow exponent range.
+    const int ctid = tid;  // consumers are threads 0 .. kConsumers * 32 - 1
+    constexpr int kConsumerThreads = kConsumers * 32;
+    const float4* x4 = reinterpret_cast<const float4*>(p.x);
+    const float4* w4 = reinterpret_cast<const float4*>(p.norm_weight);
+    float sumsq = 0.f, biggest = 0.f;
+    for (uint32_t i = ctid; i < nb * 8; i += kConsumerThreads) {
+        float4 v = x4[i];
+        sumsq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        if (p.norm_weight) {
+            float4 w = __ldg(w4 + i);
+            v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
+        }
+        biggest = fmaxf(biggest, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    sumsq = warp_sum(sumsq);
+    biggest = warp_max(biggest);
+    if (lane == 0) {
+        reduce_scratch[warp] = sumsq;
+        reduce_scratch[32 + warp] = biggest;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+    float total = 0.f, top = 0.f;
+    for (int i = 0; i < kConsumers; ++i) {
+        total += reduce_scratch[i];
+        top = fmaxf(top, reduce_scratch[32 + i]);
+    }
+    const float norm_scale = p.norm_weight ? rsqrtf(total / (float)(nb * 32) + p.eps) : 1.f;
+    int exponent = 0;
+    if (top > 0.f) frexpf(top, &exponent);             // top = m * 2^exponent, m in [0.5, 1)
+    const float up = top > 0.f ? exp2f((float)(14 - exponent)) : 1.f;  // top * up in [2^13, 2^14)
+    const float out_scale = norm_scale / up;
+    for (uint32_t i = ctid; i < nb * 4; i += kConsumerThreads) {
+        uint32_t b = i >> 2, t = i & 3;
+        float4 lo4 = x4[b * 8 + t], hi4 = x4[b * 8 + 4 + t];  // elements 4t..4t+3 and 16+4t..16+4t+3
+        if (p.norm_weight) {
+            float4 wl = __ldg(w4 + b * 8 + t), wh = __ldg(w4 + b * 8 + 4 + t);
+            lo4.x *= wl.x; lo4.y *= wl.y; lo4.z *= wl.z; lo4.w *= wl.w;
+            hi4.x *= wh.x; hi4.y *= wh.y; hi4.z *= wh.z; hi4.w *= wh.w;
+        }
+        float v[8] = {lo4.x * up, lo4.z * up, lo4.y * up, lo4.w * up, hi4.x * up, hi4.z * up, hi4.y * up, hi4.w * up};
+        __align__(16) __half hi[8];
+        __align__(16) __half lo[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            hi[j] = __float2half_rn(v[j]);
+            lo[j] = __float2half_rn(v[j] - __half2float(hi[j]));
+        }
+        xs[b * 8 + t] = *reinterpret_cast<uint4*>(hi);
+        xs[b * 8 + 4 + t] = *reinterpret_cast<uint4*>(lo);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t ring_base = smem_u32(ring);
+    for (uint32_t r = 0; r * kConsumers + warp < my_jobs; ++r) {
+        const uint32_t job = blockIdx.x + gridDim.x * (r * kConsumers + warp);
+        float acc[S][2];
+#pragma unroll
+        for (int s = 0; s < S; ++s) acc[s][0] = acc[s][1] = 0.f;
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+            for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+                const uint32_t q = s * chunks + chunk;
+                const uint32_t n = r * q_per_job + q;
+                const uint32_t stage = warp * kDepth + n % kDepth, use = n / kDepth;
+                if (!mbar_wait(smem_u32(&full_bar[stage]), use & 1)) {
+                    atomicExch(&g_error_flag, 2);
+                    return;
+                }
+                const uint32_t cb = min((uint32_t)kChunkBlocks, nb - chunk * kChunkBlocks);
+                const uint32_t quants = ring_base + stage * kStageBytes;
+                const __half* scales = reinterpret_cast<const __half*>(ring + stage * kStageBytes + cb * 256);
+                for (uint32_t pair = 0; pair < cb / 2; ++pair) {
+                    uint4 v;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(quants + (pair * 32 + lane) * 16));
+#pragma unroll
+                    for (int half_pair = 0; half_pair < 2; ++half_pair) {
+                        const uint32_t local = pair * 2 + half_pair;              // block within the chunk
+                        const uint32_t block = chunk * kChunkBlocks + local;      // block within the row
+                        uint32_t ha[4], hb[4];
+                        unpack_word_half2(half_pair ? v.z : v.x, ha);  // row g
+                        unpack_word_half2(half_pair ? v.w : v.y, hb);  // row g + 8
+                        uint4 xb = make_uint4(0, 0, 0, 0);
+                        if (g < 2) xb = xs[block * 8 + g * 4 + t];
+                        float c[4] = {0.f, 0.f, 0.f, 0.f};
+                        mma_16816(c, ha[0], hb[0], ha[1], hb[1], xb.x, xb.y);
+                        mma_16816(c, ha[2], hb[2], ha[3], hb[3], xb.z, xb.w);
+                        float d0 = __half2float(scales[local * 16 + g]), d1 = __half2float(scales[local * 16 + g + 8]);
+                        acc[s][0] += (c[0] + c[1]) * d0;
+                        acc[s][1] += (c[2] + c[3]) * d1;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
+            }
+        }
+        // Columns 0 and 1 of the product (the high and low parts of x) live in the lanes with t == 0.
+        if (t == 0) {
+#pragma unroll
+            for (int half_tile = 0; half_tile < 2; ++half_tile) {
+                const uint32_t in_tile = g + 8 * half_tile;
+                if (MODE == kPlain) {
+                    int seg = 0;
+                    uint32_t local = job;
+                    while (seg + 1 < p.n_segments && local >= p.seg_tiles[seg]) {
+                        local -= p.seg_tiles[seg];
+                        ++seg;
+                    }
+                    uint32_t row = local * 16 + in_tile;
+                    if (row < p.seg_rows[seg]) {
+                        float v = acc[0][half_tile] * out_scale;
+                        float* y = p.y[seg] + row;
+                        *y = p.accumulate ? *y + v : v;
+                    }
+                } else if (MODE == kSwiglu) {
+                    uint32_t row = job * 16 + in_tile;
+                    if (row < p.seg_rows[0]) {
+                        float gate = acc[0][half_tile] * out_scale, upv = acc[S > 1 ? 1 : 0][half_tile] * out_scale;
+                        p.y[0][row] = gate / (1.f + expf(-gate)) * upv;
+                    }
+                } else {
+                    // B, C and X of channel ch; the taps over B*X and the channel's history; the
+                    // history shift; C * conv (crates/bobcat/src/lfm2.rs:456-475, f32 sums).
+                    uint32_t ch = job * 16 + in_tile;
+                    if (ch < p.n_embd) {
+                        float b = acc[0][half_tile] * out_scale, c = acc[S > 1 ? 1 : 0][half_tile] * out_scale, xv = acc[S > 2 ? 2 : 0][half_tile] * out_scale;
+                        float bx = b * xv;
+                        const uint32_t K = p.conv_kernel;
+                        const float* taps = p.taps + (uint64_t)ch * K;
+                        float sum = taps[K - 1] * bx;
+                        for (uint32_t kk = 0; kk + 1 < K; ++kk) sum += taps[kk] * p.history[(uint64_t)kk * p.n_embd + ch];
+                        for (uint32_t kk = 0; kk + 2 < K; ++kk) p.history[(uint64_t)kk * p.n_embd + ch] = p.history[(uint64_t)(kk + 1) * p.n_embd + ch];
+                        p.history[(uint64_t)(K - 2) * p.n_embd + ch] = bx;
+                        p.y[0][ch] = c * sum;
+                    }
+                }
+            }
+        }
+    }
+}
+
+// One thread per 16 bytes of quants and one per scale: split layout -> tile layout.
+__global__ void repack_tiles_kernel(const uint4* __restrict__ quants, const __half* __restrict__ scales, uint32_t n_rows, uint32_t nb,
+                                    uint8_t* __restrict__ tiles) {
+    const uint32_t n_tiles = (n_rows + 15) / 16;
+    const uint64_t quant_items = (uint64_t)n_tiles * (nb / 2) * 32;
+    const uint64_t scale_items = (uint64_t)n_tiles * nb * 16;
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < quant_items) {
+        uint32_t lane = i % 32;
+        uint64_t rest = i / 32;
+        uint32_t pair = rest % (nb / 2), tile = rest / (nb / 2);
+        uint32_t g = lane >> 2, t = lane & 3;
+        uint32_t chunk = (2 * pair) / kChunkBlocks, local_pair = pair - chunk * (kChunkBlocks / 2);
+        uint32_t rows[2] = {tile * 16 + g, tile * 16 + g + 8};
+        uint32_t out[4];
+#pragma unroll
+        for (int half_pair = 0; half_pair < 2; ++half_pair) {
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                uint32_t word = 0;
+                if (rows[rr] < n_rows) {
+                    uint4 q = quants[(uint64_t)rows[rr] * nb + 2 * pair + half_pair];
+                    word = t == 0 ? q.x : t == 1 ? q.y : t == 2 ? q.z : q.w;
+                }
+                out[half_pair * 2 + rr] = word;
+            }
+        }
+        uint8_t* dst = tiles + (uint64_t)tile * nb * kBlockBytes + (uint64_t)chunk * kStageBytes + ((uint64_t)local_pair * 32 + lane) * 16;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(out[0], out[1], out[2], out[3]);
+    } else if (i < quant_items + scale_items) {
+        uint64_t j = i - quant_items;
+        uint32_t in_tile = j % 16;
+        uint64_t rest = j / 16;
+        uint32_t block = rest % nb, tile = rest / nb;
+        uint32_t chunk = block / kChunkBlocks, local = block - chunk * kChunkBlocks;
+        uint32_t cb = min((uint32_t)kChunkBlocks, nb - chunk * kChunkBlocks);
+        uint32_t row = tile * 16 + in_tile;
+        __half d = row < n_rows ? scales[(uint64_t)row * nb + block] : __float2half(0.f);
+        uint8_t* dst = tiles + (uint64_t)tile * nb * kBlockBytes + (uint64_t)chunk * kStageBytes + (uint64_t)cb * 256 + ((uint64_t)local * 16 + in_tile) * 2;
+        *reinterpret_cast<__half*>(dst) = d;
+    }
+}
+
+template <int MODE>
+cudaError_t launch(cudaStream_t stream, Params& p) {
+    const void* kernel = (const void*)matvec_mma_kernel<MODE>;
+    size_t smem = (size_t)kStages * kStageBytes + (size_t)p.n_blocks * 128;
+    cudaError_t e = ensure_dynamic_smem(kernel, smem);
+    if (e != cudaSuccess) return e;
+    uint32_t ctas = p.n_jobs < (uint32_t)sm_count() ? p.n_jobs : (uint32_t)sm_count();
+    void* args[] = {&p};
+    return launch_kernel(kernel, dim3(ctas), dim3(kThreads), smem, stream, args);
+}
+
+bool g_enabled = [] {
+    const char* v = getenv("BOBCAT_NO_MMA_MATVEC");
+    return !(v && v[0] == '1');
+}();
+
+}  // namespace
+
+uint64_t tiles_bytes(uint32_t n_rows, uint32_t n_cols) { return (uint64_t)((n_rows + 15) / 16) * (n_cols / 32) * kBlockBytes; }
+
+bool tiles_supported(uint32_t n_cols) { return g_enabled && n_cols % 64 == 0; }
+
+cudaError_t repack_tiles(cudaStream_t stream, const void* quants, const __half* scales, uint32_t n_rows, uint32_t n_cols, void* tiles) {
+    uint32_t nb = n_cols / 32;
+    uint64_t n_tiles = (n_rows + 15) / 16;
+    uint64_t items = n_tiles * (nb / 2) * 32 + n_tiles * nb * 16;
+    if (items == 0) return cudaSuccess;
+    repack_tiles_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(static_cast<const uint4*>(quants), scales, n_rows, nb, static_cast<uint8_t*>(tiles));
+    return cudaGetLastError();
+}
+
+cudaError_t matvec_mma_prepare(uint32_t widest_cols) {
+    size_t smem = (size_t)kStages * kStageBytes + (size_t)(widest_cols / 32) * 128;
+    for (const void* kernel : {(const void*)matvec_mma_kernel<kPlain>, (const void*)matvec_mma_kernel<kSwiglu>, (const void*)matvec_mma_kernel<kConv>}) {
+        cudaError_t e = ensure_dynamic_smem(kernel, smem);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+int matvec_error_flag() {
+    int flag = 0;
+    cudaMemcpyFromSymbol(&flag, g_error_flag, sizeof flag);
+    return flag;
+}
+
+cudaError_t matvec_mma(cudaStream_t stream, const MatvecSegment* segments, int n_segments, const float* x, Norm norm, bool accumulate) {
+    Params p{};
+    p.n_segments = n_segments;
+    for (int i = 0; i < n_segments; ++i) {
+        p.tiles[i] = static_cast<const uint8_t*>(segments[i].w.tiles);
+        p.y[i] = segments[i].y;
+        p.seg_rows[i] = segments[i].w.n_rows;
+        p.seg_tiles[i] = (segments[i].w.n_rows + 15) / 16;
+        p.n_jobs += p.seg_tiles[i];
+    }
+    p.n_blocks = segments[0].w.n_cols / 32;
+    p.x = x;
+    p.norm_weight = norm.weight;
+    p.eps = norm.eps;
+    p.accumulate = accumulate;
+    return launch<kPlain>(stream, p);
+}
+
+cudaError_t matvec_swiglu_mma(cudaStream_t stream, const Mat& gate, const Mat& up, const float* x, Norm norm, float* y) {
+    Params p{};
+    p.n_segments = 2;
+    p.tiles[0] = static_cast<const uint8_t*>(gate.tiles);
+    p.tiles[1] = static_cast<const uint8_t*>(up.tiles);
+    p.y[0] = y;
+    p.seg_rows[0] = p.seg_rows[1] = gate.n_rows;
+    p.seg_tiles[0] = p.seg_tiles[1] = (gate.n_rows + 15) / 16;
+    p.n_jobs = p.seg_tiles[0];
+    p.n_blocks = gate.n_cols / 32;
+    p.x = x;
+    p.norm_weight = norm.weight;
+    p.eps = norm.eps;
+    return launch<kSwiglu>(stream, p);
+}
+
+cudaError_t matvec_conv_mma(cudaStream_t stream, const Mat& in_proj, const float* x, Norm norm, const float* taps, float* history,
+                            float* out, uint32_t n_embd, uint32_t kernel) {
+    Params p{};
+    p.n_segments = 1;
+    p.tiles[0] = static_cast<const uint8_t*>(in_proj.tiles);
+    p.y[0] = out;
+    p.seg_rows[0] = in_proj.n_rows;
+    p.seg_tiles[0] = (in_proj.n_rows + 15) / 16;
+    p.n_jobs = n_embd / 16;
+    p.n_blocks = in_proj.n_cols / 32;
+    p.x = x;
+    p.norm_weight = norm.weight;
+    p.eps = norm.eps;
+    p.taps = taps;
+    p.history = history;
+    p.n_embd = n_embd;
+    p.conv_kernel = kernel;
+    return launch<kConv>(stream, p);
+}
+
+}  // namespace k
+}  // namespace bc

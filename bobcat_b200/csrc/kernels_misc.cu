@@ -77,8 +77,10 @@ __global__ void silu_mul_kernel(float* __restrict__ x, const float* __restrict__
 }
 
 // grid (ceil(n_embd / threads), n_tokens)
-__global__ void embed_kernel(Mat w, const uint32_t* __restrict__ tokens, float* __restrict__ out) {
-    uint32_t token = tokens[blockIdx.y];
+__global__ void embed_kernel(Mat w, const uint32_t* __restrict__ tokens, Pos pos, float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    uint32_t token = tokens[(pos.ptr ? *pos.ptr : 0u) + pos.value + blockIdx.y];
     uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= w.n_cols) return;
     float v;
@@ -199,10 +201,22 @@ __global__ void short_conv_kernel(const float* __restrict__ bcx, const float* __
 }
 
 // One CTA of 1024 threads scans the vocabulary; ties go to the lowest index.
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ x, uint32_t n, uint32_t* out,
-                                                       uint32_t* readback) {
+struct ArgmaxOut {
+    uint32_t* out;       // direct mode: the word to write
+    uint32_t* readback;  // direct mode: optional host-mapped copy
+    uint32_t* counter;   // step mode (non-null): position counter
+    int advance;
+    uint32_t* tokens;
+    uint32_t offset;
+    uint32_t* ring;
+    uint32_t ring_slots;
+};
+
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ x, uint32_t n, ArgmaxOut o) {
     __shared__ float best_value[32];
     __shared__ uint32_t best_index[32];
+    pdl_launch_dependents();
+    pdl_wait();
     float value = -INFINITY;
     uint32_t index = 0xffffffffu;
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
@@ -241,10 +255,82 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
             }
         }
         if (lane == 0) {
-            *out = index;
-            if (readback) *readback = index;
+            if (o.counter) {
+                uint32_t pos = *o.counter;
+                if (o.advance) {
+                    pos += 1;
+                    *o.counter = pos;
+                }
+                o.tokens[pos + o.offset] = index;
+                if (o.ring) o.ring[pos % o.ring_slots] = index;
+            } else {
+                *o.out = index;
+                if (o.readback) *o.readback = index;
+            }
         }
     }
+}
+
+// One warp per head. Blocks [0, n_heads) treat q, [n_heads, n_heads + n_kv) treat k, the rest copy v.
+__global__ void rope_store_kernel(RopeStore p, Pos pos_ref) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x;
+    const uint32_t pos = (pos_ref.ptr ? *pos_ref.ptr : 0u) + pos_ref.value;
+    const uint32_t hd = p.head_dim, kv_dim = p.n_kv_heads * hd;
+    uint32_t block = blockIdx.x;
+    if (block >= p.n_heads + p.n_kv_heads) {
+        uint32_t head = block - p.n_heads - p.n_kv_heads;
+        const float* src = p.v + (uint64_t)head * hd;
+        uint64_t at = (uint64_t)pos * kv_dim + (uint64_t)head * hd;
+        for (uint32_t e = lane; e < hd; e += 32) {
+            if (p.kv_half) static_cast<__half*>(p.v_cache)[at + e] = __float2half_rn(src[e]);
+            else static_cast<float*>(p.v_cache)[at + e] = src[e];
+        }
+        return;
+    }
+    const bool is_q = block < p.n_heads;
+    const uint32_t head = is_q ? block : block - p.n_heads;
+    const float* src = is_q ? p.q + (uint64_t)head * p.q_head_stride : p.k + (uint64_t)head * hd;
+    const float* weight = is_q ? p.q_norm : p.k_norm;
+    __shared__ float values[256];
+    float sumsq = 0.f;
+    for (uint32_t e = lane; e < hd; e += 32) {
+        float v = src[e];
+        values[e] = v;
+        sumsq += v * v;
+    }
+    sumsq = warp_sum(sumsq);
+    const float scale = rsqrtf(sumsq / (float)hd + p.eps);
+    __syncwarp();
+    for (uint32_t e = lane; e < hd; e += 32) values[e] = weight[e] * (values[e] * scale);
+    __syncwarp();
+    const uint32_t half_rot = p.n_rot / 2;
+    for (uint32_t e = lane; e < hd; e += 32) {
+        float result = values[e];
+        if (e < p.n_rot) {
+            uint32_t i = e < half_rot ? e : e - half_rot;
+            float inv_freq = 1.0f / powf(p.theta, (float)(2 * i) / (float)p.n_rot);
+            float angle = (float)pos * inv_freq;
+            float s, c;
+            sincosf(angle, &s, &c);
+            float a = values[i], b = values[i + half_rot];
+            result = e < half_rot ? a * c - b * s : b * c + a * s;
+        }
+        if (is_q) {
+            p.q[(uint64_t)head * p.q_head_stride + e] = result;
+        } else {
+            uint64_t at = (uint64_t)pos * kv_dim + (uint64_t)head * hd + e;
+            if (p.kv_half) static_cast<__half*>(p.k_cache)[at] = __float2half_rn(result);
+            else static_cast<float*>(p.k_cache)[at] = result;
+        }
+    }
+}
+
+__global__ void advance_kernel(uint32_t* counter) {
+    pdl_launch_dependents();
+    pdl_wait();
+    *counter += 1;
 }
 
 }  // namespace
@@ -274,11 +360,12 @@ cudaError_t expand(cudaStream_t stream, const Mat& w, void* out, bool out_half) 
     return cudaGetLastError();
 }
 
-cudaError_t embed(cudaStream_t stream, const Mat& w, const uint32_t* tokens, float* out, uint32_t n_tokens) {
+cudaError_t embed(cudaStream_t stream, const Mat& w, const uint32_t* tokens, Pos pos, float* out, uint32_t n_tokens) {
     if (n_tokens == 0) return cudaSuccess;
     dim3 grid(blocks_for(w.n_cols), n_tokens);
-    embed_kernel<<<grid, kThreads, 0, stream>>>(w, tokens, out);
-    return cudaGetLastError();
+    Mat wm = w;
+    void* args[] = {&wm, &tokens, &pos, &out};
+    return launch_kernel((const void*)embed_kernel, grid, dim3(kThreads), 0, stream, args);
 }
 
 cudaError_t rms_norm(cudaStream_t stream, const float* x, const float* weight, float* out, uint32_t n_cols, uint32_t n_rows,
@@ -323,8 +410,27 @@ cudaError_t short_conv(cudaStream_t stream, const float* bcx, const float* taps,
 }
 
 cudaError_t argmax(cudaStream_t stream, const float* x, uint32_t n, uint32_t* out, uint32_t* readback) {
-    argmax_kernel<<<1, 1024, 0, stream>>>(x, n, out, readback);
-    return cudaGetLastError();
+    ArgmaxOut o{out, readback, nullptr, 0, nullptr, 0, nullptr, 1};
+    void* args[] = {&x, &n, &o};
+    return launch_kernel((const void*)argmax_kernel, dim3(1), dim3(1024), 0, stream, args);
+}
+
+cudaError_t argmax_step(cudaStream_t stream, const float* x, uint32_t n, uint32_t* counter, bool advance, uint32_t* tokens,
+                        uint32_t offset, uint32_t* ring, uint32_t ring_slots) {
+    ArgmaxOut o{nullptr, nullptr, counter, advance ? 1 : 0, tokens, offset, ring, ring_slots ? ring_slots : 1};
+    void* args[] = {&x, &n, &o};
+    return launch_kernel((const void*)argmax_kernel, dim3(1), dim3(1024), 0, stream, args);
+}
+
+cudaError_t advance(cudaStream_t stream, uint32_t* counter) {
+    void* args[] = {&counter};
+    return launch_kernel((const void*)advance_kernel, dim3(1), dim3(1), 0, stream, args);
+}
+
+cudaError_t rope_store(cudaStream_t stream, const RopeStore& p, Pos pos) {
+    RopeStore params = p;
+    void* args[] = {&params, &pos};
+    return launch_kernel((const void*)rope_store_kernel, dim3(p.n_heads + 2 * p.n_kv_heads), dim3(32), 0, stream, args);
 }
 
 }  // namespace k

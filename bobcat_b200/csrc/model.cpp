@@ -272,7 +272,10 @@ uint64_t aligned(uint64_t n) { return round_up(n, 256); }
 uint64_t device_bytes(const HostMatrix& hm) {
     if (!hm.t) return 0;
     uint64_t n = (uint64_t)hm.n_rows * hm.n_cols;
-    if (hm.t->type == T_Q4_0) return aligned(n / 32 * 16) + aligned(n / 32 * 2);
+    if (hm.t->type == T_Q4_0) {
+        uint64_t tiles = k::tiles_supported(hm.n_cols) ? aligned(k::tiles_bytes(hm.n_rows, hm.n_cols)) : 0;
+        return aligned(n / 32 * 16) + aligned(n / 32 * 2) + tiles;
+    }
     return aligned(hm.t->n_bytes);
 }
 
@@ -343,7 +346,10 @@ bc_status bc_model::device_model(bc_backend* backend, std::shared_ptr<DeviceMode
         mat->n_cols = hm.n_cols;
         mat->data = dst;
         uint64_t n_blocks = (uint64_t)hm.n_rows * hm.n_cols / 32;
-        if (hm.t->type == T_Q4_0) mat->scales = reinterpret_cast<const __half*>(dst + aligned(n_blocks * 16));
+        if (hm.t->type == T_Q4_0) {
+            mat->scales = reinterpret_cast<const __half*>(dst + aligned(n_blocks * 16));
+            if (k::tiles_supported(hm.n_cols)) mat->tiles = dst + aligned(n_blocks * 16) + aligned(n_blocks * 2);
+        }
         if (uploaded[hm.t]) return BC_OK;
         uploaded[hm.t] = true;
         if (hm.t->type == T_Q4_0) {
@@ -351,6 +357,11 @@ bc_status bc_model::device_model(bc_backend* backend, std::shared_ptr<DeviceMode
             // tensor before it.
             BC_CUDA(cudaMemcpyAsync(staging, gguf.data(*hm.t), hm.t->n_bytes, cudaMemcpyHostToDevice, backend->stream));
             BC_CUDA(k::repack_q4_0(backend->stream, static_cast<const uint8_t*>(staging), n_blocks, dst, const_cast<__half*>(mat->scales)));
+            if (k::tiles_supported(hm.n_cols)) {
+                // A second copy in the layout the tensor-core decode kernel streams.
+                char* tiles = dst + aligned(n_blocks * 16) + aligned(n_blocks * 2);
+                BC_CUDA(k::repack_tiles(backend->stream, dst, mat->scales, hm.n_rows, hm.n_cols, tiles));
+            }
         } else {
             BC_CUDA(cudaMemcpyAsync(dst, gguf.data(*hm.t), hm.t->n_bytes, cudaMemcpyHostToDevice, backend->stream));
         }

@@ -20,8 +20,13 @@ struct Recorder {
     const bc_hparams& hp;
     cudaStream_t stream;
     bc_status status = BC_OK;
+    // When set, single-token passes read their position from s.step_pos on the device, so the
+    // launches can be captured once and replayed at every position.
+    bool replayed = false;
 
     explicit Recorder(bc_seq& seq) : s(seq), hp(seq.model->hp), stream(seq.backend->stream) {}
+
+    k::Pos at(uint32_t pos) const { return replayed ? k::Pos{s.step_pos, 0} : k::Pos{nullptr, pos}; }
 
     // Launch helper: counts the kernel, keeps the first failure.
     template <typename F>
@@ -88,14 +93,29 @@ struct Recorder {
         return static_cast<float*>(cache_at(s.v_cache, layer_base(cache_index) + (size_t)pos * kv_dim()));
     }
 
+    // One token: norm and rotation of q and k, the K and V rows of position `pos` into the caches
+    // (one launch), then attention over positions [0, pos].
+    void decode_attend(const DeviceLayer& D, uint32_t cache_index, uint32_t pos, uint32_t q_stride, uint32_t q_head_stride) {
+        k::RopeStore rs{s.q, s.k, s.v, cache_at(s.k_cache, layer_base(cache_index)), cache_at(s.v_cache, layer_base(cache_index)),
+                        D.q_norm, D.k_norm, hp.n_heads, hp.n_kv_heads, hp.head_dim, q_head_stride, hp.n_rot, hp.rope_theta, hp.norm_eps, s.kv_half};
+        k::Pos p = at(pos);
+        run("rope_store", hp.n_heads + 2 * hp.n_kv_heads, hp.head_dim, 0, 1, [&] { return k::rope_store(stream, rs, p); });
+        k::AttentionShape shape{hp.n_heads, hp.n_kv_heads, hp.head_dim, p.value, 1, s.n_ctx, q_stride, q_head_stride, p.ptr};
+        uint64_t kv_bytes = (uint64_t)(pos + 1) * kv_dim() * kv_element_bytes() * 2;
+        run("attention", 1, pos + 1, kv_bytes, 2, [&] {
+            return k::attention(stream, s.q, cache_at(s.k_cache, layer_base(cache_index)), cache_at(s.v_cache, layer_base(cache_index)), s.kv_half,
+                                s.scores, s.attn, shape);
+        });
+    }
+
     void lfm2_attention(const DeviceLayer& D, uint32_t cache_index, uint32_t pos) {
         // The three projections share the normalised input, so one launch computes them.
-        k::MatvecSegment segs[3] = {{D.q, s.q}, {D.k, s.k}, {D.v, value_target(cache_index, pos)}};
+        k::MatvecSegment segs[3] = {{D.q, s.q}, {D.k, s.k}, {D.v, s.v}};
         uint64_t bytes = D.q.bytes() + D.k.bytes() + D.v.bytes();
         run("matvec_qkv", D.q.n_rows + D.k.n_rows + D.v.n_rows, D.q.n_cols, bytes, 1,
             [&] { return k::matvec(stream, segs, 3, s.hidden, norm(D.attn_norm), false); });
         uint32_t q_dim = hp.n_heads * hp.head_dim;
-        rotate_and_attend(D, cache_index, pos, 1, q_dim, hp.head_dim);
+        decode_attend(D, cache_index, pos, q_dim, hp.head_dim);
         matvec(D.output, s.attn, s.hidden, k::Norm{}, true);
     }
 
@@ -112,7 +132,7 @@ struct Recorder {
     // lfm2_metal.rs:1162-1242
     void lfm2_step(uint32_t pos, bool want_logits, bool traced) {
         const DeviceModel& W = *s.weights;
-        run("embed", 1, hp.n_embd, 0, 1, [&] { return k::embed(stream, W.token_embd, s.tokens + pos, s.hidden, 1); });
+        run("embed", 1, hp.n_embd, 0, 1, [&] { return k::embed(stream, W.token_embd, s.tokens, at(pos), s.hidden, 1); });
         if (traced) copy(s.hidden, s.trace_embedding, hp.n_embd);
         for (size_t il = 0; il < W.layers.size(); ++il) {
             const LayerSpec& S = s.model->layers[il];
@@ -135,7 +155,7 @@ struct Recorder {
     void lfm2_batch(uint32_t pos, uint32_t n, bool want_logits, bool traced, size_t trace_stride) {
         const DeviceModel& W = *s.weights;
         const uint32_t n_embd = hp.n_embd;
-        run("embed", n, n_embd, 0, 1, [&] { return k::embed(stream, W.token_embd, s.tokens + pos, s.hidden, n); });
+        run("embed", n, n_embd, 0, 1, [&] { return k::embed(stream, W.token_embd, s.tokens, k::Pos{nullptr, pos}, s.hidden, n); });
         if (traced) copy(s.hidden, s.trace_embedding, (uint64_t)n * n_embd);
         for (size_t il = 0; il < W.layers.size(); ++il) {
             const LayerSpec& S = s.model->layers[il];
@@ -235,6 +255,66 @@ bc_status timing_end(bc_seq* s, double* seconds) {
     float ms = 0.f;
     cudaEventElapsedTime(&ms, s->timing_start, s->timing_end);
     *seconds = ms * 1e-3;
+    // A kernel whose bounded wait ran out leaves a flag rather than hanging the device.
+    if (int flag = k::matvec_error_flag()) return fail(BC_ERR_EXECUTION, "a decode kernel gave up waiting for its weight stream (code %d)", flag);
+    return BC_OK;
+}
+
+// Replay needs a stream that can be captured (not the legacy default stream) and no per-launch
+// event timing.
+bool replay_enabled(const bc_seq* s) {
+    return s->use_graphs && !s->backend->profiling && s->backend->stream != nullptr && s->backend->stream != cudaStreamLegacy;
+}
+
+// Capture one generated step into a graph. The generate variant picks tokens[pos] from the logits,
+// then runs the forward pass at pos; the stream variant runs the forward pass at pos, then picks
+// tokens[pos + 1] and mirrors it into the host-mapped ring at slot pos % kGenerateInFlight. Both
+// start by adding one to s->step_pos, so the host seeds it with the first position minus one.
+bc_status capture_step(bc_seq* s, bool stream_variant) {
+    cudaStream_t stream = s->backend->stream;
+    const uint32_t n_vocab = s->model->hp.n_vocab;
+    uint64_t before = s->launches;
+    BC_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+    Recorder r(*s);
+    r.replayed = true;
+    if (stream_variant) {
+        r.run("advance", 1, 1, 0, 1, [&] { return k::advance(stream, s->step_pos); });
+        r.step(0, true, false);
+        r.run("argmax", 1, n_vocab, 0, 1,
+              [&] { return k::argmax_step(stream, s->logits, n_vocab, s->step_pos, false, s->tokens, 1, s->readback, kGenerateInFlight); });
+    } else {
+        r.run("argmax", 1, n_vocab, 0, 1,
+              [&] { return k::argmax_step(stream, s->logits, n_vocab, s->step_pos, true, s->tokens, 0, nullptr, 1); });
+        r.step(0, true, false);
+    }
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(stream, &graph);
+    uint64_t kernels = s->launches - before;
+    s->launches = before;  // capturing launches nothing
+    if (r.status != BC_OK) {
+        if (graph) cudaGraphDestroy(graph);
+        return r.status;
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture");
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate");
+    if (stream_variant) {
+        s->stream_graph = exec;
+        s->stream_graph_kernels = kernels;
+    } else {
+        s->generate_graph = exec;
+        s->generate_graph_kernels = kernels;
+    }
+    return BC_OK;
+}
+
+// Make sure the wanted graph exists and seed the device position for a run that starts at `first`.
+bc_status prepare_replay(bc_seq* s, bool stream_variant, uint32_t first) {
+    if (stream_variant ? !s->stream_graph : !s->generate_graph) BC_TRY(capture_step(s, stream_variant));
+    s->host_pos = first - 1;  // first >= 1: generation needs a prompt
+    BC_CUDA(cudaMemcpyAsync(s->step_pos, &s->host_pos, 4, cudaMemcpyHostToDevice, s->backend->stream));
     return BC_OK;
 }
 
@@ -250,6 +330,8 @@ bc_status generate_inner(bc_seq* s, uint32_t* out, size_t count, bool select_nex
     if (n == 0) return BC_OK;
 
     auto encode_start = Clock::now();
+    const bool replay = replay_enabled(s);
+    if (replay) BC_TRY(prepare_replay(s, /*stream_variant=*/false, s->n_past));
     BC_TRY(timing_begin(s));
     Recorder r(*s);
     for (uint32_t i = 0; i < n && r.status == BC_OK; ++i) {
@@ -260,8 +342,13 @@ bc_status generate_inner(bc_seq* s, uint32_t* out, size_t count, bool select_nex
             cudaError_t e = cudaEventSynchronize(s->slot_done[slot]);
             if (e != cudaSuccess) return cuda_fail(e, "generation step");
         }
-        r.argmax(s->logits, s->tokens + pos, nullptr);
-        r.step(pos, true, false);
+        if (replay) {
+            BC_CUDA(cudaGraphLaunch(s->generate_graph, s->backend->stream));
+            s->launches += s->generate_graph_kernels;
+        } else {
+            r.argmax(s->logits, s->tokens + pos, nullptr);
+            r.step(pos, true, false);
+        }
         if (select_next && i + 1 == n) r.argmax(s->logits, s->greedy_token, nullptr);
         if (r.status == BC_OK) BC_CUDA(cudaEventRecord(s->slot_done[slot], s->backend->stream));
     }
@@ -296,6 +383,8 @@ bc_seq::~bc_seq() {
     cudaFree(trace_layers);
     cudaFree(trace_final);
     if (readback) cudaFreeHost(readback);
+    if (generate_graph) cudaGraphExecDestroy(generate_graph);
+    if (stream_graph) cudaGraphExecDestroy(stream_graph);
     for (cudaEvent_t e : slot_done)
         if (e) cudaEventDestroy(e);
     if (timing_start) cudaEventDestroy(timing_start);
@@ -345,7 +434,14 @@ bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32
         {(void**)&s->logits, (size_t)hp.n_vocab * 4},
         {(void**)&s->tokens, ((size_t)n_ctx + 1) * 4},
         {(void**)&s->greedy_token, 4},
+        {(void**)&s->step_pos, 4},
     };
+    const char* no_graph = getenv("BOBCAT_NO_GRAPH");
+    s->use_graphs = !(no_graph && no_graph[0] == '1');
+    // Kernels whose input vector outgrows the default shared-memory limit get their limit raised
+    // now, so no launch inside a capture has to.
+    uint32_t widest = std::max({hp.n_embd, hp.n_ff, hp.n_ff_expert, (uint32_t)q_dim, hp.n_v_heads * hp.v_head_dim});
+    BC_CUDA(k::matvec_prepare(widest));
     size_t total = 0;
     for (Item& it : items) total += round_up(std::max<size_t>(it.bytes, 4), 256);
     cudaError_t e = cudaMalloc(&s->arena, total);
@@ -518,19 +614,33 @@ bc_status bc_seq_generate_stream(bc_seq* s, uint32_t max_tokens, bc_emit_fn emit
         if (emitting) emitting = emit(s->readback[slot], user) != 0;
         return BC_OK;
     };
+    const bool replay = replay_enabled(s);
+    if (replay && steps > 0) {
+        Recorder first_pick(*s);
+        first_pick.argmax(s->logits, s->tokens + start, nullptr);
+        if (first_pick.status != BC_OK) return first_pick.status;
+        BC_TRY(prepare_replay(s, /*stream_variant=*/true, start));
+    }
 
     for (uint32_t step = 0; step < steps; ++step) {
-        // The slot's previous step selected the token that goes out next.
-        int slot = (int)(step % kGenerateInFlight);
+        // The slot's previous step selected the token that goes out next. A step at position p
+        // uses slot p % kGenerateInFlight, which is also where the replayed argmax writes.
+        uint32_t pos = start + step;
+        int slot = (int)(pos % kGenerateInFlight);
         if (pending[slot] && (result = finish_slot(slot)) != BC_OK) break;
         if (!emitting) break;
         auto encode_start = Clock::now();
-        uint32_t pos = start + step;
         Recorder r(*s);
-        if (step == 0) r.argmax(s->logits, s->tokens + pos, nullptr);
-        r.step(pos, true, false);
-        // tokens has n_ctx + 1 slots, so the pick at the last position has a place to go.
-        r.argmax(s->logits, s->tokens + pos + 1, s->readback + slot);
+        if (replay) {
+            cudaError_t ge = cudaGraphLaunch(s->stream_graph, stream);
+            if (ge != cudaSuccess) r.status = cuda_fail(ge, "cudaGraphLaunch");
+            else s->launches += s->stream_graph_kernels;
+        } else {
+            if (step == 0) r.argmax(s->logits, s->tokens + pos, nullptr);
+            r.step(pos, true, false);
+            // tokens has n_ctx + 1 slots, so the pick at the last position has a place to go.
+            r.argmax(s->logits, s->tokens + pos + 1, s->readback + slot);
+        }
         if (r.status != BC_OK) {
             result = r.status;
             break;
@@ -546,7 +656,7 @@ bc_status bc_seq_generate_stream(bc_seq* s, uint32_t max_tokens, bc_emit_fn emit
     }
     // Finish the steps still in flight in submission order, which is the order of their tokens.
     for (int offset = 0; offset < kGenerateInFlight; ++offset) {
-        int slot = (int)((committed + offset) % kGenerateInFlight);
+        int slot = (int)((start + committed + offset) % kGenerateInFlight);
         if (!pending[slot]) continue;
         bc_status st = finish_slot(slot);
         if (st != BC_OK && result == BC_OK) result = st;

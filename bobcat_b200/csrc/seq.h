@@ -49,5 +49,15 @@ struct bc_seq {
     cudaEvent_t slot_done[kGenerateInFlight] = {};
     cudaEvent_t timing_start = nullptr, timing_end = nullptr;
 
+    // Replayed decode: the launches of one generated step are captured once into a CUDA graph whose
+    // kernels read the position from `step_pos` on the device, then replayed once per token
+    // (the reference's plan for stable commands, docs/design.md:94-98).
+    uint32_t* step_pos = nullptr;             // device word: position of the step being run
+    cudaGraphExec_t generate_graph = nullptr; // argmax -> tokens[pos], forward pass at pos
+    cudaGraphExec_t stream_graph = nullptr;   // forward pass at pos, argmax -> tokens[pos + 1] and the readback ring
+    uint64_t generate_graph_kernels = 0, stream_graph_kernels = 0;  // kernels per replay, for the launch count
+    uint32_t host_pos = 0;                    // staging for the seed of step_pos
+    bool use_graphs = true;                   // BOBCAT_NO_GRAPH=1 turns replay off (launch every kernel eagerly)
+
     ~bc_seq();
 };
