@@ -133,6 +133,28 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
 // a host-mapped word that receives the same value.
 cudaError_t argmax(cudaStream_t stream, const float* x, uint32_t n, uint32_t* out, uint32_t* readback);
 
+// ---- mixture of experts (kernels_moe.cu). A token's route is 2 * n_used words: expert ids, then
+// weights as float bits.
+// Router: optional RMSNorm (normalised tokens also go to `normed`), F32 router logits in f64,
+// sigmoid, top n_used of score + bias with ties to the lower id, weights = score / (sum + 1e-6).
+cudaError_t moe_route(cudaStream_t stream, const float* x, Norm norm, float* normed, const float* router, const float* bias,
+                      uint32_t* route, uint32_t n_cols, uint32_t n_experts, uint32_t n_used, uint32_t n_tokens);
+// Counting sort of the (token, slot) entries by expert: offsets[n_experts + 1], entries[n_tokens * n_used].
+cudaError_t moe_group(cudaStream_t stream, const uint32_t* route, uint32_t* offsets, uint32_t* entries, uint32_t n_experts,
+                      uint32_t n_used, uint32_t n_tokens);
+// Decode: y[token][slot][row] = silu(gate_e x) * (up_e x) for the slot's expert e; n_rows per expert.
+cudaError_t matvec_experts_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, uint32_t n_rows, const float* x,
+                                  const uint32_t* route, uint32_t n_used, float* y, uint32_t n_tokens);
+// Decode: y[token][row] += sum over slots of weight * (down_e row . x[token][slot]).
+cudaError_t matvec_experts_down(cudaStream_t stream, const Mat& down, uint32_t n_rows, const float* x, const uint32_t* route,
+                                uint32_t n_used, float* y, uint32_t n_tokens);
+// Prefill: for each expert, its entries times its rows; with `up` the store is silu(gate) * up.
+// Input rows are the tokens' (gather) or the entries' own; output rows are the entries'.
+cudaError_t matmul_experts(cudaStream_t stream, const Mat& w, const Mat* up, uint32_t n_rows, uint32_t n_experts, const float* x,
+                           bool gather, const uint32_t* offsets, const uint32_t* entries, uint32_t n_used, float* y, uint32_t n_tokens);
+cudaError_t moe_combine(cudaStream_t stream, const float* expert_out, const uint32_t* route, float* y, uint32_t n_embd,
+                        uint32_t n_used, uint32_t n_tokens);
+
 // Y[t][r] (store) sum_c W[r][c] X[t][c]. X is [n_tokens][n_cols] f32, Y is [n_tokens][y_stride].
 cudaError_t matmul(cudaStream_t stream, const Mat& w, const float* x, float* y, uint32_t n_tokens, uint32_t y_stride,
                    int32_t store);

@@ -24,9 +24,7 @@
 #include <mutex>
 #include <utility>
 
-#include "device_utils.cuh"
-#include "kernels.h"
-#include "../../include/bobcat_cuda.h"
+#include "matvec_common.cuh"
 
 namespace bc {
 namespace k {
@@ -39,151 +37,6 @@ constexpr int kWarps = kThreads / 32;
 constexpr uint32_t kPrefetchCap = 96 * 1024;
 
 enum Mode { kPlain = 0, kSwiglu = 1, kConv = 2 };
-
-struct RowPtr {
-    const void* data;      // first byte of the row's weights
-    const __half* scales;  // first scale of the row (Q4_0 only)
-};
-
-__device__ __forceinline__ RowPtr row_of(const Mat& m, uint32_t row) {
-    RowPtr p;
-    if (m.format == BC_Q4_0) {
-        uint64_t nb = m.n_cols >> 5;
-        p.data = static_cast<const uint4*>(m.data) + row * nb;
-        p.scales = m.scales + row * nb;
-    } else if (m.format == BC_F16) {
-        p.data = static_cast<const __half*>(m.data) + (uint64_t)row * m.n_cols;
-        p.scales = nullptr;
-    } else {
-        p.data = static_cast<const float*>(m.data) + (uint64_t)row * m.n_cols;
-        p.scales = nullptr;
-    }
-    return p;
-}
-
-// Ask the L2 to fetch [p, p + bytes); both must be multiples of 16.
-__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-
-template <int FORMAT>
-__device__ __forceinline__ void prefetch_row(const RowPtr& r, uint32_t n_cols) {
-    if (FORMAT == BC_Q4_0) {
-        uint32_t nb = n_cols >> 5;
-        prefetch_l2(r.data, nb * 16);
-        if ((reinterpret_cast<uintptr_t>(r.scales) & 15) == 0 && (nb & 7) == 0) prefetch_l2(r.scales, nb * 2);
-    } else {
-        prefetch_l2(r.data, n_cols * (FORMAT == BC_F16 ? 2u : 4u));
-    }
-}
-
-// Stage x into shared memory in the rotated chunk layout, times the norm weight when given.
-// Returns the factor the finished row sums are multiplied by (1 without a norm).
-__device__ float stage_input(const float* __restrict__ x, const float* __restrict__ norm_weight, float eps,
-                             uint32_t n_cols, float4* xs, float* reduce_scratch) {
-    const float4* x4 = reinterpret_cast<const float4*>(x);
-    const float4* w4 = reinterpret_cast<const float4*>(norm_weight);
-    float sumsq = 0.f;
-    for (uint32_t ci = threadIdx.x; ci < n_cols / 4; ci += blockDim.x) {
-        float4 v = x4[ci];
-        if (norm_weight) {
-            sumsq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-            float4 w = __ldg(w4 + ci);
-            v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
-        }
-        xs[x_slot(ci >> 3, ci & 7)] = v;
-    }
-    float scale = 1.f;
-    if (norm_weight) {
-        float total = block_sum(sumsq, reduce_scratch);
-        scale = rsqrtf(total / (float)n_cols + eps);
-    } else {
-        __syncthreads();
-    }
-    return scale;
-}
-
-// Partial dot products of R rows with the staged input over this warp's share of the columns:
-// part `kpart` of `ksplit` interleaved parts, each a stride of 32 lanes.
-template <int FORMAT, int R>
-__device__ __forceinline__ void dot_rows(const RowPtr (&rows)[R], uint32_t n_cols, const float4* __restrict__ xs, int lane,
-                                         int kpart, int ksplit, float (&acc)[R]) {
-#pragma unroll
-    for (int r = 0; r < R; ++r) acc[r] = 0.f;
-    const int step = 32 * ksplit;
-    if (FORMAT == BC_Q4_0) {
-        const int nb = n_cols >> 5;
-#pragma unroll 2
-        for (int b0 = kpart * 32; b0 < nb; b0 += step) {
-            int b = b0 + lane;
-            bool live = b < nb;
-            int bc_ = live ? b : nb - 1;
-            uint4 q[R];
-            float d[R];
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                q[r] = ldg_stream(static_cast<const uint4*>(rows[r].data) + bc_);
-                d[r] = live ? __half2float(rows[r].scales[bc_]) : 0.f;
-            }
-            float sum[R];
-#pragma unroll
-            for (int r = 0; r < R; ++r) sum[r] = 0.f;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                float4 xl = xs[x_slot(bc_, w)];
-                float4 xh = xs[x_slot(bc_, 4 + w)];
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    uint32_t word = w == 0 ? q[r].x : w == 1 ? q[r].y : w == 2 ? q[r].z : q[r].w;
-                    float lo[4], hi[4];
-                    unpack_q4_word(word, lo, hi);
-                    sum[r] += lo[0] * xl.x + lo[1] * xl.y + lo[2] * xl.z + lo[3] * xl.w;
-                    sum[r] += hi[0] * xh.x + hi[1] * xh.y + hi[2] * xh.z + hi[3] * xh.w;
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < R; ++r) acc[r] += d[r] * sum[r];
-        }
-    } else if (FORMAT == BC_F32) {
-        const int nc = n_cols >> 2;
-#pragma unroll 4
-        for (int c0 = kpart * 32; c0 < nc; c0 += step) {
-            int c = c0 + lane;
-            bool live = c < nc;
-            int cc = live ? c : nc - 1;
-            float4 xv = xs[x_slot(cc >> 3, cc & 7)];
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                float4 w = ldg_stream(static_cast<const float4*>(rows[r].data) + cc);
-                float s = w.x * xv.x + w.y * xv.y + w.z * xv.z + w.w * xv.w;
-                acc[r] += live ? s : 0.f;
-            }
-        }
-    } else {  // BC_F16
-        const int nc = n_cols >> 3;
-#pragma unroll 2
-        for (int c0 = kpart * 32; c0 < nc; c0 += step) {
-            int c = c0 + lane;
-            bool live = c < nc;
-            int cc = live ? c : nc - 1;
-            float4 x0 = xs[x_slot(cc >> 2, (2 * cc) & 7)];
-            float4 x1 = xs[x_slot(cc >> 2, (2 * cc + 1) & 7)];
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                uint4 w = ldg_stream(static_cast<const uint4*>(rows[r].data) + cc);
-                float2 a = __half22float2(*reinterpret_cast<__half2*>(&w.x));
-                float2 b = __half22float2(*reinterpret_cast<__half2*>(&w.y));
-                float2 c2 = __half22float2(*reinterpret_cast<__half2*>(&w.z));
-                float2 e = __half22float2(*reinterpret_cast<__half2*>(&w.w));
-                float s = a.x * x0.x + a.y * x0.y + b.x * x0.z + b.y * x0.w + c2.x * x1.x + c2.y * x1.y + e.x * x1.z +
-                          e.y * x1.w;
-                acc[r] += live ? s : 0.f;
-            }
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < R; ++r) acc[r] = warp_sum(acc[r]);
-}
 
 struct Params {
     // kPlain: up to three matrices that share x; kSwiglu: seg[0] = gate, seg[1] = up;

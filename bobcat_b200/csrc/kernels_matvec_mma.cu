@@ -36,7 +36,7 @@ namespace k {
 
 namespace {
 
-constexpr int kConsumers = 8;                    // consumer warps per CTA
+constexpr int kConsumers = 16;                   // consumer warps per CTA
 constexpr int kThreads = (kConsumers + 1) * 32;  // plus the producer warp
 constexpr int kDepth = 2;                        // ring slots per consumer warp
 constexpr int kStages = kConsumers * kDepth;
@@ -85,6 +85,13 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The same with a zero accumulator going in.
+__device__ __forceinline__ void mma_16816_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
 // The eight 4-bit quants of a word, minus 8, as four half2 registers of exact integers:
@@ -150,6 +157,15 @@ __device__ __forceinline__ const uint8_t* job_tiles(const Params& p, uint32_t jo
     return p.tiles[0] + ((uint64_t)s * (p.n_embd / 16) + job) * tile_bytes;
 }
 
+// Warps per group: the warps of a group share one job, taking its chunks in turn, so a CTA with only
+// a few jobs still keeps all its warps busy. The smallest power of two that covers the job's
+// chunks, at most all consumers.
+__device__ __forceinline__ uint32_t group_size(uint32_t q_per_job) {
+    uint32_t gs = 1;
+    while (gs < (uint32_t)kConsumers && gs < q_per_job) gs *= 2;
+    return gs;
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1) matvec_mma_kernel(Params p) {
     constexpr int S = segments_per_job<MODE>();
@@ -158,15 +174,17 @@ __global__ void __launch_bounds__(kThreads, 1) matvec_mma_kernel(Params p) {
     uint4* xs = reinterpret_cast<uint4*>(smem + kStages * kStageBytes);     // [block][hi | lo][t]: 8 x 16 bytes per block
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
     __shared__ float reduce_scratch[64];
+    __shared__ float partial[2][kConsumers][3 * 16];  // [job parity][warp][segment * 16 + row in tile]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t nb = p.n_blocks;
     const uint32_t tile_bytes = nb * kBlockBytes;
     const uint32_t chunks = (nb + kChunkBlocks - 1) / kChunkBlocks;  // per tile
     const uint32_t q_per_job = S * chunks;
-    // Jobs of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ... dealt round-robin to its warps.
+    const uint32_t gs = group_size(q_per_job), groups = kConsumers / gs;
+    // Jobs of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ... Job m goes to group m % groups.
     const uint32_t my_jobs = p.n_jobs > blockIdx.x ? (p.n_jobs - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const uint32_t rounds = (my_jobs + kConsumers - 1) / kConsumers;
+    const uint32_t rounds = (my_jobs + groups - 1) / groups;
 
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
@@ -179,26 +197,33 @@ __global__ void __launch_bounds__(kThreads, 1) matvec_mma_kernel(Params p) {
     pdl_launch_dependents();
 
     if (warp == kConsumers) {
-        // ---- producer: one thread streams this CTA's chunks into the ring, in the order the
-        // consumers take them: round by round, chunk position by chunk position, warp by warp.
+        // ---- producer: one thread streams this CTA's chunks into the ring in the order the
+        // consumers take them: round by round, chunk position by chunk position, group by group.
+        // Each warp owns kDepth slots; its k-th chunk goes to its slot k % kDepth, so every slot is
+        // filled and drained by one pair of threads in strict order.
         if (lane == 0) {
+            uint32_t issued[kConsumers];
+#pragma unroll
+            for (int w = 0; w < kConsumers; ++w) issued[w] = 0;
             bool ok = true;
             for (uint32_t r = 0; r < rounds && ok; ++r) {
-                uint32_t in_round = min((uint32_t)kConsumers, my_jobs - r * kConsumers);
+                uint32_t in_round = min(groups, my_jobs - r * groups);
                 for (uint32_t q = 0; q < q_per_job && ok; ++q) {
                     uint32_t seg = q / chunks, chunk = q % chunks;
                     uint32_t cb = min((uint32_t)kChunkBlocks, nb - chunk * kChunkBlocks);
-                    // Warp w's n-th chunk goes to slot n % kDepth of that warp's own slots, so each
-                    // slot is filled and drained by one pair of threads in strict order.
-                    const uint32_t n = r * q_per_job + q;
-                    for (uint32_t w = 0; w < in_round; ++w) {
-                        uint32_t stage = w * kDepth + n % kDepth, use = n / kDepth;
+                    for (uint32_t grp = 0; grp < in_round; ++grp) {
+                        uint32_t w = grp * gs + q % gs;
+                        uint32_t k = 0;
+#pragma unroll
+                        for (int i = 0; i < kConsumers; ++i)
+                            if ((uint32_t)i == w) k = issued[i]++;
+                        uint32_t stage = w * kDepth + k % kDepth, use = k / kDepth;
                         if (use > 0 && !mbar_wait(smem_u32(&empty_bar[stage]), (use - 1) & 1)) {
                             atomicExch(&g_error_flag, 1);
                             ok = false;
                             break;
                         }
-                        uint32_t job = blockIdx.x + gridDim.x * (r * kConsumers + w);
+                        uint32_t job = blockIdx.x + gridDim.x * (r * groups + grp);
                         const uint8_t* src = job_tiles<MODE>(p, job, (int)seg, tile_bytes) + (uint64_t)chunk * kStageBytes;
                         uint32_t bytes = cb * kBlockBytes;
                         mbar_arrive_expect(smem_u32(&full_bar[stage]), bytes);
@@ -214,8 +239,8 @@ __global__ void __launch_bounds__(kThreads, 1) matvec_mma_kernel(Params p) {
     // history) belong to earlier launches.
     pdl_wait();
 
-    // Stage x: the rotation-free layout the B fragments want. For block b and word index t the 16
-    // bytes at xs[b * 8 + part * 4 + t] hold half2(x[4t], x[4t+2]), half2(x[4t+1], x[4t+3]),
+    // Stage x in the layout the B fragments want. For block b and word index t the 16 bytes at
+    // xs[b * 8 + part * 4 + t] hold half2(x[4t], x[4t+2]), half2(x[4t+1], x[4t+3]),
     // half2(x[16+4t], x[16+4t+2]), half2(x[16+4t+1], x[16+4t+3]) of the block, as the high fp16
     // part (part 0) or the low part (part 1) of x * 2^shift. The shift brings the largest |x| to
     // [2^13, 2^14), so neither part loses bits to fp16's narrow exponent range.
@@ -272,88 +297,115 @@ __global__ void __launch_bounds__(kThreads, 1) matvec_mma_kernel(Params p) {
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
 
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t ring_base = smem_u32(ring);
-    for (uint32_t r = 0; r * kConsumers + warp < my_jobs; ++r) {
-        const uint32_t job = blockIdx.x + gridDim.x * (r * kConsumers + warp);
+    const uint32_t ring_base = smem_u32(ring), xs_base = smem_u32(xs);
+    const uint32_t grp = warp / gs, rank = warp % gs;
+    uint32_t taken = 0;  // chunks this warp has consumed
+    bool dead = false;
+    for (uint32_t r = 0; r * groups + grp < my_jobs; ++r) {
+        const uint32_t job = blockIdx.x + gridDim.x * (r * groups + grp);
         float acc[S][2];
 #pragma unroll
         for (int s = 0; s < S; ++s) acc[s][0] = acc[s][1] = 0.f;
+        for (uint32_t q = rank; q < q_per_job; q += gs, ++taken) {
+            const uint32_t s_of_q = q / chunks, chunk = q % chunks;
+            const uint32_t stage = warp * kDepth + taken % kDepth, use = taken / kDepth;
+            // A wait that runs out marks the launch failed; the warp then skips its remaining chunks
+            // but still meets its group at every barrier, so nothing is left waiting on it.
+            if (!dead && !mbar_wait(smem_u32(&full_bar[stage]), use & 1)) {
+                atomicExch(&g_error_flag, 2);
+                dead = true;
+            }
+            if (dead) continue;
+            const uint32_t cb = min((uint32_t)kChunkBlocks, nb - chunk * kChunkBlocks);
+            // 32-bit shared-memory addresses of this lane's quants, scales and inputs.
+            uint32_t q_addr = ring_base + stage * kStageBytes + lane * 16;
+            uint32_t s_addr = ring_base + stage * kStageBytes + cb * 256 + g * 2;
+            uint32_t x_addr = xs_base + (chunk * kChunkBlocks * 8 + g * 4 + t) * 16;
+            float a0 = 0.f, a1 = 0.f;
+            for (uint32_t pair = 0; pair < cb / 2; ++pair, q_addr += 512, s_addr += 64, x_addr += 256) {
+                uint4 v;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(q_addr));
 #pragma unroll
-        for (int s = 0; s < S; ++s) {
-            for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
-                const uint32_t q = s * chunks + chunk;
-                const uint32_t n = r * q_per_job + q;
-                const uint32_t stage = warp * kDepth + n % kDepth, use = n / kDepth;
-                if (!mbar_wait(smem_u32(&full_bar[stage]), use & 1)) {
-                    atomicExch(&g_error_flag, 2);
-                    return;
+                for (int half_pair = 0; half_pair < 2; ++half_pair) {
+                    uint32_t ha[4], hb[4];
+                    unpack_word_half2(half_pair ? v.z : v.x, ha);  // row g
+                    unpack_word_half2(half_pair ? v.w : v.y, hb);  // row g + 8
+                    uint4 xb = make_uint4(0, 0, 0, 0);
+                    if (g < 2) asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xb.x), "=r"(xb.y), "=r"(xb.z), "=r"(xb.w) : "r"(x_addr + half_pair * 128));
+                    float c[4];
+                    mma_16816_zero(c, ha[0], hb[0], ha[1], hb[1], xb.x, xb.y);
+                    mma_16816(c, ha[2], hb[2], ha[3], hb[3], xb.z, xb.w);
+                    uint16_t d0h, d1h;
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(d0h) : "r"(s_addr + half_pair * 32));
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(d1h) : "r"(s_addr + half_pair * 32 + 16));
+                    a0 = fmaf(c[0] + c[1], __half2float(__ushort_as_half(d0h)), a0);
+                    a1 = fmaf(c[2] + c[3], __half2float(__ushort_as_half(d1h)), a1);
                 }
-                const uint32_t cb = min((uint32_t)kChunkBlocks, nb - chunk * kChunkBlocks);
-                const uint32_t quants = ring_base + stage * kStageBytes;
-                const __half* scales = reinterpret_cast<const __half*>(ring + stage * kStageBytes + cb * 256);
-                for (uint32_t pair = 0; pair < cb / 2; ++pair) {
-                    uint4 v;
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(quants + (pair * 32 + lane) * 16));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
 #pragma unroll
-                    for (int half_pair = 0; half_pair < 2; ++half_pair) {
-                        const uint32_t local = pair * 2 + half_pair;              // block within the chunk
-                        const uint32_t block = chunk * kChunkBlocks + local;      // block within the row
-                        uint32_t ha[4], hb[4];
-                        unpack_word_half2(half_pair ? v.z : v.x, ha);  // row g
-                        unpack_word_half2(half_pair ? v.w : v.y, hb);  // row g + 8
-                        uint4 xb = make_uint4(0, 0, 0, 0);
-                        if (g < 2) xb = xs[block * 8 + g * 4 + t];
-                        float c[4] = {0.f, 0.f, 0.f, 0.f};
-                        mma_16816(c, ha[0], hb[0], ha[1], hb[1], xb.x, xb.y);
-                        mma_16816(c, ha[2], hb[2], ha[3], hb[3], xb.z, xb.w);
-                        float d0 = __half2float(scales[local * 16 + g]), d1 = __half2float(scales[local * 16 + g + 8]);
-                        acc[s][0] += (c[0] + c[1]) * d0;
-                        acc[s][1] += (c[2] + c[3]) * d1;
-                    }
+            for (int s = 0; s < S; ++s) {
+                if ((uint32_t)s == s_of_q) {
+                    acc[s][0] += a0;
+                    acc[s][1] += a1;
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
             }
         }
-        // Columns 0 and 1 of the product (the high and low parts of x) live in the lanes with t == 0.
+        // Columns 0 and 1 of the product (the high and low parts of x) live in the lanes with
+        // t == 0. The group's warps leave their partial sums in shared memory; after the group's
+        // barrier its first warp adds them in warp order and finishes the 16 rows.
+        const int parity = r & 1;
         if (t == 0) {
 #pragma unroll
-            for (int half_tile = 0; half_tile < 2; ++half_tile) {
-                const uint32_t in_tile = g + 8 * half_tile;
-                if (MODE == kPlain) {
-                    int seg = 0;
-                    uint32_t local = job;
-                    while (seg + 1 < p.n_segments && local >= p.seg_tiles[seg]) {
-                        local -= p.seg_tiles[seg];
-                        ++seg;
-                    }
-                    uint32_t row = local * 16 + in_tile;
-                    if (row < p.seg_rows[seg]) {
-                        float v = acc[0][half_tile] * out_scale;
-                        float* y = p.y[seg] + row;
-                        *y = p.accumulate ? *y + v : v;
-                    }
-                } else if (MODE == kSwiglu) {
-                    uint32_t row = job * 16 + in_tile;
-                    if (row < p.seg_rows[0]) {
-                        float gate = acc[0][half_tile] * out_scale, upv = acc[S > 1 ? 1 : 0][half_tile] * out_scale;
-                        p.y[0][row] = gate / (1.f + expf(-gate)) * upv;
-                    }
-                } else {
-                    // B, C and X of channel ch; the taps over B*X and the channel's history; the
-                    // history shift; C * conv (crates/bobcat/src/lfm2.rs:456-475, f32 sums).
-                    uint32_t ch = job * 16 + in_tile;
-                    if (ch < p.n_embd) {
-                        float b = acc[0][half_tile] * out_scale, c = acc[S > 1 ? 1 : 0][half_tile] * out_scale, xv = acc[S > 2 ? 2 : 0][half_tile] * out_scale;
-                        float bx = b * xv;
-                        const uint32_t K = p.conv_kernel;
-                        const float* taps = p.taps + (uint64_t)ch * K;
-                        float sum = taps[K - 1] * bx;
-                        for (uint32_t kk = 0; kk + 1 < K; ++kk) sum += taps[kk] * p.history[(uint64_t)kk * p.n_embd + ch];
-                        for (uint32_t kk = 0; kk + 2 < K; ++kk) p.history[(uint64_t)kk * p.n_embd + ch] = p.history[(uint64_t)(kk + 1) * p.n_embd + ch];
-                        p.history[(uint64_t)(K - 2) * p.n_embd + ch] = bx;
-                        p.y[0][ch] = c * sum;
-                    }
+            for (int s = 0; s < S; ++s) {
+                partial[parity][warp][s * 16 + g] = acc[s][0];
+                partial[parity][warp][s * 16 + g + 8] = acc[s][1];
+            }
+        }
+        if (gs > 1) asm volatile("bar.sync %0, %1;" ::"r"(2 + grp), "r"(gs * 32) : "memory");
+        else __syncwarp();
+        if (rank == 0 && lane < 16) {
+            float sum[S];
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                sum[s] = 0.f;
+                for (uint32_t w = 0; w < gs; ++w) sum[s] += partial[parity][warp + w][s * 16 + lane];
+                sum[s] *= out_scale;
+            }
+            const uint32_t in_tile = lane;
+            if (MODE == kPlain) {
+                int seg = 0;
+                uint32_t local = job;
+                while (seg + 1 < p.n_segments && local >= p.seg_tiles[seg]) {
+                    local -= p.seg_tiles[seg];
+                    ++seg;
+                }
+                uint32_t row = local * 16 + in_tile;
+                if (row < p.seg_rows[seg]) {
+                    float* y = p.y[seg] + row;
+                    *y = p.accumulate ? *y + sum[0] : sum[0];
+                }
+            } else if (MODE == kSwiglu) {
+                uint32_t row = job * 16 + in_tile;
+                if (row < p.seg_rows[0]) {
+                    float gate = sum[0], upv = sum[S > 1 ? 1 : 0];
+                    p.y[0][row] = gate / (1.f + expf(-gate)) * upv;
+                }
+            } else {
+                // B, C and X of channel ch; the taps over B*X and the channel's history; the
+                // history shift; C * conv (crates/bobcat/src/lfm2.rs:456-475, f32 sums).
+                uint32_t ch = job * 16 + in_tile;
+                if (ch < p.n_embd) {
+                    float b = sum[0], c = sum[S > 1 ? 1 : 0], xv = sum[S > 2 ? 2 : 0];
+                    float bx = b * xv;
+                    const uint32_t K = p.conv_kernel;
+                    const float* taps = p.taps + (uint64_t)ch * K;
+                    float total_taps = taps[K - 1] * bx;
+                    for (uint32_t kk = 0; kk + 1 < K; ++kk) total_taps += taps[kk] * p.history[(uint64_t)kk * p.n_embd + ch];
+                    for (uint32_t kk = 0; kk + 2 < K; ++kk) p.history[(uint64_t)kk * p.n_embd + ch] = p.history[(uint64_t)(kk + 1) * p.n_embd + ch];
+                    p.history[(uint64_t)(K - 2) * p.n_embd + ch] = bx;
+                    p.y[0][ch] = c * total_taps;
                 }
             }
         }
