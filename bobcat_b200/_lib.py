@@ -71,6 +71,18 @@ SIGNATURES = {
     "bc_attention_static": (i32, [vp, vp, vp, vp, i32, vp] + [u32] * 6),
     "bc_op_argmax": (i32, [vp] + _VIEW + _VIEW + [u32]),
     "bc_op_silu_mul": (i32, [vp] + _VIEW + _VIEW + [u32]),
+    "bc_op_gdn_conv": (i32, [vp] + _VIEW + _VIEW + _VIEW + _VIEW + [u32] * 3),
+    "bc_op_gdn_gates": (i32, [vp] + _VIEW + _VIEW + _VIEW + _VIEW + [u32] * 2),
+    "bc_op_gdn_recurrence": (i32, [vp] + _VIEW + _VIEW + _VIEW + _VIEW + _VIEW + [u32] * 5 + [i32]),
+    "bc_op_gdn_gated_norm": (i32, [vp] + _VIEW + _VIEW + _VIEW + [u32, u32, f32]),
+    "bc_op_attention_gate": (i32, [vp] + _VIEW + _VIEW + [u32] * 3),
+    "bc_route_bytes": (sz, [u32, u32]),
+    "bc_op_moe_route": (i32, [vp] + _VIEW + _VIEW + [f32] + _VIEW + _VIEW + _VIEW + _VIEW + [u32] * 4),
+    "bc_op_moe_group": (i32, [vp] + _VIEW + _VIEW + _VIEW + [u32] * 3),
+    "bc_op_matvec_experts_swiglu": (i32, [vp, i32] + _VIEW + _VIEW + [u32] * 3 + _VIEW + _VIEW + [u32] + _VIEW + [u32]),
+    "bc_op_matvec_experts_down": (i32, [vp, i32] + _VIEW + [u32] * 3 + _VIEW + _VIEW + [u32] + _VIEW + [u32]),
+    "bc_op_matmul_experts": (i32, [vp, i32] + _VIEW + _VIEW + [u32] * 3 + _VIEW + [i32] + _VIEW + _VIEW + [u32] + _VIEW + [u32]),
+    "bc_op_moe_combine": (i32, [vp] + _VIEW + _VIEW + _VIEW + [u32] * 3),
     "bc_model_load": (i32, [C.c_char_p, C.POINTER(vp)]),
     "bc_model_free": (None, [vp]),
     "bc_model_hparams": (i32, [vp, C.POINTER(Hparams)]),

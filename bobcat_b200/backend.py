@@ -213,6 +213,55 @@ class Cuda:
     def argmax(self, x, out, n) -> None:
         self._check(self._L.bc_op_argmax(self._h, *_v(x), *_v(out), n))
 
+    # ---- mixture of experts (argument order of backend.rs:1428-1737)
+    def route_bytes(self, n_used, n_tokens) -> int:
+        return int(self._L.bc_route_bytes(n_used, n_tokens))
+
+    def moe_route(self, x, norm, router, bias, route, n_cols, n_experts, n_used, n_tokens) -> None:
+        """``norm`` is None or ``(Norm, normed_view)``."""
+        if norm is None:
+            nb, no, eps, ob, oo = None, 0, 0.0, None, 0
+        else:
+            (nb, no), eps, (ob, oo) = _v(norm[0].weight), norm[0].eps, _v(norm[1])
+        self._check(self._L.bc_op_moe_route(self._h, *_v(x), nb, no, eps, ob, oo, *_v(router), *_v(bias), *_v(route), n_cols, n_experts,
+                                            n_used, n_tokens))
+
+    def moe_group(self, route, offsets, entries, n_experts, n_used, n_tokens) -> None:
+        self._check(self._L.bc_op_moe_group(self._h, *_v(route), *_v(offsets), *_v(entries), n_experts, n_used, n_tokens))
+
+    def matvec_experts_swiglu(self, fmt, gate, up, n_rows, n_cols, n_experts, x, route, n_used, y, n_tokens) -> None:
+        self._check(self._L.bc_op_matvec_experts_swiglu(self._h, fmt, *_v(gate), *_v(up), n_rows, n_cols, n_experts, *_v(x), *_v(route), n_used,
+                                                        *_v(y), n_tokens))
+
+    def matvec_experts_down(self, fmt, down, n_rows, n_cols, n_experts, x, route, n_used, y, n_tokens) -> None:
+        self._check(self._L.bc_op_matvec_experts_down(self._h, fmt, *_v(down), n_rows, n_cols, n_experts, *_v(x), *_v(route), n_used, *_v(y),
+                                                      n_tokens))
+
+    def matmul_experts(self, fmt, weights, up, n_rows, n_cols, n_experts, x, gather, offsets, entries, n_used, y, n_tokens) -> None:
+        ub, uo = _v(up)
+        self._check(self._L.bc_op_matmul_experts(self._h, fmt, *_v(weights), ub, uo, n_rows, n_cols, n_experts, *_v(x), int(gather), *_v(offsets),
+                                                 *_v(entries), n_used, *_v(y), n_tokens))
+
+    def moe_combine(self, expert_out, route, y, n_embd, n_used, n_tokens) -> None:
+        self._check(self._L.bc_op_moe_combine(self._h, *_v(expert_out), *_v(route), *_v(y), n_embd, n_used, n_tokens))
+
+    # ---- Qwen3.5 (argument order of backend.rs:1739-2032)
+    def gdn_conv(self, x, taps, history, out, conv_dim, kernel, n_tokens) -> None:
+        self._check(self._L.bc_op_gdn_conv(self._h, *_v(x), *_v(taps), *_v(history), *_v(out), conv_dim, kernel, n_tokens))
+
+    def gdn_gates(self, beta, alpha, a, dt_bias, n_v_heads, n_tokens) -> None:
+        self._check(self._L.bc_op_gdn_gates(self._h, *_v(beta), *_v(alpha), *_v(a), *_v(dt_bias), n_v_heads, n_tokens))
+
+    def gdn_recurrence(self, qkv, beta, decay, state, out, n_k_heads, n_v_heads, k_dim, v_dim, n_tokens, normalize=True) -> None:
+        self._check(self._L.bc_op_gdn_recurrence(self._h, *_v(qkv), *_v(beta), *_v(decay), *_v(state), *_v(out), n_k_heads, n_v_heads, k_dim,
+                                                 v_dim, n_tokens, int(normalize)))
+
+    def gdn_gated_norm(self, x, z, weight, v_dim, n_rows, eps) -> None:
+        self._check(self._L.bc_op_gdn_gated_norm(self._h, *_v(x), *_v(z), *_v(weight), v_dim, n_rows, eps))
+
+    def attention_gate(self, out, q_gate, n_heads, head_dim, n_tokens) -> None:
+        self._check(self._L.bc_op_attention_gate(self._h, *_v(out), *_v(q_gate), n_heads, head_dim, n_tokens))
+
     def silu_mul(self, x, gate, n) -> None:
         self._check(self._L.bc_op_silu_mul(self._h, *_v(x), *_v(gate), n))
 

@@ -34,7 +34,7 @@ struct Norm {
     float eps = 0.f;
 };
 
-// Up to three matrices that share an input vector, multiplied in one launch.
+// Up to four matrices that share an input vector, multiplied in one launch.
 struct MatvecSegment {
     Mat w;
     float* y = nullptr;
@@ -132,6 +132,22 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
 // argmax over n floats, ties to the lowest index. `out` is a device word; `readback` (nullable) is
 // a host-mapped word that receives the same value.
 cudaError_t argmax(cudaStream_t stream, const float* x, uint32_t n, uint32_t* out, uint32_t* readback);
+
+// ---- Qwen3.5 (kernels_gdn.cu)
+// DeltaNet causal convolution with SiLU over [n_tokens][conv_dim]; history [conv_dim][kernel - 1].
+cudaError_t gdn_conv(cudaStream_t stream, const float* x, const float* taps, float* history, float* out, uint32_t conv_dim,
+                     uint32_t kernel, uint32_t n_tokens);
+// In place: beta = sigmoid(beta); alpha = exp(a * softplus(alpha + dt_bias)).
+cudaError_t gdn_gates(cudaStream_t stream, float* beta, float* alpha, const float* a, const float* dt_bias, uint32_t n_v_heads,
+                      uint32_t n_tokens);
+// The gated delta rule over n_tokens; state [n_v_heads][k_dim][v_dim]; `normalize` L2-normalises q and k.
+cudaError_t gdn_recurrence(cudaStream_t stream, const float* qkv, const float* beta, const float* decay, float* state, float* out,
+                           uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t n_tokens, bool normalize);
+// x = RMSNorm(x) * weight * silu(z) per row of v_dim.
+cudaError_t gdn_gated_norm(cudaStream_t stream, float* x, const float* z, const float* weight, uint32_t v_dim, uint32_t n_rows,
+                           float eps);
+// out *= sigmoid(gate), the gate read from the interleaved [q | gate] projection.
+cudaError_t attention_gate(cudaStream_t stream, float* out, const float* q_gate, uint32_t n_heads, uint32_t head_dim, uint32_t n_tokens);
 
 // ---- mixture of experts (kernels_moe.cu). A token's route is 2 * n_used words: expert ids, then
 // weights as float bits.

@@ -1,0 +1,202 @@
+// Qwen3.5 kernels: the Gated DeltaNet layer (causal convolution, gates, the delta-rule recurrence,
+// the gated output norm) and the sigmoid output gate of Qwen's attention layers.
+// Counterparts: crates/bobcat-metal/src/gdn.metal (gdn_conv :14, gdn_gated_norm :106, gdn_gates :132,
+// gdn_qk_norm :181, gdn_recurrence :222, attention_gate :307); the arithmetic they must reproduce is
+// crates/bobcat/src/qwen35.rs:430-516 and :754-778, f32 throughout and in the reference's order.
+
+#include "device_utils.cuh"
+#include "kernels.h"
+
+namespace bc {
+namespace k {
+
+namespace {
+
+// One thread per channel, serial over tokens. x and out are [n_tokens][conv_dim]; taps are
+// [conv_dim][K], oldest first; history is [conv_dim][K - 1] raw inputs, oldest first. The sum starts
+// from the newest tap's term and adds the history terms oldest first (qwen35.rs:449-461). K <= 8.
+__global__ void gdn_conv_kernel(const float* __restrict__ x, const float* __restrict__ taps, float* __restrict__ history,
+                                float* __restrict__ out, uint32_t conv_dim, uint32_t kernel, uint32_t n_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= conv_dim) return;
+    const uint32_t H = kernel - 1;
+    float tap[8], past[7];
+    for (uint32_t i = 0; i < kernel; ++i) tap[i] = taps[(uint64_t)c * kernel + i];
+    for (uint32_t i = 0; i < H; ++i) past[i] = history[(uint64_t)c * H + i];
+    for (uint32_t t = 0; t < n_tokens; ++t) {
+        float input = x[(uint64_t)t * conv_dim + c];
+        float sum = tap[H] * input;
+        for (uint32_t i = 0; i < H; ++i) sum += tap[i] * past[i];
+        out[(uint64_t)t * conv_dim + c] = sum / (1.f + expf(-sum));
+        for (uint32_t i = 0; i + 1 < H; ++i) past[i] = past[i + 1];
+        past[H - 1] = input;
+    }
+    for (uint32_t i = 0; i < H; ++i) history[(uint64_t)c * H + i] = past[i];
+}
+
+// beta = sigmoid(beta); decay = exp(a * softplus(alpha + dt_bias)), softplus(x) = x above 20
+// (qwen35.rs:479-481, :776-778). In place over [n_tokens][n_v_heads]; alpha receives the decay.
+__global__ void gdn_gates_kernel(float* __restrict__ beta, float* __restrict__ alpha, const float* __restrict__ a,
+                                 const float* __restrict__ dt_bias, uint32_t n_v_heads, uint32_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    uint32_t head = i % n_v_heads;
+    beta[i] = 1.f / (1.f + expf(-beta[i]));
+    float v = alpha[i] + dt_bias[head];
+    float sp = v > 20.f ? v : log1pf(expf(v));
+    alpha[i] = expf(a[head] * sp);
+}
+
+struct RecurrenceParams {
+    const float* qkv;    // [n_tokens][2 * key_dim + value_dim]: q heads, k heads, v heads (after the conv)
+    const float* beta;   // [n_tokens][n_v_heads]
+    const float* decay;  // [n_tokens][n_v_heads]
+    float* state;        // [n_v_heads][k_dim][v_dim]
+    float* out;          // [n_tokens][n_v_heads * v_dim]
+    uint32_t n_k_heads, n_v_heads, k_dim, v_dim, n_tokens;
+    int normalize;       // L2-normalise q (times 1/sqrt(k_dim)) and k here, as decode does
+};
+
+// One CTA per value head, one thread per state column, which holds its k_dim state values in
+// registers for the whole run of tokens. Per token (qwen35.rs:483-506): S *= decay;
+// r = sum_i S[i] k_i; delta = (v - r) beta; S[i] += k_i delta; o = sum_i S[i] q_i, the sums in
+// row order. Value head h reads key head h % n_k_heads.
+template <int KDIM>
+__global__ void __launch_bounds__(256) gdn_recurrence_kernel(RecurrenceParams p) {
+    __shared__ float qs[KDIM], ks[KDIM];
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t head = blockIdx.x, j = threadIdx.x, vd = p.v_dim;
+    const uint32_t key_head = head % p.n_k_heads;
+    const uint32_t key_dim = p.n_k_heads * KDIM, conv_dim = 2 * key_dim + p.n_v_heads * vd;
+    float* state = p.state + (uint64_t)head * KDIM * vd;
+    float S[KDIM];
+    if (j < vd) {
+#pragma unroll
+        for (int i = 0; i < KDIM; ++i) S[i] = state[(uint64_t)i * vd + j];
+    }
+    for (uint32_t t = 0; t < p.n_tokens; ++t) {
+        const float* row = p.qkv + (uint64_t)t * conv_dim;
+        __syncthreads();  // the previous token's readers are done with qs and ks
+        if (p.normalize) {
+            // l2_normalize (qwen35.rs:762-768): f32 sum of squares, x *= scale / sqrt(sum + 1e-6).
+            float qv = j < KDIM ? row[key_head * KDIM + j] : 0.f;
+            float kv = j < KDIM ? row[key_dim + key_head * KDIM + j] : 0.f;
+            float qsum = block_sum(qv * qv, scratch);
+            float ksum = block_sum(kv * kv, scratch);
+            if (j < KDIM) {
+                qs[j] = qv * ((1.0f / sqrtf((float)KDIM)) / sqrtf(qsum + 1e-6f));
+                ks[j] = kv * (1.0f / sqrtf(ksum + 1e-6f));
+            }
+        } else if (j < KDIM) {
+            qs[j] = row[key_head * KDIM + j];
+            ks[j] = row[key_dim + key_head * KDIM + j];
+        }
+        __syncthreads();
+        if (j < vd) {
+            const float beta = p.beta[(uint64_t)t * p.n_v_heads + head], decay = p.decay[(uint64_t)t * p.n_v_heads + head];
+            const float v = row[2 * key_dim + head * vd + j];
+            float r = 0.f;
+#pragma unroll
+            for (int i = 0; i < KDIM; ++i) {
+                S[i] *= decay;
+                r += S[i] * ks[i];
+            }
+            const float delta = (v - r) * beta;
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < KDIM; ++i) {
+                S[i] += ks[i] * delta;
+                o += S[i] * qs[i];
+            }
+            p.out[(uint64_t)t * p.n_v_heads * vd + head * vd + j] = o;
+        }
+    }
+    if (j < vd) {
+#pragma unroll
+        for (int i = 0; i < KDIM; ++i) state[(uint64_t)i * vd + j] = S[i];
+    }
+}
+
+// One warp per (token, value head): x = RMSNorm(x) * weight * silu(z) (qwen35.rs:508-513).
+__global__ void gdn_gated_norm_kernel(float* __restrict__ x, const float* __restrict__ z, const float* __restrict__ weight,
+                                      uint32_t v_dim, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x;
+    float* row = x + (uint64_t)blockIdx.x * v_dim;
+    const float* gate = z + (uint64_t)blockIdx.x * v_dim;
+    float sumsq = 0.f;
+    for (uint32_t d = lane; d < v_dim; d += 32) sumsq += row[d] * row[d];
+    sumsq = warp_sum(sumsq);
+    const float scale = rsqrtf(sumsq / (float)v_dim + eps);
+    for (uint32_t d = lane; d < v_dim; d += 32) {
+        float g = gate[d];
+        row[d] = weight[d] * (row[d] * scale) * (g / (1.f + expf(-g)));
+    }
+}
+
+// out[t][h][d] *= sigmoid(gate) with the gate read from the interleaved q projection:
+// q_gate[t][h][head_dim + d] of [n_tokens][n_heads][2 * head_dim] (qwen35.rs:383-390, :422-424).
+__global__ void attention_gate_kernel(float* __restrict__ out, const float* __restrict__ q_gate, uint32_t n_heads, uint32_t head_dim,
+                                      uint64_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    uint32_t d = i % head_dim;
+    uint64_t th = i / head_dim;  // token * n_heads + head
+    float g = q_gate[th * 2 * head_dim + head_dim + d];
+    out[i] *= 1.f / (1.f + expf(-g));
+}
+
+}  // namespace
+
+cudaError_t gdn_conv(cudaStream_t stream, const float* x, const float* taps, float* history, float* out, uint32_t conv_dim,
+                     uint32_t kernel, uint32_t n_tokens) {
+    if (n_tokens == 0) return cudaSuccess;
+    void* args[] = {&x, &taps, &history, &out, &conv_dim, &kernel, &n_tokens};
+    return launch_kernel((const void*)gdn_conv_kernel, dim3((conv_dim + 127) / 128), dim3(128), 0, stream, args);
+}
+
+cudaError_t gdn_gates(cudaStream_t stream, float* beta, float* alpha, const float* a, const float* dt_bias, uint32_t n_v_heads,
+                      uint32_t n_tokens) {
+    uint32_t n = n_v_heads * n_tokens;
+    if (n == 0) return cudaSuccess;
+    void* args[] = {&beta, &alpha, &a, &dt_bias, &n_v_heads, &n};
+    return launch_kernel((const void*)gdn_gates_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, args);
+}
+
+cudaError_t gdn_recurrence(cudaStream_t stream, const float* qkv, const float* beta, const float* decay, float* state, float* out,
+                           uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t n_tokens, bool normalize) {
+    if (n_tokens == 0) return cudaSuccess;
+    RecurrenceParams p{qkv, beta, decay, state, out, n_k_heads, n_v_heads, k_dim, v_dim, n_tokens, normalize ? 1 : 0};
+    void* args[] = {&p};
+    // One thread per state column, and at least k_dim threads to stage q and k.
+    uint32_t threads = ((v_dim > k_dim ? v_dim : k_dim) + 31) / 32 * 32;
+    const void* kernel = k_dim == 32 ? (const void*)gdn_recurrence_kernel<32> : k_dim == 64 ? (const void*)gdn_recurrence_kernel<64>
+                       : k_dim == 96 ? (const void*)gdn_recurrence_kernel<96> : (const void*)gdn_recurrence_kernel<128>;
+    return launch_kernel(kernel, dim3(n_v_heads), dim3(threads), 0, stream, args);
+}
+
+cudaError_t gdn_gated_norm(cudaStream_t stream, float* x, const float* z, const float* weight, uint32_t v_dim, uint32_t n_rows,
+                           float eps) {
+    if (n_rows == 0) return cudaSuccess;
+    void* args[] = {&x, &z, &weight, &v_dim, &eps};
+    return launch_kernel((const void*)gdn_gated_norm_kernel, dim3(n_rows), dim3(32), 0, stream, args);
+}
+
+cudaError_t attention_gate(cudaStream_t stream, float* out, const float* q_gate, uint32_t n_heads, uint32_t head_dim, uint32_t n_tokens) {
+    uint64_t n = (uint64_t)n_tokens * n_heads * head_dim;
+    if (n == 0) return cudaSuccess;
+    void* args[] = {&out, &q_gate, &n_heads, &head_dim, &n};
+    return launch_kernel((const void*)attention_gate_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, args);
+}
+
+}  // namespace k
+}  // namespace bc

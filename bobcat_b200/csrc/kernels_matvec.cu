@@ -41,7 +41,7 @@ enum Mode { kPlain = 0, kSwiglu = 1, kConv = 2 };
 struct Params {
     // kPlain: up to three matrices that share x; kSwiglu: seg[0] = gate, seg[1] = up;
     // kConv: seg[0] = in_proj.
-    MatvecSegment seg[3];
+    MatvecSegment seg[4];
     int n_segments;
     uint32_t total_rows;  // kPlain: rows over all segments
     uint32_t units;       // kPlain: row pairs; kSwiglu: rows; kConv: channels

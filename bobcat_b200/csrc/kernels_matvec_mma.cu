@@ -123,10 +123,10 @@ struct Params {
     // Tile streams. kPlain: up to three matrices sharing x, one job per tile of their
     // concatenation. kSwiglu: gate, up; one job per tile pair. kConv: in_proj; a job is the tiles
     // of 16 channels' B, C and X rows.
-    const uint8_t* tiles[3];
-    float* y[3];
-    uint32_t seg_tiles[3];  // tiles per segment
-    uint32_t seg_rows[3];   // rows per segment (the last tile may be padded)
+    const uint8_t* tiles[4];
+    float* y[4];
+    uint32_t seg_tiles[4];  // tiles per segment
+    uint32_t seg_rows[4];   // rows per segment (the last tile may be padded)
     int n_segments;
     uint32_t n_jobs, n_blocks;  // blocks per row
     const float* x;

@@ -125,6 +125,39 @@ struct Recorder {
         matvec(D.down, s.ffn, s.hidden, k::Norm{}, true);
     }
 
+    // The mixture of experts on the n tokens of the batch, added to the residual stream
+    // (lfm2_metal.rs:1251-1370). With `fused_norm` the router launch normalises the residual stream
+    // into the normed buffer first; otherwise the normed buffer already holds the tokens. One token
+    // runs matrix-vector products on its experts; a batch groups its tokens by expert so each
+    // expert's weights stream once.
+    void lfm2_moe(const DeviceLayer& D, uint32_t n, bool fused_norm) {
+        const uint32_t n_used = hp.n_experts_used, n_ff = hp.n_ff_expert, n_embd = hp.n_embd;
+        const float* input = fused_norm ? s.hidden : s.normed;
+        k::Norm nm = fused_norm ? norm(D.ffn_norm) : k::Norm{};
+        run("moe_route", hp.n_experts, n_embd, D.router.bytes(), 1, [&] {
+            return k::moe_route(stream, input, nm, s.normed, static_cast<const float*>(D.router.data), D.expert_bias, s.route, n_embd, hp.n_experts,
+                                n_used, n);
+        });
+        // Bytes the experts stream: the picked experts of each token (decode) or every expert once (batch).
+        uint64_t expert_bytes = D.gate.bytes() / hp.n_experts;
+        if (n == 1) {
+            run("matvec_experts_swiglu", n_ff, n_embd, 2 * expert_bytes * n_used, 1,
+                [&] { return k::matvec_experts_swiglu(stream, D.gate, D.up, n_ff, s.normed, s.route, n_used, s.ffn, n); });
+            run("matvec_experts_down", n_embd, n_ff, expert_bytes * n_used, 1,
+                [&] { return k::matvec_experts_down(stream, D.down, n_embd, s.ffn, s.route, n_used, s.hidden, n); });
+            return;
+        }
+        run("moe_group", n, hp.n_experts, 0, 1, [&] { return k::moe_group(stream, s.route, s.expert_offsets, s.expert_entries, hp.n_experts, n_used, n); });
+        run("matmul_experts", n_ff, n_embd, 2 * D.gate.bytes(), 1, [&] {
+            return k::matmul_experts(stream, D.gate, &D.up, n_ff, hp.n_experts, s.normed, true, s.expert_offsets, s.expert_entries, n_used, s.ffn, n);
+        });
+        run("matmul_experts", n_embd, n_ff, D.down.bytes(), 1, [&] {
+            return k::matmul_experts(stream, D.down, nullptr, n_embd, hp.n_experts, s.ffn, false, s.expert_offsets, s.expert_entries, n_used,
+                                     s.expert_out, n);
+        });
+        run("moe_combine", n, n_embd, 0, 1, [&] { return k::moe_combine(stream, s.expert_out, s.route, s.hidden, n_embd, n_used, n); });
+    }
+
     void copy(const float* src, float* dst, uint64_t n) {
         run("copy", 1, (uint32_t)n, 0, 0, [&] { return k::copy_floats(stream, src, dst, n); });
     }
@@ -139,11 +172,8 @@ struct Recorder {
             const DeviceLayer& D = W.layers[il];
             if (S.mixer == Mixer::Attention) lfm2_attention(D, S.cache_index, pos);
             else lfm2_conv(D, S.cache_index);
-            if (S.moe) {
-                if (status == BC_OK) status = fail(BC_ERR_UNSUPPORTED, "mixture-of-experts layers are not built yet");
-            } else {
-                lfm2_dense_ffn(D);
-            }
+            if (S.moe) lfm2_moe(D, 1, true);
+            else lfm2_dense_ffn(D);
             if (traced) copy(s.hidden, s.trace_layers + il * hp.n_embd, hp.n_embd);
         }
         if (traced)
@@ -177,7 +207,7 @@ struct Recorder {
             }
             run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.ffn_norm, s.normed, n_embd, n, hp.norm_eps); });
             if (S.moe) {
-                if (status == BC_OK) status = fail(BC_ERR_UNSUPPORTED, "mixture-of-experts layers are not built yet");
+                lfm2_moe(D, n, false);
             } else {
                 // The up projection's store combines with the gate projection already in the
                 // buffer, which applies the SwiGLU.
@@ -192,20 +222,122 @@ struct Recorder {
         if (want_logits) matvec(W.output, s.hidden + (size_t)(n - 1) * n_embd, s.logits, norm(W.output_norm), false);
     }
 
-    void step(uint32_t pos, bool want_logits, bool traced) {
-        if (hp.architecture == BC_ARCH_QWEN35) {
-            if (status == BC_OK) status = fail(BC_ERR_UNSUPPORTED, "Qwen3.5 models are not built yet");
-            return;
+    // ---- Qwen3.5 (qwen35_metal.rs:867-1134)
+
+    uint32_t conv_dim() const { return 2 * hp.n_k_heads * hp.k_head_dim + hp.n_v_heads * hp.v_head_dim; }
+    uint32_t value_dim() const { return hp.n_v_heads * hp.v_head_dim; }
+
+    // The DeltaNet mixer from the conv onward, over n tokens whose projections sit in gdn_qkv,
+    // gdn_z, gdn_beta and gdn_alpha (qwen35_metal.rs:965-1033). The recurrence normalises q and k itself.
+    void qwen_delta_tail(const DeviceLayer& D, uint32_t cache_index, uint32_t n) {
+        const uint32_t K = hp.conv_kernel;
+        float* history = s.conv_state + (size_t)cache_index * conv_dim() * (K - 1);
+        float* state = s.delta_state + (size_t)cache_index * hp.n_v_heads * hp.k_head_dim * hp.v_head_dim;
+        run("gdn_conv", n, conv_dim(), 0, 1, [&] { return k::gdn_conv(stream, s.gdn_qkv, D.conv1d, history, s.gdn_conv_out, conv_dim(), K, n); });
+        run("gdn_gates", n, hp.n_v_heads, 0, 1, [&] { return k::gdn_gates(stream, s.gdn_beta, s.gdn_alpha, D.a, D.dt_bias, hp.n_v_heads, n); });
+        uint64_t state_bytes = (uint64_t)hp.n_v_heads * hp.k_head_dim * hp.v_head_dim * 4 * 2;
+        run("gdn_recurrence", n, value_dim(), state_bytes, 1, [&] {
+            return k::gdn_recurrence(stream, s.gdn_conv_out, s.gdn_beta, s.gdn_alpha, state, s.gdn_out, hp.n_k_heads, hp.n_v_heads, hp.k_head_dim,
+                                     hp.v_head_dim, n, true);
+        });
+        run("gdn_gated_norm", n * hp.n_v_heads, hp.v_head_dim, 0, 1,
+            [&] { return k::gdn_gated_norm(stream, s.gdn_out, s.gdn_z, D.ssm_norm, hp.v_head_dim, n * hp.n_v_heads, hp.norm_eps); });
+    }
+
+    // qwen35_metal.rs:1038-1134
+    void qwen_step(uint32_t pos, bool want_logits, bool traced) {
+        const DeviceModel& W = *s.weights;
+        const uint32_t q_dim = hp.n_heads * hp.head_dim;
+        run("embed", 1, hp.n_embd, 0, 1, [&] { return k::embed(stream, W.token_embd, s.tokens, at(pos), s.hidden, 1); });
+        if (traced) copy(s.hidden, s.trace_embedding, hp.n_embd);
+        for (size_t il = 0; il < W.layers.size(); ++il) {
+            const LayerSpec& S = s.model->layers[il];
+            const DeviceLayer& D = W.layers[il];
+            if (S.mixer == Mixer::Attention) {
+                // Each query head's rows hold its queries, then the gate of its output.
+                k::MatvecSegment segs[3] = {{D.q, s.q}, {D.k, s.k}, {D.v, s.v}};
+                run("matvec_qkv", D.q.n_rows + D.k.n_rows + D.v.n_rows, D.q.n_cols, D.q.bytes() + D.k.bytes() + D.v.bytes(), 1,
+                    [&] { return k::matvec(stream, segs, 3, s.hidden, norm(D.attn_norm), false); });
+                decode_attend(D, S.cache_index, pos, 2 * q_dim, 2 * hp.head_dim);
+                run("attention_gate", 1, q_dim, 0, 1, [&] { return k::attention_gate(stream, s.attn, s.q, hp.n_heads, hp.head_dim, 1); });
+                matvec(D.output, s.attn, s.hidden, k::Norm{}, true);
+            } else {
+                k::MatvecSegment segs[4] = {{D.qkv, s.gdn_qkv}, {D.z, s.gdn_z}, {D.beta, s.gdn_beta}, {D.alpha, s.gdn_alpha}};
+                uint64_t bytes = D.qkv.bytes() + D.z.bytes() + D.beta.bytes() + D.alpha.bytes();
+                run("matvec_delta", D.qkv.n_rows + D.z.n_rows + 2 * D.beta.n_rows, D.qkv.n_cols, bytes, 1,
+                    [&] { return k::matvec(stream, segs, 4, s.hidden, norm(D.attn_norm), false); });
+                qwen_delta_tail(D, S.cache_index, 1);
+                matvec(D.ssm_out, s.gdn_out, s.hidden, k::Norm{}, true);
+            }
+            lfm2_dense_ffn(D);
+            if (traced) copy(s.hidden, s.trace_layers + il * hp.n_embd, hp.n_embd);
         }
-        lfm2_step(pos, want_logits, traced);
+        if (traced)
+            run("rms_norm", 1, hp.n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, W.output_norm, s.trace_final, hp.n_embd, 1, hp.norm_eps); });
+        if (want_logits) matvec(W.output, s.hidden, s.logits, norm(W.output_norm), false);
+    }
+
+    // qwen35_metal.rs:1142-1240
+    void qwen_batch(uint32_t pos, uint32_t n, bool want_logits, bool traced, size_t trace_stride) {
+        const DeviceModel& W = *s.weights;
+        const uint32_t n_embd = hp.n_embd, q_dim = hp.n_heads * hp.head_dim;
+        run("embed", n, n_embd, 0, 1, [&] { return k::embed(stream, W.token_embd, s.tokens, k::Pos{nullptr, pos}, s.hidden, n); });
+        if (traced) copy(s.hidden, s.trace_embedding, (uint64_t)n * n_embd);
+        for (size_t il = 0; il < W.layers.size(); ++il) {
+            const LayerSpec& S = s.model->layers[il];
+            const DeviceLayer& D = W.layers[il];
+            run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.attn_norm, s.normed, n_embd, n, hp.norm_eps); });
+            if (S.mixer == Mixer::Attention) {
+                matmul(D.q, s.normed, s.q, n, BC_STORE_OVERWRITE);
+                matmul(D.k, s.normed, s.k, n, BC_STORE_OVERWRITE);
+                matmul(D.v, s.normed, value_target(S.cache_index, pos), n, BC_STORE_OVERWRITE);
+                size_t slot = layer_base(S.cache_index) + (size_t)pos * kv_dim();
+                // The rotated queries go to their own compact rows; the gates stay in the projection.
+                run("norm_rope", hp.n_heads * n, hp.head_dim, 0, 1, [&] {
+                    return k::norm_rope(stream, s.q, s.q_rot, false, D.q_norm, hp.n_heads, hp.head_dim, 2 * hp.head_dim, hp.n_rot, pos, n, 2 * q_dim,
+                                        q_dim, hp.rope_theta, hp.norm_eps);
+                });
+                run("norm_rope", hp.n_kv_heads * n, hp.head_dim, 0, 1, [&] {
+                    return k::norm_rope(stream, s.k, cache_at(s.k_cache, slot), s.kv_half, D.k_norm, hp.n_kv_heads, hp.head_dim, hp.head_dim,
+                                        hp.n_rot, pos, n, (uint32_t)kv_dim(), (uint32_t)kv_dim(), hp.rope_theta, hp.norm_eps);
+                });
+                if (s.kv_half)
+                    run("convert_half", 1, n * (uint32_t)kv_dim(), 0, 1,
+                        [&] { return k::convert_half(stream, s.v, static_cast<__half*>(cache_at(s.v_cache, slot)), (uint64_t)n * kv_dim()); });
+                k::AttentionShape shape{hp.n_heads, hp.n_kv_heads, hp.head_dim, pos, n, s.n_ctx, q_dim, hp.head_dim};
+                run("attention", n, pos + n, (uint64_t)(pos + n) * kv_dim() * kv_element_bytes() * 2, 2 * (int)((n + 63) / 64), [&] {
+                    return k::attention(stream, s.q_rot, cache_at(s.k_cache, layer_base(S.cache_index)), cache_at(s.v_cache, layer_base(S.cache_index)),
+                                        s.kv_half, s.scores, s.attn, shape);
+                });
+                run("attention_gate", n, q_dim, 0, 1, [&] { return k::attention_gate(stream, s.attn, s.q, hp.n_heads, hp.head_dim, n); });
+                matmul(D.output, s.attn, s.hidden, n, BC_STORE_ACCUMULATE);
+            } else {
+                matmul(D.qkv, s.normed, s.gdn_qkv, n, BC_STORE_OVERWRITE);
+                matmul(D.z, s.normed, s.gdn_z, n, BC_STORE_OVERWRITE);
+                matmul(D.beta, s.normed, s.gdn_beta, n, BC_STORE_OVERWRITE);
+                matmul(D.alpha, s.normed, s.gdn_alpha, n, BC_STORE_OVERWRITE);
+                qwen_delta_tail(D, S.cache_index, n);
+                matmul(D.ssm_out, s.gdn_out, s.hidden, n, BC_STORE_ACCUMULATE);
+            }
+            run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.ffn_norm, s.normed, n_embd, n, hp.norm_eps); });
+            matmul(D.gate, s.normed, s.ffn, n, BC_STORE_OVERWRITE);
+            matmul(D.up, s.normed, s.ffn, n, BC_STORE_SWIGLU);
+            matmul(D.down, s.ffn, s.hidden, n, BC_STORE_ACCUMULATE);
+            if (traced) copy(s.hidden, s.trace_layers + il * trace_stride, (uint64_t)n * n_embd);
+        }
+        if (traced)
+            run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, W.output_norm, s.trace_final, n_embd, n, hp.norm_eps); });
+        if (want_logits) matvec(W.output, s.hidden + (size_t)(n - 1) * n_embd, s.logits, norm(W.output_norm), false);
+    }
+
+    void step(uint32_t pos, bool want_logits, bool traced) {
+        if (hp.architecture == BC_ARCH_QWEN35) qwen_step(pos, want_logits, traced);
+        else lfm2_step(pos, want_logits, traced);
     }
 
     void batch(uint32_t pos, uint32_t n, bool want_logits, bool traced, size_t trace_stride) {
-        if (hp.architecture == BC_ARCH_QWEN35) {
-            if (status == BC_OK) status = fail(BC_ERR_UNSUPPORTED, "Qwen3.5 models are not built yet");
-            return;
-        }
-        lfm2_batch(pos, n, want_logits, traced, trace_stride);
+        if (hp.architecture == BC_ARCH_QWEN35) qwen_batch(pos, n, want_logits, traced, trace_stride);
+        else lfm2_batch(pos, n, want_logits, traced, trace_stride);
     }
 
     void argmax(const float* x, uint32_t* out, uint32_t* readback) {
@@ -411,7 +543,12 @@ bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32
     const size_t kv_dim = (size_t)hp.n_kv_heads * hp.head_dim, q_dim = (size_t)hp.n_heads * hp.head_dim;
     const size_t q_width = hp.architecture == BC_ARCH_QWEN35 ? 2 * q_dim : q_dim;  // Qwen's q holds [q | gate]
     const size_t cache_bytes = (size_t)hp.n_attention_layers * n_ctx * kv_dim * (s->kv_half ? 2 : 4);
-    s->conv_floats = (size_t)hp.n_conv_layers * (hp.conv_kernel - 1) * n_embd;
+    const size_t key_dim = (size_t)hp.n_k_heads * hp.k_head_dim, value_dim = (size_t)hp.n_v_heads * hp.v_head_dim;
+    const size_t conv_dim = 2 * key_dim + value_dim;
+    const bool qwen = hp.architecture == BC_ARCH_QWEN35;
+    // LFM2: [conv layer][K - 1][n_embd] of B*X products. Qwen3.5: [delta layer][channel][K - 1] raw inputs.
+    s->conv_floats = qwen ? (size_t)hp.n_delta_layers * conv_dim * (hp.conv_kernel - 1) : (size_t)hp.n_conv_layers * (hp.conv_kernel - 1) * n_embd;
+    s->delta_floats = (size_t)hp.n_delta_layers * hp.n_v_heads * hp.k_head_dim * hp.v_head_dim;
     const size_t ffn_width = std::max<size_t>(hp.n_ff, (size_t)hp.n_experts_used * hp.n_ff_expert);
     const size_t scratch_floats = hp.n_attention_layers ? k::attention_scratch_floats(hp.n_heads, hp.head_dim, n_ctx, s->batch) : 0;
 
@@ -434,6 +571,18 @@ bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32
         {(void**)&s->logits, (size_t)hp.n_vocab * 4},
         {(void**)&s->tokens, ((size_t)n_ctx + 1) * 4},
         {(void**)&s->greedy_token, 4},
+        {(void**)&s->route, rows * 2 * hp.n_experts_used * 4},
+        {(void**)&s->expert_offsets, ((size_t)hp.n_experts + 1) * 4},
+        {(void**)&s->expert_entries, rows * hp.n_experts_used * 4},
+        {(void**)&s->expert_out, rows * hp.n_experts_used * n_embd * 4},
+        {(void**)&s->delta_state, s->delta_floats * 4},
+        {(void**)&s->gdn_qkv, rows * conv_dim * 4},
+        {(void**)&s->gdn_conv_out, rows * conv_dim * 4},
+        {(void**)&s->gdn_z, rows * value_dim * 4},
+        {(void**)&s->gdn_beta, rows * hp.n_v_heads * 4},
+        {(void**)&s->gdn_alpha, rows * hp.n_v_heads * 4},
+        {(void**)&s->gdn_out, rows * value_dim * 4},
+        {(void**)&s->q_rot, qwen ? rows * q_dim * 4 : 0},
         {(void**)&s->step_pos, 4},
     };
     const char* no_graph = getenv("BOBCAT_NO_GRAPH");
@@ -682,6 +831,7 @@ bc_status bc_seq_reset(bc_seq* s) {
     // A new sequence starts from zero convolution history (and zero DeltaNet state). The KV cache
     // needs no clearing, because attention reads only the positions a sequence has written.
     if (s->conv_floats) BC_CUDA(cudaMemsetAsync(s->conv_state, 0, s->conv_floats * 4, s->backend->stream));
+    if (s->delta_floats) BC_CUDA(cudaMemsetAsync(s->delta_state, 0, s->delta_floats * 4, s->backend->stream));
     BC_CUDA(cudaStreamSynchronize(s->backend->stream));
     s->n_past = 0;
     s->resets += 1;
@@ -699,6 +849,8 @@ bc_status bc_seq_checkpoint(bc_seq* s, bc_checkpoint** out) {
     c->logits.resize(s->model->hp.n_vocab);
     cudaStream_t stream = s->backend->stream;
     if (s->conv_floats) BC_CUDA(cudaMemcpyAsync(c->conv_state.data(), s->conv_state, s->conv_floats * 4, cudaMemcpyDeviceToHost, stream));
+    c->delta_state.resize(s->delta_floats);
+    if (s->delta_floats) BC_CUDA(cudaMemcpyAsync(c->delta_state.data(), s->delta_state, s->delta_floats * 4, cudaMemcpyDeviceToHost, stream));
     BC_CUDA(cudaMemcpyAsync(c->logits.data(), s->logits, c->logits.size() * 4, cudaMemcpyDeviceToHost, stream));
     BC_CUDA(cudaStreamSynchronize(stream));
     *out = c.release();
@@ -708,11 +860,12 @@ bc_status bc_seq_checkpoint(bc_seq* s, bc_checkpoint** out) {
 bc_status bc_seq_restore(bc_seq* s, const bc_checkpoint* c) {
     if (!s || !c) return fail(BC_ERR_ARGUMENT, "seq and checkpoint must be non-null");
     if (c->resets != s->resets) return fail(BC_ERR_ARGUMENT, "the checkpoint predates a reset");
-    if (c->conv_state.size() != s->conv_floats || c->logits.size() != s->model->hp.n_vocab || c->n_past > s->n_ctx)
+    if (c->conv_state.size() != s->conv_floats || c->delta_state.size() != s->delta_floats || c->logits.size() != s->model->hp.n_vocab || c->n_past > s->n_ctx)
         return fail(BC_ERR_ARGUMENT, "the checkpoint comes from a different model or context");
     BC_TRY(s->backend->activate());
     cudaStream_t stream = s->backend->stream;
     if (s->conv_floats) BC_CUDA(cudaMemcpyAsync(s->conv_state, c->conv_state.data(), s->conv_floats * 4, cudaMemcpyHostToDevice, stream));
+    if (s->delta_floats) BC_CUDA(cudaMemcpyAsync(s->delta_state, c->delta_state.data(), s->delta_floats * 4, cudaMemcpyHostToDevice, stream));
     BC_CUDA(cudaMemcpyAsync(s->logits, c->logits.data(), c->logits.size() * 4, cudaMemcpyHostToDevice, stream));
     BC_CUDA(cudaStreamSynchronize(stream));
     s->n_past = c->n_past;
@@ -761,6 +914,16 @@ bc_status bc_seq_read_state(bc_seq* s, int32_t which, uint32_t layer, float* out
             BC_CUDA(cudaMemcpyAsync(out, cache + (size_t)layer * count * 4, count * 4, cudaMemcpyDeviceToHost, stream));
             BC_CUDA(cudaStreamSynchronize(stream));
         }
+        return BC_OK;
+    }
+    if (which == 3) {
+        if (layer >= hp.n_delta_layers) return fail(BC_ERR_ARGUMENT, "no DeltaNet layer %u", layer);
+        size_t count = (size_t)hp.n_v_heads * hp.k_head_dim * hp.v_head_dim;
+        *n = count;
+        if (!out) return BC_OK;
+        if (cap < count) return fail(BC_ERR_ARGUMENT, "out must hold %zu floats", count);
+        BC_CUDA(cudaMemcpyAsync(out, s->delta_state + (size_t)layer * count, count * 4, cudaMemcpyDeviceToHost, stream));
+        BC_CUDA(cudaStreamSynchronize(stream));
         return BC_OK;
     }
     return fail(BC_ERR_ARGUMENT, "unknown state %d", which);

@@ -42,6 +42,16 @@ struct bc_seq {
     float *trace_embedding = nullptr, *trace_layers = nullptr, *trace_final = nullptr;
     uint32_t* tokens = nullptr;        // n_ctx + 1 ids; the extra slot takes the pick at the last position
     uint32_t* greedy_token = nullptr;
+    // Mixture of experts: each token's route, the routes grouped by expert, and one row of n_embd
+    // floats per routed expert of each token (lfm2_metal.rs:59-65).
+    uint32_t *route = nullptr, *expert_offsets = nullptr, *expert_entries = nullptr;
+    float* expert_out = nullptr;
+    // Qwen3.5 (qwen35_metal.rs:161-196): the DeltaNet state matrices [delta layer][value head][k_dim]
+    // [v_dim] (the conv history lives in conv_state as [delta layer][channel][K - 1]), the scratch
+    // rows of a DeltaNet layer, and the rotated queries of a batch.
+    float *delta_state = nullptr, *gdn_qkv = nullptr, *gdn_conv_out = nullptr, *gdn_z = nullptr, *gdn_beta = nullptr;
+    float *gdn_alpha = nullptr, *gdn_out = nullptr, *q_rot = nullptr;
+    size_t delta_floats = 0;
     size_t conv_floats = 0;
     uint32_t trace_rows = 0;
     // Host-mapped words the device writes picked tokens into, one per step in flight.

@@ -213,6 +213,68 @@ bc_status bc_attention_static(void* stream, const float* q, const void* k_cache,
                               uint32_t n_queries, uint32_t n_ctx);
 /* Metal::argmax (backend.rs:2612-2617): index of the largest of n floats, ties to the lowest. */
 bc_status bc_op_argmax(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* out, size_t out_off, uint32_t n);
+/* ---- mixture of experts. A token's route is 2 * n_used 32-bit words: the picked expert ids, then
+ * their weights as float bits (crates/bobcat-metal/src/moe.metal:4-6); bc_route_bytes sizes it
+ * (route_bytes, backend.rs:2724). At most 128 experts, 8 used (backend.rs:97-100). */
+size_t bc_route_bytes(uint32_t n_used, uint32_t n_tokens);
+/* Metal::moe_route (backend.rs:1428-1479): sigmoid router scores of an F32 router matrix, the
+ * n_used largest of score + bias with ties to the lower expert, weights score / (sum + 1e-6).
+ * With `norm` non-null each token is RMS-normalised first and stored at `normed`. The picked ids
+ * equal the reference's `route` (crates/bobcat/src/lfm2.rs:691-709) on the same input. */
+bc_status bc_op_moe_route(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* norm, size_t norm_off, float eps,
+                          bc_buffer* normed, size_t normed_off, bc_buffer* router, size_t router_off, bc_buffer* bias,
+                          size_t bias_off, bc_buffer* route, size_t route_off, uint32_t n_cols, uint32_t n_experts,
+                          uint32_t n_used, uint32_t n_tokens);
+/* Metal::moe_group (backend.rs:1599-1637): offsets[n_experts + 1], entries[n_tokens * n_used]. */
+bc_status bc_op_moe_group(bc_backend* b, bc_buffer* route, size_t route_off, bc_buffer* offsets, size_t off_off,
+                          bc_buffer* entries, size_t ent_off, uint32_t n_experts, uint32_t n_used, uint32_t n_tokens);
+/* Metal::matvec_experts_swiglu (backend.rs:1481-1536): `gate` and `up` hold n_experts stacked
+ * matrices of n_rows rows; y[token][slot][row] = silu(gate_e x) * (up_e x). */
+bc_status bc_op_matvec_experts_swiglu(bc_backend* b, int32_t format, bc_buffer* gate, size_t gate_off, bc_buffer* up,
+                                      size_t up_off, uint32_t n_rows, uint32_t n_cols, uint32_t n_experts, bc_buffer* x,
+                                      size_t x_off, bc_buffer* route, size_t route_off, uint32_t n_used, bc_buffer* y,
+                                      size_t y_off, uint32_t n_tokens);
+/* Metal::matvec_experts_down (backend.rs:1538-1597): y[token][row] += sum over slots of
+ * weight * (down_e row . x[token][slot]). */
+bc_status bc_op_matvec_experts_down(bc_backend* b, int32_t format, bc_buffer* down, size_t down_off, uint32_t n_rows,
+                                    uint32_t n_cols, uint32_t n_experts, bc_buffer* x, size_t x_off, bc_buffer* route,
+                                    size_t route_off, uint32_t n_used, bc_buffer* y, size_t y_off, uint32_t n_tokens);
+/* Metal::matmul_experts (backend.rs:1639-1703): grouped multiply over the entries of moe_group.
+ * `up` non-null pairs gate and up with a SwiGLU store. `gather` reads a token's shared input row;
+ * otherwise each entry reads its own row. Output rows are the entries'. */
+bc_status bc_op_matmul_experts(bc_backend* b, int32_t format, bc_buffer* weights, size_t w_off, bc_buffer* up, size_t up_off,
+                               uint32_t n_rows, uint32_t n_cols, uint32_t n_experts, bc_buffer* x, size_t x_off,
+                               int32_t gather, bc_buffer* offsets, size_t off_off, bc_buffer* entries, size_t ent_off,
+                               uint32_t n_used, bc_buffer* y, size_t y_off, uint32_t n_tokens);
+/* Metal::moe_combine (backend.rs:1705-1737): y[t] += sum_s weight[t, s] * expert_out[t * n_used + s]. */
+bc_status bc_op_moe_combine(bc_backend* b, bc_buffer* expert_out, size_t eo_off, bc_buffer* route, size_t route_off,
+                            bc_buffer* y, size_t y_off, uint32_t n_embd, uint32_t n_used, uint32_t n_tokens);
+/* ---- Qwen3.5 Gated DeltaNet and gated attention. Shapes follow DeltaShape (backend.rs:2704-2722):
+ * n_k_heads key heads of k_dim, n_v_heads value heads of v_dim (a multiple of n_k_heads), conv_dim =
+ * 2 * n_k_heads * k_dim + n_v_heads * v_dim. Limits: conv kernel 2..8, k_dim a multiple of 32 up to
+ * 128, v_dim a multiple of 32 up to 256 (backend.rs:109-112, :1899-1911). */
+/* Metal::gdn_conv (backend.rs:1739-1817): causal convolution + SiLU over the q|k|v channels of
+ * n_tokens rows; `history` holds the last kernel - 1 raw inputs of each channel, [conv_dim][kernel - 1]. */
+bc_status bc_op_gdn_conv(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* taps, size_t taps_off, bc_buffer* history,
+                         size_t hist_off, bc_buffer* out, size_t out_off, uint32_t conv_dim, uint32_t kernel, uint32_t n_tokens);
+/* Metal::gdn_gates (backend.rs:1851-1886), in place: beta = sigmoid(beta);
+ * alpha = exp(a * softplus(alpha + dt_bias)) over [n_tokens][n_v_heads]. */
+bc_status bc_op_gdn_gates(bc_backend* b, bc_buffer* beta, size_t beta_off, bc_buffer* alpha, size_t alpha_off, bc_buffer* a,
+                          size_t a_off, bc_buffer* dt_bias, size_t dt_off, uint32_t n_v_heads, uint32_t n_tokens);
+/* Metal::gdn_recurrence (backend.rs:1888-1979): the gated delta rule over n_tokens rows of the
+ * convolved q|k|v, carrying `state` [n_v_heads][k_dim][v_dim]. Value head h reads key head
+ * h % n_k_heads. `normalize` L2-normalises q (times 1/sqrt(k_dim)) and k first. */
+bc_status bc_op_gdn_recurrence(bc_backend* b, bc_buffer* qkv, size_t qkv_off, bc_buffer* beta, size_t beta_off, bc_buffer* decay,
+                               size_t decay_off, bc_buffer* state, size_t state_off, bc_buffer* out, size_t out_off,
+                               uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t n_tokens,
+                               int32_t normalize);
+/* Metal::gdn_gated_norm (backend.rs:1819-1849): x = RMSNorm(x) * weight * silu(z) per row of v_dim. */
+bc_status bc_op_gdn_gated_norm(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* z, size_t z_off, bc_buffer* weight,
+                               size_t w_off, uint32_t v_dim, uint32_t n_rows, float eps);
+/* Metal::attention_gate (backend.rs:2001-2032): out[t][h][d] *= sigmoid(q_gate[t][h][head_dim + d])
+ * with q_gate the interleaved [q | gate] projection of [n_tokens][n_heads][2 * head_dim]. */
+bc_status bc_op_attention_gate(bc_backend* b, bc_buffer* out, size_t out_off, bc_buffer* q_gate, size_t qg_off, uint32_t n_heads,
+                               uint32_t head_dim, uint32_t n_tokens);
 /* Metal::silu_mul (backend.rs:1983-1999): x = silu(gate) * x, elementwise. */
 bc_status bc_op_silu_mul(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* gate, size_t g_off, uint32_t n);
 
