@@ -48,8 +48,8 @@ def test_gdn_gates_including_the_linear_branch(cuda):
     alpha = np.array([[-3, 0.5, 19.5, 25.0], [30, -30, 1, 2], [0, 0, 0, 0]], dtype=np.float32)  # softplus switches at 20
     a = np.array([-0.5, -1.0, -0.01, -0.02], dtype=np.float32)
     dt = np.array([0.1, -0.1, 0.6, 0.0], dtype=np.float32)
-    bb, ab = cuda.buffer_from(beta), cuda.buffer_from(alpha)
-    cuda.begin(); cuda.gdn_gates(bb, ab, cuda.buffer_from(a), cuda.buffer_from(dt), n_v, n_tokens); cuda.end()
+    bb, ab, a_b, dt_b = cuda.buffer_from(beta), cuda.buffer_from(alpha), cuda.buffer_from(a), cuda.buffer_from(dt)
+    cuda.begin(); cuda.gdn_gates(bb, ab, a_b, dt_b, n_v, n_tokens); cuda.end()
     v = alpha.astype(np.float64) + dt
     sp = np.where(v > 20, v, np.log1p(np.exp(np.minimum(v, 50))))
     assert np.abs(cuda.read(bb, np.zeros_like(beta)) - 1 / (1 + np.exp(-beta.astype(np.float64)))).max() < 1e-6
@@ -89,8 +89,9 @@ def test_recurrence_carries_state(cuda, kd, vd):
         beta = rng.uniform(0.1, 0.9, (n, n_v)).astype(np.float32)
         decay = rng.uniform(0.8, 1.0, (n, n_v)).astype(np.float32)
         ob = cuda.new_buffer(n * n_v * vd * 4)
+        qb, bb, db = cuda.buffer_from(qkv), cuda.buffer_from(beta), cuda.buffer_from(decay)
         cuda.begin()
-        cuda.gdn_recurrence(cuda.buffer_from(qkv), cuda.buffer_from(beta), cuda.buffer_from(decay), sb, ob, n_k, n_v, kd, vd, n, normalize=True)
+        cuda.gdn_recurrence(qb, bb, db, sb, ob, n_k, n_v, kd, vd, n, normalize=True)
         cuda.end()
         want = delta_rule_f64(qkv, beta.astype(np.float64), decay.astype(np.float64), state, n_k, n_v, kd, vd, True)
         assert np.abs(cuda.read(ob, np.zeros((n, n_v * vd), dtype=np.float32)) - want).max() < GDN_TOLERANCE
@@ -109,16 +110,16 @@ def test_gated_norm_and_attention_gate(cuda):
     x = rng.standard_normal((rows, vd)).astype(np.float32)
     z = rng.standard_normal((rows, vd)).astype(np.float32)
     w = rng.uniform(0.5, 1.5, vd).astype(np.float32)
-    xb = cuda.buffer_from(x)
-    cuda.begin(); cuda.gdn_gated_norm(xb, cuda.buffer_from(z), cuda.buffer_from(w), vd, rows, 1e-6); cuda.end()
+    xb, zb, wb = cuda.buffer_from(x), cuda.buffer_from(z), cuda.buffer_from(w)
+    cuda.begin(); cuda.gdn_gated_norm(xb, zb, wb, vd, rows, 1e-6); cuda.end()
     x64 = x.astype(np.float64)
     want = x64 / np.sqrt((x64 ** 2).mean(axis=1, keepdims=True) + 1e-6) * w * silu(z.astype(np.float64))
     assert np.abs(cuda.read(xb, np.zeros_like(x)) - want).max() < GDN_TOLERANCE
     n_tokens, n_heads, hd = 3, 4, 64
     out = rng.standard_normal((n_tokens, n_heads, hd)).astype(np.float32)
     q_gate = rng.standard_normal((n_tokens, n_heads, 2 * hd)).astype(np.float32)
-    ob = cuda.buffer_from(out)
-    cuda.begin(); cuda.attention_gate(ob, cuda.buffer_from(q_gate), n_heads, hd, n_tokens); cuda.end()
+    ob, gb = cuda.buffer_from(out), cuda.buffer_from(q_gate)
+    cuda.begin(); cuda.attention_gate(ob, gb, n_heads, hd, n_tokens); cuda.end()
     want = out / (1 + np.exp(-q_gate[:, :, hd:].astype(np.float64)))
     assert np.abs(cuda.read(ob, np.zeros_like(out)) - want).max() < 1e-6
 
