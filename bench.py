@@ -153,8 +153,17 @@ def run_reference(args) -> None:
 def dominant_kernel(cuda, seq, prompt) -> dict:
     """Time every launch of one more decode pass with CUDA events (profiling mode serialises the
     launches) and report the kernel with the largest share of the time."""
+    def rows_of(entries, count):
+        total = sum(e["seconds"] for e in entries) or 1.0
+        return [{"kernel": e["name"], "rows": e["n_rows"], "cols": e["n_cols"], "calls": e["calls"], "us": 1e6 * e["seconds"] / e["calls"],
+                 "gbs": (e["bytes"] / e["seconds"] / 1e9) if e["seconds"] else 0.0, "share": e["seconds"] / total}
+                for e in sorted(entries, key=lambda e: -e["seconds"])[:count]]
+
     seq.reset()
+    cuda.set_profiling(True)
     seq.prefill(prompt)
+    cuda.set_profiling(False)
+    prefill_table = rows_of(cuda.profile(), 10)
     cuda.set_profiling(True)
     seq.generate(min(16, DECODE_TOKENS))
     cuda.set_profiling(False)
@@ -163,10 +172,8 @@ def dominant_kernel(cuda, seq, prompt) -> dict:
     top = max(entries, key=lambda e: e["seconds"])
     per_launch_s = top["seconds"] / top["calls"]
     per_launch_bytes = top["bytes"] / top["calls"]
-    table = sorted(entries, key=lambda e: -e["seconds"])[:8]
     return {"top": top, "share": top["seconds"] / total, "seconds": per_launch_s, "bytes": per_launch_bytes,
-            "table": [{"kernel": e["name"], "rows": e["n_rows"], "cols": e["n_cols"], "calls": e["calls"], "us": 1e6 * e["seconds"] / e["calls"],
-                       "gbs": (e["bytes"] / e["seconds"] / 1e9) if e["seconds"] else 0.0, "share": e["seconds"] / total} for e in table]}
+            "table": rows_of(entries, 8), "prefill_table": prefill_table}
 
 
 def run_ours(args) -> None:
@@ -272,7 +279,7 @@ def run_ours(args) -> None:
             "decode": {"tok_s": decode_tok_s, "tpot_ms": 1e3 * decode_gpu / DECODE_TOKENS, "bytes_per_token": token_bytes,
                        "hbm_gbs": token_bytes * DECODE_TOKENS / decode_gpu / 1e9, "hbm_frac": token_bytes * DECODE_TOKENS / decode_gpu / 1e9 / peak,
                        "hbm_frac_of_nominal_8tbs": token_bytes * DECODE_TOKENS / decode_gpu / 8e12, "token_hash": token_hash},
-            "prefill": {"tok_s": prefill_tok_s, "ttft_ms": 1e3 * prefill_gpu, "tokens": PROMPT_TOKENS},
+            "prefill": {"tok_s": prefill_tok_s, "ttft_ms": 1e3 * prefill_gpu, "tokens": PROMPT_TOKENS, "kernels": dom["prefill_table"]},
             "roofline": {"bound": "hbm", "kernel": "%s %dx%d" % (dom["top"]["name"], dom["top"]["n_rows"], dom["top"]["n_cols"]),
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                          "share_of_decode": dom["share"], "launch_us": 1e6 * dom["seconds"], "bytes_per_launch": dom["bytes"], "kernels": dom["table"]},

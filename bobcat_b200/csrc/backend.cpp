@@ -45,6 +45,21 @@ bc_status bc_backend::activate() {
     return BC_OK;
 }
 
+bc_status bc_backend::pack_scratch(size_t bytes, void** out) {
+    if (bytes > pack_len) {
+        // Launches that read the old scratch may still be queued: drain the stream before freeing it.
+        BC_CUDA(cudaStreamSynchronize(stream));
+        if (pack) cudaFree(pack);
+        pack = nullptr;
+        pack_len = 0;
+        size_t want = bytes + bytes / 2;
+        BC_CUDA(cudaMalloc(&pack, want));
+        pack_len = want;
+    }
+    *out = pack;
+    return BC_OK;
+}
+
 namespace {
 
 bc_status need_recording(bc_backend* b) {
@@ -114,6 +129,7 @@ void bc_backend_close(bc_backend* b) {
         buffer->ptr = nullptr;
         buffer->backend = nullptr;
     }
+    if (b->pack) cudaFree(b->pack);
     if (b->owns_stream) cudaStreamDestroy(b->stream);
     delete b;
 }
@@ -282,6 +298,9 @@ bc_status bc_wait(bc_backend* b, bc_ticket ticket, double* seconds) {
     cudaEventDestroy(end->second);
     b->tickets.erase(end);
     if (seconds) *seconds = ms * 1e-3;
+    // A kernel whose bounded wait ran out leaves a flag rather than hanging the device.
+    if (int flag = k::matvec_error_flag()) return fail(BC_ERR_EXECUTION, "a matvec kernel gave up waiting for its weight stream (code %d)", flag);
+    if (int flag = k::matmul_error_flag()) return fail(BC_ERR_EXECUTION, "a matmul kernel gave up waiting on its pipeline (code %d)", flag);
     return BC_OK;
 }
 
@@ -412,9 +431,11 @@ bc_status bc_op_matmul(bc_backend* b, int32_t format, bc_buffer* weights, size_t
     BC_TRY(matrix_view(b, weights, w_off, format, n_rows, n_cols, "matmul", &w));
     BC_TRY(check_range(b, x, x_off, (size_t)n_tokens * n_cols * 4, "matmul"));
     BC_TRY(check_range(b, y, y_off, (size_t)n_tokens * n_rows * 4, "matmul"));
-    return b->run("matmul", n_rows, n_cols, w.bytes(), 1, [&] {
+    void* pack = nullptr;
+    if (k::matmul_umma_supported(w, n_tokens)) BC_TRY(b->pack_scratch(k::matmul_pack_bytes(n_tokens, n_cols), &pack));
+    return b->run("matmul", n_rows, n_cols, w.bytes(), pack ? 2 : 1, [&] {
         return k::matmul(b->stream, w, reinterpret_cast<const float*>(at(x, x_off)), reinterpret_cast<float*>(at(y, y_off)), n_tokens,
-                         n_rows, store);
+                         n_rows, store, pack);
     });
 }
 

@@ -51,6 +51,11 @@ struct bc_backend {
     std::map<uint64_t, cudaEvent_t> ticket_starts;
     std::set<bc_buffer*> buffers;
     uint64_t launches = 0;  // kernels launched through this backend
+    // Scratch of the tensor-core prefill kernel: the fp16 operand-layout copy of a matmul's inputs.
+    // Grown on demand; only launches of this backend's stream touch it, one after another.
+    void* pack = nullptr;
+    size_t pack_len = 0;
+    bc_status pack_scratch(size_t bytes, void** out);
 
     bool profiling = false;
     std::map<ProfileKey, ProfileTotals> profile;

@@ -114,8 +114,13 @@ __global__ void __launch_bounds__(kThreads) matmul_simt_kernel(MatmulParams p) {
 }  // namespace
 
 cudaError_t matmul(cudaStream_t stream, const Mat& w, const float* x, float* y, uint32_t n_tokens, uint32_t y_stride,
-                   int32_t store) {
+                   int32_t store, void* pack) {
     if (n_tokens == 0 || w.n_rows == 0) return cudaSuccess;
+    if (pack && matmul_umma_supported(w, n_tokens)) {
+        cudaError_t e = matmul_pack(stream, x, n_tokens, w.n_cols, pack);
+        if (e != cudaSuccess) return e;
+        return matmul_umma(stream, w, pack, y, n_tokens, y_stride, store);
+    }
     MatmulParams p{w, x, y, n_tokens, y_stride, store};
     dim3 grid((n_tokens + kTileTokens - 1) / kTileTokens, (w.n_rows + kTileRows - 1) / kTileRows);
     matmul_simt_kernel<<<grid, kThreads, 0, stream>>>(p);

@@ -1,0 +1,341 @@
+// The prefill Q4_0 contraction on the fifth-generation tensor cores: Y[t][r] (store) sum_c W[r][c] X[t][c]
+// for a batch of tokens, with tcgen05.mma accumulating in tensor memory.
+//
+// Arithmetic. Weights are dequantised to fp16 ((q - 8) * d, one rounding) and inputs are rounded to
+// fp16; products accumulate in f32. That is the arithmetic of the reference's prefill kernel for
+// Q4_0 (crates/bobcat-metal/src/matmul.metal:249-470: half weight tiles, half inputs at :519-521,
+// f32 accumulation) and of its three stores (crates/bobcat-metal/src/backend.rs:361-370).
+//
+// Shape of the kernel. One CTA owns 128 weight rows (the MMA's M) and up to 256 tokens (its N);
+// the accumulator is 128 lanes x N columns of tensor memory. K advances 64 columns (two Q4_0
+// blocks per row) per pipeline stage:
+//   * 8 producer warps stream the tile's quants and scales from the split layout with cp.async
+//     into a private raw ring (8 chunks in flight per thread, which covers HBM latency), turn
+//     nibbles into fp16 with logic ops on packed halves, and store them in the operand layout;
+//   * one thread brings the stage's token tile, already fp16 and already in operand layout (see
+//     pack_kernel), with a single bulk copy;
+//   * one thread issues four tcgen05.mma (K = 16 each) per stage and commits the stage's release;
+//   * after the last stage the producer warps become the epilogue: tcgen05.ld, the store mode,
+//     coalesced stores (a warp's 32 lanes are 32 consecutive rows of one token).
+// Operand layout (both operands, K-major, no swizzle): core matrices of 8 rows x 8 halves (128
+// contiguous bytes); the 8 core matrices of an 8-row group follow one another along K, and groups
+// follow one another, so a tile of R rows is R / 8 kilobytes-sized groups whatever R is.
+// Within a Q4_0 block the K order is permuted to the order the nibbles fall out of a quant word
+// (word j gives elements 4j, 4j+2, 4j+1, 4j+3, 16+4j, 16+4j+2, 16+4j+1, 16+4j+3); the packed
+// inputs use the same order, and a dot product does not care.
+//
+// Every wait on a barrier is bounded. A wait that runs out raises a flag in shared memory that
+// makes every other wait of the CTA give up, records a code the host reads, skips the stores, and
+// the CTA still frees its tensor memory and returns.
+
+#include <cstdlib>
+
+#include "async_utils.cuh"
+#include "device_utils.cuh"
+#include "kernels.h"
+#include "../../include/bobcat_cuda.h"
+
+namespace bc {
+namespace k {
+
+namespace {
+
+using namespace async;
+
+constexpr uint32_t kRows = 128;       // weight rows per CTA: the MMA's M
+constexpr uint32_t kMaxTokens = 256;  // tokens per CTA: the MMA's N, a multiple of 16
+constexpr uint32_t kChunkK = 64;      // columns per stage
+constexpr uint32_t kStages = 3;
+constexpr uint32_t kRawDepth = 8;  // chunks of raw quants in flight per producer thread
+constexpr uint32_t kProducers = 256;
+constexpr uint32_t kTmaWarp = kProducers / 32, kMmaWarp = kTmaWarp + 1;
+constexpr uint32_t kThreads = kProducers + 64;
+constexpr uint32_t kATile = kRows * kChunkK * 2;       // 16 KB
+constexpr uint32_t kBTile = kMaxTokens * kChunkK * 2;  // 32 KB
+constexpr uint32_t kGroupBytes = 8 * kChunkK * 2;      // an 8-row group of a stage: 1 KB
+constexpr uint32_t kCoreBytes = 128;
+constexpr uint32_t kTmemColumns = 256;
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr size_t kSmemBytes =
+    kStages * (kATile + kBTile) + kRawDepth * kProducers * (16 + 4) + (2 * kStages + 1) * 8 + 16;
+
+__device__ int g_matmul_error;
+
+struct UmmaParams {
+    const uint4* quants;   // split layout: [n_rows][n_blocks] 16-byte groups
+    const __half* scales;  // [n_rows][n_blocks]
+    const __half* packed;  // inputs in operand layout: [n_chunks][token_groups][8 cores][8 tokens][8 halves]
+    float* y;
+    uint32_t n_rows, n_blocks, n_chunks, n_tokens, y_stride, token_groups;
+    int store;
+};
+
+// X [n_tokens][n_cols] f32 -> fp16 operand layout, zero rows up to the padded token count. One
+// thread writes one core-matrix row (16 bytes): 8 halves of one token.
+__global__ void __launch_bounds__(256) pack_kernel(const float* __restrict__ x, __half* __restrict__ packed, uint32_t n_tokens,
+                                                   uint32_t n_cols, uint32_t token_groups, uint64_t total) {
+    uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;  // index of the 16-byte output
+    if (o >= total) return;
+    uint32_t tr = o & 7, core = (o >> 3) & 7;
+    uint64_t group = o >> 6;  // chunk * token_groups + token group
+    uint32_t tg = group % token_groups, chunk = group / token_groups;
+    uint32_t token = tg * 8 + tr, block = core >> 2, j = core & 3;
+    uint4 out = make_uint4(0, 0, 0, 0);
+    if (token < n_tokens) {
+        const float* src = x + (uint64_t)token * n_cols + chunk * kChunkK + block * 32 + 4 * j;
+        float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 16);
+        __half2 a = __floats2half2_rn(lo.x, lo.z), b = __floats2half2_rn(lo.y, lo.w);
+        __half2 c = __floats2half2_rn(hi.x, hi.z), d = __floats2half2_rn(hi.y, hi.w);
+        out.x = *reinterpret_cast<uint32_t*>(&a);
+        out.y = *reinterpret_cast<uint32_t*>(&b);
+        out.z = *reinterpret_cast<uint32_t*>(&c);
+        out.w = *reinterpret_cast<uint32_t*>(&d);
+    }
+    reinterpret_cast<uint4*>(packed)[o] = out;
+}
+
+// The eight weights of quant word `w` times the block scale, as fp16 in the permuted order.
+__device__ __forceinline__ uint4 dequant_word(uint32_t w, __half2 scale) {
+    const uint32_t magic = 0x64006400u;  // half2(1024, 1024)
+    uint32_t lo02 = (w & 0x000f000fu) | magic;
+    uint32_t hi02 = (w & 0x00f000f0u) | magic;
+    uint32_t w8 = w >> 8;
+    uint32_t lo13 = (w8 & 0x000f000fu) | magic;
+    uint32_t hi13 = (w8 & 0x00f000f0u) | magic;
+    const __half2 bias_lo = __floats2half2_rn(1032.f, 1032.f);
+    const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
+    const __half2 bias_hi = __floats2half2_rn(-72.f, -72.f);  // (1024 + 16 q) / 16 - 72 = q - 8
+    __half2 a = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&lo02), bias_lo), scale);
+    __half2 b = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&lo13), bias_lo), scale);
+    __half2 c = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&hi02), sixteenth, bias_hi), scale);
+    __half2 d = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&hi13), sixteenth, bias_hi), scale);
+    return make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b), *reinterpret_cast<uint32_t*>(&c),
+                      *reinterpret_cast<uint32_t*>(&d));
+}
+
+__device__ __forceinline__ void give_up(volatile int* dead, int code) {
+    *dead = 1;
+    atomicCAS(&g_matmul_error, 0, code);
+}
+
+__global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* a_tiles = smem;
+    uint8_t* b_tiles = a_tiles + kStages * kATile;
+    uint4* raw_q = reinterpret_cast<uint4*>(b_tiles + kStages * kBTile);
+    uint32_t* raw_s = reinterpret_cast<uint32_t*>(raw_q + kRawDepth * kProducers);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raw_s + kRawDepth * kProducers);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+    volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t tok0 = blockIdx.x * kMaxTokens, row0 = blockIdx.y * kRows;
+    const uint32_t left = p.n_tokens - tok0;
+    const uint32_t n_tile = left >= kMaxTokens ? kMaxTokens : ((left + 15u) & ~15u);  // the MMA's N
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + kStages * 8, accum = empty0 + kStages * 8;
+    const uint32_t a0 = smem_u32(a_tiles), b0 = smem_u32(b_tiles);
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            mbar_init(full0 + 8 * s, kProducers + 1);  // every producer thread, plus the bulk copy's arrive.expect_tx
+            mbar_init(empty0 + 8 * s, 1);              // the MMA thread's commit
+        }
+        mbar_init(accum, 1);
+        *dead = 0;
+        mbar_init_fence();
+    }
+    if (warp == kMmaWarp) tmem_alloc(smem_u32(tmem_slot), kTmemColumns);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < kTmaWarp) {
+        // ---- producers: row `row` of the tile, block `half` of each chunk
+        const uint32_t row = tid & (kRows - 1), half = tid >> 7;
+        const uint32_t grow = row0 + row;
+        const bool valid = grow < p.n_rows;
+        const uint4* qsrc = p.quants + (uint64_t)(valid ? grow : 0) * p.n_blocks + half;
+        const __half* ssrc = p.scales + (uint64_t)(valid ? grow : 0) * p.n_blocks;
+        const uint32_t rq = smem_u32(raw_q) + tid * 16, rs = smem_u32(raw_s) + tid * 4;
+        auto issue = [&](uint32_t kc) {
+            if (valid && kc < p.n_chunks) {
+                uint32_t slot = kc % kRawDepth;
+                cp_async_16(rq + slot * (kProducers * 16), qsrc + 2 * kc);
+                cp_async_4(rs + slot * (kProducers * 4), ssrc + 2 * kc);
+            }
+            cp_async_commit();
+        };
+        for (uint32_t kc = 0; kc + 1 < kRawDepth; ++kc) issue(kc);
+        const uint32_t a_off = (row >> 3) * kGroupBytes + (row & 7) * 16 + half * 4 * kCoreBytes;
+        bool alive = true;
+        for (uint32_t kc = 0; kc < p.n_chunks; ++kc) {
+            issue(kc + kRawDepth - 1);
+            cp_async_wait<kRawDepth - 1>();
+            const uint32_t slot = kc % kRawDepth;
+            uint4 q = make_uint4(0, 0, 0, 0);
+            uint32_t sbits = 0;  // rows past the matrix: scale zero, so the tile row is zero
+            if (valid) {
+                q = raw_q[slot * kProducers + tid];
+                sbits = raw_s[slot * kProducers + tid];
+            }
+            const uint16_t dbits = half ? (uint16_t)(sbits >> 16) : (uint16_t)(sbits & 0xffffu);
+            const __half d = __ushort_as_half(dbits);
+            const __half2 scale = __halves2half2(d, d);
+            const uint32_t stage = kc % kStages, use = kc / kStages;
+            if (!mbar_wait(empty0 + 8 * stage, (use & 1) ^ 1, kSpinLimit, dead)) {
+                give_up(dead, 1);
+                alive = false;
+                break;
+            }
+            const uint32_t dst = a0 + stage * kATile + a_off;
+            const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint4 v = dequant_word(words[j], scale);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + j * kCoreBytes), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                             : "memory");
+            }
+            fence_proxy_async();
+            mbar_arrive(full0 + 8 * stage);
+        }
+        cp_async_wait<0>();
+
+        // ---- epilogue: lanes 32 * (warp % 4).. of tensor memory, half of the columns per warp
+        alive = __all_sync(0xffffffffu, alive);
+        if (alive && !mbar_wait(accum, 0, kSpinLimit, dead)) {
+            give_up(dead, 2);
+            alive = false;
+        }
+        alive = __all_sync(0xffffffffu, alive);
+        if (alive) {
+            tc_fence_after_sync();
+            const uint32_t quarter = warp & 3, units = n_tile / 16, mid = (units + 1) / 2;
+            const uint32_t first = warp >= 4 ? mid : 0, last = warp >= 4 ? units : mid;
+            const uint32_t out_row = row0 + quarter * 32 + lane;
+            for (uint32_t u = first; u < last; ++u) {
+                float v[16];
+                __syncwarp();
+                tmem_load_16(tmem + ((quarter * 32) << 16) + u * 16, v);
+                if (out_row < p.n_rows) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        uint32_t tok = tok0 + u * 16 + j;
+                        if (tok < p.n_tokens) {
+                            float* y = p.y + (uint64_t)tok * p.y_stride + out_row;
+                            float r = v[j];
+                            if (p.store == BC_STORE_ACCUMULATE) r += *y;
+                            else if (p.store == BC_STORE_SWIGLU) {
+                                float g = *y;
+                                r = g / (1.f + expf(-g)) * r;
+                            }
+                            *y = r;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == kTmaWarp) {
+        // ---- the token tiles: one bulk copy per stage
+        if (lane == 0) {
+            const uint32_t bytes = n_tile * kChunkK * 2;
+            const __half* src = p.packed + (uint64_t)(tok0 / 8) * (8 * kChunkK);
+            for (uint32_t kc = 0; kc < p.n_chunks; ++kc) {
+                const uint32_t stage = kc % kStages, use = kc / kStages;
+                if (!mbar_wait(empty0 + 8 * stage, (use & 1) ^ 1, kSpinLimit, dead)) {
+                    give_up(dead, 3);
+                    break;
+                }
+                mbar_arrive_expect(full0 + 8 * stage, bytes);
+                bulk_load(b0 + stage * kBTile, src + (uint64_t)kc * p.token_groups * (8 * kChunkK), bytes, full0 + 8 * stage);
+            }
+        }
+    } else {
+        // ---- the tensor core: four K = 16 steps per stage
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_f16(kRows, n_tile);
+            bool alive = true;
+            for (uint32_t kc = 0; kc < p.n_chunks; ++kc) {
+                const uint32_t stage = kc % kStages, use = kc / kStages;
+                if (!mbar_wait(full0 + 8 * stage, use & 1, kSpinLimit, dead)) {
+                    give_up(dead, 4);
+                    alive = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t a = a0 + stage * kATile, b = b0 + stage * kBTile;
+#pragma unroll
+                for (uint32_t j = 0; j < kChunkK / 16; ++j) {
+                    umma_f16(tmem, umma_desc(a + j * 2 * kCoreBytes, kCoreBytes, kGroupBytes),
+                             umma_desc(b + j * 2 * kCoreBytes, kCoreBytes, kGroupBytes), idesc, (kc | j) != 0);
+                }
+                umma_commit(empty0 + 8 * stage);
+            }
+            if (alive) umma_commit(accum);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*dead) __nanosleep(100000);  // let copies and instructions still in flight land before the CTA goes
+    if (warp == kMmaWarp) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, kTmemColumns);
+    }
+}
+
+bool umma_disabled() {
+    static const bool off = [] {
+        const char* v = std::getenv("BOBCAT_NO_UMMA_MATMUL");
+        return v && v[0] == '1';
+    }();
+    return off;
+}
+
+}  // namespace
+
+uint64_t matmul_pack_bytes(uint32_t n_tokens, uint32_t n_cols) { return (uint64_t)((n_tokens + 15u) & ~15u) * n_cols * 2; }
+
+bool matmul_umma_supported(const Mat& w, uint32_t n_tokens) {
+    return !umma_disabled() && w.format == BC_Q4_0 && w.n_cols % kChunkK == 0 && w.n_cols > 0 && n_tokens >= 16;
+}
+
+cudaError_t matmul_pack(cudaStream_t stream, const float* x, uint32_t n_tokens, uint32_t n_cols, void* packed) {
+    uint32_t token_groups = ((n_tokens + 15u) & ~15u) / 8;
+    uint64_t total = (uint64_t)(n_cols / kChunkK) * token_groups * 64;
+    if (total == 0) return cudaSuccess;
+    pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, static_cast<__half*>(packed), n_tokens, n_cols, token_groups, total);
+    return cudaGetLastError();
+}
+
+cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* packed, float* y, uint32_t n_tokens, uint32_t y_stride,
+                        int32_t store) {
+    if (n_tokens == 0 || w.n_rows == 0) return cudaSuccess;
+    cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel), kSmemBytes);
+    if (err != cudaSuccess) return err;
+    UmmaParams p;
+    p.quants = static_cast<const uint4*>(w.data);
+    p.scales = w.scales;
+    p.packed = static_cast<const __half*>(packed);
+    p.y = y;
+    p.n_rows = w.n_rows;
+    p.n_blocks = w.n_cols / 32;
+    p.n_chunks = w.n_cols / kChunkK;
+    p.n_tokens = n_tokens;
+    p.y_stride = y_stride;
+    p.token_groups = ((n_tokens + 15u) & ~15u) / 8;
+    p.store = store;
+    dim3 grid((n_tokens + kMaxTokens - 1) / kMaxTokens, (w.n_rows + kRows - 1) / kRows);
+    matmul_umma_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+int matmul_error_flag() {
+    int flag = 0;
+    cudaMemcpyFromSymbol(&flag, g_matmul_error, sizeof flag);
+    return flag;
+}
+
+}  // namespace k
+}  // namespace bc

@@ -44,7 +44,9 @@ struct Recorder {
     }
 
     void matmul(const k::Mat& w, const float* x, float* y, uint32_t n, int store) {
-        run("matmul", w.n_rows, w.n_cols, w.bytes(), 1, [&] { return k::matmul(stream, w, x, y, n, w.n_rows, store); });
+        void* pack = nullptr;
+        if (status == BC_OK && k::matmul_umma_supported(w, n)) status = s.backend->pack_scratch(k::matmul_pack_bytes(n, w.n_cols), &pack);
+        run("matmul", w.n_rows, w.n_cols, w.bytes(), pack ? 2 : 1, [&] { return k::matmul(stream, w, x, y, n, w.n_rows, store, pack); });
     }
 
     size_t kv_element_bytes() const { return s.kv_half ? 2 : 4; }
@@ -389,6 +391,7 @@ bc_status timing_end(bc_seq* s, double* seconds) {
     *seconds = ms * 1e-3;
     // A kernel whose bounded wait ran out leaves a flag rather than hanging the device.
     if (int flag = k::matvec_error_flag()) return fail(BC_ERR_EXECUTION, "a decode kernel gave up waiting for its weight stream (code %d)", flag);
+    if (int flag = k::matmul_error_flag()) return fail(BC_ERR_EXECUTION, "a prefill kernel gave up waiting on its pipeline (code %d)", flag);
     return BC_OK;
 }
 

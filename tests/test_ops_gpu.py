@@ -292,9 +292,21 @@ def test_argmax_ties_go_to_the_lowest_index(cuda):
 
 
 # Full and partial tiles (crates/bobcat/tests/metal_matmul.rs:226-294): (n_rows, n_cols, n_tokens)
-MATMUL_SHAPES = [(64, 64, 32), (128, 256, 64), (70, 96, 33), (1, 32, 1), (6144, 2048, 128), (2048, 10752, 65), (513, 2048, 512)]
+MATMUL_SHAPES = [(64, 64, 32), (128, 256, 64), (70, 96, 33), (1, 32, 1), (6144, 2048, 128), (2048, 10752, 65), (513, 2048, 512),
+                 (128, 64, 16), (256, 128, 272), (300, 192, 100), (128, 4096, 257)]
 # Tolerance of the reference's matmul test (metal_matmul.rs), per unit of sum |w x|.
 MATMUL_TOLERANCE = 1e-4
+# The tensor-core kernel rounds weights and inputs to fp16 like the reference's Q4_0 prefill kernel
+# (matmul.metal:519-521): each product carries up to 2 * 2^-11 of relative error, so against exact
+# operands the bound per unit of sum |w x| is 1e-3; against operands rounded the same way only the
+# f32 accumulation is left.
+HALF_OPERAND_TOLERANCE = 1e-3
+ROUNDED_OPERAND_TOLERANCE = 2e-5
+
+
+def on_tensor_cores(fmt, n_cols, n_tokens):
+    """The shapes the batched multiply sends to its tcgen05 kernel."""
+    return fmt == Q4_0 and n_cols % 64 == 0 and n_tokens >= 16
 
 
 @pytest.mark.parametrize("fmt", [Q4_0, F32])
@@ -309,13 +321,20 @@ def test_matmul_stores(cuda, fmt, shape):
     y0 = rng.uniform(-1, 1, (n_tokens, n_rows)).astype(np.float32)
     wb = cuda.upload_matrix(fmt, raw, n_rows, n_cols)
     xb, yb = cuda.buffer_from(x), cuda.buffer_from(y0)
-    product = x.astype(np.float64) @ w.astype(np.float64).T
+    exact = x.astype(np.float64) @ w.astype(np.float64).T
+    tolerance, product = MATMUL_TOLERANCE, exact
+    if on_tensor_cores(fmt, n_cols, n_tokens):
+        tolerance = ROUNDED_OPERAND_TOLERANCE
+        product = x.astype(np.float16).astype(np.float64) @ w.astype(np.float16).astype(np.float64).T
     budget = np.abs(x.astype(np.float64)) @ np.abs(w.astype(np.float64)).T
     out = np.zeros_like(y0)
 
     def check(want, extra=1.0):
         err = np.abs(cuda.read(yb, out).astype(np.float64) - want) / np.maximum(budget * extra, 1e-30)
-        assert float(err.max()) < MATMUL_TOLERANCE
+        assert float(err.max()) < tolerance
+        if product is not exact and want is product:
+            loose = np.abs(cuda.read(yb, out).astype(np.float64) - exact) / np.maximum(budget, 1e-30)
+            assert float(loose.max()) < HALF_OPERAND_TOLERANCE
 
     cuda.begin(); cuda.matmul(fmt, wb, n_rows, n_cols, xb, yb, n_tokens, OVERWRITE); cuda.end()
     check(product)
