@@ -416,7 +416,7 @@ bc_status bc_op_short_conv(bc_backend* b, bc_buffer* bcx, size_t bcx_off, bc_buf
     BC_TRY(check_range(b, taps, taps_off, (size_t)n_embd * kernel * 4, "short_conv"));
     BC_TRY(check_range(b, history, hist_off, (size_t)n_embd * (kernel - 1) * 4, "short_conv"));
     BC_TRY(check_range(b, out, out_off, (size_t)n_tokens * n_embd * 4, "short_conv"));
-    return b->run("short_conv", n_tokens, n_embd, 0, 1, [&] {
+    return b->run("short_conv", n_tokens, n_embd, 0, 2, [&] {
         return k::short_conv(b->stream, reinterpret_cast<const float*>(at(bcx, bcx_off)), reinterpret_cast<const float*>(at(taps, taps_off)),
                              reinterpret_cast<float*>(at(history, hist_off)), reinterpret_cast<float*>(at(out, out_off)), n_embd, kernel,
                              n_tokens);
@@ -432,8 +432,8 @@ bc_status bc_op_matmul(bc_backend* b, int32_t format, bc_buffer* weights, size_t
     BC_TRY(check_range(b, x, x_off, (size_t)n_tokens * n_cols * 4, "matmul"));
     BC_TRY(check_range(b, y, y_off, (size_t)n_tokens * n_rows * 4, "matmul"));
     void* pack = nullptr;
-    if (k::matmul_umma_supported(w, n_tokens)) BC_TRY(b->pack_scratch(k::matmul_pack_bytes(n_tokens, n_cols), &pack));
-    return b->run("matmul", n_rows, n_cols, w.bytes(), pack ? 2 : 1, [&] {
+    if (k::matmul_umma_supported(w, n_tokens)) BC_TRY(b->pack_scratch(k::matmul_scratch_bytes(w, n_tokens), &pack));
+    return b->run("matmul", n_rows, n_cols, w.bytes(), pack ? k::matmul_umma_launches(w, n_tokens) : 1, [&] {
         return k::matmul(b->stream, w, reinterpret_cast<const float*>(at(x, x_off)), reinterpret_cast<float*>(at(y, y_off)), n_tokens,
                          n_rows, store, pack);
     });

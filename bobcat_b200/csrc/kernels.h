@@ -172,14 +172,18 @@ cudaError_t moe_combine(cudaStream_t stream, const float* expert_out, const uint
                         uint32_t n_used, uint32_t n_tokens);
 
 // Y[t][r] (store) sum_c W[r][c] X[t][c]. X is [n_tokens][n_cols] f32, Y is [n_tokens][y_stride].
-// With `pack` (matmul_pack_bytes(n_tokens, n_cols) bytes of scratch) and a matrix the tensor-core
-// kernel supports, the inputs are packed to fp16 there and the tcgen05 kernel runs (two launches);
-// otherwise the f32 SIMT tile kernel runs.
+// With `pack` (matmul_scratch_bytes(w, n_tokens) bytes of scratch) and a matrix the tensor-core
+// kernel supports, the inputs are packed to fp16 there and the tcgen05 kernel runs
+// (matmul_umma_launches launches); otherwise the f32 SIMT tile kernel runs. y_stride must be
+// w.n_rows on the tensor-core path's split-K shapes, which is what every caller passes.
 cudaError_t matmul(cudaStream_t stream, const Mat& w, const float* x, float* y, uint32_t n_tokens, uint32_t y_stride,
                    int32_t store, void* pack);
 // The tensor-core prefill kernel (kernels_matmul_umma.cu) and its input packing.
 bool matmul_umma_supported(const Mat& w, uint32_t n_tokens);
 uint64_t matmul_pack_bytes(uint32_t n_tokens, uint32_t n_cols);
+// Packed inputs plus, for shapes that split K, the partial products.
+uint64_t matmul_scratch_bytes(const Mat& w, uint32_t n_tokens);
+int matmul_umma_launches(const Mat& w, uint32_t n_tokens);
 cudaError_t matmul_pack(cudaStream_t stream, const float* x, uint32_t n_tokens, uint32_t n_cols, void* packed);
 cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* packed, float* y, uint32_t n_tokens, uint32_t y_stride,
                         int32_t store);

@@ -8,18 +8,23 @@
 //
 // Shape of the kernel. One CTA owns 128 weight rows (the MMA's M) and up to 256 tokens (its N);
 // the accumulator is 128 lanes x N columns of tensor memory. K advances 64 columns (two Q4_0
-// blocks per row) per pipeline stage:
-//   * 8 producer warps stream the tile's quants and scales from the split layout with cp.async
-//     into a private raw ring (8 chunks in flight per thread, which covers HBM latency), turn
-//     nibbles into fp16 with logic ops on packed halves, and store them in the operand layout;
+// blocks per row) per pipeline stage, four stages:
+//   * 16 producer warps in four groups. Group g takes every fourth chunk: a thread loads its
+//     row's two blocks (32 bytes of quants, two scales) two turns ahead into registers, turns
+//     nibbles into fp16 with logic ops on packed halves before it waits for the stage, and then
+//     only stores them in the operand layout. The groups' turns overlap, which hides the latency
+//     of a turn (the wait for the stage, the proxy fence, the arrival), not only that of the loads;
 //   * one thread brings the stage's token tile, already fp16 and already in operand layout (see
 //     pack_kernel), with a single bulk copy;
 //   * one thread issues four tcgen05.mma (K = 16 each) per stage and commits the stage's release;
 //   * after the last stage the producer warps become the epilogue: tcgen05.ld, the store mode,
 //     coalesced stores (a warp's 32 lanes are 32 consecutive rows of one token).
+// Matrices with few row tiles split K over blockIdx.z so the grid fills the device; the partial
+// products go to scratch and reduce_kernel adds them in a fixed order, so results do not depend on
+// scheduling.
 // Operand layout (both operands, K-major, no swizzle): core matrices of 8 rows x 8 halves (128
 // contiguous bytes); the 8 core matrices of an 8-row group follow one another along K, and groups
-// follow one another, so a tile of R rows is R / 8 kilobytes-sized groups whatever R is.
+// follow one another, so a tile of R rows is R / 8 groups of a kilobyte whatever R is.
 // Within a Q4_0 block the K order is permuted to the order the nibbles fall out of a quant word
 // (word j gives elements 4j, 4j+2, 4j+1, 4j+3, 16+4j, 16+4j+2, 16+4j+1, 16+4j+3); the packed
 // inputs use the same order, and a dot product does not care.
@@ -45,9 +50,12 @@ using namespace async;
 constexpr uint32_t kRows = 128;       // weight rows per CTA: the MMA's M
 constexpr uint32_t kMaxTokens = 256;  // tokens per CTA: the MMA's N, a multiple of 16
 constexpr uint32_t kChunkK = 64;      // columns per stage
-constexpr uint32_t kStages = 3;
-constexpr uint32_t kRawDepth = 8;  // chunks of raw quants in flight per producer thread
-constexpr uint32_t kProducers = 256;
+constexpr uint32_t kChunkBlocks = kChunkK / 32;  // Q4_0 blocks per row per stage
+constexpr uint32_t kCores = kChunkK / 8;         // core matrices along K per stage
+constexpr uint32_t kStages = 4;
+constexpr uint32_t kGroups = 4;            // producer groups; group g takes every kGroups-th chunk
+constexpr uint32_t kGroupThreads = kRows;  // a producer thread per row of the tile
+constexpr uint32_t kProducers = kGroups * kGroupThreads;
 constexpr uint32_t kTmaWarp = kProducers / 32, kMmaWarp = kTmaWarp + 1;
 constexpr uint32_t kThreads = kProducers + 64;
 constexpr uint32_t kATile = kRows * kChunkK * 2;       // 16 KB
@@ -56,8 +64,8 @@ constexpr uint32_t kGroupBytes = 8 * kChunkK * 2;      // an 8-row group of a st
 constexpr uint32_t kCoreBytes = 128;
 constexpr uint32_t kTmemColumns = 256;
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr size_t kSmemBytes =
-    kStages * (kATile + kBTile) + kRawDepth * kProducers * (16 + 4) + (2 * kStages + 1) * 8 + 16;
+constexpr uint32_t kMaxSplit = 8;
+constexpr size_t kSmemBytes = kStages * (kATile + kBTile) + (2 * kStages + 1) * 8 + 16;
 
 __device__ int g_matmul_error;
 
@@ -65,9 +73,11 @@ struct UmmaParams {
     const uint4* quants;   // split layout: [n_rows][n_blocks] 16-byte groups
     const __half* scales;  // [n_rows][n_blocks]
     const __half* packed;  // inputs in operand layout: [n_chunks][token_groups][8 cores][8 tokens][8 halves]
-    float* y;
+    float* y;              // the output, or with split > 1 the partial products [split][n_tokens][n_rows]
     uint32_t n_rows, n_blocks, n_chunks, n_tokens, y_stride, token_groups;
+    uint32_t split;  // parts K is divided into (blockIdx.z)
     int store;
+    int debug;  // timing experiments: 1 no dequant, 2 no token copies, 4 no MMA, 8 no stores
 };
 
 // X [n_tokens][n_cols] f32 -> fp16 operand layout, zero rows up to the padded token count. One
@@ -76,13 +86,13 @@ __global__ void __launch_bounds__(256) pack_kernel(const float* __restrict__ x, 
                                                    uint32_t n_cols, uint32_t token_groups, uint64_t total) {
     uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;  // index of the 16-byte output
     if (o >= total) return;
-    uint32_t tr = o & 7, core = (o >> 3) & 7;
-    uint64_t group = o >> 6;  // chunk * token_groups + token group
+    uint32_t tr = o & 7, j = (o >> 3) & (kCores - 1);
+    uint64_t group = o / (8 * kCores);  // chunk * token_groups + token group
     uint32_t tg = group % token_groups, chunk = group / token_groups;
-    uint32_t token = tg * 8 + tr, block = core >> 2, j = core & 3;
+    uint32_t token = tg * 8 + tr;
     uint4 out = make_uint4(0, 0, 0, 0);
     if (token < n_tokens) {
-        const float* src = x + (uint64_t)token * n_cols + chunk * kChunkK + block * 32 + 4 * j;
+        const float* src = x + (uint64_t)token * n_cols + chunk * kChunkK + (j >> 2) * 32 + 4 * (j & 3);
         float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 16);
         __half2 a = __floats2half2_rn(lo.x, lo.z), b = __floats2half2_rn(lo.y, lo.w);
         __half2 c = __floats2half2_rn(hi.x, hi.z), d = __floats2half2_rn(hi.y, hi.w);
@@ -122,9 +132,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* a_tiles = smem;
     uint8_t* b_tiles = a_tiles + kStages * kATile;
-    uint4* raw_q = reinterpret_cast<uint4*>(b_tiles + kStages * kBTile);
-    uint32_t* raw_s = reinterpret_cast<uint32_t*>(raw_q + kRawDepth * kProducers);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(raw_s + kRawDepth * kProducers);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(b_tiles + kStages * kBTile);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
     volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -132,13 +140,18 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
     const uint32_t tok0 = blockIdx.x * kMaxTokens, row0 = blockIdx.y * kRows;
     const uint32_t left = p.n_tokens - tok0;
     const uint32_t n_tile = left >= kMaxTokens ? kMaxTokens : ((left + 15u) & ~15u);  // the MMA's N
+    // This CTA's share of K.
+    const uint32_t per_part = (p.n_chunks + p.split - 1) / p.split;
+    const uint32_t kc_begin = blockIdx.z * per_part;
+    const uint32_t kc_end = kc_begin + per_part < p.n_chunks ? kc_begin + per_part : p.n_chunks;
+    const uint32_t my_chunks = kc_end > kc_begin ? kc_end - kc_begin : 0;
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + kStages * 8, accum = empty0 + kStages * 8;
     const uint32_t a0 = smem_u32(a_tiles), b0 = smem_u32(b_tiles);
 
     if (tid == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
-            mbar_init(full0 + 8 * s, kProducers + 1);  // every producer thread, plus the bulk copy's arrive.expect_tx
-            mbar_init(empty0 + 8 * s, 1);              // the MMA thread's commit
+            mbar_init(full0 + 8 * s, kGroupThreads / 32 + 1);  // the group's warps, plus the bulk copy's arrive.expect_tx
+            mbar_init(empty0 + 8 * s, 1);                      // the MMA thread's commit
         }
         mbar_init(accum, 1);
         *dead = 0;
@@ -151,57 +164,79 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
     const uint32_t tmem = *tmem_slot;
 
     if (warp < kTmaWarp) {
-        // ---- producers: row `row` of the tile, block `half` of each chunk
-        const uint32_t row = tid & (kRows - 1), half = tid >> 7;
+        // ---- producers: group `group` takes chunks group, group + kGroups, ...
+        const uint32_t row = tid & (kRows - 1), group = tid / kGroupThreads;
         const uint32_t grow = row0 + row;
         const bool valid = grow < p.n_rows;
-        const uint4* qsrc = p.quants + (uint64_t)(valid ? grow : 0) * p.n_blocks + half;
-        const __half* ssrc = p.scales + (uint64_t)(valid ? grow : 0) * p.n_blocks;
-        const uint32_t rq = smem_u32(raw_q) + tid * 16, rs = smem_u32(raw_s) + tid * 4;
-        auto issue = [&](uint32_t kc) {
-            if (valid && kc < p.n_chunks) {
-                uint32_t slot = kc % kRawDepth;
-                cp_async_16(rq + slot * (kProducers * 16), qsrc + 2 * kc);
-                cp_async_4(rs + slot * (kProducers * 4), ssrc + 2 * kc);
-            }
-            cp_async_commit();
+        const uint4* qsrc = p.quants + (uint64_t)(valid ? grow : 0) * p.n_blocks + (uint64_t)kc_begin * kChunkBlocks;
+        const unsigned short* ssrc =
+            reinterpret_cast<const unsigned short*>(p.scales) + (uint64_t)(valid ? grow : 0) * p.n_blocks + (uint64_t)kc_begin * kChunkBlocks;
+        const uint32_t a_off = (row >> 3) * kGroupBytes + (row & 7) * 16;
+        const bool load = valid && !(p.debug & 1);
+        // A row's share of a chunk. Rows past the matrix keep scale zero, so their tile rows are zero.
+        struct Share {
+            uint4 q[kChunkBlocks];
+            unsigned short d[kChunkBlocks];
         };
-        for (uint32_t kc = 0; kc + 1 < kRawDepth; ++kc) issue(kc);
-        const uint32_t a_off = (row >> 3) * kGroupBytes + (row & 7) * 16 + half * 4 * kCoreBytes;
-        bool alive = true;
-        for (uint32_t kc = 0; kc < p.n_chunks; ++kc) {
-            issue(kc + kRawDepth - 1);
-            cp_async_wait<kRawDepth - 1>();
-            const uint32_t slot = kc % kRawDepth;
-            uint4 q = make_uint4(0, 0, 0, 0);
-            uint32_t sbits = 0;  // rows past the matrix: scale zero, so the tile row is zero
-            if (valid) {
-                q = raw_q[slot * kProducers + tid];
-                sbits = raw_s[slot * kProducers + tid];
+        auto fetch = [&](uint32_t i) {
+            Share r;
+#pragma unroll
+            for (uint32_t b = 0; b < kChunkBlocks; ++b) {
+                r.q[b] = make_uint4(0, 0, 0, 0);
+                r.d[b] = 0;
+                if (load && i < my_chunks) {
+                    r.q[b] = __ldg(qsrc + (uint64_t)i * kChunkBlocks + b);
+                    r.d[b] = __ldg(ssrc + (uint64_t)i * kChunkBlocks + b);
+                }
             }
-            const uint16_t dbits = half ? (uint16_t)(sbits >> 16) : (uint16_t)(sbits & 0xffffu);
-            const __half d = __ushort_as_half(dbits);
-            const __half2 scale = __halves2half2(d, d);
-            const uint32_t stage = kc % kStages, use = kc / kStages;
-            if (!mbar_wait(empty0 + 8 * stage, (use & 1) ^ 1, kSpinLimit, dead)) {
-                give_up(dead, 1);
+            return r;
+        };
+        // Two turns of loads stay in flight in registers.
+        Share cur = fetch(group), next = fetch(group + kGroups);
+        bool alive = true;
+        uint32_t stage = group % kStages, phase = 1;  // the parity a free stage shows
+        for (uint32_t i = group; i < my_chunks; i += kGroups) {
+            Share after = fetch(i + 2 * kGroups);
+            // Dequantise before waiting for the stage, so only the stores follow the wait.
+            uint4 v[kChunkBlocks * 4];
+#pragma unroll
+            for (uint32_t b = 0; b < kChunkBlocks; ++b) {
+                const __half d = __ushort_as_half(cur.d[b]);
+                const __half2 scale = __halves2half2(d, d);
+                v[4 * b + 0] = dequant_word(cur.q[b].x, scale);
+                v[4 * b + 1] = dequant_word(cur.q[b].y, scale);
+                v[4 * b + 2] = dequant_word(cur.q[b].z, scale);
+                v[4 * b + 3] = dequant_word(cur.q[b].w, scale);
+            }
+            // Lane 0 polls for the whole warp.
+            bool ok = lane != 0 || mbar_wait(empty0 + 8 * stage, phase, kSpinLimit, dead);
+            if (!__all_sync(0xffffffffu, ok)) {
+                if (lane == 0) give_up(dead, 1);
                 alive = false;
                 break;
             }
-            const uint32_t dst = a0 + stage * kATile + a_off;
-            const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+            if (!(p.debug & 1)) {
+                const uint32_t dst = a0 + stage * kATile + a_off;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint4 v = dequant_word(words[j], scale);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + j * kCoreBytes), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                             : "memory");
+                for (uint32_t j = 0; j < kChunkBlocks * 4; ++j) {
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + j * kCoreBytes), "r"(v[j].x), "r"(v[j].y), "r"(v[j].z),
+                                 "r"(v[j].w)
+                                 : "memory");
+                }
             }
             fence_proxy_async();
-            mbar_arrive(full0 + 8 * stage);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full0 + 8 * stage);
+            cur = next;
+            next = after;
+            stage += kGroups;
+            if (stage >= kStages) {
+                stage -= kStages;
+                phase ^= 1;
+            }
         }
-        cp_async_wait<0>();
 
-        // ---- epilogue: lanes 32 * (warp % 4).. of tensor memory, half of the columns per warp
+        // ---- epilogue: lanes 32 * (warp % 4).. of tensor memory, a quarter of the columns per warp
         alive = __all_sync(0xffffffffu, alive);
         if (alive && !mbar_wait(accum, 0, kSpinLimit, dead)) {
             give_up(dead, 2);
@@ -210,20 +245,20 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
         alive = __all_sync(0xffffffffu, alive);
         if (alive) {
             tc_fence_after_sync();
-            const uint32_t quarter = warp & 3, units = n_tile / 16, mid = (units + 1) / 2;
-            const uint32_t first = warp >= 4 ? mid : 0, last = warp >= 4 ? units : mid;
+            const uint32_t quarter = warp & 3, part = warp >> 2, units = n_tile / 16;
             const uint32_t out_row = row0 + quarter * 32 + lane;
-            for (uint32_t u = first; u < last; ++u) {
+            float* out = p.y + (p.split > 1 ? (uint64_t)blockIdx.z * p.n_tokens * p.y_stride : 0);
+            for (uint32_t u = part; u < units; u += kGroups) {
                 float v[16];
                 __syncwarp();
                 tmem_load_16(tmem + ((quarter * 32) << 16) + u * 16, v);
-                if (out_row < p.n_rows) {
+                if (out_row < p.n_rows && !(p.debug & 8)) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         uint32_t tok = tok0 + u * 16 + j;
                         if (tok < p.n_tokens) {
-                            float* y = p.y + (uint64_t)tok * p.y_stride + out_row;
-                            float r = v[j];
+                            float* y = out + (uint64_t)tok * p.y_stride + out_row;
+                            float r = my_chunks ? v[j] : 0.f;
                             if (p.store == BC_STORE_ACCUMULATE) r += *y;
                             else if (p.store == BC_STORE_SWIGLU) {
                                 float g = *y;
@@ -240,34 +275,48 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
         if (lane == 0) {
             const uint32_t bytes = n_tile * kChunkK * 2;
             const __half* src = p.packed + (uint64_t)(tok0 / 8) * (8 * kChunkK);
-            for (uint32_t kc = 0; kc < p.n_chunks; ++kc) {
-                const uint32_t stage = kc % kStages, use = kc / kStages;
-                if (!mbar_wait(empty0 + 8 * stage, (use & 1) ^ 1, kSpinLimit, dead)) {
+            uint32_t stage = 0, phase = 1;
+            for (uint32_t i = 0; i < my_chunks; ++i, ++stage) {
+                if (stage == kStages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+                if (!mbar_wait(empty0 + 8 * stage, phase, kSpinLimit, dead)) {
                     give_up(dead, 3);
                     break;
                 }
+                if (p.debug & 2) {
+                    mbar_arrive(full0 + 8 * stage);
+                    continue;
+                }
                 mbar_arrive_expect(full0 + 8 * stage, bytes);
-                bulk_load(b0 + stage * kBTile, src + (uint64_t)kc * p.token_groups * (8 * kChunkK), bytes, full0 + 8 * stage);
+                bulk_load(b0 + stage * kBTile, src + (uint64_t)(kc_begin + i) * p.token_groups * (8 * kChunkK), bytes, full0 + 8 * stage);
             }
         }
     } else {
-        // ---- the tensor core: four K = 16 steps per stage
+        // ---- the tensor core: kChunkK / 16 steps of K = 16 per stage
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_f16(kRows, n_tile);
+            const uint64_t a_desc0 = umma_desc(a0, kCoreBytes, kGroupBytes), b_desc0 = umma_desc(b0, kCoreBytes, kGroupBytes);
             bool alive = true;
-            for (uint32_t kc = 0; kc < p.n_chunks; ++kc) {
-                const uint32_t stage = kc % kStages, use = kc / kStages;
-                if (!mbar_wait(full0 + 8 * stage, use & 1, kSpinLimit, dead)) {
+            uint32_t stage = 0, phase = 0;
+            for (uint32_t i = 0; i < my_chunks; ++i, ++stage) {
+                if (stage == kStages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+                if (!mbar_wait(full0 + 8 * stage, phase, kSpinLimit, dead)) {
                     give_up(dead, 4);
                     alive = false;
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t a = a0 + stage * kATile, b = b0 + stage * kBTile;
+                // The address field counts 16-byte units, so stepping a descriptor is an add.
+                const uint64_t a_desc = a_desc0 + ((stage * kATile) >> 4), b_desc = b_desc0 + ((stage * kBTile) >> 4);
+                if (!(p.debug & 4)) {
 #pragma unroll
-                for (uint32_t j = 0; j < kChunkK / 16; ++j) {
-                    umma_f16(tmem, umma_desc(a + j * 2 * kCoreBytes, kCoreBytes, kGroupBytes),
-                             umma_desc(b + j * 2 * kCoreBytes, kCoreBytes, kGroupBytes), idesc, (kc | j) != 0);
+                    for (uint32_t j = 0; j < kChunkK / 16; ++j)
+                        umma_f16(tmem, a_desc + ((j * 2 * kCoreBytes) >> 4), b_desc + ((j * 2 * kCoreBytes) >> 4), idesc, (i | j) != 0);
                 }
                 umma_commit(empty0 + 8 * stage);
             }
@@ -285,6 +334,49 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
     }
 }
 
+// y (store) the sum of the `split` partial products, added in index order.
+__global__ void __launch_bounds__(256) reduce_kernel(const float* __restrict__ partial, float* __restrict__ y, uint32_t n_rows,
+                                                     uint32_t n_tokens, uint32_t y_stride, uint32_t split, int store) {
+    const uint64_t total = (uint64_t)n_tokens * n_rows;
+    const uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= total) return;  // n_rows is a multiple of 4 here, so a float4 never straddles tokens
+    float4 sum = *reinterpret_cast<const float4*>(partial + i);
+    for (uint32_t s = 1; s < split; ++s) {
+        float4 v = *reinterpret_cast<const float4*>(partial + s * total + i);
+        sum.x += v.x;
+        sum.y += v.y;
+        sum.z += v.z;
+        sum.w += v.w;
+    }
+    const uint32_t tok = (uint32_t)(i / n_rows), row = (uint32_t)(i % n_rows);
+    float4* out = reinterpret_cast<float4*>(y + (uint64_t)tok * y_stride + row);
+    if (store == BC_STORE_ACCUMULATE) {
+        float4 o = *out;
+        sum.x += o.x;
+        sum.y += o.y;
+        sum.z += o.z;
+        sum.w += o.w;
+    } else if (store == BC_STORE_SWIGLU) {
+        float4 g = *out;
+        sum.x = g.x / (1.f + expf(-g.x)) * sum.x;
+        sum.y = g.y / (1.f + expf(-g.y)) * sum.y;
+        sum.z = g.z / (1.f + expf(-g.z)) * sum.z;
+        sum.w = g.w / (1.f + expf(-g.w)) * sum.w;
+    }
+    *out = sum;
+}
+
+// Parts to split K into: enough CTAs to fill the device, at least 512 columns each.
+uint32_t choose_split(uint32_t n_rows, uint32_t n_cols, uint32_t n_tokens, uint32_t y_stride) {
+    const uint32_t tiles = ((n_rows + kRows - 1) / kRows) * ((n_tokens + kMaxTokens - 1) / kMaxTokens);
+    const uint32_t chunks = n_cols / kChunkK;
+    if (n_rows % 4 != 0 || y_stride % 4 != 0) return 1;
+    uint32_t split = (uint32_t)sm_count() / (tiles ? tiles : 1);
+    if (split > kMaxSplit) split = kMaxSplit;
+    while (split > 1 && chunks / split < 8) --split;
+    return split < 1 ? 1 : split;
+}
+
 bool umma_disabled() {
     static const bool off = [] {
         const char* v = std::getenv("BOBCAT_NO_UMMA_MATMUL");
@@ -297,37 +389,59 @@ bool umma_disabled() {
 
 uint64_t matmul_pack_bytes(uint32_t n_tokens, uint32_t n_cols) { return (uint64_t)((n_tokens + 15u) & ~15u) * n_cols * 2; }
 
+uint64_t matmul_scratch_bytes(const Mat& w, uint32_t n_tokens) {
+    uint64_t pack = (matmul_pack_bytes(n_tokens, w.n_cols) + 255) & ~255ull;
+    uint32_t split = choose_split(w.n_rows, w.n_cols, n_tokens, w.n_rows);
+    return pack + (split > 1 ? (uint64_t)split * n_tokens * w.n_rows * 4 : 0);
+}
+
+int matmul_umma_launches(const Mat& w, uint32_t n_tokens) { return choose_split(w.n_rows, w.n_cols, n_tokens, w.n_rows) > 1 ? 3 : 2; }
+
 bool matmul_umma_supported(const Mat& w, uint32_t n_tokens) {
     return !umma_disabled() && w.format == BC_Q4_0 && w.n_cols % kChunkK == 0 && w.n_cols > 0 && n_tokens >= 16;
 }
 
 cudaError_t matmul_pack(cudaStream_t stream, const float* x, uint32_t n_tokens, uint32_t n_cols, void* packed) {
     uint32_t token_groups = ((n_tokens + 15u) & ~15u) / 8;
-    uint64_t total = (uint64_t)(n_cols / kChunkK) * token_groups * 64;
+    uint64_t total = (uint64_t)(n_cols / kChunkK) * token_groups * (8 * kCores);
     if (total == 0) return cudaSuccess;
     pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, static_cast<__half*>(packed), n_tokens, n_cols, token_groups, total);
     return cudaGetLastError();
 }
 
-cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* packed, float* y, uint32_t n_tokens, uint32_t y_stride,
+cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, float* y, uint32_t n_tokens, uint32_t y_stride,
                         int32_t store) {
     if (n_tokens == 0 || w.n_rows == 0) return cudaSuccess;
     cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel), kSmemBytes);
     if (err != cudaSuccess) return err;
+    // The split must match matmul_scratch_bytes, which sized the scratch for a dense output.
+    const uint32_t split = y_stride == w.n_rows ? choose_split(w.n_rows, w.n_cols, n_tokens, y_stride) : 1;
+    float* partial = reinterpret_cast<float*>(static_cast<char*>(const_cast<void*>(scratch)) +
+                                              ((matmul_pack_bytes(n_tokens, w.n_cols) + 255) & ~255ull));
     UmmaParams p;
     p.quants = static_cast<const uint4*>(w.data);
     p.scales = w.scales;
-    p.packed = static_cast<const __half*>(packed);
-    p.y = y;
+    p.packed = static_cast<const __half*>(scratch);
+    p.y = split > 1 ? partial : y;
     p.n_rows = w.n_rows;
     p.n_blocks = w.n_cols / 32;
-    p.n_chunks = w.n_cols / kChunkK;
+    p.n_chunks = w.n_cols / kChunkK;  // matmul_umma_supported checked the width
     p.n_tokens = n_tokens;
-    p.y_stride = y_stride;
+    p.y_stride = split > 1 ? w.n_rows : y_stride;
     p.token_groups = ((n_tokens + 15u) & ~15u) / 8;
-    p.store = store;
-    dim3 grid((n_tokens + kMaxTokens - 1) / kMaxTokens, (w.n_rows + kRows - 1) / kRows);
+    p.split = split;
+    p.store = split > 1 ? BC_STORE_OVERWRITE : store;
+    static const int debug = [] {
+        const char* v = std::getenv("BOBCAT_UMMA_DEBUG");
+        return v ? std::atoi(v) : 0;
+    }();
+    p.debug = debug;
+    dim3 grid((n_tokens + kMaxTokens - 1) / kMaxTokens, (w.n_rows + kRows - 1) / kRows, split);
     matmul_umma_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+    err = cudaGetLastError();
+    if (err != cudaSuccess || split == 1) return err;
+    const uint64_t quads = (uint64_t)n_tokens * w.n_rows / 4;
+    reduce_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(partial, y, w.n_rows, n_tokens, y_stride, split, store);
     return cudaGetLastError();
 }
 

@@ -176,28 +176,58 @@ __global__ void norm_rope_kernel(NormRopeParams p) {
     }
 }
 
-// One thread per channel, serial over tokens: bx = B * X, the taps over bx and the history, the
-// history shift (crates/bobcat/src/lfm2.rs:456-475). bcx is [n_tokens][3 n_embd], out is
-// [n_tokens][n_embd], history is [kernel - 1][n_embd]. kernel <= 9.
-__global__ void short_conv_kernel(const float* __restrict__ bcx, const float* __restrict__ taps,
-                                  float* __restrict__ history, float* __restrict__ out, uint32_t n_embd,
-                                  uint32_t kernel, uint32_t n_tokens) {
-    uint32_t ch = blockIdx.x * blockDim.x + threadIdx.x;
-    if (ch >= n_embd) return;
-    float tap[9], hist[8];
-    for (uint32_t kk = 0; kk < kernel; ++kk) tap[kk] = taps[(uint64_t)ch * kernel + kk];
-    for (uint32_t kk = 0; kk + 1 < kernel; ++kk) hist[kk] = history[(uint64_t)kk * n_embd + ch];
-    for (uint32_t t = 0; t < n_tokens; ++t) {
-        const float* row = bcx + (uint64_t)t * 3 * n_embd;
-        float b = row[ch], c = row[n_embd + ch], x = row[2 * n_embd + ch];
-        float bx = b * x;
-        float sum = tap[kernel - 1] * bx;
-        for (uint32_t kk = 0; kk + 1 < kernel; ++kk) sum += tap[kk] * hist[kk];
-        for (uint32_t kk = 0; kk + 2 < kernel; ++kk) hist[kk] = hist[kk + 1];
-        hist[kernel - 2] = bx;
-        out[(uint64_t)t * n_embd + ch] = c * sum;
+// The gated short convolution over a batch (crates/bobcat/src/lfm2.rs:456-475): bx = B * X, the
+// taps over bx of this token and the kernel - 1 before it (from the batch, or from the history for
+// the first tokens), times C. bcx is [n_tokens][3 n_embd], out is [n_tokens][n_embd], history is
+// [kernel - 1][n_embd], oldest first. kernel <= 9. One thread per (token, channel); the sum runs in
+// the order of the token-by-token recurrence, so batches of any split give the same bits. The
+// history is only read here; short_conv_history_kernel rewrites it afterwards.
+__device__ __forceinline__ void short_conv_token(const float* __restrict__ bcx, const float* __restrict__ taps,
+                                                 const float* __restrict__ history, float* __restrict__ out, uint32_t n_embd,
+                                                 uint32_t kernel, uint32_t t, uint32_t ch) {
+    const float* row = bcx + (uint64_t)t * 3 * n_embd;
+    const float b = row[ch], c = row[n_embd + ch], x = row[2 * n_embd + ch];
+    float sum = taps[(uint64_t)ch * kernel + kernel - 1] * (b * x);
+    // Tap kk meets the product of token t - (kernel - 1) + kk.
+    for (uint32_t kk = 0; kk + 1 < kernel; ++kk) {
+        int64_t src = (int64_t)t - (int64_t)(kernel - 1) + kk;
+        float past;
+        if (src >= 0) {
+            const float* r = bcx + (uint64_t)src * 3 * n_embd;
+            past = r[ch] * r[2 * n_embd + ch];
+        } else {
+            past = history[(uint64_t)(src + (int64_t)(kernel - 1)) * n_embd + ch];
+        }
+        sum += taps[(uint64_t)ch * kernel + kk] * past;
     }
-    for (uint32_t kk = 0; kk + 1 < kernel; ++kk) history[(uint64_t)kk * n_embd + ch] = hist[kk];
+    out[(uint64_t)t * n_embd + ch] = c * sum;
+}
+
+__global__ void __launch_bounds__(256) short_conv_kernel(const float* __restrict__ bcx, const float* __restrict__ taps,
+                                                         const float* __restrict__ history, float* __restrict__ out, uint32_t n_embd,
+                                                         uint32_t kernel, uint32_t n_tokens) {
+    const uint32_t ch = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ch >= n_embd) return;
+    for (uint32_t t = blockIdx.y; t < n_tokens; t += gridDim.y) short_conv_token(bcx, taps, history, out, n_embd, kernel, t, ch);
+}
+
+// The history after the batch: slot kk holds the product of token n_tokens - (kernel - 1) + kk, or
+// an older slot when the batch is shorter than the history. One thread per channel.
+__global__ void short_conv_history_kernel(const float* __restrict__ bcx, float* __restrict__ history, uint32_t n_embd, uint32_t kernel,
+                                          uint32_t n_tokens) {
+    const uint32_t ch = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ch >= n_embd) return;
+    float next[8];
+    for (uint32_t kk = 0; kk + 1 < kernel; ++kk) {
+        int64_t src = (int64_t)n_tokens - (int64_t)(kernel - 1) + kk;
+        if (src >= 0) {
+            const float* r = bcx + (uint64_t)src * 3 * n_embd;
+            next[kk] = r[ch] * r[2 * n_embd + ch];
+        } else {
+            next[kk] = history[(uint64_t)(src + (int64_t)(kernel - 1)) * n_embd + ch];
+        }
+    }
+    for (uint32_t kk = 0; kk + 1 < kernel; ++kk) history[(uint64_t)kk * n_embd + ch] = next[kk];
 }
 
 // One CTA of 1024 threads scans the vocabulary; ties go to the lowest index.
@@ -405,7 +435,8 @@ cudaError_t silu_mul(cudaStream_t stream, float* x, const float* gate, uint64_t 
 cudaError_t short_conv(cudaStream_t stream, const float* bcx, const float* taps, float* history, float* out, uint32_t n_embd,
                        uint32_t kernel, uint32_t n_tokens) {
     if (n_tokens == 0) return cudaSuccess;
-    short_conv_kernel<<<blocks_for(n_embd, 128), 128, 0, stream>>>(bcx, taps, history, out, n_embd, kernel, n_tokens);
+    short_conv_kernel<<<dim3(blocks_for(n_embd, 256), n_tokens < 65535u ? n_tokens : 65535u), 256, 0, stream>>>(bcx, taps, history, out, n_embd, kernel, n_tokens);
+    short_conv_history_kernel<<<blocks_for(n_embd, 128), 128, 0, stream>>>(bcx, history, n_embd, kernel, n_tokens);
     return cudaGetLastError();
 }
 

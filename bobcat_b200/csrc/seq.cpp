@@ -45,8 +45,8 @@ struct Recorder {
 
     void matmul(const k::Mat& w, const float* x, float* y, uint32_t n, int store) {
         void* pack = nullptr;
-        if (status == BC_OK && k::matmul_umma_supported(w, n)) status = s.backend->pack_scratch(k::matmul_pack_bytes(n, w.n_cols), &pack);
-        run("matmul", w.n_rows, w.n_cols, w.bytes(), pack ? 2 : 1, [&] { return k::matmul(stream, w, x, y, n, w.n_rows, store, pack); });
+        if (status == BC_OK && k::matmul_umma_supported(w, n)) status = s.backend->pack_scratch(k::matmul_scratch_bytes(w, n), &pack);
+        run("matmul", w.n_rows, w.n_cols, w.bytes(), pack ? k::matmul_umma_launches(w, n) : 1, [&] { return k::matmul(stream, w, x, y, n, w.n_rows, store, pack); });
     }
 
     size_t kv_element_bytes() const { return s.kv_half ? 2 : 4; }
@@ -203,7 +203,7 @@ struct Recorder {
             } else {
                 float* history = s.conv_state + (size_t)S.cache_index * (hp.conv_kernel - 1) * n_embd;
                 matmul(D.in_proj, s.normed, s.bcx, n, BC_STORE_OVERWRITE);
-                run("short_conv", n, n_embd, 0, 1,
+                run("short_conv", n, n_embd, 0, 2,
                     [&] { return k::short_conv(stream, s.bcx, D.taps, history, s.conv_out, n_embd, hp.conv_kernel, n); });
                 matmul(D.out_proj, s.conv_out, s.hidden, n, BC_STORE_ACCUMULATE);
             }
