@@ -532,7 +532,7 @@ bc_status bc_op_attention(bc_backend* b, bc_buffer* q, size_t q_off, bc_buffer* 
     BC_TRY(check_range(b, scratch, s_off, bc_attention_scratch_floats(n_heads, head_dim, n_ctx, n_queries) * 4, "attention"));
     BC_TRY(check_range(b, out, out_off, (size_t)n_queries * n_heads * head_dim * 4, "attention"));
     k::AttentionShape shape{n_heads, n_kv_heads, head_dim, first_pos, n_queries, n_ctx, n_heads * head_dim, head_dim};
-    int launches = 2 * (int)((n_queries + 63) / 64);
+    int launches = k::attention_launches(kv_half != 0, shape);
     return b->run("attention", n_queries, first_pos + n_queries, kv_bytes * 2, launches, [&] {
         return k::attention(b->stream, reinterpret_cast<const float*>(at(q, q_off)), at(k_cache, k_off), at(v_cache, v_off), kv_half != 0,
                             reinterpret_cast<float*>(at(scratch, s_off)), reinterpret_cast<float*>(at(out, out_off)), shape);

@@ -128,6 +128,13 @@ struct AttentionShape {
 uint64_t attention_scratch_floats(uint32_t n_heads, uint32_t head_dim, uint32_t n_ctx, uint32_t n_queries);
 cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, const void* v_cache, bool kv_half,
                       float* scratch, float* out, const AttentionShape& shape);
+// Kernels `attention` launches for this shape.
+int attention_launches(bool kv_half, const AttentionShape& shape);
+// The tensor-core prefill kernel (kernels_attention_flash.cu): heads of 64 elements, f16 cache, at
+// least 32 queries, positions known at launch. `attention` picks it when it applies.
+bool attention_flash_supported(bool kv_half, const AttentionShape& shape);
+cudaError_t attention_flash(cudaStream_t stream, const float* q, const void* k_cache, const void* v_cache, float* out,
+                            const AttentionShape& shape);
 
 // argmax over n floats, ties to the lowest index. `out` is a device word; `readback` (nullable) is
 // a host-mapped word that receives the same value.

@@ -179,9 +179,14 @@ uint64_t attention_scratch_floats(uint32_t n_heads, uint32_t head_dim, uint32_t 
     return queries * n_heads * chunks * (head_dim + 2);
 }
 
+int attention_launches(bool kv_half, const AttentionShape& s) {
+    return attention_flash_supported(kv_half, s) ? 1 : 2 * (int)((s.n_queries + kQueryBatch - 1) / kQueryBatch);
+}
+
 cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, const void* v_cache, bool kv_half,
                       float* scratch, float* out, const AttentionShape& s) {
     if (s.n_queries == 0) return cudaSuccess;
+    if (attention_flash_supported(kv_half, s)) return attention_flash(stream, q, k_cache, v_cache, out, s);
     const uint32_t group = s.n_heads / s.n_kv_heads;
     const uint32_t max_chunks = (s.n_ctx + kChunk - 1) / kChunk;
     const uint32_t n_slices = kChunkThreads / s.head_dim;

@@ -81,7 +81,7 @@ struct Recorder {
             run("convert_half", 1, n * (uint32_t)kv_dim(), 0, 1,
                 [&] { return k::convert_half(stream, s.v, static_cast<__half*>(cache_at(s.v_cache, slot)), (uint64_t)n * kv_dim()); });
         k::AttentionShape shape{hp.n_heads, hp.n_kv_heads, hp.head_dim, pos, n, s.n_ctx, q_stride, q_head_stride};
-        int kernels = 2 * (int)((n + 63) / 64);
+        int kernels = k::attention_launches(s.kv_half, shape);
         uint64_t kv_bytes = (uint64_t)(pos + n) * kv_dim() * kv_element_bytes() * 2;
         (void)q_dim;
         run("attention", n, pos + n, kv_bytes, kernels, [&] {
@@ -307,7 +307,7 @@ struct Recorder {
                     run("convert_half", 1, n * (uint32_t)kv_dim(), 0, 1,
                         [&] { return k::convert_half(stream, s.v, static_cast<__half*>(cache_at(s.v_cache, slot)), (uint64_t)n * kv_dim()); });
                 k::AttentionShape shape{hp.n_heads, hp.n_kv_heads, hp.head_dim, pos, n, s.n_ctx, q_dim, hp.head_dim};
-                run("attention", n, pos + n, (uint64_t)(pos + n) * kv_dim() * kv_element_bytes() * 2, 2 * (int)((n + 63) / 64), [&] {
+                run("attention", n, pos + n, (uint64_t)(pos + n) * kv_dim() * kv_element_bytes() * 2, k::attention_launches(s.kv_half, shape), [&] {
                     return k::attention(stream, s.q_rot, cache_at(s.k_cache, layer_base(S.cache_index)), cache_at(s.v_cache, layer_base(S.cache_index)),
                                         s.kv_half, s.scores, s.attn, shape);
                 });

@@ -177,7 +177,13 @@ def test_norm_rope_matches_scalar(cuda, head_dim, n_rot, dst_half):
 
 
 # (first_pos, n_queries, n_heads, n_kv_heads, head_dim): crates/bobcat/tests/metal_attention.rs:19-27
-ATTENTION_CASES = [(0, 1, 4, 2, 64), (5, 1, 4, 2, 64), (63, 3, 8, 2, 64), (100, 70, 4, 4, 32), (0, 130, 4, 1, 64), (37, 2, 2, 1, 256), (700, 1, 32, 8, 64)]
+ATTENTION_CASES = [(0, 1, 4, 2, 64), (5, 1, 4, 2, 64), (63, 3, 8, 2, 64), (100, 70, 4, 4, 32), (0, 130, 4, 1, 64), (37, 2, 2, 1, 256), (700, 1, 32, 8, 64),
+                   (0, 512, 8, 2, 64), (100, 70, 8, 2, 64), (3, 33, 4, 2, 64), (61, 200, 4, 4, 64)]
+
+
+def on_flash_kernel(kv_half, n_q, hd):
+    """The shapes attention sends to its tensor-core prefill kernel (the reference's own rule for its flash kernel)."""
+    return kv_half and hd == 64 and n_q >= 32
 
 
 def attention_f64(q, k, v, first_pos, n_heads, n_kv_heads):
@@ -213,15 +219,20 @@ def test_attention_against_f64(cuda, case, kv_half):
     got = cuda.read(ob, np.zeros_like(q))
     want = attention_f64(q, k.astype(np.float32), v.astype(np.float32), first_pos, n_heads, n_kv)
     # The reference's kernel test allows 1e-6 absolute on inputs of this size (metal_attention.rs).
-    assert np.abs(got - want).max() < 2e-6
+    flash = on_flash_kernel(kv_half, n_q, hd)
+    # The tensor-core kernel carries queries and probabilities as two fp16 halves (about 22 bits).
+    assert np.abs(got - want).max() < (4e-6 if flash else 2e-6)
     if n_q > 1:
-        # Batched equals one query at a time.
+        # Batched equals one query at a time: bit for bit on the chunk kernels, to rounding when the batch ran on tensor cores.
         one = np.zeros_like(q)
         tmp = cuda.new_buffer(n_heads * hd * 4)
-        for i in range(n_q):
+        for i in range(0, n_q, 7 if n_q > 100 else 1):
             cuda.begin(); cuda.attention(qb.at(i * n_heads * hd * 4), kb, vb, kv_half, sb, tmp, n_heads, n_kv, hd, first_pos + i, 1, n_ctx); cuda.end()
             cuda.read(tmp, one[i])
-        assert np.array_equal(one, got)
+            if flash:
+                assert np.abs(one[i] - got[i]).max() < 4e-6
+            else:
+                assert np.array_equal(one[i], got[i])
 
 
 def test_attention_limits(cuda):
