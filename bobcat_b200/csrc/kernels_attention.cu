@@ -17,7 +17,9 @@ namespace k {
 
 namespace {
 
-constexpr int kChunk = 64;         // positions per chunk
+constexpr int kChunk = 64;         // positions per chunk of a batch
+constexpr int kDecodeChunk = 16;   // positions per chunk when only a few queries run: more, smaller CTAs fill the device
+constexpr int kDecodeQueries = 4;  // up to this many queries use the small chunks
 constexpr int kMaxGroup = 8;       // query heads per KV head
 constexpr int kQueryBatch = 64;    // queries per launch, which bounds the scratch
 constexpr int kChunkThreads = 256;
@@ -38,6 +40,7 @@ struct ChunkParams {
     uint32_t query0;      // first query of this launch
     uint32_t max_chunks;  // chunks the scratch holds per (query, head)
     const uint32_t* pos_ptr;  // when set, added to first_pos at run time
+    uint32_t chunk;           // positions per chunk
 };
 
 // Scratch layout: [query in batch][head][chunk][head_dim + 2] = (max, sum, acc[head_dim]).
@@ -48,17 +51,17 @@ __global__ void __launch_bounds__(kChunkThreads) attention_chunk_kernel(ChunkPar
     const uint32_t kv_head = blockIdx.x, chunk = blockIdx.y, qi = blockIdx.z;
     const uint32_t query = p.query0 + qi;
     const uint32_t pos = p.first_pos + (p.pos_ptr ? *p.pos_ptr : 0u) + query;  // the query attends to positions 0..pos
-    const uint32_t start = chunk * kChunk;
+    const uint32_t start = chunk * p.chunk;
     if (start > pos) return;
-    const uint32_t count = min((uint32_t)kChunk, pos + 1 - start);
+    const uint32_t count = min(p.chunk, pos + 1 - start);
     const uint32_t hd = p.head_dim, group = p.n_heads / p.n_kv_heads;
     const uint32_t kv_dim = p.n_kv_heads * hd;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = kChunkThreads / 32;
 
     extern __shared__ float smem[];
     float* qs = smem;                         // [group][hd], pre-scaled
-    float* scores = qs + group * hd;          // [group][kChunk]
-    float* partial = scores + group * kChunk; // [slices][group][hd]
+    float* scores = qs + group * hd;           // [group][chunk]
+    float* partial = scores + group * p.chunk; // [slices][group][hd]
     __shared__ float head_max[kMaxGroup], head_sum[kMaxGroup];
 
     const float scale = 1.0f / sqrtf((float)hd);
@@ -87,7 +90,7 @@ __global__ void __launch_bounds__(kChunkThreads) attention_chunk_kernel(ChunkPar
         for (int g = 0; g < kMaxGroup; ++g) {
             if (g < group) {
                 float s = warp_sum(dot[g]);
-                if (lane == 0) scores[g * kChunk + t] = s;
+                if (lane == 0) scores[g * p.chunk + t] = s;
             }
         }
     }
@@ -96,12 +99,12 @@ __global__ void __launch_bounds__(kChunkThreads) attention_chunk_kernel(ChunkPar
     // Per head: chunk maximum, exponentials, their sum. A warp per head.
     for (uint32_t g = warp; g < group; g += n_warps) {
         float m = -INFINITY;
-        for (uint32_t t = lane; t < count; t += 32) m = fmaxf(m, scores[g * kChunk + t]);
+        for (uint32_t t = lane; t < count; t += 32) m = fmaxf(m, scores[g * p.chunk + t]);
         m = warp_max(m);
         float sum = 0.f;
         for (uint32_t t = lane; t < count; t += 32) {
-            float e = expf(scores[g * kChunk + t] - m);
-            scores[g * kChunk + t] = e;
+            float e = expf(scores[g * p.chunk + t] - m);
+            scores[g * p.chunk + t] = e;
             sum += e;
         }
         sum = warp_sum(sum);
@@ -123,7 +126,7 @@ __global__ void __launch_bounds__(kChunkThreads) attention_chunk_kernel(ChunkPar
             float v = load_kv<T>(vc + (uint64_t)t * kv_dim + d);
 #pragma unroll
             for (int g = 0; g < kMaxGroup; ++g)
-                if (g < group) acc[g] += scores[g * kChunk + t] * v;
+                if (g < group) acc[g] += scores[g * p.chunk + t] * v;
         }
 #pragma unroll
         for (int g = 0; g < kMaxGroup; ++g)
@@ -149,6 +152,7 @@ struct CombineParams {
     float* out;
     uint32_t n_heads, head_dim, first_pos, query0, max_chunks;
     const uint32_t* pos_ptr;
+    uint32_t chunk;
 };
 
 // grid (n_heads, queries in batch), head_dim threads.
@@ -157,7 +161,7 @@ __global__ void attention_combine_kernel(CombineParams p) {
     pdl_wait();
     const uint32_t head = blockIdx.x, qi = blockIdx.y, d = threadIdx.x;
     const uint32_t query = p.query0 + qi, pos = p.first_pos + (p.pos_ptr ? *p.pos_ptr : 0u) + query;
-    const uint32_t n_chunks = pos / kChunk + 1, hd = p.head_dim;
+    const uint32_t n_chunks = pos / p.chunk + 1, hd = p.head_dim;
     const float* base = p.scratch + ((uint64_t)qi * p.n_heads + head) * p.max_chunks * (hd + 2);
     float m = -INFINITY;
     for (uint32_t c = 0; c < n_chunks; ++c) m = fmaxf(m, base[(uint64_t)c * (hd + 2)]);
@@ -174,9 +178,12 @@ __global__ void attention_combine_kernel(CombineParams p) {
 }  // namespace
 
 uint64_t attention_scratch_floats(uint32_t n_heads, uint32_t head_dim, uint32_t n_ctx, uint32_t n_queries) {
+    // A buffer sized for n queries also serves any smaller count, which may use the small chunks.
     uint64_t queries = n_queries < (uint32_t)kQueryBatch ? n_queries : (uint32_t)kQueryBatch;
-    uint64_t chunks = ((uint64_t)n_ctx + kChunk - 1) / kChunk;
-    return queries * n_heads * chunks * (head_dim + 2);
+    uint64_t few = n_queries < (uint32_t)kDecodeQueries ? n_queries : (uint32_t)kDecodeQueries;
+    uint64_t batch = queries * (((uint64_t)n_ctx + kChunk - 1) / kChunk);
+    uint64_t decode = few * (((uint64_t)n_ctx + kDecodeChunk - 1) / kDecodeChunk);
+    return (batch > decode ? batch : decode) * n_heads * (head_dim + 2);
 }
 
 int attention_launches(bool kv_half, const AttentionShape& s) {
@@ -188,9 +195,10 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
     if (s.n_queries == 0) return cudaSuccess;
     if (attention_flash_supported(kv_half, s)) return attention_flash(stream, q, k_cache, v_cache, out, s);
     const uint32_t group = s.n_heads / s.n_kv_heads;
-    const uint32_t max_chunks = (s.n_ctx + kChunk - 1) / kChunk;
+    const uint32_t chunk = s.n_queries <= (uint32_t)kDecodeQueries ? kDecodeChunk : kChunk;
+    const uint32_t max_chunks = (s.n_ctx + chunk - 1) / chunk;
     const uint32_t n_slices = kChunkThreads / s.head_dim;
-    size_t smem = ((size_t)group * s.head_dim + (size_t)group * kChunk + (size_t)n_slices * group * s.head_dim) * sizeof(float);
+    size_t smem = ((size_t)group * s.head_dim + (size_t)group * chunk + (size_t)n_slices * group * s.head_dim) * sizeof(float);
     cudaError_t e;
     if (kv_half) e = ensure_dynamic_smem(reinterpret_cast<const void*>(attention_chunk_kernel<__half>), smem);
     else e = ensure_dynamic_smem(reinterpret_cast<const void*>(attention_chunk_kernel<float>), smem);
@@ -199,13 +207,13 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
         uint32_t nq = s.n_queries - q0 < (uint32_t)kQueryBatch ? s.n_queries - q0 : (uint32_t)kQueryBatch;
         uint32_t last_pos = s.first_pos + q0 + nq - 1;
         ChunkParams cp{q, k_cache, v_cache, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.first_pos, s.n_ctx,
-                       s.q_stride, s.q_head_stride, q0, max_chunks, s.pos_ptr};
+                       s.q_stride, s.q_head_stride, q0, max_chunks, s.pos_ptr, chunk};
         // With a run-time position the grid covers every chunk of the context; CTAs past the position exit at once.
-        dim3 grid(s.n_kv_heads, s.pos_ptr ? max_chunks : last_pos / kChunk + 1, nq);
+        dim3 grid(s.n_kv_heads, s.pos_ptr ? max_chunks : last_pos / chunk + 1, nq);
         void* chunk_args[] = {&cp};
         const void* chunk_kernel = kv_half ? (const void*)attention_chunk_kernel<__half> : (const void*)attention_chunk_kernel<float>;
         if ((e = launch_kernel(chunk_kernel, grid, dim3(kChunkThreads), smem, stream, chunk_args)) != cudaSuccess) return e;
-        CombineParams mp{scratch, out, s.n_heads, s.head_dim, s.first_pos, q0, max_chunks, s.pos_ptr};
+        CombineParams mp{scratch, out, s.n_heads, s.head_dim, s.first_pos, q0, max_chunks, s.pos_ptr, chunk};
         void* combine_args[] = {&mp};
         if ((e = launch_kernel((const void*)attention_combine_kernel, dim3(s.n_heads, nq), dim3(s.head_dim), 0, stream, combine_args)) != cudaSuccess) return e;
     }

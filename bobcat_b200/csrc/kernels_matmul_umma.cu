@@ -253,18 +253,23 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
                 __syncwarp();
                 tmem_load_16(tmem + ((quarter * 32) << 16) + u * 16, v);
                 if (out_row < p.n_rows && !(p.debug & 8)) {
+                    // Old values first, all 16 in flight at once, so the read-modify-write stores cost one round trip.
+                    float old[16];
+                    if (p.store != BC_STORE_OVERWRITE) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            uint32_t tok = tok0 + u * 16 + j;
+                            old[j] = tok < p.n_tokens ? __ldcg(out + (uint64_t)tok * p.y_stride + out_row) : 0.f;
+                        }
+                    }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         uint32_t tok = tok0 + u * 16 + j;
                         if (tok < p.n_tokens) {
-                            float* y = out + (uint64_t)tok * p.y_stride + out_row;
                             float r = my_chunks ? v[j] : 0.f;
-                            if (p.store == BC_STORE_ACCUMULATE) r += *y;
-                            else if (p.store == BC_STORE_SWIGLU) {
-                                float g = *y;
-                                r = g / (1.f + expf(-g)) * r;
-                            }
-                            *y = r;
+                            if (p.store == BC_STORE_ACCUMULATE) r += old[j];
+                            else if (p.store == BC_STORE_SWIGLU) r = old[j] / (1.f + expf(-old[j])) * r;
+                            out[(uint64_t)tok * p.y_stride + out_row] = r;
                         }
                     }
                 }

@@ -36,7 +36,7 @@ namespace k {
 
 namespace {
 
-constexpr int kConsumers = 16;                   // consumer warps per CTA
+constexpr int kConsumers = 8;                    // consumer warps per CTA
 constexpr int kThreads = (kConsumers + 1) * 32;  // plus the producer warp
 constexpr int kDepth = 2;                        // ring slots per consumer warp
 constexpr int kStages = kConsumers * kDepth;
@@ -167,7 +167,7 @@ __device__ __forceinline__ uint32_t group_size(uint32_t q_per_job) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(kThreads, 1) matvec_mma_kernel(Params p) {
+__global__ void __launch_bounds__(kThreads, 2) matvec_mma_kernel(Params p) {
     constexpr int S = segments_per_job<MODE>();
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;                                                   // kStages * kStageBytes
@@ -461,7 +461,9 @@ cudaError_t launch(cudaStream_t stream, Params& p) {
     size_t smem = (size_t)kStages * kStageBytes + (size_t)p.n_blocks * 128;
     cudaError_t e = ensure_dynamic_smem(kernel, smem);
     if (e != cudaSuccess) return e;
-    uint32_t ctas = p.n_jobs < (uint32_t)sm_count() ? p.n_jobs : (uint32_t)sm_count();
+    static const uint32_t per_sm = [] { const char* v = getenv("BOBCAT_MMA_CTAS_PER_SM"); return v ? (uint32_t)atoi(v) : 2u; }();
+    uint32_t cap = per_sm * (uint32_t)sm_count();
+    uint32_t ctas = p.n_jobs < cap ? p.n_jobs : cap;
     void* args[] = {&p};
     return launch_kernel(kernel, dim3(ctas), dim3(kThreads), smem, stream, args);
 }

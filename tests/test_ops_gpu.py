@@ -223,16 +223,14 @@ def test_attention_against_f64(cuda, case, kv_half):
     # The tensor-core kernel carries queries and probabilities as two fp16 halves (about 22 bits).
     assert np.abs(got - want).max() < (4e-6 if flash else 2e-6)
     if n_q > 1:
-        # Batched equals one query at a time: bit for bit on the chunk kernels, to rounding when the batch ran on tensor cores.
+        # Batched equals one query at a time, to rounding: a single query splits its keys into smaller chunks than a
+        # batch does (and a batch may run on tensor cores), so the sums are taken in another order.
         one = np.zeros_like(q)
         tmp = cuda.new_buffer(n_heads * hd * 4)
         for i in range(0, n_q, 7 if n_q > 100 else 1):
             cuda.begin(); cuda.attention(qb.at(i * n_heads * hd * 4), kb, vb, kv_half, sb, tmp, n_heads, n_kv, hd, first_pos + i, 1, n_ctx); cuda.end()
             cuda.read(tmp, one[i])
-            if flash:
-                assert np.abs(one[i] - got[i]).max() < 4e-6
-            else:
-                assert np.array_equal(one[i], got[i])
+            assert np.abs(one[i] - got[i]).max() < (4e-6 if flash else 2e-6)
 
 
 def test_attention_limits(cuda):
