@@ -32,18 +32,24 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 PROMPT_TOKENS, DECODE_TOKENS = 512, 128
-METRIC = "decode tok/s, Q4_0 LFM2.5-2.6B-shape, batch 1"
+# The reference's headline metric; `value` is its decode half, the prefill half rides along under "prefill".
+METRIC = "decode & prefill tok/s, Q4 LFM2.5-2.6B-shape, batch 1; % of HBM roofline"
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
+# capture summarised in profiles/matvec_mma_lfm2-2.6b_decode.md (null for kernels not captured).
+NCU_DRAM_BYTES_PER_LAUNCH = {"matvec_swiglu 10752x2048": 24823296}
 
 
-def measured_peaks() -> tuple[float, str]:
-    """HBM GB/s to divide by: the measured copy bandwidth of this pool, else the stated fallback."""
+def measured_peaks() -> tuple[float, float, str]:
+    """(HBM GB/s, sustained dense bf16 TFLOP/s) to divide by: measured on this pool, else the stated fallback."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         try:
-            return float(json.load(open(path))["hbm_gbs"]), "measured"
+            peaks = json.load(open(path))
+            return float(peaks["hbm_gbs"]), float(peaks["bf16_tflops_sustained"]), "measured"
         except Exception:
             pass
-    return 6650.0, "fallback"
+    return 6650.0, 1400.0, "fallback"
 
 
 class ClockSampler:
@@ -255,13 +261,18 @@ def run_ours(args) -> None:
     decode_gpu, prefill_gpu, decode_wall, prefill_wall, ms_per_step = [float(v) for v in stats.tolist()]
 
     if rank == 0:
-        peak, peak_kind = measured_peaks()
+        peak, tensor_peak, peak_kind = measured_peaks()
         weight_bytes = model.decode_bytes()
         # KV traffic: f16 K and V rows of every attention layer at the mean decode position.
         kv_bytes = hp.n_attention_layers * 2 * hp.n_kv_heads * hp.head_dim * 2 * (PROMPT_TOKENS + DECODE_TOKENS / 2)
         token_bytes = weight_bytes + kv_bytes
         decode_tok_s = world * DECODE_TOKENS / decode_gpu
         prefill_tok_s = world * PROMPT_TOKENS / prefill_gpu
+        decode_rates = [DECODE_TOKENS / r[1] for r in rows]
+        # Flops of a prefilled token: two per weight of the quantised linears (the F32 output
+        # matrix runs once per prompt, for the last token only).
+        linear_weights = (weight_bytes - hp.n_vocab * hp.n_embd * 4) * 32 / 18
+        prefill_tflops = 2 * linear_weights * PROMPT_TOKENS / prefill_gpu / 1e12
         token_hash = 0
         for tok in rows[-1][4].tolist():
             token_hash = (token_hash * 1000003 + tok) & 0xFFFFFFFFFFFFFFFF
@@ -278,10 +289,14 @@ def run_ours(args) -> None:
                        "n_ctx": n_ctx, "kv_cache": "f16"},
             "decode": {"tok_s": decode_tok_s, "tpot_ms": 1e3 * decode_gpu / DECODE_TOKENS, "bytes_per_token": token_bytes,
                        "hbm_gbs": token_bytes * DECODE_TOKENS / decode_gpu / 1e9, "hbm_frac": token_bytes * DECODE_TOKENS / decode_gpu / 1e9 / peak,
-                       "hbm_frac_of_nominal_8tbs": token_bytes * DECODE_TOKENS / decode_gpu / 8e12, "token_hash": token_hash},
-            "prefill": {"tok_s": prefill_tok_s, "ttft_ms": 1e3 * prefill_gpu, "tokens": PROMPT_TOKENS, "kernels": dom["prefill_table"]},
+                       "hbm_frac_of_nominal_8tbs": token_bytes * DECODE_TOKENS / decode_gpu / 8e12, "token_hash": token_hash,
+                       "tok_s_sd_rank0": float(np.std(decode_rates))},
+            "prefill": {"tok_s": prefill_tok_s, "ttft_ms": 1e3 * prefill_gpu, "tokens": PROMPT_TOKENS, "tflops": prefill_tflops,
+                        "tensor_peak_tflops": tensor_peak, "tensor_frac": prefill_tflops / tensor_peak,
+                        "weights_pass_ms": 1e3 * (weight_bytes - hp.n_vocab * hp.n_embd * 4) / (peak * 1e9), "kernels": dom["prefill_table"]},
             "roofline": {"bound": "hbm", "kernel": "%s %dx%d" % (dom["top"]["name"], dom["top"]["n_rows"], dom["top"]["n_cols"]),
-                         "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get("%s %dx%d" % (dom["top"]["name"], dom["top"]["n_rows"], dom["top"]["n_cols"])),
                          "share_of_decode": dom["share"], "launch_us": 1e6 * dom["seconds"], "bytes_per_launch": dom["bytes"], "kernels": dom["table"]},
             "e2e": {"value": world * DECODE_TOKENS / decode_wall, "unit": "tok/s", "h2d_bytes_per_step": PROMPT_TOKENS * 4,
                     "d2h_bytes_per_step": DECODE_TOKENS * 4, "prefill_tok_s": world * PROMPT_TOKENS / prefill_wall},

@@ -40,20 +40,9 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 }
 // Wait for the phase of `parity` to complete. Gives up after `limit` polls, or as soon as `*dead`
 // (a shared flag another thread of the CTA raised when its own wait ran out) is set.
-__device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit, volatile int* dead, int poll = 0) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit, volatile int* dead) {
     for (uint32_t spin = 0; spin < limit; ++spin) {
-        if (poll ? mbar_poll(bar, parity) : mbar_test(bar, parity)) return true;
+        if (mbar_test(bar, parity)) return true;
         if ((spin & 255u) == 255u && *dead) return false;
     }
     return false;

@@ -155,22 +155,37 @@ struct CombineParams {
     uint32_t chunk;
 };
 
-// grid (n_heads, queries in batch), head_dim threads.
+// grid (n_heads, queries in batch), head_dim threads. The threads first share out the chunks'
+// maxima and sums (so the exponentials are computed once, in parallel), then each thread adds up
+// its element over the chunks with independent loads.
 __global__ void attention_combine_kernel(CombineParams p) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ float weights[512];  // exp(max_c - max) of a slice of chunks
+    __shared__ float scratch[32];
     const uint32_t head = blockIdx.x, qi = blockIdx.y, d = threadIdx.x;
     const uint32_t query = p.query0 + qi, pos = p.first_pos + (p.pos_ptr ? *p.pos_ptr : 0u) + query;
     const uint32_t n_chunks = pos / p.chunk + 1, hd = p.head_dim;
     const float* base = p.scratch + ((uint64_t)qi * p.n_heads + head) * p.max_chunks * (hd + 2);
     float m = -INFINITY;
-    for (uint32_t c = 0; c < n_chunks; ++c) m = fmaxf(m, base[(uint64_t)c * (hd + 2)]);
+    for (uint32_t c = d; c < n_chunks; c += blockDim.x) m = fmaxf(m, base[(uint64_t)c * (hd + 2)]);
+    m = warp_max(m);
+    if ((d & 31) == 0) scratch[d >> 5] = m;
+    __syncthreads();
+    m = scratch[0];
+    for (uint32_t w = 1; w < (blockDim.x + 31) / 32; ++w) m = fmaxf(m, scratch[w]);
     float sum = 0.f, acc = 0.f;
-    for (uint32_t c = 0; c < n_chunks; ++c) {
-        const float* part = base + (uint64_t)c * (hd + 2);
-        float w = expf(part[0] - m);
-        sum += w * part[1];
-        acc += w * part[2 + d];
+    for (uint32_t c0 = 0; c0 < n_chunks; c0 += 512) {
+        const uint32_t count = min(512u, n_chunks - c0);
+        __syncthreads();
+        for (uint32_t c = d; c < count; c += blockDim.x) weights[c] = expf(base[(uint64_t)(c0 + c) * (hd + 2)] - m);
+        __syncthreads();
+#pragma unroll 4
+        for (uint32_t c = 0; c < count; ++c) {
+            const float* part = base + (uint64_t)(c0 + c) * (hd + 2);
+            sum += weights[c] * part[1];
+            acc += weights[c] * part[2 + d];
+        }
     }
     p.out[(uint64_t)query * p.n_heads * hd + (uint64_t)head * hd + d] = acc / sum;
 }

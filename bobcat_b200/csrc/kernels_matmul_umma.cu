@@ -77,7 +77,6 @@ struct UmmaParams {
     uint32_t n_rows, n_blocks, n_chunks, n_tokens, y_stride, token_groups;
     uint32_t split;  // parts K is divided into (blockIdx.z)
     int store;
-    int debug;  // timing experiments: 1 no dequant, 2 no token copies, 4 no MMA, 8 no stores
 };
 
 // X [n_tokens][n_cols] f32 -> fp16 operand layout, zero rows up to the padded token count. One
@@ -172,7 +171,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
         const unsigned short* ssrc =
             reinterpret_cast<const unsigned short*>(p.scales) + (uint64_t)(valid ? grow : 0) * p.n_blocks + (uint64_t)kc_begin * kChunkBlocks;
         const uint32_t a_off = (row >> 3) * kGroupBytes + (row & 7) * 16;
-        const bool load = valid && !(p.debug & 1);
+        const bool load = valid;
         // A row's share of a chunk. Rows past the matrix keep scale zero, so their tile rows are zero.
         struct Share {
             uint4 q[kChunkBlocks];
@@ -215,14 +214,11 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
                 alive = false;
                 break;
             }
-            if (!(p.debug & 1)) {
-                const uint32_t dst = a0 + stage * kATile + a_off;
+            const uint32_t dst = a0 + stage * kATile + a_off;
 #pragma unroll
-                for (uint32_t j = 0; j < kChunkBlocks * 4; ++j) {
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + j * kCoreBytes), "r"(v[j].x), "r"(v[j].y), "r"(v[j].z),
-                                 "r"(v[j].w)
-                                 : "memory");
-                }
+            for (uint32_t j = 0; j < kChunkBlocks * 4; ++j) {
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + j * kCoreBytes), "r"(v[j].x), "r"(v[j].y), "r"(v[j].z), "r"(v[j].w)
+                             : "memory");
             }
             fence_proxy_async();
             __syncwarp();
@@ -252,7 +248,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
                 float v[16];
                 __syncwarp();
                 tmem_load_16(tmem + ((quarter * 32) << 16) + u * 16, v);
-                if (out_row < p.n_rows && !(p.debug & 8)) {
+                if (out_row < p.n_rows) {
                     // Old values first, all 16 in flight at once, so the read-modify-write stores cost one round trip.
                     float old[16];
                     if (p.store != BC_STORE_OVERWRITE) {
@@ -290,10 +286,6 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
                     give_up(dead, 3);
                     break;
                 }
-                if (p.debug & 2) {
-                    mbar_arrive(full0 + 8 * stage);
-                    continue;
-                }
                 mbar_arrive_expect(full0 + 8 * stage, bytes);
                 bulk_load(b0 + stage * kBTile, src + (uint64_t)(kc_begin + i) * p.token_groups * (8 * kChunkK), bytes, full0 + 8 * stage);
             }
@@ -318,11 +310,9 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
                 tc_fence_after_sync();
                 // The address field counts 16-byte units, so stepping a descriptor is an add.
                 const uint64_t a_desc = a_desc0 + ((stage * kATile) >> 4), b_desc = b_desc0 + ((stage * kBTile) >> 4);
-                if (!(p.debug & 4)) {
 #pragma unroll
-                    for (uint32_t j = 0; j < kChunkK / 16; ++j)
-                        umma_f16(tmem, a_desc + ((j * 2 * kCoreBytes) >> 4), b_desc + ((j * 2 * kCoreBytes) >> 4), idesc, (i | j) != 0);
-                }
+                for (uint32_t j = 0; j < kChunkK / 16; ++j)
+                    umma_f16(tmem, a_desc + ((j * 2 * kCoreBytes) >> 4), b_desc + ((j * 2 * kCoreBytes) >> 4), idesc, (i | j) != 0);
                 umma_commit(empty0 + 8 * stage);
             }
             if (alive) umma_commit(accum);
@@ -436,11 +426,6 @@ cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, 
     p.token_groups = ((n_tokens + 15u) & ~15u) / 8;
     p.split = split;
     p.store = split > 1 ? BC_STORE_OVERWRITE : store;
-    static const int debug = [] {
-        const char* v = std::getenv("BOBCAT_UMMA_DEBUG");
-        return v ? std::atoi(v) : 0;
-    }();
-    p.debug = debug;
     dim3 grid((n_tokens + kMaxTokens - 1) / kMaxTokens, (w.n_rows + kRows - 1) / kRows, split);
     matmul_umma_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
     err = cudaGetLastError();

@@ -13,7 +13,9 @@
 // only after its input exists idles HBM for microseconds at every link. Here one thread per CTA
 // streams the CTA's share of the matrix into a shared-memory ring with bulk async copies, starting
 // before the kernel waits for its predecessor (programmatic dependent launch): the weights depend
-// on nothing, only the few kilobytes of activations do.
+// on nothing, only the few kilobytes of activations do. A CTA is 8 consumer warps and the
+// producer, with a 16-slot ring, small enough for two CTAs per SM: the next launch's CTAs move in
+// next to the running ones and fill their rings while those still compute.
 //
 // Layout ("tiles"): rows in tiles of 16, columns in chunks of 16 blocks. A chunk of a tile is
 // contiguous: for each pair of blocks 512 bytes ordered by lane - lane (g, t) = (lane / 4, lane % 4)
@@ -39,6 +41,7 @@ namespace {
 constexpr int kConsumers = 8;                    // consumer warps per CTA
 constexpr int kThreads = (kConsumers + 1) * 32;  // plus the producer warp
 constexpr int kDepth = 2;                        // ring slots per consumer warp
+constexpr uint32_t kCtasPerSm = 2;               // CTAs a launch may put on one SM (registers and the ring allow two)
 constexpr int kStages = kConsumers * kDepth;
 constexpr int kChunkBlocks = 16;                 // blocks of 32 weights per chunk of a tile
 constexpr int kBlockBytes = 288;                 // 16 rows x 18 bytes
@@ -167,7 +170,7 @@ __device__ __forceinline__ uint32_t group_size(uint32_t q_per_job) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(kThreads, 2) matvec_mma_kernel(Params p) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params p) {
     constexpr int S = segments_per_job<MODE>();
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;                                                   // kStages * kStageBytes
@@ -461,8 +464,7 @@ cudaError_t launch(cudaStream_t stream, Params& p) {
     size_t smem = (size_t)kStages * kStageBytes + (size_t)p.n_blocks * 128;
     cudaError_t e = ensure_dynamic_smem(kernel, smem);
     if (e != cudaSuccess) return e;
-    static const uint32_t per_sm = [] { const char* v = getenv("BOBCAT_MMA_CTAS_PER_SM"); return v ? (uint32_t)atoi(v) : 2u; }();
-    uint32_t cap = per_sm * (uint32_t)sm_count();
+    uint32_t cap = kCtasPerSm * (uint32_t)sm_count();
     uint32_t ctas = p.n_jobs < cap ? p.n_jobs : cap;
     void* args[] = {&p};
     return launch_kernel(kernel, dim3(ctas), dim3(kThreads), smem, stream, args);
