@@ -211,14 +211,18 @@ def run_ours(args) -> None:
     cuda = Cuda.open(local_rank, stream)
     n_ctx = PROMPT_TOKENS + DECODE_TOKENS
     seq = Lfm2Cuda(model, cuda, n_ctx, kv_half=True)
-    prompt = prompt_for(hp.n_vocab, 1 + rank)
-    pinned_prompt = torch.from_numpy(prompt.view(np.int32).copy()).pin_memory()  # the prompt's ids in pinned host memory
+    # Request replicas: timed step i of rank r serves request r + i * world, each with its own prompt.
+    from bobcat_b200 import replicas
+    mine = replicas.requests_of(rank, world, world * args.steps)
+    prompts = [torch.from_numpy(prompt_for(hp.n_vocab, replicas.prompt_seed(r)).view(np.int32).copy()).pin_memory() for r in mine]
+    prompt = prompts[0].numpy().view(np.uint32)
 
-    def request():
-        """One request through the public API with host buffers. Returns device and wall seconds."""
+    def request(i=0):
+        """One request through the public API with host buffers (pinned prompt ids in, token ids out).
+        Returns device and wall seconds."""
         seq.reset()
         t0 = time.perf_counter()
-        seq.prefill(pinned_prompt.numpy().view(np.uint32))
+        seq.prefill(prompts[i % len(prompts)].numpy().view(np.uint32))
         t1 = time.perf_counter()
         prefill_gpu = seq.last_gpu_seconds()
         tokens = seq.generate(DECODE_TOKENS)
@@ -241,7 +245,7 @@ def run_ours(args) -> None:
     sync_all()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    rows = [request() for _ in range(args.steps)]
+    rows = [request(i) for i in range(args.steps)]
     end.record()
     sync_all()
     clocks = sampler.stop() if rank == 0 else None
@@ -252,13 +256,10 @@ def run_ours(args) -> None:
     decode_gpu = float(np.mean([r[1] for r in rows]))
     prefill_wall = float(np.mean([r[2] for r in rows]))
     decode_wall = float(np.mean([r[3] for r in rows]))
-    stats = torch.tensor([decode_gpu, prefill_gpu, decode_wall, prefill_wall, total_ms / args.steps], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        launch_count = torch.tensor([launches], dtype=torch.int64, device="cuda")
-        dist.all_reduce(launch_count)
-        launches = int(launch_count.item())
-    decode_gpu, prefill_gpu, decode_wall, prefill_wall, ms_per_step = [float(v) for v in stats.tolist()]
+    # The slowest rank sets the job's time; launches add up.
+    decode_gpu, prefill_gpu, decode_wall, prefill_wall, ms_per_step = replicas.max_over_ranks(
+        [decode_gpu, prefill_gpu, decode_wall, prefill_wall, total_ms / args.steps], device="cuda")
+    launches = replicas.sum_over_ranks([launches], device="cuda")[0]
 
     if rank == 0:
         peak, tensor_peak, peak_kind = measured_peaks()
@@ -284,7 +285,7 @@ def run_ours(args) -> None:
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations, Q4_0 weights, f16 KV",
             "data": "synthetic",
             "config": {"workload": "%s Q4_0 (random init N(0,0.02), seed 0), batch 1 per GPU, %d-token uniform-random prompt then %d greedy tokens; "
-                                   "%d request replica(s), one per GPU" % (args.config, PROMPT_TOKENS, DECODE_TOKENS, world),
+                                   "%d request replica(s), one per GPU, %d requests with distinct prompts" % (args.config, PROMPT_TOKENS, DECODE_TOKENS, world, world * args.steps),
                        "l2": "every token streams %.2f GB of weights, far larger than the 126 MB L2" % (weight_bytes / 1e9),
                        "n_ctx": n_ctx, "kv_cache": "f16"},
             "decode": {"tok_s": decode_tok_s, "tpot_ms": 1e3 * decode_gpu / DECODE_TOKENS, "bytes_per_token": token_bytes,
