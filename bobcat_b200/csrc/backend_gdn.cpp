@@ -29,7 +29,7 @@ bc_status bc_op_gdn_conv(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* t
     BC_TRY(check_range(b, taps, taps_off, (size_t)conv_dim * kernel * 4, "gdn_conv"));
     BC_TRY(check_range(b, history, hist_off, (size_t)conv_dim * (kernel - 1) * 4, "gdn_conv"));
     BC_TRY(check_range(b, out, out_off, (size_t)n_tokens * conv_dim * 4, "gdn_conv"));
-    return b->run("gdn_conv", n_tokens, conv_dim, 0, 1, [&] {
+    return b->run("gdn_conv", n_tokens, conv_dim, 0, k::gdn_conv_launches(n_tokens), [&] {
         return k::gdn_conv(b->stream, at<const float>(x, x_off), at<const float>(taps, taps_off), at<float>(history, hist_off), at<float>(out, out_off),
                            conv_dim, kernel, n_tokens);
     });

@@ -144,6 +144,7 @@ cudaError_t argmax(cudaStream_t stream, const float* x, uint32_t n, uint32_t* ou
 // DeltaNet causal convolution with SiLU over [n_tokens][conv_dim]; history [conv_dim][kernel - 1].
 cudaError_t gdn_conv(cudaStream_t stream, const float* x, const float* taps, float* history, float* out, uint32_t conv_dim,
                      uint32_t kernel, uint32_t n_tokens);
+int gdn_conv_launches(uint32_t n_tokens);
 // In place: beta = sigmoid(beta); alpha = exp(a * softplus(alpha + dt_bias)).
 cudaError_t gdn_gates(cudaStream_t stream, float* beta, float* alpha, const float* a, const float* dt_bias, uint32_t n_v_heads,
                       uint32_t n_tokens);

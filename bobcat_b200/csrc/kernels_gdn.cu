@@ -12,11 +12,55 @@ namespace k {
 
 namespace {
 
-// One thread per channel, serial over tokens. x and out are [n_tokens][conv_dim]; taps are
-// [conv_dim][K], oldest first; history is [conv_dim][K - 1] raw inputs, oldest first. The sum starts
-// from the newest tap's term and adds the history terms oldest first (qwen35.rs:449-461). K <= 8.
-__global__ void gdn_conv_kernel(const float* __restrict__ x, const float* __restrict__ taps, float* __restrict__ history,
-                                float* __restrict__ out, uint32_t conv_dim, uint32_t kernel, uint32_t n_tokens) {
+constexpr uint32_t kConvSerialTokens = 4;  // up to this many tokens one launch walks them serially
+
+// One thread per (token, channel). x and out are [n_tokens][conv_dim]; taps are [conv_dim][K],
+// oldest first; history is [conv_dim][K - 1] raw inputs, oldest first. The sum starts from the
+// newest tap's term and adds the earlier inputs oldest first (qwen35.rs:449-461), from the batch or,
+// for its first tokens, from the history, so any split into batches gives the same bits. K <= 8.
+// The history is only read here; gdn_conv_history_kernel rewrites it afterwards.
+__global__ void __launch_bounds__(256) gdn_conv_kernel(const float* __restrict__ x, const float* __restrict__ taps,
+                                                       const float* __restrict__ history, float* __restrict__ out, uint32_t conv_dim,
+                                                       uint32_t kernel, uint32_t n_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= conv_dim) return;
+    const uint32_t H = kernel - 1;
+    float tap[8];
+    for (uint32_t i = 0; i < kernel; ++i) tap[i] = taps[(uint64_t)c * kernel + i];
+    for (uint32_t t = blockIdx.y; t < n_tokens; t += gridDim.y) {
+        float sum = tap[H] * x[(uint64_t)t * conv_dim + c];
+        for (uint32_t i = 0; i < H; ++i) {
+            int64_t src = (int64_t)t - (int64_t)H + i;  // tap i meets the input of token t - H + i
+            float past = src >= 0 ? x[(uint64_t)src * conv_dim + c] : history[(uint64_t)c * H + (uint32_t)(src + (int64_t)H)];
+            sum += tap[i] * past;
+        }
+        out[(uint64_t)t * conv_dim + c] = sum / (1.f + expf(-sum));
+    }
+}
+
+// The history after the batch: slot i holds the input of token n_tokens - H + i, or an older slot
+// when the batch is shorter than the history. One thread per channel.
+__global__ void gdn_conv_history_kernel(const float* __restrict__ x, float* __restrict__ history, uint32_t conv_dim, uint32_t kernel,
+                                        uint32_t n_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= conv_dim) return;
+    const uint32_t H = kernel - 1;
+    float next[7];
+    for (uint32_t i = 0; i < H; ++i) {
+        int64_t src = (int64_t)n_tokens - (int64_t)H + i;
+        next[i] = src >= 0 ? x[(uint64_t)src * conv_dim + c] : history[(uint64_t)c * H + (uint32_t)(src + (int64_t)H)];
+    }
+    for (uint32_t i = 0; i < H; ++i) history[(uint64_t)c * H + i] = next[i];
+}
+
+// The same for a few tokens (a decode step): one thread per channel walks the tokens and
+// updates the history itself, so one launch does it all. Same order of additions, same bits.
+__global__ void gdn_conv_serial_kernel(const float* __restrict__ x, const float* __restrict__ taps, float* __restrict__ history,
+                                       float* __restrict__ out, uint32_t conv_dim, uint32_t kernel, uint32_t n_tokens) {
     pdl_launch_dependents();
     pdl_wait();
     uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -67,11 +111,14 @@ struct RecurrenceParams {
 // row order. Value head h reads key head h % n_k_heads.
 template <int KDIM>
 __global__ void __launch_bounds__(256) gdn_recurrence_kernel(RecurrenceParams p) {
-    __shared__ float qs[KDIM], ks[KDIM];
-    __shared__ float scratch[32];
+    // Two copies of the staged q, k and of the reduction scratch, used on alternate tokens, so a
+    // token needs two block barriers and the next token's inputs load while this one computes.
+    __shared__ float qs[2][KDIM], ks[2][KDIM];
+    __shared__ float scratch[2][16];
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t head = blockIdx.x, j = threadIdx.x, vd = p.v_dim;
+    const uint32_t lane = j & 31, warp = j >> 5, n_warps = (blockDim.x + 31) >> 5;
     const uint32_t key_head = head % p.n_k_heads;
     const uint32_t key_dim = p.n_k_heads * KDIM, conv_dim = 2 * key_dim + p.n_v_heads * vd;
     float* state = p.state + (uint64_t)head * KDIM * vd;
@@ -80,42 +127,69 @@ __global__ void __launch_bounds__(256) gdn_recurrence_kernel(RecurrenceParams p)
 #pragma unroll
         for (int i = 0; i < KDIM; ++i) S[i] = state[(uint64_t)i * vd + j];
     }
+    // This thread's inputs of a token: its element of q and of k, its element of v, the head's gates.
+    struct Inputs {
+        float q, k, v, beta, decay;
+    };
+    auto load = [&](uint32_t t) {
+        Inputs in{0.f, 0.f, 0.f, 0.f, 0.f};
+        if (t < p.n_tokens) {
+            const float* row = p.qkv + (uint64_t)t * conv_dim;
+            if (j < KDIM) {
+                in.q = row[key_head * KDIM + j];
+                in.k = row[key_dim + key_head * KDIM + j];
+            }
+            if (j < vd) {
+                in.v = row[2 * key_dim + head * vd + j];
+                in.beta = p.beta[(uint64_t)t * p.n_v_heads + head];
+                in.decay = p.decay[(uint64_t)t * p.n_v_heads + head];
+            }
+        }
+        return in;
+    };
+    Inputs cur = load(0);
     for (uint32_t t = 0; t < p.n_tokens; ++t) {
-        const float* row = p.qkv + (uint64_t)t * conv_dim;
-        __syncthreads();  // the previous token's readers are done with qs and ks
+        const Inputs next = load(t + 1);
+        const uint32_t buf = t & 1;
         if (p.normalize) {
             // l2_normalize (qwen35.rs:762-768): f32 sum of squares, x *= scale / sqrt(sum + 1e-6).
-            float qv = j < KDIM ? row[key_head * KDIM + j] : 0.f;
-            float kv = j < KDIM ? row[key_dim + key_head * KDIM + j] : 0.f;
-            float qsum = block_sum(qv * qv, scratch);
-            float ksum = block_sum(kv * kv, scratch);
+            float q2 = warp_sum(cur.q * cur.q), k2 = warp_sum(cur.k * cur.k);
+            if (lane == 0) {
+                scratch[buf][warp] = q2;
+                scratch[buf][8 + warp] = k2;
+            }
+            __syncthreads();
+            float qsum = 0.f, ksum = 0.f;
+            for (uint32_t w = 0; w < n_warps; ++w) {
+                qsum += scratch[buf][w];
+                ksum += scratch[buf][8 + w];
+            }
             if (j < KDIM) {
-                qs[j] = qv * ((1.0f / sqrtf((float)KDIM)) / sqrtf(qsum + 1e-6f));
-                ks[j] = kv * (1.0f / sqrtf(ksum + 1e-6f));
+                qs[buf][j] = cur.q * ((1.0f / sqrtf((float)KDIM)) / sqrtf(qsum + 1e-6f));
+                ks[buf][j] = cur.k * (1.0f / sqrtf(ksum + 1e-6f));
             }
         } else if (j < KDIM) {
-            qs[j] = row[key_head * KDIM + j];
-            ks[j] = row[key_dim + key_head * KDIM + j];
+            qs[buf][j] = cur.q;
+            ks[buf][j] = cur.k;
         }
         __syncthreads();
         if (j < vd) {
-            const float beta = p.beta[(uint64_t)t * p.n_v_heads + head], decay = p.decay[(uint64_t)t * p.n_v_heads + head];
-            const float v = row[2 * key_dim + head * vd + j];
             float r = 0.f;
 #pragma unroll
             for (int i = 0; i < KDIM; ++i) {
-                S[i] *= decay;
-                r += S[i] * ks[i];
+                S[i] *= cur.decay;
+                r += S[i] * ks[buf][i];
             }
-            const float delta = (v - r) * beta;
+            const float delta = (cur.v - r) * cur.beta;
             float o = 0.f;
 #pragma unroll
             for (int i = 0; i < KDIM; ++i) {
-                S[i] += ks[i] * delta;
-                o += S[i] * qs[i];
+                S[i] += ks[buf][i] * delta;
+                o += S[i] * qs[buf][i];
             }
             p.out[(uint64_t)t * p.n_v_heads * vd + head * vd + j] = o;
         }
+        cur = next;
     }
     if (j < vd) {
 #pragma unroll
@@ -157,11 +231,22 @@ __global__ void attention_gate_kernel(float* __restrict__ out, const float* __re
 
 }  // namespace
 
+int gdn_conv_launches(uint32_t n_tokens) { return n_tokens <= kConvSerialTokens ? 1 : 2; }
+
 cudaError_t gdn_conv(cudaStream_t stream, const float* x, const float* taps, float* history, float* out, uint32_t conv_dim,
                      uint32_t kernel, uint32_t n_tokens) {
     if (n_tokens == 0) return cudaSuccess;
-    void* args[] = {&x, &taps, &history, &out, &conv_dim, &kernel, &n_tokens};
-    return launch_kernel((const void*)gdn_conv_kernel, dim3((conv_dim + 127) / 128), dim3(128), 0, stream, args);
+    if (n_tokens <= kConvSerialTokens) {
+        void* args[] = {&x, &taps, &history, &out, &conv_dim, &kernel, &n_tokens};
+        return launch_kernel((const void*)gdn_conv_serial_kernel, dim3((conv_dim + 127) / 128), dim3(128), 0, stream, args);
+    }
+    const float* read_history = history;
+    void* args[] = {&x, &taps, &read_history, &out, &conv_dim, &kernel, &n_tokens};
+    cudaError_t e = launch_kernel((const void*)gdn_conv_kernel, dim3((conv_dim + 255) / 256, n_tokens < 65535u ? n_tokens : 65535u), dim3(256), 0,
+                                  stream, args);
+    if (e != cudaSuccess) return e;
+    void* history_args[] = {&x, &history, &conv_dim, &kernel, &n_tokens};
+    return launch_kernel((const void*)gdn_conv_history_kernel, dim3((conv_dim + 127) / 128), dim3(128), 0, stream, history_args);
 }
 
 cudaError_t gdn_gates(cudaStream_t stream, float* beta, float* alpha, const float* a, const float* dt_bias, uint32_t n_v_heads,

@@ -36,12 +36,16 @@ struct RouteParams {
     uint32_t n_cols, n_experts, n_used;
 };
 
-// One CTA per token. The token's norm and the router's dot products accumulate in f64, as the
-// scalar reference does (scalar.rs:240-249, :292-304), so the scores - and with them the picked
-// expert ids - do not depend on the order a parallel sum happens to take.
-__global__ void __launch_bounds__(kThreads) moe_route_kernel(RouteParams p) {
+constexpr int kRouteThreads = 1024;
+constexpr int kRouteWarps = kRouteThreads / 32;
+
+// One CTA per token, a warp per expert. The token's norm and the router's dot products accumulate
+// in f64, as the scalar reference does (scalar.rs:240-249, :292-304), so the scores - and with them
+// the picked expert ids - do not depend on the order a parallel sum happens to take. Each lane
+// keeps four independent sums so the f64 adds do not wait on one another.
+__global__ void __launch_bounds__(kRouteThreads) moe_route_kernel(RouteParams p) {
     extern __shared__ float xs[];  // the normalised token
-    __shared__ double reduce[kWarps];
+    __shared__ double reduce[kRouteWarps];
     __shared__ float scores[kMaxExperts];
     pdl_launch_dependents();
     pdl_wait();
@@ -50,28 +54,35 @@ __global__ void __launch_bounds__(kThreads) moe_route_kernel(RouteParams p) {
     const float* x = p.x + (uint64_t)token * n_cols;
     if (p.norm_weight) {
         double sumsq = 0.0;
-        for (uint32_t c = tid; c < n_cols; c += kThreads) sumsq += (double)x[c] * (double)x[c];
+        for (uint32_t c = tid; c < n_cols; c += kRouteThreads) sumsq += (double)x[c] * (double)x[c];
         sumsq = warp_sum_f64(sumsq);
         if (lane == 0) reduce[warp] = sumsq;
         __syncthreads();
         double total = 0.0;
-        for (int w = 0; w < kWarps; ++w) total += reduce[w];
+        for (int w = 0; w < kRouteWarps; ++w) total += reduce[w];
         float scale = (float)(1.0 / sqrt(total / (double)n_cols + (double)p.eps));
         float* normed = p.normed + (uint64_t)token * n_cols;
-        for (uint32_t c = tid; c < n_cols; c += kThreads) {
+        for (uint32_t c = tid; c < n_cols; c += kRouteThreads) {
             float v = p.norm_weight[c] * (x[c] * scale);
             xs[c] = v;
             normed[c] = v;
         }
     } else {
-        for (uint32_t c = tid; c < n_cols; c += kThreads) xs[c] = x[c];
+        for (uint32_t c = tid; c < n_cols; c += kRouteThreads) xs[c] = x[c];
     }
     __syncthreads();
-    for (uint32_t e = warp; e < p.n_experts; e += kWarps) {
+    for (uint32_t e = warp; e < p.n_experts; e += kRouteWarps) {
         const float* row = p.router + (uint64_t)e * n_cols;
-        double sum = 0.0;
-        for (uint32_t c = lane; c < n_cols; c += 32) sum += (double)row[c] * (double)xs[c];
-        sum = warp_sum_f64(sum);
+        double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+        uint32_t c = lane;
+        for (; c + 96 < n_cols; c += 128) {
+            s0 += (double)row[c] * (double)xs[c];
+            s1 += (double)row[c + 32] * (double)xs[c + 32];
+            s2 += (double)row[c + 64] * (double)xs[c + 64];
+            s3 += (double)row[c + 96] * (double)xs[c + 96];
+        }
+        for (; c < n_cols; c += 32) s0 += (double)row[c] * (double)xs[c];
+        double sum = warp_sum_f64((s0 + s1) + (s2 + s3));
         if (lane == 0) scores[e] = 1.0f / (1.0f + expf(-(float)sum));
     }
     __syncthreads();
@@ -331,7 +342,7 @@ cudaError_t moe_route(cudaStream_t stream, const float* x, Norm norm, float* nor
     cudaError_t e = ensure_dynamic_smem((const void*)moe_route_kernel, smem);
     if (e != cudaSuccess) return e;
     void* args[] = {&p};
-    return launch_kernel((const void*)moe_route_kernel, dim3(n_tokens), dim3(kThreads), smem, stream, args);
+    return launch_kernel((const void*)moe_route_kernel, dim3(n_tokens), dim3(kRouteThreads), smem, stream, args);
 }
 
 cudaError_t moe_group(cudaStream_t stream, const uint32_t* route, uint32_t* offsets, uint32_t* entries, uint32_t n_experts,
