@@ -193,6 +193,9 @@ uint64_t matmul_pack_bytes(uint32_t n_tokens, uint32_t n_cols);
 uint64_t matmul_scratch_bytes(const Mat& w, uint32_t n_tokens);
 int matmul_umma_launches(const Mat& w, uint32_t n_tokens);
 cudaError_t matmul_pack(cudaStream_t stream, const float* x, uint32_t n_tokens, uint32_t n_cols, void* packed);
+// RMSNorm fused into the packing: packed = fp16(weight * (x * scale)), so a normalised batch that only feeds
+// tensor-core products never exists in f32.
+cudaError_t matmul_pack_norm(cudaStream_t stream, const float* x, Norm norm, uint32_t n_tokens, uint32_t n_cols, void* packed);
 cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* packed, float* y, uint32_t n_tokens, uint32_t y_stride,
                         int32_t store);
 // Nonzero once a bounded wait inside the tensor-core prefill kernel gave up (1: producers on a free

@@ -103,6 +103,51 @@ __global__ void __launch_bounds__(256) pack_kernel(const float* __restrict__ x, 
     reinterpret_cast<uint4*>(packed)[o] = out;
 }
 
+// RMSNorm and packing in one pass: packed = fp16(weight * (x * scale)), scale = 1 / sqrt(mean x^2 + eps)
+// per token, the arithmetic of rms_norm_kernel followed by pack_kernel. One CTA per group of 8
+// tokens: a warp per token sums its squares, then the CTA writes the group's kilobyte of every
+// chunk. Rows past the batch are zero.
+__global__ void __launch_bounds__(256) pack_norm_kernel(const float* __restrict__ x, const float* __restrict__ weight, float eps,
+                                                        __half* __restrict__ packed, uint32_t n_tokens, uint32_t n_cols, uint32_t token_groups) {
+    __shared__ float scales[8];
+    const uint32_t tg = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    {
+        const uint32_t token = tg * 8 + warp;
+        float sumsq = 0.f;
+        if (token < n_tokens) {
+            const float4* row = reinterpret_cast<const float4*>(x + (uint64_t)token * n_cols);
+            for (uint32_t i = lane; i < n_cols / 4; i += 32) {
+                float4 v = row[i];
+                sumsq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+        }
+        sumsq = warp_sum(sumsq);
+        if (lane == 0) scales[warp] = rsqrtf(sumsq / (float)n_cols + eps);
+    }
+    __syncthreads();
+    const uint32_t tr = tid & 7, j = (tid >> 3) & (kCores - 1), sub = tid / (8 * kCores);  // 256 / 64 = 4 chunks per pass
+    const uint32_t token = tg * 8 + tr, n_chunks = n_cols / kChunkK;
+    const float scale = scales[tr];
+    for (uint32_t chunk = sub; chunk < n_chunks; chunk += 256 / (8 * kCores)) {
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (token < n_tokens) {
+            const uint32_t col = chunk * kChunkK + (j >> 2) * 32 + 4 * (j & 3);
+            const float* src = x + (uint64_t)token * n_cols + col;
+            float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 16);
+            const float4 wl = __ldg(reinterpret_cast<const float4*>(weight + col)), wh = __ldg(reinterpret_cast<const float4*>(weight + col + 16));
+            lo.x = wl.x * (lo.x * scale); lo.y = wl.y * (lo.y * scale); lo.z = wl.z * (lo.z * scale); lo.w = wl.w * (lo.w * scale);
+            hi.x = wh.x * (hi.x * scale); hi.y = wh.y * (hi.y * scale); hi.z = wh.z * (hi.z * scale); hi.w = wh.w * (hi.w * scale);
+            __half2 a = __floats2half2_rn(lo.x, lo.z), b = __floats2half2_rn(lo.y, lo.w);
+            __half2 c = __floats2half2_rn(hi.x, hi.z), d = __floats2half2_rn(hi.y, hi.w);
+            out.x = *reinterpret_cast<uint32_t*>(&a);
+            out.y = *reinterpret_cast<uint32_t*>(&b);
+            out.z = *reinterpret_cast<uint32_t*>(&c);
+            out.w = *reinterpret_cast<uint32_t*>(&d);
+        }
+        reinterpret_cast<uint4*>(packed)[(((uint64_t)chunk * token_groups + tg) * kCores + j) * 8 + tr] = out;
+    }
+}
+
 // The eight weights of quant word `w` times the block scale, as fp16 in the permuted order.
 __device__ __forceinline__ uint4 dequant_word(uint32_t w, __half2 scale) {
     const uint32_t magic = 0x64006400u;  // half2(1024, 1024)
@@ -401,6 +446,13 @@ cudaError_t matmul_pack(cudaStream_t stream, const float* x, uint32_t n_tokens, 
     uint64_t total = (uint64_t)(n_cols / kChunkK) * token_groups * (8 * kCores);
     if (total == 0) return cudaSuccess;
     pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, static_cast<__half*>(packed), n_tokens, n_cols, token_groups, total);
+    return cudaGetLastError();
+}
+
+cudaError_t matmul_pack_norm(cudaStream_t stream, const float* x, Norm norm, uint32_t n_tokens, uint32_t n_cols, void* packed) {
+    uint32_t token_groups = ((n_tokens + 15u) & ~15u) / 8;
+    if (token_groups == 0 || n_cols == 0) return cudaSuccess;
+    pack_norm_kernel<<<token_groups, 256, 0, stream>>>(x, norm.weight, norm.eps, static_cast<__half*>(packed), n_tokens, n_cols, token_groups);
     return cudaGetLastError();
 }
 

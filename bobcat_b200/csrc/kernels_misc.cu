@@ -249,13 +249,35 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     pdl_wait();
     float value = -INFINITY;
     uint32_t index = 0xffffffffu;
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        float v = x[i];
+    auto consider = [&](float v, uint32_t i) {
         if (v > value || index == 0xffffffffu) {
             value = v;
             index = i;
         }
+    };
+    // Eight 16-byte loads in flight per thread, visited in increasing index order so the first
+    // maximum wins; whatever does not fill a float4 goes one by one.
+    const uint32_t n4 = (reinterpret_cast<uintptr_t>(x) & 15) == 0 ? n / 4 : 0;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    for (uint32_t base = threadIdx.x; base < n4; base += blockDim.x * 8) {
+        float4 v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            uint32_t i = base + k * blockDim.x;
+            v[k] = i < n4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            uint32_t i = base + k * blockDim.x;
+            if (i < n4) {
+                consider(v[k].x, 4 * i);
+                consider(v[k].y, 4 * i + 1);
+                consider(v[k].z, 4 * i + 2);
+                consider(v[k].w, 4 * i + 3);
+            }
+        }
     }
+    for (uint32_t i = 4 * n4 + threadIdx.x; i < n; i += blockDim.x) consider(x[i], i);
     auto better = [](float v, uint32_t i, float bv, uint32_t bi) { return i != 0xffffffffu && (bi == 0xffffffffu || v > bv || (v == bv && i < bi)); };
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

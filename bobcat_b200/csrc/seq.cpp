@@ -1,6 +1,7 @@
 #include "seq.h"
 
 #include <algorithm>
+#include <initializer_list>
 #include <cstring>
 
 using namespace bc;
@@ -47,6 +48,37 @@ struct Recorder {
         void* pack = nullptr;
         if (status == BC_OK && k::matmul_umma_supported(w, n)) status = s.backend->pack_scratch(k::matmul_scratch_bytes(w, n), &pack);
         run("matmul", w.n_rows, w.n_cols, w.bytes(), pack ? k::matmul_umma_launches(w, n) : 1, [&] { return k::matmul(stream, w, x, y, n, w.n_rows, store, pack); });
+    }
+
+    // RMSNorm of the batch, then products that all read the normalised rows. When every product
+    // runs on the tensor-core kernel the normalised rows are packed to fp16 once, straight from the
+    // residual stream, and the f32 copy is never written; otherwise s.normed takes them first.
+    struct Product {
+        const k::Mat* w;
+        float* y;
+        int store;
+    };
+    void normed_matmuls(const float* x, const float* norm_weight, uint32_t n, std::initializer_list<Product> products) {
+        const uint32_t cols = hp.n_embd;
+        bool fused = true;
+        size_t bytes = 0;
+        for (const Product& q : products) {
+            fused = fused && k::matmul_umma_supported(*q.w, n);
+            bytes = std::max(bytes, (size_t)k::matmul_scratch_bytes(*q.w, n));
+        }
+        if (!fused) {
+            run("rms_norm", n, cols, 0, 1, [&] { return k::rms_norm(stream, x, norm_weight, s.normed, cols, n, hp.norm_eps); });
+            for (const Product& q : products) matmul(*q.w, s.normed, q.y, n, q.store);
+            return;
+        }
+        void* scratch = nullptr;
+        if (status == BC_OK) status = s.backend->pack_scratch(bytes, &scratch);
+        run("pack_norm", n, cols, 0, 1, [&] { return k::matmul_pack_norm(stream, x, norm(norm_weight), n, cols, scratch); });
+        for (const Product& q : products) {
+            const k::Mat& w = *q.w;
+            run("matmul", w.n_rows, w.n_cols, w.bytes(), k::matmul_umma_launches(w, n) - 1,
+                [&] { return k::matmul_umma(stream, w, scratch, q.y, n, w.n_rows, q.store); });
+        }
     }
 
     size_t kv_element_bytes() const { return s.kv_half ? 2 : 4; }
@@ -192,29 +224,26 @@ struct Recorder {
         for (size_t il = 0; il < W.layers.size(); ++il) {
             const LayerSpec& S = s.model->layers[il];
             const DeviceLayer& D = W.layers[il];
-            run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.attn_norm, s.normed, n_embd, n, hp.norm_eps); });
             if (S.mixer == Mixer::Attention) {
-                matmul(D.q, s.normed, s.q, n, BC_STORE_OVERWRITE);
-                matmul(D.k, s.normed, s.k, n, BC_STORE_OVERWRITE);
-                matmul(D.v, s.normed, value_target(S.cache_index, pos), n, BC_STORE_OVERWRITE);
+                normed_matmuls(s.hidden, D.attn_norm, n,
+                               {{&D.q, s.q, BC_STORE_OVERWRITE}, {&D.k, s.k, BC_STORE_OVERWRITE}, {&D.v, value_target(S.cache_index, pos), BC_STORE_OVERWRITE}});
                 uint32_t q_dim = hp.n_heads * hp.head_dim;
                 rotate_and_attend(D, S.cache_index, pos, n, q_dim, hp.head_dim);
                 matmul(D.output, s.attn, s.hidden, n, BC_STORE_ACCUMULATE);
             } else {
                 float* history = s.conv_state + (size_t)S.cache_index * (hp.conv_kernel - 1) * n_embd;
-                matmul(D.in_proj, s.normed, s.bcx, n, BC_STORE_OVERWRITE);
+                normed_matmuls(s.hidden, D.attn_norm, n, {{&D.in_proj, s.bcx, BC_STORE_OVERWRITE}});
                 run("short_conv", n, n_embd, 0, 2,
                     [&] { return k::short_conv(stream, s.bcx, D.taps, history, s.conv_out, n_embd, hp.conv_kernel, n); });
                 matmul(D.out_proj, s.conv_out, s.hidden, n, BC_STORE_ACCUMULATE);
             }
-            run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.ffn_norm, s.normed, n_embd, n, hp.norm_eps); });
             if (S.moe) {
+                run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.ffn_norm, s.normed, n_embd, n, hp.norm_eps); });
                 lfm2_moe(D, n, false);
             } else {
                 // The up projection's store combines with the gate projection already in the
                 // buffer, which applies the SwiGLU.
-                matmul(D.gate, s.normed, s.ffn, n, BC_STORE_OVERWRITE);
-                matmul(D.up, s.normed, s.ffn, n, BC_STORE_SWIGLU);
+                normed_matmuls(s.hidden, D.ffn_norm, n, {{&D.gate, s.ffn, BC_STORE_OVERWRITE}, {&D.up, s.ffn, BC_STORE_SWIGLU}});
                 matmul(D.down, s.ffn, s.hidden, n, BC_STORE_ACCUMULATE);
             }
             if (traced) copy(s.hidden, s.trace_layers + il * trace_stride, (uint64_t)n * n_embd);
@@ -288,11 +317,9 @@ struct Recorder {
         for (size_t il = 0; il < W.layers.size(); ++il) {
             const LayerSpec& S = s.model->layers[il];
             const DeviceLayer& D = W.layers[il];
-            run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.attn_norm, s.normed, n_embd, n, hp.norm_eps); });
             if (S.mixer == Mixer::Attention) {
-                matmul(D.q, s.normed, s.q, n, BC_STORE_OVERWRITE);
-                matmul(D.k, s.normed, s.k, n, BC_STORE_OVERWRITE);
-                matmul(D.v, s.normed, value_target(S.cache_index, pos), n, BC_STORE_OVERWRITE);
+                normed_matmuls(s.hidden, D.attn_norm, n,
+                               {{&D.q, s.q, BC_STORE_OVERWRITE}, {&D.k, s.k, BC_STORE_OVERWRITE}, {&D.v, value_target(S.cache_index, pos), BC_STORE_OVERWRITE}});
                 size_t slot = layer_base(S.cache_index) + (size_t)pos * kv_dim();
                 // The rotated queries go to their own compact rows; the gates stay in the projection.
                 run("norm_rope", hp.n_heads * n, hp.head_dim, 0, 1, [&] {
@@ -314,16 +341,13 @@ struct Recorder {
                 run("attention_gate", n, q_dim, 0, 1, [&] { return k::attention_gate(stream, s.attn, s.q, hp.n_heads, hp.head_dim, n); });
                 matmul(D.output, s.attn, s.hidden, n, BC_STORE_ACCUMULATE);
             } else {
-                matmul(D.qkv, s.normed, s.gdn_qkv, n, BC_STORE_OVERWRITE);
-                matmul(D.z, s.normed, s.gdn_z, n, BC_STORE_OVERWRITE);
-                matmul(D.beta, s.normed, s.gdn_beta, n, BC_STORE_OVERWRITE);
-                matmul(D.alpha, s.normed, s.gdn_alpha, n, BC_STORE_OVERWRITE);
+                normed_matmuls(s.hidden, D.attn_norm, n,
+                               {{&D.qkv, s.gdn_qkv, BC_STORE_OVERWRITE}, {&D.z, s.gdn_z, BC_STORE_OVERWRITE}, {&D.beta, s.gdn_beta, BC_STORE_OVERWRITE},
+                                {&D.alpha, s.gdn_alpha, BC_STORE_OVERWRITE}});
                 qwen_delta_tail(D, S.cache_index, n);
                 matmul(D.ssm_out, s.gdn_out, s.hidden, n, BC_STORE_ACCUMULATE);
             }
-            run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.ffn_norm, s.normed, n_embd, n, hp.norm_eps); });
-            matmul(D.gate, s.normed, s.ffn, n, BC_STORE_OVERWRITE);
-            matmul(D.up, s.normed, s.ffn, n, BC_STORE_SWIGLU);
+            normed_matmuls(s.hidden, D.ffn_norm, n, {{&D.gate, s.ffn, BC_STORE_OVERWRITE}, {&D.up, s.ffn, BC_STORE_SWIGLU}});
             matmul(D.down, s.ffn, s.hidden, n, BC_STORE_ACCUMULATE);
             if (traced) copy(s.hidden, s.trace_layers + il * trace_stride, (uint64_t)n * n_embd);
         }
