@@ -198,6 +198,11 @@ cudaError_t matmul_pack(cudaStream_t stream, const float* x, uint32_t n_tokens, 
 cudaError_t matmul_pack_norm(cudaStream_t stream, const float* x, Norm norm, uint32_t n_tokens, uint32_t n_cols, void* packed);
 cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* packed, float* y, uint32_t n_tokens, uint32_t y_stride,
                         int32_t store);
+// Gate and up of a SwiGLU in one launch: both weight tiles meet the same token tile, two
+// accumulators in tensor memory, y = silu(gate x) * (up x).
+bool matmul_umma_swiglu_supported(const Mat& gate, const Mat& up, uint32_t n_tokens);
+cudaError_t matmul_umma_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, const void* packed, float* y, uint32_t n_tokens,
+                               uint32_t y_stride);
 // Nonzero once a bounded wait inside the tensor-core prefill kernel gave up (1: producers on a free
 // stage, 2: epilogue on the accumulator, 3: token copy on a free stage, 4: MMA thread on a full stage).
 int matmul_error_flag();

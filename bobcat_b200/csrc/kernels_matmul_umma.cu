@@ -9,11 +9,13 @@
 // Shape of the kernel. One CTA owns 128 weight rows (the MMA's M) and up to 256 tokens (its N);
 // the accumulator is 128 lanes x N columns of tensor memory. K advances 64 columns (two Q4_0
 // blocks per row) per pipeline stage, four stages:
-//   * 16 producer warps in four groups. Group g takes every fourth chunk: a thread loads its
-//     row's two blocks (32 bytes of quants, two scales) two turns ahead into registers, turns
-//     nibbles into fp16 with logic ops on packed halves before it waits for the stage, and then
-//     only stores them in the operand layout. The groups' turns overlap, which hides the latency
-//     of a turn (the wait for the stage, the proxy fence, the arrival), not only that of the loads;
+//   * producer warps in groups of four, one group per stage (four stages; three when two weight
+//     matrices share the token tile). Group g takes every chunk that lands in stage g: a thread
+//     loads its row's two blocks (32 bytes of quants, two scales) two turns ahead into registers,
+//     turns nibbles into fp16 with logic ops on packed halves before it waits for the stage, and
+//     then only stores them in the operand layout. The groups' turns overlap, which hides the
+//     latency of a turn (the wait for the stage, the proxy fence, the arrival), not only that of
+//     the loads;
 //   * one thread brings the stage's token tile, already fp16 and already in operand layout (see
 //     pack_kernel), with a single bulk copy;
 //   * one thread issues four tcgen05.mma (K = 16 each) per stage and commits the stage's release;
@@ -52,26 +54,36 @@ constexpr uint32_t kMaxTokens = 256;  // tokens per CTA: the MMA's N, a multiple
 constexpr uint32_t kChunkK = 64;      // columns per stage
 constexpr uint32_t kChunkBlocks = kChunkK / 32;  // Q4_0 blocks per row per stage
 constexpr uint32_t kCores = kChunkK / 8;         // core matrices along K per stage
-constexpr uint32_t kStages = 4;
-constexpr uint32_t kGroups = 4;            // producer groups; group g takes every kGroups-th chunk
 constexpr uint32_t kGroupThreads = kRows;  // a producer thread per row of the tile
-constexpr uint32_t kProducers = kGroups * kGroupThreads;
-constexpr uint32_t kTmaWarp = kProducers / 32, kMmaWarp = kTmaWarp + 1;
-constexpr uint32_t kThreads = kProducers + 64;
 constexpr uint32_t kATile = kRows * kChunkK * 2;       // 16 KB
 constexpr uint32_t kBTile = kMaxTokens * kChunkK * 2;  // 32 KB
 constexpr uint32_t kGroupBytes = 8 * kChunkK * 2;      // an 8-row group of a stage: 1 KB
 constexpr uint32_t kCoreBytes = 128;
-constexpr uint32_t kTmemColumns = 256;
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr uint32_t kMaxSplit = 8;
-constexpr size_t kSmemBytes = kStages * (kATile + kBTile) + (2 * kStages + 1) * 8 + 16;
+// The kernel multiplies one weight matrix, or two that share the token tile (gate and up of a
+// SwiGLU, two accumulators): DUAL is that count. Two weight tiles per stage leave room for three
+// stages instead of four. There is one producer group per stage: group g fills stage g on every
+// turn, so a group is never more than one phase ahead of its stage's barrier and a parity is
+// enough to tell the phases apart. (Were a stage shared by several groups, a group two uses ahead
+// would see the parity of an older phase and overwrite a tile still in use.)
+template <int DUAL>
+struct Shape {
+    static constexpr uint32_t kStages = DUAL == 2 ? 3 : 4;
+    static constexpr uint32_t kGroups = kStages;
+    static constexpr uint32_t kProducers = kGroups * kGroupThreads;
+    static constexpr uint32_t kTmaWarp = kProducers / 32, kMmaWarp = kTmaWarp + 1;
+    static constexpr uint32_t kThreads = kProducers + 64;
+    static constexpr uint32_t kStageA = DUAL * kATile;
+    static constexpr uint32_t kTmemColumns = DUAL * kMaxTokens;
+    static constexpr size_t kSmemBytes = kStages * (kStageA + kBTile) + (2 * kStages + 1) * 8 + 16;
+};
 
 __device__ int g_matmul_error;
 
 struct UmmaParams {
-    const uint4* quants;   // split layout: [n_rows][n_blocks] 16-byte groups
-    const __half* scales;  // [n_rows][n_blocks]
+    const uint4* quants[2];   // split layout: [n_rows][n_blocks] 16-byte groups (the second matrix only when DUAL == 2)
+    const __half* scales[2];  // [n_rows][n_blocks]
     const __half* packed;  // inputs in operand layout: [n_chunks][token_groups][8 cores][8 tokens][8 halves]
     float* y;              // the output, or with split > 1 the partial products [split][n_tokens][n_rows]
     uint32_t n_rows, n_blocks, n_chunks, n_tokens, y_stride, token_groups;
@@ -172,10 +184,13 @@ __device__ __forceinline__ void give_up(volatile int* dead, int code) {
     atomicCAS(&g_matmul_error, 0, code);
 }
 
-__global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) {
+template <int DUAL>
+__global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(UmmaParams p) {
+    constexpr uint32_t kStages = Shape<DUAL>::kStages, kStageA = Shape<DUAL>::kStageA, kTmemColumns = Shape<DUAL>::kTmemColumns;
+    constexpr uint32_t kGroups = Shape<DUAL>::kGroups, kTmaWarp = Shape<DUAL>::kTmaWarp, kMmaWarp = Shape<DUAL>::kMmaWarp;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* a_tiles = smem;
-    uint8_t* b_tiles = a_tiles + kStages * kATile;
+    uint8_t* b_tiles = a_tiles + kStages * kStageA;
     uint64_t* bars = reinterpret_cast<uint64_t*>(b_tiles + kStages * kBTile);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
     volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -212,68 +227,80 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
         const uint32_t row = tid & (kRows - 1), group = tid / kGroupThreads;
         const uint32_t grow = row0 + row;
         const bool valid = grow < p.n_rows;
-        const uint4* qsrc = p.quants + (uint64_t)(valid ? grow : 0) * p.n_blocks + (uint64_t)kc_begin * kChunkBlocks;
-        const unsigned short* ssrc =
-            reinterpret_cast<const unsigned short*>(p.scales) + (uint64_t)(valid ? grow : 0) * p.n_blocks + (uint64_t)kc_begin * kChunkBlocks;
+        const uint64_t first = (uint64_t)(valid ? grow : 0) * p.n_blocks + (uint64_t)kc_begin * kChunkBlocks;
         const uint32_t a_off = (row >> 3) * kGroupBytes + (row & 7) * 16;
-        const bool load = valid;
-        // A row's share of a chunk. Rows past the matrix keep scale zero, so their tile rows are zero.
+        // A row's share of a chunk of one matrix. Rows past the matrix keep scale zero, so their tile rows are zero.
         struct Share {
             uint4 q[kChunkBlocks];
             unsigned short d[kChunkBlocks];
         };
-        auto fetch = [&](uint32_t i) {
+        auto fetch = [&](uint32_t i, int m) {
             Share r;
+            const uint4* qsrc = p.quants[m] + first;
+            const unsigned short* ssrc = reinterpret_cast<const unsigned short*>(p.scales[m]) + first;
 #pragma unroll
             for (uint32_t b = 0; b < kChunkBlocks; ++b) {
                 r.q[b] = make_uint4(0, 0, 0, 0);
                 r.d[b] = 0;
-                if (load && i < my_chunks) {
+                if (valid && i < my_chunks) {
                     r.q[b] = __ldg(qsrc + (uint64_t)i * kChunkBlocks + b);
                     r.d[b] = __ldg(ssrc + (uint64_t)i * kChunkBlocks + b);
                 }
             }
             return r;
         };
-        // Two turns of loads stay in flight in registers.
-        Share cur = fetch(group), next = fetch(group + kGroups);
+        // Loads stay in flight in registers: two turns ahead with one matrix, one turn ahead with two.
+        Share cur[DUAL], next[DUAL], after[DUAL];
+#pragma unroll
+        for (int m = 0; m < DUAL; ++m) {
+            cur[m] = fetch(group, m);
+            next[m] = fetch(group + kGroups, m);
+        }
         bool alive = true;
-        uint32_t stage = group % kStages, phase = 1;  // the parity a free stage shows
-        for (uint32_t i = group; i < my_chunks; i += kGroups) {
-            Share after = fetch(i + 2 * kGroups);
-            // Dequantise before waiting for the stage, so only the stores follow the wait.
-            uint4 v[kChunkBlocks * 4];
+        const uint32_t stage = group;  // kGroups == kStages
+        uint32_t phase = 1;            // the parity a free stage shows
+        for (uint32_t i = group; i < my_chunks; i += kGroups, phase ^= 1) {
+            if (DUAL == 1) after[0] = fetch(i + 2 * kGroups, 0);
 #pragma unroll
-            for (uint32_t b = 0; b < kChunkBlocks; ++b) {
-                const __half d = __ushort_as_half(cur.d[b]);
-                const __half2 scale = __halves2half2(d, d);
-                v[4 * b + 0] = dequant_word(cur.q[b].x, scale);
-                v[4 * b + 1] = dequant_word(cur.q[b].y, scale);
-                v[4 * b + 2] = dequant_word(cur.q[b].z, scale);
-                v[4 * b + 3] = dequant_word(cur.q[b].w, scale);
-            }
-            // Lane 0 polls for the whole warp.
-            bool ok = lane != 0 || mbar_wait(empty0 + 8 * stage, phase, kSpinLimit, dead);
-            if (!__all_sync(0xffffffffu, ok)) {
-                if (lane == 0) give_up(dead, 1);
-                alive = false;
-                break;
-            }
-            const uint32_t dst = a0 + stage * kATile + a_off;
+            for (int m = 0; m < DUAL; ++m) {
+                // Dequantise before waiting for the stage, so only the stores follow the wait.
+                uint4 v[kChunkBlocks * 4];
 #pragma unroll
-            for (uint32_t j = 0; j < kChunkBlocks * 4; ++j) {
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + j * kCoreBytes), "r"(v[j].x), "r"(v[j].y), "r"(v[j].z), "r"(v[j].w)
-                             : "memory");
+                for (uint32_t b = 0; b < kChunkBlocks; ++b) {
+                    const __half d = __ushort_as_half(cur[m].d[b]);
+                    const __half2 scale = __halves2half2(d, d);
+                    v[4 * b + 0] = dequant_word(cur[m].q[b].x, scale);
+                    v[4 * b + 1] = dequant_word(cur[m].q[b].y, scale);
+                    v[4 * b + 2] = dequant_word(cur[m].q[b].z, scale);
+                    v[4 * b + 3] = dequant_word(cur[m].q[b].w, scale);
+                }
+                if (m == 0) {
+                    // Lane 0 polls for the whole warp.
+                    bool ok = lane != 0 || mbar_wait(empty0 + 8 * stage, phase, kSpinLimit, dead);
+                    if (!__all_sync(0xffffffffu, ok)) {
+                        if (lane == 0) give_up(dead, 1);
+                        alive = false;
+                    }
+                }
+                if (alive) {
+                    const uint32_t dst = a0 + stage * kStageA + m * kATile + a_off;
+#pragma unroll
+                    for (uint32_t j = 0; j < kChunkBlocks * 4; ++j) {
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + j * kCoreBytes), "r"(v[j].x), "r"(v[j].y), "r"(v[j].z),
+                                     "r"(v[j].w)
+                                     : "memory");
+                    }
+                }
             }
+            if (!alive) break;
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(full0 + 8 * stage);
-            cur = next;
-            next = after;
-            stage += kGroups;
-            if (stage >= kStages) {
-                stage -= kStages;
-                phase ^= 1;
+#pragma unroll
+            for (int m = 0; m < DUAL; ++m) {
+                cur[m] = next[m];
+                if (DUAL == 1) next[m] = after[m];
+                else next[m] = fetch(i + 2 * kGroups, m);
             }
         }
 
@@ -293,10 +320,17 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
                 float v[16];
                 __syncwarp();
                 tmem_load_16(tmem + ((quarter * 32) << 16) + u * 16, v);
+                if (DUAL == 2) {
+                    // silu(gate) * up, both from tensor memory.
+                    float up[16];
+                    tmem_load_16(tmem + ((quarter * 32) << 16) + kMaxTokens + u * 16, up);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.f + expf(-v[j])) * up[j];
+                }
                 if (out_row < p.n_rows) {
                     // Old values first, all 16 in flight at once, so the read-modify-write stores cost one round trip.
                     float old[16];
-                    if (p.store != BC_STORE_OVERWRITE) {
+                    if (DUAL == 1 && p.store != BC_STORE_OVERWRITE) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             uint32_t tok = tok0 + u * 16 + j;
@@ -308,8 +342,8 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
                         uint32_t tok = tok0 + u * 16 + j;
                         if (tok < p.n_tokens) {
                             float r = my_chunks ? v[j] : 0.f;
-                            if (p.store == BC_STORE_ACCUMULATE) r += old[j];
-                            else if (p.store == BC_STORE_SWIGLU) r = old[j] / (1.f + expf(-old[j])) * r;
+                            if (DUAL == 1 && p.store == BC_STORE_ACCUMULATE) r += old[j];
+                            else if (DUAL == 1 && p.store == BC_STORE_SWIGLU) r = old[j] / (1.f + expf(-old[j])) * r;
                             out[(uint64_t)tok * p.y_stride + out_row] = r;
                         }
                     }
@@ -336,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
             }
         }
     } else {
-        // ---- the tensor core: kChunkK / 16 steps of K = 16 per stage
+        // ---- the tensor core: kChunkK / 16 steps of K = 16 per stage and matrix
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_f16(kRows, n_tile);
             const uint64_t a_desc0 = umma_desc(a0, kCoreBytes, kGroupBytes), b_desc0 = umma_desc(b0, kCoreBytes, kGroupBytes);
@@ -354,10 +388,15 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_umma_kernel(UmmaParams p) 
                 }
                 tc_fence_after_sync();
                 // The address field counts 16-byte units, so stepping a descriptor is an add.
-                const uint64_t a_desc = a_desc0 + ((stage * kATile) >> 4), b_desc = b_desc0 + ((stage * kBTile) >> 4);
+                const uint64_t b_desc = b_desc0 + ((stage * kBTile) >> 4);
 #pragma unroll
-                for (uint32_t j = 0; j < kChunkK / 16; ++j)
-                    umma_f16(tmem, a_desc + ((j * 2 * kCoreBytes) >> 4), b_desc + ((j * 2 * kCoreBytes) >> 4), idesc, (i | j) != 0);
+                for (uint32_t m = 0; m < (uint32_t)DUAL; ++m) {
+                    const uint64_t a_desc = a_desc0 + ((stage * kStageA + m * kATile) >> 4);
+#pragma unroll
+                    for (uint32_t j = 0; j < kChunkK / 16; ++j)
+                        umma_f16(tmem + m * kMaxTokens, a_desc + ((j * 2 * kCoreBytes) >> 4), b_desc + ((j * 2 * kCoreBytes) >> 4), idesc,
+                                 (i | j) != 0);
+                }
                 umma_commit(empty0 + 8 * stage);
             }
             if (alive) umma_commit(accum);
@@ -459,15 +498,15 @@ cudaError_t matmul_pack_norm(cudaStream_t stream, const float* x, Norm norm, uin
 cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, float* y, uint32_t n_tokens, uint32_t y_stride,
                         int32_t store) {
     if (n_tokens == 0 || w.n_rows == 0) return cudaSuccess;
-    cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel), kSmemBytes);
+    cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), Shape<1>::kSmemBytes);
     if (err != cudaSuccess) return err;
     // The split must match matmul_scratch_bytes, which sized the scratch for a dense output.
     const uint32_t split = y_stride == w.n_rows ? choose_split(w.n_rows, w.n_cols, n_tokens, y_stride) : 1;
     float* partial = reinterpret_cast<float*>(static_cast<char*>(const_cast<void*>(scratch)) +
                                               ((matmul_pack_bytes(n_tokens, w.n_cols) + 255) & ~255ull));
-    UmmaParams p;
-    p.quants = static_cast<const uint4*>(w.data);
-    p.scales = w.scales;
+    UmmaParams p{};
+    p.quants[0] = static_cast<const uint4*>(w.data);
+    p.scales[0] = w.scales;
     p.packed = static_cast<const __half*>(scratch);
     p.y = split > 1 ? partial : y;
     p.n_rows = w.n_rows;
@@ -479,11 +518,40 @@ cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, 
     p.split = split;
     p.store = split > 1 ? BC_STORE_OVERWRITE : store;
     dim3 grid((n_tokens + kMaxTokens - 1) / kMaxTokens, (w.n_rows + kRows - 1) / kRows, split);
-    matmul_umma_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+    matmul_umma_kernel<1><<<grid, Shape<1>::kThreads, Shape<1>::kSmemBytes, stream>>>(p);
     err = cudaGetLastError();
     if (err != cudaSuccess || split == 1) return err;
     const uint64_t quads = (uint64_t)n_tokens * w.n_rows / 4;
     reduce_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(partial, y, w.n_rows, n_tokens, y_stride, split, store);
+    return cudaGetLastError();
+}
+
+bool matmul_umma_swiglu_supported(const Mat& gate, const Mat& up, uint32_t n_tokens) {
+    return matmul_umma_supported(gate, n_tokens) && matmul_umma_supported(up, n_tokens) && gate.n_rows == up.n_rows && gate.n_cols == up.n_cols;
+}
+
+cudaError_t matmul_umma_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, const void* packed, float* y, uint32_t n_tokens,
+                               uint32_t y_stride) {
+    if (n_tokens == 0 || gate.n_rows == 0) return cudaSuccess;
+    cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<2>), Shape<2>::kSmemBytes);
+    if (err != cudaSuccess) return err;
+    UmmaParams p{};
+    p.quants[0] = static_cast<const uint4*>(gate.data);
+    p.scales[0] = gate.scales;
+    p.quants[1] = static_cast<const uint4*>(up.data);
+    p.scales[1] = up.scales;
+    p.packed = static_cast<const __half*>(packed);
+    p.y = y;
+    p.n_rows = gate.n_rows;
+    p.n_blocks = gate.n_cols / 32;
+    p.n_chunks = gate.n_cols / kChunkK;
+    p.n_tokens = n_tokens;
+    p.y_stride = y_stride;
+    p.token_groups = ((n_tokens + 15u) & ~15u) / 8;
+    p.split = 1;
+    p.store = BC_STORE_OVERWRITE;
+    dim3 grid((n_tokens + kMaxTokens - 1) / kMaxTokens, (gate.n_rows + kRows - 1) / kRows, 1);
+    matmul_umma_kernel<2><<<grid, Shape<2>::kThreads, Shape<2>::kSmemBytes, stream>>>(p);
     return cudaGetLastError();
 }
 

@@ -58,6 +58,21 @@ struct Recorder {
         float* y;
         int store;
     };
+    // ffn = silu(gate x^) * (up x^) over the batch, x^ the normalised rows.
+    void normed_swiglu(const float* x, const float* norm_weight, uint32_t n, const k::Mat& gate, const k::Mat& up, float* y) {
+        if (!k::matmul_umma_swiglu_supported(gate, up, n)) {
+            // The up projection's store combines with the gate projection already in the buffer.
+            normed_matmuls(x, norm_weight, n, {{&gate, y, BC_STORE_OVERWRITE}, {&up, y, BC_STORE_SWIGLU}});
+            return;
+        }
+        const uint32_t cols = hp.n_embd;
+        void* scratch = nullptr;
+        if (status == BC_OK) status = s.backend->pack_scratch(k::matmul_pack_bytes(n, cols), &scratch);
+        run("pack_norm", n, cols, 0, 1, [&] { return k::matmul_pack_norm(stream, x, norm(norm_weight), n, cols, scratch); });
+        run("matmul_swiglu", gate.n_rows, gate.n_cols, 2 * gate.bytes(), 1,
+            [&] { return k::matmul_umma_swiglu(stream, gate, up, scratch, y, n, gate.n_rows); });
+    }
+
     void normed_matmuls(const float* x, const float* norm_weight, uint32_t n, std::initializer_list<Product> products) {
         const uint32_t cols = hp.n_embd;
         bool fused = true;
@@ -241,9 +256,7 @@ struct Recorder {
                 run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.ffn_norm, s.normed, n_embd, n, hp.norm_eps); });
                 lfm2_moe(D, n, false);
             } else {
-                // The up projection's store combines with the gate projection already in the
-                // buffer, which applies the SwiGLU.
-                normed_matmuls(s.hidden, D.ffn_norm, n, {{&D.gate, s.ffn, BC_STORE_OVERWRITE}, {&D.up, s.ffn, BC_STORE_SWIGLU}});
+                normed_swiglu(s.hidden, D.ffn_norm, n, D.gate, D.up, s.ffn);
                 matmul(D.down, s.ffn, s.hidden, n, BC_STORE_ACCUMULATE);
             }
             if (traced) copy(s.hidden, s.trace_layers + il * trace_stride, (uint64_t)n * n_embd);
@@ -347,7 +360,7 @@ struct Recorder {
                 qwen_delta_tail(D, S.cache_index, n);
                 matmul(D.ssm_out, s.gdn_out, s.hidden, n, BC_STORE_ACCUMULATE);
             }
-            normed_matmuls(s.hidden, D.ffn_norm, n, {{&D.gate, s.ffn, BC_STORE_OVERWRITE}, {&D.up, s.ffn, BC_STORE_SWIGLU}});
+            normed_swiglu(s.hidden, D.ffn_norm, n, D.gate, D.up, s.ffn);
             matmul(D.down, s.ffn, s.hidden, n, BC_STORE_ACCUMULATE);
             if (traced) copy(s.hidden, s.trace_layers + il * trace_stride, (uint64_t)n * n_embd);
         }

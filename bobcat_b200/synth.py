@@ -41,6 +41,10 @@ CONFIGS: dict[str, dict] = {
                       theta=1e6, eps=1e-5),
     "lfm2-small": dict(arch="lfm2", vocab=2048, hidden=256, layers=6, attention=[2, 5], heads=8, kv_heads=2, ff=704, conv_kernel=3,
                        theta=1e6, eps=1e-5),
+    # Wide enough that every pipeline of the prefill kernels wraps its stages many times (16 chunks of 64 columns
+    # in the projections, 44 in the down projection) and heads of 64 elements take the tensor-core attention.
+    "lfm2-medium": dict(arch="lfm2", vocab=4096, hidden=1024, layers=4, attention=[1, 3], heads=16, kv_heads=4, ff=2816, conv_kernel=3,
+                        theta=1e6, eps=1e-5),
     "lfm2moe-tiny": dict(arch="lfm2moe", vocab=512, hidden=128, layers=4, attention=[1, 3], heads=4, kv_heads=2, ff=256, conv_kernel=3,
                          theta=1e6, eps=1e-5, experts=8, experts_used=2, ff_expert=96, dense_layers=1),
     "qwen35-tiny": dict(arch="qwen35", vocab=512, hidden=128, layers=4, heads=2, kv_heads=1, head_dim=64, n_rot=32, ff=256, k_heads=2,

@@ -76,6 +76,41 @@ def test_prefill_matches_steps_and_oracle(pair, cuda, kv_half):
     assert rel_error(logits, step_logits) < tolerance
 
 
+def test_long_prefill_matches_steps(model_path, cuda):
+    """512 tokens in two batched calls against 512 single steps, on a model wide enough that the
+    prefill kernels' stage rings wrap many times (crates/bobcat/tests/lfm2_reference.rs:118-151),
+    then the oracle on the last token's logits and a greedy continuation."""
+    path = model_path("lfm2-medium")
+    model = Model.load(path)
+    hp = model.hyperparameters()
+    tokens = prompt_tokens(hp.n_vocab, 512, seed=5)
+    seq = Lfm2Cuda(model, cuda, 640, kv_half=True)
+    logits = np.zeros(hp.n_vocab, dtype=np.float32)
+    seq.prefill(tokens[:300])
+    seq.prefill(tokens[300:], logits)
+    steps = Lfm2Cuda(model, cuda, 640, kv_half=True)
+    step_logits = np.zeros_like(logits)
+    for tok in tokens:
+        steps.step(int(tok), step_logits)
+    assert rel_error(logits, step_logits) < HALF_TOLERANCE
+    assert seq.generate(16).tolist() == steps.generate(16).tolist()
+    # A second pass over the same prompt gives the same bits: nothing in the batched path depends on scheduling.
+    again = np.zeros_like(logits)
+    seq.reset()
+    seq.prefill(tokens[:300])
+    seq.prefill(tokens[300:], again)
+    assert np.array_equal(logits, again)
+    ref = oracle.Model(path, threads=8)
+    st = ref.state(64)
+    short = tokens[:40]
+    for i, tok in enumerate(short):
+        want = st.step(int(tok), want_logits=(i == len(short) - 1))
+    check = Lfm2Cuda(model, cuda, 64, kv_half=False)
+    got = np.zeros_like(logits)
+    check.prefill(short, got)
+    assert rel_error(got, want["logits"]) < HALF_TOLERANCE
+
+
 def test_greedy_tokens_match(pair, cuda):
     model, ref = pair
     hp = model.hyperparameters()
