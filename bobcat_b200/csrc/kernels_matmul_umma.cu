@@ -116,9 +116,10 @@ __global__ void __launch_bounds__(256) pack_kernel(const float* __restrict__ x, 
 }
 
 // RMSNorm and packing in one pass: packed = fp16(weight * (x * scale)), scale = 1 / sqrt(mean x^2 + eps)
-// per token, the arithmetic of rms_norm_kernel followed by pack_kernel. One CTA per group of 8
-// tokens: a warp per token sums its squares, then the CTA writes the group's kilobyte of every
-// chunk. Rows past the batch are zero.
+// per token, the arithmetic of rms_norm_kernel followed by pack_kernel. A CTA serves a group of 8
+// tokens: a warp per token sums its squares, then the CTA writes the group's kilobyte of its share
+// of the chunks (blockIdx.y of gridDim.y; each share repeats the cheap sums, which keeps the grid
+// wide). Rows past the batch are zero.
 __global__ void __launch_bounds__(256) pack_norm_kernel(const float* __restrict__ x, const float* __restrict__ weight, float eps,
                                                         __half* __restrict__ packed, uint32_t n_tokens, uint32_t n_cols, uint32_t token_groups) {
     __shared__ float scales[8];
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(256) pack_norm_kernel(const float* __restrict_
     const uint32_t tr = tid & 7, j = (tid >> 3) & (kCores - 1), sub = tid / (8 * kCores);  // 256 / 64 = 4 chunks per pass
     const uint32_t token = tg * 8 + tr, n_chunks = n_cols / kChunkK;
     const float scale = scales[tr];
-    for (uint32_t chunk = sub; chunk < n_chunks; chunk += 256 / (8 * kCores)) {
+    for (uint32_t chunk = blockIdx.y * (256 / (8 * kCores)) + sub; chunk < n_chunks; chunk += gridDim.y * (256 / (8 * kCores))) {
         uint4 out = make_uint4(0, 0, 0, 0);
         if (token < n_tokens) {
             const uint32_t col = chunk * kChunkK + (j >> 2) * 32 + 4 * (j & 3);
@@ -491,7 +492,9 @@ cudaError_t matmul_pack(cudaStream_t stream, const float* x, uint32_t n_tokens, 
 cudaError_t matmul_pack_norm(cudaStream_t stream, const float* x, Norm norm, uint32_t n_tokens, uint32_t n_cols, void* packed) {
     uint32_t token_groups = ((n_tokens + 15u) & ~15u) / 8;
     if (token_groups == 0 || n_cols == 0) return cudaSuccess;
-    pack_norm_kernel<<<token_groups, 256, 0, stream>>>(x, norm.weight, norm.eps, static_cast<__half*>(packed), n_tokens, n_cols, token_groups);
+    const uint32_t shares = token_groups >= 256 ? 1 : token_groups >= 64 ? 4 : 8;
+    pack_norm_kernel<<<dim3(token_groups, shares), 256, 0, stream>>>(x, norm.weight, norm.eps, static_cast<__half*>(packed), n_tokens, n_cols,
+                                                                    token_groups);
     return cudaGetLastError();
 }
 

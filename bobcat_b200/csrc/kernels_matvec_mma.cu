@@ -306,6 +306,23 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     bool dead = false;
     for (uint32_t r = 0; r * groups + grp < my_jobs; ++r) {
         const uint32_t job = blockIdx.x + gridDim.x * (r * groups + grp);
+        // The thread that will finish a row of a plain product finds the row now and, when the
+        // product adds to y, starts reading the old value, so that read overlaps the multiply.
+        float* y_row = nullptr;
+        float y_old = 0.f;
+        if (MODE == kPlain && rank == 0 && lane < 16) {
+            int seg = 0;
+            uint32_t local = job;
+            while (seg + 1 < p.n_segments && local >= p.seg_tiles[seg]) {
+                local -= p.seg_tiles[seg];
+                ++seg;
+            }
+            uint32_t row = local * 16 + lane;
+            if (row < p.seg_rows[seg]) {
+                y_row = p.y[seg] + row;
+                if (p.accumulate) y_old = *y_row;
+            }
+        }
         float acc[S][2];
 #pragma unroll
         for (int s = 0; s < S; ++s) acc[s][0] = acc[s][1] = 0.f;
@@ -378,17 +395,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
             }
             const uint32_t in_tile = lane;
             if (MODE == kPlain) {
-                int seg = 0;
-                uint32_t local = job;
-                while (seg + 1 < p.n_segments && local >= p.seg_tiles[seg]) {
-                    local -= p.seg_tiles[seg];
-                    ++seg;
-                }
-                uint32_t row = local * 16 + in_tile;
-                if (row < p.seg_rows[seg]) {
-                    float* y = p.y[seg] + row;
-                    *y = p.accumulate ? *y + sum[0] : sum[0];
-                }
+                if (y_row) *y_row = y_old + sum[0];
             } else if (MODE == kSwiglu) {
                 uint32_t row = job * 16 + in_tile;
                 if (row < p.seg_rows[0]) {
