@@ -260,6 +260,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
             v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
         }
         biggest = fmaxf(biggest, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        // The weighted values wait in the staging buffer as f32 (element for element the bytes
+        // their fp16 pair will take), so the second pass needs neither global memory nor the weights.
+        reinterpret_cast<float4*>(xs)[i] = v;
     }
     sumsq = warp_sum(sumsq);
     biggest = warp_max(biggest);
@@ -280,12 +283,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     const float out_scale = norm_scale / up;
     for (uint32_t i = ctid; i < nb * 4; i += kConsumerThreads) {
         uint32_t b = i >> 2, t = i & 3;
-        float4 lo4 = x4[b * 8 + t], hi4 = x4[b * 8 + 4 + t];  // elements 4t..4t+3 and 16+4t..16+4t+3
-        if (p.norm_weight) {
-            float4 wl = __ldg(w4 + b * 8 + t), wh = __ldg(w4 + b * 8 + 4 + t);
-            lo4.x *= wl.x; lo4.y *= wl.y; lo4.z *= wl.z; lo4.w *= wl.w;
-            hi4.x *= wh.x; hi4.y *= wh.y; hi4.z *= wh.z; hi4.w *= wh.w;
-        }
+        // Elements 4t..4t+3 and 16+4t..16+4t+3: the same 32 bytes this thread then overwrites.
+        const float4 lo4 = reinterpret_cast<const float4*>(xs)[b * 8 + t], hi4 = reinterpret_cast<const float4*>(xs)[b * 8 + 4 + t];
         float v[8] = {lo4.x * up, lo4.z * up, lo4.y * up, lo4.w * up, hi4.x * up, hi4.z * up, hi4.y * up, hi4.w * up};
         __align__(16) __half hi[8];
         __align__(16) __half lo[8];
