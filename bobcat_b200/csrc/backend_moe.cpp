@@ -132,9 +132,13 @@ bc_status bc_op_matmul_experts(bc_backend* b, int32_t format, bc_buffer* weights
     BC_TRY(check_range(b, offsets, off_off, ((size_t)n_experts + 1) * 4, "matmul_experts"));
     BC_TRY(check_range(b, entries, ent_off, (size_t)n_tokens * n_used * 4, "matmul_experts"));
     BC_TRY(check_range(b, y, y_off, (size_t)n_tokens * n_used * n_rows * 4, "matmul_experts"));
-    return b->run("matmul_experts", n_rows, n_cols, w.bytes() * (up ? 2 : 1), 1, [&] {
+    void* scratch = nullptr;
+    if (k::matmul_experts_umma_supported(w, up ? &u : nullptr, n_tokens))
+        BC_TRY(b->pack_scratch(k::matmul_experts_scratch_bytes(n_experts, n_tokens, n_cols), &scratch));
+    return b->run("matmul_experts", n_rows, n_cols, w.bytes() * (up ? 2 : 1), scratch ? 2 : 1, [&] {
         return k::matmul_experts(b->stream, w, up ? &u : nullptr, n_rows, n_experts, at<const float>(x, x_off), gather != 0,
-                                 at<const uint32_t>(offsets, off_off), at<const uint32_t>(entries, ent_off), n_used, at<float>(y, y_off), n_tokens);
+                                 at<const uint32_t>(offsets, off_off), at<const uint32_t>(entries, ent_off), n_used, at<float>(y, y_off), n_tokens,
+                                 scratch);
     });
 }
 

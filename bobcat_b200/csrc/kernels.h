@@ -174,8 +174,15 @@ cudaError_t matvec_experts_down(cudaStream_t stream, const Mat& down, uint32_t n
                                 uint32_t n_used, float* y, uint32_t n_tokens);
 // Prefill: for each expert, its entries times its rows; with `up` the store is silu(gate) * up.
 // Input rows are the tokens' (gather) or the entries' own; output rows are the entries'.
+// With `scratch` (matmul_experts_scratch_bytes) and Q4_0 experts the tcgen05 kernel runs in its
+// grouped mode (two launches: gather-pack, then the product); otherwise the SIMT tile kernel.
 cudaError_t matmul_experts(cudaStream_t stream, const Mat& w, const Mat* up, uint32_t n_rows, uint32_t n_experts, const float* x,
-                           bool gather, const uint32_t* offsets, const uint32_t* entries, uint32_t n_used, float* y, uint32_t n_tokens);
+                           bool gather, const uint32_t* offsets, const uint32_t* entries, uint32_t n_used, float* y, uint32_t n_tokens,
+                           void* scratch);
+bool matmul_experts_umma_supported(const Mat& w, const Mat* up, uint32_t n_tokens);
+uint64_t matmul_experts_scratch_bytes(uint32_t n_experts, uint32_t n_tokens, uint32_t n_cols);
+cudaError_t matmul_experts_umma(cudaStream_t stream, const Mat& w, const Mat* up, uint32_t n_rows, uint32_t n_experts, const float* x, bool gather,
+                                const uint32_t* offsets, const uint32_t* entries, uint32_t n_used, float* y, uint32_t n_tokens, void* scratch);
 cudaError_t moe_combine(cudaStream_t stream, const float* expert_out, const uint32_t* route, float* y, uint32_t n_embd,
                         uint32_t n_used, uint32_t n_tokens);
 

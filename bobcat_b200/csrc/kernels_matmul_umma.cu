@@ -89,6 +89,13 @@ struct UmmaParams {
     uint32_t n_rows, n_blocks, n_chunks, n_tokens, y_stride, token_groups;
     uint32_t split;  // parts K is divided into (blockIdx.z)
     int store;
+    // Grouped mode (mixture of experts), when offsets is set: blockIdx.z is an expert, whose weights
+    // are rows [z * n_rows, (z + 1) * n_rows) of the stacked matrices, whose tokens are the entries
+    // offsets[z] .. offsets[z + 1], packed from token group z * cap_groups on, and whose output
+    // row for its t-th token is entries[offsets[z] + t].
+    const uint32_t* offsets;
+    const uint32_t* entries;
+    uint32_t cap_groups;
 };
 
 // X [n_tokens][n_cols] f32 -> fp16 operand layout, zero rows up to the padded token count. One
@@ -161,6 +168,38 @@ __global__ void __launch_bounds__(256) pack_norm_kernel(const float* __restrict_
     }
 }
 
+// Packing for grouped mode: sorted entry i of expert e (offsets[e] <= i < offsets[e + 1]) becomes
+// token i - offsets[e] of the expert's region, which starts at token group e * cap_groups; its row
+// of x is the entry's token (gather: entry / n_used) or the entry itself. One thread per 16-byte
+// output. Rows between an expert's last token and the end of its last group of 16 stay unwritten:
+// they only reach accumulator columns nobody stores.
+__global__ void __launch_bounds__(256) pack_grouped_kernel(const float* __restrict__ x, __half* __restrict__ packed, const uint32_t* __restrict__ offsets,
+                                                           const uint32_t* __restrict__ entries, uint32_t n_experts, uint32_t n_used, int gather,
+                                                           uint32_t n_cols, uint32_t cap_groups, uint32_t total_entries) {
+    const uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t n_chunks = n_cols / kChunkK;
+    if (o >= (uint64_t)total_entries * n_chunks * kCores) return;
+    const uint32_t j = o % kCores;
+    const uint32_t i = (o / kCores) % total_entries, chunk = (uint32_t)(o / ((uint64_t)kCores * total_entries));
+    // The expert of sorted entry i: the last e with offsets[e] <= i.
+    uint32_t lo = 0, hi = n_experts;
+    while (hi - lo > 1) {
+        uint32_t mid = (lo + hi) / 2;
+        if (offsets[mid] <= i) lo = mid;
+        else hi = mid;
+    }
+    const uint32_t local = i - offsets[lo], entry = entries[i];
+    const uint32_t row = gather ? entry / n_used : entry;
+    const float* src = x + (uint64_t)row * n_cols + chunk * kChunkK + (j >> 2) * 32 + 4 * (j & 3);
+    const float4 l4 = *reinterpret_cast<const float4*>(src), h4 = *reinterpret_cast<const float4*>(src + 16);
+    __half2 a = __floats2half2_rn(l4.x, l4.z), b = __floats2half2_rn(l4.y, l4.w);
+    __half2 c = __floats2half2_rn(h4.x, h4.z), d = __floats2half2_rn(h4.y, h4.w);
+    uint4 out = make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b), *reinterpret_cast<uint32_t*>(&c),
+                           *reinterpret_cast<uint32_t*>(&d));
+    const uint64_t token_groups = (uint64_t)n_experts * cap_groups, tg = (uint64_t)lo * cap_groups + local / 8;
+    reinterpret_cast<uint4*>(packed)[((chunk * token_groups + tg) * kCores + j) * 8 + (local & 7)] = out;
+}
+
 // The eight weights of quant word `w` times the block scale, as fp16 in the permuted order.
 __device__ __forceinline__ uint4 dequant_word(uint32_t w, __half2 scale) {
     const uint32_t magic = 0x64006400u;  // half2(1024, 1024)
@@ -198,11 +237,22 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t tok0 = blockIdx.x * kMaxTokens, row0 = blockIdx.y * kRows;
-    const uint32_t left = p.n_tokens - tok0;
+    uint32_t n_tokens = p.n_tokens, group0 = 0;
+    uint64_t weight0 = 0;  // first block of this CTA's matrix in the stacked weights
+    const uint32_t* out_rows = nullptr;
+    if (p.offsets) {
+        const uint32_t first = p.offsets[blockIdx.z];
+        n_tokens = p.offsets[blockIdx.z + 1] - first;
+        if (tok0 >= n_tokens) return;  // the whole CTA, before it owns anything
+        group0 = blockIdx.z * p.cap_groups;
+        weight0 = (uint64_t)blockIdx.z * p.n_rows * p.n_blocks;
+        out_rows = p.entries + first;
+    }
+    const uint32_t left = n_tokens - tok0;
     const uint32_t n_tile = left >= kMaxTokens ? kMaxTokens : ((left + 15u) & ~15u);  // the MMA's N
     // This CTA's share of K.
     const uint32_t per_part = (p.n_chunks + p.split - 1) / p.split;
-    const uint32_t kc_begin = blockIdx.z * per_part;
+    const uint32_t kc_begin = p.offsets ? 0 : blockIdx.z * per_part;
     const uint32_t kc_end = kc_begin + per_part < p.n_chunks ? kc_begin + per_part : p.n_chunks;
     const uint32_t my_chunks = kc_end > kc_begin ? kc_end - kc_begin : 0;
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + kStages * 8, accum = empty0 + kStages * 8;
@@ -228,7 +278,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
         const uint32_t row = tid & (kRows - 1), group = tid / kGroupThreads;
         const uint32_t grow = row0 + row;
         const bool valid = grow < p.n_rows;
-        const uint64_t first = (uint64_t)(valid ? grow : 0) * p.n_blocks + (uint64_t)kc_begin * kChunkBlocks;
+        const uint64_t first = weight0 + (uint64_t)(valid ? grow : 0) * p.n_blocks + (uint64_t)kc_begin * kChunkBlocks;
         const uint32_t a_off = (row >> 3) * kGroupBytes + (row & 7) * 16;
         // A row's share of a chunk of one matrix. Rows past the matrix keep scale zero, so their tile rows are zero.
         struct Share {
@@ -316,7 +366,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
             tc_fence_after_sync();
             const uint32_t quarter = warp & 3, part = warp >> 2, units = n_tile / 16;
             const uint32_t out_row = row0 + quarter * 32 + lane;
-            float* out = p.y + (p.split > 1 ? (uint64_t)blockIdx.z * p.n_tokens * p.y_stride : 0);
+            float* out = p.y + (p.split > 1 ? (uint64_t)blockIdx.z * n_tokens * p.y_stride : 0);
             for (uint32_t u = part; u < units; u += kGroups) {
                 float v[16];
                 __syncwarp();
@@ -331,21 +381,24 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
                 if (out_row < p.n_rows) {
                     // Old values first, all 16 in flight at once, so the read-modify-write stores cost one round trip.
                     float old[16];
-                    if (DUAL == 1 && p.store != BC_STORE_OVERWRITE) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            uint32_t tok = tok0 + u * 16 + j;
-                            old[j] = tok < p.n_tokens ? __ldcg(out + (uint64_t)tok * p.y_stride + out_row) : 0.f;
-                        }
-                    }
+                    // The output row of each token: itself, or in grouped mode the entry it came from.
+                    uint32_t dest[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         uint32_t tok = tok0 + u * 16 + j;
-                        if (tok < p.n_tokens) {
+                        dest[j] = tok < n_tokens ? (out_rows ? __ldg(out_rows + tok) : tok) : 0xffffffffu;
+                    }
+                    if (DUAL == 1 && p.store != BC_STORE_OVERWRITE) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) old[j] = dest[j] != 0xffffffffu ? __ldcg(out + (uint64_t)dest[j] * p.y_stride + out_row) : 0.f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (dest[j] != 0xffffffffu) {
                             float r = my_chunks ? v[j] : 0.f;
                             if (DUAL == 1 && p.store == BC_STORE_ACCUMULATE) r += old[j];
                             else if (DUAL == 1 && p.store == BC_STORE_SWIGLU) r = old[j] / (1.f + expf(-old[j])) * r;
-                            out[(uint64_t)tok * p.y_stride + out_row] = r;
+                            out[(uint64_t)dest[j] * p.y_stride + out_row] = r;
                         }
                     }
                 }
@@ -355,7 +408,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
         // ---- the token tiles: one bulk copy per stage
         if (lane == 0) {
             const uint32_t bytes = n_tile * kChunkK * 2;
-            const __half* src = p.packed + (uint64_t)(tok0 / 8) * (8 * kChunkK);
+            const __half* src = p.packed + (uint64_t)(group0 + tok0 / 8) * (8 * kChunkK);
             uint32_t stage = 0, phase = 1;
             for (uint32_t i = 0; i < my_chunks; ++i, ++stage) {
                 if (stage == kStages) {
@@ -555,6 +608,58 @@ cudaError_t matmul_umma_swiglu(cudaStream_t stream, const Mat& gate, const Mat& 
     p.store = BC_STORE_OVERWRITE;
     dim3 grid((n_tokens + kMaxTokens - 1) / kMaxTokens, (gate.n_rows + kRows - 1) / kRows, 1);
     matmul_umma_kernel<2><<<grid, Shape<2>::kThreads, Shape<2>::kSmemBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+// ---- grouped products over experts (mixture-of-experts prefill)
+
+bool matmul_experts_umma_supported(const Mat& w, const Mat* up, uint32_t n_tokens) {
+    if (umma_disabled() || w.format != BC_Q4_0 || w.n_cols % kChunkK != 0 || n_tokens < 16) return false;
+    return !up || (up->format == BC_Q4_0 && up->n_cols == w.n_cols && up->n_rows == w.n_rows);
+}
+
+uint64_t matmul_experts_scratch_bytes(uint32_t n_experts, uint32_t n_tokens, uint32_t n_cols) {
+    return (uint64_t)n_experts * ((n_tokens + 15u) & ~15u) * n_cols * 2;
+}
+
+cudaError_t matmul_experts_umma(cudaStream_t stream, const Mat& w, const Mat* up, uint32_t n_rows, uint32_t n_experts, const float* x, bool gather,
+                                const uint32_t* offsets, const uint32_t* entries, uint32_t n_used, float* y, uint32_t n_tokens, void* scratch) {
+    if (n_tokens == 0 || n_rows == 0) return cudaSuccess;
+    const uint32_t cap_groups = ((n_tokens + 15u) & ~15u) / 8, total = n_tokens * n_used;
+    const uint64_t outputs = (uint64_t)total * (w.n_cols / kChunkK) * kCores;
+    pack_grouped_kernel<<<(unsigned)((outputs + 255) / 256), 256, 0, stream>>>(x, static_cast<__half*>(scratch), offsets, entries, n_experts, n_used,
+                                                                            gather ? 1 : 0, w.n_cols, cap_groups, total);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+    UmmaParams p{};
+    p.quants[0] = static_cast<const uint4*>(w.data);
+    p.scales[0] = w.scales;
+    if (up) {
+        p.quants[1] = static_cast<const uint4*>(up->data);
+        p.scales[1] = up->scales;
+    }
+    p.packed = static_cast<const __half*>(scratch);
+    p.y = y;
+    p.n_rows = n_rows;
+    p.n_blocks = w.n_cols / 32;
+    p.n_chunks = w.n_cols / kChunkK;
+    p.n_tokens = n_tokens;
+    p.y_stride = n_rows;
+    p.token_groups = n_experts * cap_groups;
+    p.split = 1;
+    p.store = BC_STORE_OVERWRITE;
+    p.offsets = offsets;
+    p.entries = entries;
+    p.cap_groups = cap_groups;
+    // Any one expert can receive up to n_tokens entries (a token picks an expert at most once).
+    dim3 grid((n_tokens + kMaxTokens - 1) / kMaxTokens, (n_rows + kRows - 1) / kRows, n_experts);
+    if (up) {
+        if ((err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<2>), Shape<2>::kSmemBytes)) != cudaSuccess) return err;
+        matmul_umma_kernel<2><<<grid, Shape<2>::kThreads, Shape<2>::kSmemBytes, stream>>>(p);
+    } else {
+        if ((err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), Shape<1>::kSmemBytes)) != cudaSuccess) return err;
+        matmul_umma_kernel<1><<<grid, Shape<1>::kThreads, Shape<1>::kSmemBytes, stream>>>(p);
+    }
     return cudaGetLastError();
 }
 

@@ -142,12 +142,21 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const uint32_t* __restr
     __syncthreads();
     for (uint32_t e = threadIdx.x; e <= n_experts; e += blockDim.x) offsets[e] = counts[e];
     __syncthreads();
-    // One thread per expert places its entries in token order, which keeps the order stable.
-    for (uint32_t e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    // A warp per expert walks the entries 32 at a time in token order; a ballot and a count of the
+    // lower lanes give each of the expert's entries its place, which keeps the order stable.
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    for (uint32_t e = warp; e < n_experts; e += n_warps) {
         uint32_t at = counts[e];
-        for (uint32_t i = 0; i < total; ++i) {
-            uint32_t token = i / n_used, slot = i % n_used;
-            if (route[(uint64_t)token * 2 * n_used + slot] == e) entries[at++] = i;
+        for (uint32_t base = 0; base < total; base += 32) {
+            const uint32_t i = base + lane;
+            bool mine = false;
+            if (i < total) {
+                uint32_t token = i / n_used, slot = i % n_used;
+                mine = route[(uint64_t)token * 2 * n_used + slot] == e;
+            }
+            const uint32_t votes = __ballot_sync(0xffffffffu, mine);
+            if (mine) entries[at + __popc(votes & ((1u << lane) - 1u))] = i;
+            at += __popc(votes);
         }
     }
 }
@@ -382,8 +391,11 @@ cudaError_t matvec_experts_down(cudaStream_t stream, const Mat& down, uint32_t n
 }
 
 cudaError_t matmul_experts(cudaStream_t stream, const Mat& w, const Mat* up, uint32_t n_rows, uint32_t n_experts, const float* x,
-                           bool gather, const uint32_t* offsets, const uint32_t* entries, uint32_t n_used, float* y, uint32_t n_tokens) {
+                           bool gather, const uint32_t* offsets, const uint32_t* entries, uint32_t n_used, float* y, uint32_t n_tokens,
+                           void* scratch) {
     if (n_tokens == 0) return cudaSuccess;
+    if (scratch && matmul_experts_umma_supported(w, up, n_tokens))
+        return matmul_experts_umma(stream, w, up, n_rows, n_experts, x, gather, offsets, entries, n_used, y, n_tokens, scratch);
     GroupedParams p{w, up ? *up : w, up != nullptr, x, gather, offsets, entries, y, n_rows, n_used};
     // Any one expert can receive up to n_tokens entries (a token picks an expert at most once).
     dim3 grid((n_tokens + 63) / 64, (n_rows + 63) / 64, n_experts);

@@ -197,12 +197,25 @@ struct Recorder {
             return;
         }
         run("moe_group", n, hp.n_experts, 0, 1, [&] { return k::moe_group(stream, s.route, s.expert_offsets, s.expert_entries, hp.n_experts, n_used, n); });
-        run("matmul_experts", n_ff, n_embd, 2 * D.gate.bytes(), 1, [&] {
-            return k::matmul_experts(stream, D.gate, &D.up, n_ff, hp.n_experts, s.normed, true, s.expert_offsets, s.expert_entries, n_used, s.ffn, n);
+        // Q4_0 experts run on the tensor-core kernel in its grouped mode, from a gathered fp16 packing.
+        void* up_scratch = nullptr;
+        void* down_scratch = nullptr;
+        const bool tensor_up = k::matmul_experts_umma_supported(D.gate, &D.up, n), tensor_down = k::matmul_experts_umma_supported(D.down, nullptr, n);
+        if (status == BC_OK && (tensor_up || tensor_down)) {
+            size_t bytes = (size_t)std::max(tensor_up ? k::matmul_experts_scratch_bytes(hp.n_experts, n, n_embd) : 0,
+                                            tensor_down ? k::matmul_experts_scratch_bytes(hp.n_experts, n, n_ff) : 0);
+            void* scratch = nullptr;
+            status = s.backend->pack_scratch(bytes, &scratch);
+            if (tensor_up) up_scratch = scratch;
+            if (tensor_down) down_scratch = scratch;
+        }
+        run("matmul_experts", n_ff, n_embd, 2 * D.gate.bytes(), up_scratch ? 2 : 1, [&] {
+            return k::matmul_experts(stream, D.gate, &D.up, n_ff, hp.n_experts, s.normed, true, s.expert_offsets, s.expert_entries, n_used, s.ffn, n,
+                                     up_scratch);
         });
-        run("matmul_experts", n_embd, n_ff, D.down.bytes(), 1, [&] {
+        run("matmul_experts", n_embd, n_ff, D.down.bytes(), down_scratch ? 2 : 1, [&] {
             return k::matmul_experts(stream, D.down, nullptr, n_embd, hp.n_experts, s.ffn, false, s.expert_offsets, s.expert_entries, n_used,
-                                     s.expert_out, n);
+                                     s.expert_out, n, down_scratch);
         });
         run("moe_combine", n, n_embd, 0, 1, [&] { return k::moe_combine(stream, s.expert_out, s.route, s.hidden, n_embd, n_used, n); });
     }

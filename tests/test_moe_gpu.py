@@ -87,12 +87,15 @@ def test_group_is_a_stable_counting_sort(cuda):
     assert np.array_equal(offsets, want_offsets) and np.array_equal(entries, want_entries)
 
 
-@pytest.mark.parametrize("n_tokens", [1, 5, 70])
-def test_expert_paths_match_the_scalar_block(cuda, n_tokens):
+# (n_tokens, n_ff): widths that are multiples of 64 with at least 16 tokens send the grouped product to the
+# tensor-core kernel (fp16 operands, like the reference's Q4_0 prefill kernel); the rest stay on the f32 tile kernel.
+@pytest.mark.parametrize("n_tokens,n_ff", [(1, 96), (5, 96), (70, 96), (70, 128), (300, 192)])
+def test_expert_paths_match_the_scalar_block(cuda, n_tokens, n_ff):
     """Decode (per-token expert matvecs) and prefill (group, grouped matmul, combine) both equal
     lfm2.rs:413-440 computed with the checker's f64 matvec."""
     rng = np.random.default_rng(n_tokens + 11)
-    n_embd, n_ff, n_experts, n_used = 128, 96, 8, 2
+    n_embd, n_experts, n_used = 128, 8, 2
+    prefill_tolerance = 5e-3 if n_tokens >= 16 else 1e-5
     gate_raw, up_raw = random_q4_0(rng, n_experts * n_ff, n_embd), random_q4_0(rng, n_experts * n_ff, n_embd)
     down_raw = random_q4_0(rng, n_experts * n_embd, n_ff)
     x = rng.uniform(-1, 1, (n_tokens, n_embd)).astype(np.float32)
@@ -131,7 +134,7 @@ def test_expert_paths_match_the_scalar_block(cuda, n_tokens):
     cuda.moe_combine(eo, rb, yb2, n_embd, n_used, n_tokens)
     cuda.end()
     prefill = cuda.read(yb2, np.zeros_like(y0))
-    assert rel_error(prefill, want) < 1e-5
+    assert rel_error(prefill, want) < prefill_tolerance
 
 
 @pytest.fixture(scope="module")
