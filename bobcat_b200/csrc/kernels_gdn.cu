@@ -107,13 +107,13 @@ struct RecurrenceParams {
 
 // One CTA per value head, one thread per state column, which holds its k_dim state values in
 // registers for the whole run of tokens. Per token (qwen35.rs:483-506): S *= decay;
-// r = sum_i S[i] k_i; delta = (v - r) beta; S[i] += k_i delta; o = sum_i S[i] q_i, the sums in
-// row order. Value head h reads key head h % n_k_heads.
+// r = sum_i S[i] k_i; delta = (v - r) beta; S[i] += k_i delta; o = sum_i S[i] q_i, each sum as
+// four interleaved partial sums. Value head h reads key head h % n_k_heads.
 template <int KDIM>
 __global__ void __launch_bounds__(256) gdn_recurrence_kernel(RecurrenceParams p) {
     // Two copies of the staged q, k and of the reduction scratch, used on alternate tokens, so a
     // token needs two block barriers and the next token's inputs load while this one computes.
-    __shared__ float qs[2][KDIM], ks[2][KDIM];
+    __shared__ __align__(16) float qs[2][KDIM], ks[2][KDIM];
     __shared__ float scratch[2][16];
     pdl_launch_dependents();
     pdl_wait();
@@ -174,20 +174,38 @@ __global__ void __launch_bounds__(256) gdn_recurrence_kernel(RecurrenceParams p)
         }
         __syncthreads();
         if (j < vd) {
-            float r = 0.f;
+            // Four partial sums per dot product: a single running sum would make each token a chain
+            // of KDIM dependent adds, which is what bounds this kernel. q and k come four at a time.
+            const float4* k4 = reinterpret_cast<const float4*>(ks[buf]);
+            const float4* q4 = reinterpret_cast<const float4*>(qs[buf]);
+            float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < KDIM; ++i) {
-                S[i] *= cur.decay;
-                r += S[i] * ks[buf][i];
+            for (int i = 0; i < KDIM / 4; ++i) {
+                const float4 kv = k4[i];
+                S[4 * i] *= cur.decay;
+                S[4 * i + 1] *= cur.decay;
+                S[4 * i + 2] *= cur.decay;
+                S[4 * i + 3] *= cur.decay;
+                r0 += S[4 * i] * kv.x;
+                r1 += S[4 * i + 1] * kv.y;
+                r2 += S[4 * i + 2] * kv.z;
+                r3 += S[4 * i + 3] * kv.w;
             }
-            const float delta = (cur.v - r) * cur.beta;
-            float o = 0.f;
+            const float delta = (cur.v - ((r0 + r1) + (r2 + r3))) * cur.beta;
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < KDIM; ++i) {
-                S[i] += ks[buf][i] * delta;
-                o += S[i] * qs[buf][i];
+            for (int i = 0; i < KDIM / 4; ++i) {
+                const float4 kv = k4[i], qv = q4[i];
+                S[4 * i] += kv.x * delta;
+                S[4 * i + 1] += kv.y * delta;
+                S[4 * i + 2] += kv.z * delta;
+                S[4 * i + 3] += kv.w * delta;
+                o0 += S[4 * i] * qv.x;
+                o1 += S[4 * i + 1] * qv.y;
+                o2 += S[4 * i + 2] * qv.z;
+                o3 += S[4 * i + 3] * qv.w;
             }
-            p.out[(uint64_t)t * p.n_v_heads * vd + head * vd + j] = o;
+            p.out[(uint64_t)t * p.n_v_heads * vd + head * vd + j] = (o0 + o1) + (o2 + o3);
         }
         cur = next;
     }
