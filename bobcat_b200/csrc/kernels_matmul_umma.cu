@@ -87,7 +87,8 @@ struct UmmaParams {
     const __half* packed;  // inputs in operand layout: [n_chunks][token_groups][8 cores][8 tokens][8 halves]
     float* y;              // the output, or with split > 1 the partial products [split][n_tokens][n_rows]
     uint32_t n_rows, n_blocks, n_chunks, n_tokens, y_stride, token_groups;
-    uint32_t split;  // parts K is divided into (blockIdx.z)
+    uint32_t split;        // parts K is divided into (blockIdx.z)
+    uint32_t tile_tokens;  // tokens per CTA, a multiple of 16 up to kMaxTokens
     int store;
     // Grouped mode (mixture of experts), when offsets is set: blockIdx.z is an expert, whose weights
     // are rows [z * n_rows, (z + 1) * n_rows) of the stacked matrices, whose tokens are the entries
@@ -236,7 +237,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
     volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t tok0 = blockIdx.x * kMaxTokens, row0 = blockIdx.y * kRows;
+    const uint32_t tok0 = blockIdx.x * p.tile_tokens, row0 = blockIdx.y * kRows;
     uint32_t n_tokens = p.n_tokens, group0 = 0;
     uint64_t weight0 = 0;  // first block of this CTA's matrix in the stacked weights
     const uint32_t* out_rows = nullptr;
@@ -249,7 +250,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
         out_rows = p.entries + first;
     }
     const uint32_t left = n_tokens - tok0;
-    const uint32_t n_tile = left >= kMaxTokens ? kMaxTokens : ((left + 15u) & ~15u);  // the MMA's N
+    const uint32_t n_tile = left >= p.tile_tokens ? p.tile_tokens : ((left + 15u) & ~15u);  // the MMA's N
     // This CTA's share of K.
     const uint32_t per_part = (p.n_chunks + p.split - 1) / p.split;
     const uint32_t kc_begin = p.offsets ? 0 : blockIdx.z * per_part;
@@ -499,15 +500,41 @@ __global__ void __launch_bounds__(256) reduce_kernel(const float* __restrict__ p
     *out = sum;
 }
 
-// Parts to split K into: enough CTAs to fill the device, at least 512 columns each.
-uint32_t choose_split(uint32_t n_rows, uint32_t n_cols, uint32_t n_tokens, uint32_t y_stride) {
-    const uint32_t tiles = ((n_rows + kRows - 1) / kRows) * ((n_tokens + kMaxTokens - 1) / kMaxTokens);
-    const uint32_t chunks = n_cols / kChunkK;
-    if (n_rows % 4 != 0 || y_stride % 4 != 0) return 1;
-    uint32_t split = (uint32_t)sm_count() / (tiles ? tiles : 1);
-    if (split > kMaxSplit) split = kMaxSplit;
-    while (split > 1 && chunks / split < 8) --split;
-    return split < 1 ? 1 : split;
+// How a product is cut into CTAs: the token tile's width and the parts K is split into.
+struct Tiling {
+    uint32_t tile_tokens, split;
+};
+
+// Pick the tiling with the smallest modelled time. A CTA costs a fixed prologue and epilogue plus,
+// per 64-column chunk, a handshake and MMA time in proportion to the tile width; the launch takes
+// as many waves as its CTAs need on the device; a split adds its reduction launch. The constants
+// are rough fits to measurements on this kernel; only the ranking matters. Narrower token tiles
+// trade a little MMA efficiency for fuller waves (84 row tiles x 2 token tiles fill 1.14 waves;
+// x 3 fill 1.7 waves of tiles two thirds the size).
+Tiling choose_tiling(uint32_t n_rows, uint32_t n_cols, uint32_t n_tokens, uint32_t y_stride, int dual, bool may_split) {
+    const uint32_t row_tiles = (n_rows + kRows - 1) / kRows, chunks = n_cols / kChunkK, sms = (uint32_t)sm_count();
+    const bool can_split = may_split && dual == 1 && n_rows % 4 == 0 && y_stride % 4 == 0;
+    Tiling best{kMaxTokens, 1};
+    double best_cost = 1e30;
+    const uint32_t min_tiles = (n_tokens + kMaxTokens - 1) / kMaxTokens;
+    for (uint32_t token_tiles = min_tiles; token_tiles <= min_tiles + 6; ++token_tiles) {
+        uint32_t width = (((n_tokens + token_tiles - 1) / token_tiles) + 15u) & ~15u;
+        if (width < 64 && token_tiles > min_tiles) break;
+        const uint32_t tiles_needed = (n_tokens + width - 1) / width;
+        for (uint32_t split = 1; split <= (can_split ? kMaxSplit : 1u); ++split) {
+            if (split > 1 && chunks / split < 8) break;
+            const uint32_t ctas = row_tiles * tiles_needed * split;
+            const double waves = (double)((ctas + sms - 1) / sms);
+            const double per_chunk = 0.25 + 0.25 * dual * width / 256.0;  // microseconds
+            double cost = waves * (5.0 + ((chunks + split - 1) / split) * per_chunk);
+            if (split > 1) cost += 4.0 + 0.5 * split;
+            if (cost < best_cost) {
+                best_cost = cost;
+                best = Tiling{width, split};
+            }
+        }
+    }
+    return best;
 }
 
 bool umma_disabled() {
@@ -524,11 +551,11 @@ uint64_t matmul_pack_bytes(uint32_t n_tokens, uint32_t n_cols) { return (uint64_
 
 uint64_t matmul_scratch_bytes(const Mat& w, uint32_t n_tokens) {
     uint64_t pack = (matmul_pack_bytes(n_tokens, w.n_cols) + 255) & ~255ull;
-    uint32_t split = choose_split(w.n_rows, w.n_cols, n_tokens, w.n_rows);
+    uint32_t split = choose_tiling(w.n_rows, w.n_cols, n_tokens, w.n_rows, 1, true).split;
     return pack + (split > 1 ? (uint64_t)split * n_tokens * w.n_rows * 4 : 0);
 }
 
-int matmul_umma_launches(const Mat& w, uint32_t n_tokens) { return choose_split(w.n_rows, w.n_cols, n_tokens, w.n_rows) > 1 ? 3 : 2; }
+int matmul_umma_launches(const Mat& w, uint32_t n_tokens) { return choose_tiling(w.n_rows, w.n_cols, n_tokens, w.n_rows, 1, true).split > 1 ? 3 : 2; }
 
 bool matmul_umma_supported(const Mat& w, uint32_t n_tokens) {
     return !umma_disabled() && w.format == BC_Q4_0 && w.n_cols % kChunkK == 0 && w.n_cols > 0 && n_tokens >= 16;
@@ -557,7 +584,8 @@ cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, 
     cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), Shape<1>::kSmemBytes);
     if (err != cudaSuccess) return err;
     // The split must match matmul_scratch_bytes, which sized the scratch for a dense output.
-    const uint32_t split = y_stride == w.n_rows ? choose_split(w.n_rows, w.n_cols, n_tokens, y_stride) : 1;
+    const Tiling tiling = choose_tiling(w.n_rows, w.n_cols, n_tokens, y_stride, 1, y_stride == w.n_rows);
+    const uint32_t split = tiling.split;
     float* partial = reinterpret_cast<float*>(static_cast<char*>(const_cast<void*>(scratch)) +
                                               ((matmul_pack_bytes(n_tokens, w.n_cols) + 255) & ~255ull));
     UmmaParams p{};
@@ -572,8 +600,9 @@ cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, 
     p.y_stride = split > 1 ? w.n_rows : y_stride;
     p.token_groups = ((n_tokens + 15u) & ~15u) / 8;
     p.split = split;
+    p.tile_tokens = tiling.tile_tokens;
     p.store = split > 1 ? BC_STORE_OVERWRITE : store;
-    dim3 grid((n_tokens + kMaxTokens - 1) / kMaxTokens, (w.n_rows + kRows - 1) / kRows, split);
+    dim3 grid((n_tokens + tiling.tile_tokens - 1) / tiling.tile_tokens, (w.n_rows + kRows - 1) / kRows, split);
     matmul_umma_kernel<1><<<grid, Shape<1>::kThreads, Shape<1>::kSmemBytes, stream>>>(p);
     err = cudaGetLastError();
     if (err != cudaSuccess || split == 1) return err;
@@ -605,8 +634,9 @@ cudaError_t matmul_umma_swiglu(cudaStream_t stream, const Mat& gate, const Mat& 
     p.y_stride = y_stride;
     p.token_groups = ((n_tokens + 15u) & ~15u) / 8;
     p.split = 1;
+    p.tile_tokens = choose_tiling(gate.n_rows, gate.n_cols, n_tokens, y_stride, 2, false).tile_tokens;
     p.store = BC_STORE_OVERWRITE;
-    dim3 grid((n_tokens + kMaxTokens - 1) / kMaxTokens, (gate.n_rows + kRows - 1) / kRows, 1);
+    dim3 grid((n_tokens + p.tile_tokens - 1) / p.tile_tokens, (gate.n_rows + kRows - 1) / kRows, 1);
     matmul_umma_kernel<2><<<grid, Shape<2>::kThreads, Shape<2>::kSmemBytes, stream>>>(p);
     return cudaGetLastError();
 }
@@ -647,6 +677,7 @@ cudaError_t matmul_experts_umma(cudaStream_t stream, const Mat& w, const Mat* up
     p.y_stride = n_rows;
     p.token_groups = n_experts * cap_groups;
     p.split = 1;
+    p.tile_tokens = kMaxTokens;
     p.store = BC_STORE_OVERWRITE;
     p.offsets = offsets;
     p.entries = entries;
