@@ -85,15 +85,15 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 }
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // The same with a zero accumulator going in.
 __device__ __forceinline__ void mma_16816_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                 : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
@@ -299,7 +299,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
 
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t ring_base = smem_u32(ring), xs_base = smem_u32(xs);
     const uint32_t grp = warp / gs, rank = warp % gs;
     uint32_t taken = 0;  // chunks this warp has consumed
     bool dead = false;
@@ -336,29 +335,30 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
             }
             if (dead) continue;
             const uint32_t cb = min((uint32_t)kChunkBlocks, nb - chunk * kChunkBlocks);
-            // 32-bit shared-memory addresses of this lane's quants, scales and inputs.
-            uint32_t q_addr = ring_base + stage * kStageBytes + lane * 16;
-            uint32_t s_addr = ring_base + stage * kStageBytes + cb * 256 + g * 2;
-            uint32_t x_addr = xs_base + (chunk * kChunkBlocks * 8 + g * 4 + t) * 16;
+            // This lane's quants (one 16-byte group per block pair), scales and inputs. Plain loads,
+            // so the compiler can run the next pair's loads ahead of this pair's arithmetic. Lanes
+            // with g >= 2 hold columns of the product nobody reads; they repeat the reads of g & 1.
+            const uint8_t* slot = ring + stage * kStageBytes;
+            const uint4* quants = reinterpret_cast<const uint4*>(slot) + lane;
+            const __half* scales = reinterpret_cast<const __half*>(slot + cb * 256) + g;
+            const uint4* xq = xs + (size_t)chunk * kChunkBlocks * 8 + (g & 1) * 4 + t;
             float a0 = 0.f, a1 = 0.f;
-            for (uint32_t pair = 0; pair < cb / 2; ++pair, q_addr += 512, s_addr += 64, x_addr += 256) {
-                uint4 v;
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(q_addr));
+#pragma unroll 2
+            for (uint32_t pair = 0; pair < cb / 2; ++pair) {
+                const uint4 v = quants[pair * 32];
 #pragma unroll
                 for (int half_pair = 0; half_pair < 2; ++half_pair) {
                     uint32_t ha[4], hb[4];
                     unpack_word_half2(half_pair ? v.z : v.x, ha);  // row g
                     unpack_word_half2(half_pair ? v.w : v.y, hb);  // row g + 8
-                    uint4 xb = make_uint4(0, 0, 0, 0);
-                    if (g < 2) asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(xb.x), "=r"(xb.y), "=r"(xb.z), "=r"(xb.w) : "r"(x_addr + half_pair * 128));
+                    const uint4 xb = xq[(pair * 2 + half_pair) * 8];
                     float c[4];
                     mma_16816_zero(c, ha[0], hb[0], ha[1], hb[1], xb.x, xb.y);
                     mma_16816(c, ha[2], hb[2], ha[3], hb[3], xb.z, xb.w);
-                    uint16_t d0h, d1h;
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(d0h) : "r"(s_addr + half_pair * 32));
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(d1h) : "r"(s_addr + half_pair * 32 + 16));
-                    a0 = fmaf(c[0] + c[1], __half2float(__ushort_as_half(d0h)), a0);
-                    a1 = fmaf(c[2] + c[3], __half2float(__ushort_as_half(d1h)), a1);
+                    const float d0 = __half2float(scales[(pair * 2 + half_pair) * 16]);
+                    const float d1 = __half2float(scales[(pair * 2 + half_pair) * 16 + 8]);
+                    a0 = fmaf(c[0] + c[1], d0, a0);
+                    a1 = fmaf(c[2] + c[3], d1, a1);
                 }
             }
             __syncwarp();
