@@ -74,45 +74,81 @@ __global__ void __launch_bounds__(kRouteThreads) moe_route_kernel(RouteParams p)
     for (uint32_t e = warp; e < p.n_experts; e += kRouteWarps) {
         const float* row = p.router + (uint64_t)e * n_cols;
         double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
-        uint32_t c = lane;
-        for (; c + 96 < n_cols; c += 128) {
-            s0 += (double)row[c] * (double)xs[c];
-            s1 += (double)row[c + 32] * (double)xs[c + 32];
-            s2 += (double)row[c + 64] * (double)xs[c + 64];
-            s3 += (double)row[c + 96] * (double)xs[c + 96];
+        uint32_t c = 0;
+        if ((n_cols & 3u) == 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+            // Four 16-byte loads in flight per lane and trip, so a row costs a few round trips to L2, not one per element.
+            const float4* row4 = reinterpret_cast<const float4*>(row);
+            const float4* x4 = reinterpret_cast<const float4*>(xs);
+            const uint32_t n4 = n_cols / 4;
+            uint32_t i = lane;
+            for (; i + 96 < n4; i += 128) {
+                const float4 a = __ldg(row4 + i), b = __ldg(row4 + i + 32), cc = __ldg(row4 + i + 64), d = __ldg(row4 + i + 96);
+                const float4 xa = x4[i], xb = x4[i + 32], xc = x4[i + 64], xd = x4[i + 96];
+                s0 += (double)a.x * xa.x + (double)a.y * xa.y + (double)a.z * xa.z + (double)a.w * xa.w;
+                s1 += (double)b.x * xb.x + (double)b.y * xb.y + (double)b.z * xb.z + (double)b.w * xb.w;
+                s2 += (double)cc.x * xc.x + (double)cc.y * xc.y + (double)cc.z * xc.z + (double)cc.w * xc.w;
+                s3 += (double)d.x * xd.x + (double)d.y * xd.y + (double)d.z * xd.z + (double)d.w * xd.w;
+            }
+            for (; i < n4; i += 32) {
+                const float4 a = __ldg(row4 + i);
+                const float4 xa = x4[i];
+                s0 += (double)a.x * xa.x + (double)a.y * xa.y + (double)a.z * xa.z + (double)a.w * xa.w;
+            }
+            c = n_cols;
         }
-        for (; c < n_cols; c += 32) s0 += (double)row[c] * (double)xs[c];
+        for (c += lane; c < n_cols; c += 32) s0 += (double)row[c] * (double)xs[c];
         double sum = warp_sum_f64((s0 + s1) + (s2 + s3));
         if (lane == 0) scores[e] = 1.0f / (1.0f + expf(-(float)sum));
     }
     __syncthreads();
-    if (tid == 0) {
+    if (warp == 0) {
         // Top n_used by repeated argmax of score + bias, ties to the lower id; the weights are the
-        // unbiased scores over their f32 sum plus 1e-6 (lfm2.rs:698-708).
-        uint32_t picked[kMaxUsed];
-        bool taken[kMaxExperts];
-        for (uint32_t e = 0; e < p.n_experts; ++e) taken[e] = false;
-        float sum = 0.f;
+        // unbiased scores over their f32 sum plus 1e-6 (lfm2.rs:698-708). Lane l looks after experts
+        // l, l + 32, l + 64, l + 96; a round is a lane-local scan and a warp-wide compare.
+        float value[kMaxExperts / 32];
+        bool taken[kMaxExperts / 32];
+#pragma unroll
+        for (int k = 0; k < kMaxExperts / 32; ++k) {
+            const uint32_t e = lane + 32 * k;
+            value[k] = e < p.n_experts ? scores[e] + p.bias[e] : 0.f;
+            taken[k] = e >= p.n_experts;
+        }
+        uint32_t picked = 0;   // lane i < n_used ends up holding the i-th pick
+        float picked_score = 0.f, sum = 0.f;
         for (uint32_t i = 0; i < p.n_used; ++i) {
-            int best = -1;
             float best_value = 0.f;
-            for (uint32_t e = 0; e < p.n_experts; ++e) {
-                if (taken[e]) continue;
-                float v = scores[e] + p.bias[e];
-                if (best < 0 || v > best_value) {
-                    best = (int)e;
-                    best_value = v;
+            uint32_t best = 0xffffffffu;
+#pragma unroll
+            for (int k = 0; k < kMaxExperts / 32; ++k) {
+                if (!taken[k] && (best == 0xffffffffu || value[k] > best_value)) {
+                    best_value = value[k];
+                    best = lane + 32 * k;
                 }
             }
-            taken[best] = true;
-            picked[i] = (uint32_t)best;
-            sum += scores[best];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float other_value = __shfl_xor_sync(0xffffffffu, best_value, o);
+                const uint32_t other = __shfl_xor_sync(0xffffffffu, best, o);
+                if (other != 0xffffffffu && (best == 0xffffffffu || other_value > best_value || (other_value == best_value && other < best))) {
+                    best_value = other_value;
+                    best = other;
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kMaxExperts / 32; ++k)
+                if (best == lane + 32 * k) taken[k] = true;
+            const float score = scores[best];
+            sum += score;  // in pick order, as the scalar code adds them
+            if (lane == i) {
+                picked = best;
+                picked_score = score;
+            }
         }
-        float norm = sum + 1e-6f;
+        const float norm = sum + 1e-6f;
         uint32_t* route = p.route + (uint64_t)token * 2 * p.n_used;
-        for (uint32_t i = 0; i < p.n_used; ++i) {
-            route[i] = picked[i];
-            route[p.n_used + i] = __float_as_uint(scores[picked[i]] / norm);
+        if (lane < p.n_used) {
+            route[lane] = picked;
+            route[p.n_used + lane] = __float_as_uint(picked_score / norm);
         }
     }
 }
