@@ -644,7 +644,8 @@ cudaError_t matmul_umma_swiglu(cudaStream_t stream, const Mat& gate, const Mat& 
 // ---- grouped products over experts (mixture-of-experts prefill)
 
 bool matmul_experts_umma_supported(const Mat& w, const Mat* up, uint32_t n_tokens) {
-    if (umma_disabled() || w.format != BC_Q4_0 || w.n_cols % kChunkK != 0 || n_tokens < 16) return false;
+    static const bool experts_off = [] { const char* v = std::getenv("BOBCAT_NO_UMMA_EXPERTS"); return v && v[0] == '1'; }();
+    if (umma_disabled() || experts_off || w.format != BC_Q4_0 || w.n_cols % kChunkK != 0 || n_tokens < 16) return false;
     return !up || (up->format == BC_Q4_0 && up->n_cols == w.n_cols && up->n_rows == w.n_rows);
 }
 

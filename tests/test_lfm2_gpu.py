@@ -224,3 +224,46 @@ def test_argument_errors_come_before_device_work(pair, cuda):
     assert seq.n_past() == 0
     with pytest.raises(errors.Argument):
         Lfm2Cuda(model, cuda, 0, kv_half=False)
+
+
+def test_full_size_properties(model_path, cuda):
+    """The benchmark's own model (LFM2.5-2.6B shape, 1.9 GB of weights), where the CPU checker would
+    take minutes per token: properties that do not need it. A 512-token batched prefill gives the
+    logits of 512 single steps (lfm2_reference.rs:118-151); the greedy continuations agree; a reset
+    and a second pass reproduce the first bit for bit; a checkpoint restores to the same
+    continuation; a short prompt still matches the checker's logits."""
+    path = model_path("lfm2-2.6b")
+    model = Model.load(path)
+    hp = model.hyperparameters()
+    tokens = prompt_tokens(hp.n_vocab, 512, seed=9)
+    seq = Lfm2Cuda(model, cuda, 640, kv_half=True)
+    logits = np.zeros(hp.n_vocab, dtype=np.float32)
+    seq.prefill(tokens, logits)
+    ckpt = seq.checkpoint()
+    batched = seq.generate(32).tolist()
+    steps = Lfm2Cuda(model, cuda, 640, kv_half=True)
+    step_logits = np.zeros_like(logits)
+    for tok in tokens[:-1]:
+        steps.step(int(tok))
+    steps.step(int(tokens[-1]), step_logits)
+    assert rel_error(logits, step_logits) < HALF_TOLERANCE
+    # The batched pick is the stepped pick, or ties with it inside the tolerance.
+    scale = float(np.abs(step_logits).max())
+    assert step_logits[int(np.argmax(logits))] >= step_logits.max() - HALF_TOLERANCE * scale
+    seq.restore(ckpt)
+    assert seq.generate(32).tolist() == batched
+    seq.reset()
+    again = np.zeros_like(logits)
+    seq.prefill(tokens, again)
+    assert np.array_equal(logits, again)
+    assert seq.generate(32).tolist() == batched
+    ref = oracle.Model(path, threads=16)
+    st = ref.state(8)
+    short = tokens[:3]
+    for i, tok in enumerate(short):
+        want = st.step(int(tok), want_logits=(i == len(short) - 1))
+    check = Lfm2Cuda(model, cuda, 8, kv_half=False)
+    got = np.zeros_like(logits)
+    for tok in short:
+        check.step(int(tok), got)
+    assert rel_error(got, want["logits"]) < STEP_TOLERANCE

@@ -89,12 +89,12 @@ def test_group_is_a_stable_counting_sort(cuda):
 
 # (n_tokens, n_ff): widths that are multiples of 64 with at least 16 tokens send the grouped product to the
 # tensor-core kernel (fp16 operands, like the reference's Q4_0 prefill kernel); the rest stay on the f32 tile kernel.
-@pytest.mark.parametrize("n_tokens,n_ff", [(1, 96), (5, 96), (70, 96), (70, 128), (300, 192)])
-def test_expert_paths_match_the_scalar_block(cuda, n_tokens, n_ff):
+@pytest.mark.parametrize("n_tokens,n_ff,n_embd", [(1, 96, 128), (5, 96, 128), (70, 96, 128), (70, 128, 128), (300, 192, 128), (300, 256, 1024)])
+def test_expert_paths_match_the_scalar_block(cuda, n_tokens, n_ff, n_embd):
     """Decode (per-token expert matvecs) and prefill (group, grouped matmul, combine) both equal
     lfm2.rs:413-440 computed with the checker's f64 matvec."""
     rng = np.random.default_rng(n_tokens + 11)
-    n_embd, n_experts, n_used = 128, 8, 2
+    n_experts, n_used = 8, 2
     prefill_tolerance = 5e-3 if n_tokens >= 16 else 1e-5
     gate_raw, up_raw = random_q4_0(rng, n_experts * n_ff, n_embd), random_q4_0(rng, n_experts * n_ff, n_embd)
     down_raw = random_q4_0(rng, n_experts * n_embd, n_ff)
@@ -174,3 +174,37 @@ def test_moe_prefill_and_greedy_match(moe_pair, cuda):
     for tok in tokens:
         steps.step(int(tok), step_logits)
     assert rel_error(logits, step_logits) < 5e-3
+
+
+def test_moe_full_size_properties(model_path, cuda):
+    """The 8B-A1B shape (32 experts, 4 used, 4.6 GB of weights), without the CPU checker: a batched
+    prefill tracks single steps (loosely: a router near-tie that falls the other way for one token is a
+    legitimate difference between the two paths, lfm2_reference.rs:57-71), a second pass reproduces
+    the first bit for bit, and a checkpoint restores to the same continuation."""
+    path = model_path("lfm2moe-8b-a1b")
+    model = Model.load(path)
+    hp = model.hyperparameters()
+    tokens = np.random.default_rng(9).integers(0, hp.n_vocab, size=192).astype(np.uint32)
+    seq = Lfm2Cuda(model, cuda, 256, kv_half=True)
+    logits = np.zeros(hp.n_vocab, dtype=np.float32)
+    seq.prefill(tokens, logits)
+    ckpt = seq.checkpoint()
+    batched = seq.generate(16).tolist()
+    steps = Lfm2Cuda(model, cuda, 256, kv_half=True)
+    step_logits = np.zeros_like(logits)
+    for tok in tokens[:-1]:
+        steps.step(int(tok))
+    steps.step(int(tokens[-1]), step_logits)
+    # Batched rows reach the router with fp16-class differences from the stepped rows, and of the
+    # 4224 top-4-of-32 choices behind these logits a few percent are near-ties on random weights,
+    # so the two paths legitimately part ways for some tokens; the check is loose on purpose. The
+    # grouped products themselves are held to the scalar block in test_expert_paths_match_the_scalar_block.
+    assert rel_error(logits, step_logits) < 0.5
+    cosine = float(np.dot(logits, step_logits) / (np.linalg.norm(logits) * np.linalg.norm(step_logits)))
+    assert cosine > 0.97
+    seq.restore(ckpt)
+    assert seq.generate(16).tolist() == batched
+    seq.reset()
+    again = np.zeros_like(logits)
+    seq.prefill(tokens, again)
+    assert np.array_equal(logits, again)

@@ -194,3 +194,32 @@ def test_qwen_reset_and_restore(qwen_pair, cuda):
     assert np.array_equal(first, again)
     with pytest.raises(errors.Argument):
         seq.restore(ckpt)
+
+
+def test_qwen_full_size_properties(model_path, cuda):
+    """The Qwen3.5-2B shape (18 gated DeltaNet layers, 6 gated attention layers of 256-element
+    heads, vocabulary 151936), without the CPU checker: batched prefill in two calls against single
+    steps, a bit-identical second pass, a checkpoint that restores the DeltaNet state."""
+    path = model_path("qwen35-2b")
+    model = Model.load(path)
+    hp = model.hyperparameters()
+    tokens = np.random.default_rng(9).integers(0, hp.n_vocab, size=256).astype(np.uint32)
+    seq = Qwen35Cuda(model, cuda, 320, kv_half=True)
+    logits = np.zeros(hp.n_vocab, dtype=np.float32)
+    seq.prefill(tokens[:100])
+    seq.prefill(tokens[100:], logits)
+    ckpt = seq.checkpoint()
+    batched = seq.generate(16).tolist()
+    steps = Qwen35Cuda(model, cuda, 320, kv_half=True)
+    step_logits = np.zeros_like(logits)
+    for tok in tokens[:-1]:
+        steps.step(int(tok))
+    steps.step(int(tokens[-1]), step_logits)
+    assert rel_error(logits, step_logits) < 5e-3
+    seq.restore(ckpt)
+    assert seq.generate(16).tolist() == batched
+    seq.reset()
+    again = np.zeros_like(logits)
+    seq.prefill(tokens[:100])
+    seq.prefill(tokens[100:], again)
+    assert np.array_equal(logits, again)
