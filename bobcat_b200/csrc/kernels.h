@@ -151,6 +151,12 @@ cudaError_t gdn_gates(cudaStream_t stream, float* beta, float* alpha, const floa
 // The gated delta rule over n_tokens; state [n_v_heads][k_dim][v_dim]; `normalize` L2-normalises q and k.
 cudaError_t gdn_recurrence(cudaStream_t stream, const float* qkv, const float* beta, const float* decay, float* state, float* out,
                            uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t n_tokens, bool normalize);
+// One token through the whole mixer after its projections (conv with history shift, gates, L2
+// norms, delta rule, gated norm) in one launch; gdn_step_supported says whether the shape fits.
+bool gdn_step_supported(uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t kernel);
+cudaError_t gdn_step(cudaStream_t stream, const float* qkv, const float* taps, float* history, const float* beta, const float* alpha,
+                     const float* a, const float* dt_bias, float* state, const float* z, const float* norm_weight, float* out,
+                     uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t kernel, float eps);
 // x = RMSNorm(x) * weight * silu(z) per row of v_dim.
 cudaError_t gdn_gated_norm(cudaStream_t stream, float* x, const float* z, const float* weight, uint32_t v_dim, uint32_t n_rows,
                            float eps);

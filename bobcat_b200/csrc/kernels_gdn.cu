@@ -233,6 +233,152 @@ __global__ void gdn_gated_norm_kernel(float* __restrict__ x, const float* __rest
     }
 }
 
+// ---- One token through a whole DeltaNet mixer in one launch (decode): the causal convolution
+// with SiLU and its history shift, the gates, the L2 norms of q and k, the delta rule on the state
+// and the gated RMSNorm of the output, i.e. gdn_conv + gdn_gates + gdn_recurrence + gdn_gated_norm
+// for n_tokens == 1 (qwen35.rs:430-516). One CTA per key head; it serves the value heads that read
+// that key head (h = key_head + m * n_k_heads), one thread per state column of each, so the
+// convolution of q and k happens once and nothing races on its history.
+struct StepParams {
+    const float* qkv;      // [conv_dim] projections before the convolution: q heads, k heads, v heads
+    const float* taps;     // [conv_dim][kernel]
+    float* history;        // [conv_dim][kernel - 1]
+    const float* beta;     // [n_v_heads] before the sigmoid
+    const float* alpha;    // [n_v_heads] before the softplus
+    const float* a;        // [n_v_heads]
+    const float* dt_bias;  // [n_v_heads]
+    float* state;          // [n_v_heads][k_dim][v_dim]
+    const float* z;        // [n_v_heads * v_dim]
+    const float* norm_weight;  // [v_dim]
+    float* out;            // [n_v_heads * v_dim]
+    uint32_t n_k_heads, n_v_heads, k_dim, v_dim, kernel;
+    float eps;
+};
+
+// The convolution of one channel for one token, and the history shift (same order of additions as gdn_conv).
+__device__ __forceinline__ float conv_step(const StepParams& p, uint32_t channel) {
+    const uint32_t H = p.kernel - 1;
+    const float* tap = p.taps + (uint64_t)channel * p.kernel;
+    float* hist = p.history + (uint64_t)channel * H;
+    const float input = p.qkv[channel];
+    float sum = tap[H] * input;
+    float past[7];
+    for (uint32_t i = 0; i < H; ++i) {
+        past[i] = hist[i];
+        sum += tap[i] * past[i];
+    }
+    for (uint32_t i = 0; i + 1 < H; ++i) hist[i] = past[i + 1];
+    hist[H - 1] = input;
+    return sum / (1.f + expf(-sum));
+}
+
+constexpr int kStepParts = 4;  // threads that share a state column, each holding a quarter of its rows
+
+template <int KDIM>
+__global__ void __launch_bounds__(1024) gdn_step_kernel(StepParams p) {
+    // Thread (part, m, j): rows [part * KDIM / 4, (part + 1) * KDIM / 4) of column j of the state of
+    // value head key_head + m * n_k_heads. The quarter column is loaded into registers first of
+    // all, so that read overlaps the convolution; the quarters' partial dot products meet in shared memory.
+    constexpr int kRows = KDIM / kStepParts;
+    __shared__ __align__(16) float qs[KDIM], ks[KDIM];
+    __shared__ float scratch[96];
+    __shared__ float r_part[kStepParts][256], o_part[kStepParts][256], o_full[256];
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t key_head = blockIdx.x, tid = threadIdx.x, vd = p.v_dim;
+    const uint32_t lane = tid & 31, warp = tid >> 5;
+    const uint32_t key_dim = p.n_k_heads * KDIM, ratio = p.n_v_heads / p.n_k_heads;
+    const uint32_t column_id = tid % (ratio * vd), part = tid / (ratio * vd);  // blockDim.x == kStepParts * ratio * v_dim
+    const uint32_t m = column_id / vd, j = column_id % vd, head = key_head + m * p.n_k_heads;
+    float* column = p.state + (uint64_t)head * KDIM * vd + (uint64_t)(part * kRows) * vd + j;
+    float S[kRows];
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) S[i] = column[(uint64_t)i * vd];
+    // q and k of this key head: threads below KDIM convolve one channel of each.
+    float qv = 0.f, kv = 0.f;
+    if (tid < KDIM) {
+        qv = conv_step(p, key_head * KDIM + tid);
+        kv = conv_step(p, key_dim + key_head * KDIM + tid);
+    }
+    // l2_normalize (qwen35.rs:762-768): f32 sum of squares, x *= scale / sqrt(sum + 1e-6).
+    float q2 = warp_sum(qv * qv), k2 = warp_sum(kv * kv);
+    if (lane == 0) {
+        scratch[warp] = q2;
+        scratch[32 + warp] = k2;
+    }
+    __syncthreads();
+    if (tid < KDIM) {
+        float qsum = 0.f, ksum = 0.f;
+        for (uint32_t w = 0; w < (KDIM + 31) / 32; ++w) {
+            qsum += scratch[w];
+            ksum += scratch[32 + w];
+        }
+        qs[tid] = qv * ((1.0f / sqrtf((float)KDIM)) / sqrtf(qsum + 1e-6f));
+        ks[tid] = kv * (1.0f / sqrtf(ksum + 1e-6f));
+    }
+    // The column's element of v (convolved once, by the part-0 thread) and the head's gates.
+    float v = 0.f;
+    if (part == 0) v = conv_step(p, 2 * key_dim + head * vd + j);
+    // beta = sigmoid(beta); decay = exp(a * softplus(alpha + dt_bias)), softplus(x) = x above 20.
+    const float braw = p.beta[head], araw = p.alpha[head] + p.dt_bias[head];
+    const float beta = 1.f / (1.f + expf(-braw));
+    const float decay = expf(p.a[head] * (araw > 20.f ? araw : log1pf(expf(araw))));
+    __syncthreads();
+    const float4* k4 = reinterpret_cast<const float4*>(ks + part * kRows);
+    const float4* q4 = reinterpret_cast<const float4*>(qs + part * kRows);
+    float r0 = 0.f, r1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kRows / 4; ++i) {
+        const float4 kk = k4[i];
+        S[4 * i] *= decay;
+        S[4 * i + 1] *= decay;
+        S[4 * i + 2] *= decay;
+        S[4 * i + 3] *= decay;
+        r0 += S[4 * i] * kk.x + S[4 * i + 2] * kk.z;
+        r1 += S[4 * i + 1] * kk.y + S[4 * i + 3] * kk.w;
+    }
+    r_part[part][column_id] = r0 + r1;
+    if (part == 0) o_full[column_id] = v;  // parks v where every part can read it
+    __syncthreads();
+    float r = 0.f;
+#pragma unroll
+    for (int q = 0; q < kStepParts; ++q) r += r_part[q][column_id];  // every part adds them in the same order
+    const float delta = (o_full[column_id] - r) * beta;
+    float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kRows / 4; ++i) {
+        const float4 kk = k4[i], qq = q4[i];
+        S[4 * i] += kk.x * delta;
+        S[4 * i + 1] += kk.y * delta;
+        S[4 * i + 2] += kk.z * delta;
+        S[4 * i + 3] += kk.w * delta;
+        o0 += S[4 * i] * qq.x + S[4 * i + 2] * qq.z;
+        o1 += S[4 * i + 1] * qq.y + S[4 * i + 3] * qq.w;
+    }
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) column[(uint64_t)i * vd] = S[i];
+    o_part[part][column_id] = o0 + o1;
+    __syncthreads();
+    // Gated RMSNorm over each value head's v_dim outputs, by the part-0 threads (v_dim is a multiple
+    // of 32, so a warp belongs to one head): out = weight * (o * scale) * silu(z).
+    float o = 0.f;
+    if (part == 0) {
+#pragma unroll
+        for (int q = 0; q < kStepParts; ++q) o += o_part[q][column_id];
+    }
+    const float sq = warp_sum(o * o);
+    if (lane == 0) scratch[64 + warp] = sq;
+    __syncthreads();
+    if (part == 0) {
+        const uint32_t warps_per_head = vd / 32, first = m * warps_per_head;
+        float sumsq = 0.f;
+        for (uint32_t w = 0; w < warps_per_head; ++w) sumsq += scratch[64 + first + w];
+        const float scale = rsqrtf(sumsq / (float)vd + p.eps);
+        const float g = p.z[head * vd + j];
+        p.out[head * vd + j] = p.norm_weight[j] * (o * scale) * (g / (1.f + expf(-g)));
+    }
+}
+
 // out[t][h][d] *= sigmoid(gate) with the gate read from the interleaved q projection:
 // q_gate[t][h][head_dim + d] of [n_tokens][n_heads][2 * head_dim] (qwen35.rs:383-390, :422-424).
 __global__ void attention_gate_kernel(float* __restrict__ out, const float* __restrict__ q_gate, uint32_t n_heads, uint32_t head_dim,
@@ -285,6 +431,24 @@ cudaError_t gdn_recurrence(cudaStream_t stream, const float* qkv, const float* b
     const void* kernel = k_dim == 32 ? (const void*)gdn_recurrence_kernel<32> : k_dim == 64 ? (const void*)gdn_recurrence_kernel<64>
                        : k_dim == 96 ? (const void*)gdn_recurrence_kernel<96> : (const void*)gdn_recurrence_kernel<128>;
     return launch_kernel(kernel, dim3(n_v_heads), dim3(threads), 0, stream, args);
+}
+
+bool gdn_step_supported(uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t kernel) {
+    if (n_k_heads == 0 || n_v_heads % n_k_heads != 0 || kernel < 2 || kernel > 8) return false;
+    if (k_dim != 32 && k_dim != 64 && k_dim != 96 && k_dim != 128) return false;
+    const uint32_t columns = (n_v_heads / n_k_heads) * v_dim;  // state columns a CTA serves
+    return v_dim % 32 == 0 && columns <= 256 && kStepParts * columns >= k_dim;
+}
+
+cudaError_t gdn_step(cudaStream_t stream, const float* qkv, const float* taps, float* history, const float* beta, const float* alpha,
+                     const float* a, const float* dt_bias, float* state, const float* z, const float* norm_weight, float* out,
+                     uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t kernel, float eps) {
+    StepParams p{qkv, taps, history, beta, alpha, a, dt_bias, state, z, norm_weight, out, n_k_heads, n_v_heads, k_dim, v_dim, kernel, eps};
+    void* args[] = {&p};
+    const uint32_t threads = kStepParts * (n_v_heads / n_k_heads) * v_dim;
+    const void* kernel_fn = k_dim == 32 ? (const void*)gdn_step_kernel<32> : k_dim == 64 ? (const void*)gdn_step_kernel<64>
+                          : k_dim == 96 ? (const void*)gdn_step_kernel<96> : (const void*)gdn_step_kernel<128>;
+    return launch_kernel(kernel_fn, dim3(n_k_heads), dim3(threads), 0, stream, args);
 }
 
 cudaError_t gdn_gated_norm(cudaStream_t stream, float* x, const float* z, const float* weight, uint32_t v_dim, uint32_t n_rows,

@@ -290,6 +290,15 @@ struct Recorder {
         const uint32_t K = hp.conv_kernel;
         float* history = s.conv_state + (size_t)cache_index * conv_dim() * (K - 1);
         float* state = s.delta_state + (size_t)cache_index * hp.n_v_heads * hp.k_head_dim * hp.v_head_dim;
+        if (n == 1 && k::gdn_step_supported(hp.n_k_heads, hp.n_v_heads, hp.k_head_dim, hp.v_head_dim, K)) {
+            // A decode step: the whole tail in one launch.
+            uint64_t step_bytes = (uint64_t)hp.n_v_heads * hp.k_head_dim * hp.v_head_dim * 4 * 2;
+            run("gdn_step", 1, value_dim(), step_bytes, 1, [&] {
+                return k::gdn_step(stream, s.gdn_qkv, D.conv1d, history, s.gdn_beta, s.gdn_alpha, D.a, D.dt_bias, state, s.gdn_z, D.ssm_norm, s.gdn_out,
+                                   hp.n_k_heads, hp.n_v_heads, hp.k_head_dim, hp.v_head_dim, K, hp.norm_eps);
+            });
+            return;
+        }
         run("gdn_conv", n, conv_dim(), 0, k::gdn_conv_launches(n), [&] { return k::gdn_conv(stream, s.gdn_qkv, D.conv1d, history, s.gdn_conv_out, conv_dim(), K, n); });
         run("gdn_gates", n, hp.n_v_heads, 0, 1, [&] { return k::gdn_gates(stream, s.gdn_beta, s.gdn_alpha, D.a, D.dt_bias, hp.n_v_heads, n); });
         uint64_t state_bytes = (uint64_t)hp.n_v_heads * hp.k_head_dim * hp.v_head_dim * 4 * 2;
