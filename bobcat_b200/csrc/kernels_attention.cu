@@ -6,7 +6,9 @@
 // head are scored together, so each key and value row is read from the cache once per group.
 // Each CTA writes, per query head, the chunk's score maximum, the sum of exponentials and the
 // unnormalised weighted value sum. Combine pass: one CTA per (query head, query) rescales the
-// chunk partials by exp(max_c - max) and divides.
+// chunk partials by exp(max_c - max) and divides. A decode step over a half-precision cache takes
+// attention_decode_kernel for its chunk pass: the same partials from 16-byte cache loads with the
+// group's running sums in registers.
 
 #include "common.h"
 #include "device_utils.cuh"
@@ -147,6 +149,179 @@ __global__ void __launch_bounds__(kChunkThreads) attention_chunk_kernel(ChunkPar
     }
 }
 
+// Decode form of the chunk pass for a half-precision cache: the same partials as
+// attention_chunk_kernel, computed with 16-byte cache loads. A lane owns 8 consecutive elements of a
+// row, HD / 8 lanes cover a row and a warp reads 256 / HD rows with one load per lane; the query
+// heads of the group and their running (max, sum, weighted values) stay in registers. The rows of
+// a warp are merged with shuffles and the four warps through shared memory.
+constexpr int kDecodeThreads = 128;
+
+__device__ __forceinline__ void unpack_row(const uint4& raw, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 v = __half22float2(h[i]);
+        f[2 * i] = v.x;
+        f[2 * i + 1] = v.y;
+    }
+}
+
+template <int HD, int GROUP>
+__global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(ChunkParams p) {
+    constexpr int kLanesPerRow = HD / 8, kRowsPerLoad = 32 / kLanesPerRow, kWarps = kDecodeThreads / 32;
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t kv_head = blockIdx.x, chunk = blockIdx.y, qi = blockIdx.z;
+    const uint32_t query = p.query0 + qi;
+    const uint32_t pos = p.first_pos + (p.pos_ptr ? *p.pos_ptr : 0u) + query;
+    const uint32_t start = chunk * p.chunk;
+    if (start > pos) return;
+    const uint32_t count = min(p.chunk, pos + 1 - start);
+    const uint32_t group = p.n_heads / p.n_kv_heads, kv_dim = p.n_kv_heads * HD;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sub = lane / kLanesPerRow, d0 = (lane % kLanesPerRow) * 8;
+
+    __shared__ float merged[kWarps][GROUP][HD + 2];
+
+    const __half* kc = static_cast<const __half*>(p.k_cache) + (uint64_t)start * kv_dim + (uint64_t)kv_head * HD + d0;
+    const __half* vc = static_cast<const __half*>(p.v_cache) + (uint64_t)start * kv_dim + (uint64_t)kv_head * HD + d0;
+
+    // The first row's loads go out before the query arrives. `base` is the same for the whole
+    // warp, so the shuffles below run with every lane present; rows past the chunk's end only skip
+    // the update.
+    uint32_t base = warp * kRowsPerLoad;
+    uint4 k_raw = make_uint4(0, 0, 0, 0), v_raw = make_uint4(0, 0, 0, 0);
+    if (base + sub < count) {
+        k_raw = __ldg(reinterpret_cast<const uint4*>(kc + (uint64_t)(base + sub) * kv_dim));
+        v_raw = __ldg(reinterpret_cast<const uint4*>(vc + (uint64_t)(base + sub) * kv_dim));
+    }
+
+    const float scale = 1.0f / sqrtf((float)HD);
+    float qv[GROUP][8], acc[GROUP][8], top[GROUP], sum[GROUP];
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+        top[g] = -INFINITY;
+        sum[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+        if (g < (int)group) {
+            const float* qp = p.q + (uint64_t)query * p.q_stride + (uint64_t)(kv_head * group + g) * p.q_head_stride + d0;
+            float4 a = *reinterpret_cast<const float4*>(qp), b = *reinterpret_cast<const float4*>(qp + 4);
+            qv[g][0] = a.x * scale; qv[g][1] = a.y * scale; qv[g][2] = a.z * scale; qv[g][3] = a.w * scale;
+            qv[g][4] = b.x * scale; qv[g][5] = b.y * scale; qv[g][6] = b.z * scale; qv[g][7] = b.w * scale;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qv[g][i] = 0.f;
+        }
+    }
+
+    while (base < count) {
+        float kf[8], vf[8];
+        unpack_row(k_raw, kf);
+        unpack_row(v_raw, vf);
+        const bool valid = base + sub < count;
+        const uint32_t next = base + kWarps * kRowsPerLoad;
+        if (next + sub < count) {
+            k_raw = __ldg(reinterpret_cast<const uint4*>(kc + (uint64_t)(next + sub) * kv_dim));
+            v_raw = __ldg(reinterpret_cast<const uint4*>(vc + (uint64_t)(next + sub) * kv_dim));
+        }
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) {
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dot += kf[i] * qv[g][i];
+#pragma unroll
+            for (int o = 1; o < kLanesPerRow; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            if (valid) {
+                const float m = fmaxf(top[g], dot);
+                const float keep = expf(top[g] - m), w = expf(dot - m);  // exp(-inf) = 0 on the first row
+                sum[g] = sum[g] * keep + w;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * keep + w * vf[i];
+                top[g] = m;
+            }
+        }
+        base = next;
+    }
+
+    // Merge the rows of the warp: lanes that hold the same elements of different rows.
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+#pragma unroll
+        for (int o = kLanesPerRow; o < 32; o <<= 1) {
+            const float other_top = __shfl_xor_sync(0xffffffffu, top[g], o);
+            const float other_sum = __shfl_xor_sync(0xffffffffu, sum[g], o);
+            const float m = fmaxf(top[g], other_top);
+            const float mine = top[g] == -INFINITY ? 0.f : expf(top[g] - m);
+            const float theirs = other_top == -INFINITY ? 0.f : expf(other_top - m);
+            sum[g] = sum[g] * mine + other_sum * theirs;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float other = __shfl_xor_sync(0xffffffffu, acc[g][i], o);
+                acc[g][i] = acc[g][i] * mine + other * theirs;
+            }
+            top[g] = m;
+        }
+        if (sub == 0 && g < (int)group) {
+            float* out = merged[warp][g];
+            if (d0 == 0) {
+                out[0] = top[g];
+                out[1] = sum[g];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) out[2 + d0 + i] = acc[g][i];
+        }
+    }
+    __syncthreads();
+
+    // Merge the warps and write the chunk's partial.
+    for (uint32_t i = tid; i < group * HD; i += kDecodeThreads) {
+        const uint32_t g = i / HD, d = i % HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) m = fmaxf(m, merged[w][g][0]);
+        float total = 0.f, weight = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float t = merged[w][g][0];
+            const float f = t == -INFINITY ? 0.f : expf(t - m);
+            weight += merged[w][g][1] * f;
+            total += merged[w][g][2 + d] * f;
+        }
+        const uint32_t head = kv_head * group + g;
+        float* out = p.scratch + (((uint64_t)qi * p.n_heads + head) * p.max_chunks + chunk) * (HD + 2);
+        out[2 + d] = total;
+        if (d == 0) {
+            out[0] = m;
+            out[1] = weight;
+        }
+    }
+}
+
+template <int HD>
+const void* decode_kernel_for(uint32_t group) {
+    if (group <= 2) return (const void*)attention_decode_kernel<HD, 2>;
+    if (group <= 4) return (const void*)attention_decode_kernel<HD, 4>;
+    return (const void*)attention_decode_kernel<HD, 8>;
+}
+
+// The decode form covers a half-precision cache, heads of 64, 128 or 256 elements and 16-byte aligned
+// query rows; everything else takes the general kernel.
+bool decode_shape(bool kv_half, const AttentionShape& s) {
+    return kv_half && s.n_queries <= (uint32_t)kDecodeQueries && s.q_stride % 4 == 0 && s.q_head_stride % 4 == 0 &&
+           (s.head_dim == 64 || s.head_dim == 128 || s.head_dim == 256);
+}
+
+const void* decode_kernel(bool kv_half, const AttentionShape& s, const float* q, const void* k_cache, const void* v_cache) {
+    if (!decode_shape(kv_half, s) || ((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16 != 0) return nullptr;
+    const uint32_t group = s.n_heads / s.n_kv_heads;
+    switch (s.head_dim) {
+        case 64: return decode_kernel_for<64>(group);
+        case 128: return decode_kernel_for<128>(group);
+        default: return decode_kernel_for<256>(group);
+    }
+}
+
 struct CombineParams {
     const float* scratch;
     float* out;
@@ -202,7 +377,8 @@ uint64_t attention_scratch_floats(uint32_t n_heads, uint32_t head_dim, uint32_t 
 }
 
 int attention_launches(bool kv_half, const AttentionShape& s) {
-    return attention_flash_supported(kv_half, s) ? 1 : 2 * (int)((s.n_queries + kQueryBatch - 1) / kQueryBatch);
+    if (attention_flash_supported(kv_half, s)) return 1;
+    return 2 * (int)((s.n_queries + kQueryBatch - 1) / kQueryBatch);
 }
 
 cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, const void* v_cache, bool kv_half,
@@ -226,8 +402,13 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
         // With a run-time position the grid covers every chunk of the context; CTAs past the position exit at once.
         dim3 grid(s.n_kv_heads, s.pos_ptr ? max_chunks : last_pos / chunk + 1, nq);
         void* chunk_args[] = {&cp};
-        const void* chunk_kernel = kv_half ? (const void*)attention_chunk_kernel<__half> : (const void*)attention_chunk_kernel<float>;
-        if ((e = launch_kernel(chunk_kernel, grid, dim3(kChunkThreads), smem, stream, chunk_args)) != cudaSuccess) return e;
+        const void* fast = decode_kernel(kv_half, s, q, k_cache, v_cache);
+        if (fast) {
+            if ((e = launch_kernel(fast, grid, dim3(kDecodeThreads), 0, stream, chunk_args)) != cudaSuccess) return e;
+        } else {
+            const void* chunk_kernel = kv_half ? (const void*)attention_chunk_kernel<__half> : (const void*)attention_chunk_kernel<float>;
+            if ((e = launch_kernel(chunk_kernel, grid, dim3(kChunkThreads), smem, stream, chunk_args)) != cudaSuccess) return e;
+        }
         CombineParams mp{scratch, out, s.n_heads, s.head_dim, s.first_pos, q0, max_chunks, s.pos_ptr, chunk};
         void* combine_args[] = {&mp};
         if ((e = launch_kernel((const void*)attention_combine_kernel, dim3(s.n_heads, nq), dim3(s.head_dim), 0, stream, combine_args)) != cudaSuccess) return e;

@@ -298,9 +298,9 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
         value = best_value[lane];
         index = best_index[lane];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, value, o);
-            uint32_t oi = __shfl_xor_sync(0xffffffffu, index, o);
+        for (int step = 16; step > 0; step >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, value, step);
+            uint32_t oi = __shfl_xor_sync(0xffffffffu, index, step);
             if (better(ov, oi, value, index)) {
                 value = ov;
                 index = oi;

@@ -17,7 +17,6 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxExperts = 128;
-constexpr int kMaxUsed = 8;
 
 __device__ __forceinline__ double warp_sum_f64(double v) {
 #pragma unroll

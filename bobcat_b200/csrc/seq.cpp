@@ -115,7 +115,6 @@ struct Recorder {
     // Norm and rotation of q and k, cache stores, attention over positions [0, pos + n).
     void rotate_and_attend(const DeviceLayer& D, uint32_t cache_index, uint32_t pos, uint32_t n, uint32_t q_stride, uint32_t q_head_stride) {
         size_t slot = layer_base(cache_index) + (size_t)pos * kv_dim();
-        uint32_t q_dim = hp.n_heads * hp.head_dim;
         run("norm_rope", hp.n_heads * n, hp.head_dim, 0, 1, [&] {
             return k::norm_rope(stream, s.q, s.q, false, D.q_norm, hp.n_heads, hp.head_dim, q_head_stride, hp.n_rot, pos, n, q_stride, q_stride,
                                 hp.rope_theta, hp.norm_eps);
@@ -130,7 +129,6 @@ struct Recorder {
         k::AttentionShape shape{hp.n_heads, hp.n_kv_heads, hp.head_dim, pos, n, s.n_ctx, q_stride, q_head_stride};
         int kernels = k::attention_launches(s.kv_half, shape);
         uint64_t kv_bytes = (uint64_t)(pos + n) * kv_dim() * kv_element_bytes() * 2;
-        (void)q_dim;
         run("attention", n, pos + n, kv_bytes, kernels, [&] {
             return k::attention(stream, s.q, cache_at(s.k_cache, layer_base(cache_index)), cache_at(s.v_cache, layer_base(cache_index)), s.kv_half,
                                 s.scores, s.attn, shape);
@@ -151,7 +149,7 @@ struct Recorder {
         run("rope_store", hp.n_heads + 2 * hp.n_kv_heads, hp.head_dim, 0, 1, [&] { return k::rope_store(stream, rs, p); });
         k::AttentionShape shape{hp.n_heads, hp.n_kv_heads, hp.head_dim, p.value, 1, s.n_ctx, q_stride, q_head_stride, p.ptr};
         uint64_t kv_bytes = (uint64_t)(pos + 1) * kv_dim() * kv_element_bytes() * 2;
-        run("attention", 1, pos + 1, kv_bytes, 2, [&] {
+        run("attention", 1, pos + 1, kv_bytes, k::attention_launches(s.kv_half, shape), [&] {
             return k::attention(stream, s.q, cache_at(s.k_cache, layer_base(cache_index)), cache_at(s.v_cache, layer_base(cache_index)), s.kv_half,
                                 s.scores, s.attn, shape);
         });
@@ -968,9 +966,7 @@ bc_status bc_seq_read_state(bc_seq* s, int32_t which, uint32_t layer, float* out
             BC_CUDA(cudaMemcpyAsync(halfs.data(), cache + (size_t)layer * count * 2, count * 2, cudaMemcpyDeviceToHost, stream));
             BC_CUDA(cudaStreamSynchronize(stream));
             for (size_t i = 0; i < count; ++i) {
-                __half h;
-                std::memcpy(&h, &halfs[i], 2);
-                out[i] = __half2float(h);
+                out[i] = __half2float(__half(__half_raw{halfs[i]}));
             }
         } else {
             BC_CUDA(cudaMemcpyAsync(out, cache + (size_t)layer * count * 4, count * 4, cudaMemcpyDeviceToHost, stream));

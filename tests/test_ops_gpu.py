@@ -178,7 +178,8 @@ def test_norm_rope_matches_scalar(cuda, head_dim, n_rot, dst_half):
 
 # (first_pos, n_queries, n_heads, n_kv_heads, head_dim): crates/bobcat/tests/metal_attention.rs:19-27
 ATTENTION_CASES = [(0, 1, 4, 2, 64), (5, 1, 4, 2, 64), (63, 3, 8, 2, 64), (100, 70, 4, 4, 32), (0, 130, 4, 1, 64), (37, 2, 2, 1, 256), (700, 1, 32, 8, 64),
-                   (0, 512, 8, 2, 64), (100, 70, 8, 2, 64), (3, 33, 4, 2, 64), (61, 200, 4, 4, 64)]
+                   (0, 512, 8, 2, 64), (100, 70, 8, 2, 64), (3, 33, 4, 2, 64), (61, 200, 4, 4, 64), (45, 1, 8, 1, 128), (130, 4, 16, 4, 128),
+                   (15, 2, 6, 2, 64), (300, 1, 4, 4, 256)]
 
 
 def on_flash_kernel(kv_half, n_q, hd):
