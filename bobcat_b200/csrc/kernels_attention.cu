@@ -330,39 +330,57 @@ struct CombineParams {
     uint32_t chunk;
 };
 
-// grid (n_heads, queries in batch), head_dim threads. The threads first share out the chunks'
-// maxima and sums (so the exponentials are computed once, in parallel), then each thread adds up
-// its element over the chunks with independent loads.
+// grid (n_heads, queries in batch), kCombineParts * head_dim threads. The threads first share out
+// the chunks' maxima and sums (so the exponentials are computed once, in parallel); then part r
+// of the threads adds up every kCombineParts-th chunk, each thread one element of the head with
+// independent loads, and the parts are added in order.
+constexpr int kCombineParts = 4;
+constexpr int kCombineSlice = 512;  // chunks whose weights shared memory holds at a time
+
 __global__ void attention_combine_kernel(CombineParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float weights[512];  // exp(max_c - max) of a slice of chunks
-    __shared__ float scratch[32];
-    const uint32_t head = blockIdx.x, qi = blockIdx.y, d = threadIdx.x;
+    __shared__ float weights[kCombineSlice];  // exp(max_c - max) of a slice of chunks
+    __shared__ float across[32];
+    extern __shared__ float parts[];           // [kCombineParts][head_dim]
+    const uint32_t head = blockIdx.x, qi = blockIdx.y, tid = threadIdx.x, hd = p.head_dim;
+    const uint32_t d = tid % hd, part = tid / hd, n_warps = blockDim.x / 32;
     const uint32_t query = p.query0 + qi, pos = p.first_pos + (p.pos_ptr ? *p.pos_ptr : 0u) + query;
-    const uint32_t n_chunks = pos / p.chunk + 1, hd = p.head_dim;
+    const uint32_t n_chunks = pos / p.chunk + 1;
     const float* base = p.scratch + ((uint64_t)qi * p.n_heads + head) * p.max_chunks * (hd + 2);
     float m = -INFINITY;
-    for (uint32_t c = d; c < n_chunks; c += blockDim.x) m = fmaxf(m, base[(uint64_t)c * (hd + 2)]);
+    for (uint32_t c = tid; c < n_chunks; c += blockDim.x) m = fmaxf(m, base[(uint64_t)c * (hd + 2)]);
     m = warp_max(m);
-    if ((d & 31) == 0) scratch[d >> 5] = m;
+    if ((tid & 31) == 0) across[tid >> 5] = m;
     __syncthreads();
-    m = scratch[0];
-    for (uint32_t w = 1; w < (blockDim.x + 31) / 32; ++w) m = fmaxf(m, scratch[w]);
+    m = across[0];
+    for (uint32_t w = 1; w < n_warps; ++w) m = fmaxf(m, across[w]);
     float sum = 0.f, acc = 0.f;
-    for (uint32_t c0 = 0; c0 < n_chunks; c0 += 512) {
-        const uint32_t count = min(512u, n_chunks - c0);
+    for (uint32_t c0 = 0; c0 < n_chunks; c0 += kCombineSlice) {
+        const uint32_t count = min((uint32_t)kCombineSlice, n_chunks - c0);
         __syncthreads();
-        for (uint32_t c = d; c < count; c += blockDim.x) weights[c] = expf(base[(uint64_t)(c0 + c) * (hd + 2)] - m);
-        __syncthreads();
-#pragma unroll 4
-        for (uint32_t c = 0; c < count; ++c) {
-            const float* part = base + (uint64_t)(c0 + c) * (hd + 2);
-            sum += weights[c] * part[1];
-            acc += weights[c] * part[2 + d];
+        for (uint32_t c = tid; c < count; c += blockDim.x) {
+            const float* at = base + (uint64_t)(c0 + c) * (hd + 2);
+            const float w = expf(at[0] - m);
+            weights[c] = w;
+            sum += w * at[1];
         }
+        __syncthreads();
+#pragma unroll 8
+        for (uint32_t c = part; c < count; c += kCombineParts) acc += weights[c] * base[(uint64_t)(c0 + c) * (hd + 2) + 2 + d];
     }
-    p.out[(uint64_t)query * p.n_heads * hd + (uint64_t)head * hd + d] = acc / sum;
+    sum = warp_sum(sum);
+    __syncthreads();  // the maxima in `across` have been read
+    if ((tid & 31) == 0) across[tid >> 5] = sum;
+    parts[part * hd + d] = acc;
+    __syncthreads();
+    if (part == 0) {
+        float total = 0.f, all = 0.f;
+        for (uint32_t w = 0; w < n_warps; ++w) total += across[w];
+#pragma unroll
+        for (int r = 0; r < kCombineParts; ++r) all += parts[r * hd + d];
+        p.out[(uint64_t)query * p.n_heads * hd + (uint64_t)head * hd + d] = all / total;
+    }
 }
 
 }  // namespace
@@ -411,7 +429,9 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
         }
         CombineParams mp{scratch, out, s.n_heads, s.head_dim, s.first_pos, q0, max_chunks, s.pos_ptr, chunk};
         void* combine_args[] = {&mp};
-        if ((e = launch_kernel((const void*)attention_combine_kernel, dim3(s.n_heads, nq), dim3(s.head_dim), 0, stream, combine_args)) != cudaSuccess) return e;
+        if ((e = launch_kernel((const void*)attention_combine_kernel, dim3(s.n_heads, nq), dim3(kCombineParts * s.head_dim),
+                               (size_t)kCombineParts * s.head_dim * sizeof(float), stream, combine_args)) != cudaSuccess)
+            return e;
     }
     return cudaSuccess;
 }

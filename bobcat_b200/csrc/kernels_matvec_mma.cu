@@ -5,10 +5,12 @@
 // else of size, so the only goal is to keep HBM streaming. Two things stand in the way. (1) A lane
 // that turns nibbles into floats and multiplies them one by one spends about 3.5 instructions per
 // weight, more than an SM can issue at the rate HBM delivers weights (40 per clock per SM). Here
-// the nibbles become exact fp16 integers with one logic op per pair, and an mma.m16n8k16 does the
-// multiply-adds: the 16-row weight tile is the A operand, the input vector is the B operand, split
-// into a high and a low fp16 half in two of its eight columns so no input precision is lost; the
-// fp16 block scale multiplies the per-block f32 result. That is about 1.6 instructions per weight.
+// the multiply-adds run on the tensor cores in integers, which keeps them exact: four nibbles of
+// a word become the signed bytes 16 * (q - 8) with two logic ops, the 16-row weight tile is the A
+// operand of an mma.m16n8k32 (one per block of 32 weights), and the input vector, scaled to 31-bit
+// integers and split into four signed base-256 digits, fills four of the eight columns of B. The
+// digit sums are joined in integers and the fp16 block scale multiplies the per-block result in
+// f32: about 0.6 instructions per weight.
 // (2) A decode step is a chain of small dependent launches, and a launch that starts its loads
 // only after its input exists idles HBM for microseconds at every link. Here one thread per CTA
 // streams the CTA's share of the matrix into a shared-memory ring with bulk async copies, starting
@@ -20,9 +22,9 @@
 // Layout ("tiles"): rows in tiles of 16, columns in chunks of 16 blocks. A chunk of a tile is
 // contiguous: for each pair of blocks 512 bytes ordered by lane - lane (g, t) = (lane / 4, lane % 4)
 // holds word t of the quants of rows g and g + 8 for both blocks, exactly its A-fragment share -
-// then the chunk's fp16 scales, 16 per block. A tile's chunks follow one another, 288 bytes per
-// block, so a tile is one contiguous run and the matrix is the tiles in order. Values are the GGUF
-// values bit for bit.
+// then the chunk's fp16 scales, 8 bytes per (block pair, g): rows g and g + 8 of the first block,
+// then of the second. A tile's chunks follow one another, 288 bytes per block, so a tile is one
+// contiguous run and the matrix is the tiles in order. Values are the GGUF values bit for bit.
 //
 // Reference counterpart: matvec_k<q4_0_lanes> (crates/bobcat-metal/src/matvec.metal:298-365,
 // quant.metal:587-656) and its swiglu / conv variants (:386-585).
@@ -84,41 +86,21 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                  : "memory");
 }
 
-__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// d = a * b over 16 rows, 8 columns and 32 signed bytes of depth, from a zero accumulator.
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-// The same with a zero accumulator going in.
-__device__ __forceinline__ void mma_16816_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-}
+// The four low (high) nibbles q of a word as signed bytes 16 * (q - 8): the nibble moves to the top
+// of its byte and flipping the byte's sign bit takes off 128.
+__device__ __forceinline__ uint32_t low_nibbles_s8(uint32_t w) { return ((w << 4) & 0xf0f0f0f0u) ^ 0x80808080u; }
+__device__ __forceinline__ uint32_t high_nibbles_s8(uint32_t w) { return (w & 0xf0f0f0f0u) ^ 0x80808080u; }
 
-// The eight 4-bit quants of a word, minus 8, as four half2 registers of exact integers:
-// h[0] = elements (4t, 4t+2), h[1] = (4t+1, 4t+3), h[2] = (16+4t, 16+4t+2), h[3] = (16+4t+1, 16+4t+3)
-// of the block, for word t.
-__device__ __forceinline__ void unpack_word_half2(uint32_t w, uint32_t (&h)[4]) {
-    const uint32_t magic = 0x64006400u;  // half2(1024, 1024)
-    uint32_t lo02 = (w & 0x000f000fu) | magic;
-    uint32_t hi02 = (w & 0x00f000f0u) | magic;
-    uint32_t w8 = w >> 8;
-    uint32_t lo13 = (w8 & 0x000f000fu) | magic;
-    uint32_t hi13 = (w8 & 0x00f000f0u) | magic;
-    const __half2 bias_lo = __floats2half2_rn(1032.f, 1032.f);
-    const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
-    const __half2 bias_hi = __floats2half2_rn(-72.f, -72.f);
-    __half2 a = __hsub2(*reinterpret_cast<__half2*>(&lo02), bias_lo);
-    __half2 b = __hsub2(*reinterpret_cast<__half2*>(&lo13), bias_lo);
-    __half2 c = __hfma2(*reinterpret_cast<__half2*>(&hi02), sixteenth, bias_hi);
-    __half2 d = __hfma2(*reinterpret_cast<__half2*>(&hi13), sixteenth, bias_hi);
-    h[0] = *reinterpret_cast<uint32_t*>(&a);
-    h[1] = *reinterpret_cast<uint32_t*>(&b);
-    h[2] = *reinterpret_cast<uint32_t*>(&c);
-    h[3] = *reinterpret_cast<uint32_t*>(&d);
-}
+// An integer as four signed base-256 digits, one per byte, least significant first: adding 128 at
+// every byte position makes each byte digit + 128, and flipping the sign bits takes it off again.
+__device__ __forceinline__ uint32_t signed_digits(int v) { return ((uint32_t)v + 0x80808080u) ^ 0x80808080u; }
 
 enum Mode { kPlain = 0, kSwiglu = 1, kConv = 2 };
 
@@ -174,7 +156,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     constexpr int S = segments_per_job<MODE>();
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;                                                   // kStages * kStageBytes
-    uint4* xs = reinterpret_cast<uint4*>(smem + kStages * kStageBytes);     // [block][hi | lo][t]: 8 x 16 bytes per block
+    uint4* xs = reinterpret_cast<uint4*>(smem + kStages * kStageBytes);     // [block][digit][t]: 16 x 8 bytes per block
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
     __shared__ float reduce_scratch[64];
     __shared__ float partial[2][kConsumers][3 * 16];  // [job parity][warp][segment * 16 + row in tile]
@@ -242,11 +224,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     // history) belong to earlier launches.
     pdl_wait();
 
-    // Stage x in the layout the B fragments want. For block b and word index t the 16 bytes at
-    // xs[b * 8 + part * 4 + t] hold half2(x[4t], x[4t+2]), half2(x[4t+1], x[4t+3]),
-    // half2(x[16+4t], x[16+4t+2]), half2(x[16+4t+1], x[16+4t+3]) of the block, as the high fp16
-    // part (part 0) or the low part (part 1) of x * 2^shift. The shift brings the largest |x| to
-    // [2^13, 2^14), so neither part loses bits to fp16's narrow exponent range.
+    // Stage x as the B operand: RMSNorm weights applied, scaled by a power of two so that the
+    // largest |x| lands in [2^29, 2^30), rounded to integers (no change for a value of at least
+    // 2^-7 of the largest, an absolute error below 2^-30 of the largest for the rest) and split
+    // into four signed base-256 digits, one digit per column of B. The norm's scalar and the power of two multiply
+    // the finished rows instead.
     const int ctid = tid;  // consumers are threads 0 .. kConsumers * 32 - 1
     constexpr int kConsumerThreads = kConsumers * 32;
     const float4* x4 = reinterpret_cast<const float4*>(p.x);
@@ -260,8 +242,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
             v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
         }
         biggest = fmaxf(biggest, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-        // The weighted values wait in the staging buffer as f32 (element for element the bytes
-        // their fp16 pair will take), so the second pass needs neither global memory nor the weights.
+        // The weighted values wait in the staging buffer as f32 (a block's 32 floats are the 128
+        // bytes its digits will take), so the second pass needs neither global memory nor the weights.
         reinterpret_cast<float4*>(xs)[i] = v;
     }
     sumsq = warp_sum(sumsq);
@@ -279,25 +261,46 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     const float norm_scale = p.norm_weight ? rsqrtf(total / (float)(nb * 32) + p.eps) : 1.f;
     int exponent = 0;
     if (top > 0.f) frexpf(top, &exponent);             // top = m * 2^exponent, m in [0.5, 1)
-    const float up = top > 0.f ? exp2f((float)(14 - exponent)) : 1.f;  // top * up in [2^13, 2^14)
-    const float out_scale = norm_scale / up;
-    for (uint32_t i = ctid; i < nb * 4; i += kConsumerThreads) {
-        uint32_t b = i >> 2, t = i & 3;
-        // Elements 4t..4t+3 and 16+4t..16+4t+3: the same 32 bytes this thread then overwrites.
-        const float4 lo4 = reinterpret_cast<const float4*>(xs)[b * 8 + t], hi4 = reinterpret_cast<const float4*>(xs)[b * 8 + 4 + t];
-        float v[8] = {lo4.x * up, lo4.z * up, lo4.y * up, lo4.w * up, hi4.x * up, hi4.z * up, hi4.y * up, hi4.w * up};
-        __align__(16) __half hi[8];
-        __align__(16) __half lo[8];
+    // Second pass, in place: the values become integers and the integers signed bytes.
+    const int shift = min(30 - exponent, 96);
+    const float out_scale = norm_scale * exp2f((float)(-shift - 4));  // the weights come as 16 * (q - 8)
+    {
+        // x * up is an integer below 2^30 in magnitude, held exactly as four signed bytes per
+        // element. For block b, digit column j (0 = most significant) and word index t the 8
+        // bytes at xs8[b * 16 + j * 4 + t] hold that digit of elements 4t..4t+3 and 16+4t..16+4t+3.
+        const float up = top > 0.f ? exp2f((float)shift) : 1.f;
+        uint2* xs8 = reinterpret_cast<uint2*>(xs);
+        for (uint32_t first = (uint32_t)(ctid & ~31); first < nb * 4; first += kConsumerThreads) {
+            const uint32_t i = first + lane, b = i >> 2, t = i & 3;
+            const bool valid = i < nb * 4;
+            float4 lo4 = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo4;
+            if (valid) {
+                lo4 = reinterpret_cast<const float4*>(xs)[b * 8 + t];
+                hi4 = reinterpret_cast<const float4*>(xs)[b * 8 + 4 + t];
+            }
+            __syncwarp();  // the four threads of a block have read it before any of them overwrites it
+            if (valid) {
+                const float v[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
+                uint32_t word[2][4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            hi[j] = __float2half_rn(v[j]);
-            lo[j] = __float2half_rn(v[j] - __half2float(hi[j]));
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t d[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) d[e] = signed_digits(__float2int_rn(v[h * 4 + e] * up));
+                    // Transpose the 4 x 4 bytes: word[h][j] = byte 3 - j of the four elements.
+                    const uint32_t lo01 = __byte_perm(d[0], d[1], 0x5140), hi01 = __byte_perm(d[0], d[1], 0x7362);
+                    const uint32_t lo23 = __byte_perm(d[2], d[3], 0x5140), hi23 = __byte_perm(d[2], d[3], 0x7362);
+                    word[h][3] = __byte_perm(lo01, lo23, 0x5410);
+                    word[h][2] = __byte_perm(lo01, lo23, 0x7632);
+                    word[h][1] = __byte_perm(hi01, hi23, 0x5410);
+                    word[h][0] = __byte_perm(hi01, hi23, 0x7632);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) xs8[b * 16 + j * 4 + t] = make_uint2(word[0][j], word[1][j]);
+            }
         }
-        xs[b * 8 + t] = *reinterpret_cast<uint4*>(hi);
-        xs[b * 8 + 4 + t] = *reinterpret_cast<uint4*>(lo);
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-
     const int g = lane >> 2, t = lane & 3;
     const uint32_t grp = warp / gs, rank = warp % gs;
     uint32_t taken = 0;  // chunks this warp has consumed
@@ -340,25 +343,25 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
             // with g >= 2 hold columns of the product nobody reads; they repeat the reads of g & 1.
             const uint8_t* slot = ring + stage * kStageBytes;
             const uint4* quants = reinterpret_cast<const uint4*>(slot) + lane;
-            const __half* scales = reinterpret_cast<const __half*>(slot + cb * 256) + g;
-            const uint4* xq = xs + (size_t)chunk * kChunkBlocks * 8 + (g & 1) * 4 + t;
+            const uint2* scales = reinterpret_cast<const uint2*>(slot + cb * 256) + g;
+            const uint2* xq8 = reinterpret_cast<const uint2*>(xs) + (size_t)chunk * kChunkBlocks * 16 + (g & 3) * 4 + t;
             float a0 = 0.f, a1 = 0.f;
 #pragma unroll 2
             for (uint32_t pair = 0; pair < cb / 2; ++pair) {
                 const uint4 v = quants[pair * 32];
+                const uint2 dd = scales[pair * 8];  // the scales of rows g and g + 8, first block then second
 #pragma unroll
                 for (int half_pair = 0; half_pair < 2; ++half_pair) {
-                    uint32_t ha[4], hb[4];
-                    unpack_word_half2(half_pair ? v.z : v.x, ha);  // row g
-                    unpack_word_half2(half_pair ? v.w : v.y, hb);  // row g + 8
-                    const uint4 xb = xq[(pair * 2 + half_pair) * 8];
-                    float c[4];
-                    mma_16816_zero(c, ha[0], hb[0], ha[1], hb[1], xb.x, xb.y);
-                    mma_16816(c, ha[2], hb[2], ha[3], hb[3], xb.z, xb.w);
-                    const float d0 = __half2float(scales[(pair * 2 + half_pair) * 16]);
-                    const float d1 = __half2float(scales[(pair * 2 + half_pair) * 16 + 8]);
-                    a0 = fmaf(c[0] + c[1], d0, a0);
-                    a1 = fmaf(c[2] + c[3], d1, a1);
+                    const uint32_t wa = half_pair ? v.z : v.x, wb = half_pair ? v.w : v.y;  // rows g and g + 8
+                    const uint32_t dw = half_pair ? dd.y : dd.x;
+                    const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&dw));
+                    // One multiply per block: columns 2t and 2t + 1 of the product are two
+                    // neighbouring digits of x, joined here before the block's scale.
+                    const uint2 xb = xq8[(pair * 2 + half_pair) * 16];
+                    int c[4];
+                    mma_s8(c, low_nibbles_s8(wa), low_nibbles_s8(wb), high_nibbles_s8(wa), high_nibbles_s8(wb), xb.x, xb.y);
+                    a0 = fmaf((float)(c[0] * 256 + c[1]), d.x, a0);
+                    a1 = fmaf((float)(c[2] * 256 + c[3]), d.y, a1);
                 }
             }
             __syncwarp();
@@ -371,10 +374,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
                 }
             }
         }
-        // Columns 0 and 1 of the product (the high and low parts of x) live in the lanes with
-        // t == 0. The group's warps leave their partial sums in shared memory; after the group's
-        // barrier its first warp adds them in warp order and finishes the 16 rows.
+        // Lanes with t == 0 hold the sums over the two high digits of x, their neighbours (t == 1)
+        // those over the two low ones; joined, they are the rows' sums. The group's warps leave
+        // their partial sums in shared memory; after the group's barrier its first warp adds them
+        // in warp order and finishes the 16 rows.
         const int parity = r & 1;
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+            acc[s][0] = fmaf(acc[s][0], 65536.f, __shfl_down_sync(0xffffffffu, acc[s][0], 1));
+            acc[s][1] = fmaf(acc[s][1], 65536.f, __shfl_down_sync(0xffffffffu, acc[s][1], 1));
+        }
         if (t == 0) {
 #pragma unroll
             for (int s = 0; s < S; ++s) {
@@ -459,7 +468,9 @@ __global__ void repack_tiles_kernel(const uint4* __restrict__ quants, const __ha
         uint32_t cb = min((uint32_t)kChunkBlocks, nb - chunk * kChunkBlocks);
         uint32_t row = tile * 16 + in_tile;
         __half d = row < n_rows ? scales[(uint64_t)row * nb + block] : __float2half(0.f);
-        uint8_t* dst = tiles + (uint64_t)tile * nb * kBlockBytes + (uint64_t)chunk * kStageBytes + (uint64_t)cb * 256 + ((uint64_t)local * 16 + in_tile) * 2;
+        // 8 bytes per (block pair, g): rows g and g + 8 of the first block, then of the second.
+        uint8_t* dst = tiles + (uint64_t)tile * nb * kBlockBytes + (uint64_t)chunk * kStageBytes + (uint64_t)cb * 256 +
+                       ((uint64_t)(local / 2) * 8 + (in_tile & 7)) * 8 + ((local & 1) * 2 + (in_tile >> 3)) * 2;
         *reinterpret_cast<__half*>(dst) = d;
     }
 }
