@@ -92,6 +92,12 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
+// d += a * b.
+__device__ __forceinline__ void mma_s8_add(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
 // The four low (high) nibbles q of a word as signed bytes 16 * (q - 8): the nibble moves to the top
 // of its byte and flipping the byte's sign bit takes off 128.
@@ -159,6 +165,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     uint4* xs = reinterpret_cast<uint4*>(smem + kStages * kStageBytes);     // [block][digit][t]: 16 x 8 bytes per block
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
     __shared__ float reduce_scratch[64];
+    __shared__ uint2 zero_columns[kChunkBlocks * 16];  // a chunk's worth of B operand that is all zero
     __shared__ float partial[2][kConsumers][3 * 16];  // [job parity][warp][segment * 16 + row in tile]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -246,6 +253,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
         // bytes its digits will take), so the second pass needs neither global memory nor the weights.
         reinterpret_cast<float4*>(xs)[i] = v;
     }
+    for (int i = ctid; i < kChunkBlocks * 16; i += kConsumerThreads) zero_columns[i] = make_uint2(0u, 0u);
     sumsq = warp_sum(sumsq);
     biggest = warp_max(biggest);
     if (lane == 0) {
@@ -343,26 +351,29 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
             // with g >= 2 hold columns of the product nobody reads; they repeat the reads of g & 1.
             const uint8_t* slot = ring + stage * kStageBytes;
             const uint4* quants = reinterpret_cast<const uint4*>(slot) + lane;
-            const uint2* scales = reinterpret_cast<const uint2*>(slot + cb * 256) + g;
-            const uint2* xq8 = reinterpret_cast<const uint2*>(xs) + (size_t)chunk * kChunkBlocks * 16 + (g & 3) * 4 + t;
+            // Two blocks share one pass over the product's columns: the first block's multiply
+            // sees the digits of x in columns 0..3 and zeros in 4..7, the second block's the
+            // reverse, and both add into one accumulator. Afterwards lanes t = 0, 1 hold the first
+            // block's sums (high and low digit pair) and lanes t = 2, 3 the second block's, so
+            // the conversion and the block scale run once per pair of blocks with every lane useful.
+            // A lane supplies column g of B: real digits for one block of the pair, zeros for the other.
+            const uint2* chunk_x = reinterpret_cast<const uint2*>(xs) + (size_t)chunk * kChunkBlocks * 16 + (g & 3) * 4 + t;
+            const uint2* x_first = g < 4 ? chunk_x : zero_columns + (g & 3) * 4 + t;
+            const uint2* x_second = g < 4 ? zero_columns + (g & 3) * 4 + t : chunk_x + 16;
+            const uint32_t* scales = reinterpret_cast<const uint32_t*>(slot + cb * 256) + g * 2 + (t >> 1);
             float a0 = 0.f, a1 = 0.f;
-#pragma unroll 2
+#pragma unroll 4
             for (uint32_t pair = 0; pair < cb / 2; ++pair) {
-                const uint4 v = quants[pair * 32];
-                const uint2 dd = scales[pair * 8];  // the scales of rows g and g + 8, first block then second
-#pragma unroll
-                for (int half_pair = 0; half_pair < 2; ++half_pair) {
-                    const uint32_t wa = half_pair ? v.z : v.x, wb = half_pair ? v.w : v.y;  // rows g and g + 8
-                    const uint32_t dw = half_pair ? dd.y : dd.x;
-                    const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&dw));
-                    // One multiply per block: columns 2t and 2t + 1 of the product are two
-                    // neighbouring digits of x, joined here before the block's scale.
-                    const uint2 xb = xq8[(pair * 2 + half_pair) * 16];
-                    int c[4];
-                    mma_s8(c, low_nibbles_s8(wa), low_nibbles_s8(wb), high_nibbles_s8(wa), high_nibbles_s8(wb), xb.x, xb.y);
-                    a0 = fmaf((float)(c[0] * 256 + c[1]), d.x, a0);
-                    a1 = fmaf((float)(c[2] * 256 + c[3]), d.y, a1);
-                }
+                const uint4 v = quants[pair * 32];  // rows g, g + 8 of the first block, then of the second
+                const uint32_t dw = scales[pair * 16];  // the scales of rows g and g + 8 in this lane's block
+                const uint2 xa = x_first[pair * 32], xb = x_second[pair * 32];
+                int c[4];
+                mma_s8(c, low_nibbles_s8(v.x), low_nibbles_s8(v.y), high_nibbles_s8(v.x), high_nibbles_s8(v.y), xa.x, xa.y);
+                mma_s8_add(c, low_nibbles_s8(v.z), low_nibbles_s8(v.w), high_nibbles_s8(v.z), high_nibbles_s8(v.w), xb.x, xb.y);
+                const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&dw));
+                // Columns 2t and 2t + 1 are neighbouring digits of x, joined before the scale.
+                a0 = fmaf((float)(c[0] * 256 + c[1]), d.x, a0);
+                a1 = fmaf((float)(c[2] * 256 + c[3]), d.y, a1);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
@@ -374,15 +385,21 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
                 }
             }
         }
-        // Lanes with t == 0 hold the sums over the two high digits of x, their neighbours (t == 1)
-        // those over the two low ones; joined, they are the rows' sums. The group's warps leave
-        // their partial sums in shared memory; after the group's barrier its first warp adds them
-        // in warp order and finishes the 16 rows.
+        // Lanes with even t hold sums over the two high digits of x, lanes with odd t over the two
+        // low ones, each for every other block; the four lanes of a row add up to the row's sum.
+        // The group's warps leave their partial sums in shared memory; after the group's barrier
+        // its first warp adds them in warp order and finishes the 16 rows.
         const int parity = r & 1;
+        const float digit_weight = (t & 1) ? 1.f : 65536.f;
 #pragma unroll
         for (int s = 0; s < S; ++s) {
-            acc[s][0] = fmaf(acc[s][0], 65536.f, __shfl_down_sync(0xffffffffu, acc[s][0], 1));
-            acc[s][1] = fmaf(acc[s][1], 65536.f, __shfl_down_sync(0xffffffffu, acc[s][1], 1));
+#pragma unroll
+            for (int half_rows = 0; half_rows < 2; ++half_rows) {
+                float v = acc[s][half_rows] * digit_weight;
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                acc[s][half_rows] = v;
+            }
         }
         if (t == 0) {
 #pragma unroll
