@@ -130,6 +130,12 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
                       float* scratch, float* out, const AttentionShape& shape);
 // Kernels `attention` launches for this shape.
 int attention_launches(bool kv_half, const AttentionShape& shape);
+// One decoded token of an attention layer in two launches: the chunk pass normalises and rotates
+// the raw q itself, and the CTA whose chunk ends at the new position prepares that position's key
+// and value rows, stores them in the caches and uses them; then the combine pass. Covers
+// half-precision caches, heads of 64, 128 or 256 elements rotated whole, 16-byte aligned rows.
+bool attention_step_supported(const RopeStore& r, const AttentionShape& shape);
+cudaError_t attention_step(cudaStream_t stream, const RopeStore& r, float* scratch, float* out, const AttentionShape& shape);
 // The tensor-core prefill kernel (kernels_attention_flash.cu): heads of 64 elements, f16 cache, at
 // least 32 queries, positions known at launch. `attention` picks it when it applies.
 bool attention_flash_supported(bool kv_half, const AttentionShape& shape);

@@ -43,6 +43,13 @@ struct ChunkParams {
     uint32_t max_chunks;  // chunks the scratch holds per (query, head)
     const uint32_t* pos_ptr;  // when set, added to first_pos at run time
     uint32_t chunk;           // positions per chunk
+    // The fused decode step: q is the raw projection, and the new position's key and value rows
+    // come from raw_k and raw_v instead of the caches, which this launch also fills.
+    const float* raw_k;
+    const float* raw_v;
+    const float* q_norm;
+    const float* k_norm;
+    float eps, theta;
 };
 
 // Scratch layout: [query in batch][head][chunk][head_dim + 2] = (max, sum, acc[head_dim]).
@@ -166,7 +173,38 @@ __device__ __forceinline__ void unpack_row(const uint4& raw, float (&f)[8]) {
     }
 }
 
-template <int HD, int GROUP>
+// Per-head RMSNorm, norm weights and NeoX rotation of the 8 elements d0..d0+7 a lane holds of a
+// head (the lanes of a row hold the whole head); the same arithmetic as rope_store_kernel, with the
+// rotation over the whole head. `rot[i]` is (cos, sin) of pair i at this position.
+template <int HD>
+__device__ __forceinline__ void norm_rotate(float (&v)[8], const float* __restrict__ weight, float eps, int d0, const float2* rot) {
+    constexpr int kLanesPerRow = HD / 8;
+    float sumsq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sumsq += v[i] * v[i];
+#pragma unroll
+    for (int o = 1; o < kLanesPerRow; o <<= 1) sumsq += __shfl_xor_sync(0xffffffffu, sumsq, o);
+    const float scale = rsqrtf(sumsq / (float)HD + eps);
+    const bool low = d0 < HD / 2;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = weight[d0 + i] * (v[i] * scale);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[i], kLanesPerRow / 2);  // element d0 + i +- HD / 2
+        const float2 cs = rot[(d0 % (HD / 2)) + i];
+        v[i] = low ? v[i] * cs.x - other * cs.y : v[i] * cs.x + other * cs.y;
+    }
+}
+
+__device__ __forceinline__ uint4 pack_row(const float (&f)[8]) {
+    uint4 raw;
+    __half2* h = reinterpret_cast<__half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    return raw;
+}
+
+template <int HD, int GROUP, bool FUSED>
 __global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(ChunkParams p) {
     constexpr int kLanesPerRow = HD / 8, kRowsPerLoad = 32 / kLanesPerRow, kWarps = kDecodeThreads / 32;
     pdl_launch_dependents();
@@ -196,6 +234,43 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(ChunkP
         v_raw = __ldg(reinterpret_cast<const uint4*>(vc + (uint64_t)(base + sub) * kv_dim));
     }
 
+    // Fused step: the rotation's cosines and sines for this position, one pair per thread; the
+    // CTA whose chunk ends at the new position prepares that position's key and value rows,
+    // rounds them to the cache's precision, stores them, and uses them in place of the cache.
+    __shared__ float2 rot[HD / 2];
+    const uint32_t new_row = pos - start;  // the new position's row, when it lies in this chunk
+    const bool holds_new = FUSED && new_row < p.chunk;
+    uint4 k_new = make_uint4(0, 0, 0, 0), v_new = make_uint4(0, 0, 0, 0);
+    if (FUSED) {
+        if (tid < HD / 2) {
+            const float inv_freq = 1.0f / powf(p.theta, (float)(2 * tid) / (float)HD);
+            float sn, cs;
+            sincosf((float)pos * inv_freq, &sn, &cs);
+            rot[tid] = make_float2(cs, sn);
+        }
+        __syncthreads();
+        if (holds_new) {
+            const float* kp = p.raw_k + (uint64_t)kv_head * HD + d0;
+            const float* vp = p.raw_v + (uint64_t)kv_head * HD + d0;
+            const float4 ka = *reinterpret_cast<const float4*>(kp), kb = *reinterpret_cast<const float4*>(kp + 4);
+            const float4 va = *reinterpret_cast<const float4*>(vp), vb = *reinterpret_cast<const float4*>(vp + 4);
+            float kf[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
+            const float vf[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+            norm_rotate<HD>(kf, p.k_norm, p.eps, d0, rot);
+            k_new = pack_row(kf);
+            v_new = pack_row(vf);
+            if (warp == 0 && sub == 0) {
+                const uint64_t at = (uint64_t)pos * kv_dim + (uint64_t)kv_head * HD + d0;
+                *reinterpret_cast<uint4*>(static_cast<__half*>(const_cast<void*>(p.k_cache)) + at) = k_new;
+                *reinterpret_cast<uint4*>(static_cast<__half*>(const_cast<void*>(p.v_cache)) + at) = v_new;
+            }
+            if (base + sub == new_row) {
+                k_raw = k_new;
+                v_raw = v_new;
+            }
+        }
+    }
+
     const float scale = 1.0f / sqrtf((float)HD);
     float qv[GROUP][8], acc[GROUP][8], top[GROUP], sum[GROUP];
 #pragma unroll
@@ -207,8 +282,10 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(ChunkP
         if (g < (int)group) {
             const float* qp = p.q + (uint64_t)query * p.q_stride + (uint64_t)(kv_head * group + g) * p.q_head_stride + d0;
             float4 a = *reinterpret_cast<const float4*>(qp), b = *reinterpret_cast<const float4*>(qp + 4);
-            qv[g][0] = a.x * scale; qv[g][1] = a.y * scale; qv[g][2] = a.z * scale; qv[g][3] = a.w * scale;
-            qv[g][4] = b.x * scale; qv[g][5] = b.y * scale; qv[g][6] = b.z * scale; qv[g][7] = b.w * scale;
+            float raw[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            if (FUSED) norm_rotate<HD>(raw, p.q_norm, p.eps, d0, rot);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qv[g][i] = raw[i] * scale;
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) qv[g][i] = 0.f;
@@ -224,6 +301,10 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(ChunkP
         if (next + sub < count) {
             k_raw = __ldg(reinterpret_cast<const uint4*>(kc + (uint64_t)(next + sub) * kv_dim));
             v_raw = __ldg(reinterpret_cast<const uint4*>(vc + (uint64_t)(next + sub) * kv_dim));
+            if (holds_new && next + sub == new_row) {
+                k_raw = k_new;
+                v_raw = v_new;
+            }
         }
 #pragma unroll
         for (int g = 0; g < GROUP; ++g) {
@@ -299,10 +380,15 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(ChunkP
 }
 
 template <int HD>
-const void* decode_kernel_for(uint32_t group) {
-    if (group <= 2) return (const void*)attention_decode_kernel<HD, 2>;
-    if (group <= 4) return (const void*)attention_decode_kernel<HD, 4>;
-    return (const void*)attention_decode_kernel<HD, 8>;
+const void* decode_kernel_for(uint32_t group, bool fused) {
+    if (fused) {
+        if (group <= 2) return (const void*)attention_decode_kernel<HD, 2, true>;
+        if (group <= 4) return (const void*)attention_decode_kernel<HD, 4, true>;
+        return (const void*)attention_decode_kernel<HD, 8, true>;
+    }
+    if (group <= 2) return (const void*)attention_decode_kernel<HD, 2, false>;
+    if (group <= 4) return (const void*)attention_decode_kernel<HD, 4, false>;
+    return (const void*)attention_decode_kernel<HD, 8, false>;
 }
 
 // The decode form covers a half-precision cache, heads of 64, 128 or 256 elements and 16-byte aligned
@@ -312,13 +398,13 @@ bool decode_shape(bool kv_half, const AttentionShape& s) {
            (s.head_dim == 64 || s.head_dim == 128 || s.head_dim == 256);
 }
 
-const void* decode_kernel(bool kv_half, const AttentionShape& s, const float* q, const void* k_cache, const void* v_cache) {
+const void* decode_kernel(bool kv_half, const AttentionShape& s, const float* q, const void* k_cache, const void* v_cache, bool fused = false) {
     if (!decode_shape(kv_half, s) || ((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16 != 0) return nullptr;
     const uint32_t group = s.n_heads / s.n_kv_heads;
     switch (s.head_dim) {
-        case 64: return decode_kernel_for<64>(group);
-        case 128: return decode_kernel_for<128>(group);
-        default: return decode_kernel_for<256>(group);
+        case 64: return decode_kernel_for<64>(group, fused);
+        case 128: return decode_kernel_for<128>(group, fused);
+        default: return decode_kernel_for<256>(group, fused);
     }
 }
 
@@ -416,7 +502,7 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
         uint32_t nq = s.n_queries - q0 < (uint32_t)kQueryBatch ? s.n_queries - q0 : (uint32_t)kQueryBatch;
         uint32_t last_pos = s.first_pos + q0 + nq - 1;
         ChunkParams cp{q, k_cache, v_cache, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.first_pos, s.n_ctx,
-                       s.q_stride, s.q_head_stride, q0, max_chunks, s.pos_ptr, chunk};
+                       s.q_stride, s.q_head_stride, q0, max_chunks, s.pos_ptr, chunk, nullptr, nullptr, nullptr, nullptr, 0.f, 0.f};
         // With a run-time position the grid covers every chunk of the context; CTAs past the position exit at once.
         dim3 grid(s.n_kv_heads, s.pos_ptr ? max_chunks : last_pos / chunk + 1, nq);
         void* chunk_args[] = {&cp};
@@ -434,6 +520,27 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
             return e;
     }
     return cudaSuccess;
+}
+
+bool attention_step_supported(const RopeStore& r, const AttentionShape& s) {
+    return r.kv_half && s.n_queries == 1 && decode_shape(true, s) && r.n_rot == s.head_dim && r.q_head_stride == s.q_head_stride &&
+           ((uintptr_t)r.q | (uintptr_t)r.k | (uintptr_t)r.v | (uintptr_t)r.k_cache | (uintptr_t)r.v_cache) % 16 == 0;
+}
+
+cudaError_t attention_step(cudaStream_t stream, const RopeStore& r, float* scratch, float* out, const AttentionShape& s) {
+    const uint32_t chunk = kDecodeChunk, max_chunks = (s.n_ctx + chunk - 1) / chunk;
+    ChunkParams cp{r.q, r.k_cache, r.v_cache, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.first_pos, s.n_ctx,
+                   s.q_stride, s.q_head_stride, 0, max_chunks, s.pos_ptr, chunk, r.k, r.v, r.q_norm, r.k_norm, r.eps, r.theta};
+    dim3 grid(s.n_kv_heads, s.pos_ptr ? max_chunks : s.first_pos / chunk + 1, 1);
+    void* chunk_args[] = {&cp};
+    const void* kernel = decode_kernel(true, s, r.q, r.k_cache, r.v_cache, true);
+    if (!kernel) return cudaErrorInvalidValue;
+    cudaError_t e = launch_kernel(kernel, grid, dim3(kDecodeThreads), 0, stream, chunk_args);
+    if (e != cudaSuccess) return e;
+    CombineParams mp{scratch, out, s.n_heads, s.head_dim, s.first_pos, 0, max_chunks, s.pos_ptr, chunk};
+    void* combine_args[] = {&mp};
+    return launch_kernel((const void*)attention_combine_kernel, dim3(s.n_heads, 1), dim3(kCombineParts * s.head_dim),
+                         (size_t)kCombineParts * s.head_dim * sizeof(float), stream, combine_args);
 }
 
 }  // namespace k

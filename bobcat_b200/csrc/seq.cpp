@@ -146,9 +146,13 @@ struct Recorder {
         k::RopeStore rs{s.q, s.k, s.v, cache_at(s.k_cache, layer_base(cache_index)), cache_at(s.v_cache, layer_base(cache_index)),
                         D.q_norm, D.k_norm, hp.n_heads, hp.n_kv_heads, hp.head_dim, q_head_stride, hp.n_rot, hp.rope_theta, hp.norm_eps, s.kv_half};
         k::Pos p = at(pos);
-        run("rope_store", hp.n_heads + 2 * hp.n_kv_heads, hp.head_dim, 0, 1, [&] { return k::rope_store(stream, rs, p); });
         k::AttentionShape shape{hp.n_heads, hp.n_kv_heads, hp.head_dim, p.value, 1, s.n_ctx, q_stride, q_head_stride, p.ptr};
         uint64_t kv_bytes = (uint64_t)(pos + 1) * kv_dim() * kv_element_bytes() * 2;
+        if (k::attention_step_supported(rs, shape)) {
+            run("attention_step", 1, pos + 1, kv_bytes, 2, [&] { return k::attention_step(stream, rs, s.scores, s.attn, shape); });
+            return;
+        }
+        run("rope_store", hp.n_heads + 2 * hp.n_kv_heads, hp.head_dim, 0, 1, [&] { return k::rope_store(stream, rs, p); });
         run("attention", 1, pos + 1, kv_bytes, k::attention_launches(s.kv_half, shape), [&] {
             return k::attention(stream, s.q, cache_at(s.k_cache, layer_base(cache_index)), cache_at(s.v_cache, layer_base(cache_index)), s.kv_half,
                                 s.scores, s.attn, shape);
