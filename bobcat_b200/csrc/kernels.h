@@ -99,7 +99,12 @@ struct RopeStore {
     uint32_t n_heads, n_kv_heads, head_dim, q_head_stride, n_rot;
     float theta, eps;
     bool kv_half;
+    // Optional [position][n_rot / 2] table of (cos, sin) from rope_table, read by attention_step
+    // in place of computing them.
+    const float2* table = nullptr;
 };
+// (cos, sin) of every rotation pair at positions [0, n_positions), the values rope_store computes.
+cudaError_t rope_table(cudaStream_t stream, float2* table, uint32_t n_positions, uint32_t n_rot, float theta);
 cudaError_t rope_store(cudaStream_t stream, const RopeStore& p, Pos pos);
 // One thread: *counter += 1.
 cudaError_t advance(cudaStream_t stream, uint32_t* counter);

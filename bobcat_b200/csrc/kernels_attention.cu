@@ -50,6 +50,7 @@ struct ChunkParams {
     const float* q_norm;
     const float* k_norm;
     float eps, theta;
+    const float2* rope_table;  // [position][HD / 2] (cos, sin), or null to compute them here
 };
 
 // Scratch layout: [query in batch][head][chunk][head_dim + 2] = (max, sum, acc[head_dim]).
@@ -243,10 +244,14 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(ChunkP
     uint4 k_new = make_uint4(0, 0, 0, 0), v_new = make_uint4(0, 0, 0, 0);
     if (FUSED) {
         if (tid < HD / 2) {
-            const float inv_freq = 1.0f / powf(p.theta, (float)(2 * tid) / (float)HD);
-            float sn, cs;
-            sincosf((float)pos * inv_freq, &sn, &cs);
-            rot[tid] = make_float2(cs, sn);
+            if (p.rope_table) {
+                rot[tid] = p.rope_table[(uint64_t)pos * (HD / 2) + tid];
+            } else {
+                const float inv_freq = 1.0f / powf(p.theta, (float)(2 * tid) / (float)HD);
+                float sn, cs;
+                sincosf((float)pos * inv_freq, &sn, &cs);
+                rot[tid] = make_float2(cs, sn);
+            }
         }
         __syncthreads();
         if (holds_new) {
@@ -502,7 +507,7 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
         uint32_t nq = s.n_queries - q0 < (uint32_t)kQueryBatch ? s.n_queries - q0 : (uint32_t)kQueryBatch;
         uint32_t last_pos = s.first_pos + q0 + nq - 1;
         ChunkParams cp{q, k_cache, v_cache, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.first_pos, s.n_ctx,
-                       s.q_stride, s.q_head_stride, q0, max_chunks, s.pos_ptr, chunk, nullptr, nullptr, nullptr, nullptr, 0.f, 0.f};
+                       s.q_stride, s.q_head_stride, q0, max_chunks, s.pos_ptr, chunk, nullptr, nullptr, nullptr, nullptr, 0.f, 0.f, nullptr};
         // With a run-time position the grid covers every chunk of the context; CTAs past the position exit at once.
         dim3 grid(s.n_kv_heads, s.pos_ptr ? max_chunks : last_pos / chunk + 1, nq);
         void* chunk_args[] = {&cp};
@@ -530,7 +535,7 @@ bool attention_step_supported(const RopeStore& r, const AttentionShape& s) {
 cudaError_t attention_step(cudaStream_t stream, const RopeStore& r, float* scratch, float* out, const AttentionShape& s) {
     const uint32_t chunk = kDecodeChunk, max_chunks = (s.n_ctx + chunk - 1) / chunk;
     ChunkParams cp{r.q, r.k_cache, r.v_cache, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.first_pos, s.n_ctx,
-                   s.q_stride, s.q_head_stride, 0, max_chunks, s.pos_ptr, chunk, r.k, r.v, r.q_norm, r.k_norm, r.eps, r.theta};
+                   s.q_stride, s.q_head_stride, 0, max_chunks, s.pos_ptr, chunk, r.k, r.v, r.q_norm, r.k_norm, r.eps, r.theta, r.table};
     dim3 grid(s.n_kv_heads, s.pos_ptr ? max_chunks : s.first_pos / chunk + 1, 1);
     void* chunk_args[] = {&cp};
     const void* kernel = decode_kernel(true, s, r.q, r.k_cache, r.v_cache, true);

@@ -379,6 +379,17 @@ __global__ void rope_store_kernel(RopeStore p, Pos pos_ref) {
     }
 }
 
+__global__ void rope_table_kernel(float2* table, uint32_t n_positions, uint32_t n_rot, float theta) {
+    const uint32_t half_rot = n_rot / 2;
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (uint64_t)n_positions * half_rot) return;
+    const uint32_t pos = (uint32_t)(i / half_rot), pair = (uint32_t)(i % half_rot);
+    const float inv_freq = 1.0f / powf(theta, (float)(2 * pair) / (float)n_rot);
+    float s, c;
+    sincosf((float)pos * inv_freq, &s, &c);
+    table[i] = make_float2(c, s);
+}
+
 __global__ void advance_kernel(uint32_t* counter) {
     pdl_launch_dependents();
     pdl_wait();
@@ -478,6 +489,13 @@ cudaError_t argmax_step(cudaStream_t stream, const float* x, uint32_t n, uint32_
 cudaError_t advance(cudaStream_t stream, uint32_t* counter) {
     void* args[] = {&counter};
     return launch_kernel((const void*)advance_kernel, dim3(1), dim3(1), 0, stream, args);
+}
+
+cudaError_t rope_table(cudaStream_t stream, float2* table, uint32_t n_positions, uint32_t n_rot, float theta) {
+    const uint64_t items = (uint64_t)n_positions * (n_rot / 2);
+    if (items == 0) return cudaSuccess;
+    rope_table_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(table, n_positions, n_rot, theta);
+    return cudaGetLastError();
 }
 
 cudaError_t rope_store(cudaStream_t stream, const RopeStore& p, Pos pos) {

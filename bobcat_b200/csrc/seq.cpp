@@ -144,7 +144,7 @@ struct Recorder {
     // (one launch), then attention over positions [0, pos].
     void decode_attend(const DeviceLayer& D, uint32_t cache_index, uint32_t pos, uint32_t q_stride, uint32_t q_head_stride) {
         k::RopeStore rs{s.q, s.k, s.v, cache_at(s.k_cache, layer_base(cache_index)), cache_at(s.v_cache, layer_base(cache_index)),
-                        D.q_norm, D.k_norm, hp.n_heads, hp.n_kv_heads, hp.head_dim, q_head_stride, hp.n_rot, hp.rope_theta, hp.norm_eps, s.kv_half};
+                        D.q_norm, D.k_norm, hp.n_heads, hp.n_kv_heads, hp.head_dim, q_head_stride, hp.n_rot, hp.rope_theta, hp.norm_eps, s.kv_half, s.rope_table};
         k::Pos p = at(pos);
         k::AttentionShape shape{hp.n_heads, hp.n_kv_heads, hp.head_dim, p.value, 1, s.n_ctx, q_stride, q_head_stride, p.ptr};
         uint64_t kv_bytes = (uint64_t)(pos + 1) * kv_dim() * kv_element_bytes() * 2;
@@ -648,6 +648,7 @@ bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32
         {(void**)&s->gdn_out, rows * value_dim * 4},
         {(void**)&s->q_rot, qwen ? rows * q_dim * 4 : 0},
         {(void**)&s->step_pos, 4},
+        {(void**)&s->rope_table, hp.n_attention_layers && !qwen ? (size_t)n_ctx * (hp.n_rot / 2) * sizeof(float2) : 0},
     };
     const char* no_graph = getenv("BOBCAT_NO_GRAPH");
     s->use_graphs = !(no_graph && no_graph[0] == '1');
@@ -666,6 +667,7 @@ bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32
         *it.slot = p;
         p += round_up(std::max<size_t>(it.bytes, 4), 256);
     }
+    if (hp.n_attention_layers && !qwen) BC_CUDA(k::rope_table(backend->stream, s->rope_table, n_ctx, hp.n_rot, hp.rope_theta));
     BC_TRY(ensure_trace_rows(s.get(), 1));
     e = cudaHostAlloc((void**)&s->readback, sizeof(uint32_t) * kGenerateInFlight, cudaHostAllocMapped);
     if (e != cudaSuccess) return fail(BC_ERR_ALLOCATION, "cannot allocate the token readback: %s", cudaGetErrorString(e));

@@ -62,6 +62,7 @@ struct bc_seq {
     // Replayed decode: the launches of one generated step are captured once into a CUDA graph whose
     // kernels read the position from `step_pos` on the device, then replayed once per token
     // (the reference's plan for stable commands, docs/design.md:94-98).
+    float2* rope_table = nullptr;             // (cos, sin) per position and rotation pair, for the decode attention step
     uint32_t* step_pos = nullptr;             // device word: position of the step being run
     cudaGraphExec_t generate_graph = nullptr; // argmax -> tokens[pos], forward pass at pos
     cudaGraphExec_t stream_graph = nullptr;   // forward pass at pos, argmax -> tokens[pos + 1] and the readback ring
