@@ -112,9 +112,13 @@ bc_status bc_op_matvec_experts_down(bc_backend* b, int32_t format, bc_buffer* do
     BC_TRY(check_range(b, route, route_off, bc_route_bytes(n_used, n_tokens), "matvec_experts_down"));
     BC_TRY(check_range(b, y, y_off, (size_t)n_tokens * n_rows * 4, "matvec_experts_down"));
     uint64_t bytes = (uint64_t)n_used * n_tokens * n_rows * type_row_bytes((uint32_t)format, n_cols);
-    return b->run("matvec_experts_down", n_rows, n_cols, bytes, 1, [&] {
+    // A single token on the tile kernel leaves its slots' outputs in the backend's scratch first.
+    void* slots = nullptr;
+    const int launches = k::matvec_experts_down_launches(d, n_rows, n_used, n_tokens, true);
+    if (launches == 2) BC_TRY(b->pack_scratch((size_t)n_used * n_rows * 4, &slots));
+    return b->run("matvec_experts_down", n_rows, n_cols, bytes, launches, [&] {
         return k::matvec_experts_down(b->stream, d, n_rows, at<const float>(x, x_off), at<const uint32_t>(route, route_off), n_used, at<float>(y, y_off),
-                                      n_tokens);
+                                      n_tokens, static_cast<float*>(slots));
     });
 }
 

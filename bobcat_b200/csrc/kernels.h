@@ -61,6 +61,14 @@ cudaError_t repack_tiles(cudaStream_t stream, const void* quants, const __half* 
 // The tensor-core decode kernels; every matrix must carry `tiles`. matvec / matvec_swiglu /
 // matvec_conv below pick them when they can.
 cudaError_t matvec_mma(cudaStream_t stream, const MatvecSegment* segments, int n_segments, const float* x, Norm norm, bool accumulate);
+// One token's experts on the same kernel: the stacked matrices' tiles, the slot's expert read from
+// route on the device. swiglu: y[slot][n_rows] from x; down: expert_out[slot][n_rows] from
+// x[slot][n_cols], to be added to the residual stream by moe_combine.
+bool matvec_experts_mma_supported(const Mat& w, uint32_t n_rows, uint32_t n_used);
+cudaError_t matvec_experts_swiglu_mma(cudaStream_t stream, const Mat& gate, const Mat& up, uint32_t n_rows, const float* x, const uint32_t* route,
+                                      uint32_t n_used, float* y);
+cudaError_t matvec_experts_down_mma(cudaStream_t stream, const Mat& down, uint32_t n_rows, const float* x, const uint32_t* route, uint32_t n_used,
+                                    float* expert_out);
 cudaError_t matvec_swiglu_mma(cudaStream_t stream, const Mat& gate, const Mat& up, const float* x, Norm norm, float* y);
 cudaError_t matvec_conv_mma(cudaStream_t stream, const Mat& in_proj, const float* x, Norm norm, const float* taps, float* history,
                             float* out, uint32_t n_embd, uint32_t kernel);
@@ -187,8 +195,11 @@ cudaError_t moe_group(cudaStream_t stream, const uint32_t* route, uint32_t* offs
 cudaError_t matvec_experts_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, uint32_t n_rows, const float* x,
                                   const uint32_t* route, uint32_t n_used, float* y, uint32_t n_tokens);
 // Decode: y[token][row] += sum over slots of weight * (down_e row . x[token][slot]).
+// With `expert_out` ([n_used][n_rows] floats of scratch) a single token may run on the tile kernel,
+// its slots' outputs added to y by moe_combine: two launches, see matvec_experts_down_launches.
 cudaError_t matvec_experts_down(cudaStream_t stream, const Mat& down, uint32_t n_rows, const float* x, const uint32_t* route,
-                                uint32_t n_used, float* y, uint32_t n_tokens);
+                                uint32_t n_used, float* y, uint32_t n_tokens, float* expert_out = nullptr);
+int matvec_experts_down_launches(const Mat& down, uint32_t n_rows, uint32_t n_used, uint32_t n_tokens, bool has_scratch);
 // Prefill: for each expert, its entries times its rows; with `up` the store is silu(gate) * up.
 // Input rows are the tokens' (gather) or the entries' own; output rows are the entries'.
 // With `scratch` (matmul_experts_scratch_bytes) and Q4_0 experts the tcgen05 kernel runs in its

@@ -127,6 +127,12 @@ struct Params {
     const float* taps;
     float* history;
     uint32_t n_embd, conv_kernel;
+    // Mixture of experts: the matrices are stacks of n_experts matrices of tiles_per_expert tiles
+    // and route[slot] names the expert of a slot. kSwiglu: job j is tile j % tiles_per_expert of
+    // slot j / tiles_per_expert, all slots read x. kPlain: CTA c works for slot c % n_used on the
+    // tiles of that slot's expert, reads x + slot * n_cols and writes y + slot * rows.
+    const uint32_t* route;
+    uint32_t tiles_per_expert, n_used;
 };
 
 template <int MODE>
@@ -144,7 +150,10 @@ __device__ __forceinline__ const uint8_t* job_tiles(const Params& p, uint32_t jo
         }
         return p.tiles[seg] + (uint64_t)local * tile_bytes;
     }
-    if (MODE == kSwiglu) return p.tiles[s] + (uint64_t)job * tile_bytes;
+    if (MODE == kSwiglu) {
+        if (p.route) job = p.route[job / p.tiles_per_expert] * p.tiles_per_expert + job % p.tiles_per_expert;
+        return p.tiles[s] + (uint64_t)job * tile_bytes;
+    }
     return p.tiles[0] + ((uint64_t)s * (p.n_embd / 16) + job) * tile_bytes;
 }
 
@@ -174,8 +183,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     const uint32_t chunks = (nb + kChunkBlocks - 1) / kChunkBlocks;  // per tile
     const uint32_t q_per_job = S * chunks;
     const uint32_t gs = group_size(q_per_job), groups = kConsumers / gs;
-    // Jobs of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ... Job m goes to group m % groups.
-    const uint32_t my_jobs = p.n_jobs > blockIdx.x ? (p.n_jobs - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // Jobs of this CTA: cta, cta + n_ctas, ... Job m goes to group m % groups. A routed plain
+    // product splits the grid among the slots, and a CTA's jobs are the tiles of its slot's expert.
+    const bool slotted = MODE == kPlain && p.route != nullptr;
+    const uint32_t slot = slotted ? blockIdx.x % p.n_used : 0u;
+    const uint32_t cta = slotted ? blockIdx.x / p.n_used : blockIdx.x, n_ctas = slotted ? gridDim.x / p.n_used : gridDim.x;
+    const uint32_t my_jobs = p.n_jobs > cta ? (p.n_jobs - cta + n_ctas - 1) / n_ctas : 0;
     const uint32_t rounds = (my_jobs + groups - 1) / groups;
 
     if (tid == 0) {
@@ -194,6 +207,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
         // Each warp owns kDepth slots; its k-th chunk goes to its slot k % kDepth, so every slot is
         // filled and drained by one pair of threads in strict order.
         if (lane == 0) {
+            uint32_t first_tile = 0;
+            if (p.route) {
+                pdl_wait();  // the routing decides which weights to stream
+                if (slotted) first_tile = p.route[slot] * p.tiles_per_expert;
+            }
             uint32_t issued[kConsumers];
 #pragma unroll
             for (int w = 0; w < kConsumers; ++w) issued[w] = 0;
@@ -215,8 +233,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
                             ok = false;
                             break;
                         }
-                        uint32_t job = blockIdx.x + gridDim.x * (r * groups + grp);
-                        const uint8_t* src = job_tiles<MODE>(p, job, (int)seg, tile_bytes) + (uint64_t)chunk * kStageBytes;
+                        uint32_t job = cta + n_ctas * (r * groups + grp);
+                        const uint8_t* src = job_tiles<MODE>(p, first_tile + job, (int)seg, tile_bytes) + (uint64_t)chunk * kStageBytes;
                         uint32_t bytes = cb * kBlockBytes;
                         mbar_arrive_expect(smem_u32(&full_bar[stage]), bytes);
                         bulk_load(smem_u32(ring + stage * kStageBytes), src, bytes, smem_u32(&full_bar[stage]));
@@ -238,7 +256,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     // the finished rows instead.
     const int ctid = tid;  // consumers are threads 0 .. kConsumers * 32 - 1
     constexpr int kConsumerThreads = kConsumers * 32;
-    const float4* x4 = reinterpret_cast<const float4*>(p.x);
+    const float4* x4 = reinterpret_cast<const float4*>(p.x) + (size_t)slot * nb * 8;
     const float4* w4 = reinterpret_cast<const float4*>(p.norm_weight);
     float sumsq = 0.f, biggest = 0.f;
     for (uint32_t i = ctid; i < nb * 8; i += kConsumerThreads) {
@@ -314,7 +332,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     uint32_t taken = 0;  // chunks this warp has consumed
     bool dead = false;
     for (uint32_t r = 0; r * groups + grp < my_jobs; ++r) {
-        const uint32_t job = blockIdx.x + gridDim.x * (r * groups + grp);
+        const uint32_t job = cta + n_ctas * (r * groups + grp);
         // The thread that will finish a row of a plain product finds the row now and, when the
         // product adds to y, starts reading the old value, so that read overlaps the multiply.
         float* y_row = nullptr;
@@ -328,7 +346,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
             }
             uint32_t row = local * 16 + lane;
             if (row < p.seg_rows[seg]) {
-                y_row = p.y[seg] + row;
+                y_row = p.y[seg] + (size_t)slot * p.seg_rows[seg] + row;
                 if (p.accumulate) y_old = *y_row;
             }
         }
@@ -500,6 +518,11 @@ cudaError_t launch(cudaStream_t stream, Params& p) {
     if (e != cudaSuccess) return e;
     uint32_t cap = kCtasPerSm * (uint32_t)sm_count();
     uint32_t ctas = p.n_jobs < cap ? p.n_jobs : cap;
+    if (MODE == kPlain && p.route) {
+        // The grid is split evenly among the slots; n_jobs counts the tiles of one slot.
+        uint32_t per_slot = cap / p.n_used > 0 ? cap / p.n_used : 1;
+        ctas = p.n_used * (p.n_jobs < per_slot ? p.n_jobs : per_slot);
+    }
     void* args[] = {&p};
     return launch_kernel(kernel, dim3(ctas), dim3(kThreads), smem, stream, args);
 }
@@ -571,6 +594,45 @@ cudaError_t matvec_swiglu_mma(cudaStream_t stream, const Mat& gate, const Mat& u
     p.norm_weight = norm.weight;
     p.eps = norm.eps;
     return launch<kSwiglu>(stream, p);
+}
+
+bool matvec_experts_mma_supported(const Mat& w, uint32_t n_rows, uint32_t n_used) {
+    return w.format == BC_Q4_0 && w.tiles != nullptr && n_rows % 16 == 0 && n_used >= 1 && n_used <= 64;
+}
+
+cudaError_t matvec_experts_swiglu_mma(cudaStream_t stream, const Mat& gate, const Mat& up, uint32_t n_rows, const float* x, const uint32_t* route,
+                                      uint32_t n_used, float* y) {
+    Params p{};
+    p.n_segments = 2;
+    p.tiles[0] = static_cast<const uint8_t*>(gate.tiles);
+    p.tiles[1] = static_cast<const uint8_t*>(up.tiles);
+    p.y[0] = y;
+    p.tiles_per_expert = n_rows / 16;
+    p.n_used = n_used;
+    p.route = route;
+    p.seg_rows[0] = p.seg_rows[1] = n_used * n_rows;  // y holds the slots' rows one after another
+    p.seg_tiles[0] = p.seg_tiles[1] = n_used * p.tiles_per_expert;
+    p.n_jobs = p.seg_tiles[0];
+    p.n_blocks = gate.n_cols / 32;
+    p.x = x;
+    return launch<kSwiglu>(stream, p);
+}
+
+cudaError_t matvec_experts_down_mma(cudaStream_t stream, const Mat& down, uint32_t n_rows, const float* x, const uint32_t* route, uint32_t n_used,
+                                    float* expert_out) {
+    Params p{};
+    p.n_segments = 1;
+    p.tiles[0] = static_cast<const uint8_t*>(down.tiles);
+    p.y[0] = expert_out;
+    p.tiles_per_expert = n_rows / 16;
+    p.n_used = n_used;
+    p.route = route;
+    p.seg_rows[0] = n_rows;
+    p.seg_tiles[0] = 0xffffffffu;  // one segment: a job is a tile of the stack
+    p.n_jobs = p.tiles_per_expert;
+    p.n_blocks = down.n_cols / 32;
+    p.x = x;
+    return launch<kPlain>(stream, p);
 }
 
 cudaError_t matvec_conv_mma(cudaStream_t stream, const Mat& in_proj, const float* x, Norm norm, const float* taps, float* history,

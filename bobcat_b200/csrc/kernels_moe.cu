@@ -398,6 +398,8 @@ cudaError_t moe_group(cudaStream_t stream, const uint32_t* route, uint32_t* offs
 cudaError_t matvec_experts_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, uint32_t n_rows, const float* x,
                                   const uint32_t* route, uint32_t n_used, float* y, uint32_t n_tokens) {
     if (n_tokens == 0) return cudaSuccess;
+    if (n_tokens == 1 && matvec_experts_mma_supported(gate, n_rows, n_used) && up.tiles)
+        return matvec_experts_swiglu_mma(stream, gate, up, n_rows, x, route, n_used, y);
     ExpertsParams p{gate, up, x, route, y, n_rows, n_used};
     unsigned groups = (n_rows + kWarps - 1) / kWarps;
     unsigned cap = (unsigned)sm_count() * 8 / (n_used * n_tokens) + 1;
@@ -410,9 +412,18 @@ cudaError_t matvec_experts_swiglu(cudaStream_t stream, const Mat& gate, const Ma
     }
 }
 
+int matvec_experts_down_launches(const Mat& down, uint32_t n_rows, uint32_t n_used, uint32_t n_tokens, bool has_scratch) {
+    return n_tokens == 1 && has_scratch && matvec_experts_mma_supported(down, n_rows, n_used) ? 2 : 1;
+}
+
 cudaError_t matvec_experts_down(cudaStream_t stream, const Mat& down, uint32_t n_rows, const float* x, const uint32_t* route,
-                                uint32_t n_used, float* y, uint32_t n_tokens) {
+                                uint32_t n_used, float* y, uint32_t n_tokens, float* expert_out) {
     if (n_tokens == 0) return cudaSuccess;
+    if (n_tokens == 1 && expert_out && matvec_experts_mma_supported(down, n_rows, n_used)) {
+        cudaError_t e = matvec_experts_down_mma(stream, down, n_rows, x, route, n_used, expert_out);
+        if (e != cudaSuccess) return e;
+        return moe_combine(stream, expert_out, route, y, n_rows, n_used, 1);
+    }
     ExpertsParams p{down, down, x, route, y, n_rows, n_used};
     unsigned groups = (n_rows + kWarps - 1) / kWarps;
     unsigned cap = (unsigned)sm_count() * 8 / n_tokens + 1;

@@ -194,8 +194,8 @@ struct Recorder {
         if (n == 1) {
             run("matvec_experts_swiglu", n_ff, n_embd, 2 * expert_bytes * n_used, 1,
                 [&] { return k::matvec_experts_swiglu(stream, D.gate, D.up, n_ff, s.normed, s.route, n_used, s.ffn, n); });
-            run("matvec_experts_down", n_embd, n_ff, expert_bytes * n_used, 1,
-                [&] { return k::matvec_experts_down(stream, D.down, n_embd, s.ffn, s.route, n_used, s.hidden, n); });
+            run("matvec_experts_down", n_embd, n_ff, expert_bytes * n_used, k::matvec_experts_down_launches(D.down, n_embd, n_used, n, true),
+                [&] { return k::matvec_experts_down(stream, D.down, n_embd, s.ffn, s.route, n_used, s.hidden, n, s.expert_out); });
             return;
         }
         run("moe_group", n, hp.n_experts, 0, 1, [&] { return k::moe_group(stream, s.route, s.expert_offsets, s.expert_entries, hp.n_experts, n_used, n); });
