@@ -7,10 +7,11 @@
 // weight, more than an SM can issue at the rate HBM delivers weights (40 per clock per SM). Here
 // the multiply-adds run on the tensor cores in integers, which keeps them exact: four nibbles of
 // a word become the signed bytes 16 * (q - 8) with two logic ops, the 16-row weight tile is the A
-// operand of an mma.m16n8k32 (one per block of 32 weights), and the input vector, scaled to 31-bit
-// integers and split into four signed base-256 digits, fills four of the eight columns of B. The
-// digit sums are joined in integers and the fp16 block scale multiplies the per-block result in
-// f32: about 0.6 instructions per weight.
+// operand of an mma.m16n8k32 (one per block of 32 weights), and the input vector, each block of 32
+// values scaled by its own power of two to 31-bit integers and split into four signed base-256
+// digits, fills four of the eight columns of B. The digit sums are joined in integers and the
+// block's two scales (the fp16 weight scale, the input's power of two) multiply the per-block
+// result in f32: about 0.6 instructions per weight.
 // (2) A decode step is a chain of small dependent launches, and a launch that starts its loads
 // only after its input exists idles HBM for microseconds at every link. Here one thread per CTA
 // streams the CTA's share of the matrix into a shared-memory ring with bulk async copies, starting
@@ -172,6 +173,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;                                                   // kStages * kStageBytes
     uint4* xs = reinterpret_cast<uint4*>(smem + kStages * kStageBytes);     // [block][digit][t]: 16 x 8 bytes per block
+    float* x_scale = reinterpret_cast<float*>(smem + kStages * kStageBytes + (size_t)p.n_blocks * 128);  // [block]
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
     __shared__ float reduce_scratch[64];
     __shared__ uint2 zero_columns[kChunkBlocks * 16];  // a chunk's worth of B operand that is all zero
@@ -249,84 +251,74 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     // history) belong to earlier launches.
     pdl_wait();
 
-    // Stage x as the B operand: RMSNorm weights applied, scaled by a power of two so that the
-    // largest |x| lands in [2^29, 2^30), rounded to integers (no change for a value of at least
-    // 2^-7 of the largest, an absolute error below 2^-30 of the largest for the rest) and split
-    // into four signed base-256 digits, one digit per column of B. The norm's scalar and the power of two multiply
-    // the finished rows instead.
+    // Stage x as the B operand in one pass over global memory: RMSNorm weights applied, every
+    // block of 32 values scaled by its own power of two so that its largest magnitude lands in
+    // [2^29, 2^30), rounded to integers (no change for a value of at least 2^-7 of the block's
+    // largest, an absolute error below 2^-30 of it for the rest) and split into four signed
+    // base-256 digits, one digit per column of B. Thread (b, t) holds elements 4t..4t+3 and
+    // 16+4t..16+4t+3 of block b, so a block's maximum is two shuffles among four lanes, and the 8
+    // bytes at xs8[b * 16 + j * 4 + t] take digit j (0 = most significant) of those elements.
+    // The inverse of the block's power of two goes to x_scale[b] and multiplies the block's sum;
+    // the norm's scalar multiplies the finished rows.
     const int ctid = tid;  // consumers are threads 0 .. kConsumers * 32 - 1
     constexpr int kConsumerThreads = kConsumers * 32;
     const float4* x4 = reinterpret_cast<const float4*>(p.x) + (size_t)slot * nb * 8;
     const float4* w4 = reinterpret_cast<const float4*>(p.norm_weight);
-    float sumsq = 0.f, biggest = 0.f;
-    for (uint32_t i = ctid; i < nb * 8; i += kConsumerThreads) {
-        float4 v = x4[i];
-        sumsq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        if (p.norm_weight) {
-            float4 w = __ldg(w4 + i);
-            v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
+    uint2* xs8 = reinterpret_cast<uint2*>(xs);
+    float sumsq = 0.f;
+    for (uint32_t first = (uint32_t)(ctid & ~31); first < nb * 4; first += kConsumerThreads) {
+        const uint32_t i = first + lane, b = i >> 2, t = i & 3;
+        const bool valid = i < nb * 4;
+        float4 lo4 = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo4;
+        if (valid) {
+            lo4 = x4[b * 8 + t];
+            hi4 = x4[b * 8 + 4 + t];
+            sumsq += (lo4.x * lo4.x + lo4.y * lo4.y + lo4.z * lo4.z + lo4.w * lo4.w) + (hi4.x * hi4.x + hi4.y * hi4.y + hi4.z * hi4.z + hi4.w * hi4.w);
+            if (p.norm_weight) {
+                const float4 wl = __ldg(w4 + b * 8 + t), wh = __ldg(w4 + b * 8 + 4 + t);
+                lo4.x *= wl.x; lo4.y *= wl.y; lo4.z *= wl.z; lo4.w *= wl.w;
+                hi4.x *= wh.x; hi4.y *= wh.y; hi4.z *= wh.z; hi4.w *= wh.w;
+            }
         }
-        biggest = fmaxf(biggest, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-        // The weighted values wait in the staging buffer as f32 (a block's 32 floats are the 128
-        // bytes its digits will take), so the second pass needs neither global memory nor the weights.
-        reinterpret_cast<float4*>(xs)[i] = v;
+        const float v[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
+        float top = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) top = fmaxf(top, fabsf(v[e]));
+        top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
+        top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
+        // top lies in [2^(e - 127), 2^(e - 126)) for its exponent field e; 2^(156 - e) brings it
+        // to [2^29, 2^30). Fields below 60 (and zero) share the scale 2^96.
+        const uint32_t field = max(__float_as_uint(top) >> 23, 60u);
+        const float up = __uint_as_float((283u - field) << 23);
+        if (valid) {
+            uint32_t word[2][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t d[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) d[e] = signed_digits(__float2int_rn(v[h * 4 + e] * up));
+                // Transpose the 4 x 4 bytes: word[h][j] = byte 3 - j of the four elements.
+                const uint32_t lo01 = __byte_perm(d[0], d[1], 0x5140), hi01 = __byte_perm(d[0], d[1], 0x7362);
+                const uint32_t lo23 = __byte_perm(d[2], d[3], 0x5140), hi23 = __byte_perm(d[2], d[3], 0x7362);
+                word[h][3] = __byte_perm(lo01, lo23, 0x5410);
+                word[h][2] = __byte_perm(lo01, lo23, 0x7632);
+                word[h][1] = __byte_perm(hi01, hi23, 0x5410);
+                word[h][0] = __byte_perm(hi01, hi23, 0x7632);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) xs8[b * 16 + j * 4 + t] = make_uint2(word[0][j], word[1][j]);
+            if (t == 0) x_scale[b] = __uint_as_float((field - 29u) << 23);  // 1 / up
+        }
     }
     for (int i = ctid; i < kChunkBlocks * 16; i += kConsumerThreads) zero_columns[i] = make_uint2(0u, 0u);
     sumsq = warp_sum(sumsq);
-    biggest = warp_max(biggest);
-    if (lane == 0) {
-        reduce_scratch[warp] = sumsq;
-        reduce_scratch[32 + warp] = biggest;
-    }
+    if (lane == 0) reduce_scratch[warp] = sumsq;
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-    float total = 0.f, top = 0.f;
-    for (int i = 0; i < kConsumers; ++i) {
-        total += reduce_scratch[i];
-        top = fmaxf(top, reduce_scratch[32 + i]);
-    }
+    float total = 0.f;
+    for (int i = 0; i < kConsumers; ++i) total += reduce_scratch[i];
     const float norm_scale = p.norm_weight ? rsqrtf(total / (float)(nb * 32) + p.eps) : 1.f;
-    int exponent = 0;
-    if (top > 0.f) frexpf(top, &exponent);             // top = m * 2^exponent, m in [0.5, 1)
-    // Second pass, in place: the values become integers and the integers signed bytes.
-    const int shift = min(30 - exponent, 96);
-    const float out_scale = norm_scale * exp2f((float)(-shift - 4));  // the weights come as 16 * (q - 8)
-    {
-        // x * up is an integer below 2^30 in magnitude, held exactly as four signed bytes per
-        // element. For block b, digit column j (0 = most significant) and word index t the 8
-        // bytes at xs8[b * 16 + j * 4 + t] hold that digit of elements 4t..4t+3 and 16+4t..16+4t+3.
-        const float up = top > 0.f ? exp2f((float)shift) : 1.f;
-        uint2* xs8 = reinterpret_cast<uint2*>(xs);
-        for (uint32_t first = (uint32_t)(ctid & ~31); first < nb * 4; first += kConsumerThreads) {
-            const uint32_t i = first + lane, b = i >> 2, t = i & 3;
-            const bool valid = i < nb * 4;
-            float4 lo4 = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo4;
-            if (valid) {
-                lo4 = reinterpret_cast<const float4*>(xs)[b * 8 + t];
-                hi4 = reinterpret_cast<const float4*>(xs)[b * 8 + 4 + t];
-            }
-            __syncwarp();  // the four threads of a block have read it before any of them overwrites it
-            if (valid) {
-                const float v[8] = {lo4.x, lo4.y, lo4.z, lo4.w, hi4.x, hi4.y, hi4.z, hi4.w};
-                uint32_t word[2][4];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    uint32_t d[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) d[e] = signed_digits(__float2int_rn(v[h * 4 + e] * up));
-                    // Transpose the 4 x 4 bytes: word[h][j] = byte 3 - j of the four elements.
-                    const uint32_t lo01 = __byte_perm(d[0], d[1], 0x5140), hi01 = __byte_perm(d[0], d[1], 0x7362);
-                    const uint32_t lo23 = __byte_perm(d[2], d[3], 0x5140), hi23 = __byte_perm(d[2], d[3], 0x7362);
-                    word[h][3] = __byte_perm(lo01, lo23, 0x5410);
-                    word[h][2] = __byte_perm(lo01, lo23, 0x7632);
-                    word[h][1] = __byte_perm(hi01, hi23, 0x5410);
-                    word[h][0] = __byte_perm(hi01, hi23, 0x7632);
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) xs8[b * 16 + j * 4 + t] = make_uint2(word[0][j], word[1][j]);
-            }
-        }
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+    const float out_scale = norm_scale * 0.0625f;  // the weights come as 16 * (q - 8)
+
     const int g = lane >> 2, t = lane & 3;
     const uint32_t grp = warp / gs, rank = warp % gs;
     uint32_t taken = 0;  // chunks this warp has consumed
@@ -379,6 +371,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
             const uint2* x_first = g < 4 ? chunk_x : zero_columns + (g & 3) * 4 + t;
             const uint2* x_second = g < 4 ? zero_columns + (g & 3) * 4 + t : chunk_x + 16;
             const uint32_t* scales = reinterpret_cast<const uint32_t*>(slot + cb * 256) + g * 2 + (t >> 1);
+            const float* block_scale = x_scale + chunk * kChunkBlocks + (t >> 1);  // of this lane's block of each pair
             float a0 = 0.f, a1 = 0.f;
 #pragma unroll 4
             for (uint32_t pair = 0; pair < cb / 2; ++pair) {
@@ -389,9 +382,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
                 mma_s8(c, low_nibbles_s8(v.x), low_nibbles_s8(v.y), high_nibbles_s8(v.x), high_nibbles_s8(v.y), xa.x, xa.y);
                 mma_s8_add(c, low_nibbles_s8(v.z), low_nibbles_s8(v.w), high_nibbles_s8(v.z), high_nibbles_s8(v.w), xb.x, xb.y);
                 const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&dw));
-                // Columns 2t and 2t + 1 are neighbouring digits of x, joined before the scale.
-                a0 = fmaf((float)(c[0] * 256 + c[1]), d.x, a0);
-                a1 = fmaf((float)(c[2] * 256 + c[3]), d.y, a1);
+                const float bs = block_scale[pair * 2];
+                // Columns 2t and 2t + 1 are neighbouring digits of x, joined before the scales.
+                a0 = fmaf((float)(c[0] * 256 + c[1]) * bs, d.x, a0);
+                a1 = fmaf((float)(c[2] * 256 + c[3]) * bs, d.y, a1);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
@@ -513,7 +507,7 @@ __global__ void repack_tiles_kernel(const uint4* __restrict__ quants, const __ha
 template <int MODE>
 cudaError_t launch(cudaStream_t stream, Params& p) {
     const void* kernel = (const void*)matvec_mma_kernel<MODE>;
-    size_t smem = (size_t)kStages * kStageBytes + (size_t)p.n_blocks * 128;
+    size_t smem = (size_t)kStages * kStageBytes + (size_t)p.n_blocks * 132;  // ring, digits, block scales
     cudaError_t e = ensure_dynamic_smem(kernel, smem);
     if (e != cudaSuccess) return e;
     uint32_t cap = kCtasPerSm * (uint32_t)sm_count();
@@ -548,7 +542,7 @@ cudaError_t repack_tiles(cudaStream_t stream, const void* quants, const __half* 
 }
 
 cudaError_t matvec_mma_prepare(uint32_t widest_cols) {
-    size_t smem = (size_t)kStages * kStageBytes + (size_t)(widest_cols / 32) * 128;
+    size_t smem = (size_t)kStages * kStageBytes + (size_t)(widest_cols / 32) * 132;
     for (const void* kernel : {(const void*)matvec_mma_kernel<kPlain>, (const void*)matvec_mma_kernel<kSwiglu>, (const void*)matvec_mma_kernel<kConv>}) {
         cudaError_t e = ensure_dynamic_smem(kernel, smem);
         if (e != cudaSuccess) return e;
