@@ -266,13 +266,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     const float4* w4 = reinterpret_cast<const float4*>(p.norm_weight);
     uint2* xs8 = reinterpret_cast<uint2*>(xs);
     float sumsq = 0.f;
-    for (uint32_t first = (uint32_t)(ctid & ~31); first < nb * 4; first += kConsumerThreads) {
-        const uint32_t i = first + lane, b = i >> 2, t = i & 3;
+    // Whole warps call this together: item i is (block, word index) = (i / 4, i % 4).
+    auto stage_item = [&](uint32_t i, float4 lo4, float4 hi4) {
+        const uint32_t b = i >> 2, t = i & 3;
         const bool valid = i < nb * 4;
-        float4 lo4 = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo4;
         if (valid) {
-            lo4 = x4[b * 8 + t];
-            hi4 = x4[b * 8 + 4 + t];
             sumsq += (lo4.x * lo4.x + lo4.y * lo4.y + lo4.z * lo4.z + lo4.w * lo4.w) + (hi4.x * hi4.x + hi4.y * hi4.y + hi4.z * hi4.z + hi4.w * hi4.w);
             if (p.norm_weight) {
                 const float4 wl = __ldg(w4 + b * 8 + t), wh = __ldg(w4 + b * 8 + 4 + t);
@@ -308,6 +306,27 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
 #pragma unroll
             for (int j = 0; j < 4; ++j) xs8[b * 16 + j * 4 + t] = make_uint2(word[0][j], word[1][j]);
             if (t == 0) x_scale[b] = __uint_as_float((field - 29u) << 23);  // 1 / up
+        }
+    };
+    if (nb * 4 <= (uint32_t)kConsumerThreads) {
+        const uint32_t i = (uint32_t)ctid;
+        float4 lo4 = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo4;
+        if (i < nb * 4) {
+            lo4 = x4[(i >> 2) * 8 + (i & 3)];
+            hi4 = x4[(i >> 2) * 8 + 4 + (i & 3)];
+        }
+        if ((uint32_t)(ctid & ~31) < nb * 4) stage_item(i, lo4, hi4);
+    } else {
+        // The loads of a thread's next item go out before it works on the current one.
+        float4 next_lo = x4[((uint32_t)ctid >> 2) * 8 + (ctid & 3)], next_hi = x4[((uint32_t)ctid >> 2) * 8 + 4 + (ctid & 3)];
+        for (uint32_t first = (uint32_t)(ctid & ~31); first < nb * 4; first += kConsumerThreads) {
+            const uint32_t i = first + lane, ahead = i + kConsumerThreads;
+            const float4 lo4 = next_lo, hi4 = next_hi;
+            if (ahead < nb * 4) {
+                next_lo = x4[(ahead >> 2) * 8 + (ahead & 3)];
+                next_hi = x4[(ahead >> 2) * 8 + 4 + (ahead & 3)];
+            }
+            stage_item(i, lo4, hi4);
         }
     }
     for (int i = ctid; i < kChunkBlocks * 16; i += kConsumerThreads) zero_columns[i] = make_uint2(0u, 0u);
