@@ -361,6 +361,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
                 if (p.accumulate) y_old = *y_row;
             }
         }
+        // The same for the conv: the channel's taps and history (kernels of up to kMaxTaps taps)
+        // are on their way while the products run.
+        constexpr int kMaxTaps = 4;
+        float tap[kMaxTaps], past[kMaxTaps - 1];
+        const bool taps_early = MODE == kConv && p.conv_kernel <= (uint32_t)kMaxTaps && rank == 0 && lane < 16 && job * 16 + lane < p.n_embd;
+        if (taps_early) {
+            const uint32_t ch = job * 16 + lane;
+#pragma unroll
+            for (int kk = 0; kk < kMaxTaps; ++kk)
+                if ((uint32_t)kk < p.conv_kernel) tap[kk] = p.taps[(uint64_t)ch * p.conv_kernel + kk];
+#pragma unroll
+            for (int kk = 0; kk < kMaxTaps - 1; ++kk)
+                if ((uint32_t)kk + 1 < p.conv_kernel) past[kk] = p.history[(uint64_t)kk * p.n_embd + ch];
+        }
         float acc[S][2];
 #pragma unroll
         for (int s = 0; s < S; ++s) acc[s][0] = acc[s][1] = 0.f;
@@ -466,12 +480,28 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
                     float b = sum[0], c = sum[S > 1 ? 1 : 0], xv = sum[S > 2 ? 2 : 0];
                     float bx = b * xv;
                     const uint32_t K = p.conv_kernel;
-                    const float* taps = p.taps + (uint64_t)ch * K;
-                    float total_taps = taps[K - 1] * bx;
-                    for (uint32_t kk = 0; kk + 1 < K; ++kk) total_taps += taps[kk] * p.history[(uint64_t)kk * p.n_embd + ch];
-                    for (uint32_t kk = 0; kk + 2 < K; ++kk) p.history[(uint64_t)kk * p.n_embd + ch] = p.history[(uint64_t)(kk + 1) * p.n_embd + ch];
-                    p.history[(uint64_t)(K - 2) * p.n_embd + ch] = bx;
-                    p.y[0][ch] = c * total_taps;
+                    if (taps_early) {
+                        float last_tap = 0.f;
+#pragma unroll
+                        for (int kk = 0; kk < kMaxTaps; ++kk)
+                            if ((uint32_t)kk + 1 == K) last_tap = tap[kk];
+                        float total_taps = last_tap * bx;
+#pragma unroll
+                        for (int kk = 0; kk < kMaxTaps - 1; ++kk)
+                            if ((uint32_t)kk + 1 < K) total_taps += tap[kk] * past[kk];
+#pragma unroll
+                        for (int kk = 0; kk < kMaxTaps - 2; ++kk)
+                            if ((uint32_t)kk + 2 < K) p.history[(uint64_t)kk * p.n_embd + ch] = past[kk + 1];
+                        p.history[(uint64_t)(K - 2) * p.n_embd + ch] = bx;
+                        p.y[0][ch] = c * total_taps;
+                    } else {
+                        const float* taps = p.taps + (uint64_t)ch * K;
+                        float total_taps = taps[K - 1] * bx;
+                        for (uint32_t kk = 0; kk + 1 < K; ++kk) total_taps += taps[kk] * p.history[(uint64_t)kk * p.n_embd + ch];
+                        for (uint32_t kk = 0; kk + 2 < K; ++kk) p.history[(uint64_t)kk * p.n_embd + ch] = p.history[(uint64_t)(kk + 1) * p.n_embd + ch];
+                        p.history[(uint64_t)(K - 2) * p.n_embd + ch] = bx;
+                        p.y[0][ch] = c * total_taps;
+                    }
                 }
             }
         }
