@@ -191,7 +191,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     const uint32_t slot = slotted ? blockIdx.x % p.n_used : 0u;
     const uint32_t cta = slotted ? blockIdx.x / p.n_used : blockIdx.x, n_ctas = slotted ? gridDim.x / p.n_used : gridDim.x;
     const uint32_t my_jobs = p.n_jobs > cta ? (p.n_jobs - cta + n_ctas - 1) / n_ctas : 0;
-    const uint32_t rounds = (my_jobs + groups - 1) / groups;
 
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
@@ -204,43 +203,34 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     pdl_launch_dependents();
 
     if (warp == kConsumers) {
-        // ---- producer: one thread streams this CTA's chunks into the ring in the order the
-        // consumers take them: round by round, chunk position by chunk position, group by group.
-        // Each warp owns kDepth slots; its k-th chunk goes to its slot k % kDepth, so every slot is
-        // filled and drained by one pair of threads in strict order.
-        if (lane == 0) {
+        // ---- producers: lane w of this warp streams consumer warp w's chunks into that warp's
+        // kDepth slots, in the order the warp takes them (its group's jobs round by round, every
+        // gs-th chunk of a job), so every slot is filled and drained by one pair of threads in
+        // strict order and the first copies of all warps go out side by side.
+        if (lane < kConsumers) {
+            const uint32_t w = lane, grp = w / gs, rank = w % gs;
             uint32_t first_tile = 0;
             if (p.route) {
                 pdl_wait();  // the routing decides which weights to stream
                 if (slotted) first_tile = p.route[slot] * p.tiles_per_expert;
             }
-            uint32_t issued[kConsumers];
-#pragma unroll
-            for (int w = 0; w < kConsumers; ++w) issued[w] = 0;
+            uint32_t k = 0;
             bool ok = true;
-            for (uint32_t r = 0; r < rounds && ok; ++r) {
-                uint32_t in_round = min(groups, my_jobs - r * groups);
-                for (uint32_t q = 0; q < q_per_job && ok; ++q) {
-                    uint32_t seg = q / chunks, chunk = q % chunks;
-                    uint32_t cb = min((uint32_t)kChunkBlocks, nb - chunk * kChunkBlocks);
-                    for (uint32_t grp = 0; grp < in_round; ++grp) {
-                        uint32_t w = grp * gs + q % gs;
-                        uint32_t k = 0;
-#pragma unroll
-                        for (int i = 0; i < kConsumers; ++i)
-                            if ((uint32_t)i == w) k = issued[i]++;
-                        uint32_t stage = w * kDepth + k % kDepth, use = k / kDepth;
-                        if (use > 0 && !mbar_wait(smem_u32(&empty_bar[stage]), (use - 1) & 1)) {
-                            atomicExch(&g_error_flag, 1);
-                            ok = false;
-                            break;
-                        }
-                        uint32_t job = cta + n_ctas * (r * groups + grp);
-                        const uint8_t* src = job_tiles<MODE>(p, first_tile + job, (int)seg, tile_bytes) + (uint64_t)chunk * kStageBytes;
-                        uint32_t bytes = cb * kBlockBytes;
-                        mbar_arrive_expect(smem_u32(&full_bar[stage]), bytes);
-                        bulk_load(smem_u32(ring + stage * kStageBytes), src, bytes, smem_u32(&full_bar[stage]));
+            for (uint32_t r = 0; r * groups + grp < my_jobs && ok; ++r) {
+                const uint32_t job = cta + n_ctas * (r * groups + grp);
+                for (uint32_t q = rank; q < q_per_job; q += gs, ++k) {
+                    const uint32_t seg = q / chunks, chunk = q % chunks;
+                    const uint32_t cb = min((uint32_t)kChunkBlocks, nb - chunk * kChunkBlocks);
+                    const uint32_t stage = w * kDepth + k % kDepth, use = k / kDepth;
+                    if (use > 0 && !mbar_wait(smem_u32(&empty_bar[stage]), (use - 1) & 1)) {
+                        atomicExch(&g_error_flag, 1);
+                        ok = false;
+                        break;
                     }
+                    const uint8_t* src = job_tiles<MODE>(p, first_tile + job, (int)seg, tile_bytes) + (uint64_t)chunk * kStageBytes;
+                    const uint32_t bytes = cb * kBlockBytes;
+                    mbar_arrive_expect(smem_u32(&full_bar[stage]), bytes);
+                    bulk_load(smem_u32(ring + stage * kStageBytes), src, bytes, smem_u32(&full_bar[stage]));
                 }
             }
         }
