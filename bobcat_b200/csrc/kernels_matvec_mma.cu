@@ -13,12 +13,16 @@
 // block's two scales (the fp16 weight scale, the input's power of two) multiply the per-block
 // result in f32: about 0.6 instructions per weight.
 // (2) A decode step is a chain of small dependent launches, and a launch that starts its loads
-// only after its input exists idles HBM for microseconds at every link. Here one thread per CTA
-// streams the CTA's share of the matrix into a shared-memory ring with bulk async copies, starting
-// before the kernel waits for its predecessor (programmatic dependent launch): the weights depend
-// on nothing, only the few kilobytes of activations do. A CTA is 8 consumer warps and the
-// producer, with a 16-slot ring, small enough for two CTAs per SM: the next launch's CTAs move in
-// next to the running ones and fill their rings while those still compute.
+// only after its input exists idles HBM for microseconds at every link. Here every warp streams
+// its own share of the matrix into its two slots of a shared-memory ring with bulk async copies
+// (lane 0 issues them, an mbarrier per slot reports their arrival, every wait is bounded), and the
+// first copies go out before the kernel waits for its predecessor (programmatic dependent launch):
+// the weights depend on nothing, only the few kilobytes of activations do. A slot is refilled by
+// the warp that has just read it, so there is no producer to hand it back to. A CTA is 8 warps
+// with a 16-slot ring, small enough for two CTAs per SM: the next launch's CTAs move in next to
+// the running ones and fill their rings while those still compute. (A single thread issuing all
+// of a CTA's copies was the largest cost of this kernel once the multiplies were cheap: the
+// sixteenth copy left more than a microsecond after the first. A lane per warp: +9 % tokens/s.)
 //
 // Layout ("tiles"): rows in tiles of 16, columns in chunks of 16 blocks. A chunk of a tile is
 // contiguous: for each pair of blocks 512 bytes ordered by lane - lane (g, t) = (lane / 4, lane % 4)
@@ -41,9 +45,9 @@ namespace k {
 
 namespace {
 
-constexpr int kConsumers = 8;                    // consumer warps per CTA
-constexpr int kThreads = (kConsumers + 1) * 32;  // plus the producer warp
-constexpr int kDepth = 2;                        // ring slots per consumer warp
+constexpr int kConsumers = 8;                    // warps per CTA
+constexpr int kThreads = kConsumers * 32;
+constexpr int kDepth = 2;                        // ring slots per warp
 constexpr uint32_t kCtasPerSm = 2;               // CTAs a launch may put on one SM (registers and the ring allow two)
 constexpr int kStages = kConsumers * kDepth;
 constexpr int kChunkBlocks = 16;                 // blocks of 32 weights per chunk of a tile
@@ -59,9 +63,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -160,7 +161,7 @@ __device__ __forceinline__ const uint8_t* job_tiles(const Params& p, uint32_t jo
 
 // Warps per group: the warps of a group share one job, taking its chunks in turn, so a CTA with only
 // a few jobs still keeps all its warps busy. The smallest power of two that covers the job's
-// chunks, at most all consumers.
+// chunks, at most all warps.
 __device__ __forceinline__ uint32_t group_size(uint32_t q_per_job) {
     uint32_t gs = 1;
     while (gs < (uint32_t)kConsumers && gs < q_per_job) gs *= 2;
@@ -174,7 +175,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     uint8_t* ring = smem;                                                   // kStages * kStageBytes
     uint4* xs = reinterpret_cast<uint4*>(smem + kStages * kStageBytes);     // [block][digit][t]: 16 x 8 bytes per block
     float* x_scale = reinterpret_cast<float*>(smem + kStages * kStageBytes + (size_t)p.n_blocks * 128);  // [block]
-    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
+    __shared__ __align__(8) uint64_t full_bar[kStages];
     __shared__ float reduce_scratch[64];
     __shared__ uint2 zero_columns[kChunkBlocks * 16];  // a chunk's worth of B operand that is all zero
     __shared__ float partial[2][kConsumers][3 * 16];  // [job parity][warp][segment * 16 + row in tile]
@@ -195,51 +196,48 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
             mbar_init(smem_u32(&full_bar[i]), 1);
-            mbar_init(smem_u32(&empty_bar[i]), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     pdl_launch_dependents();
 
-    if (warp == kConsumers) {
-        // ---- producers: lane w of this warp streams consumer warp w's chunks into that warp's
-        // kDepth slots, in the order the warp takes them (its group's jobs round by round, every
-        // gs-th chunk of a job), so every slot is filled and drained by one pair of threads in
-        // strict order and the first copies of all warps go out side by side.
-        if (lane < kConsumers) {
-            const uint32_t w = lane, grp = w / gs, rank = w % gs;
-            uint32_t first_tile = 0;
-            if (p.route) {
-                pdl_wait();  // the routing decides which weights to stream
-                if (slotted) first_tile = p.route[slot] * p.tiles_per_expert;
-            }
-            uint32_t k = 0;
-            bool ok = true;
-            for (uint32_t r = 0; r * groups + grp < my_jobs && ok; ++r) {
-                const uint32_t job = cta + n_ctas * (r * groups + grp);
-                for (uint32_t q = rank; q < q_per_job; q += gs, ++k) {
-                    const uint32_t seg = q / chunks, chunk = q % chunks;
-                    const uint32_t cb = min((uint32_t)kChunkBlocks, nb - chunk * kChunkBlocks);
-                    const uint32_t stage = w * kDepth + k % kDepth, use = k / kDepth;
-                    if (use > 0 && !mbar_wait(smem_u32(&empty_bar[stage]), (use - 1) & 1)) {
-                        atomicExch(&g_error_flag, 1);
-                        ok = false;
-                        break;
-                    }
-                    const uint8_t* src = job_tiles<MODE>(p, first_tile + job, (int)seg, tile_bytes) + (uint64_t)chunk * kStageBytes;
-                    const uint32_t bytes = cb * kBlockBytes;
-                    mbar_arrive_expect(smem_u32(&full_bar[stage]), bytes);
-                    bulk_load(smem_u32(ring + stage * kStageBytes), src, bytes, smem_u32(&full_bar[stage]));
-                }
-            }
-        }
-        return;
+    // ---- Every warp streams its own chunks: lane 0 copies the warp's next chunk into the slot
+    // the warp has just finished reading, in the order the warp takes them (its group's jobs round
+    // by round, every gs-th chunk of a job). The first kDepth copies go out now, before the wait
+    // for the predecessor, unless the routing (a predecessor's output) picks the weights.
+    const uint32_t grp = warp / gs, rank = warp % gs;
+    uint32_t first_tile = 0;
+    if (p.route) {
+        pdl_wait();
+        if (slotted) first_tile = p.route[slot] * p.tiles_per_expert;
     }
+    uint32_t ahead_r = 0, ahead_q = rank, issued = 0;  // the next chunk to copy and how many were
+    auto copy_next = [&]() {
+        if (ahead_r * groups + grp >= my_jobs) return;
+        if (lane == 0) {
+            const uint32_t job = cta + n_ctas * (ahead_r * groups + grp);
+            const uint32_t seg = ahead_q / chunks, chunk = ahead_q % chunks;
+            const uint32_t cb = min((uint32_t)kChunkBlocks, nb - chunk * kChunkBlocks);
+            const uint32_t stage = warp * kDepth + issued % kDepth;
+            const uint8_t* src = job_tiles<MODE>(p, first_tile + job, (int)seg, tile_bytes) + (uint64_t)chunk * kStageBytes;
+            const uint32_t bytes = cb * kBlockBytes;
+            mbar_arrive_expect(smem_u32(&full_bar[stage]), bytes);
+            bulk_load(smem_u32(ring + stage * kStageBytes), src, bytes, smem_u32(&full_bar[stage]));
+        }
+        ++issued;
+        ahead_q += gs;
+        if (ahead_q >= q_per_job) {
+            ahead_q = rank;
+            ++ahead_r;
+        }
+    };
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) copy_next();
 
-    // ---- consumers. Everything above touched only weights; the input vector (and y, the conv
-    // history) belong to earlier launches.
-    pdl_wait();
+    // Everything above touched only weights; the input vector (and y, the conv history) belong
+    // to earlier launches.
+    if (!p.route) pdl_wait();
 
     // Stage x as the B operand in one pass over global memory: RMSNorm weights applied, every
     // block of 32 values scaled by its own power of two so that its largest magnitude lands in
@@ -250,7 +248,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     // bytes at xs8[b * 16 + j * 4 + t] take digit j (0 = most significant) of those elements.
     // The inverse of the block's power of two goes to x_scale[b] and multiplies the block's sum;
     // the norm's scalar multiplies the finished rows.
-    const int ctid = tid;  // consumers are threads 0 .. kConsumers * 32 - 1
+    const int ctid = tid;
     constexpr int kConsumerThreads = kConsumers * 32;
     const float4* x4 = reinterpret_cast<const float4*>(p.x) + (size_t)slot * nb * 8;
     const float4* w4 = reinterpret_cast<const float4*>(p.norm_weight);
@@ -329,7 +327,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     const float out_scale = norm_scale * 0.0625f;  // the weights come as 16 * (q - 8)
 
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t grp = warp / gs, rank = warp % gs;
     uint32_t taken = 0;  // chunks this warp has consumed
     bool dead = false;
     for (uint32_t r = 0; r * groups + grp < my_jobs; ++r) {
@@ -410,8 +407,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
                 a0 = fmaf((float)(c[0] * 256 + c[1]) * bs, d.x, a0);
                 a1 = fmaf((float)(c[2] * 256 + c[3]) * bs, d.y, a1);
             }
+            // The slot is read out: order the reads before the copy engine's writes, then refill it.
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            copy_next();
 #pragma unroll
             for (int s = 0; s < S; ++s) {
                 if ((uint32_t)s == s_of_q) {
