@@ -209,13 +209,9 @@ template <int HD, int GROUP, bool FUSED>
 __global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(ChunkParams p) {
     constexpr int kLanesPerRow = HD / 8, kRowsPerLoad = 32 / kLanesPerRow, kWarps = kDecodeThreads / 32;
     pdl_launch_dependents();
-    pdl_wait();
     const uint32_t kv_head = blockIdx.x, chunk = blockIdx.y, qi = blockIdx.z;
     const uint32_t query = p.query0 + qi;
-    const uint32_t pos = p.first_pos + (p.pos_ptr ? *p.pos_ptr : 0u) + query;
     const uint32_t start = chunk * p.chunk;
-    if (start > pos) return;
-    const uint32_t count = min(p.chunk, pos + 1 - start);
     const uint32_t group = p.n_heads / p.n_kv_heads, kv_dim = p.n_kv_heads * HD;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int sub = lane / kLanesPerRow, d0 = (lane % kLanesPerRow) * 8;
@@ -227,10 +223,22 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(ChunkP
 
     // The first row's loads go out before the query arrives. `base` is the same for the whole
     // warp, so the shuffles below run with every lane present; rows past the chunk's end only skip
-    // the update.
+    // the update. In the fused step the cache rows of earlier positions were written by earlier
+    // tokens' launches, long finished, so these loads also go out before the wait for the
+    // predecessor, for every row of the chunk inside the context: which rows count is known
+    // after the wait, and the new position's row is replaced below. They bypass L1, which must
+    // not keep a row read before it was written.
     uint32_t base = warp * kRowsPerLoad;
     uint4 k_raw = make_uint4(0, 0, 0, 0), v_raw = make_uint4(0, 0, 0, 0);
-    if (base + sub < count) {
+    if (FUSED && base + sub < p.chunk && start + base + sub < p.n_ctx) {
+        k_raw = __ldcg(reinterpret_cast<const uint4*>(kc + (uint64_t)(base + sub) * kv_dim));
+        v_raw = __ldcg(reinterpret_cast<const uint4*>(vc + (uint64_t)(base + sub) * kv_dim));
+    }
+    pdl_wait();
+    const uint32_t pos = p.first_pos + (p.pos_ptr ? *p.pos_ptr : 0u) + query;
+    if (start > pos) return;
+    const uint32_t count = min(p.chunk, pos + 1 - start);
+    if (!FUSED && base + sub < count) {
         k_raw = __ldg(reinterpret_cast<const uint4*>(kc + (uint64_t)(base + sub) * kv_dim));
         v_raw = __ldg(reinterpret_cast<const uint4*>(vc + (uint64_t)(base + sub) * kv_dim));
     }
@@ -303,13 +311,12 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_kernel(ChunkP
         unpack_row(v_raw, vf);
         const bool valid = base + sub < count;
         const uint32_t next = base + kWarps * kRowsPerLoad;
-        if (next + sub < count) {
+        if (holds_new && next + sub == new_row) {
+            k_raw = k_new;  // not in the cache when this launch began: never read it from there
+            v_raw = v_new;
+        } else if (next + sub < count) {
             k_raw = __ldg(reinterpret_cast<const uint4*>(kc + (uint64_t)(next + sub) * kv_dim));
             v_raw = __ldg(reinterpret_cast<const uint4*>(vc + (uint64_t)(next + sub) * kv_dim));
-            if (holds_new && next + sub == new_row) {
-                k_raw = k_new;
-                v_raw = v_new;
-            }
         }
 #pragma unroll
         for (int g = 0; g < GROUP; ++g) {
@@ -439,6 +446,18 @@ __global__ void attention_combine_kernel(CombineParams p) {
     const uint32_t query = p.query0 + qi, pos = p.first_pos + (p.pos_ptr ? *p.pos_ptr : 0u) + query;
     const uint32_t n_chunks = pos / p.chunk + 1;
     const float* base = p.scratch + ((uint64_t)qi * p.n_heads + head) * p.max_chunks * (hd + 2);
+    // With up to kCombineParts * kCombineHeld chunks a thread's share of the weighted values is
+    // read now, together with the maxima, so the combine costs one trip to L2 instead of three.
+    constexpr int kCombineHeld = 16;
+    const bool held = n_chunks <= (uint32_t)(kCombineParts * kCombineHeld);
+    float mine[kCombineHeld];
+    if (held) {
+#pragma unroll
+        for (int j = 0; j < kCombineHeld; ++j) {
+            const uint32_t c = part + (uint32_t)j * kCombineParts;
+            mine[j] = c < n_chunks ? base[(uint64_t)c * (hd + 2) + 2 + d] : 0.f;
+        }
+    }
     float m = -INFINITY;
     for (uint32_t c = tid; c < n_chunks; c += blockDim.x) m = fmaxf(m, base[(uint64_t)c * (hd + 2)]);
     m = warp_max(m);
@@ -457,8 +476,16 @@ __global__ void attention_combine_kernel(CombineParams p) {
             sum += w * at[1];
         }
         __syncthreads();
+        if (held) {
+#pragma unroll
+            for (int j = 0; j < kCombineHeld; ++j) {
+                const uint32_t c = part + (uint32_t)j * kCombineParts;
+                if (c < count) acc += weights[c] * mine[j];
+            }
+        } else {
 #pragma unroll 8
-        for (uint32_t c = part; c < count; c += kCombineParts) acc += weights[c] * base[(uint64_t)(c0 + c) * (hd + 2) + 2 + d];
+            for (uint32_t c = part; c < count; c += kCombineParts) acc += weights[c] * base[(uint64_t)(c0 + c) * (hd + 2) + 2 + d];
+        }
     }
     sum = warp_sum(sum);
     __syncthreads();  // the maxima in `across` have been read
