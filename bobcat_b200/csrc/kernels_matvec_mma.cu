@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
     }
     uint32_t ahead_r = 0, ahead_q = rank, issued = 0;  // the next chunk to copy and how many were
     auto copy_next = [&]() {
-        if (ahead_r * groups + grp >= my_jobs) return;
+        if (ahead_q >= q_per_job || ahead_r * groups + grp >= my_jobs) return;  // a group may have more warps than a job has chunks
         if (lane == 0) {
             const uint32_t job = cta + n_ctas * (ahead_r * groups + grp);
             const uint32_t seg = ahead_q / chunks, chunk = ahead_q % chunks;
