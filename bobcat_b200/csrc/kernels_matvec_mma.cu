@@ -14,18 +14,20 @@
 // result in f32: about 0.6 instructions per weight.
 // (2) A decode step is a chain of small dependent launches, and a launch that starts its loads
 // only after its input exists idles HBM for microseconds at every link. Here every warp streams
-// its own share of the matrix into its two slots of a shared-memory ring with bulk async copies
+// its own share of the matrix into its slot of a shared-memory ring with bulk async copies
 // (lane 0 issues them, an mbarrier per slot reports their arrival, every wait is bounded), and the
 // first copies go out before the kernel waits for its predecessor (programmatic dependent launch):
 // the weights depend on nothing, only the few kilobytes of activations do. A slot is refilled by
-// the warp that has just read it, so there is no producer to hand it back to. A CTA is 16 warps
-// with a 32-slot ring (147 KB), one per SM: with every warp issuing its own copies this measured
-// a little ahead of two 8-warp CTAs per SM (one staging of the input per SM instead of two), by
-// 0.3 to 4 % over the four model shapes. (A single thread issuing all
-// of a CTA's copies was the largest cost of this kernel once the multiplies were cheap: the
-// sixteenth copy left more than a microsecond after the first. A lane per warp: +9 % tokens/s.)
+// the warp that has just read it, so there is no producer to hand it back to. A CTA is 16 warps,
+// one CTA per SM, and a warp has one slot of 32 blocks (9 KB): 147 KB in flight per SM. Measured on
+// the 2.6B shape with every warp issuing its own copies: two 8-warp CTAs per SM with two 16-block
+// slots per warp 1 170 tok/s, this CTA with two 16-block slots 1 184, with one 16-block slot 1 195,
+// with one 32-block slot 1 226 - fewer, larger copies and fewer bytes queued ahead of the input's
+// loads, which wait behind the ring's copies once the dependency wait releases. (A single thread
+// issuing all of a CTA's copies was the largest cost of this kernel once the multiplies were
+// cheap: the sixteenth copy left more than a microsecond after the first. A lane per warp: +9 %.)
 //
-// Layout ("tiles"): rows in tiles of 16, columns in chunks of 16 blocks. A chunk of a tile is
+// Layout ("tiles"): rows in tiles of 16, columns in chunks of 32 blocks. A chunk of a tile is
 // contiguous: for each pair of blocks 512 bytes ordered by lane - lane (g, t) = (lane / 4, lane % 4)
 // holds word t of the quants of rows g and g + 8 for both blocks, exactly its A-fragment share -
 // then the chunk's fp16 scales, 8 bytes per (block pair, g): rows g and g + 8 of the first block,
@@ -48,10 +50,10 @@ namespace {
 
 constexpr int kConsumers = 16;                   // warps per CTA
 constexpr int kThreads = kConsumers * 32;
-constexpr int kDepth = 2;                        // ring slots per warp
+constexpr int kDepth = 1;                        // ring slots per warp
 constexpr uint32_t kCtasPerSm = 1;               // CTAs a launch may put on one SM
 constexpr int kStages = kConsumers * kDepth;
-constexpr int kChunkBlocks = 16;                 // blocks of 32 weights per chunk of a tile
+constexpr int kChunkBlocks = 32;                 // blocks of 32 weights per chunk of a tile
 constexpr int kBlockBytes = 288;                 // 16 rows x 18 bytes
 constexpr int kStageBytes = kChunkBlocks * kBlockBytes;
 constexpr uint32_t kSpinLimit = 1u << 22;        // bounded waits: give up rather than hang
