@@ -31,13 +31,34 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-PROMPT_TOKENS, DECODE_TOKENS = 512, 128
+PROMPT_TOKENS, DECODE_TOKENS, PREFILL_CHUNK = 512, 128, 512
 # The reference's headline metric; `value` is its decode half, the prefill half rides along under "prefill".
 METRIC = "decode & prefill tok/s, Q4 LFM2.5-2.6B-shape, batch 1; % of HBM roofline"
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
-# capture summarised in profiles/matvec_mma_lfm2-2.6b_decode.md (null for kernels not captured).
-NCU_DRAM_BYTES_PER_LAUNCH = {"matvec_swiglu 10752x2048": 24819456}
+# Request shape per configuration: (prompt tokens, decode tokens, prefill chunk). The headline shape
+# follows the reference benchmark (512 + 128, one prefill call); the others follow the run each
+# configuration is specified with.
+PROTOCOLS = {
+    "lfm2-350m": (128, 64, 128),
+    "lfm2-2.6b": (512, 128, 512),
+    "qwen35-2b": (2048, 256, 64),
+    "lfm2moe-8b-a1b": (256, 128, 256),
+    "qwen35-9b": (2048, 256, 512),
+}
+
+
+def recorded_traffic(kernel_key: str):
+    """DRAM bytes per launch of `kernel_key` ("name ROWSxCOLS") from the profiler summaries under
+    profiles/: lines of the form `traffic <name> <rows>x<cols> <bytes>`. None when no summary
+    records that kernel and shape."""
+    import glob
+    import re
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", "*.md")) + glob.glob(os.path.join(ROOT, "profiles", "*.txt"))):
+        for line in open(path, errors="replace"):
+            m = re.match(r"^\s*traffic\s+(\S+)\s+(\d+x\d+)\s+(\d+)\s*$", line)
+            if m and "%s %s" % (m.group(1), m.group(2)) == kernel_key:
+                return int(m.group(3))
+    return None
 
 
 def measured_peaks() -> tuple[float, float, str]:
@@ -112,12 +133,12 @@ def model_file(config: str) -> str:
     return synth.cached_model(config, seed=0, directory=os.environ.get("BOBCAT_SYNTH_DIR", os.path.join(tempfile.gettempdir(), "bobcat_synth")))
 
 
-def cpu_sample(path: str, n_vocab: int, threads: int, n_prompt: int, n_decode: int) -> tuple[float, float]:
+def cpu_sample(path: str, threads: int, n_prompt: int, n_decode: int) -> tuple[float, float]:
     """Run the CPU restatement on a short request. Returns (decode tok/s, seconds)."""
     from oracle import oracle
     model = oracle.Model(path, threads=threads)
     state = model.state(n_prompt + n_decode + 1)
-    prompt = prompt_for(n_vocab, 1)[:n_prompt]
+    prompt = prompt_for(model.n_vocab, 1)[:n_prompt]
     logits = None
     for i, tok in enumerate(prompt):
         logits = state.step(int(tok), want_logits=(i == n_prompt - 1)).get("logits")
@@ -132,14 +153,13 @@ def run_reference(args) -> None:
     rank, _, world = rank_info()
     if rank != 0:
         return
-    from bobcat_b200 import Model
+    # This arm runs the CPU restatement only: it neither loads the CUDA library nor touches a GPU.
     path = model_file(args.config)
-    n_vocab = Model.load(path).hyperparameters().n_vocab
     threads = len(os.sched_getaffinity(0))
     n_prompt, n_decode = 4, 4
     times = []
     for i in range(args.warmup + args.steps):
-        rate, seconds = cpu_sample(path, n_vocab, threads, n_prompt, n_decode)
+        rate, seconds = cpu_sample(path, threads, n_prompt, n_decode)
         if i >= args.warmup:
             times.append(seconds)
     ms_per_step = 1e3 * float(np.mean(times))
@@ -148,7 +168,7 @@ def run_reference(args) -> None:
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (f64 sums)", "data": "synthetic",
-        "config": {"workload": "%s Q4_0, batch 1, decode after a short prompt (bounded sample of the 512+128 request)" % args.config},
+        "config": {"workload": "%s Q4_0, batch 1, decode after a short prompt (bounded sample of the %d+%d request)" % (args.config, PROMPT_TOKENS, DECODE_TOKENS)},
         "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -180,6 +200,42 @@ def dominant_kernel(cuda, seq, prompt) -> dict:
     per_launch_bytes = top["bytes"] / top["calls"]
     return {"top": top, "share": top["seconds"] / total, "seconds": per_launch_s, "bytes": per_launch_bytes,
             "table": rows_of(entries, 8), "prefill_table": prefill_table}
+
+
+def in_graph_costs(seq, prompt, table, full_token_seconds: float) -> list[dict]:
+    """What each kind of launch costs inside the replayed decode step, where launches overlap their
+    neighbours: the step is re-captured with that kind left out and the difference in time per token
+    is divided by its launches per token. (The per-launch event timing of `dominant_kernel`
+    serialises launches, so it over-states kernels that normally start under their predecessor.)"""
+    per_token = DECODE_TOKENS
+
+    def decode_seconds():
+        seq.reset()
+        seq.prefill(prompt)
+        seq.generate(per_token)
+        return seq.last_gpu_seconds() / per_token
+
+    out = []
+    steps = min(16, DECODE_TOKENS)
+    try:
+        full = decode_seconds()
+        seen = set()
+        for row in table:
+            # Attention launches are recorded with their position as the column count, which the
+            # replayed step does not carry: leave every launch of that name out together.
+            by_name = row["kernel"].startswith("attention")
+            key = (row["kernel"],) if by_name else (row["kernel"], row["rows"], row["cols"])
+            if key in seen:
+                continue
+            seen.add(key)
+            seq.set_skip(row["kernel"], 0 if by_name else row["rows"], 0 if by_name else row["cols"])
+            without = decode_seconds()
+            calls_per_token = sum(r["calls"] for r in table if r["kernel"] == row["kernel"]) / steps if by_name else row["calls"] / steps
+            out.append({"kernel": row["kernel"], "rows": row["rows"], "cols": row["cols"], "calls_per_token": calls_per_token,
+                        "us": 1e6 * (full - without) / calls_per_token if calls_per_token else None})
+    finally:
+        seq.set_skip(None)
+    return out
 
 
 def run_ours(args) -> None:
@@ -221,10 +277,13 @@ def run_ours(args) -> None:
         """One request through the public API with host buffers (pinned prompt ids in, token ids out).
         Returns device and wall seconds."""
         seq.reset()
+        ids = prompts[i % len(prompts)].numpy().view(np.uint32)
         t0 = time.perf_counter()
-        seq.prefill(prompts[i % len(prompts)].numpy().view(np.uint32))
+        prefill_gpu = 0.0
+        for first in range(0, PROMPT_TOKENS, PREFILL_CHUNK):
+            seq.prefill(ids[first:first + PREFILL_CHUNK])
+            prefill_gpu += seq.last_gpu_seconds()
         t1 = time.perf_counter()
-        prefill_gpu = seq.last_gpu_seconds()
         tokens = seq.generate(DECODE_TOKENS)
         t2 = time.perf_counter()
         return prefill_gpu, seq.last_gpu_seconds(), t1 - t0, t2 - t1, tokens
@@ -261,6 +320,18 @@ def run_ours(args) -> None:
         [decode_gpu, prefill_gpu, decode_wall, prefill_wall, total_ms / args.steps], device="cuda")
     launches = replicas.sum_over_ranks([launches], device="cuda")[0]
 
+    # Replicas must not change results: every rank also serves request 0, and the token hashes must agree.
+    replica_check = None
+    if world > 1:
+        seq.reset()
+        seq.prefill(prompt_for(hp.n_vocab, replicas.prompt_seed(0)))
+        mine_hash = replicas.token_hash(seq.generate(DECODE_TOKENS).tolist()) & 0x7FFFFFFFFFFFFFFF
+        lo, hi = replicas.max_over_ranks([-float(mine_hash >> 32), float(mine_hash >> 32)], device="cuda")
+        lo2, hi2 = replicas.max_over_ranks([-float(mine_hash & 0xFFFFFFFF), float(mine_hash & 0xFFFFFFFF)], device="cuda")
+        replica_check = {"request": 0, "token_hash": mine_hash, "identical_on_all_ranks": (-lo == hi) and (-lo2 == hi2)}
+        if not replica_check["identical_on_all_ranks"]:
+            raise SystemExit("request 0 decoded to different tokens on different ranks")
+
     if rank == 0:
         peak, tensor_peak, peak_kind = measured_peaks()
         weight_bytes = model.decode_bytes()
@@ -278,14 +349,16 @@ def run_ours(args) -> None:
         for tok in rows[-1][4].tolist():
             token_hash = (token_hash * 1000003 + tok) & 0xFFFFFFFFFFFFFFFF
         dom = dominant_kernel(cuda, seq, prompt)
+        in_graph = in_graph_costs(seq, prompt, dom["table"], decode_gpu / DECODE_TOKENS)
         achieved = dom["bytes"] / dom["seconds"] / 1e9
-        cpu_rate, cpu_seconds = cpu_sample(path, hp.n_vocab, 1, 2, 4) if world == 1 and not args.no_cpu_baseline else (None, None)
+        top_key = "%s %dx%d" % (dom["top"]["name"], dom["top"]["n_rows"], dom["top"]["n_cols"])
+        cpu_rate, cpu_seconds = cpu_sample(path, 1, 2, 4) if world == 1 and not args.no_cpu_baseline else (None, None)
         line = {
             "metric": METRIC, "value": decode_tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations, Q4_0 weights, f16 KV",
             "data": "synthetic",
-            "config": {"workload": "%s Q4_0 (random init N(0,0.02), seed 0), batch 1 per GPU, %d-token uniform-random prompt then %d greedy tokens; "
-                                   "%d request replica(s), one per GPU, %d requests with distinct prompts" % (args.config, PROMPT_TOKENS, DECODE_TOKENS, world, world * args.steps),
+            "config": {"workload": "%s Q4_0 (random init N(0,0.02), seed 0), batch 1 per GPU, %d-token uniform-random prompt prefilled in chunks of %d then %d greedy tokens; "
+                                   "%d request replica(s), one per GPU, %d requests with distinct prompts" % (args.config, PROMPT_TOKENS, PREFILL_CHUNK, DECODE_TOKENS, world, world * args.steps),
                        "l2": "every token streams %.2f GB of weights, far larger than the 126 MB L2" % (weight_bytes / 1e9),
                        "n_ctx": n_ctx, "kv_cache": "f16"},
             "decode": {"tok_s": decode_tok_s, "tpot_ms": 1e3 * decode_gpu / DECODE_TOKENS, "bytes_per_token": token_bytes,
@@ -297,13 +370,16 @@ def run_ours(args) -> None:
                         "weights_pass_ms": 1e3 * (weight_bytes - hp.n_vocab * hp.n_embd * 4) / (peak * 1e9), "kernels": dom["prefill_table"]},
             "roofline": {"bound": "hbm", "kernel": "%s %dx%d" % (dom["top"]["name"], dom["top"]["n_rows"], dom["top"]["n_cols"]),
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get("%s %dx%d" % (dom["top"]["name"], dom["top"]["n_rows"], dom["top"]["n_cols"])),
-                         "share_of_decode": dom["share"], "launch_us": 1e6 * dom["seconds"], "bytes_per_launch": dom["bytes"], "kernels": dom["table"]},
+                         "traffic": recorded_traffic(top_key), "traffic_source": "ncu summary under profiles/ (recorded, not captured in this run)",
+                         "share_of_decode": dom["share"], "launch_us": 1e6 * dom["seconds"], "bytes_per_launch": dom["bytes"], "kernels": dom["table"],
+                         "in_graph_us": in_graph},
             "e2e": {"value": world * DECODE_TOKENS / decode_wall, "unit": "tok/s", "h2d_bytes_per_step": PROMPT_TOKENS * 4,
                     "d2h_bytes_per_step": DECODE_TOKENS * 4, "prefill_tok_s": world * PROMPT_TOKENS / prefill_wall},
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        if replica_check is not None:
+            line["replica_check"] = replica_check
         if cpu_rate is not None:
             line["cpu_baseline"] = {"value": cpu_rate, "unit": "tok/s", "cores": 1, "kind": "port",
                                     "sample": "2-token prompt then 4 greedy decode steps of the scalar restatement, single thread (%.1f s)" % cpu_seconds}
@@ -314,7 +390,7 @@ def run_ours(args) -> None:
 
 
 def main() -> None:
-    global PROMPT_TOKENS, DECODE_TOKENS
+    global PROMPT_TOKENS, DECODE_TOKENS, PREFILL_CHUNK
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=5)
@@ -322,10 +398,14 @@ def main() -> None:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--config", default="lfm2-2.6b")
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--prompt-tokens", type=int, default=PROMPT_TOKENS, help="shorter requests, for profiler captures only")
-    parser.add_argument("--decode-tokens", type=int, default=DECODE_TOKENS)
+    parser.add_argument("--prompt-tokens", type=int, default=0, help="shorter requests, for profiler captures only (0: the configuration's own)")
+    parser.add_argument("--decode-tokens", type=int, default=0)
+    parser.add_argument("--prefill-chunk", type=int, default=0)
     args = parser.parse_args()
-    PROMPT_TOKENS, DECODE_TOKENS = args.prompt_tokens, args.decode_tokens
+    protocol = PROTOCOLS.get(args.config, (512, 128, 512))
+    PROMPT_TOKENS = args.prompt_tokens or protocol[0]
+    DECODE_TOKENS = args.decode_tokens or protocol[1]
+    PREFILL_CHUNK = args.prefill_chunk or min(protocol[2], PROMPT_TOKENS)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

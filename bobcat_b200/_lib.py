@@ -70,6 +70,10 @@ SIGNATURES = {
     "bc_attention_scratch_floats": (sz, [u32, u32, u32, u32]),
     "bc_attention_static": (i32, [vp, vp, vp, vp, i32, vp] + [u32] * 6),
     "bc_op_argmax": (i32, [vp] + _VIEW + _VIEW + [u32]),
+    "bc_readback_new": (i32, [vp, sz, C.POINTER(vp)]),
+    "bc_readback_free": (None, [vp]),
+    "bc_op_argmax_readback": (i32, [vp] + _VIEW + _VIEW + [vp, sz, u32]),
+    "bc_read_readback": (i32, [vp, vp, sz, C.POINTER(u32)]),
     "bc_op_silu_mul": (i32, [vp] + _VIEW + _VIEW + [u32]),
     "bc_op_gdn_conv": (i32, [vp] + _VIEW + _VIEW + _VIEW + _VIEW + [u32] * 3),
     "bc_op_gdn_gates": (i32, [vp] + _VIEW + _VIEW + _VIEW + _VIEW + [u32] * 2),
@@ -104,13 +108,7 @@ SIGNATURES = {
     "bc_seq_timings": (i32, [vp, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "bc_seq_read_state": (i32, [vp, i32, u32, vp, sz, C.POINTER(sz)]),
     "bc_seq_launches": (u64, [vp]),
-    "bc_gguf_writer_new": (i32, [C.c_char_p, u64, C.POINTER(vp)]),
-    "bc_gguf_writer_kv_u32": (i32, [vp, C.c_char_p, u32]),
-    "bc_gguf_writer_kv_f32": (i32, [vp, C.c_char_p, f32]),
-    "bc_gguf_writer_kv_str": (i32, [vp, C.c_char_p, C.c_char_p]),
-    "bc_gguf_writer_kv_u32_array": (i32, [vp, C.c_char_p, C.POINTER(u32), u64]),
-    "bc_gguf_writer_tensor": (i32, [vp, C.c_char_p, i32, C.POINTER(u64), u32, i32, f32]),
-    "bc_gguf_writer_finish": (i32, [vp]),
+    "bc_seq_set_skip": (i32, [vp, C.c_char_p, u32, u32]),
 }
 
 _lib = None

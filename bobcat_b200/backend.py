@@ -69,6 +69,24 @@ def _v(view):
     return view.buffer._h, view.offset
 
 
+class Readback:
+    """Token slots the CPU reads while later recordings still run (``Readback``, backend.rs:324-333)."""
+
+    def __init__(self, cuda: "Cuda", handle):
+        self.cuda, self._h = cuda, handle
+
+    def close(self) -> None:
+        if self._h:
+            self.cuda._L.bc_readback_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class Cuda:
     """One CUDA device, one stream, the buffers allocated on it, and the op launches."""
 
@@ -212,6 +230,19 @@ class Cuda:
 
     def argmax(self, x, out, n) -> None:
         self._check(self._L.bc_op_argmax(self._h, *_v(x), *_v(out), n))
+
+    def new_readback(self, slots: int) -> "Readback":
+        h = C.c_void_p()
+        self._check(self._L.bc_readback_new(self._h, slots, C.byref(h)))
+        return Readback(self, h)
+
+    def argmax_readback(self, x, out, readback: "Readback", slot: int, n: int) -> None:
+        self._check(self._L.bc_op_argmax_readback(self._h, *_v(x), *_v(out), readback._h, slot, n))
+
+    def read_readback(self, readback: "Readback", slot: int) -> int:
+        tok = C.c_uint32()
+        self._check(self._L.bc_read_readback(self._h, readback._h, slot, C.byref(tok)))
+        return int(tok.value)
 
     # ---- mixture of experts (argument order of backend.rs:1428-1737)
     def route_bytes(self, n_used, n_tokens) -> int:

@@ -29,6 +29,7 @@ def sources() -> list[str]:
 def headers() -> list[str]:
     found = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     found.append(os.path.join(HERE, "..", "include", "bobcat_cuda.h"))
+    found.append(os.path.join(HERE, "..", "include", "bobcat_cuda_test.h"))
     return found
 
 

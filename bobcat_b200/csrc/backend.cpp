@@ -5,6 +5,7 @@
 
 #include <cstdarg>
 #include <cstring>
+#include <initializer_list>
 
 namespace bc {
 
@@ -33,6 +34,14 @@ bc_status check_range(const bc_backend* backend, const bc_buffer* buffer, size_t
     if (offset > buffer->len || needed > buffer->len - offset)
         return fail(BC_ERR_OUT_OF_BOUNDS, "the %s launch needs %zu bytes at offset %zu of a %zu-byte buffer", op, needed, offset,
                     buffer->len);
+    return BC_OK;
+}
+
+// A kernel whose bounded wait ran out leaves a flag rather than hanging the device. Reading a flag
+// clears it, so one failure is reported once and later healthy work is not blamed for it.
+bc_status kernel_wait_status() {
+    if (int flag = k::matvec_error_flag()) return fail(BC_ERR_EXECUTION, "a decode kernel gave up waiting for its weight stream or its input (code %d)", flag);
+    if (int flag = k::matmul_error_flag()) return fail(BC_ERR_EXECUTION, "a prefill kernel gave up waiting on its pipeline (code %d)", flag);
     return BC_OK;
 }
 
@@ -85,6 +94,15 @@ bc_status matrix_view(bc_backend* b, bc_buffer* buffer, size_t offset, int32_t f
         return fail(BC_ERR_OUT_OF_BOUNDS, "the %s launch needs %llu bytes at offset %zu of a %llu-byte matrix", op,
                     (unsigned long long)(n_rows * row_bytes), offset, (unsigned long long)(m.n_rows * row_bytes));
     *out = m.rows((uint32_t)first, n_rows);
+    return BC_OK;
+}
+
+// The vectorised kernels read activations 16 bytes at a time: views of activation vectors must
+// start on a 16-byte boundary (cudaMalloc bases are 256-byte aligned, so only the offset matters).
+// Checked before any launch, because a misaligned vector load is a device fault, not a status code.
+bc_status check_aligned(const char* op, std::initializer_list<size_t> offsets) {
+    for (size_t offset : offsets)
+        if (offset % 16 != 0) return fail(BC_ERR_ARGUMENT, "the %s launch needs 16-byte aligned activation offsets, got %zu", op, offset);
     return BC_OK;
 }
 
@@ -298,10 +316,7 @@ bc_status bc_wait(bc_backend* b, bc_ticket ticket, double* seconds) {
     cudaEventDestroy(end->second);
     b->tickets.erase(end);
     if (seconds) *seconds = ms * 1e-3;
-    // A kernel whose bounded wait ran out leaves a flag rather than hanging the device.
-    if (int flag = k::matvec_error_flag()) return fail(BC_ERR_EXECUTION, "a matvec kernel gave up waiting for its weight stream (code %d)", flag);
-    if (int flag = k::matmul_error_flag()) return fail(BC_ERR_EXECUTION, "a matmul kernel gave up waiting on its pipeline (code %d)", flag);
-    return BC_OK;
+    return kernel_wait_status();
 }
 
 bc_status bc_end(bc_backend* b, double* seconds) {
@@ -356,6 +371,7 @@ bc_status bc_op_matvec(bc_backend* b, int32_t format, bc_buffer* weights, size_t
     BC_TRY(matrix_view(b, weights, w_off, format, n_rows, n_cols, "matvec", &seg.w));
     BC_TRY(check_range(b, x, x_off, (size_t)n_cols * 4, "matvec"));
     BC_TRY(check_range(b, y, y_off, (size_t)n_rows * 4, "matvec"));
+    BC_TRY(check_aligned("matvec", {x_off, y_off, norm ? norm_off : 0}));
     k::Norm nm;
     if (norm) {
         BC_TRY(check_range(b, norm, norm_off, (size_t)n_cols * 4, "matvec"));
@@ -379,6 +395,7 @@ bc_status bc_op_matvec_swiglu(bc_backend* b, int32_t format, bc_buffer* gate, si
     BC_TRY(check_range(b, y, y_off, (size_t)n_rows * 4, "matvec_swiglu"));
     if (!norm) return fail(BC_ERR_ARGUMENT, "matvec_swiglu needs a norm");
     BC_TRY(check_range(b, norm, norm_off, (size_t)n_cols * 4, "matvec_swiglu"));
+    BC_TRY(check_aligned("matvec_swiglu", {x_off, y_off, norm_off}));
     k::Norm nm{reinterpret_cast<const float*>(at(norm, norm_off)), eps};
     return b->run("matvec_swiglu", n_rows, n_cols, g.bytes() * 2, 1, [&] {
         return k::matvec_swiglu(b->stream, g, u, reinterpret_cast<const float*>(at(x, x_off)), nm, reinterpret_cast<float*>(at(y, y_off)));
@@ -396,6 +413,7 @@ bc_status bc_op_matvec_conv(bc_backend* b, int32_t format, bc_buffer* in_proj, s
     BC_TRY(check_range(b, taps, taps_off, (size_t)n_embd * kernel * 4, "matvec_conv"));
     BC_TRY(check_range(b, history, hist_off, (size_t)n_embd * (kernel - 1) * 4, "matvec_conv"));
     BC_TRY(check_range(b, out, out_off, (size_t)n_embd * 4, "matvec_conv"));
+    BC_TRY(check_aligned("matvec_conv", {x_off, out_off, norm ? norm_off : 0}));
     k::Norm nm;
     if (norm) {
         BC_TRY(check_range(b, norm, norm_off, (size_t)n_cols * 4, "matvec_conv"));
@@ -431,6 +449,7 @@ bc_status bc_op_matmul(bc_backend* b, int32_t format, bc_buffer* weights, size_t
     BC_TRY(matrix_view(b, weights, w_off, format, n_rows, n_cols, "matmul", &w));
     BC_TRY(check_range(b, x, x_off, (size_t)n_tokens * n_cols * 4, "matmul"));
     BC_TRY(check_range(b, y, y_off, (size_t)n_tokens * n_rows * 4, "matmul"));
+    BC_TRY(check_aligned("matmul", {x_off, y_off}));
     void* pack = nullptr;
     if (k::matmul_umma_supported(w, n_tokens)) BC_TRY(b->pack_scratch(k::matmul_scratch_bytes(w, n_tokens), &pack));
     return b->run("matmul", n_rows, n_cols, w.bytes(), pack ? k::matmul_umma_launches(w, n_tokens) : 1, [&] {
@@ -547,6 +566,66 @@ bc_status bc_op_argmax(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* out
     return b->run("argmax", 1, n, 0, 1, [&] {
         return k::argmax(b->stream, reinterpret_cast<const float*>(at(x, x_off)), n, reinterpret_cast<uint32_t*>(at(out, out_off)), nullptr);
     });
+}
+
+bc_status bc_readback_new(bc_backend* b, size_t slots, bc_readback** out) {
+    if (!b || !out) return fail(BC_ERR_ARGUMENT, "backend and out must be non-null");
+    BC_TRY(b->activate());
+    std::unique_ptr<bc_readback> r(new bc_readback());
+    r->backend = b;
+    r->writers.assign(slots, 0);
+    cudaError_t e = cudaHostAlloc((void**)&r->words, sizeof(uint32_t) * std::max<size_t>(slots, 1), cudaHostAllocMapped);
+    if (e != cudaSuccess) return fail(BC_ERR_ALLOCATION, "cannot allocate %zu readback slots: %s", slots, cudaGetErrorString(e));
+    *out = r.release();
+    return BC_OK;
+}
+
+void bc_readback_free(bc_readback* r) {
+    if (!r) return;
+    if (r->words) {
+        // A recorded argmax may still be about to write a slot.
+        if (r->backend) {
+            cudaSetDevice(r->backend->device);
+            cudaStreamSynchronize(r->backend->stream);
+        }
+        cudaFreeHost(r->words);
+    }
+    delete r;
+}
+
+bc_status bc_op_argmax_readback(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* out, size_t out_off, bc_readback* readback, size_t slot,
+                                uint32_t n) {
+    BC_TRY(need_recording(b));
+    if (!readback || readback->backend != b) return fail(BC_ERR_FOREIGN_BUFFER, "the readback belongs to another backend");
+    if (slot >= readback->writers.size())
+        return fail(BC_ERR_OUT_OF_BOUNDS, "CPU access of 4 bytes at offset %zu exceeds a %zu-byte buffer", slot * 4, readback->writers.size() * 4);
+    if (n == 0) return fail(BC_ERR_ARGUMENT, "argmax needs at least one value");
+    BC_TRY(check_range(b, x, x_off, (size_t)n * 4, "argmax"));
+    BC_TRY(check_range(b, out, out_off, 4, "argmax"));
+    // The open recording becomes the slot's writer; the slot is readable once that ticket finished.
+    readback->writers[slot] = b->next_ticket;
+    return b->run("argmax", 1, n, 0, 1, [&] {
+        return k::argmax(b->stream, reinterpret_cast<const float*>(at(x, x_off)), n, reinterpret_cast<uint32_t*>(at(out, out_off)),
+                         readback->words + slot);
+    });
+}
+
+bc_status bc_read_readback(bc_backend* b, const bc_readback* readback, size_t slot, uint32_t* token) {
+    if (!b || !readback || !token) return fail(BC_ERR_ARGUMENT, "backend, readback and token must be non-null");
+    if (slot >= readback->writers.size() || readback->writers[slot] == 0)
+        return fail(BC_ERR_OUT_OF_BOUNDS, "CPU access of 4 bytes at offset %zu exceeds a %zu-byte buffer", slot * 4, readback->writers.size() * 4);
+    uint64_t writer = readback->writers[slot];
+    // Finished: collected by bc_wait, or its end event has completed. An open or unfinished
+    // recording still owns the slot.
+    if (writer >= b->next_ticket) return fail(BC_ERR_BUSY, "the recording that writes this slot has not been committed");
+    auto end = b->tickets.find(writer);
+    if (end != b->tickets.end()) {
+        cudaError_t e = cudaEventQuery(end->second);
+        if (e == cudaErrorNotReady) return fail(BC_ERR_BUSY, "the recording that writes this slot is still running");
+        if (e != cudaSuccess) return cuda_fail(e, "recorded work");
+    }
+    *token = *(volatile uint32_t*)(readback->words + slot);
+    return BC_OK;
 }
 
 bc_status bc_op_silu_mul(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* gate, size_t g_off, uint32_t n) {

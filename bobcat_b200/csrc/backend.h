@@ -24,6 +24,14 @@ struct bc_buffer {
     bc::k::Mat matrix;
 };
 
+// Token slots in host-mapped memory that argmax launches write and the CPU reads once the
+// recording that wrote a slot has finished (Readback, crates/bobcat-metal/src/backend.rs:324-333).
+struct bc_readback {
+    bc_backend* backend = nullptr;
+    uint32_t* words = nullptr;
+    std::vector<uint64_t> writers;  // per slot: ticket of the recording that last wrote it, 0 = never
+};
+
 struct ProfileKey {
     std::string name;
     uint32_t n_rows, n_cols;
@@ -72,6 +80,8 @@ namespace bc {
 // Check that [offset, offset + needed) lies inside `buffer`, which must belong to `backend`
 // (check_range, crates/bobcat-metal/src/backend.rs:2772-2790).
 bc_status check_range(const bc_backend* backend, const bc_buffer* buffer, size_t offset, size_t needed, const char* op);
+// BC_ERR_EXECUTION when a kernel's bounded wait ran out since the last call; clears the record.
+bc_status kernel_wait_status();
 
 }  // namespace bc
 

@@ -9,6 +9,7 @@
 #include <string>
 
 #include "../../include/bobcat_cuda.h"
+#include "../../include/bobcat_cuda_test.h"
 
 namespace bc {
 

@@ -520,7 +520,10 @@ int attention_launches(bool kv_half, const AttentionShape& s) {
 cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, const void* v_cache, bool kv_half,
                       float* scratch, float* out, const AttentionShape& s) {
     if (s.n_queries == 0) return cudaSuccess;
-    if (attention_flash_supported(kv_half, s)) return attention_flash(stream, q, k_cache, v_cache, out, s);
+    // The tensor-core kernel reads q and out 8 bytes and the caches 16 bytes at a time; views that
+    // do not start on those boundaries take the chunk kernels, whose loads are scalar.
+    const bool flash_aligned = ((uintptr_t)q | (uintptr_t)out) % 8 == 0 && ((uintptr_t)k_cache | (uintptr_t)v_cache) % 16 == 0;
+    if (flash_aligned && attention_flash_supported(kv_half, s)) return attention_flash(stream, q, k_cache, v_cache, out, s);
     const uint32_t group = s.n_heads / s.n_kv_heads;
     const uint32_t chunk = s.n_queries <= (uint32_t)kDecodeQueries ? kDecodeChunk : kChunk;
     const uint32_t max_chunks = (s.n_ctx + chunk - 1) / chunk;
@@ -588,8 +591,10 @@ cudaError_t attention_step(cudaStream_t stream, const RopeStore& r, float* scrat
 // every GPU that loads this library holds from load until exit.
 // ------------------------------------------------------------------------------------------------
 
-// 2 Mi floats = 8 MiB: enough for one query over 32 heads of 64 elements at 63 000 positions, or a
-// 64-query batch of the same heads at 980 positions.
+// 2 Mi floats = 8 MiB. A call needs ceil(positions / chunk) * queries in a pass * n_heads *
+// (head_dim + 2) floats, positions = first_pos + n_queries, chunk = 16 positions for up to 4
+// queries and 64 for more (at most 64 queries in a pass): one query over 32 heads of 64 elements
+// fits up to 15 872 positions, a 64-query pass of the same heads up to 960 positions.
 #define BC_STATIC_ATTENTION_SCRATCH_FLOATS (2u << 20)
 static __device__ __align__(256) float bc_static_attention_scratch[BC_STATIC_ATTENTION_SCRATCH_FLOATS];
 
@@ -604,11 +609,14 @@ extern "C" bc_status bc_attention_static(void* stream, const float* q, const voi
                     "attention needs heads of a multiple of 32 up to 256 elements, at most 8 query heads per KV head and queries inside the "
                     "context, got head_dim %u, %u/%u heads, positions %u..%u of %u",
                     head_dim, n_heads, n_kv_heads, first_pos, first_pos + n_queries, n_ctx);
-    uint64_t need = k::attention_scratch_floats(n_heads, head_dim, n_ctx, n_queries);
+    // The partials are laid out for the positions in use, not for the cache's capacity: positions
+    // are known here (no device-side position), so no chunk past the last query is ever written.
+    const uint32_t positions = first_pos + n_queries;
+    uint64_t need = k::attention_scratch_floats(n_heads, head_dim, positions, n_queries);
     if (need > BC_STATIC_ATTENTION_SCRATCH_FLOATS)
         return fail(BC_ERR_ARGUMENT,
                     "this shape needs %llu floats of chunk partials and the built-in scratch holds %u; use bc_op_attention with a scratch "
-                    "buffer of your own, or a smaller n_ctx",
+                    "buffer of your own, or fewer positions",
                     (unsigned long long)need, (unsigned)BC_STATIC_ATTENTION_SCRATCH_FLOATS);
     // The array's name is only a host-side handle; the kernels need its address on the current
     // device, looked up once per device.
@@ -623,7 +631,8 @@ extern "C" bc_status bc_attention_static(void* stream, const float* q, const voi
         if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(bc_static_attention_scratch)");
         address_on_device[device] = scratch;
     }
-    k::AttentionShape shape{n_heads, n_kv_heads, head_dim, first_pos, n_queries, n_ctx, n_heads * head_dim, head_dim};
+    (void)n_ctx;
+    k::AttentionShape shape{n_heads, n_kv_heads, head_dim, first_pos, n_queries, positions, n_heads * head_dim, head_dim};
     e = k::attention(static_cast<cudaStream_t>(stream), q, k_cache, v_cache, kv_half != 0, scratch, out, shape);
     if (e != cudaSuccess) return cuda_fail(e, "attention");
     return BC_OK;

@@ -698,6 +698,10 @@ cudaError_t matmul_experts_umma(cudaStream_t stream, const Mat& w, const Mat* up
 int matmul_error_flag() {
     int flag = 0;
     cudaMemcpyFromSymbol(&flag, g_matmul_error, sizeof flag);
+    if (flag) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_matmul_error, &zero, sizeof zero);
+    }
     return flag;
 }
 

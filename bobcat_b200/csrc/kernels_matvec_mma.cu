@@ -594,6 +594,10 @@ cudaError_t matvec_mma_prepare(uint32_t widest_cols) {
 int matvec_error_flag() {
     int flag = 0;
     cudaMemcpyFromSymbol(&flag, g_error_flag, sizeof flag);
+    if (flag) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_error_flag, &zero, sizeof zero);
+    }
     return flag;
 }
 

@@ -24,6 +24,8 @@ struct Recorder {
     // When set, single-token passes read their position from s.step_pos on the device, so the
     // launches can be captured once and replayed at every position.
     bool replayed = false;
+    // Traced passes of a mixture-of-experts model: where the next router launch's routes are copied to.
+    uint32_t* route_trace = nullptr;
 
     explicit Recorder(bc_seq& seq) : s(seq), hp(seq.model->hp), stream(seq.backend->stream) {}
 
@@ -33,6 +35,8 @@ struct Recorder {
     template <typename F>
     void run(const char* name, uint32_t rows, uint32_t cols, uint64_t bytes, int kernels, F&& f) {
         if (status != BC_OK) return;
+        // Timing diagnostics: a launch kind left out of the pass (its outputs keep stale values).
+        if (!s.skip_name.empty() && s.skip_name == name && (s.skip_rows == 0 || s.skip_rows == rows) && (s.skip_cols == 0 || s.skip_cols == cols)) return;
         s.launches += (uint64_t)kernels;
         status = s.backend->run(name, rows, cols, bytes, kernels, f);
     }
@@ -189,6 +193,9 @@ struct Recorder {
             return k::moe_route(stream, input, nm, s.normed, static_cast<const float*>(D.router.data), D.expert_bias, s.route, n_embd, hp.n_experts,
                                 n_used, n);
         });
+        if (route_trace) run("copy", 1, n * 2 * n_used, 0, 0, [&] {
+            return k::copy_floats(stream, reinterpret_cast<const float*>(s.route), reinterpret_cast<float*>(route_trace), (uint64_t)n * 2 * n_used);
+        });
         // Bytes the experts stream: the picked experts of each token (decode) or every expert once (batch).
         uint64_t expert_bytes = D.gate.bytes() / hp.n_experts;
         if (n == 1) {
@@ -236,8 +243,10 @@ struct Recorder {
             const DeviceLayer& D = W.layers[il];
             if (S.mixer == Mixer::Attention) lfm2_attention(D, S.cache_index, pos);
             else lfm2_conv(D, S.cache_index);
-            if (S.moe) lfm2_moe(D, 1, true);
-            else lfm2_dense_ffn(D);
+            if (S.moe) {
+                route_trace = traced ? s.trace_routes + il * (size_t)s.trace_rows * 2 * hp.n_experts_used : nullptr;
+                lfm2_moe(D, 1, true);
+            } else lfm2_dense_ffn(D);
             if (traced) copy(s.hidden, s.trace_layers + il * hp.n_embd, hp.n_embd);
         }
         if (traced)
@@ -269,6 +278,7 @@ struct Recorder {
             }
             if (S.moe) {
                 run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.ffn_norm, s.normed, n_embd, n, hp.norm_eps); });
+                route_trace = traced ? s.trace_routes + il * (size_t)s.trace_rows * 2 * hp.n_experts_used : nullptr;
                 lfm2_moe(D, n, false);
             } else {
                 normed_swiglu(s.hidden, D.ffn_norm, n, D.gate, D.up, s.ffn);
@@ -415,11 +425,15 @@ bc_status ensure_trace_rows(bc_seq* s, uint32_t rows) {
     cudaFree(s->trace_embedding);
     cudaFree(s->trace_layers);
     cudaFree(s->trace_final);
+    cudaFree(s->trace_routes);
     s->trace_embedding = s->trace_layers = s->trace_final = nullptr;
+    s->trace_routes = nullptr;
     s->trace_rows = 0;
     size_t floats = (size_t)rows * hp.n_embd;
+    size_t route_words = std::max<size_t>(1, (size_t)rows * hp.n_layers * 2 * hp.n_experts_used);
     if (cudaMalloc(&s->trace_embedding, floats * 4) != cudaSuccess || cudaMalloc(&s->trace_layers, floats * 4 * hp.n_layers) != cudaSuccess ||
-        cudaMalloc(&s->trace_final, floats * 4) != cudaSuccess)
+        cudaMalloc(&s->trace_final, floats * 4) != cudaSuccess || cudaMalloc(&s->trace_routes, route_words * 4) != cudaSuccess ||
+        cudaMemset(s->trace_routes, 0, route_words * 4) != cudaSuccess)
         return fail(BC_ERR_ALLOCATION, "cannot allocate trace buffers for %u tokens", rows);
     s->trace_rows = rows;
     return BC_OK;
@@ -450,10 +464,7 @@ bc_status timing_end(bc_seq* s, double* seconds) {
     float ms = 0.f;
     cudaEventElapsedTime(&ms, s->timing_start, s->timing_end);
     *seconds = ms * 1e-3;
-    // A kernel whose bounded wait ran out leaves a flag rather than hanging the device.
-    if (int flag = k::matvec_error_flag()) return fail(BC_ERR_EXECUTION, "a decode kernel gave up waiting for its weight stream (code %d)", flag);
-    if (int flag = k::matmul_error_flag()) return fail(BC_ERR_EXECUTION, "a prefill kernel gave up waiting on its pipeline (code %d)", flag);
-    return BC_OK;
+    return kernel_wait_status();
 }
 
 // Replay needs a stream that can be captured (not the legacy default stream) and no per-launch
@@ -578,6 +589,7 @@ bc_seq::~bc_seq() {
     cudaFree(trace_embedding);
     cudaFree(trace_layers);
     cudaFree(trace_final);
+    cudaFree(trace_routes);
     if (readback) cudaFreeHost(readback);
     if (generate_graph) cudaGraphExecDestroy(generate_graph);
     if (stream_graph) cudaGraphExecDestroy(stream_graph);
@@ -925,6 +937,9 @@ bc_status bc_seq_checkpoint(bc_seq* s, bc_checkpoint** out) {
 
 bc_status bc_seq_restore(bc_seq* s, const bc_checkpoint* c) {
     if (!s || !c) return fail(BC_ERR_ARGUMENT, "seq and checkpoint must be non-null");
+    // A checkpoint holds the recurrent state only; the KV rows of its prefix live in the cache of
+    // the sequence that took it, so no other sequence can continue from it.
+    if (c->owner != s) return fail(BC_ERR_ARGUMENT, "the checkpoint belongs to another sequence");
     if (c->resets != s->resets) return fail(BC_ERR_ARGUMENT, "the checkpoint predates a reset");
     if (c->conv_state.size() != s->conv_floats || c->delta_state.size() != s->delta_floats || c->logits.size() != s->model->hp.n_vocab || c->n_past > s->n_ctx)
         return fail(BC_ERR_ARGUMENT, "the checkpoint comes from a different model or context");
@@ -944,6 +959,20 @@ bc_status bc_seq_timings(const bc_seq* s, double* encode_seconds, double* gpu_se
     if (!s) return fail(BC_ERR_ARGUMENT, "seq must be non-null");
     if (encode_seconds) *encode_seconds = s->last_encode_seconds;
     if (gpu_seconds) *gpu_seconds = s->last_gpu_seconds;
+    return BC_OK;
+}
+
+bc_status bc_seq_set_skip(bc_seq* s, const char* name, uint32_t n_rows, uint32_t n_cols) {
+    if (!s) return fail(BC_ERR_ARGUMENT, "seq must be non-null");
+    BC_TRY(s->backend->activate());
+    BC_CUDA(cudaStreamSynchronize(s->backend->stream));
+    s->skip_name = name ? name : "";
+    s->skip_rows = n_rows;
+    s->skip_cols = n_cols;
+    // The captured steps hold the old launch list.
+    if (s->generate_graph) cudaGraphExecDestroy(s->generate_graph);
+    if (s->stream_graph) cudaGraphExecDestroy(s->stream_graph);
+    s->generate_graph = s->stream_graph = nullptr;
     return BC_OK;
 }
 
@@ -987,6 +1016,17 @@ bc_status bc_seq_read_state(bc_seq* s, int32_t which, uint32_t layer, float* out
         if (!out) return BC_OK;
         if (cap < count) return fail(BC_ERR_ARGUMENT, "out must hold %zu floats", count);
         BC_CUDA(cudaMemcpyAsync(out, s->delta_state + (size_t)layer * count, count * 4, cudaMemcpyDeviceToHost, stream));
+        BC_CUDA(cudaStreamSynchronize(stream));
+        return BC_OK;
+    }
+    if (which == 4) {
+        // The routes the last traced pass recorded, [layer][trace row][2 * n_used] 32-bit words (ids,
+        // then weights as float bits), copied out bit for bit.
+        size_t count = (size_t)s->trace_rows * hp.n_layers * 2 * hp.n_experts_used;
+        *n = count;
+        if (!out) return BC_OK;
+        if (cap < count) return fail(BC_ERR_ARGUMENT, "out must hold %zu words", count);
+        if (count) BC_CUDA(cudaMemcpyAsync(out, s->trace_routes, count * 4, cudaMemcpyDeviceToHost, stream));
         BC_CUDA(cudaStreamSynchronize(stream));
         return BC_OK;
     }

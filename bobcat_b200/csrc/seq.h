@@ -4,6 +4,7 @@
 
 #include <chrono>
 #include <memory>
+#include <string>
 #include <vector>
 
 #include "model.h"
@@ -40,6 +41,7 @@ struct bc_seq {
     float *k = nullptr, *v = nullptr, *conv_state = nullptr, *hidden = nullptr, *normed = nullptr, *bcx = nullptr;
     float *conv_out = nullptr, *q = nullptr, *attn = nullptr, *scores = nullptr, *ffn = nullptr, *logits = nullptr;
     float *trace_embedding = nullptr, *trace_layers = nullptr, *trace_final = nullptr;
+    uint32_t* trace_routes = nullptr;  // [layer][trace_rows][2 * n_used]: routes of the last traced pass
     uint32_t* tokens = nullptr;        // n_ctx + 1 ids; the extra slot takes the pick at the last position
     uint32_t* greedy_token = nullptr;
     // Mixture of experts: each token's route, the routes grouped by expert, and one row of n_embd
@@ -68,6 +70,9 @@ struct bc_seq {
     cudaGraphExec_t stream_graph = nullptr;   // forward pass at pos, argmax -> tokens[pos + 1] and the readback ring
     uint64_t generate_graph_kernels = 0, stream_graph_kernels = 0;  // kernels per replay, for the launch count
     uint32_t host_pos = 0;                    // staging for the seed of step_pos
+    // Timing diagnostics (bc_seq_set_skip): launches of this name (and shape, when nonzero) are left out.
+    std::string skip_name;
+    uint32_t skip_rows = 0, skip_cols = 0;
     bool use_graphs = true;                   // BOBCAT_NO_GRAPH=1 turns replay off (launch every kernel eagerly)
 
     ~bc_seq();

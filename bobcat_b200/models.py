@@ -178,6 +178,17 @@ class SeqCuda:
             self._check(self._L.bc_seq_read_state(self._h, which, layer, out.ctypes.data_as(C.c_void_p), out.size, C.byref(n)))
         return out
 
+    def set_skip(self, name: str | None, n_rows: int = 0, n_cols: int = 0) -> None:
+        """Timing diagnostics: leave one kind of launch out of the forward passes (None restores)."""
+        self._check(self._L.bc_seq_set_skip(self._h, name.encode() if name else None, n_rows, n_cols))
+
+    def traced_routes(self) -> np.ndarray:
+        """Expert ids the last traced pass picked: [layer][trace row][n_used] (rows of layers
+        without experts are zero)."""
+        hp = self.model.hp
+        words = self.read_state(4).view(np.uint32)
+        return words.reshape(hp.n_layers, -1, 2 * hp.n_experts_used)[:, :, : hp.n_experts_used].copy()
+
     def close(self) -> None:
         if self._h:
             self._L.bc_seq_free(self._h)

@@ -5,20 +5,55 @@ the reference's loaders demand (crates/bobcat/src/lfm2.rs:737-1004, crates/bobca
 Recipe (fixed; the tensor order below is part of it because each tensor's random stream is keyed
 by its position): every linear is N(0, 0.02) quantised to Q4_0; embeddings, conv taps, routers,
 biases and DeltaNet vectors are N(0, 0.02) in F32; every norm weight is 1.0; ``ssm_a`` is
--exp(N(0, 0.02)) so the DeltaNet state decays. Values are drawn inside ``libbobcat_cuda.so`` by a
-counter-based generator, so a file depends only on (config, seed), not on thread count.
+-exp(N(0, 0.02)) so the DeltaNet state decays. Values are drawn by ``libbobcat_synth.so`` (plain
+C++, built from ``synthlib/`` with g++; not part of the product library) with a counter-based
+generator, so a file depends only on (config, seed), not on thread count.
 """
 
 from __future__ import annotations
 
 import ctypes as C
 import os
+import subprocess
 
-from . import _lib, errors
-
-F32, Q4_0 = 0, 2
+F32, Q4_0, Q8_0 = 0, 2, 8
 NORMAL, CONSTANT, NEG_EXP_NORMAL = 0, 1, 2
 STD = 0.02
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SYNTH_SOURCES = [os.path.join(HERE, "synthlib", "gguf_writer.cpp"), os.path.join(HERE, "synthlib", "synth_writer.h")]
+SYNTH_LIB = os.path.join(HERE, "libbobcat_synth.so")
+_synth = None
+
+
+def build_writer(force: bool = False) -> str:
+    """Compile the writer library in-tree when it is missing or older than its sources."""
+    stale = force or not os.path.exists(SYNTH_LIB) or any(os.path.getmtime(f) > os.path.getmtime(SYNTH_LIB) for f in SYNTH_SOURCES)
+    if stale:
+        subprocess.run(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-o", SYNTH_LIB, SYNTH_SOURCES[0], "-lpthread"], check=True)
+    return SYNTH_LIB
+
+
+def _writer_lib() -> C.CDLL:
+    global _synth
+    if _synth is None:
+        L = C.CDLL(build_writer())
+        vp, u32, u64, i32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32
+        L.bcs_last_error.restype = C.c_char_p
+        L.bcs_writer_new.argtypes = [C.c_char_p, u64, C.POINTER(vp)]
+        L.bcs_writer_kv_u32.argtypes = [vp, C.c_char_p, u32]
+        L.bcs_writer_kv_f32.argtypes = [vp, C.c_char_p, C.c_float]
+        L.bcs_writer_kv_str.argtypes = [vp, C.c_char_p, C.c_char_p]
+        L.bcs_writer_kv_u32_array.argtypes = [vp, C.c_char_p, C.POINTER(u32), u64]
+        L.bcs_writer_tensor.argtypes = [vp, C.c_char_p, i32, C.POINTER(u64), u32, i32, C.c_float]
+        L.bcs_writer_finish.argtypes = [vp]
+        _synth = L
+    return _synth
+
+
+def _check(status: int, L) -> None:
+    if status != 0:
+        raise OSError("synthetic model writer: %s" % L.bcs_last_error().decode())
 
 
 def _even_attention(n_layers: int, n_attention: int) -> list[int]:
@@ -54,34 +89,34 @@ CONFIGS: dict[str, dict] = {
 
 class _Writer:
     def __init__(self, path: str, seed: int):
-        self.L = _lib.load()
+        self.L = _writer_lib()
         h = C.c_void_p()
-        errors.check(self.L.bc_gguf_writer_new(path.encode(), seed, C.byref(h)), self.L)
+        _check(self.L.bcs_writer_new(path.encode(), seed, C.byref(h)), self.L)
         self.h = h
 
     def u32(self, key, value):
-        errors.check(self.L.bc_gguf_writer_kv_u32(self.h, key.encode(), value), self.L)
+        _check(self.L.bcs_writer_kv_u32(self.h, key.encode(), value), self.L)
 
     def f32(self, key, value):
-        errors.check(self.L.bc_gguf_writer_kv_f32(self.h, key.encode(), value), self.L)
+        _check(self.L.bcs_writer_kv_f32(self.h, key.encode(), value), self.L)
 
     def string(self, key, value):
-        errors.check(self.L.bc_gguf_writer_kv_str(self.h, key.encode(), value.encode()), self.L)
+        _check(self.L.bcs_writer_kv_str(self.h, key.encode(), value.encode()), self.L)
 
     def array(self, key, values):
         arr = (C.c_uint32 * len(values))(*values)
-        errors.check(self.L.bc_gguf_writer_kv_u32_array(self.h, key.encode(), arr, len(values)), self.L)
+        _check(self.L.bcs_writer_kv_u32_array(self.h, key.encode(), arr, len(values)), self.L)
 
     def tensor(self, name, ttype, dims, init=NORMAL, value=STD):
         arr = (C.c_uint64 * len(dims))(*dims)
-        errors.check(self.L.bc_gguf_writer_tensor(self.h, name.encode(), ttype, arr, len(dims), init, value), self.L)
+        _check(self.L.bcs_writer_tensor(self.h, name.encode(), ttype, arr, len(dims), init, value), self.L)
 
     def ones(self, name, dims):
         self.tensor(name, F32, dims, CONSTANT, 1.0)
 
     def finish(self):
         h, self.h = self.h, None
-        errors.check(self.L.bc_gguf_writer_finish(h), self.L)
+        _check(self.L.bcs_writer_finish(h), self.L)
 
 
 def _write_lfm2(w: _Writer, c: dict) -> None:

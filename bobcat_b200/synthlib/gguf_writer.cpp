@@ -1,4 +1,6 @@
-// GGUF writer for synthetic model files.
+// GGUF writer for synthetic model files: a small library of its own (libbobcat_synth.so, plain
+// C++), used by the tests and the benchmark to make their model files. It is not part of the
+// product library and links nothing of it.
 //
 // The reference only reads GGUF; its tests and benchmarks use downloaded checkpoints. This writer
 // produces files with the layout the reference's parser checks (crates/bobcat-gguf/src/lib.rs:
@@ -23,10 +25,41 @@
 #include <thread>
 #include <vector>
 
-#include "common.h"
-#include "gguf.h"
+#include <algorithm>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <memory>
+
+#include "synth_writer.h"
 
 namespace {
+
+// This library keeps its own failure message: it does not link against the CUDA library.
+std::string& last_error() {
+    thread_local std::string message;
+    return message;
+}
+
+int32_t fail(int32_t status, const char* format, ...) __attribute__((format(printf, 2, 3)));
+int32_t fail(int32_t status, const char* format, ...) {
+    char buffer[512];
+    va_list args;
+    va_start(args, format);
+    vsnprintf(buffer, sizeof buffer, format, args);
+    va_end(args);
+    last_error() = buffer;
+    return status;
+}
+
+inline uint64_t round_up(uint64_t a, uint64_t b) { return (a + b - 1) / b * b; }
+
+// Bytes of one row: F32 4 per element, Q4_0 18 per block of 32, Q8_0 34 per block of 32.
+inline uint64_t type_row_bytes(uint32_t type, uint64_t n_cols) {
+    if (type == BCS_Q4_0) return n_cols / 32 * 18;
+    if (type == BCS_Q8_0) return n_cols / 32 * 34;
+    return n_cols * 4;
+}
 
 constexpr uint64_t kAlignment = 32;
 
@@ -115,9 +148,24 @@ void quantize_row_q4_0(const float* x, uint8_t* out, uint64_t n_cols) {
     }
 }
 
+// ggml's reference Q8_0 rounding (quantize_row_q8_0_ref): d = amax / 127 as fp16, q = round(x / d).
+void quantize_row_q8_0(const float* x, uint8_t* out, uint64_t n_cols) {
+    for (uint64_t b = 0; b < n_cols / 32; ++b) {
+        const float* xb = x + 32 * b;
+        uint8_t* ob = out + 34 * b;
+        float amax = 0.f;
+        for (int j = 0; j < 32; ++j) amax = std::max(amax, fabsf(xb[j]));
+        float d = amax / 127.0f;
+        float id = d != 0.f ? 1.0f / d : 0.f;
+        uint16_t dh = f32_to_f16(d);
+        std::memcpy(ob, &dh, 2);
+        for (int j = 0; j < 32; ++j) ob[2 + j] = (uint8_t)(int8_t)roundf(xb[j] * id);
+    }
+}
+
 void fill_row(const TensorSpec& t, uint64_t seed, uint64_t tensor_index, uint64_t row, float* scratch, uint8_t* out) {
-    float* dst = t.type == BC_F32 ? (float*)out : scratch;
-    if (t.init == BC_INIT_CONSTANT) {
+    float* dst = t.type == BCS_F32 ? (float*)out : scratch;
+    if (t.init == BCS_INIT_CONSTANT) {
         for (uint64_t i = 0; i < t.n_cols; ++i) dst[i] = t.value;
     } else {
         uint64_t key = mix64(mix64(seed ^ (tensor_index * 0xd1342543de82ef95ull)) ^ (row * 0x2545f4914f6cdd1dull));
@@ -127,15 +175,16 @@ void fill_row(const TensorSpec& t, uint64_t seed, uint64_t tensor_index, uint64_
             dst[i] = z0 * t.value;
             if (i + 1 < t.n_cols) dst[i + 1] = z1 * t.value;
         }
-        if (t.init == BC_INIT_NEG_EXP_NORMAL)
+        if (t.init == BCS_INIT_NEG_EXP_NORMAL)
             for (uint64_t i = 0; i < t.n_cols; ++i) dst[i] = -expf(dst[i]);
     }
-    if (t.type == BC_Q4_0) quantize_row_q4_0(scratch, out, t.n_cols);
+    if (t.type == BCS_Q4_0) quantize_row_q4_0(scratch, out, t.n_cols);
+    if (t.type == BCS_Q8_0) quantize_row_q8_0(scratch, out, t.n_cols);
 }
 
 }  // namespace
 
-struct bc_gguf_writer {
+struct bcs_writer {
     std::string path;
     uint64_t seed = 0;
     std::vector<uint8_t> kv;
@@ -145,61 +194,63 @@ struct bc_gguf_writer {
 
 extern "C" {
 
-bc_status bc_gguf_writer_new(const char* path, uint64_t seed, bc_gguf_writer** out) {
-    if (!path || !out) return bc::fail(BC_ERR_ARGUMENT, "path and out must be non-null");
-    bc_gguf_writer* w = new bc_gguf_writer();
+const char* bcs_last_error(void) { return last_error().c_str(); }
+
+int32_t bcs_writer_new(const char* path, uint64_t seed, bcs_writer** out) {
+    if (!path || !out) return fail(BCS_ERR_ARGUMENT, "path and out must be non-null");
+    bcs_writer* w = new bcs_writer();
     w->path = path;
     w->seed = seed;
     *out = w;
-    return BC_OK;
+    return BCS_OK;
 }
 
-bc_status bc_gguf_writer_kv_u32(bc_gguf_writer* w, const char* key, uint32_t value) {
-    if (!w || !key) return bc::fail(BC_ERR_ARGUMENT, "writer and key must be non-null");
+int32_t bcs_writer_kv_u32(bcs_writer* w, const char* key, uint32_t value) {
+    if (!w || !key) return fail(BCS_ERR_ARGUMENT, "writer and key must be non-null");
     put_str(w->kv, key);
     put_u32(w->kv, 4);
     put_u32(w->kv, value);
     ++w->n_kv;
-    return BC_OK;
+    return BCS_OK;
 }
 
-bc_status bc_gguf_writer_kv_f32(bc_gguf_writer* w, const char* key, float value) {
-    if (!w || !key) return bc::fail(BC_ERR_ARGUMENT, "writer and key must be non-null");
+int32_t bcs_writer_kv_f32(bcs_writer* w, const char* key, float value) {
+    if (!w || !key) return fail(BCS_ERR_ARGUMENT, "writer and key must be non-null");
     put_str(w->kv, key);
     put_u32(w->kv, 6);
     uint32_t bits;
     std::memcpy(&bits, &value, 4);
     put_u32(w->kv, bits);
     ++w->n_kv;
-    return BC_OK;
+    return BCS_OK;
 }
 
-bc_status bc_gguf_writer_kv_str(bc_gguf_writer* w, const char* key, const char* value) {
-    if (!w || !key || !value) return bc::fail(BC_ERR_ARGUMENT, "writer, key and value must be non-null");
+int32_t bcs_writer_kv_str(bcs_writer* w, const char* key, const char* value) {
+    if (!w || !key || !value) return fail(BCS_ERR_ARGUMENT, "writer, key and value must be non-null");
     put_str(w->kv, key);
     put_u32(w->kv, 8);
     put_str(w->kv, value);
     ++w->n_kv;
-    return BC_OK;
+    return BCS_OK;
 }
 
-bc_status bc_gguf_writer_kv_u32_array(bc_gguf_writer* w, const char* key, const uint32_t* values, uint64_t n) {
-    if (!w || !key || (!values && n)) return bc::fail(BC_ERR_ARGUMENT, "writer, key and values must be non-null");
+int32_t bcs_writer_kv_u32_array(bcs_writer* w, const char* key, const uint32_t* values, uint64_t n) {
+    if (!w || !key || (!values && n)) return fail(BCS_ERR_ARGUMENT, "writer, key and values must be non-null");
     put_str(w->kv, key);
     put_u32(w->kv, 9);
     put_u32(w->kv, 4);
     put_u64(w->kv, n);
     for (uint64_t i = 0; i < n; ++i) put_u32(w->kv, values[i]);
     ++w->n_kv;
-    return BC_OK;
+    return BCS_OK;
 }
 
-bc_status bc_gguf_writer_tensor(bc_gguf_writer* w, const char* name, int32_t type, const uint64_t* dims, uint32_t n_dims,
+int32_t bcs_writer_tensor(bcs_writer* w, const char* name, int32_t type, const uint64_t* dims, uint32_t n_dims,
                                 int32_t init, float value) {
-    if (!w || !name || !dims) return bc::fail(BC_ERR_ARGUMENT, "writer, name and dims must be non-null");
-    if (n_dims < 1 || n_dims > 4) return bc::fail(BC_ERR_ARGUMENT, "a tensor has 1 to 4 dimensions");
-    if (type != BC_F32 && type != BC_Q4_0) return bc::fail(BC_ERR_ARGUMENT, "the writer draws F32 and Q4_0 tensors");
-    if (init < BC_INIT_NORMAL || init > BC_INIT_NEG_EXP_NORMAL) return bc::fail(BC_ERR_ARGUMENT, "unknown init kind");
+    if (!w || !name || !dims) return fail(BCS_ERR_ARGUMENT, "writer, name and dims must be non-null");
+    if (n_dims < 1 || n_dims > 4) return fail(BCS_ERR_ARGUMENT, "a tensor has 1 to 4 dimensions");
+    if (type != BCS_F32 && type != BCS_Q4_0 && type != BCS_Q8_0) return fail(BCS_ERR_ARGUMENT, "the writer draws F32, Q4_0 and Q8_0 tensors");
+    if (init < BCS_INIT_NORMAL || init > BCS_INIT_NEG_EXP_NORMAL) return fail(BCS_ERR_ARGUMENT, "unknown init kind");
     TensorSpec t;
     t.name = name;
     t.type = (uint32_t)type;
@@ -209,17 +260,17 @@ bc_status bc_gguf_writer_tensor(bc_gguf_writer* w, const char* name, int32_t typ
     t.n_cols = dims[0];
     t.n_rows = 1;
     for (uint32_t d = 1; d < n_dims; ++d) t.n_rows *= dims[d];
-    if (t.n_cols == 0 || t.n_rows == 0) return bc::fail(BC_ERR_ARGUMENT, "tensor %s has an empty dimension", name);
-    if (type == BC_Q4_0 && t.n_cols % 32 != 0) return bc::fail(BC_ERR_ARGUMENT, "Q4_0 rows hold whole blocks of 32");
-    t.row_bytes = bc::type_row_bytes(t.type, t.n_cols);
+    if (t.n_cols == 0 || t.n_rows == 0) return fail(BCS_ERR_ARGUMENT, "tensor %s has an empty dimension", name);
+    if (type != BCS_F32 && t.n_cols % 32 != 0) return fail(BCS_ERR_ARGUMENT, "quantised rows hold whole blocks of 32");
+    t.row_bytes = type_row_bytes(t.type, t.n_cols);
     t.offset = 0;
     w->tensors.push_back(std::move(t));
-    return BC_OK;
+    return BCS_OK;
 }
 
-bc_status bc_gguf_writer_finish(bc_gguf_writer* w) {
-    if (!w) return bc::fail(BC_ERR_ARGUMENT, "writer must be non-null");
-    std::unique_ptr<bc_gguf_writer> owner(w);
+int32_t bcs_writer_finish(bcs_writer* w) {
+    if (!w) return fail(BCS_ERR_ARGUMENT, "writer must be non-null");
+    std::unique_ptr<bcs_writer> owner(w);
 
     std::vector<uint8_t> head;
     put_u32(head, 0x46554747u);
@@ -233,25 +284,25 @@ bc_status bc_gguf_writer_finish(bc_gguf_writer* w) {
     uint64_t relative = 0;
     for (TensorSpec& t : w->tensors) {
         t.offset = relative;
-        relative = bc::round_up(relative + t.n_rows * t.row_bytes, kAlignment);
+        relative = round_up(relative + t.n_rows * t.row_bytes, kAlignment);
         put_str(head, t.name);
         put_u32(head, (uint32_t)t.dims.size());
         for (uint64_t d : t.dims) put_u64(head, d);
         put_u32(head, t.type);
         put_u64(head, t.offset);
     }
-    uint64_t data_start = bc::round_up(head.size(), kAlignment);
+    uint64_t data_start = round_up(head.size(), kAlignment);
     uint64_t total = data_start + relative;
 
     int fd = ::open(w->path.c_str(), O_RDWR | O_CREAT | O_TRUNC, 0644);
-    if (fd < 0) return bc::fail(BC_ERR_IO, "cannot create %s: %s", w->path.c_str(), strerror(errno));
+    if (fd < 0) return fail(BCS_ERR_IO, "cannot create %s: %s", w->path.c_str(), strerror(errno));
     if (ftruncate(fd, (off_t)total) != 0) {
         ::close(fd);
-        return bc::fail(BC_ERR_IO, "cannot size %s: %s", w->path.c_str(), strerror(errno));
+        return fail(BCS_ERR_IO, "cannot size %s: %s", w->path.c_str(), strerror(errno));
     }
     void* map = mmap(nullptr, (size_t)total, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
     ::close(fd);
-    if (map == MAP_FAILED) return bc::fail(BC_ERR_IO, "cannot map %s: %s", w->path.c_str(), strerror(errno));
+    if (map == MAP_FAILED) return fail(BCS_ERR_IO, "cannot map %s: %s", w->path.c_str(), strerror(errno));
     uint8_t* base = (uint8_t*)map;
     std::memcpy(base, head.data(), head.size());
 
@@ -284,7 +335,7 @@ bc_status bc_gguf_writer_finish(bc_gguf_writer* w) {
     worker();
     for (std::thread& t : threads) t.join();
     munmap(map, (size_t)total);
-    return BC_OK;
+    return BCS_OK;
 }
 
 }  // extern "C"

@@ -12,6 +12,9 @@
  *    (crates/bobcat/src/lfm2_metal.rs:314-332, :363).
  *  - Handles are not thread-safe; distinct handles are independent
  *    (crates/bobcat/tests/metal_commands.rs:12-59).
+ *  - Views of activation vectors (x, y, norm weights, q, out) must start on a 16-byte boundary; the
+ *    kernels read them with 128-bit loads. Ops with a scalar variant fall back to it; the others
+ *    reject the offset with BC_ERR_ARGUMENT before launching anything.
  *  - There is no CPU fallback. Opening a backend without a CUDA device fails with BC_ERR_NO_DEVICE.
  */
 #ifndef BOBCAT_CUDA_H
@@ -213,6 +216,17 @@ bc_status bc_attention_static(void* stream, const float* q, const void* k_cache,
                               uint32_t n_queries, uint32_t n_ctx);
 /* Metal::argmax (backend.rs:2612-2617): index of the largest of n floats, ties to the lowest. */
 bc_status bc_op_argmax(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* out, size_t out_off, uint32_t n);
+/* Readback / Metal::new_readback / argmax_readback / read_readback (backend.rs:324-333,
+ * :2619-2676): token slots the CPU reads while later recordings still run. argmax_readback stores
+ * the index at `out` and in `slot`; bc_read_readback returns the slot's token once the recording
+ * that last wrote it has finished, BC_ERR_BUSY before that, BC_ERR_OUT_OF_BOUNDS for a slot no
+ * recording has written. */
+typedef struct bc_readback bc_readback;
+bc_status bc_readback_new(bc_backend* backend, size_t slots, bc_readback** out);
+void bc_readback_free(bc_readback* readback);
+bc_status bc_op_argmax_readback(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* out, size_t out_off, bc_readback* readback,
+                                size_t slot, uint32_t n);
+bc_status bc_read_readback(bc_backend* b, const bc_readback* readback, size_t slot, uint32_t* token);
 /* ---- mixture of experts. A token's route is 2 * n_used 32-bit words: the picked expert ids, then
  * their weights as float bits (crates/bobcat-metal/src/moe.metal:4-6); bc_route_bytes sizes it
  * (route_bytes, backend.rs:2724). At most 128 experts, 8 used (backend.rs:97-100). */
@@ -307,9 +321,6 @@ bc_status bc_model_hparams(const bc_model* model, bc_hparams* out);
 /* Writes 1 for each attention layer and 0 for each other layer (Model::attention_layers,
  * lfm2.rs:241-245). `out` holds n_layers bytes. */
 bc_status bc_model_attention_layers(const bc_model* model, uint8_t* out, size_t len);
-/* Bytes of weights one decoded token reads (every matrix once, active experts only), the figure
- * the decode roofline divides by (docs/design.md:15-34). */
-uint64_t bc_model_decode_bytes(const bc_model* model);
 
 /* ============================================================================================
  * Sequence: the device state of one decode.
@@ -357,35 +368,6 @@ bc_status bc_seq_restore(bc_seq* seq, const bc_checkpoint* checkpoint);
 void bc_checkpoint_free(bc_checkpoint* checkpoint);
 /* last_encode_seconds / last_gpu_seconds (lfm2_metal.rs:223-230). */
 bc_status bc_seq_timings(const bc_seq* seq, double* encode_seconds, double* gpu_seconds);
-/* Read back sequence state for tests: which = 0 conv / DeltaNet conv history, 1 K cache, 2 V cache
- * (as f32), 3 DeltaNet state. `layer` indexes layers of that kind. Returns the float count in
- * `n` and fills `out` (capacity `cap` floats) when non-null. */
-bc_status bc_seq_read_state(bc_seq* seq, int32_t which, uint32_t layer, float* out, size_t cap, size_t* n);
-/* How many kernels this sequence has launched so far (its own kernels, not library calls). */
-uint64_t bc_seq_launches(const bc_seq* seq);
-
-/* ============================================================================================
- * GGUF writing, for synthetic model files. No reference counterpart: the reference only reads
- * GGUF (crates/bobcat-gguf/src/lib.rs); files written here follow the layout that parser checks
- * (magic, version 3, general.alignment, aligned tensor offsets, whole quant blocks per row).
- * ============================================================================================ */
-typedef struct bc_gguf_writer bc_gguf_writer;
-/* How a tensor's values are drawn: a normal distribution N(0, std^2) from a counter-based
- * generator keyed by (seed, tensor order, row) so the bytes do not depend on thread count; a
- * constant; or -exp(N(0, std^2)) (the stored form of a DeltaNet decay, always negative). */
-enum { BC_INIT_NORMAL = 0, BC_INIT_CONSTANT = 1, BC_INIT_NEG_EXP_NORMAL = 2 };
-
-bc_status bc_gguf_writer_new(const char* path, uint64_t seed, bc_gguf_writer** out);
-bc_status bc_gguf_writer_kv_u32(bc_gguf_writer* w, const char* key, uint32_t value);
-bc_status bc_gguf_writer_kv_f32(bc_gguf_writer* w, const char* key, float value);
-bc_status bc_gguf_writer_kv_str(bc_gguf_writer* w, const char* key, const char* value);
-bc_status bc_gguf_writer_kv_u32_array(bc_gguf_writer* w, const char* key, const uint32_t* values, uint64_t n);
-/* `dims` is innermost-first (ne0 = columns). `type` is BC_F32 or BC_Q4_0 (quantised from the
- * drawn f32 values with ggml's reference Q4_0 rounding). */
-bc_status bc_gguf_writer_tensor(bc_gguf_writer* w, const char* name, int32_t type, const uint64_t* dims,
-                                uint32_t n_dims, int32_t init, float value);
-/* Draws every tensor (in parallel over rows) and writes the file. Frees the writer. */
-bc_status bc_gguf_writer_finish(bc_gguf_writer* w);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,243 @@
+"""The acceptance test of the path on the benchmark's own model shapes: the CUDA path against the
+CPU parity checker (the restated scalar path of the reference), not against itself.
+
+For each shape: a uniform-random prompt (seed 1), then greedy decoding. The generated tokens must
+equal the checker's for the first 64 tokens (fewer where the checker would take minutes), the
+logits after the last prompt token must lie within max-abs 2e-2 and cosine >= 0.9995 of the
+checker's, and the per-layer activations within the reference's 5e-3 (crates/bobcat/tests/
+lfm2_reference.rs:19-25, :581-672). For the mixture-of-experts shape the expert ids every layer
+picks must equal the checker's. Where a greedy sequence parts from the checker's, the failure
+names the index and the logit gap at that step."""
+
+import json
+import os
+
+import numpy as np
+import pytest
+
+from bobcat_b200 import Lfm2Cuda, Model, Qwen35Cuda
+from conftest import rel_error
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, COSINE, LAYER_TOLERANCE = 2e-2, 0.9995, 5e-3
+
+
+def note(**fields):
+    """Append a measurement to the file BOBCAT_MEASUREMENTS names (when set), for the record."""
+    path = os.environ.get("BOBCAT_MEASUREMENTS")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps(fields) + "\n")
+
+
+def cosine(a, b):
+    a, b = a.astype(np.float64), b.astype(np.float64)
+    return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b)))
+
+
+def checker_run(ref, prompt, n_decode, want_trace=False, want_experts=False):
+    """Prompt then greedy decode on the CPU checker. Returns the generated tokens, the logits of
+    every step from the last prompt token on, and (optionally) the traced layers / expert ids of
+    every prompt token."""
+    st = ref.state(len(prompt) + n_decode + 1)
+    layers, experts, logits = [], [], None
+    for i, tok in enumerate(prompt):
+        out = st.step(int(tok), want_logits=(i == len(prompt) - 1), want_trace=want_trace, want_experts=want_experts)
+        if want_trace:
+            layers.append(out["layers"])
+        if want_experts:
+            experts.append(out["experts"])
+        logits = out.get("logits")
+    all_logits, tokens = [logits], []
+    for _ in range(n_decode):
+        tok = int(np.argmax(all_logits[-1]))
+        tokens.append(tok)
+        all_logits.append(st.step(tok)["logits"])
+    return tokens, all_logits, layers, experts
+
+
+def assert_same_tokens(got, want, step_logits, label):
+    """Greedy tokens must be the checker's. On a difference, say where and how close the call was."""
+    got = [int(t) for t in got]
+    if got == want:
+        note(test=label, tokens=len(want), identical=True)
+        return
+    i = next(j for j, (a, b) in enumerate(zip(got, want)) if a != b)
+    lg = step_logits[i]
+    gap = float(lg[want[i]] - lg[got[i]])
+    note(test=label, tokens=len(want), identical=False, first_divergence=i, logit_gap=gap, logit_scale=float(np.abs(lg).max()))
+    raise AssertionError("%s: greedy token %d differs (checker %d, GPU %d); the checker's logits separate them by %.3g of a largest magnitude %.3g"
+                         % (label, i, want[i], got[i], gap, float(np.abs(lg).max())))
+
+
+def assert_logits(got, want, label):
+    max_abs, cos = float(np.abs(got - want).max()), cosine(got, want)
+    note(test=label, logits_max_abs=max_abs, logits_cosine=cos, logit_scale=float(np.abs(want).max()))
+    assert max_abs <= MAX_ABS, "%s: logits differ by %g" % (label, max_abs)
+    assert cos >= COSINE, "%s: logits cosine %g" % (label, cos)
+
+
+def test_lfm2_350m_full_request(model_path, cuda):
+    """Config 1 in full: 128-token prompt, 64 greedy tokens, every layer of every prompt token; f32
+    and f16 caches."""
+    path = model_path("lfm2-350m")
+    model, ref = Model.load(path), oracle.Model(path)
+    hp = model.hyperparameters()
+    prompt = np.random.default_rng(1).integers(0, hp.n_vocab, size=128).astype(np.uint32)
+    want_tokens, want_logits, want_layers, _ = checker_run(ref, prompt, 64, want_trace=True)
+    for kv_half in (False, True):
+        seq = Lfm2Cuda(model, cuda, 256, kv_half)
+        logits = np.zeros(hp.n_vocab, dtype=np.float32)
+        trace = model.trace(len(prompt))
+        seq.prefill(prompt, logits, trace=trace)
+        worst = max(rel_error(trace.layers[il, t], want_layers[t][il]) for t in range(len(prompt)) for il in range(hp.n_layers))
+        note(test="lfm2-350m layers kv_half=%s" % kv_half, worst_rel_error=worst)
+        assert worst < LAYER_TOLERANCE
+        label = "lfm2-350m 128+64 kv_half=%s" % kv_half
+        assert_logits(logits, want_logits[0], label)
+        assert_same_tokens(seq.generate(64), want_tokens, want_logits, label)
+        seq.close()
+
+
+def test_lfm2_2p6b_request(model_path, cuda):
+    """Config 2's model: 40-token prompt, 64 greedy tokens (the checker runs a few tokens a second
+    at this size), f16 cache as the benchmark uses, and the single-step path for the same tokens."""
+    path = model_path("lfm2-2.6b")
+    model, ref = Model.load(path), oracle.Model(path)
+    hp = model.hyperparameters()
+    prompt = np.random.default_rng(1).integers(0, hp.n_vocab, size=40).astype(np.uint32)
+    want_tokens, want_logits, _, _ = checker_run(ref, prompt, 64)
+    for kv_half in (True, False):
+        seq = Lfm2Cuda(model, cuda, 128, kv_half)
+        logits = np.zeros(hp.n_vocab, dtype=np.float32)
+        seq.prefill(prompt, logits)
+        label = "lfm2-2.6b 40+64 kv_half=%s" % kv_half
+        assert_logits(logits, want_logits[0], label)
+        assert_same_tokens(seq.generate(64), want_tokens, want_logits, label)
+        seq.close()
+    steps = Lfm2Cuda(model, cuda, 128, kv_half=False)
+    logits = np.zeros(hp.n_vocab, dtype=np.float32)
+    for tok in prompt:
+        steps.step(int(tok), logits)
+    assert_logits(logits, want_logits[0], "lfm2-2.6b stepped prompt")
+    assert_same_tokens(steps.generate(64), want_tokens, want_logits, "lfm2-2.6b stepped")
+    steps.close()
+
+
+def test_qwen35_2b_request(model_path, cuda):
+    """Config 3's model: 24-token prompt, 40 greedy tokens, layers of every prompt token."""
+    path = model_path("qwen35-2b")
+    model, ref = Model.load(path), oracle.Model(path)
+    hp = model.hyperparameters()
+    prompt = np.random.default_rng(1).integers(0, hp.n_vocab, size=24).astype(np.uint32)
+    want_tokens, want_logits, want_layers, _ = checker_run(ref, prompt, 40, want_trace=True)
+    seq = Qwen35Cuda(model, cuda, 96, kv_half=False)
+    logits = np.zeros(hp.n_vocab, dtype=np.float32)
+    trace = model.trace(len(prompt))
+    seq.prefill(prompt, logits, trace=trace)
+    worst = max(rel_error(trace.layers[il, t], want_layers[t][il]) for t in range(len(prompt)) for il in range(hp.n_layers))
+    note(test="qwen35-2b layers", worst_rel_error=worst)
+    assert worst < LAYER_TOLERANCE
+    assert_logits(logits, want_logits[0], "qwen35-2b 24+40")
+    assert_same_tokens(seq.generate(40), want_tokens, want_logits, "qwen35-2b 24+40")
+    seq.close()
+    half = Qwen35Cuda(model, cuda, 96, kv_half=True)
+    half.prefill(prompt, logits)
+    assert_logits(logits, want_logits[0], "qwen35-2b 24+40 f16 cache")
+    assert_same_tokens(half.generate(40), want_tokens, want_logits, "qwen35-2b 24+40 f16 cache")
+    half.close()
+
+
+def test_lfm2moe_8b_a1b_request_and_expert_ids(model_path, cuda):
+    """Config 4's model: on the single-step path the expert ids of every mixture-of-experts layer
+    equal the checker's for every prompt token; then 40 greedy tokens."""
+    path = model_path("lfm2moe-8b-a1b")
+    model, ref = Model.load(path), oracle.Model(path)
+    hp = model.hyperparameters()
+    prompt = np.random.default_rng(1).integers(0, hp.n_vocab, size=24).astype(np.uint32)
+    want_tokens, want_logits, want_layers, want_experts = checker_run(ref, prompt, 40, want_trace=True, want_experts=True)
+    seq = Lfm2Cuda(model, cuda, 96, kv_half=False)
+    logits = np.zeros(hp.n_vocab, dtype=np.float32)
+    picks = different = 0
+    for t, tok in enumerate(prompt):
+        trace = model.trace(1)
+        seq.step(int(tok), logits, trace)
+        got_ids = seq.traced_routes()[:, 0, :]
+        for il in range(hp.n_layers):
+            if want_experts[t][il][0] < 0:
+                continue  # a dense layer
+            picks += hp.n_experts_used
+            different += int(np.sum(got_ids[il].astype(np.int64) != want_experts[t][il].astype(np.int64)))
+            assert np.array_equal(got_ids[il].astype(np.int64), want_experts[t][il].astype(np.int64)), (t, il)
+            assert rel_error(trace.layers[il, 0], want_layers[t][il]) < LAYER_TOLERANCE, (t, il)
+    note(test="lfm2moe-8b-a1b expert ids, stepped", picks=picks, different=different)
+    assert picks == len(prompt) * (hp.n_layers - 2) * hp.n_experts_used
+    assert_logits(logits, want_logits[0], "lfm2moe-8b-a1b stepped prompt")
+    assert_same_tokens(seq.generate(40), want_tokens, want_logits, "lfm2moe-8b-a1b 24+40")
+    seq.close()
+
+
+def test_lfm2moe_8b_a1b_batched_against_stepped_routes(model_path, cuda):
+    """Batched prefill rounds its inputs to half precision (as the reference's Q4_0 prefill does), so
+    a router near-tie can fall the other way than on the single-step path. Measured, not assumed:
+    count the picks that differ over 192 tokens x 22 layers x 4, and hold the logits to the
+    acceptance bound whenever none differs."""
+    path = model_path("lfm2moe-8b-a1b")
+    model = Model.load(path)
+    hp = model.hyperparameters()
+    tokens = np.random.default_rng(9).integers(0, hp.n_vocab, size=192).astype(np.uint32)
+    seq = Lfm2Cuda(model, cuda, 256, kv_half=True)
+    logits = np.zeros(hp.n_vocab, dtype=np.float32)
+    trace = model.trace(len(tokens))
+    seq.prefill(tokens, logits, trace=trace)
+    batched = np.sort(seq.traced_routes()[:, : len(tokens), :], axis=2)
+    steps = Lfm2Cuda(model, cuda, 256, kv_half=True)
+    step_logits = np.zeros_like(logits)
+    stepped = np.zeros_like(batched)
+    for t, tok in enumerate(tokens):
+        one = model.trace(1)
+        steps.step(int(tok), step_logits, one)
+        stepped[:, t, :] = np.sort(steps.traced_routes()[:, 0, :], axis=1)
+    moe_layers = hp.n_layers - 2
+    total = moe_layers * len(tokens) * hp.n_experts_used
+    different = int(np.sum(batched[2:] != stepped[2:]))
+    max_abs, cos = float(np.abs(logits - step_logits).max()), cosine(logits, step_logits)
+    note(test="lfm2moe-8b-a1b batched vs stepped", picks=total, different=different, logits_max_abs=max_abs, logits_cosine=cos,
+         logit_scale=float(np.abs(step_logits).max()))
+    # A pick differs only at a near-tie; more than one in a hundred would mean the batched router is wrong.
+    assert different <= total // 100, "%d of %d picks differ" % (different, total)
+    if different == 0:
+        assert max_abs <= MAX_ABS and cos >= COSINE
+    seq.close()
+    steps.close()
+
+
+# (n_heads, n_kv_heads, head_dim, last position): one query deep into a long context, the decode
+# shapes of configs 3 and 5 (crates/bobcat/tests/metal_attention.rs:11-161 at the reference's sizes).
+LONG_CONTEXT = [(8, 2, 256, 2303), (16, 4, 256, 2303), (8, 2, 256, 65535), (16, 4, 256, 65535), (32, 8, 64, 65535)]
+
+
+@pytest.mark.parametrize("case", LONG_CONTEXT)
+def test_attention_deep_in_a_long_context(cuda, case):
+    n_heads, n_kv, hd, pos = case
+    n_ctx = pos + 1
+    rng = np.random.default_rng(pos + n_heads)
+    q = rng.uniform(-1, 1, (1, n_heads, hd)).astype(np.float32)
+    k = rng.uniform(-1, 1, (n_ctx, n_kv, hd)).astype(np.float16)
+    v = rng.uniform(-1, 1, (n_ctx, n_kv, hd)).astype(np.float16)
+    qb, kb, vb = cuda.buffer_from(q), cuda.buffer_from(k), cuda.buffer_from(v)
+    sb = cuda.new_buffer(cuda.attention_scratch_floats(n_heads, hd, n_ctx, 1) * 4)
+    ob = cuda.new_buffer(q.nbytes)
+    cuda.begin(); cuda.attention(qb, kb, vb, True, sb, ob, n_heads, n_kv, hd, pos, 1, n_ctx); cuda.end()
+    got = cuda.read(ob, np.zeros_like(q))
+    group = n_heads // n_kv
+    want = np.zeros((n_heads, hd))
+    for kv_head in range(n_kv):
+        k64, v64 = k[:, kv_head].astype(np.float64), v[:, kv_head].astype(np.float64)
+        for h in range(kv_head * group, (kv_head + 1) * group):
+            s = k64 @ q[0, h].astype(np.float64) / np.sqrt(hd)
+            p = np.exp(s - s.max())
+            want[h] = (p / p.sum()) @ v64
+    assert np.abs(got[0] - want).max() < 2e-6

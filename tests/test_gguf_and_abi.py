@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "bobcat_cuda.h")).read()
+    text = "".join(open(os.path.join(ROOT, "include", name)).read() for name in sorted(os.listdir(os.path.join(ROOT, "include"))) if name.endswith(".h"))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(bc_[a-z0-9_]+)\s*\(", text)) - {"bc_emit_fn"})
 

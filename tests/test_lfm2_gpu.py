@@ -157,6 +157,24 @@ def test_restore_continues_from_the_checkpoint(pair, cuda):
         seq.restore(ckpt)
 
 
+def test_restore_rejects_another_sequences_checkpoint(pair, cuda):
+    """A checkpoint carries the recurrent state only; the KV rows of its prefix stay in the cache
+    of the sequence that took it (lfm2_metal.rs:250-288), so a second sequence of the same model
+    must refuse it instead of decoding over rows it never wrote."""
+    model, _ = pair
+    hp = model.hyperparameters()
+    tokens = prompt_tokens(hp.n_vocab, 12, seed=6)
+    a = Lfm2Cuda(model, cuda, 64, kv_half=True)
+    b = Lfm2Cuda(model, cuda, 64, kv_half=True)
+    a.prefill(tokens)
+    b.prefill(tokens)
+    ckpt = a.checkpoint()
+    with pytest.raises(errors.Argument):
+        b.restore(ckpt)
+    assert b.n_past() == 12
+    a.restore(ckpt)
+
+
 def test_streaming_matches_generate(pair, cuda):
     model, _ = pair
     hp = model.hyperparameters()

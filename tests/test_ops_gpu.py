@@ -387,3 +387,83 @@ def test_profile_table(cuda):
     entries = cuda.profile()
     entry = [e for e in entries if e["name"] == "matvec" and e["n_rows"] == 64][0]
     assert entry["calls"] == 3 and entry["seconds"] > 0 and entry["bytes"] == 3 * 64 * 64 // 32 * 18
+
+
+def test_unaligned_attention_views_take_the_scalar_kernels(cuda):
+    """A view may start at any float (the reference's View allows any element-aligned offset). The
+    tensor-core and the 16-byte-load kernels need aligned rows, so a q that starts 4 bytes into its
+    buffer must run on the scalar chunk kernels and give what the aligned call gives."""
+    rng = np.random.default_rng(5)
+    first_pos, n_q, n_heads, n_kv, hd = 40, 40, 8, 2, 64  # a shape the tensor-core prefill kernel takes
+    n_ctx = first_pos + n_q
+    q = rng.uniform(-1, 1, (n_q, n_heads, hd)).astype(np.float32)
+    k = rng.uniform(-1, 1, (n_ctx, n_kv, hd)).astype(np.float16)
+    v = rng.uniform(-1, 1, (n_ctx, n_kv, hd)).astype(np.float16)
+    shifted = np.concatenate([np.zeros(1, dtype=np.float32), q.ravel()])
+    qb, qs, kb, vb = cuda.buffer_from(q), cuda.buffer_from(shifted), cuda.buffer_from(k), cuda.buffer_from(v)
+    sb = cuda.new_buffer(cuda.attention_scratch_floats(n_heads, hd, n_ctx, n_q) * 4)
+    a, b = cuda.new_buffer(q.nbytes), cuda.new_buffer(q.nbytes + 4)
+    cuda.begin()
+    cuda.attention(qb, kb, vb, True, sb, a, n_heads, n_kv, hd, first_pos, n_q, n_ctx)
+    cuda.end()
+    cuda.begin()
+    cuda.attention(qs.at(4), kb, vb, True, sb, b.at(4), n_heads, n_kv, hd, first_pos, n_q, n_ctx)
+    cuda.end()
+    aligned = cuda.read(a, np.zeros_like(q))
+    unaligned = cuda.read(b.at(4), np.zeros_like(q))
+    assert np.abs(aligned - unaligned).max() < 4e-6
+    # One query, where the aligned call takes the 16-byte-load decode kernel.
+    cuda.begin()
+    cuda.attention(qb, kb, vb, True, sb, a, n_heads, n_kv, hd, first_pos, 1, n_ctx)
+    cuda.attention(qs.at(4), kb, vb, True, sb, b.at(4), n_heads, n_kv, hd, first_pos, 1, n_ctx)
+    cuda.end()
+    one_a = cuda.read(a, np.zeros((n_heads, hd), dtype=np.float32))
+    one_b = cuda.read(b.at(4), np.zeros((n_heads, hd), dtype=np.float32))
+    assert np.abs(one_a - one_b).max() < 2e-6
+
+
+def test_unaligned_activation_offsets_are_rejected_before_launch(cuda):
+    """The matrix-vector and batched products read their vectors 16 bytes at a time and have no
+    scalar variant, so an offset off that boundary is an argument error, never a launch."""
+    rng = np.random.default_rng(6)
+    raw, _ = make_matrix(rng, Q4_0, 64, 64)
+    wb = cuda.upload_matrix(Q4_0, raw, 64, 64)
+    xb, yb, nb = cuda.new_buffer(1024), cuda.new_buffer(1024), cuda.new_buffer(1024)
+    cuda.begin()
+    with pytest.raises(errors.Argument):
+        cuda.matvec(Q4_0, wb, 64, 64, xb.at(4), yb)
+    with pytest.raises(errors.Argument):
+        cuda.matvec(Q4_0, wb, 64, 64, xb, yb.at(8))
+    with pytest.raises(errors.Argument):
+        cuda.matvec(Q4_0, wb, 64, 64, xb, yb, Norm(nb.at(12), 1e-5))
+    with pytest.raises(errors.Argument):
+        cuda.matvec_swiglu(Q4_0, wb, wb, 64, 64, xb.at(4), Norm(nb.at(0), 1e-5), yb)
+    with pytest.raises(errors.Argument):
+        cuda.matmul(Q4_0, wb, 64, 64, xb.at(4), yb, 2, OVERWRITE)
+    cuda.matvec(Q4_0, wb, 64, 64, xb.at(16), yb.at(32))  # aligned offsets still launch
+    cuda.end()
+
+
+def test_argmax_readback_slots(cuda):
+    """Metal::argmax_readback / read_readback (backend.rs:2619-2663): the slot holds the token once
+    the recording that wrote it has finished; an unwritten slot is out of bounds; a slot whose
+    writer is still open is busy."""
+    x = np.zeros(5000, dtype=np.float32)
+    x[777] = 2.0
+    xb, ob = cuda.buffer_from(x), cuda.new_buffer(4)
+    rb = cuda.new_readback(3)
+    with pytest.raises(errors.OutOfBounds):
+        cuda.read_readback(rb, 1)
+    cuda.begin()
+    cuda.argmax_readback(xb, ob, rb, 1, x.size)
+    with pytest.raises(errors.Busy):
+        cuda.read_readback(rb, 1)
+    with pytest.raises(errors.OutOfBounds):
+        cuda.argmax_readback(xb, ob, rb, 3, x.size)
+    ticket = cuda.commit()
+    cuda.wait(ticket)
+    assert cuda.read_readback(rb, 1) == 777
+    assert int(cuda.read(ob, np.zeros(1, dtype=np.uint32))[0]) == 777
+    with pytest.raises(errors.OutOfBounds):
+        cuda.read_readback(rb, 0)
+    rb.close()

@@ -46,13 +46,66 @@ def test_static_scratch_attention_matches_twice_in_a_row():
     cuda.close()
 
 
+def test_static_scratch_attention_allocates_nothing():
+    """The property the entry point exists for: after a warm-up call (which looks up the array's
+    address once), further calls on all three dispatch paths (16-position chunks, 64-position
+    chunks, the tensor-core prefill kernel) leave the device's free memory unchanged."""
+    import torch
+
+    cuda = Cuda.open(0)
+    rng = np.random.default_rng(7)
+    L = cuda._L
+    cases = [(300, 1, 32, 8, 64, True), (20, 40, 8, 2, 128, False), (64, 64, 16, 4, 64, True)]
+    prepared = []
+    for first_pos, n_q, n_heads, n_kv, hd, kv_half in cases:
+        n_ctx = first_pos + n_q
+        kv_type = np.float16 if kv_half else np.float32
+        q = cuda.buffer_from(rng.uniform(-1, 1, (n_q, n_heads, hd)).astype(np.float32))
+        k = cuda.buffer_from(rng.uniform(-1, 1, (n_ctx, n_kv, hd)).astype(kv_type))
+        v = cuda.buffer_from(rng.uniform(-1, 1, (n_ctx, n_kv, hd)).astype(kv_type))
+        out = cuda.new_buffer(n_q * n_heads * hd * 4)
+        prepared.append((q, k, v, out, int(kv_half), n_heads, n_kv, hd, first_pos, n_q, n_ctx))
+
+    def call(c):
+        q, k, v, out, half, n_heads, n_kv, hd, first_pos, n_q, n_ctx = c
+        errors.check(L.bc_attention_static(cuda.stream, q.device_ptr, k.device_ptr, v.device_ptr, half, out.device_ptr, n_heads, n_kv, hd,
+                                           first_pos, n_q, n_ctx), L)
+
+    for c in prepared:  # warm-up: kernels loaded, shared-memory limits raised, address looked up
+        call(c)
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        for c in prepared:
+            call(c)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    cuda.close()
+
+
+def test_static_scratch_attention_at_its_capacity():
+    """One query over 32 heads of 64 elements fits up to 15 872 positions (992 chunks of 16); the
+    largest accepted shape matches bc_op_attention and one chunk more is rejected. The capacity
+    follows the positions in use, not the cache's size."""
+    cuda = Cuda.open(0)
+    rng = np.random.default_rng(3)
+    got, want = run_both(cuda, rng, 15871, 1, 32, 8, 64, True)
+    assert np.array_equal(got, want)
+    L = cuda._L
+    b = cuda.new_buffer(1 << 12)
+    p = b.device_ptr
+    status = L.bc_attention_static(cuda.stream, p, p, p, 1, p, 32, 8, 64, 15872, 1, 1 << 18)
+    assert status == errors.Argument.status and b"built-in scratch" in L.bc_last_error()
+    cuda.close()
+
+
 def test_static_scratch_attention_rejects_what_does_not_fit():
     cuda = Cuda.open(0)
     L = cuda._L
     b = cuda.new_buffer(1 << 12)
     p = b.device_ptr
     # 64 queries x 32 heads x 4096 chunks x 66 floats is far beyond the built-in 2 Mi floats.
-    status = L.bc_attention_static(cuda.stream, p, p, p, 0, p, 32, 8, 64, 0, 64, 1 << 18)
+    status = L.bc_attention_static(cuda.stream, p, p, p, 0, p, 32, 8, 64, (1 << 18) - 64, 64, 1 << 18)
     assert status == errors.Argument.status and b"built-in scratch" in L.bc_last_error()
     assert L.bc_attention_static(cuda.stream, None, p, p, 0, p, 32, 8, 64, 0, 1, 64) == errors.Argument.status
     assert L.bc_attention_static(cuda.stream, p, p, p, 0, p, 32, 8, 48, 0, 1, 64) == errors.AttentionLimits.status
