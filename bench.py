@@ -199,10 +199,10 @@ def dominant_kernel(cuda, seq, prompt) -> dict:
     per_launch_s = top["seconds"] / top["calls"]
     per_launch_bytes = top["bytes"] / top["calls"]
     return {"top": top, "share": top["seconds"] / total, "seconds": per_launch_s, "bytes": per_launch_bytes,
-            "table": rows_of(entries, 8), "prefill_table": prefill_table}
+            "table": rows_of(entries, 8), "all": rows_of(entries, len(entries)), "prefill_table": prefill_table}
 
 
-def in_graph_costs(seq, prompt, table, full_token_seconds: float) -> list[dict]:
+def in_graph_costs(seq, prompt, table, every) -> list[dict]:
     """What each kind of launch costs inside the replayed decode step, where launches overlap their
     neighbours: the step is re-captured with that kind left out and the difference in time per token
     is divided by its launches per token. (The per-launch event timing of `dominant_kernel`
@@ -230,12 +230,110 @@ def in_graph_costs(seq, prompt, table, full_token_seconds: float) -> list[dict]:
             seen.add(key)
             seq.set_skip(row["kernel"], 0 if by_name else row["rows"], 0 if by_name else row["cols"])
             without = decode_seconds()
-            calls_per_token = sum(r["calls"] for r in table if r["kernel"] == row["kernel"]) / steps if by_name else row["calls"] / steps
+            calls_per_token = sum(r["calls"] for r in every if r["kernel"] == row["kernel"]) / steps if by_name else row["calls"] / steps
             out.append({"kernel": row["kernel"], "rows": row["rows"], "cols": row["cols"], "calls_per_token": calls_per_token,
                         "us": 1e6 * (full - without) / calls_per_token if calls_per_token else None})
     finally:
         seq.set_skip(None)
     return out
+
+
+def run_batch(args) -> None:
+    """--seqs B > 1: B concurrent sequences of one model per GPU (the multi-sequence decode), every
+    weight read once per pass for all of them. `value` is aggregate decode tokens per second."""
+    import torch
+    import torch.distributed as dist
+
+    from bobcat_b200 import BatchCuda, Cuda, Model, replicas
+
+    rank, local_rank, world = rank_info()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if rank == 0:
+        model_file(args.config)
+    if world > 1:
+        dist.barrier()
+    path = model_file(args.config)
+    model = Model.load(path)
+    hp = model.hyperparameters()
+    torch.cuda.set_stream(torch.cuda.Stream())
+    cuda = Cuda.open(local_rank, torch.cuda.current_stream().cuda_stream)
+    n_seqs = args.seqs
+    batch = BatchCuda(model, cuda, n_seqs, PROMPT_TOKENS + DECODE_TOKENS, kv_half=True)
+    # Every sequence of every rank has its own prompt.
+    prompts = [torch.from_numpy(prompt_for(hp.n_vocab, 1 + rank * n_seqs + i).view(np.int32).copy()).pin_memory() for i in range(n_seqs)]
+
+    def request():
+        t0 = time.perf_counter()
+        prefill_gpu = 0.0
+        for i in range(n_seqs):
+            seq = batch.seq(i)
+            seq.reset()
+            ids = prompts[i].numpy().view(np.uint32)
+            for first in range(0, PROMPT_TOKENS, PREFILL_CHUNK):
+                seq.prefill(ids[first:first + PREFILL_CHUNK])
+                prefill_gpu += seq.last_gpu_seconds()
+        t1 = time.perf_counter()
+        tokens = batch.generate(DECODE_TOKENS)
+        t2 = time.perf_counter()
+        return prefill_gpu, batch.last_gpu_seconds(), t1 - t0, t2 - t1, tokens
+
+    for _ in range(args.warmup):
+        request()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    launches_before = batch.launches()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    rows = [request() for _ in range(args.steps)]
+    end.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    prefill_gpu, decode_gpu, prefill_wall, decode_wall, ms_per_step = replicas.max_over_ranks(
+        [float(np.mean([r[0] for r in rows])), float(np.mean([r[1] for r in rows])), float(np.mean([r[2] for r in rows])),
+         float(np.mean([r[3] for r in rows])), start.elapsed_time(end) / args.steps], device="cuda")
+    launches = replicas.sum_over_ranks([batch.launches() - launches_before], device="cuda")[0]
+    if rank == 0:
+        peak, tensor_peak, peak_kind = measured_peaks()
+        # A pass of many sequences touches (nearly) every expert, so its bytes are every weight
+        # once (each distinct expert counted once), plus every sequence's KV rows.
+        import gguf
+        reader = gguf.GGUFReader(path)
+        all_weight_bytes = int(sum(int(t.n_bytes) for t in reader.tensors)) - hp.n_vocab * hp.n_embd * 4 + hp.n_vocab * hp.n_embd * 4
+        kv_bytes = n_seqs * hp.n_attention_layers * 2 * hp.n_kv_heads * hp.head_dim * 2 * (PROMPT_TOKENS + DECODE_TOKENS / 2)
+        step_bytes = all_weight_bytes + kv_bytes
+        tok_s = world * n_seqs * DECODE_TOKENS / decode_gpu
+        line = {
+            "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations (half-precision operands in the batched products), Q4_0 weights, f16 KV",
+            "data": "synthetic",
+            "config": {"workload": "%s Q4_0 (random init N(0,0.02), seed 0), %d concurrent sequences per GPU, each a %d-token uniform-random prompt then %d greedy tokens; "
+                                   "%d replica(s) of that batch, one per GPU" % (args.config, n_seqs, PROMPT_TOKENS, DECODE_TOKENS, world),
+                       "l2": "every pass streams %.2f GB of weights, far larger than the 126 MB L2" % (all_weight_bytes / 1e9), "kv_cache": "f16"},
+            "decode": {"tok_s": tok_s, "passes_per_s": world * DECODE_TOKENS / decode_gpu, "ms_per_pass": 1e3 * decode_gpu / DECODE_TOKENS,
+                       "bytes_per_pass": step_bytes, "hbm_gbs": step_bytes * DECODE_TOKENS / decode_gpu / 1e9,
+                       "hbm_frac": step_bytes * DECODE_TOKENS / decode_gpu / 1e9 / peak, "token_hash": replicas.token_hash(rows[-1][4].ravel().tolist())},
+            "prefill": {"tok_s": world * n_seqs * PROMPT_TOKENS / prefill_gpu},
+            "roofline": {"bound": "hbm", "kernel": "whole multi-sequence pass", "achieved": step_bytes * DECODE_TOKENS / decode_gpu / 1e9, "peak": peak,
+                         "peak_kind": peak_kind, "unit": "GB/s", "frac": step_bytes * DECODE_TOKENS / decode_gpu / 1e9 / peak, "traffic": None},
+            "e2e": {"value": world * n_seqs * DECODE_TOKENS / decode_wall, "unit": "tok/s", "h2d_bytes_per_step": n_seqs * PROMPT_TOKENS * 4,
+                    "d2h_bytes_per_step": n_seqs * DECODE_TOKENS * 4},
+            "gpu_launches": launches, "clocks": clocks,
+        }
+        print(json.dumps(line))
+    batch.close()
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_ours(args) -> None:
@@ -349,7 +447,7 @@ def run_ours(args) -> None:
         for tok in rows[-1][4].tolist():
             token_hash = (token_hash * 1000003 + tok) & 0xFFFFFFFFFFFFFFFF
         dom = dominant_kernel(cuda, seq, prompt)
-        in_graph = in_graph_costs(seq, prompt, dom["table"], decode_gpu / DECODE_TOKENS)
+        in_graph = in_graph_costs(seq, prompt, dom["table"], dom["all"])
         achieved = dom["bytes"] / dom["seconds"] / 1e9
         top_key = "%s %dx%d" % (dom["top"]["name"], dom["top"]["n_rows"], dom["top"]["n_cols"])
         cpu_rate, cpu_seconds = cpu_sample(path, 1, 2, 4) if world == 1 and not args.no_cpu_baseline else (None, None)
@@ -401,6 +499,7 @@ def main() -> None:
     parser.add_argument("--prompt-tokens", type=int, default=0, help="shorter requests, for profiler captures only (0: the configuration's own)")
     parser.add_argument("--decode-tokens", type=int, default=0)
     parser.add_argument("--prefill-chunk", type=int, default=0)
+    parser.add_argument("--seqs", type=int, default=1, help="concurrent sequences per GPU (the multi-sequence decode when > 1)")
     args = parser.parse_args()
     protocol = PROTOCOLS.get(args.config, (512, 128, 512))
     PROMPT_TOKENS = args.prompt_tokens or protocol[0]
@@ -409,6 +508,8 @@ def main() -> None:
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.seqs > 1:
+        run_batch(args)
     else:
         run_ours(args)
 

@@ -107,6 +107,12 @@ SIGNATURES = {
     "bc_checkpoint_free": (None, [vp]),
     "bc_seq_timings": (i32, [vp, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "bc_seq_read_state": (i32, [vp, i32, u32, vp, sz, C.POINTER(sz)]),
+    "bc_batch_new": (i32, [vp, vp, u32, u32, i32, C.POINTER(vp)]),
+    "bc_batch_free": (None, [vp]),
+    "bc_batch_n_seqs": (u32, [vp]),
+    "bc_batch_seq": (i32, [vp, u32, C.POINTER(vp)]),
+    "bc_batch_generate": (i32, [vp, vp, sz]),
+    "bc_batch_timings": (i32, [vp, C.POINTER(C.c_double), C.POINTER(u64)]),
     "bc_seq_launches": (u64, [vp]),
     "bc_seq_set_skip": (i32, [vp, C.c_char_p, u32, u32]),
 }

@@ -47,6 +47,9 @@ bc_status kernel_wait_status() {
 
 }  // namespace bc
 
+// Defined with the sequence (seq.cpp): frees its device state and detaches it from its backend.
+void release_seq(bc_seq* seq);
+
 using namespace bc;
 
 bc_status bc_backend::activate() {
@@ -138,6 +141,9 @@ void bc_backend_close(bc_backend* b) {
     if (!b) return;
     cudaSetDevice(b->device);
     cudaStreamSynchronize(b->stream);
+    // Sequences that outlive their backend give up their device state now and stay behind as
+    // handles that only bc_seq_free may still be called on.
+    while (!b->seqs.empty()) release_seq(*b->seqs.begin());
     for (auto& t : b->tickets) cudaEventDestroy(t.second);
     for (auto& t : b->ticket_starts) cudaEventDestroy(t.second);
     if (b->record_start) cudaEventDestroy(b->record_start);

@@ -15,6 +15,8 @@
 #include "gguf.h"
 #include "kernels.h"
 
+struct bc_seq;
+
 struct bc_buffer {
     bc_backend* backend = nullptr;
     void* ptr = nullptr;
@@ -58,6 +60,7 @@ struct bc_backend {
     std::map<uint64_t, cudaEvent_t> tickets;  // ticket -> end-of-recording event
     std::map<uint64_t, cudaEvent_t> ticket_starts;
     std::set<bc_buffer*> buffers;
+    std::set<bc_seq*> seqs;  // sequences recording onto this backend; closing the backend releases them
     uint64_t launches = 0;  // kernels launched through this backend
     // Scratch of the tensor-core prefill kernel: the fp16 operand-layout copy of a matmul's inputs.
     // Grown on demand; only launches of this backend's stream touch it, one after another.

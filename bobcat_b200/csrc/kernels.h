@@ -73,7 +73,8 @@ cudaError_t matvec_swiglu_mma(cudaStream_t stream, const Mat& gate, const Mat& u
 cudaError_t matvec_conv_mma(cudaStream_t stream, const Mat& in_proj, const float* x, Norm norm, const float* taps, float* history,
                             float* out, uint32_t n_embd, uint32_t kernel);
 cudaError_t matvec_mma_prepare(uint32_t widest_cols);
-// Nonzero once a bounded wait inside a kernel gave up (1: a ring slot never freed, 2: a chunk never arrived).
+// Nonzero once a bounded wait inside a kernel gave up (1: a ring slot never freed, 2: a chunk never
+// arrived). Reading clears it.
 int matvec_error_flag();
 // Raise the shared-memory limit of every matvec kernel for input vectors of up to `widest_cols`.
 cudaError_t matvec_prepare(uint32_t widest_cols);
@@ -158,6 +159,33 @@ cudaError_t attention_flash(cudaStream_t stream, const float* q, const void* k_c
 // argmax over n floats, ties to the lowest index. `out` is a device word; `readback` (nullable) is
 // a host-mapped word that receives the same value.
 cudaError_t argmax(cudaStream_t stream, const float* x, uint32_t n, uint32_t* out, uint32_t* readback);
+
+// ---- multi-sequence decode (kernels_batch.cu): one new token of each of n_seqs sequences per pass.
+// What is per sequence is reached through device arrays indexed by the sequence's row.
+struct SeqTable {
+    const uint32_t* pos = nullptr;      // [n_seqs] position of each sequence's new token
+    void* const* k_cache = nullptr;     // [n_seqs] each sequence's K cache (first layer's first row)
+    void* const* v_cache = nullptr;     // [n_seqs] likewise for V
+    float* const* conv_state = nullptr; // [n_seqs] each sequence's convolution history (first layer's)
+    uint64_t layer_offset = 0;          // elements from a cache base to the layer's first row
+    uint64_t conv_offset = 0;           // floats from a history base to the layer's history
+};
+// rope_store for row b of q / k / v at position pos[b] into sequence b's caches; q_stride is the
+// element stride between rows of q.
+cudaError_t rope_store_seqs(cudaStream_t stream, const RopeStore& p, const SeqTable& seqs, uint32_t q_stride, uint32_t n_seqs);
+// Attention of row b of q over positions [0, pos[b]] of sequence b's caches; out is [n_seqs][n_heads * head_dim].
+bool attention_seqs_supported(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim);
+cudaError_t attention_seqs(cudaStream_t stream, const float* q, float* out, const SeqTable& seqs, bool kv_half, uint32_t n_heads,
+                           uint32_t n_kv_heads, uint32_t head_dim, uint32_t q_stride, uint32_t q_head_stride, uint32_t n_seqs);
+// The LFM2 gated short convolution of one token per sequence, each with its own history.
+cudaError_t short_conv_seqs(cudaStream_t stream, const float* bcx, const float* taps, const SeqTable& seqs, float* out, uint32_t n_embd,
+                            uint32_t kernel, uint32_t n_seqs);
+// picked[r] = argmax of row r of x (n floats each), ties to the lowest index; when `record` is
+// non-null record[r * record_stride + record_at] takes it too.
+cudaError_t argmax_rows(cudaStream_t stream, const float* x, uint32_t n, uint32_t n_rows, uint32_t* picked, uint32_t* record,
+                        uint32_t record_stride, uint32_t record_at);
+// pos[b] += 1 for every sequence.
+cudaError_t advance_seqs(cudaStream_t stream, uint32_t* pos, uint32_t n_seqs);
 
 // ---- Qwen3.5 (kernels_gdn.cu)
 // DeltaNet causal convolution with SiLU over [n_tokens][conv_dim]; history [conv_dim][kernel - 1].

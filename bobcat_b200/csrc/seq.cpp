@@ -1,4 +1,5 @@
 #include "seq.h"
+#include "recorder.h"
 
 #include <algorithm>
 #include <initializer_list>
@@ -14,409 +15,6 @@ namespace {
 
 using Clock = std::chrono::steady_clock;
 double since(Clock::time_point start) { return std::chrono::duration<double>(Clock::now() - start).count(); }
-
-// Records forward passes of one sequence onto its backend's stream.
-struct Recorder {
-    bc_seq& s;
-    const bc_hparams& hp;
-    cudaStream_t stream;
-    bc_status status = BC_OK;
-    // When set, single-token passes read their position from s.step_pos on the device, so the
-    // launches can be captured once and replayed at every position.
-    bool replayed = false;
-    // Traced passes of a mixture-of-experts model: where the next router launch's routes are copied to.
-    uint32_t* route_trace = nullptr;
-
-    explicit Recorder(bc_seq& seq) : s(seq), hp(seq.model->hp), stream(seq.backend->stream) {}
-
-    k::Pos at(uint32_t pos) const { return replayed ? k::Pos{s.step_pos, 0} : k::Pos{nullptr, pos}; }
-
-    // Launch helper: counts the kernel, keeps the first failure.
-    template <typename F>
-    void run(const char* name, uint32_t rows, uint32_t cols, uint64_t bytes, int kernels, F&& f) {
-        if (status != BC_OK) return;
-        // Timing diagnostics: a launch kind left out of the pass (its outputs keep stale values).
-        if (!s.skip_name.empty() && s.skip_name == name && (s.skip_rows == 0 || s.skip_rows == rows) && (s.skip_cols == 0 || s.skip_cols == cols)) return;
-        s.launches += (uint64_t)kernels;
-        status = s.backend->run(name, rows, cols, bytes, kernels, f);
-    }
-
-    k::Norm norm(const float* weight) const { return k::Norm{weight, hp.norm_eps}; }
-
-    void matvec(const k::Mat& w, const float* x, float* y, k::Norm nm, bool accumulate) {
-        k::MatvecSegment seg{w, y};
-        run("matvec", w.n_rows, w.n_cols, w.bytes(), 1, [&] { return k::matvec(stream, &seg, 1, x, nm, accumulate); });
-    }
-
-    void matmul(const k::Mat& w, const float* x, float* y, uint32_t n, int store) {
-        void* pack = nullptr;
-        if (status == BC_OK && k::matmul_umma_supported(w, n)) status = s.backend->pack_scratch(k::matmul_scratch_bytes(w, n), &pack);
-        run("matmul", w.n_rows, w.n_cols, w.bytes(), pack ? k::matmul_umma_launches(w, n) : 1, [&] { return k::matmul(stream, w, x, y, n, w.n_rows, store, pack); });
-    }
-
-    // RMSNorm of the batch, then products that all read the normalised rows. When every product
-    // runs on the tensor-core kernel the normalised rows are packed to fp16 once, straight from the
-    // residual stream, and the f32 copy is never written; otherwise s.normed takes them first.
-    struct Product {
-        const k::Mat* w;
-        float* y;
-        int store;
-    };
-    // ffn = silu(gate x^) * (up x^) over the batch, x^ the normalised rows.
-    void normed_swiglu(const float* x, const float* norm_weight, uint32_t n, const k::Mat& gate, const k::Mat& up, float* y) {
-        if (!k::matmul_umma_swiglu_supported(gate, up, n)) {
-            // The up projection's store combines with the gate projection already in the buffer.
-            normed_matmuls(x, norm_weight, n, {{&gate, y, BC_STORE_OVERWRITE}, {&up, y, BC_STORE_SWIGLU}});
-            return;
-        }
-        const uint32_t cols = hp.n_embd;
-        void* scratch = nullptr;
-        if (status == BC_OK) status = s.backend->pack_scratch(k::matmul_pack_bytes(n, cols), &scratch);
-        run("pack_norm", n, cols, 0, 1, [&] { return k::matmul_pack_norm(stream, x, norm(norm_weight), n, cols, scratch); });
-        run("matmul_swiglu", gate.n_rows, gate.n_cols, 2 * gate.bytes(), 1,
-            [&] { return k::matmul_umma_swiglu(stream, gate, up, scratch, y, n, gate.n_rows); });
-    }
-
-    void normed_matmuls(const float* x, const float* norm_weight, uint32_t n, std::initializer_list<Product> products) {
-        const uint32_t cols = hp.n_embd;
-        bool fused = true;
-        size_t bytes = 0;
-        for (const Product& q : products) {
-            fused = fused && k::matmul_umma_supported(*q.w, n);
-            bytes = std::max(bytes, (size_t)k::matmul_scratch_bytes(*q.w, n));
-        }
-        if (!fused) {
-            run("rms_norm", n, cols, 0, 1, [&] { return k::rms_norm(stream, x, norm_weight, s.normed, cols, n, hp.norm_eps); });
-            for (const Product& q : products) matmul(*q.w, s.normed, q.y, n, q.store);
-            return;
-        }
-        void* scratch = nullptr;
-        if (status == BC_OK) status = s.backend->pack_scratch(bytes, &scratch);
-        run("pack_norm", n, cols, 0, 1, [&] { return k::matmul_pack_norm(stream, x, norm(norm_weight), n, cols, scratch); });
-        for (const Product& q : products) {
-            const k::Mat& w = *q.w;
-            run("matmul", w.n_rows, w.n_cols, w.bytes(), k::matmul_umma_launches(w, n) - 1,
-                [&] { return k::matmul_umma(stream, w, scratch, q.y, n, w.n_rows, q.store); });
-        }
-    }
-
-    size_t kv_element_bytes() const { return s.kv_half ? 2 : 4; }
-    size_t kv_dim() const { return (size_t)hp.n_kv_heads * hp.head_dim; }
-    // lfm2_metal.rs:1064-1067: layer-major, then position, then KV head, then element.
-    size_t layer_base(uint32_t cache_index) const { return (size_t)cache_index * s.n_ctx * kv_dim(); }
-    void* cache_at(void* cache, size_t element) const { return static_cast<char*>(cache) + element * kv_element_bytes(); }
-
-    // ---- LFM2 (lfm2_metal.rs:993-1156)
-
-    void lfm2_conv(const DeviceLayer& D, uint32_t cache_index) {
-        float* history = s.conv_state + (size_t)cache_index * (hp.conv_kernel - 1) * hp.n_embd;
-        run("matvec_conv", 3 * hp.n_embd, D.in_proj.n_cols, D.in_proj.bytes(), 1, [&] {
-            return k::matvec_conv(stream, D.in_proj, s.hidden, norm(D.attn_norm), D.taps, history, s.conv_out, hp.n_embd, hp.conv_kernel);
-        });
-        matvec(D.out_proj, s.conv_out, s.hidden, k::Norm{}, true);
-    }
-
-    // Norm and rotation of q and k, cache stores, attention over positions [0, pos + n).
-    void rotate_and_attend(const DeviceLayer& D, uint32_t cache_index, uint32_t pos, uint32_t n, uint32_t q_stride, uint32_t q_head_stride) {
-        size_t slot = layer_base(cache_index) + (size_t)pos * kv_dim();
-        run("norm_rope", hp.n_heads * n, hp.head_dim, 0, 1, [&] {
-            return k::norm_rope(stream, s.q, s.q, false, D.q_norm, hp.n_heads, hp.head_dim, q_head_stride, hp.n_rot, pos, n, q_stride, q_stride,
-                                hp.rope_theta, hp.norm_eps);
-        });
-        run("norm_rope", hp.n_kv_heads * n, hp.head_dim, 0, 1, [&] {
-            return k::norm_rope(stream, s.k, cache_at(s.k_cache, slot), s.kv_half, D.k_norm, hp.n_kv_heads, hp.head_dim, hp.head_dim, hp.n_rot,
-                                pos, n, (uint32_t)kv_dim(), (uint32_t)kv_dim(), hp.rope_theta, hp.norm_eps);
-        });
-        if (s.kv_half)
-            run("convert_half", 1, n * (uint32_t)kv_dim(), 0, 1,
-                [&] { return k::convert_half(stream, s.v, static_cast<__half*>(cache_at(s.v_cache, slot)), (uint64_t)n * kv_dim()); });
-        k::AttentionShape shape{hp.n_heads, hp.n_kv_heads, hp.head_dim, pos, n, s.n_ctx, q_stride, q_head_stride};
-        int kernels = k::attention_launches(s.kv_half, shape);
-        uint64_t kv_bytes = (uint64_t)(pos + n) * kv_dim() * kv_element_bytes() * 2;
-        run("attention", n, pos + n, kv_bytes, kernels, [&] {
-            return k::attention(stream, s.q, cache_at(s.k_cache, layer_base(cache_index)), cache_at(s.v_cache, layer_base(cache_index)), s.kv_half,
-                                s.scores, s.attn, shape);
-        });
-    }
-
-    float* value_target(uint32_t cache_index, uint32_t pos) {
-        if (s.kv_half) return s.v;
-        return static_cast<float*>(cache_at(s.v_cache, layer_base(cache_index) + (size_t)pos * kv_dim()));
-    }
-
-    // One token: norm and rotation of q and k, the K and V rows of position `pos` into the caches
-    // (one launch), then attention over positions [0, pos].
-    void decode_attend(const DeviceLayer& D, uint32_t cache_index, uint32_t pos, uint32_t q_stride, uint32_t q_head_stride) {
-        k::RopeStore rs{s.q, s.k, s.v, cache_at(s.k_cache, layer_base(cache_index)), cache_at(s.v_cache, layer_base(cache_index)),
-                        D.q_norm, D.k_norm, hp.n_heads, hp.n_kv_heads, hp.head_dim, q_head_stride, hp.n_rot, hp.rope_theta, hp.norm_eps, s.kv_half, s.rope_table};
-        k::Pos p = at(pos);
-        k::AttentionShape shape{hp.n_heads, hp.n_kv_heads, hp.head_dim, p.value, 1, s.n_ctx, q_stride, q_head_stride, p.ptr};
-        uint64_t kv_bytes = (uint64_t)(pos + 1) * kv_dim() * kv_element_bytes() * 2;
-        if (k::attention_step_supported(rs, shape)) {
-            run("attention_step", 1, pos + 1, kv_bytes, 2, [&] { return k::attention_step(stream, rs, s.scores, s.attn, shape); });
-            return;
-        }
-        run("rope_store", hp.n_heads + 2 * hp.n_kv_heads, hp.head_dim, 0, 1, [&] { return k::rope_store(stream, rs, p); });
-        run("attention", 1, pos + 1, kv_bytes, k::attention_launches(s.kv_half, shape), [&] {
-            return k::attention(stream, s.q, cache_at(s.k_cache, layer_base(cache_index)), cache_at(s.v_cache, layer_base(cache_index)), s.kv_half,
-                                s.scores, s.attn, shape);
-        });
-    }
-
-    void lfm2_attention(const DeviceLayer& D, uint32_t cache_index, uint32_t pos) {
-        // The three projections share the normalised input, so one launch computes them.
-        k::MatvecSegment segs[3] = {{D.q, s.q}, {D.k, s.k}, {D.v, s.v}};
-        uint64_t bytes = D.q.bytes() + D.k.bytes() + D.v.bytes();
-        run("matvec_qkv", D.q.n_rows + D.k.n_rows + D.v.n_rows, D.q.n_cols, bytes, 1,
-            [&] { return k::matvec(stream, segs, 3, s.hidden, norm(D.attn_norm), false); });
-        uint32_t q_dim = hp.n_heads * hp.head_dim;
-        decode_attend(D, cache_index, pos, q_dim, hp.head_dim);
-        matvec(D.output, s.attn, s.hidden, k::Norm{}, true);
-    }
-
-    void lfm2_dense_ffn(const DeviceLayer& D) {
-        run("matvec_swiglu", D.gate.n_rows, D.gate.n_cols, D.gate.bytes() * 2, 1,
-            [&] { return k::matvec_swiglu(stream, D.gate, D.up, s.hidden, norm(D.ffn_norm), s.ffn); });
-        matvec(D.down, s.ffn, s.hidden, k::Norm{}, true);
-    }
-
-    // The mixture of experts on the n tokens of the batch, added to the residual stream
-    // (lfm2_metal.rs:1251-1370). With `fused_norm` the router launch normalises the residual stream
-    // into the normed buffer first; otherwise the normed buffer already holds the tokens. One token
-    // runs matrix-vector products on its experts; a batch groups its tokens by expert so each
-    // expert's weights stream once.
-    void lfm2_moe(const DeviceLayer& D, uint32_t n, bool fused_norm) {
-        const uint32_t n_used = hp.n_experts_used, n_ff = hp.n_ff_expert, n_embd = hp.n_embd;
-        const float* input = fused_norm ? s.hidden : s.normed;
-        k::Norm nm = fused_norm ? norm(D.ffn_norm) : k::Norm{};
-        run("moe_route", hp.n_experts, n_embd, D.router.bytes(), 1, [&] {
-            return k::moe_route(stream, input, nm, s.normed, static_cast<const float*>(D.router.data), D.expert_bias, s.route, n_embd, hp.n_experts,
-                                n_used, n);
-        });
-        if (route_trace) run("copy", 1, n * 2 * n_used, 0, 0, [&] {
-            return k::copy_floats(stream, reinterpret_cast<const float*>(s.route), reinterpret_cast<float*>(route_trace), (uint64_t)n * 2 * n_used);
-        });
-        // Bytes the experts stream: the picked experts of each token (decode) or every expert once (batch).
-        uint64_t expert_bytes = D.gate.bytes() / hp.n_experts;
-        if (n == 1) {
-            run("matvec_experts_swiglu", n_ff, n_embd, 2 * expert_bytes * n_used, 1,
-                [&] { return k::matvec_experts_swiglu(stream, D.gate, D.up, n_ff, s.normed, s.route, n_used, s.ffn, n); });
-            run("matvec_experts_down", n_embd, n_ff, expert_bytes * n_used, k::matvec_experts_down_launches(D.down, n_embd, n_used, n, true),
-                [&] { return k::matvec_experts_down(stream, D.down, n_embd, s.ffn, s.route, n_used, s.hidden, n, s.expert_out); });
-            return;
-        }
-        run("moe_group", n, hp.n_experts, 0, 1, [&] { return k::moe_group(stream, s.route, s.expert_offsets, s.expert_entries, hp.n_experts, n_used, n); });
-        // Q4_0 experts run on the tensor-core kernel in its grouped mode, from a gathered fp16 packing.
-        void* up_scratch = nullptr;
-        void* down_scratch = nullptr;
-        const bool tensor_up = k::matmul_experts_umma_supported(D.gate, &D.up, n), tensor_down = k::matmul_experts_umma_supported(D.down, nullptr, n);
-        if (status == BC_OK && (tensor_up || tensor_down)) {
-            size_t bytes = (size_t)std::max(tensor_up ? k::matmul_experts_scratch_bytes(hp.n_experts, n, n_embd) : 0,
-                                            tensor_down ? k::matmul_experts_scratch_bytes(hp.n_experts, n, n_ff) : 0);
-            void* scratch = nullptr;
-            status = s.backend->pack_scratch(bytes, &scratch);
-            if (tensor_up) up_scratch = scratch;
-            if (tensor_down) down_scratch = scratch;
-        }
-        run("matmul_experts", n_ff, n_embd, 2 * D.gate.bytes(), up_scratch ? 2 : 1, [&] {
-            return k::matmul_experts(stream, D.gate, &D.up, n_ff, hp.n_experts, s.normed, true, s.expert_offsets, s.expert_entries, n_used, s.ffn, n,
-                                     up_scratch);
-        });
-        run("matmul_experts", n_embd, n_ff, D.down.bytes(), down_scratch ? 2 : 1, [&] {
-            return k::matmul_experts(stream, D.down, nullptr, n_embd, hp.n_experts, s.ffn, false, s.expert_offsets, s.expert_entries, n_used,
-                                     s.expert_out, n, down_scratch);
-        });
-        run("moe_combine", n, n_embd, 0, 1, [&] { return k::moe_combine(stream, s.expert_out, s.route, s.hidden, n_embd, n_used, n); });
-    }
-
-    void copy(const float* src, float* dst, uint64_t n) {
-        run("copy", 1, (uint32_t)n, 0, 0, [&] { return k::copy_floats(stream, src, dst, n); });
-    }
-
-    // lfm2_metal.rs:1162-1242
-    void lfm2_step(uint32_t pos, bool want_logits, bool traced) {
-        const DeviceModel& W = *s.weights;
-        run("embed", 1, hp.n_embd, 0, 1, [&] { return k::embed(stream, W.token_embd, s.tokens, at(pos), s.hidden, 1); });
-        if (traced) copy(s.hidden, s.trace_embedding, hp.n_embd);
-        for (size_t il = 0; il < W.layers.size(); ++il) {
-            const LayerSpec& S = s.model->layers[il];
-            const DeviceLayer& D = W.layers[il];
-            if (S.mixer == Mixer::Attention) lfm2_attention(D, S.cache_index, pos);
-            else lfm2_conv(D, S.cache_index);
-            if (S.moe) {
-                route_trace = traced ? s.trace_routes + il * (size_t)s.trace_rows * 2 * hp.n_experts_used : nullptr;
-                lfm2_moe(D, 1, true);
-            } else lfm2_dense_ffn(D);
-            if (traced) copy(s.hidden, s.trace_layers + il * hp.n_embd, hp.n_embd);
-        }
-        if (traced)
-            run("rms_norm", 1, hp.n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, W.output_norm, s.trace_final, hp.n_embd, 1, hp.norm_eps); });
-        if (want_logits) matvec(W.output, s.hidden, s.logits, norm(W.output_norm), false);
-    }
-
-    // lfm2_metal.rs:1455-1548
-    void lfm2_batch(uint32_t pos, uint32_t n, bool want_logits, bool traced, size_t trace_stride) {
-        const DeviceModel& W = *s.weights;
-        const uint32_t n_embd = hp.n_embd;
-        run("embed", n, n_embd, 0, 1, [&] { return k::embed(stream, W.token_embd, s.tokens, k::Pos{nullptr, pos}, s.hidden, n); });
-        if (traced) copy(s.hidden, s.trace_embedding, (uint64_t)n * n_embd);
-        for (size_t il = 0; il < W.layers.size(); ++il) {
-            const LayerSpec& S = s.model->layers[il];
-            const DeviceLayer& D = W.layers[il];
-            if (S.mixer == Mixer::Attention) {
-                normed_matmuls(s.hidden, D.attn_norm, n,
-                               {{&D.q, s.q, BC_STORE_OVERWRITE}, {&D.k, s.k, BC_STORE_OVERWRITE}, {&D.v, value_target(S.cache_index, pos), BC_STORE_OVERWRITE}});
-                uint32_t q_dim = hp.n_heads * hp.head_dim;
-                rotate_and_attend(D, S.cache_index, pos, n, q_dim, hp.head_dim);
-                matmul(D.output, s.attn, s.hidden, n, BC_STORE_ACCUMULATE);
-            } else {
-                float* history = s.conv_state + (size_t)S.cache_index * (hp.conv_kernel - 1) * n_embd;
-                normed_matmuls(s.hidden, D.attn_norm, n, {{&D.in_proj, s.bcx, BC_STORE_OVERWRITE}});
-                run("short_conv", n, n_embd, 0, 2,
-                    [&] { return k::short_conv(stream, s.bcx, D.taps, history, s.conv_out, n_embd, hp.conv_kernel, n); });
-                matmul(D.out_proj, s.conv_out, s.hidden, n, BC_STORE_ACCUMULATE);
-            }
-            if (S.moe) {
-                run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.ffn_norm, s.normed, n_embd, n, hp.norm_eps); });
-                route_trace = traced ? s.trace_routes + il * (size_t)s.trace_rows * 2 * hp.n_experts_used : nullptr;
-                lfm2_moe(D, n, false);
-            } else {
-                normed_swiglu(s.hidden, D.ffn_norm, n, D.gate, D.up, s.ffn);
-                matmul(D.down, s.ffn, s.hidden, n, BC_STORE_ACCUMULATE);
-            }
-            if (traced) copy(s.hidden, s.trace_layers + il * trace_stride, (uint64_t)n * n_embd);
-        }
-        if (traced)
-            run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, W.output_norm, s.trace_final, n_embd, n, hp.norm_eps); });
-        if (want_logits) matvec(W.output, s.hidden + (size_t)(n - 1) * n_embd, s.logits, norm(W.output_norm), false);
-    }
-
-    // ---- Qwen3.5 (qwen35_metal.rs:867-1134)
-
-    uint32_t conv_dim() const { return 2 * hp.n_k_heads * hp.k_head_dim + hp.n_v_heads * hp.v_head_dim; }
-    uint32_t value_dim() const { return hp.n_v_heads * hp.v_head_dim; }
-
-    // The DeltaNet mixer from the conv onward, over n tokens whose projections sit in gdn_qkv,
-    // gdn_z, gdn_beta and gdn_alpha (qwen35_metal.rs:965-1033). The recurrence normalises q and k itself.
-    void qwen_delta_tail(const DeviceLayer& D, uint32_t cache_index, uint32_t n) {
-        const uint32_t K = hp.conv_kernel;
-        float* history = s.conv_state + (size_t)cache_index * conv_dim() * (K - 1);
-        float* state = s.delta_state + (size_t)cache_index * hp.n_v_heads * hp.k_head_dim * hp.v_head_dim;
-        if (n == 1 && k::gdn_step_supported(hp.n_k_heads, hp.n_v_heads, hp.k_head_dim, hp.v_head_dim, K)) {
-            // A decode step: the whole tail in one launch.
-            uint64_t step_bytes = (uint64_t)hp.n_v_heads * hp.k_head_dim * hp.v_head_dim * 4 * 2;
-            run("gdn_step", 1, value_dim(), step_bytes, 1, [&] {
-                return k::gdn_step(stream, s.gdn_qkv, D.conv1d, history, s.gdn_beta, s.gdn_alpha, D.a, D.dt_bias, state, s.gdn_z, D.ssm_norm, s.gdn_out,
-                                   hp.n_k_heads, hp.n_v_heads, hp.k_head_dim, hp.v_head_dim, K, hp.norm_eps);
-            });
-            return;
-        }
-        run("gdn_conv", n, conv_dim(), 0, k::gdn_conv_launches(n), [&] { return k::gdn_conv(stream, s.gdn_qkv, D.conv1d, history, s.gdn_conv_out, conv_dim(), K, n); });
-        run("gdn_gates", n, hp.n_v_heads, 0, 1, [&] { return k::gdn_gates(stream, s.gdn_beta, s.gdn_alpha, D.a, D.dt_bias, hp.n_v_heads, n); });
-        uint64_t state_bytes = (uint64_t)hp.n_v_heads * hp.k_head_dim * hp.v_head_dim * 4 * 2;
-        run("gdn_recurrence", n, value_dim(), state_bytes, 1, [&] {
-            return k::gdn_recurrence(stream, s.gdn_conv_out, s.gdn_beta, s.gdn_alpha, state, s.gdn_out, hp.n_k_heads, hp.n_v_heads, hp.k_head_dim,
-                                     hp.v_head_dim, n, true);
-        });
-        run("gdn_gated_norm", n * hp.n_v_heads, hp.v_head_dim, 0, 1,
-            [&] { return k::gdn_gated_norm(stream, s.gdn_out, s.gdn_z, D.ssm_norm, hp.v_head_dim, n * hp.n_v_heads, hp.norm_eps); });
-    }
-
-    // qwen35_metal.rs:1038-1134
-    void qwen_step(uint32_t pos, bool want_logits, bool traced) {
-        const DeviceModel& W = *s.weights;
-        const uint32_t q_dim = hp.n_heads * hp.head_dim;
-        run("embed", 1, hp.n_embd, 0, 1, [&] { return k::embed(stream, W.token_embd, s.tokens, at(pos), s.hidden, 1); });
-        if (traced) copy(s.hidden, s.trace_embedding, hp.n_embd);
-        for (size_t il = 0; il < W.layers.size(); ++il) {
-            const LayerSpec& S = s.model->layers[il];
-            const DeviceLayer& D = W.layers[il];
-            if (S.mixer == Mixer::Attention) {
-                // Each query head's rows hold its queries, then the gate of its output.
-                k::MatvecSegment segs[3] = {{D.q, s.q}, {D.k, s.k}, {D.v, s.v}};
-                run("matvec_qkv", D.q.n_rows + D.k.n_rows + D.v.n_rows, D.q.n_cols, D.q.bytes() + D.k.bytes() + D.v.bytes(), 1,
-                    [&] { return k::matvec(stream, segs, 3, s.hidden, norm(D.attn_norm), false); });
-                decode_attend(D, S.cache_index, pos, 2 * q_dim, 2 * hp.head_dim);
-                run("attention_gate", 1, q_dim, 0, 1, [&] { return k::attention_gate(stream, s.attn, s.q, hp.n_heads, hp.head_dim, 1); });
-                matvec(D.output, s.attn, s.hidden, k::Norm{}, true);
-            } else {
-                k::MatvecSegment segs[4] = {{D.qkv, s.gdn_qkv}, {D.z, s.gdn_z}, {D.beta, s.gdn_beta}, {D.alpha, s.gdn_alpha}};
-                uint64_t bytes = D.qkv.bytes() + D.z.bytes() + D.beta.bytes() + D.alpha.bytes();
-                run("matvec_delta", D.qkv.n_rows + D.z.n_rows + 2 * D.beta.n_rows, D.qkv.n_cols, bytes, 1,
-                    [&] { return k::matvec(stream, segs, 4, s.hidden, norm(D.attn_norm), false); });
-                qwen_delta_tail(D, S.cache_index, 1);
-                matvec(D.ssm_out, s.gdn_out, s.hidden, k::Norm{}, true);
-            }
-            lfm2_dense_ffn(D);
-            if (traced) copy(s.hidden, s.trace_layers + il * hp.n_embd, hp.n_embd);
-        }
-        if (traced)
-            run("rms_norm", 1, hp.n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, W.output_norm, s.trace_final, hp.n_embd, 1, hp.norm_eps); });
-        if (want_logits) matvec(W.output, s.hidden, s.logits, norm(W.output_norm), false);
-    }
-
-    // qwen35_metal.rs:1142-1240
-    void qwen_batch(uint32_t pos, uint32_t n, bool want_logits, bool traced, size_t trace_stride) {
-        const DeviceModel& W = *s.weights;
-        const uint32_t n_embd = hp.n_embd, q_dim = hp.n_heads * hp.head_dim;
-        run("embed", n, n_embd, 0, 1, [&] { return k::embed(stream, W.token_embd, s.tokens, k::Pos{nullptr, pos}, s.hidden, n); });
-        if (traced) copy(s.hidden, s.trace_embedding, (uint64_t)n * n_embd);
-        for (size_t il = 0; il < W.layers.size(); ++il) {
-            const LayerSpec& S = s.model->layers[il];
-            const DeviceLayer& D = W.layers[il];
-            if (S.mixer == Mixer::Attention) {
-                normed_matmuls(s.hidden, D.attn_norm, n,
-                               {{&D.q, s.q, BC_STORE_OVERWRITE}, {&D.k, s.k, BC_STORE_OVERWRITE}, {&D.v, value_target(S.cache_index, pos), BC_STORE_OVERWRITE}});
-                size_t slot = layer_base(S.cache_index) + (size_t)pos * kv_dim();
-                // The rotated queries go to their own compact rows; the gates stay in the projection.
-                run("norm_rope", hp.n_heads * n, hp.head_dim, 0, 1, [&] {
-                    return k::norm_rope(stream, s.q, s.q_rot, false, D.q_norm, hp.n_heads, hp.head_dim, 2 * hp.head_dim, hp.n_rot, pos, n, 2 * q_dim,
-                                        q_dim, hp.rope_theta, hp.norm_eps);
-                });
-                run("norm_rope", hp.n_kv_heads * n, hp.head_dim, 0, 1, [&] {
-                    return k::norm_rope(stream, s.k, cache_at(s.k_cache, slot), s.kv_half, D.k_norm, hp.n_kv_heads, hp.head_dim, hp.head_dim,
-                                        hp.n_rot, pos, n, (uint32_t)kv_dim(), (uint32_t)kv_dim(), hp.rope_theta, hp.norm_eps);
-                });
-                if (s.kv_half)
-                    run("convert_half", 1, n * (uint32_t)kv_dim(), 0, 1,
-                        [&] { return k::convert_half(stream, s.v, static_cast<__half*>(cache_at(s.v_cache, slot)), (uint64_t)n * kv_dim()); });
-                k::AttentionShape shape{hp.n_heads, hp.n_kv_heads, hp.head_dim, pos, n, s.n_ctx, q_dim, hp.head_dim};
-                run("attention", n, pos + n, (uint64_t)(pos + n) * kv_dim() * kv_element_bytes() * 2, k::attention_launches(s.kv_half, shape), [&] {
-                    return k::attention(stream, s.q_rot, cache_at(s.k_cache, layer_base(S.cache_index)), cache_at(s.v_cache, layer_base(S.cache_index)),
-                                        s.kv_half, s.scores, s.attn, shape);
-                });
-                run("attention_gate", n, q_dim, 0, 1, [&] { return k::attention_gate(stream, s.attn, s.q, hp.n_heads, hp.head_dim, n); });
-                matmul(D.output, s.attn, s.hidden, n, BC_STORE_ACCUMULATE);
-            } else {
-                normed_matmuls(s.hidden, D.attn_norm, n,
-                               {{&D.qkv, s.gdn_qkv, BC_STORE_OVERWRITE}, {&D.z, s.gdn_z, BC_STORE_OVERWRITE}, {&D.beta, s.gdn_beta, BC_STORE_OVERWRITE},
-                                {&D.alpha, s.gdn_alpha, BC_STORE_OVERWRITE}});
-                qwen_delta_tail(D, S.cache_index, n);
-                matmul(D.ssm_out, s.gdn_out, s.hidden, n, BC_STORE_ACCUMULATE);
-            }
-            normed_swiglu(s.hidden, D.ffn_norm, n, D.gate, D.up, s.ffn);
-            matmul(D.down, s.ffn, s.hidden, n, BC_STORE_ACCUMULATE);
-            if (traced) copy(s.hidden, s.trace_layers + il * trace_stride, (uint64_t)n * n_embd);
-        }
-        if (traced)
-            run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, W.output_norm, s.trace_final, n_embd, n, hp.norm_eps); });
-        if (want_logits) matvec(W.output, s.hidden + (size_t)(n - 1) * n_embd, s.logits, norm(W.output_norm), false);
-    }
-
-    void step(uint32_t pos, bool want_logits, bool traced) {
-        if (hp.architecture == BC_ARCH_QWEN35) qwen_step(pos, want_logits, traced);
-        else lfm2_step(pos, want_logits, traced);
-    }
-
-    void batch(uint32_t pos, uint32_t n, bool want_logits, bool traced, size_t trace_stride) {
-        if (hp.architecture == BC_ARCH_QWEN35) qwen_batch(pos, n, want_logits, traced, trace_stride);
-        else lfm2_batch(pos, n, want_logits, traced, trace_stride);
-    }
-
-    void argmax(const float* x, uint32_t* out, uint32_t* readback) {
-        run("argmax", 1, hp.n_vocab, 0, 1, [&] { return k::argmax(stream, x, hp.n_vocab, out, readback); });
-    }
-};
 
 bc_status ensure_trace_rows(bc_seq* s, uint32_t rows) {
     if (rows <= s->trace_rows) return BC_OK;
@@ -526,7 +124,7 @@ bc_status prepare_replay(bc_seq* s, bool stream_variant, uint32_t first) {
 }
 
 bc_status generate_inner(bc_seq* s, uint32_t* out, size_t count, bool select_next) {
-    if (!s || (!out && count)) return fail(BC_ERR_ARGUMENT, "seq and out must be non-null");
+    if (!s || !s->backend || (!out && count)) return fail(BC_ERR_ARGUMENT, "seq and out must be non-null and the backend open");
     if (count > UINT32_MAX) return fail(BC_ERR_ARGUMENT, "too many tokens");
     uint32_t n = (uint32_t)count;
     uint32_t remaining = s->n_ctx - s->n_past;
@@ -580,24 +178,40 @@ bc_status generate_inner(bc_seq* s, uint32_t* out, size_t count, bool select_nex
 
 }  // namespace
 
-bc_seq::~bc_seq() {
+// Free everything the sequence holds on the device. Also called by bc_backend_close for sequences
+// that outlive their backend, which are left as empty shells for bc_seq_free.
+void bc_seq::release() {
     if (backend) {
         cudaSetDevice(backend->device);
         cudaStreamSynchronize(backend->stream);
+        backend->seqs.erase(this);
     }
     cudaFree(arena);
     cudaFree(trace_embedding);
     cudaFree(trace_layers);
     cudaFree(trace_final);
     cudaFree(trace_routes);
+    arena = nullptr;
+    trace_embedding = trace_layers = trace_final = nullptr;
+    trace_routes = nullptr;
     if (readback) cudaFreeHost(readback);
+    readback = nullptr;
     if (generate_graph) cudaGraphExecDestroy(generate_graph);
     if (stream_graph) cudaGraphExecDestroy(stream_graph);
-    for (cudaEvent_t e : slot_done)
+    generate_graph = stream_graph = nullptr;
+    for (cudaEvent_t& e : slot_done) {
         if (e) cudaEventDestroy(e);
+        e = nullptr;
+    }
     if (timing_start) cudaEventDestroy(timing_start);
     if (timing_end) cudaEventDestroy(timing_end);
+    timing_start = timing_end = nullptr;
+    backend = nullptr;
 }
+
+bc_seq::~bc_seq() { release(); }
+
+void release_seq(bc_seq* seq) { seq->release(); }
 
 extern "C" {
 
@@ -687,6 +301,7 @@ bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32
     BC_CUDA(cudaEventCreate(&s->timing_start));
     BC_CUDA(cudaEventCreate(&s->timing_end));
     BC_CUDA(cudaStreamSynchronize(backend->stream));
+    backend->seqs.insert(s.get());
     *out = s.release();
     return BC_OK;
 }
@@ -696,7 +311,7 @@ uint32_t bc_seq_n_past(const bc_seq* seq) { return seq ? seq->n_past : 0; }
 uint64_t bc_seq_launches(const bc_seq* seq) { return seq ? seq->launches : 0; }
 
 bc_status bc_seq_step(bc_seq* s, uint32_t token, float* logits, size_t logits_len, bc_trace* trace) {
-    if (!s) return fail(BC_ERR_ARGUMENT, "seq must be non-null");
+    if (!s || !s->backend) return fail(BC_ERR_ARGUMENT, "seq must be non-null and its backend open");
     const bc_hparams& hp = s->model->hp;
     uint32_t pos = s->n_past;
     if (pos >= s->n_ctx) return fail(BC_ERR_CONTEXT_FULL, "context full: 1 token requested, 0 remaining");
@@ -732,7 +347,7 @@ bc_status bc_seq_step(bc_seq* s, uint32_t token, float* logits, size_t logits_le
 
 bc_status bc_seq_prefill(bc_seq* s, const uint32_t* tokens, size_t n_tokens, float* logits, size_t logits_len, float* final_norm,
                          size_t final_norm_len, bc_trace* trace) {
-    if (!s || (!tokens && n_tokens)) return fail(BC_ERR_ARGUMENT, "seq and tokens must be non-null");
+    if (!s || !s->backend || (!tokens && n_tokens)) return fail(BC_ERR_ARGUMENT, "seq and tokens must be non-null and the backend open");
     const bc_hparams& hp = s->model->hp;
     if (n_tokens > UINT32_MAX) return fail(BC_ERR_ARGUMENT, "too many tokens");
     uint32_t n = (uint32_t)n_tokens, remaining = s->n_ctx - s->n_past;
@@ -791,7 +406,7 @@ bc_status bc_seq_prefill(bc_seq* s, const uint32_t* tokens, size_t n_tokens, flo
 }
 
 bc_status bc_seq_greedy_token(bc_seq* s, uint32_t* token) {
-    if (!s || !token) return fail(BC_ERR_ARGUMENT, "seq and token must be non-null");
+    if (!s || !s->backend || !token) return fail(BC_ERR_ARGUMENT, "seq and token must be non-null and the backend open");
     if (s->n_past == 0) return fail(BC_ERR_ARGUMENT, "generation needs a prompt first");
     if (s->backend->recording) return fail(BC_ERR_ALREADY_RECORDING, "a recording is already open");
     BC_TRY(s->backend->activate());
@@ -815,7 +430,7 @@ bc_status bc_seq_generate_next(bc_seq* s, uint32_t* out, size_t n) { return gene
 
 bc_status bc_seq_generate_stream(bc_seq* s, uint32_t max_tokens, bc_emit_fn emit, void* user, uint32_t* gained, size_t gained_cap,
                                  size_t* n_gained) {
-    if (!s || !emit || !n_gained) return fail(BC_ERR_ARGUMENT, "seq, emit and n_gained must be non-null");
+    if (!s || !s->backend || !emit || !n_gained) return fail(BC_ERR_ARGUMENT, "seq, emit and n_gained must be non-null and the backend open");
     *n_gained = 0;
     if (max_tokens == 0) return BC_OK;
     uint32_t first = 0;
@@ -904,7 +519,7 @@ bc_status bc_seq_generate_stream(bc_seq* s, uint32_t max_tokens, bc_emit_fn emit
 }
 
 bc_status bc_seq_reset(bc_seq* s) {
-    if (!s) return fail(BC_ERR_ARGUMENT, "seq must be non-null");
+    if (!s || !s->backend) return fail(BC_ERR_ARGUMENT, "seq must be non-null and its backend open");
     BC_TRY(s->backend->activate());
     // A new sequence starts from zero convolution history (and zero DeltaNet state). The KV cache
     // needs no clearing, because attention reads only the positions a sequence has written.
@@ -917,7 +532,7 @@ bc_status bc_seq_reset(bc_seq* s) {
 }
 
 bc_status bc_seq_checkpoint(bc_seq* s, bc_checkpoint** out) {
-    if (!s || !out) return fail(BC_ERR_ARGUMENT, "seq and out must be non-null");
+    if (!s || !s->backend || !out) return fail(BC_ERR_ARGUMENT, "seq and out must be non-null and the backend open");
     BC_TRY(s->backend->activate());
     std::unique_ptr<bc_checkpoint> c(new bc_checkpoint());
     c->owner = s;
@@ -936,7 +551,7 @@ bc_status bc_seq_checkpoint(bc_seq* s, bc_checkpoint** out) {
 }
 
 bc_status bc_seq_restore(bc_seq* s, const bc_checkpoint* c) {
-    if (!s || !c) return fail(BC_ERR_ARGUMENT, "seq and checkpoint must be non-null");
+    if (!s || !s->backend || !c) return fail(BC_ERR_ARGUMENT, "seq and checkpoint must be non-null and the backend open");
     // A checkpoint holds the recurrent state only; the KV rows of its prefix live in the cache of
     // the sequence that took it, so no other sequence can continue from it.
     if (c->owner != s) return fail(BC_ERR_ARGUMENT, "the checkpoint belongs to another sequence");
@@ -956,14 +571,14 @@ bc_status bc_seq_restore(bc_seq* s, const bc_checkpoint* c) {
 void bc_checkpoint_free(bc_checkpoint* c) { delete c; }
 
 bc_status bc_seq_timings(const bc_seq* s, double* encode_seconds, double* gpu_seconds) {
-    if (!s) return fail(BC_ERR_ARGUMENT, "seq must be non-null");
+    if (!s || !s->backend) return fail(BC_ERR_ARGUMENT, "seq must be non-null and its backend open");
     if (encode_seconds) *encode_seconds = s->last_encode_seconds;
     if (gpu_seconds) *gpu_seconds = s->last_gpu_seconds;
     return BC_OK;
 }
 
 bc_status bc_seq_set_skip(bc_seq* s, const char* name, uint32_t n_rows, uint32_t n_cols) {
-    if (!s) return fail(BC_ERR_ARGUMENT, "seq must be non-null");
+    if (!s || !s->backend) return fail(BC_ERR_ARGUMENT, "seq must be non-null and its backend open");
     BC_TRY(s->backend->activate());
     BC_CUDA(cudaStreamSynchronize(s->backend->stream));
     s->skip_name = name ? name : "";
@@ -977,7 +592,7 @@ bc_status bc_seq_set_skip(bc_seq* s, const char* name, uint32_t n_rows, uint32_t
 }
 
 bc_status bc_seq_read_state(bc_seq* s, int32_t which, uint32_t layer, float* out, size_t cap, size_t* n) {
-    if (!s || !n) return fail(BC_ERR_ARGUMENT, "seq and n must be non-null");
+    if (!s || !s->backend || !n) return fail(BC_ERR_ARGUMENT, "seq and n must be non-null and the backend open");
     const bc_hparams& hp = s->model->hp;
     BC_TRY(s->backend->activate());
     cudaStream_t stream = s->backend->stream;

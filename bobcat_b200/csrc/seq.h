@@ -75,5 +75,6 @@ struct bc_seq {
     uint32_t skip_rows = 0, skip_cols = 0;
     bool use_graphs = true;                   // BOBCAT_NO_GRAPH=1 turns replay off (launch every kernel eagerly)
 
+    void release();
     ~bc_seq();
 };

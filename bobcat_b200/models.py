@@ -84,11 +84,15 @@ class Checkpoint:
 class SeqCuda:
     """The device state of one decode. ``Lfm2Cuda`` and ``Qwen35Cuda`` are this class."""
 
-    def __init__(self, model: Model, cuda: Cuda, n_ctx: int, kv_half: bool):
+    def __init__(self, model: Model, cuda: Cuda, n_ctx: int, kv_half: bool, _borrowed=None):
         self._L = _lib.load()
         self.model, self.cuda = model, cuda
-        h = C.c_void_p()
-        errors.check(self._L.bc_seq_new(model._h, cuda._h, n_ctx, int(kv_half), C.byref(h)), self._L)
+        self._owned = _borrowed is None
+        if _borrowed is None:
+            h = C.c_void_p()
+            errors.check(self._L.bc_seq_new(model._h, cuda._h, n_ctx, int(kv_half), C.byref(h)), self._L)
+        else:
+            h = _borrowed
         self._h = h
         self.n_ctx = n_ctx
 
@@ -191,7 +195,8 @@ class SeqCuda:
 
     def close(self) -> None:
         if self._h:
-            self._L.bc_seq_free(self._h)
+            if self._owned:
+                self._L.bc_seq_free(self._h)
             self._h = None
 
     def __del__(self):
@@ -203,3 +208,52 @@ class SeqCuda:
 
 Lfm2Cuda = SeqCuda
 Qwen35Cuda = SeqCuda
+
+
+class BatchCuda:
+    """Several sequences of one model that decode together, one token each per pass (the C ABI's
+    ``bc_batch``): ``seq(i)`` is sequence i with the single-sequence methods (prefill, reset, ...),
+    ``generate(n)`` gives every sequence n greedy tokens and returns them as [n_seqs][n]."""
+
+    def __init__(self, model: Model, cuda: Cuda, n_seqs: int, n_ctx: int, kv_half: bool):
+        self._L = _lib.load()
+        self.model, self.cuda, self.n_seqs, self.n_ctx = model, cuda, n_seqs, n_ctx
+        h = C.c_void_p()
+        errors.check(self._L.bc_batch_new(model._h, cuda._h, n_seqs, n_ctx, int(kv_half), C.byref(h)), self._L)
+        self._h = h
+        self._seqs = []
+        for i in range(n_seqs):
+            sh = C.c_void_p()
+            errors.check(self._L.bc_batch_seq(self._h, i, C.byref(sh)), self._L)
+            self._seqs.append(SeqCuda(model, cuda, n_ctx, kv_half, _borrowed=sh))
+
+    def seq(self, index: int) -> SeqCuda:
+        return self._seqs[index]
+
+    def generate(self, n: int) -> np.ndarray:
+        out = np.zeros((self.n_seqs, n), dtype=np.uint32)
+        errors.check(self._L.bc_batch_generate(self._h, out.ctypes.data_as(C.c_void_p), n), self._L)
+        return out
+
+    def last_gpu_seconds(self) -> float:
+        g = C.c_double()
+        errors.check(self._L.bc_batch_timings(self._h, C.byref(g), None), self._L)
+        return float(g.value)
+
+    def launches(self) -> int:
+        n = C.c_uint64()
+        errors.check(self._L.bc_batch_timings(self._h, None, C.byref(n)), self._L)
+        return int(n.value)
+
+    def close(self) -> None:
+        if self._h:
+            for s in self._seqs:
+                s.close()
+            self._L.bc_batch_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

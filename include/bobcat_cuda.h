@@ -369,6 +369,32 @@ void bc_checkpoint_free(bc_checkpoint* checkpoint);
 /* last_encode_seconds / last_gpu_seconds (lfm2_metal.rs:223-230). */
 bc_status bc_seq_timings(const bc_seq* seq, double* encode_seconds, double* gpu_seconds);
 
+/* ============================================================================================
+ * Batch: n_seqs independent sequences of one model decoding together, one token each per pass,
+ * so that a pass reads every weight once for all of them (LFM2 and LFM2-MoE models).
+ * The reference has one sequence per runner and serves one request at a time
+ * (crates/bobcat/src/lfm2_metal.rs:103-105, crates/bobcat-cli/src/serve.rs:4-7); a batch is n_seqs
+ * such runners plus a pass whose row b computes what Lfm2Metal::step (lfm2_metal.rs:308) computes
+ * for sequence b. Each sequence keeps its own KV cache, convolution history, position and logits.
+ * ============================================================================================ */
+typedef struct bc_batch bc_batch;
+
+/* n_seqs sequences of `n_ctx` positions each (Lfm2Metal::new, lfm2_metal.rs:125, n_seqs times).
+ * n_ctx must be at least n_seqs. */
+bc_status bc_batch_new(bc_model* model, bc_backend* backend, uint32_t n_seqs, uint32_t n_ctx, int32_t kv_half, bc_batch** out);
+void bc_batch_free(bc_batch* batch);
+uint32_t bc_batch_n_seqs(const bc_batch* batch);
+/* Sequence `index` of the batch, for the single-sequence calls (bc_seq_prefill to give it its
+ * prompt, bc_seq_reset, bc_seq_n_past, bc_seq_step). The batch owns it: do not free it. */
+bc_status bc_batch_seq(bc_batch* batch, uint32_t index, bc_seq** out);
+/* Lfm2Metal::generate (lfm2_metal.rs:401) for every sequence at once: each sequence, which must
+ * hold a prompt, gains `n` greedy tokens; out[b * n + i] is token i of sequence b. The sequences
+ * may stand at different positions. Tokens equal those of n_seqs separate bc_seq_generate calls up
+ * to the rounding of the batched products (half-precision operands, as in prefill). */
+bc_status bc_batch_generate(bc_batch* batch, uint32_t* out, size_t n);
+/* GPU seconds of the last bc_batch_generate and the kernels the batch has launched in total. */
+bc_status bc_batch_timings(const bc_batch* batch, double* gpu_seconds, uint64_t* launches);
+
 #ifdef __cplusplus
 }
 #endif
