@@ -113,6 +113,13 @@ SIGNATURES = {
     "bc_batch_seq": (i32, [vp, u32, C.POINTER(vp)]),
     "bc_batch_generate": (i32, [vp, vp, sz]),
     "bc_batch_timings": (i32, [vp, C.POINTER(C.c_double), C.POINTER(u64)]),
+    "bc_comm_unique_id": (i32, [vp, sz]),
+    "bc_comm_init": (i32, [vp, vp, sz, i32, i32, C.POINTER(vp)]),
+    "bc_comm_free": (None, [vp]),
+    "bc_comm_rank": (i32, [vp]),
+    "bc_comm_world": (i32, [vp]),
+    "bc_comm_collectives": (u64, [vp]),
+    "bc_batch_new_expert_parallel": (i32, [vp, vp, vp, u32, u32, i32, C.POINTER(vp)]),
     "bc_seq_launches": (u64, [vp]),
     "bc_seq_set_skip": (i32, [vp, C.c_char_p, u32, u32]),
 }

@@ -11,6 +11,8 @@
 #include <memory>
 #include <vector>
 
+#include <algorithm>
+
 #include "recorder.h"
 #include "seq.h"
 
@@ -21,6 +23,7 @@ struct bc_batch {
     bc_backend* backend = nullptr;
     std::vector<bc_seq*> seqs;  // owned; seqs[0]'s activation rows also serve the batched pass
     uint32_t n_ctx = 0;
+    ExpertParallel ep;  // comm is null unless the experts are sharded over ranks
     // One device allocation: positions, picked tokens, per-sequence pointer tables, logits rows,
     // generated tokens of the current call.
     void* arena = nullptr;
@@ -95,6 +98,27 @@ bc_status bc_batch_new(bc_model* model, bc_backend* backend, uint32_t n_seqs, ui
     return BC_OK;
 }
 
+bc_status bc_batch_new_expert_parallel(bc_model* model, bc_backend* backend, bc_comm* comm, uint32_t n_seqs, uint32_t n_ctx, int32_t kv_half,
+                                       bc_batch** out) {
+    if (!model || !comm || !out) return fail(BC_ERR_ARGUMENT, "model, comm and out must be non-null");
+    if (comm->backend != backend) return fail(BC_ERR_FOREIGN_BUFFER, "the communicator belongs to another backend");
+    const bc_hparams& hp = model->hp;
+    const uint32_t world = (uint32_t)comm->world;
+    if (hp.n_experts == 0) return fail(BC_ERR_NO_EXPERTS, "expert parallelism needs a mixture-of-experts model");
+    if (hp.n_experts % world != 0) return fail(BC_ERR_EXPERT_LIMITS, "%u experts do not split over %u ranks", hp.n_experts, world);
+    // The gathered rows of all ranks pass through one sequence's prefill-sized buffers.
+    if ((uint64_t)n_seqs * world > std::min<uint64_t>(n_ctx, kPrefillBatch))
+        return fail(BC_ERR_ARGUMENT, "%u sequences on each of %u ranks need a context of at least %u positions (at most %u rows in all)", n_seqs,
+                    world, n_seqs * world, kPrefillBatch);
+    bc_batch* batch = nullptr;
+    BC_TRY(bc_batch_new(model, backend, n_seqs, n_ctx, kv_half, &batch));
+    batch->ep.comm = comm;
+    batch->ep.n_local_experts = hp.n_experts / world;
+    batch->ep.first_expert = (uint32_t)comm->rank * batch->ep.n_local_experts;
+    *out = batch;
+    return BC_OK;
+}
+
 void bc_batch_free(bc_batch* batch) { delete batch; }
 
 uint32_t bc_batch_n_seqs(const bc_batch* batch) { return batch ? (uint32_t)batch->seqs.size() : 0; }
@@ -154,7 +178,7 @@ bc_status bc_batch_generate(bc_batch* batch, uint32_t* out, size_t n_tokens) {
         // Pick each sequence's token from its logits, run it at the sequence's position, move on.
         r.run("argmax_rows", n_seqs, hp.n_vocab, 0, 1,
               [&] { return k::argmax_rows(stream, batch->logits, hp.n_vocab, n_seqs, batch->picked, batch->generated, n, i); });
-        r.lfm2_seqs_step(batch->picked, n_seqs, table, batch->logits);
+        r.lfm2_seqs_step(batch->picked, n_seqs, table, batch->logits, batch->ep.comm ? &batch->ep : nullptr);
         r.run("advance_seqs", 1, n_seqs, 0, 1, [&] { return k::advance_seqs(stream, batch->pos, n_seqs); });
     }
     batch->launches += rows.launches - before;

