@@ -93,6 +93,7 @@ SIGNATURES = {
     "bc_model_attention_layers": (i32, [vp, vp, sz]),
     "bc_model_decode_bytes": (u64, [vp]),
     "bc_seq_new": (i32, [vp, vp, u32, i32, C.POINTER(vp)]),
+    "bc_seq_new_tensor_parallel": (i32, [vp, vp, vp, u32, i32, C.POINTER(vp)]),
     "bc_seq_free": (None, [vp]),
     "bc_seq_n_past": (u32, [vp]),
     "bc_seq_step": (i32, [vp, u32, vp, sz, C.POINTER(Trace)]),
@@ -112,6 +113,7 @@ SIGNATURES = {
     "bc_batch_n_seqs": (u32, [vp]),
     "bc_batch_seq": (i32, [vp, u32, C.POINTER(vp)]),
     "bc_batch_generate": (i32, [vp, vp, sz]),
+    "bc_batch_set_exact": (i32, [vp, i32]),
     "bc_batch_timings": (i32, [vp, C.POINTER(C.c_double), C.POINTER(u64)]),
     "bc_comm_unique_id": (i32, [vp, sz]),
     "bc_comm_init": (i32, [vp, vp, sz, i32, i32, C.POINTER(vp)]),

@@ -119,6 +119,13 @@ bc_status bc_batch_new_expert_parallel(bc_model* model, bc_backend* backend, bc_
     return BC_OK;
 }
 
+bc_status bc_batch_set_exact(bc_batch* batch, int32_t exact) {
+    if (!batch) return fail(BC_ERR_ARGUMENT, "batch must be non-null");
+    // The batched pass records through sequence 0's buffers.
+    batch->seqs[0]->exact_products = exact != 0;
+    return BC_OK;
+}
+
 void bc_batch_free(bc_batch* batch) { delete batch; }
 
 uint32_t bc_batch_n_seqs(const bc_batch* batch) { return batch ? (uint32_t)batch->seqs.size() : 0; }

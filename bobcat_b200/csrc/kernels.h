@@ -129,6 +129,8 @@ cudaError_t norm_rope(cudaStream_t stream, const float* src, void* dst, bool dst
 cudaError_t convert_half(cudaStream_t stream, const float* src, __half* dst, uint64_t n);
 cudaError_t copy_floats(cudaStream_t stream, const float* src, float* dst, uint64_t n);
 cudaError_t silu_mul(cudaStream_t stream, float* x, const float* gate, uint64_t n);
+// y[i] += x[i]
+cudaError_t add_floats(cudaStream_t stream, float* y, const float* x, uint64_t n);
 
 // Causal grouped-query attention of n_queries tokens at positions first_pos.. over the cache.
 // q and out are [n_queries][n_heads * head_dim]; caches are [n_ctx][n_kv_heads * head_dim].

@@ -390,6 +390,14 @@ __global__ void rope_table_kernel(float2* table, uint32_t n_positions, uint32_t 
     table[i] = make_float2(c, s);
 }
 
+// y[i] += x[i].
+__global__ void add_floats_kernel(float* __restrict__ y, const float* __restrict__ x, uint64_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] += x[i];
+}
+
 __global__ void advance_kernel(uint32_t* counter) {
     pdl_launch_dependents();
     pdl_wait();
@@ -484,6 +492,12 @@ cudaError_t argmax_step(cudaStream_t stream, const float* x, uint32_t n, uint32_
     ArgmaxOut o{nullptr, nullptr, counter, advance ? 1 : 0, tokens, offset, ring, ring_slots ? ring_slots : 1};
     void* args[] = {&x, &n, &o};
     return launch_kernel((const void*)argmax_kernel, dim3(1), dim3(1024), 0, stream, args);
+}
+
+cudaError_t add_floats(cudaStream_t stream, float* y, const float* x, uint64_t n) {
+    if (n == 0) return cudaSuccess;
+    void* args[] = {&y, &x, &n};
+    return launch_kernel((const void*)add_floats_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, args);
 }
 
 cudaError_t advance(cudaStream_t stream, uint32_t* counter) {

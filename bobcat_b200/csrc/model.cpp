@@ -282,10 +282,9 @@ uint64_t device_bytes(const HostMatrix& hm) {
 }  // namespace
 
 bc::DeviceModel::~DeviceModel() {
-    if (arena) {
-        cudaSetDevice(device);
-        cudaFree(arena);
-    }
+    if (arena || !extra.empty()) cudaSetDevice(device);
+    if (arena) cudaFree(arena);
+    for (void* p : extra) cudaFree(p);
 }
 
 bc_status bc_model::device_model(bc_backend* backend, std::shared_ptr<DeviceModel>* out) {

@@ -58,8 +58,16 @@ struct DeviceModel {
     std::vector<DeviceLayer> layers;
     k::Mat token_embd, output;
     const float* output_norm = nullptr;
+    // Tensor-parallel shards are allocated one by one (freed with the model).
+    std::vector<void*> extra;
+    // Tensor parallelism: the rows of the output matrix this rank multiplies (all of them otherwise).
+    uint32_t first_vocab_row = 0, n_vocab_rows = 0;
     ~DeviceModel();
 };
+
+// The head and row counts a tensor-parallel rank works with: the model's hyperparameters with the
+// per-rank share of attention heads, DeltaNet heads and feed-forward rows.
+bc_hparams tensor_parallel_hparams(const bc_hparams& hp, int rank, int world);
 
 }  // namespace bc
 
@@ -73,6 +81,10 @@ struct bc_model {
     std::mutex mutex;
     std::map<int, std::shared_ptr<bc::DeviceModel>> on_device;  // by CUDA device
 
+    std::map<std::pair<int, std::pair<int, int>>, std::shared_ptr<bc::DeviceModel>> on_device_tp;  // by (device, (rank, world))
+
     // Upload the weights to the backend's device on first use; later sequences share them.
     bc_status device_model(bc_backend* backend, std::shared_ptr<bc::DeviceModel>* out);
+    // The shard of rank `rank` of `world` tensor-parallel ranks (Qwen3.5 models).
+    bc_status device_model_tp(bc_backend* backend, int rank, int world, std::shared_ptr<bc::DeviceModel>* out);
 };

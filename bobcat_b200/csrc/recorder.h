@@ -30,7 +30,7 @@ struct Recorder {
     // Traced passes of a mixture-of-experts model: where the next router launch's routes are copied to.
     uint32_t* route_trace = nullptr;
 
-    explicit Recorder(bc_seq& seq) : s(seq), hp(seq.model->hp), stream(seq.backend->stream) {}
+    explicit Recorder(bc_seq& seq) : s(seq), hp(seq.hp), stream(seq.backend->stream) {}
 
     k::Pos at(uint32_t pos) const { return replayed ? k::Pos{s.step_pos, 0} : k::Pos{nullptr, pos}; }
 
@@ -53,14 +53,52 @@ struct Recorder {
 
     k::Norm norm(const float* weight) const { return k::Norm{weight, hp.norm_eps}; }
 
+    // Batched products run on the tensor cores with half-precision operands (as the reference's
+    // Q4_0 prefill does, matmul.metal:519-521) unless the sequence asks for f32 operands, which
+    // the f32 tile kernels provide at a lower rate.
+    bool tensor_products() const { return !s.exact_products; }
+
     void matvec(const k::Mat& w, const float* x, float* y, k::Norm nm, bool accumulate) {
         k::MatvecSegment seg{w, y};
         run("matvec", w.n_rows, w.n_cols, w.bytes(), 1, [&] { return k::matvec(stream, &seg, 1, x, nm, accumulate); });
     }
 
+    // y += W x where, on a tensor-parallel rank, W holds the rank's columns of an output projection
+    // and x the matching slice of its input: the partial products are summed over ranks first
+    // (qwen35.rs:369-516 computes the whole product on one device), then added to y on every rank.
+    void matvec_reduced(const k::Mat& w, const float* x, float* y) {
+        if (!s.tp) {
+            matvec(w, x, y, k::Norm{}, true);
+            return;
+        }
+        matvec(w, x, s.partial, k::Norm{}, false);
+        run_status([&] { return comm_all_reduce_sum(s.tp, s.partial, w.n_rows); });
+        run("add", 1, w.n_rows, 0, 1, [&] { return k::add_floats(stream, y, s.partial, w.n_rows); });
+    }
+    void matmul_reduced(const k::Mat& w, const float* x, float* y, uint32_t n) {
+        if (!s.tp) {
+            matmul(w, x, y, n, BC_STORE_ACCUMULATE);
+            return;
+        }
+        matmul(w, x, s.partial, n, BC_STORE_OVERWRITE);
+        run_status([&] { return comm_all_reduce_sum(s.tp, s.partial, (size_t)n * w.n_rows); });
+        run("add", n, w.n_rows, 0, 1, [&] { return k::add_floats(stream, y, s.partial, (uint64_t)n * w.n_rows); });
+    }
+    // The logits: on a tensor-parallel rank the output matrix holds the rank's vocabulary rows;
+    // every rank ends with all of them.
+    void logits_product(const float* x) {
+        const DeviceModel& W = *s.weights;
+        if (!s.tp) {
+            matvec(W.output, x, s.logits, norm(W.output_norm), false);
+            return;
+        }
+        matvec(W.output, x, s.logits + W.first_vocab_row, norm(W.output_norm), false);
+        run_status([&] { return comm_all_gather(s.tp, s.logits + W.first_vocab_row, s.logits, W.n_vocab_rows); });
+    }
+
     void matmul(const k::Mat& w, const float* x, float* y, uint32_t n, int store) {
         void* pack = nullptr;
-        if (status == BC_OK && k::matmul_umma_supported(w, n)) status = s.backend->pack_scratch(k::matmul_scratch_bytes(w, n), &pack);
+        if (status == BC_OK && tensor_products() && k::matmul_umma_supported(w, n)) status = s.backend->pack_scratch(k::matmul_scratch_bytes(w, n), &pack);
         run("matmul", w.n_rows, w.n_cols, w.bytes(), pack ? k::matmul_umma_launches(w, n) : 1, [&] { return k::matmul(stream, w, x, y, n, w.n_rows, store, pack); });
     }
 
@@ -74,7 +112,7 @@ struct Recorder {
     };
     // ffn = silu(gate x^) * (up x^) over the batch, x^ the normalised rows.
     void normed_swiglu(const float* x, const float* norm_weight, uint32_t n, const k::Mat& gate, const k::Mat& up, float* y) {
-        if (!k::matmul_umma_swiglu_supported(gate, up, n)) {
+        if (!tensor_products() || !k::matmul_umma_swiglu_supported(gate, up, n)) {
             // The up projection's store combines with the gate projection already in the buffer.
             normed_matmuls(x, norm_weight, n, {{&gate, y, BC_STORE_OVERWRITE}, {&up, y, BC_STORE_SWIGLU}});
             return;
@@ -92,7 +130,7 @@ struct Recorder {
         bool fused = true;
         size_t bytes = 0;
         for (const Product& q : products) {
-            fused = fused && k::matmul_umma_supported(*q.w, n);
+            fused = fused && tensor_products() && k::matmul_umma_supported(*q.w, n);
             bytes = std::max(bytes, (size_t)k::matmul_scratch_bytes(*q.w, n));
         }
         if (!fused) {
@@ -184,6 +222,12 @@ struct Recorder {
         matvec(D.output, s.attn, s.hidden, k::Norm{}, true);
     }
 
+    void qwen_dense_ffn(const DeviceLayer& D) {
+        run("matvec_swiglu", D.gate.n_rows, D.gate.n_cols, D.gate.bytes() * 2, 1,
+            [&] { return k::matvec_swiglu(stream, D.gate, D.up, s.hidden, norm(D.ffn_norm), s.ffn); });
+        matvec_reduced(D.down, s.ffn, s.hidden);
+    }
+
     void lfm2_dense_ffn(const DeviceLayer& D) {
         run("matvec_swiglu", D.gate.n_rows, D.gate.n_cols, D.gate.bytes() * 2, 1,
             [&] { return k::matvec_swiglu(stream, D.gate, D.up, s.hidden, norm(D.ffn_norm), s.ffn); });
@@ -219,7 +263,8 @@ struct Recorder {
         // Q4_0 experts run on the tensor-core kernel in its grouped mode, from a gathered fp16 packing.
         void* up_scratch = nullptr;
         void* down_scratch = nullptr;
-        const bool tensor_up = k::matmul_experts_umma_supported(D.gate, &D.up, n), tensor_down = k::matmul_experts_umma_supported(D.down, nullptr, n);
+        const bool tensor_up = tensor_products() && k::matmul_experts_umma_supported(D.gate, &D.up, n);
+        const bool tensor_down = tensor_products() && k::matmul_experts_umma_supported(D.down, nullptr, n);
         if (status == BC_OK && (tensor_up || tensor_down)) {
             size_t bytes = (size_t)std::max(tensor_up ? k::matmul_experts_scratch_bytes(hp.n_experts, n, n_embd) : 0,
                                             tensor_down ? k::matmul_experts_scratch_bytes(hp.n_experts, n, n_ff) : 0);
@@ -267,7 +312,8 @@ struct Recorder {
         const k::Mat down = D.down.rows(ep.first_expert * n_embd, ep.n_local_experts * n_embd);
         void* up_scratch = nullptr;
         void* down_scratch = nullptr;
-        const bool tensor_up = k::matmul_experts_umma_supported(gate, &up, n), tensor_down = k::matmul_experts_umma_supported(down, nullptr, n);
+        const bool tensor_up = tensor_products() && k::matmul_experts_umma_supported(gate, &up, n);
+        const bool tensor_down = tensor_products() && k::matmul_experts_umma_supported(down, nullptr, n);
         if (status == BC_OK && (tensor_up || tensor_down)) {
             size_t bytes = (size_t)std::max(tensor_up ? k::matmul_experts_scratch_bytes(ep.n_local_experts, n, n_embd) : 0,
                                             tensor_down ? k::matmul_experts_scratch_bytes(ep.n_local_experts, n, n_ff) : 0);
@@ -398,21 +444,21 @@ struct Recorder {
                     [&] { return k::matvec(stream, segs, 3, s.hidden, norm(D.attn_norm), false); });
                         decode_attend(D, S.cache_index, pos, 2 * q_dim, 2 * hp.head_dim);
                 run("attention_gate", 1, q_dim, 0, 1, [&] { return k::attention_gate(stream, s.attn, s.q, hp.n_heads, hp.head_dim, 1); });
-                matvec(D.output, s.attn, s.hidden, k::Norm{}, true);
+                matvec_reduced(D.output, s.attn, s.hidden);
             } else {
                 k::MatvecSegment segs[4] = {{D.qkv, s.gdn_qkv}, {D.z, s.gdn_z}, {D.beta, s.gdn_beta}, {D.alpha, s.gdn_alpha}};
                 uint64_t bytes = D.qkv.bytes() + D.z.bytes() + D.beta.bytes() + D.alpha.bytes();
                         run("matvec_delta", D.qkv.n_rows + D.z.n_rows + 2 * D.beta.n_rows, D.qkv.n_cols, bytes, 1,
                     [&] { return k::matvec(stream, segs, 4, s.hidden, norm(D.attn_norm), false); });
                         qwen_delta_tail(D, S.cache_index, 1);
-                matvec(D.ssm_out, s.gdn_out, s.hidden, k::Norm{}, true);
+                matvec_reduced(D.ssm_out, s.gdn_out, s.hidden);
             }
-            lfm2_dense_ffn(D);
+            qwen_dense_ffn(D);
             if (traced) copy(s.hidden, s.trace_layers + il * hp.n_embd, hp.n_embd);
         }
         if (traced)
             run("rms_norm", 1, hp.n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, W.output_norm, s.trace_final, hp.n_embd, 1, hp.norm_eps); });
-        if (want_logits) matvec(W.output, s.hidden, s.logits, norm(W.output_norm), false);
+        if (want_logits) logits_product(s.hidden);
     }
 
     // qwen35_metal.rs:1142-1240
@@ -446,21 +492,21 @@ struct Recorder {
                                         s.kv_half, s.scores, s.attn, shape);
                 });
                 run("attention_gate", n, q_dim, 0, 1, [&] { return k::attention_gate(stream, s.attn, s.q, hp.n_heads, hp.head_dim, n); });
-                matmul(D.output, s.attn, s.hidden, n, BC_STORE_ACCUMULATE);
+                matmul_reduced(D.output, s.attn, s.hidden, n);
             } else {
                 normed_matmuls(s.hidden, D.attn_norm, n,
                                {{&D.qkv, s.gdn_qkv, BC_STORE_OVERWRITE}, {&D.z, s.gdn_z, BC_STORE_OVERWRITE}, {&D.beta, s.gdn_beta, BC_STORE_OVERWRITE},
                                 {&D.alpha, s.gdn_alpha, BC_STORE_OVERWRITE}});
                 qwen_delta_tail(D, S.cache_index, n);
-                matmul(D.ssm_out, s.gdn_out, s.hidden, n, BC_STORE_ACCUMULATE);
+                matmul_reduced(D.ssm_out, s.gdn_out, s.hidden, n);
             }
             normed_swiglu(s.hidden, D.ffn_norm, n, D.gate, D.up, s.ffn);
-            matmul(D.down, s.ffn, s.hidden, n, BC_STORE_ACCUMULATE);
+            matmul_reduced(D.down, s.ffn, s.hidden, n);
             if (traced) copy(s.hidden, s.trace_layers + il * trace_stride, (uint64_t)n * n_embd);
         }
         if (traced)
             run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, W.output_norm, s.trace_final, n_embd, n, hp.norm_eps); });
-        if (want_logits) matvec(W.output, s.hidden + (size_t)(n - 1) * n_embd, s.logits, norm(W.output_norm), false);
+        if (want_logits) logits_product(s.hidden + (size_t)(n - 1) * n_embd);
     }
 
     // ---- one token of each of n sequences (the multi-sequence decode step). Row b of every

@@ -18,7 +18,7 @@ double since(Clock::time_point start) { return std::chrono::duration<double>(Clo
 
 bc_status ensure_trace_rows(bc_seq* s, uint32_t rows) {
     if (rows <= s->trace_rows) return BC_OK;
-    const bc_hparams& hp = s->model->hp;
+    const bc_hparams& hp = s->hp;
     BC_CUDA(cudaStreamSynchronize(s->backend->stream));
     cudaFree(s->trace_embedding);
     cudaFree(s->trace_layers);
@@ -77,7 +77,7 @@ bool replay_enabled(const bc_seq* s) {
 // start by adding one to s->step_pos, so the host seeds it with the first position minus one.
 bc_status capture_step(bc_seq* s, bool stream_variant) {
     cudaStream_t stream = s->backend->stream;
-    const uint32_t n_vocab = s->model->hp.n_vocab;
+    const uint32_t n_vocab = s->hp.n_vocab;
     uint64_t before = s->launches;
     BC_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
     Recorder r(*s);
@@ -213,9 +213,11 @@ bc_seq::~bc_seq() { release(); }
 
 void release_seq(bc_seq* seq) { seq->release(); }
 
-extern "C" {
+namespace {
 
-bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32_t kv_half, bc_seq** out) {
+// A sequence on `backend`; with `tp` its weights are the communicator rank's tensor-parallel shard
+// and its shapes the rank's share.
+bc_status seq_new(bc_model* model, bc_backend* backend, bc_comm* tp, uint32_t n_ctx, int32_t kv_half, bc_seq** out) {
     if (!model || !backend || !out) return fail(BC_ERR_ARGUMENT, "model, backend and out must be non-null");
     if (n_ctx == 0) return fail(BC_ERR_ARGUMENT, "the context must hold a token");
     BC_TRY(model_check_supported(*model));
@@ -226,9 +228,16 @@ bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32
     s->n_ctx = n_ctx;
     s->kv_half = kv_half != 0;
     s->batch = std::min(n_ctx, kPrefillBatch);
-    BC_TRY(model->device_model(backend, &s->weights));
+    s->hp = model->hp;
+    if (tp && tp->world > 1) {
+        BC_TRY(model->device_model_tp(backend, tp->rank, tp->world, &s->weights));
+        s->hp = tensor_parallel_hparams(model->hp, tp->rank, tp->world);
+        s->tp = tp;
+    } else {
+        BC_TRY(model->device_model(backend, &s->weights));
+    }
 
-    const bc_hparams& hp = model->hp;
+    const bc_hparams& hp = s->hp;
     const size_t n_embd = hp.n_embd, rows = s->batch;
     const size_t kv_dim = (size_t)hp.n_kv_heads * hp.head_dim, q_dim = (size_t)hp.n_heads * hp.head_dim;
     const size_t q_width = hp.architecture == BC_ARCH_QWEN35 ? 2 * q_dim : q_dim;  // Qwen's q holds [q | gate]
@@ -274,10 +283,17 @@ bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32
         {(void**)&s->gdn_out, rows * value_dim * 4},
         {(void**)&s->q_rot, qwen ? rows * q_dim * 4 : 0},
         {(void**)&s->step_pos, 4},
+        {(void**)&s->partial, s->tp ? rows * n_embd * 4 : 0},
         {(void**)&s->rope_table, hp.n_attention_layers && !qwen ? (size_t)n_ctx * (hp.n_rot / 2) * sizeof(float2) : 0},
     };
     const char* no_graph = getenv("BOBCAT_NO_GRAPH");
     s->use_graphs = !(no_graph && no_graph[0] == '1');
+    // A tensor-parallel step holds collectives; it is launched kernel by kernel unless
+    // BOBCAT_TP_GRAPH=1 asks for the captured form (NCCL records into a capture as well).
+    if (s->tp) {
+        const char* tp_graph = getenv("BOBCAT_TP_GRAPH");
+        s->use_graphs = s->use_graphs && tp_graph && tp_graph[0] == '1';
+    }
     // Kernels whose input vector outgrows the default shared-memory limit get their limit raised
     // now, so no launch inside a capture has to.
     uint32_t widest = std::max({hp.n_embd, hp.n_ff, hp.n_ff_expert, (uint32_t)q_dim, hp.n_v_heads * hp.v_head_dim});
@@ -306,13 +322,27 @@ bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32
     return BC_OK;
 }
 
+}  // namespace
+
+extern "C" {
+
+bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32_t kv_half, bc_seq** out) {
+    return seq_new(model, backend, nullptr, n_ctx, kv_half, out);
+}
+
+bc_status bc_seq_new_tensor_parallel(bc_model* model, bc_backend* backend, bc_comm* comm, uint32_t n_ctx, int32_t kv_half, bc_seq** out) {
+    if (!comm) return fail(BC_ERR_ARGUMENT, "comm must be non-null");
+    if (comm->backend != backend) return fail(BC_ERR_FOREIGN_BUFFER, "the communicator belongs to another backend");
+    return seq_new(model, backend, comm, n_ctx, kv_half, out);
+}
+
 void bc_seq_free(bc_seq* seq) { delete seq; }
 uint32_t bc_seq_n_past(const bc_seq* seq) { return seq ? seq->n_past : 0; }
 uint64_t bc_seq_launches(const bc_seq* seq) { return seq ? seq->launches : 0; }
 
 bc_status bc_seq_step(bc_seq* s, uint32_t token, float* logits, size_t logits_len, bc_trace* trace) {
     if (!s || !s->backend) return fail(BC_ERR_ARGUMENT, "seq must be non-null and its backend open");
-    const bc_hparams& hp = s->model->hp;
+    const bc_hparams& hp = s->hp;
     uint32_t pos = s->n_past;
     if (pos >= s->n_ctx) return fail(BC_ERR_CONTEXT_FULL, "context full: 1 token requested, 0 remaining");
     if (token >= hp.n_vocab) return fail(BC_ERR_TOKEN, "token %u outside the vocabulary of %u", token, hp.n_vocab);
@@ -348,7 +378,7 @@ bc_status bc_seq_step(bc_seq* s, uint32_t token, float* logits, size_t logits_le
 bc_status bc_seq_prefill(bc_seq* s, const uint32_t* tokens, size_t n_tokens, float* logits, size_t logits_len, float* final_norm,
                          size_t final_norm_len, bc_trace* trace) {
     if (!s || !s->backend || (!tokens && n_tokens)) return fail(BC_ERR_ARGUMENT, "seq and tokens must be non-null and the backend open");
-    const bc_hparams& hp = s->model->hp;
+    const bc_hparams& hp = s->hp;
     if (n_tokens > UINT32_MAX) return fail(BC_ERR_ARGUMENT, "too many tokens");
     uint32_t n = (uint32_t)n_tokens, remaining = s->n_ctx - s->n_past;
     if (n == 0) return fail(BC_ERR_ARGUMENT, "the prompt must hold a token");
@@ -539,7 +569,7 @@ bc_status bc_seq_checkpoint(bc_seq* s, bc_checkpoint** out) {
     c->resets = s->resets;
     c->n_past = s->n_past;
     c->conv_state.resize(s->conv_floats);
-    c->logits.resize(s->model->hp.n_vocab);
+    c->logits.resize(s->hp.n_vocab);
     cudaStream_t stream = s->backend->stream;
     if (s->conv_floats) BC_CUDA(cudaMemcpyAsync(c->conv_state.data(), s->conv_state, s->conv_floats * 4, cudaMemcpyDeviceToHost, stream));
     c->delta_state.resize(s->delta_floats);
@@ -556,7 +586,7 @@ bc_status bc_seq_restore(bc_seq* s, const bc_checkpoint* c) {
     // the sequence that took it, so no other sequence can continue from it.
     if (c->owner != s) return fail(BC_ERR_ARGUMENT, "the checkpoint belongs to another sequence");
     if (c->resets != s->resets) return fail(BC_ERR_ARGUMENT, "the checkpoint predates a reset");
-    if (c->conv_state.size() != s->conv_floats || c->delta_state.size() != s->delta_floats || c->logits.size() != s->model->hp.n_vocab || c->n_past > s->n_ctx)
+    if (c->conv_state.size() != s->conv_floats || c->delta_state.size() != s->delta_floats || c->logits.size() != s->hp.n_vocab || c->n_past > s->n_ctx)
         return fail(BC_ERR_ARGUMENT, "the checkpoint comes from a different model or context");
     BC_TRY(s->backend->activate());
     cudaStream_t stream = s->backend->stream;
@@ -593,7 +623,7 @@ bc_status bc_seq_set_skip(bc_seq* s, const char* name, uint32_t n_rows, uint32_t
 
 bc_status bc_seq_read_state(bc_seq* s, int32_t which, uint32_t layer, float* out, size_t cap, size_t* n) {
     if (!s || !s->backend || !n) return fail(BC_ERR_ARGUMENT, "seq and n must be non-null and the backend open");
-    const bc_hparams& hp = s->model->hp;
+    const bc_hparams& hp = s->hp;
     BC_TRY(s->backend->activate());
     cudaStream_t stream = s->backend->stream;
     if (which == 0) {

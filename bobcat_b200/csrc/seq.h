@@ -24,9 +24,18 @@ struct bc_checkpoint {
     std::vector<float> logits;
 };
 
+struct bc_comm;
+
 struct bc_seq {
     bc_model* model = nullptr;
     bc_backend* backend = nullptr;
+    // The shapes this sequence's kernels run with: the model's hyperparameters, or, on a
+    // tensor-parallel rank, those with the rank's share of heads and feed-forward rows.
+    bc_hparams hp{};
+    // Tensor parallelism: the communicator whose ranks share this sequence (null otherwise), and
+    // rows of n_embd floats for an output projection's partial result before the sum over ranks.
+    bc_comm* tp = nullptr;
+    float* partial = nullptr;
     std::shared_ptr<bc::DeviceModel> weights;
     uint32_t n_ctx = 0, n_past = 0, batch = 0;
     uint64_t resets = 0;
@@ -73,6 +82,9 @@ struct bc_seq {
     // Timing diagnostics (bc_seq_set_skip): launches of this name (and shape, when nonzero) are left out.
     std::string skip_name;
     uint32_t skip_rows = 0, skip_cols = 0;
+    // Batched products with f32 operands on the f32 tile kernels instead of half-precision operands
+    // on the tensor cores (the multi-sequence decode's precise mode).
+    bool exact_products = false;
     bool use_graphs = true;                   // BOBCAT_NO_GRAPH=1 turns replay off (launch every kernel eagerly)
 
     void release();

@@ -84,11 +84,16 @@ class Checkpoint:
 class SeqCuda:
     """The device state of one decode. ``Lfm2Cuda`` and ``Qwen35Cuda`` are this class."""
 
-    def __init__(self, model: Model, cuda: Cuda, n_ctx: int, kv_half: bool, _borrowed=None):
+    def __init__(self, model: Model, cuda: Cuda, n_ctx: int, kv_half: bool, _borrowed=None, comm=None):
+        """With ``comm`` (a ``sharding.Comm``) the sequence is tensor-parallel over the
+        communicator's ranks: every rank creates one and calls the same methods."""
         self._L = _lib.load()
-        self.model, self.cuda = model, cuda
+        self.model, self.cuda, self.comm = model, cuda, comm
         self._owned = _borrowed is None
-        if _borrowed is None:
+        if _borrowed is None and comm is not None:
+            h = C.c_void_p()
+            errors.check(self._L.bc_seq_new_tensor_parallel(model._h, cuda._h, comm._h, n_ctx, int(kv_half), C.byref(h)), self._L)
+        elif _borrowed is None:
             h = C.c_void_p()
             errors.check(self._L.bc_seq_new(model._h, cuda._h, n_ctx, int(kv_half), C.byref(h)), self._L)
         else:
@@ -234,6 +239,11 @@ class BatchCuda:
 
     def seq(self, index: int) -> SeqCuda:
         return self._seqs[index]
+
+    def set_exact(self, exact: bool) -> None:
+        """f32 operands on the f32 tile kernels (True) or half-precision operands on the tensor
+        cores (False, the default) for the batched pass."""
+        errors.check(self._L.bc_batch_set_exact(self._h, int(exact)), self._L)
 
     def generate(self, n: int) -> np.ndarray:
         out = np.zeros((self.n_seqs, n), dtype=np.uint32)

@@ -392,6 +392,13 @@ bc_status bc_batch_seq(bc_batch* batch, uint32_t index, bc_seq** out);
  * may stand at different positions. Tokens equal those of n_seqs separate bc_seq_generate calls up
  * to the rounding of the batched products (half-precision operands, as in prefill). */
 bc_status bc_batch_generate(bc_batch* batch, uint32_t* out, size_t n);
+/* Which arithmetic the batched pass multiplies with. 0 (the default): half-precision operands on
+ * the tensor cores, f32 accumulation - the arithmetic of the reference's batched Q4_0 products
+ * (crates/bobcat-metal/src/matmul.metal:519-521), accurate to the 5e-3 class of its batched path.
+ * Nonzero: f32 operands on the f32 tile kernels, accurate to the 1e-5 class of the single-token
+ * products, at a lower rate. The difference matters where a small change of the activations picks
+ * a different expert: with f32 operands every sequence decodes as it does alone. */
+bc_status bc_batch_set_exact(bc_batch* batch, int32_t exact);
 /* GPU seconds of the last bc_batch_generate and the kernels the batch has launched in total. */
 bc_status bc_batch_timings(const bc_batch* batch, double* gpu_seconds, uint64_t* launches);
 
@@ -425,6 +432,21 @@ uint64_t bc_comm_collectives(const bc_comm* comm);
  * size; every rank must call bc_batch_generate together with the same token count. */
 bc_status bc_batch_new_expert_parallel(bc_model* model, bc_backend* backend, bc_comm* comm, uint32_t n_seqs, uint32_t n_ctx,
                                        int32_t kv_half, bc_batch** out);
+
+/* Tensor-parallel sequence of a Qwen3.5 model (Qwen35Metal::new, crates/bobcat/src/qwen35_metal.rs:112,
+ * sharded): every rank of the communicator creates one and calls the same sequence methods with
+ * the same arguments. A rank holds the weights of its share of the attention heads (whole KV heads
+ * with the query heads that read them; ranks beyond the KV-head count share a KV head and split
+ * its query heads), of the DeltaNet heads (key heads, and the value heads j with j % n_k_heads
+ * among them, crates/bobcat-metal/src/gdn.metal:244), of the feed-forward rows and of the
+ * vocabulary rows of the output matrix, with the KV cache, convolution history and DeltaNet state
+ * of those heads. Each mixer and each feed-forward block ends in a sum over ranks of its output
+ * projection (ncclAllReduce); the logits are gathered from every rank's vocabulary rows. The
+ * residual stream, the logits and the picked tokens are the same on every rank. Sums over ranks
+ * associate differently from the one-device sum, so results agree with bc_seq_new's to rounding
+ * (the 1e-5 class of the single-token products), not bit for bit. */
+bc_status bc_seq_new_tensor_parallel(bc_model* model, bc_backend* backend, bc_comm* comm, uint32_t n_ctx, int32_t kv_half,
+                                     bc_seq** out);
 
 #ifdef __cplusplus
 }

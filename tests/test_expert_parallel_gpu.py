@@ -66,7 +66,7 @@ def test_two_ranks_decode_what_one_gpu_decodes(model_path, cuda, case):
     procs = [ctx.Process(target=_rank_main, args=(r, world, unique_id, path, n_seqs, kv_half, out)) for r in range(world)]
     for p in procs:
         p.start()
-    results = sorted(out.get(timeout=300) for _ in procs)
+    results = sorted((out.get(timeout=300) for _ in procs), key=lambda r: r[0])
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
