@@ -94,6 +94,13 @@ SIGNATURES = {
     "bc_model_decode_bytes": (u64, [vp]),
     "bc_seq_new": (i32, [vp, vp, u32, i32, C.POINTER(vp)]),
     "bc_seq_new_tensor_parallel": (i32, [vp, vp, vp, u32, i32, C.POINTER(vp)]),
+    "bc_seq_new_paged": (i32, [vp, vp, u32, i32, C.POINTER(vp)]),
+    "bc_kv_page_locate": (i32, [u32] * 8 + [C.POINTER(u64), C.POINTER(u32), C.POINTER(u64)]),
+    "bc_seq_kv_pages": (i32, [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)]),
+    "bc_seq_prefix_save": (i32, [vp, C.POINTER(vp)]),
+    "bc_seq_prefix_load": (i32, [vp, vp]),
+    "bc_prefix_free": (None, [vp]),
+    "bc_prefix_n_past": (u32, [vp]),
     "bc_seq_free": (None, [vp]),
     "bc_seq_n_past": (u32, [vp]),
     "bc_seq_step": (i32, [vp, u32, vp, sz, C.POINTER(Trace)]),

@@ -151,7 +151,7 @@ struct Recorder {
     size_t kv_element_bytes() const { return s.kv_half ? 2 : 4; }
     size_t kv_dim() const { return (size_t)hp.n_kv_heads * hp.head_dim; }
     // lfm2_metal.rs:1064-1067: layer-major, then position, then KV head, then element.
-    size_t layer_base(uint32_t cache_index) const { return (size_t)cache_index * s.n_ctx * kv_dim(); }
+    size_t layer_base(uint32_t cache_index) const { return (size_t)cache_index * s.kv_stride * kv_dim(); }
     void* cache_at(void* cache, size_t element) const { return static_cast<char*>(cache) + element * kv_element_bytes(); }
 
     // ---- LFM2 (lfm2_metal.rs:993-1156)

@@ -186,6 +186,8 @@ void bc_seq::release() {
         cudaStreamSynchronize(backend->stream);
         backend->seqs.erase(this);
     }
+    k_pages.reset();
+    v_pages.reset();
     cudaFree(arena);
     cudaFree(trace_embedding);
     cudaFree(trace_layers);
@@ -211,13 +213,19 @@ void bc_seq::release() {
 
 bc_seq::~bc_seq() { release(); }
 
+bc_prefix::~bc_prefix() {
+    if (state || tail) cudaSetDevice(device);
+    cudaFree(state);
+    cudaFree(tail);
+}
+
 void release_seq(bc_seq* seq) { seq->release(); }
 
 namespace {
 
 // A sequence on `backend`; with `tp` its weights are the communicator rank's tensor-parallel shard
 // and its shapes the rank's share.
-bc_status seq_new(bc_model* model, bc_backend* backend, bc_comm* tp, uint32_t n_ctx, int32_t kv_half, bc_seq** out) {
+bc_status seq_new(bc_model* model, bc_backend* backend, bc_comm* tp, uint32_t n_ctx, int32_t kv_half, bool paged, bc_seq** out) {
     if (!model || !backend || !out) return fail(BC_ERR_ARGUMENT, "model, backend and out must be non-null");
     if (n_ctx == 0) return fail(BC_ERR_ARGUMENT, "the context must hold a token");
     BC_TRY(model_check_supported(*model));
@@ -241,7 +249,24 @@ bc_status seq_new(bc_model* model, bc_backend* backend, bc_comm* tp, uint32_t n_
     const size_t n_embd = hp.n_embd, rows = s->batch;
     const size_t kv_dim = (size_t)hp.n_kv_heads * hp.head_dim, q_dim = (size_t)hp.n_heads * hp.head_dim;
     const size_t q_width = hp.architecture == BC_ARCH_QWEN35 ? 2 * q_dim : q_dim;  // Qwen's q holds [q | gate]
-    const size_t cache_bytes = (size_t)hp.n_attention_layers * n_ctx * kv_dim * (s->kv_half ? 2 : 4);
+    // Paged caches live in their own mapped ranges, whose layers start on page boundaries.
+    s->kv_stride = n_ctx;
+    if (paged && hp.n_attention_layers) {
+        PageGeometry geometry;
+        geometry.kv_dim = (uint32_t)kv_dim;
+        geometry.element_bytes = s->kv_half ? 2 : 4;
+        geometry.page_positions = page_positions_for(backend->device, geometry.kv_dim, geometry.element_bytes);
+        if (geometry.page_positions == 0)
+            return fail(BC_ERR_UNSUPPORTED, "KV rows of %zu elements do not divide this device's page size (or it has no virtual memory management)", kv_dim);
+        geometry.stride = (uint32_t)round_up(n_ctx, geometry.page_positions);
+        geometry.n_layers = hp.n_attention_layers;
+        s->kv_stride = geometry.stride;
+        s->k_pages.reset(new PagedCache());
+        s->v_pages.reset(new PagedCache());
+        BC_TRY(s->k_pages->create(backend->device, geometry));
+        BC_TRY(s->v_pages->create(backend->device, geometry));
+    }
+    const size_t cache_bytes = s->k_pages ? 0 : (size_t)hp.n_attention_layers * n_ctx * kv_dim * (s->kv_half ? 2 : 4);
     const size_t key_dim = (size_t)hp.n_k_heads * hp.k_head_dim, value_dim = (size_t)hp.n_v_heads * hp.v_head_dim;
     const size_t conv_dim = 2 * key_dim + value_dim;
     const bool qwen = hp.architecture == BC_ARCH_QWEN35;
@@ -309,6 +334,10 @@ bc_status seq_new(bc_model* model, bc_backend* backend, bc_comm* tp, uint32_t n_
         *it.slot = p;
         p += round_up(std::max<size_t>(it.bytes, 4), 256);
     }
+    if (s->k_pages) {
+        s->k_cache = s->k_pages->base();
+        s->v_cache = s->v_pages->base();
+    }
     if (hp.n_attention_layers && !qwen) BC_CUDA(k::rope_table(backend->stream, s->rope_table, n_ctx, hp.n_rot, hp.rope_theta));
     BC_TRY(ensure_trace_rows(s.get(), 1));
     e = cudaHostAlloc((void**)&s->readback, sizeof(uint32_t) * kGenerateInFlight, cudaHostAllocMapped);
@@ -327,13 +356,17 @@ bc_status seq_new(bc_model* model, bc_backend* backend, bc_comm* tp, uint32_t n_
 extern "C" {
 
 bc_status bc_seq_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32_t kv_half, bc_seq** out) {
-    return seq_new(model, backend, nullptr, n_ctx, kv_half, out);
+    return seq_new(model, backend, nullptr, n_ctx, kv_half, false, out);
+}
+
+bc_status bc_seq_new_paged(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32_t kv_half, bc_seq** out) {
+    return seq_new(model, backend, nullptr, n_ctx, kv_half, true, out);
 }
 
 bc_status bc_seq_new_tensor_parallel(bc_model* model, bc_backend* backend, bc_comm* comm, uint32_t n_ctx, int32_t kv_half, bc_seq** out) {
     if (!comm) return fail(BC_ERR_ARGUMENT, "comm must be non-null");
     if (comm->backend != backend) return fail(BC_ERR_FOREIGN_BUFFER, "the communicator belongs to another backend");
-    return seq_new(model, backend, comm, n_ctx, kv_half, out);
+    return seq_new(model, backend, comm, n_ctx, kv_half, false, out);
 }
 
 void bc_seq_free(bc_seq* seq) { delete seq; }
@@ -556,6 +589,16 @@ bc_status bc_seq_reset(bc_seq* s) {
     if (s->conv_floats) BC_CUDA(cudaMemsetAsync(s->conv_state, 0, s->conv_floats * 4, s->backend->stream));
     if (s->delta_floats) BC_CUDA(cudaMemsetAsync(s->delta_state, 0, s->delta_floats * 4, s->backend->stream));
     BC_CUDA(cudaStreamSynchronize(s->backend->stream));
+    // A sequence that started from a cached prefix shares the prefix's pages; a new sequence
+    // writes from position zero again, so it takes pages of its own back first.
+    if (s->k_pages && s->shared_positions) {
+        const PageGeometry& g = s->k_pages->geometry();
+        for (uint32_t slot = 0; slot < g.n_layers * g.pages_per_layer(); ++slot) {
+            BC_TRY(s->k_pages->make_private(slot));
+            BC_TRY(s->v_pages->make_private(slot));
+        }
+    }
+    s->shared_positions = 0;
     s->n_past = 0;
     s->resets += 1;
     return BC_OK;
@@ -586,6 +629,7 @@ bc_status bc_seq_restore(bc_seq* s, const bc_checkpoint* c) {
     // the sequence that took it, so no other sequence can continue from it.
     if (c->owner != s) return fail(BC_ERR_ARGUMENT, "the checkpoint belongs to another sequence");
     if (c->resets != s->resets) return fail(BC_ERR_ARGUMENT, "the checkpoint predates a reset");
+    if (c->n_past < s->shared_positions) return fail(BC_ERR_ARGUMENT, "the checkpoint lies inside the shared prefix of %u positions", s->shared_positions);
     if (c->conv_state.size() != s->conv_floats || c->delta_state.size() != s->delta_floats || c->logits.size() != s->hp.n_vocab || c->n_past > s->n_ctx)
         return fail(BC_ERR_ARGUMENT, "the checkpoint comes from a different model or context");
     BC_TRY(s->backend->activate());
@@ -599,6 +643,133 @@ bc_status bc_seq_restore(bc_seq* s, const bc_checkpoint* c) {
 }
 
 void bc_checkpoint_free(bc_checkpoint* c) { delete c; }
+
+bc_status bc_seq_prefix_save(bc_seq* s, bc_prefix** out) {
+    if (!s || !s->backend || !out) return fail(BC_ERR_ARGUMENT, "seq and out must be non-null and the backend open");
+    if (s->n_past == 0) return fail(BC_ERR_ARGUMENT, "a prefix holds at least one token");
+    if (s->tp) return fail(BC_ERR_UNSUPPORTED, "prefixes of tensor-parallel sequences");
+    BC_TRY(s->backend->activate());
+    cudaStream_t stream = s->backend->stream;
+    const bc_hparams& hp = s->hp;
+    std::unique_ptr<bc_prefix> p(new bc_prefix());
+    p->model = s->model;
+    p->device = s->backend->device;
+    p->kv_half = s->kv_half;
+    p->hp = hp;
+    p->n_past = s->n_past;
+    p->conv_floats = s->conv_floats;
+    p->delta_floats = s->delta_floats;
+    const size_t state_floats = s->conv_floats + s->delta_floats + hp.n_vocab;
+    cudaError_t e = cudaMalloc(&p->state, state_floats * 4);
+    if (e != cudaSuccess) return fail(BC_ERR_ALLOCATION, "cannot allocate %zu bytes for the prefix state: %s", state_floats * 4, cudaGetErrorString(e));
+    if (s->conv_floats) BC_CUDA(cudaMemcpyAsync(p->state, s->conv_state, s->conv_floats * 4, cudaMemcpyDeviceToDevice, stream));
+    if (s->delta_floats) BC_CUDA(cudaMemcpyAsync(p->state + s->conv_floats, s->delta_state, s->delta_floats * 4, cudaMemcpyDeviceToDevice, stream));
+    BC_CUDA(cudaMemcpyAsync(p->state + s->conv_floats + s->delta_floats, s->logits, (size_t)hp.n_vocab * 4, cudaMemcpyDeviceToDevice, stream));
+    // KV rows: full pages by reference, the rest by copy.
+    const size_t kv_dim = (size_t)hp.n_kv_heads * hp.head_dim, element = s->kv_half ? 2 : 4;
+    uint32_t first_copied = 0;
+    if (s->k_pages) {
+        p->paged = true;
+        p->geometry = s->k_pages->geometry();
+        p->full_pages = s->n_past / p->geometry.page_positions;
+        first_copied = p->full_pages * p->geometry.page_positions;
+        for (uint32_t layer = 0; layer < hp.n_attention_layers; ++layer)
+            for (uint32_t page = 0; page < p->full_pages; ++page) {
+                p->k_pages.push_back(s->k_pages->page(layer * p->geometry.pages_per_layer() + page));
+                p->v_pages.push_back(s->v_pages->page(layer * p->geometry.pages_per_layer() + page));
+            }
+        // The source goes on writing past n_past only, which lies beyond the full pages.
+        s->shared_positions = std::max(s->shared_positions, first_copied);
+    }
+    p->tail_rows = s->n_past - first_copied;
+    if (p->tail_rows && hp.n_attention_layers) {
+        const size_t layer_bytes = (size_t)p->tail_rows * kv_dim * element;
+        e = cudaMalloc(&p->tail, 2 * hp.n_attention_layers * layer_bytes);
+        if (e != cudaSuccess) return fail(BC_ERR_ALLOCATION, "cannot allocate the prefix's KV rows: %s", cudaGetErrorString(e));
+        for (int which = 0; which < 2; ++which)
+            for (uint32_t layer = 0; layer < hp.n_attention_layers; ++layer) {
+                const char* cache = static_cast<const char*>(which == 0 ? s->k_cache : s->v_cache);
+                const char* src = cache + ((size_t)layer * s->kv_stride + first_copied) * kv_dim * element;
+                char* dst = static_cast<char*>(p->tail) + ((size_t)which * hp.n_attention_layers + layer) * layer_bytes;
+                BC_CUDA(cudaMemcpyAsync(dst, src, layer_bytes, cudaMemcpyDeviceToDevice, stream));
+            }
+    }
+    BC_CUDA(cudaStreamSynchronize(stream));
+    *out = p.release();
+    return BC_OK;
+}
+
+bc_status bc_seq_prefix_load(bc_seq* s, const bc_prefix* p) {
+    if (!s || !s->backend || !p) return fail(BC_ERR_ARGUMENT, "seq and prefix must be non-null and the backend open");
+    if (s->tp) return fail(BC_ERR_UNSUPPORTED, "prefixes of tensor-parallel sequences");
+    if (p->model != s->model || p->device != s->backend->device || p->kv_half != s->kv_half || p->conv_floats != s->conv_floats ||
+        p->delta_floats != s->delta_floats)
+        return fail(BC_ERR_ARGUMENT, "the prefix comes from a different model, device or cache type");
+    if (p->n_past > s->n_ctx) return fail(BC_ERR_CONTEXT_FULL, "context full: a prefix of %u tokens, %u positions", p->n_past, s->n_ctx);
+    if (s->backend->recording) return fail(BC_ERR_ALREADY_RECORDING, "a recording is already open");
+    const bc_hparams& hp = s->hp;
+    if (p->paged && p->full_pages) {
+        if (!s->k_pages) return fail(BC_ERR_ARGUMENT, "a prefix of a paged sequence loads into paged sequences (bc_seq_new_paged)");
+        const PageGeometry& g = s->k_pages->geometry();
+        if (g.page_positions != p->geometry.page_positions || g.kv_dim != p->geometry.kv_dim || g.element_bytes != p->geometry.element_bytes)
+            return fail(BC_ERR_ARGUMENT, "the prefix's pages have another shape");
+    }
+    BC_TRY(s->backend->activate());
+    cudaStream_t stream = s->backend->stream;
+    // Remapping pages needs the stream idle.
+    BC_CUDA(cudaStreamSynchronize(stream));
+    const size_t kv_dim = (size_t)hp.n_kv_heads * hp.head_dim, element = s->kv_half ? 2 : 4;
+    uint32_t first_copied = 0;
+    if (p->paged && p->full_pages) {
+        const PageGeometry& g = s->k_pages->geometry();
+        for (uint32_t layer = 0; layer < hp.n_attention_layers; ++layer)
+            for (uint32_t page = 0; page < p->full_pages; ++page) {
+                BC_TRY(s->k_pages->share(layer * g.pages_per_layer() + page, p->k_pages[(size_t)layer * p->full_pages + page]));
+                BC_TRY(s->v_pages->share(layer * g.pages_per_layer() + page, p->v_pages[(size_t)layer * p->full_pages + page]));
+            }
+        first_copied = p->full_pages * g.page_positions;
+    }
+    // Pages past the shared ones may still be shared from an earlier prefix: this sequence writes there.
+    if (s->k_pages) {
+        const PageGeometry& g = s->k_pages->geometry();
+        const uint32_t shared = p->paged ? p->full_pages : 0;
+        for (uint32_t layer = 0; layer < hp.n_attention_layers; ++layer)
+            for (uint32_t page = shared; page < g.pages_per_layer(); ++page) {
+                BC_TRY(s->k_pages->make_private(layer * g.pages_per_layer() + page));
+                BC_TRY(s->v_pages->make_private(layer * g.pages_per_layer() + page));
+            }
+    }
+    if (p->tail_rows && hp.n_attention_layers) {
+        const size_t layer_bytes = (size_t)p->tail_rows * kv_dim * element;
+        for (int which = 0; which < 2; ++which)
+            for (uint32_t layer = 0; layer < hp.n_attention_layers; ++layer) {
+                char* cache = static_cast<char*>(which == 0 ? s->k_cache : s->v_cache);
+                char* dst = cache + ((size_t)layer * s->kv_stride + first_copied) * kv_dim * element;
+                const char* src = static_cast<const char*>(p->tail) + ((size_t)which * hp.n_attention_layers + layer) * layer_bytes;
+                BC_CUDA(cudaMemcpyAsync(dst, src, layer_bytes, cudaMemcpyDeviceToDevice, stream));
+            }
+    }
+    if (s->conv_floats) BC_CUDA(cudaMemcpyAsync(s->conv_state, p->state, s->conv_floats * 4, cudaMemcpyDeviceToDevice, stream));
+    if (s->delta_floats) BC_CUDA(cudaMemcpyAsync(s->delta_state, p->state + s->conv_floats, s->delta_floats * 4, cudaMemcpyDeviceToDevice, stream));
+    BC_CUDA(cudaMemcpyAsync(s->logits, p->state + s->conv_floats + s->delta_floats, (size_t)hp.n_vocab * 4, cudaMemcpyDeviceToDevice, stream));
+    BC_CUDA(cudaStreamSynchronize(stream));
+    s->shared_positions = first_copied;
+    s->n_past = p->n_past;
+    return BC_OK;
+}
+
+void bc_prefix_free(bc_prefix* p) { delete p; }
+
+uint32_t bc_prefix_n_past(const bc_prefix* p) { return p ? p->n_past : 0; }
+
+bc_status bc_seq_kv_pages(const bc_seq* s, uint32_t* page_positions, uint32_t* pages, uint32_t* shared_pages) {
+    if (!s) return fail(BC_ERR_ARGUMENT, "seq must be non-null");
+    const bool paged = s->k_pages != nullptr;
+    if (page_positions) *page_positions = paged ? s->k_pages->geometry().page_positions : 0;
+    if (pages) *pages = paged ? 2 * s->k_pages->geometry().n_layers * s->k_pages->geometry().pages_per_layer() : 0;
+    if (shared_pages) *shared_pages = paged ? s->k_pages->shared_pages() + s->v_pages->shared_pages() : 0;
+    return BC_OK;
+}
 
 bc_status bc_seq_timings(const bc_seq* s, double* encode_seconds, double* gpu_seconds) {
     if (!s || !s->backend) return fail(BC_ERR_ARGUMENT, "seq must be non-null and its backend open");
@@ -636,20 +807,20 @@ bc_status bc_seq_read_state(bc_seq* s, int32_t which, uint32_t layer, float* out
     }
     if (which == 1 || which == 2) {
         if (layer >= hp.n_attention_layers) return fail(BC_ERR_ARGUMENT, "no attention layer %u", layer);
-        size_t count = (size_t)s->n_ctx * hp.n_kv_heads * hp.head_dim;
+        size_t count = (size_t)s->n_ctx * hp.n_kv_heads * hp.head_dim, layer_stride = (size_t)s->kv_stride * hp.n_kv_heads * hp.head_dim;
         *n = count;
         if (!out) return BC_OK;
         if (cap < count) return fail(BC_ERR_ARGUMENT, "out must hold %zu floats", count);
         const char* cache = static_cast<const char*>(which == 1 ? s->k_cache : s->v_cache);
         if (s->kv_half) {
             std::vector<uint16_t> halfs(count);
-            BC_CUDA(cudaMemcpyAsync(halfs.data(), cache + (size_t)layer * count * 2, count * 2, cudaMemcpyDeviceToHost, stream));
+            BC_CUDA(cudaMemcpyAsync(halfs.data(), cache + (size_t)layer * layer_stride * 2, count * 2, cudaMemcpyDeviceToHost, stream));
             BC_CUDA(cudaStreamSynchronize(stream));
             for (size_t i = 0; i < count; ++i) {
                 out[i] = __half2float(__half(__half_raw{halfs[i]}));
             }
         } else {
-            BC_CUDA(cudaMemcpyAsync(out, cache + (size_t)layer * count * 4, count * 4, cudaMemcpyDeviceToHost, stream));
+            BC_CUDA(cudaMemcpyAsync(out, cache + (size_t)layer * layer_stride * 4, count * 4, cudaMemcpyDeviceToHost, stream));
             BC_CUDA(cudaStreamSynchronize(stream));
         }
         return BC_OK;

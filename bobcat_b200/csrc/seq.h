@@ -7,6 +7,7 @@
 #include <string>
 #include <vector>
 
+#include "kv_pages.h"
 #include "model.h"
 
 // Generation keeps up to this many steps submitted ahead of the device
@@ -14,6 +15,27 @@
 constexpr int kGenerateInFlight = 3;
 // Prefill runs the prompt this many tokens at a time (PREFILL_BATCH, lfm2_metal.rs:33-34).
 constexpr uint32_t kPrefillBatch = 512;
+
+// A cached prefix: everything a sequence needs to continue from position n_past - the recurrent
+// state, the logits, and the KV rows [0, n_past) of every attention layer. Of a paged sequence the
+// full pages are held by reference (shared with every sequence that loads the prefix) and only the
+// rows of the last, partial page are copied; of a contiguous sequence all rows are copied.
+struct bc_prefix {
+    const bc_model* model = nullptr;
+    int device = 0;
+    bool kv_half = false;
+    bc_hparams hp{};
+    uint32_t n_past = 0;
+    size_t conv_floats = 0, delta_floats = 0;
+    float* state = nullptr;  // device: conv history, DeltaNet state, logits
+    bool paged = false;
+    bc::PageGeometry geometry;
+    uint32_t full_pages = 0;  // per layer
+    std::vector<std::shared_ptr<bc::PhysicalPage>> k_pages, v_pages;  // [layer][full page]
+    void* tail = nullptr;     // device: [K, V][layer][tail_rows][kv_dim] rows from position full_pages * page_positions on
+    uint32_t tail_rows = 0;
+    ~bc_prefix();
+};
 
 struct bc_checkpoint {
     const bc_seq* owner = nullptr;
@@ -47,6 +69,11 @@ struct bc_seq {
     void* arena = nullptr;
     size_t arena_bytes = 0;
     void *k_cache = nullptr, *v_cache = nullptr;
+    // Positions between two layers of a cache: n_ctx, or n_ctx rounded up to whole pages when the
+    // caches are paged (then k_cache / v_cache are the bases of the paged ranges below).
+    uint32_t kv_stride = 0;
+    std::unique_ptr<bc::PagedCache> k_pages, v_pages;
+    uint32_t shared_positions = 0;  // positions [0, shared_positions) lie in pages shared with a prefix
     float *k = nullptr, *v = nullptr, *conv_state = nullptr, *hidden = nullptr, *normed = nullptr, *bcx = nullptr;
     float *conv_out = nullptr, *q = nullptr, *attn = nullptr, *scores = nullptr, *ffn = nullptr, *logits = nullptr;
     float *trace_embedding = nullptr, *trace_layers = nullptr, *trace_final = nullptr;

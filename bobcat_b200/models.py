@@ -81,16 +81,41 @@ class Checkpoint:
             pass
 
 
+class Prefix:
+    """A cached prefix on the device (``bc_prefix``)."""
+
+    def __init__(self, lib, handle):
+        self._L, self._h = lib, handle
+
+    def n_past(self) -> int:
+        return int(self._L.bc_prefix_n_past(self._h))
+
+    def close(self) -> None:
+        if self._h:
+            self._L.bc_prefix_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class SeqCuda:
     """The device state of one decode. ``Lfm2Cuda`` and ``Qwen35Cuda`` are this class."""
 
-    def __init__(self, model: Model, cuda: Cuda, n_ctx: int, kv_half: bool, _borrowed=None, comm=None):
+    def __init__(self, model: Model, cuda: Cuda, n_ctx: int, kv_half: bool, _borrowed=None, comm=None, paged: bool = False):
         """With ``comm`` (a ``sharding.Comm``) the sequence is tensor-parallel over the
-        communicator's ranks: every rank creates one and calls the same methods."""
+        communicator's ranks: every rank creates one and calls the same methods. With ``paged``
+        the KV caches are made of pages that cached prefixes can share."""
         self._L = _lib.load()
         self.model, self.cuda, self.comm = model, cuda, comm
         self._owned = _borrowed is None
-        if _borrowed is None and comm is not None:
+        if _borrowed is None and paged:
+            h = C.c_void_p()
+            errors.check(self._L.bc_seq_new_paged(model._h, cuda._h, n_ctx, int(kv_half), C.byref(h)), self._L)
+        elif _borrowed is None and comm is not None:
             h = C.c_void_p()
             errors.check(self._L.bc_seq_new_tensor_parallel(model._h, cuda._h, comm._h, n_ctx, int(kv_half), C.byref(h)), self._L)
         elif _borrowed is None:
@@ -167,6 +192,20 @@ class SeqCuda:
 
     def restore(self, checkpoint: Checkpoint) -> None:
         self._check(self._L.bc_seq_restore(self._h, checkpoint._h))
+
+    def save_prefix(self) -> "Prefix":
+        h = C.c_void_p()
+        self._check(self._L.bc_seq_prefix_save(self._h, C.byref(h)))
+        return Prefix(self._L, h)
+
+    def load_prefix(self, prefix: "Prefix") -> None:
+        self._check(self._L.bc_seq_prefix_load(self._h, prefix._h))
+
+    def kv_pages(self) -> tuple[int, int, int]:
+        """(positions per page, pages mapped, pages shared); zeros with contiguous caches."""
+        a, b, c = C.c_uint32(), C.c_uint32(), C.c_uint32()
+        self._check(self._L.bc_seq_kv_pages(self._h, C.byref(a), C.byref(b), C.byref(c)))
+        return int(a.value), int(b.value), int(c.value)
 
     def timings(self) -> tuple[float, float]:
         e, g = C.c_double(), C.c_double()

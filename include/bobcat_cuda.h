@@ -366,6 +366,42 @@ bc_status bc_seq_reset(bc_seq* seq);
 bc_status bc_seq_checkpoint(bc_seq* seq, bc_checkpoint** out);
 bc_status bc_seq_restore(bc_seq* seq, const bc_checkpoint* checkpoint);
 void bc_checkpoint_free(bc_checkpoint* checkpoint);
+/* ---- paged KV cache and cached prefixes.
+ * The reference keeps each sequence's KV cache as one buffer indexed layer * n_ctx * kv_dim + pos *
+ * kv_dim + kv_head * head_dim + d (crates/bobcat/src/lfm2_metal.rs:1064-1067) and reuses a prompt
+ * prefix only inside the sequence that computed it (checkpoint / restore, lfm2_metal.rs:250-288;
+ * the engine's prefix cache, crates/bobcat-cli/src/engine.rs:561-584). Here a sequence made with
+ * bc_seq_new_paged keeps that index - its kernels see one contiguous range per cache - but the
+ * memory behind the range comes in physical pages (one page = page_positions positions of one layer
+ * of K or V), and sequences that continue the same cached prefix map the same pages. */
+/* Lfm2Metal::new with paged caches. Fails with BC_ERR_UNSUPPORTED when a KV row does not divide
+ * the device's page size. */
+bc_status bc_seq_new_paged(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32_t kv_half, bc_seq** out);
+/* The arithmetic of the page table: the flat index above (with `stride`, the positions between two
+ * layers: n_ctx rounded up to whole pages) and the page (numbered layer * stride / page_positions +
+ * pos / page_positions) and element offset inside the page that hold it. flat_index ==
+ * page * page_positions * kv_dim + offset for every element, which is what keeps the kernels'
+ * indexing the reference's. */
+bc_status bc_kv_page_locate(uint32_t kv_dim, uint32_t head_dim, uint32_t page_positions, uint32_t stride, uint32_t layer, uint32_t pos,
+                            uint32_t kv_head, uint32_t d, uint64_t* flat_index, uint32_t* page, uint64_t* offset);
+/* Page size in positions, pages mapped (K and V) and how many of them are shared with a prefix or
+ * another sequence; zeros for a sequence with contiguous caches. */
+bc_status bc_seq_kv_pages(const bc_seq* seq, uint32_t* page_positions, uint32_t* pages, uint32_t* shared_pages);
+/* A cached prefix: the state of `seq` at its current position - recurrent state (convolution
+ * history, DeltaNet state), logits, and the KV rows [0, n_past) - kept on the device. Full pages of
+ * a paged sequence are held by reference, everything else is copied device to device. The prefix
+ * outlives the sequence. */
+typedef struct bc_prefix bc_prefix;
+bc_status bc_seq_prefix_save(bc_seq* seq, bc_prefix** out);
+/* Start `seq` (same model, device and cache type; n_ctx at least the prefix's length) from the
+ * prefix: afterwards it stands at the prefix's position exactly as the sequence that computed it
+ * did, and prefill / step / generate continue from there. A paged sequence maps the prefix's full
+ * pages (no copy) and keeps pages of its own from the first partly-filled page on; a prefix of a
+ * paged sequence loads only into paged sequences. bc_seq_reset gives the sequence private pages
+ * again. */
+bc_status bc_seq_prefix_load(bc_seq* seq, const bc_prefix* prefix);
+void bc_prefix_free(bc_prefix* prefix);
+uint32_t bc_prefix_n_past(const bc_prefix* prefix);
 /* last_encode_seconds / last_gpu_seconds (lfm2_metal.rs:223-230). */
 bc_status bc_seq_timings(const bc_seq* seq, double* encode_seconds, double* gpu_seconds);
 
