@@ -22,6 +22,10 @@ class Hparams(C.Structure):
         "n_k_heads", "n_v_heads", "k_head_dim", "v_head_dim")] + [("rope_theta", f32), ("norm_eps", f32)]
 
 
+class Sampling(C.Structure):
+    _fields_ = [("temperature", f32), ("top_k", u32), ("top_p", f32), ("min_p", f32), ("repeat_penalty", f32)]
+
+
 class Trace(C.Structure):
     _fields_ = [("embedding", C.POINTER(f32)), ("layers", C.POINTER(f32)), ("final_norm", C.POINTER(f32)), ("n_tokens", u32)]
 
@@ -70,6 +74,8 @@ SIGNATURES = {
     "bc_attention_scratch_floats": (sz, [u32, u32, u32, u32]),
     "bc_attention_static": (i32, [vp, vp, vp, vp, i32, vp] + [u32] * 6),
     "bc_op_argmax": (i32, [vp] + _VIEW + _VIEW + [u32]),
+    "bc_op_sample": (i32, [vp] + _VIEW + [u32] + _VIEW + [u32, C.POINTER(Sampling), f32] + _VIEW),
+    "bc_seq_sample": (i32, [vp, C.POINTER(Sampling), f32, vp, sz, C.POINTER(u32)]),
     "bc_readback_new": (i32, [vp, sz, C.POINTER(vp)]),
     "bc_readback_free": (None, [vp]),
     "bc_op_argmax_readback": (i32, [vp] + _VIEW + _VIEW + [vp, sz, u32]),

@@ -231,6 +231,10 @@ class Cuda:
     def argmax(self, x, out, n) -> None:
         self._check(self._L.bc_op_argmax(self._h, *_v(x), *_v(out), n))
 
+    def sample(self, logits, n, recent, n_recent, settings: "_lib.Sampling", uniform: float, out) -> None:
+        rb, ro = _v(recent) if recent is not None else (None, 0)
+        self._check(self._L.bc_op_sample(self._h, *_v(logits), n, rb, ro, n_recent, C.byref(settings), uniform, *_v(out)))
+
     def new_readback(self, slots: int) -> "Readback":
         h = C.c_void_p()
         self._check(self._L.bc_readback_new(self._h, slots, C.byref(h)))

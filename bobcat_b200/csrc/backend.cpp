@@ -574,6 +574,28 @@ bc_status bc_op_argmax(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* out
     });
 }
 
+bc_status bc_op_sample(bc_backend* b, bc_buffer* logits, size_t logits_off, uint32_t n, bc_buffer* recent, size_t recent_off, uint32_t n_recent,
+                       const bc_sampling* settings, float uniform, bc_buffer* out, size_t out_off) {
+    BC_TRY(need_recording(b));
+    if (!settings) return fail(BC_ERR_ARGUMENT, "settings must be non-null");
+    if (n == 0) return fail(BC_ERR_ARGUMENT, "sampling needs at least one logit");
+    if (!(uniform >= 0.f && uniform < 1.f)) return fail(BC_ERR_ARGUMENT, "the draw must lie in [0, 1)");
+    if (settings->temperature > 0.f && (!(settings->top_p > 0.f) || settings->min_p < 0.f || settings->min_p > 1.f || !(settings->repeat_penalty > 0.f)))
+        return fail(BC_ERR_ARGUMENT, "top_p must be positive, min_p in [0, 1] and the repetition penalty positive");
+    BC_TRY(check_range(b, logits, logits_off, (size_t)n * 4, "sample"));
+    BC_TRY(check_range(b, out, out_off, 4, "sample"));
+    const uint32_t* recent_ptr = nullptr;
+    if (n_recent) {
+        BC_TRY(check_range(b, recent, recent_off, (size_t)n_recent * 4, "sample"));
+        recent_ptr = reinterpret_cast<const uint32_t*>(at(recent, recent_off));
+    }
+    k::Sampling s{settings->temperature, settings->top_k, settings->top_p, settings->min_p, settings->repeat_penalty};
+    return b->run("sample", 1, n, 0, 1, [&] {
+        return k::sample(b->stream, reinterpret_cast<float*>(at(logits, logits_off)), n, recent_ptr, n_recent, s, uniform,
+                         reinterpret_cast<uint32_t*>(at(out, out_off)), nullptr);
+    });
+}
+
 bc_status bc_readback_new(bc_backend* b, size_t slots, bc_readback** out) {
     if (!b || !out) return fail(BC_ERR_ARGUMENT, "backend and out must be non-null");
     BC_TRY(b->activate());

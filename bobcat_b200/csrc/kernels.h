@@ -162,6 +162,17 @@ cudaError_t attention_flash(cudaStream_t stream, const float* q, const void* k_c
 // a host-mapped word that receives the same value.
 cudaError_t argmax(cudaStream_t stream, const float* x, uint32_t n, uint32_t* out, uint32_t* readback);
 
+// ---- sampling (kernels_sample.cu): Sampler::sample of crates/bobcat-cli/src/sampler.rs:45-112.
+struct Sampling {
+    float temperature = 0.f;   // <= 0: the most likely token
+    uint32_t top_k = 0;        // 0: no limit
+    float top_p = 1.f, min_p = 0.f, repeat_penalty = 1.f;
+};
+// Picks a token from `logits` (n floats, changed in place by the repetition penalty over the last
+// 64 of `recent`): penalty, top-k, top-p, min-p, temperature, then the draw `uniform` in [0, 1).
+cudaError_t sample(cudaStream_t stream, float* logits, uint32_t n, const uint32_t* recent, uint32_t n_recent, const Sampling& settings,
+                   float uniform, uint32_t* out, uint32_t* readback);
+
 // ---- multi-sequence decode (kernels_batch.cu): one new token of each of n_seqs sequences per pass.
 // What is per sequence is reached through device arrays indexed by the sequence's row.
 struct SeqTable {

@@ -488,6 +488,31 @@ bc_status bc_seq_greedy_token(bc_seq* s, uint32_t* token) {
     return BC_OK;
 }
 
+bc_status bc_seq_sample(bc_seq* s, const bc_sampling* settings, float uniform, const uint32_t* recent, size_t n_recent, uint32_t* token) {
+    if (!s || !s->backend || !settings || !token) return fail(BC_ERR_ARGUMENT, "seq, settings and token must be non-null and the backend open");
+    if (!recent && n_recent) return fail(BC_ERR_ARGUMENT, "recent must be non-null");
+    if (s->n_past == 0) return fail(BC_ERR_ARGUMENT, "sampling needs a prompt first");
+    if (!(uniform >= 0.f && uniform < 1.f)) return fail(BC_ERR_ARGUMENT, "the draw must lie in [0, 1)");
+    if (s->backend->recording) return fail(BC_ERR_ALREADY_RECORDING, "a recording is already open");
+    BC_TRY(s->backend->activate());
+    cudaStream_t stream = s->backend->stream;
+    // Only the window the penalty looks at goes to the device; the token slots past the context's
+    // end (unused by a full context's decode) would be too few, so a scratch of the trace buffer serves.
+    const size_t window = std::min<size_t>(n_recent, 64);
+    uint32_t* device_recent = reinterpret_cast<uint32_t*>(s->trace_final);  // at least n_embd floats, idle outside traced passes
+    if (window > s->hp.n_embd) return fail(BC_ERR_ARGUMENT, "the model is narrower than the penalty window");
+    if (window) BC_CUDA(cudaMemcpyAsync(device_recent, recent + (n_recent - window), window * 4, cudaMemcpyHostToDevice, stream));
+    k::Sampling k_settings{settings->temperature, settings->top_k, settings->top_p, settings->min_p, settings->repeat_penalty};
+    Recorder r(*s);
+    r.run("sample", 1, s->hp.n_vocab, 0, 1, [&] {
+        return k::sample(stream, s->logits, s->hp.n_vocab, window ? device_recent : nullptr, (uint32_t)window, k_settings, uniform, s->greedy_token, nullptr);
+    });
+    if (r.status != BC_OK) return r.status;
+    BC_CUDA(cudaMemcpyAsync(token, s->greedy_token, 4, cudaMemcpyDeviceToHost, stream));
+    BC_CUDA(cudaStreamSynchronize(stream));
+    return BC_OK;
+}
+
 bc_status bc_seq_generate(bc_seq* s, uint32_t* out, size_t n) { return generate_inner(s, out, n, false); }
 bc_status bc_seq_generate_next(bc_seq* s, uint32_t* out, size_t n) { return generate_inner(s, out, n, true); }
 

@@ -158,6 +158,14 @@ class SeqCuda:
         self._check(self._L.bc_seq_generate(self._h, out.ctypes.data_as(C.c_void_p), n))
         return out
 
+    def sample(self, settings: "_lib.Sampling", uniform: float, recent=()) -> int:
+        """The next token from the current logits by the reference sampler's rules, on the device."""
+        recent = np.ascontiguousarray(recent, dtype=np.uint32)
+        tok = C.c_uint32()
+        self._check(self._L.bc_seq_sample(self._h, C.byref(settings), uniform, recent.ctypes.data_as(C.c_void_p) if recent.size else None,
+                                          recent.size, C.byref(tok)))
+        return int(tok.value)
+
     def generate_next(self, n: int) -> np.ndarray:
         out = np.zeros(n, dtype=np.uint32)
         self._check(self._L.bc_seq_generate_next(self._h, out.ctypes.data_as(C.c_void_p), n))

@@ -214,6 +214,23 @@ size_t bc_attention_scratch_floats(uint32_t n_heads, uint32_t head_dim, uint32_t
 bc_status bc_attention_static(void* stream, const float* q, const void* k_cache, const void* v_cache, int32_t kv_half,
                               float* out, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t first_pos,
                               uint32_t n_queries, uint32_t n_ctx);
+/* Sampler::sample (crates/bobcat-cli/src/sampler.rs:45-112) on the device, in llama.cpp's order:
+ * the repetition penalty (each distinct token among the last 64 of `recent` once: positive logits
+ * divided, the others multiplied), top-k, top-p and min-p on the softmax at temperature one, the
+ * temperature on the survivors, then the draw. temperature <= 0 picks the most likely token (ties
+ * to the lowest index). Mirrors bobcat::Sampling (crates/bobcat/src/lfm2.rs:273-282). */
+typedef struct bc_sampling {
+    float temperature;
+    uint32_t top_k; /* 0: no limit */
+    float top_p, min_p, repeat_penalty;
+} bc_sampling;
+/* The pick from `n` logits at `logits` (changed in place by the penalty, as the reference changes
+ * its slice) goes to the 32-bit word at `out`. `recent` holds n_recent token ids (may be null with
+ * n_recent 0). `uniform` in [0, 1) is the random draw: the reference takes it from its host-side
+ * generator, whose stream a caller keeps on the host. Logits equal to a cut value are all kept
+ * where the reference's unstable sort keeps an arbitrary subset. */
+bc_status bc_op_sample(bc_backend* b, bc_buffer* logits, size_t logits_off, uint32_t n, bc_buffer* recent, size_t recent_off,
+                       uint32_t n_recent, const bc_sampling* settings, float uniform, bc_buffer* out, size_t out_off);
 /* Metal::argmax (backend.rs:2612-2617): index of the largest of n floats, ties to the lowest. */
 bc_status bc_op_argmax(bc_backend* b, bc_buffer* x, size_t x_off, bc_buffer* out, size_t out_off, uint32_t n);
 /* Readback / Metal::new_readback / argmax_readback / read_readback (backend.rs:324-333,
@@ -361,6 +378,11 @@ bc_status bc_seq_generate_next(bc_seq* seq, uint32_t* out, size_t n);
 typedef int32_t (*bc_emit_fn)(uint32_t token, void* user);
 bc_status bc_seq_generate_stream(bc_seq* seq, uint32_t max_tokens, bc_emit_fn emit, void* user, uint32_t* gained,
                                  size_t gained_cap, size_t* n_gained);
+/* The engine's sampled decode step without the logits leaving the device
+ * (crates/bobcat-cli/src/engine.rs:615-630 reads them back and samples on the host): pick the next
+ * token from the sequence's current logits with bc_op_sample's rules and return it. The caller
+ * feeds it to bc_seq_step (with or without logits) to advance. */
+bc_status bc_seq_sample(bc_seq* seq, const bc_sampling* settings, float uniform, const uint32_t* recent, size_t n_recent, uint32_t* token);
 /* reset / checkpoint / restore (lfm2_metal.rs:238-288; qwen35_metal.rs:238-297). */
 bc_status bc_seq_reset(bc_seq* seq);
 bc_status bc_seq_checkpoint(bc_seq* seq, bc_checkpoint** out);
