@@ -11,7 +11,7 @@ import numpy as np
 
 from . import _lib, errors
 
-F32, F16, Q4_0, Q8_0 = 0, 1, 2, 8
+F32, F16, Q4_0, Q8_0, Q6_K = 0, 1, 2, 8, 14
 OVERWRITE, ACCUMULATE, SWIGLU = 0, 1, 2
 
 

@@ -109,7 +109,7 @@ bc_status check_aligned(const char* op, std::initializer_list<size_t> offsets) {
     return BC_OK;
 }
 
-bool known_format(int32_t format) { return format == BC_F32 || format == BC_F16 || format == BC_Q4_0; }
+bool known_format(int32_t format) { return format == BC_F32 || format == BC_F16 || format == BC_Q4_0 || format == BC_Q8_0 || format == BC_Q6_K; }
 
 }  // namespace
 
@@ -226,6 +226,7 @@ bc_status bc_matrix_upload(bc_backend* b, int32_t format, const void* data, uint
     if (!b || !data || !out) return fail(BC_ERR_ARGUMENT, "backend, data and out must be non-null");
     if (!known_format(format)) return fail(BC_ERR_UNSUPPORTED, "matrices in format %d", format);
     if (n_rows == 0 || n_cols == 0 || n_cols % 32 != 0) return fail(BC_ERR_ARGUMENT, "a matrix has rows of a multiple of 32 columns");
+    if (format == BC_Q6_K && n_cols % 256 != 0) return fail(BC_ERR_ARGUMENT, "Q6_K rows hold whole super-blocks of 256");
     BC_TRY(b->activate());
     uint64_t raw_bytes = (uint64_t)n_rows * type_row_bytes((uint32_t)format, n_cols);
     // Q4_0 matrices also get the tile layout of the tensor-core decode kernel, after the split one.

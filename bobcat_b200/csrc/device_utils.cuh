@@ -71,6 +71,39 @@ __device__ __forceinline__ void unpack_q4_word(uint32_t w, float (&lo)[4], float
     hi[0] = c.x; hi[2] = c.y; hi[1] = d.x; hi[3] = d.y;
 }
 
+// ---- formats kept in their GGUF byte layout on the device (rows of whole blocks, 2-byte aligned).
+// Element `col` of a row, with the reference's arithmetic so the value is bit-identical to
+// scalar::dequantize (crates/bobcat/src/scalar.rs:108-113 for Q8_0, :175-202 for Q6_K).
+constexpr int kQ8_0BlockBytes = 34, kQ6KBlockBytes = 210;
+
+__device__ __forceinline__ float half_at(const uint8_t* p) {
+    return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(p)));
+}
+
+// Q8_0: an fp16 scale, then 32 int8 quants; value = f32(q) * d.
+__device__ __forceinline__ float q8_0_at(const uint8_t* row, uint32_t col) {
+    const uint8_t* block = row + (uint64_t)(col >> 5) * kQ8_0BlockBytes;
+    return (float)(int)(signed char)block[2 + (col & 31)] * half_at(block);
+}
+
+// Q6_K: per super-block of 256, 128 bytes of low nibbles, 64 bytes of high bit pairs, 16 int8
+// scales of 16-element blocks, then an fp16 d. Each half spreads 128 elements over 64 low bytes
+// and 32 high bytes: element l + 32 k of a half (k = 0..3) takes the low nibble (k < 2) or high
+// nibble (k >= 2) of low[l + 32 (k & 1)], bits 2k.. of high[l], and scale l / 16 + 2 k.
+// value = (d * f32(scale)) * f32(q - 32).
+__device__ __forceinline__ float q6k_at(const uint8_t* row, uint32_t col) {
+    const uint8_t* block = row + (uint64_t)(col >> 8) * kQ6KBlockBytes;
+    const uint32_t in_block = col & 255, half_index = in_block >> 7, e = in_block & 127, l = e & 31, k = e >> 5;
+    const uint8_t* low = block + half_index * 64;
+    const uint8_t* high = block + 128 + half_index * 32;
+    const signed char* scales = reinterpret_cast<const signed char*>(block + 192 + half_index * 8);
+    const uint8_t byte = low[l + 32 * (k & 1)];
+    const uint32_t nibble = k < 2 ? (byte & 0xfu) : (byte >> 4);
+    const uint32_t top = (high[l] >> (2 * k)) & 3u;
+    const float d = half_at(block + 208);
+    return (d * (float)(int)scales[(l >> 4) + 2 * k]) * (float)((int)(nibble | (top << 4)) - 32);
+}
+
 __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"

@@ -67,8 +67,10 @@ __global__ void __launch_bounds__(kThreads) matmul_simt_kernel(MatmulParams p) {
                 float v = 0.f;
                 if (row < n_rows) {
                     uint64_t at = (uint64_t)row * n_cols + k0 + kk;
-                    v = p.w.format == BC_F16 ? __half2float(static_cast<const __half*>(p.w.data)[at])
-                                             : static_cast<const float*>(p.w.data)[at];
+                    if (p.w.format == BC_Q8_0) v = q8_0_at(static_cast<const uint8_t*>(p.w.data) + (uint64_t)row * (n_cols >> 5) * kQ8_0BlockBytes, k0 + kk);
+                    else if (p.w.format == BC_Q6_K) v = q6k_at(static_cast<const uint8_t*>(p.w.data) + (uint64_t)row * (n_cols >> 8) * kQ6KBlockBytes, k0 + kk);
+                    else v = p.w.format == BC_F16 ? __half2float(static_cast<const __half*>(p.w.data)[at])
+                                                  : static_cast<const float*>(p.w.data)[at];
                 }
                 ws[kk][r] = v;
             }

@@ -108,7 +108,8 @@ __global__ void __launch_bounds__(kThreads) matvec_kernel(Params p) {
     // first touched below the wait.
     pdl_launch_dependents();
     {
-        const uint32_t row_bytes = FORMAT == BC_Q4_0 ? (n_cols >> 5) * 18 : n_cols * (FORMAT == BC_F16 ? 2u : 4u);
+        const uint32_t row_bytes = FORMAT == BC_Q4_0 ? (n_cols >> 5) * 18 : FORMAT == BC_Q8_0 ? (n_cols >> 5) * 34 : FORMAT == BC_Q6_K ? (n_cols >> 8) * 210
+                                 : n_cols * (FORMAT == BC_F16 ? 2u : 4u);
         const uint32_t rows_per_pass = (uint32_t)units_per_pass * R;
         uint32_t max_rows = p.prefetch_bytes / (row_bytes ? row_bytes : 1);
         for (uint32_t t = threadIdx.x; t < max_rows; t += blockDim.x) {
@@ -194,7 +195,7 @@ int sm_count_impl() {
 // How many warps share a unit: split rows that would take one warp more than three trips when the
 // launch has too few units to fill the machine anyway.
 int choose_ksplit(int format, uint32_t n_cols, uint64_t units) {
-    uint32_t per_trip = format == BC_Q4_0 ? 1024 : format == BC_F16 ? 256 : 128;
+    uint32_t per_trip = format == BC_Q4_0 || format == BC_Q8_0 ? 1024 : format == BC_F16 ? 256 : 128;
     uint32_t trips = (n_cols + per_trip - 1) / per_trip;
     if (units >= (uint64_t)sm_count_impl() * kWarps * 2) return 1;
     int ksplit = 1;
@@ -207,6 +208,8 @@ const void* kernel_for(int format) {
     switch (format) {
         case BC_Q4_0: return (const void*)matvec_kernel<BC_Q4_0, MODE>;
         case BC_F16: return (const void*)matvec_kernel<BC_F16, MODE>;
+        case BC_Q8_0: return (const void*)matvec_kernel<BC_Q8_0, MODE>;
+        case BC_Q6_K: return (const void*)matvec_kernel<BC_Q6_K, MODE>;
         default: return (const void*)matvec_kernel<BC_F32, MODE>;
     }
 }
@@ -281,6 +284,10 @@ Mat Mat::rows(uint32_t first, uint32_t count) const {
         m.tiles = (tiles && first % 16 == 0) ? static_cast<const uint8_t*>(tiles) + (uint64_t)(first / 16) * nb * 288 : nullptr;
     } else if (format == BC_F16) {
         m.data = static_cast<const __half*>(data) + (uint64_t)first * n_cols;
+    } else if (format == BC_Q8_0) {
+        m.data = static_cast<const uint8_t*>(data) + (uint64_t)first * (n_cols >> 5) * 34;
+    } else if (format == BC_Q6_K) {
+        m.data = static_cast<const uint8_t*>(data) + (uint64_t)first * (n_cols >> 8) * 210;
     } else {
         m.data = static_cast<const float*>(data) + (uint64_t)first * n_cols;
     }
@@ -291,6 +298,8 @@ uint64_t Mat::bytes() const {
     uint64_t n = (uint64_t)n_rows * n_cols;
     if (format == BC_Q4_0) return n / 32 * 18;
     if (format == BC_F16) return n * 2;
+    if (format == BC_Q8_0) return n / 32 * 34;
+    if (format == BC_Q6_K) return n / 256 * 210;
     return n * 4;
 }
 
@@ -298,7 +307,7 @@ cudaError_t matvec_prepare(uint32_t widest_cols) {
     size_t smem = (size_t)widest_cols * 4;
     cudaError_t prepared = matvec_mma_prepare(widest_cols);
     if (prepared != cudaSuccess) return prepared;
-    for (int format : {BC_Q4_0, BC_F16, BC_F32}) {
+    for (int format : {BC_Q4_0, BC_F16, BC_F32, BC_Q8_0, BC_Q6_K}) {
         for (const void* kernel : {kernel_for<kPlain>(format), kernel_for<kSwiglu>(format), kernel_for<kConv>(format)}) {
             cudaError_t e = ensure_dynamic_smem(kernel, smem);
             if (e != cudaSuccess) return e;

@@ -76,6 +76,18 @@ __global__ void silu_mul_kernel(float* __restrict__ x, const float* __restrict__
     }
 }
 
+// Dequantise a matrix kept in its GGUF byte layout (Q8_0, Q6_K), one thread per element.
+template <typename Out>
+__global__ void expand_bytes_kernel(Mat w, Out* __restrict__ out) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (uint64_t)w.n_rows * w.n_cols) return;
+    const uint32_t row = (uint32_t)(i / w.n_cols), col = (uint32_t)(i % w.n_cols);
+    float v;
+    if (w.format == BC_Q8_0) v = q8_0_at(static_cast<const uint8_t*>(w.data) + (uint64_t)row * (w.n_cols >> 5) * kQ8_0BlockBytes, col);
+    else v = q6k_at(static_cast<const uint8_t*>(w.data) + (uint64_t)row * (w.n_cols >> 8) * kQ6KBlockBytes, col);
+    out[i] = (Out)v;
+}
+
 // grid (ceil(n_embd / threads), n_tokens)
 __global__ void embed_kernel(Mat w, const uint32_t* __restrict__ tokens, Pos pos, float* __restrict__ out) {
     pdl_launch_dependents();
@@ -93,6 +105,10 @@ __global__ void embed_kernel(Mat w, const uint32_t* __restrict__ tokens, Pos pos
         v = (float)(n - 8) * __half2float(w.scales[block]);
     } else if (w.format == BC_F16) {
         v = __half2float(static_cast<const __half*>(w.data)[(uint64_t)token * w.n_cols + c]);
+    } else if (w.format == BC_Q8_0) {
+        v = q8_0_at(static_cast<const uint8_t*>(w.data) + (uint64_t)token * (w.n_cols >> 5) * kQ8_0BlockBytes, c);
+    } else if (w.format == BC_Q6_K) {
+        v = q6k_at(static_cast<const uint8_t*>(w.data) + (uint64_t)token * (w.n_cols >> 8) * kQ6KBlockBytes, c);
     } else {
         v = static_cast<const float*>(w.data)[(uint64_t)token * w.n_cols + c];
     }
@@ -421,6 +437,9 @@ cudaError_t expand(cudaStream_t stream, const Mat& w, void* out, bool out_half) 
             expand_q4_0_kernel<__half><<<blocks_for(nb), kThreads, 0, stream>>>(static_cast<const uint4*>(w.data), w.scales, nb, static_cast<__half*>(out));
         else
             expand_q4_0_kernel<float><<<blocks_for(nb), kThreads, 0, stream>>>(static_cast<const uint4*>(w.data), w.scales, nb, static_cast<float*>(out));
+    } else if (w.format == BC_Q8_0 || w.format == BC_Q6_K) {
+        if (out_half) expand_bytes_kernel<__half><<<blocks_for(n), kThreads, 0, stream>>>(w, static_cast<__half*>(out));
+        else expand_bytes_kernel<float><<<blocks_for(n), kThreads, 0, stream>>>(w, static_cast<float*>(out));
     } else if (w.format == BC_F16) {
         if (out_half) convert_kernel<__half, __half><<<blocks_for(n), kThreads, 0, stream>>>(static_cast<const __half*>(w.data), static_cast<__half*>(out), n);
         else convert_kernel<__half, float><<<blocks_for(n), kThreads, 0, stream>>>(static_cast<const __half*>(w.data), static_cast<float*>(out), n);

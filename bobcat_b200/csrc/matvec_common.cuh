@@ -24,6 +24,12 @@ __device__ __forceinline__ RowPtr row_of(const Mat& m, uint32_t row) {
     } else if (m.format == BC_F16) {
         p.data = static_cast<const __half*>(m.data) + (uint64_t)row * m.n_cols;
         p.scales = nullptr;
+    } else if (m.format == BC_Q8_0) {
+        p.data = static_cast<const uint8_t*>(m.data) + (uint64_t)row * (m.n_cols >> 5) * kQ8_0BlockBytes;
+        p.scales = nullptr;
+    } else if (m.format == BC_Q6_K) {
+        p.data = static_cast<const uint8_t*>(m.data) + (uint64_t)row * (m.n_cols >> 8) * kQ6KBlockBytes;
+        p.scales = nullptr;
     } else {
         p.data = static_cast<const float*>(m.data) + (uint64_t)row * m.n_cols;
         p.scales = nullptr;
@@ -42,9 +48,10 @@ __device__ __forceinline__ void prefetch_row(const RowPtr& r, uint32_t n_cols) {
         uint32_t nb = n_cols >> 5;
         prefetch_l2(r.data, nb * 16);
         if ((reinterpret_cast<uintptr_t>(r.scales) & 15) == 0 && (nb & 7) == 0) prefetch_l2(r.scales, nb * 2);
-    } else {
+    } else if (FORMAT == BC_F16 || FORMAT == BC_F32) {
         prefetch_l2(r.data, n_cols * (FORMAT == BC_F16 ? 2u : 4u));
     }
+    // Rows of the byte-layout formats are only 2-byte aligned: no bulk prefetch for them.
 }
 
 // Stage x into shared memory in the rotated chunk layout, times the norm weight when given.
@@ -127,6 +134,62 @@ __device__ __forceinline__ void dot_rows(const RowPtr (&rows)[R], uint32_t n_col
                 float4 w = ldg_stream(static_cast<const float4*>(rows[r].data) + cc);
                 float s = w.x * xv.x + w.y * xv.y + w.z * xv.z + w.w * xv.w;
                 acc[r] += live ? s : 0.f;
+            }
+        }
+    } else if (FORMAT == BC_Q8_0) {
+        // A lane owns whole blocks: 32 int8 quants (read as 16 aligned byte pairs) and one scale.
+        const int nb = n_cols >> 5;
+        for (int b0 = kpart * 32; b0 < nb; b0 += step) {
+            const int b = b0 + lane;
+            if (b >= nb) continue;
+            float xv[32];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const float4 v = xs[x_slot(b, c)];
+                xv[4 * c] = v.x; xv[4 * c + 1] = v.y; xv[4 * c + 2] = v.z; xv[4 * c + 3] = v.w;
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint8_t* block = static_cast<const uint8_t*>(rows[r].data) + (uint64_t)b * kQ8_0BlockBytes;
+                const unsigned short* pairs = reinterpret_cast<const unsigned short*>(block + 2);
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const unsigned short two = pairs[i];
+                    sum += (float)(int)(signed char)(two & 0xff) * xv[2 * i] + (float)(int)(signed char)(two >> 8) * xv[2 * i + 1];
+                }
+                acc[r] += half_at(block) * sum;
+            }
+        }
+    } else if (FORMAT == BC_Q6_K) {
+        // Item (super-block, half, l) yields the four elements l + 32 k of that half; lanes take
+        // consecutive l, so their byte reads are contiguous.
+        const int items = (n_cols >> 8) * 64;
+        const float* xf = reinterpret_cast<const float*>(xs);
+        for (int j0 = kpart * 32; j0 < items; j0 += step) {
+            const int j = j0 + lane;
+            if (j >= items) continue;
+            const int sb = j >> 6, half_index = (j >> 5) & 1, l = j & 31;
+            float xv[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int e = sb * 256 + half_index * 128 + l + 32 * k;
+                xv[k] = xf[x_slot(e >> 5, (e & 31) >> 2) * 4 + (e & 3)];
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint8_t* block = static_cast<const uint8_t*>(rows[r].data) + (uint64_t)sb * kQ6KBlockBytes;
+                const uint8_t* low = block + half_index * 64;
+                const uint8_t hb = block[128 + half_index * 32 + l];
+                const signed char* scales = reinterpret_cast<const signed char*>(block + 192 + half_index * 8);
+                const float d = half_at(block + 208);
+                const uint8_t b0 = low[l], b1 = low[l + 32];
+                const int q[4] = {(int)((b0 & 0xfu) | ((hb & 3u) << 4)) - 32, (int)((b1 & 0xfu) | (((hb >> 2) & 3u) << 4)) - 32,
+                                  (int)((b0 >> 4) | (((hb >> 4) & 3u) << 4)) - 32, (int)((b1 >> 4) | (((hb >> 6) & 3u) << 4)) - 32};
+                float sum = 0.f;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) sum += (d * (float)(int)scales[(l >> 4) + 2 * k]) * (float)q[k] * xv[k];
+                acc[r] += sum;
             }
         }
     } else {  // BC_F16

@@ -235,7 +235,7 @@ bc_status load_qwen35(bc_model& m) {
     return BC_OK;
 }
 
-bool kernel_format(uint32_t type) { return type == T_F32 || type == T_F16 || type == T_Q4_0; }
+bool kernel_format(uint32_t type) { return type == T_F32 || type == T_F16 || type == T_Q4_0 || type == T_Q8_0 || type == T_Q6K; }
 
 // What the kernels can run (check_supported, crates/bobcat/src/lfm2_metal.rs:797-866, and the
 // DeltaNet limits of crates/bobcat-metal/src/backend.rs:1899-1911).
@@ -251,8 +251,9 @@ bc_status check_supported(const bc_model& m) {
         if (S.moe && S.router.t->type != T_F32) return fail(BC_ERR_UNSUPPORTED, "an F32 router, got type %u", S.router.t->type);
     }
     for (const HostMatrix* hm : all) {
-        if (!kernel_format(hm->t->type)) return fail(BC_ERR_UNSUPPORTED, "matrices in Q4_0, F16 or F32, got type %u for %s", hm->t->type, hm->t->name.c_str());
+        if (!kernel_format(hm->t->type)) return fail(BC_ERR_UNSUPPORTED, "matrices in Q4_0, Q8_0, Q6_K, F16 or F32, got type %u for %s", hm->t->type, hm->t->name.c_str());
         if (hm->n_cols % 32 != 0) return fail(BC_ERR_UNSUPPORTED, "matrix rows of a multiple of 32 columns, got %u for %s", hm->n_cols, hm->t->name.c_str());
+        if (hm->t->type == T_Q6K && hm->n_cols % 256 != 0) return fail(BC_ERR_UNSUPPORTED, "Q6_K rows of whole super-blocks of 256, got %u for %s", hm->n_cols, hm->t->name.c_str());
     }
     uint32_t group = hp.n_heads / (hp.n_kv_heads ? hp.n_kv_heads : 1);
     if (hp.n_attention_layers && (hp.head_dim % 32 != 0 || hp.head_dim > 256 || group > 8))

@@ -80,6 +80,9 @@ CONFIGS: dict[str, dict] = {
     # in the projections, 44 in the down projection) and heads of 64 elements take the tensor-core attention.
     "lfm2-medium": dict(arch="lfm2", vocab=4096, hidden=1024, layers=4, attention=[1, 3], heads=16, kv_heads=4, ff=2816, conv_kernel=3,
                         theta=1e6, eps=1e-5),
+    # The embedding (and tied output) matrix in Q8_0, as quantised checkpoints keep it in a quantised type.
+    "lfm2-tiny-q8": dict(arch="lfm2", vocab=512, hidden=128, layers=4, attention=[1, 3], heads=4, kv_heads=2, ff=256, conv_kernel=3,
+                         theta=1e6, eps=1e-5, embd_type=Q8_0),
     "lfm2moe-tiny": dict(arch="lfm2moe", vocab=512, hidden=128, layers=4, attention=[1, 3], heads=4, kv_heads=2, ff=256, conv_kernel=3,
                          theta=1e6, eps=1e-5, experts=8, experts_used=2, ff_expert=96, dense_layers=1),
     "qwen35-tiny": dict(arch="qwen35", vocab=512, hidden=128, layers=4, heads=2, kv_heads=1, head_dim=64, n_rot=32, ff=256, k_heads=2,
@@ -140,7 +143,7 @@ def _write_lfm2(w: _Writer, c: dict) -> None:
         w.u32(f"{arch}.expert_feed_forward_length", c["ff_expert"])
         w.u32(f"{arch}.expert_gating_func", 2)
         w.u32(f"{arch}.leading_dense_block_count", c["dense_layers"])
-    w.tensor("token_embd.weight", F32, [hidden, c["vocab"]])
+    w.tensor("token_embd.weight", c.get("embd_type", F32), [hidden, c["vocab"]])
     w.ones("token_embd_norm.weight", [hidden])
     for il in range(layers):
         p = f"blk.{il}."

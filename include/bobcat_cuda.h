@@ -69,7 +69,7 @@ const char* bc_version(void);
 
 /* ---- weight formats: bobcat_metal::Format (crates/bobcat-metal/src/backend.rs:408-449).
  * The numeric values are the ggml type ids (crates/bobcat-gguf/src/lib.rs:126-152). */
-enum { BC_F32 = 0, BC_F16 = 1, BC_Q4_0 = 2, BC_Q8_0 = 8 };
+enum { BC_F32 = 0, BC_F16 = 1, BC_Q4_0 = 2, BC_Q8_0 = 8, BC_Q6_K = 14 };
 
 /* ---- how a batched multiply combines with its output: bobcat_metal::Store (backend.rs:361-370) */
 enum { BC_STORE_OVERWRITE = 0, BC_STORE_ACCUMULATE = 1, BC_STORE_SWIGLU = 2 };
@@ -100,8 +100,11 @@ bc_status bc_buffer_write(bc_buffer* buffer, size_t offset, const void* data, si
 bc_status bc_buffer_read(bc_buffer* buffer, size_t offset, void* out, size_t len);
 
 /* Convert a matrix of `format` from its GGUF byte layout (`data`, n_rows * row_bytes) into the
- * device layout the kernels read, in a new buffer. F32/F16 are copied unchanged. Q4_0 is split
- * into 16-byte quant groups followed by the fp16 scales; values are unchanged bit for bit.
+ * device layout the kernels read, in a new buffer. F32, F16, Q8_0 and Q6_K are copied unchanged.
+ * Q4_0 is split into 16-byte quant groups followed by the fp16 scales; values are unchanged bit
+ * for bit. (Q8_0 and Q6_K - the embedding type of the published Q4_0 files,
+ * crates/bobcat/tests/lfm2_reference.rs:39 - run on the general kernels: every op takes them, at a
+ * lower rate than Q4_0.)
  * No reference counterpart by name: the reference reads the mapped file in place
  * (crates/bobcat/src/lfm2_metal.rs:137-146); a discrete GPU uploads once instead. */
 bc_status bc_matrix_upload(bc_backend* backend, int32_t format, const void* data, uint32_t n_rows,

@@ -79,7 +79,7 @@ def default_threads() -> int:
 # scalar ops
 # ---------------------------------------------------------------------------------------------
 
-TYPE_IDS = {"F32": 0, "F16": 1, "Q4_0": 2, "Q8_0": 8, "BF16": 30}
+TYPE_IDS = {"F32": 0, "F16": 1, "Q4_0": 2, "Q8_0": 8, "Q6_K": 14, "BF16": 30}
 
 
 def dequantize(type_id: int, raw: np.ndarray, n: int) -> np.ndarray:

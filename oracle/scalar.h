@@ -19,7 +19,7 @@
 namespace oracle {
 
 // ggml tensor type ids the reference reads (crates/bobcat-gguf/src/lib.rs:126-152).
-enum : uint32_t { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q8_0 = 8, T_BF16 = 30 };
+enum : uint32_t { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q8_0 = 8, T_Q6K = 14, T_BF16 = 30 };
 
 // Elements and bytes of one block of `type` (crates/bobcat-gguf/src/lib.rs:156-166).
 inline bool block_of(uint32_t type, size_t* elements, size_t* bytes) {
@@ -28,6 +28,7 @@ inline bool block_of(uint32_t type, size_t* elements, size_t* bytes) {
         case T_F16: case T_BF16: *elements = 1; *bytes = 2; return true;
         case T_Q4_0: *elements = 32; *bytes = 18; return true;
         case T_Q8_0: *elements = 32; *bytes = 34; return true;
+        case T_Q6K: *elements = 256; *bytes = 210; return true;
         default: return false;
     }
 }
@@ -92,6 +93,28 @@ inline void dequantize_q8_0(const uint8_t* block, float* out) {
     for (int i = 0; i < 32; ++i) out[i] = (float)(int8_t)block[2 + i] * d;
 }
 
+// scalar.rs:175-202 — a super-block of 256: 128 bytes of low 4-bit halves, 64 bytes of high 2-bit
+// pairs, 16 int8 scales of 16-element blocks, then an fp16 d. Each half spreads 128 elements over
+// 64 low bytes and 32 high bytes; value = (d * f32(scale)) * f32(quant - 32).
+inline void dequantize_q6k(const uint8_t* block, float* out) {
+    float d = f16_to_f32(le16(block + 208));
+    for (int half = 0; half < 2; ++half) {
+        const uint8_t* low = block + half * 64;
+        const uint8_t* high = block + 128 + half * 32;
+        const int8_t* scales = reinterpret_cast<const int8_t*>(block + 192 + half * 8);
+        float* o = out + half * 128;
+        for (int l = 0; l < 32; ++l) {
+            int is = l / 16;
+            auto quant = [&](uint8_t lo, int shift) { return (float)((int16_t)(lo | (((high[l] >> shift) & 3) << 4)) - 32); };
+            auto scale = [&](int index) { return d * (float)scales[index]; };
+            o[l] = scale(is) * quant(low[l] & 0xf, 0);
+            o[l + 32] = scale(is + 2) * quant(low[l + 32] & 0xf, 2);
+            o[l + 64] = scale(is + 4) * quant(low[l] >> 4, 4);
+            o[l + 96] = scale(is + 6) * quant(low[l + 32] >> 4, 6);
+        }
+    }
+}
+
 // scalar.rs:59-82 — `n` elements of `type` from `bytes` into `out`.
 inline void dequantize(uint32_t type, const uint8_t* bytes, size_t n, float* out) {
     switch (type) {
@@ -100,6 +123,7 @@ inline void dequantize(uint32_t type, const uint8_t* bytes, size_t n, float* out
         case T_BF16: for (size_t i = 0; i < n; ++i) out[i] = bf16_to_f32(le16(bytes + 2 * i)); break;
         case T_Q4_0: for (size_t b = 0; b < n / 32; ++b) dequantize_q4_0(bytes + 18 * b, out + 32 * b); break;
         case T_Q8_0: for (size_t b = 0; b < n / 32; ++b) dequantize_q8_0(bytes + 34 * b, out + 32 * b); break;
+        case T_Q6K: for (size_t b = 0; b < n / 256; ++b) dequantize_q6k(bytes + 210 * b, out + 256 * b); break;
         default: break;
     }
 }

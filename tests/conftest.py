@@ -86,3 +86,24 @@ def random_q4_0(rng: np.random.Generator, n_rows: int, n_cols: int) -> np.ndarra
     blocks[:, :, 1] = bits >> 8
     blocks[:, :, 2:] = rng.integers(0, 256, size=(n_rows, nb, 16), dtype=np.uint8)
     return blocks.reshape(n_rows, nb * 18)
+
+
+def random_q8_0(rng: np.random.Generator, n_rows: int, n_cols: int) -> np.ndarray:
+    """Random Q8_0 rows: fp16 scales in [2^-10, 2^-6), random int8 quants, as bytes [n_rows, n_cols/32*34]."""
+    nb = n_cols // 32
+    blocks = np.zeros((n_rows, nb, 34), dtype=np.uint8)
+    bits = (rng.integers(5, 9, size=(n_rows, nb)) << 10) | rng.integers(0, 1024, size=(n_rows, nb)) | (rng.integers(0, 2, size=(n_rows, nb)) << 15)
+    blocks[:, :, 0] = bits & 0xFF
+    blocks[:, :, 1] = bits >> 8
+    blocks[:, :, 2:] = rng.integers(0, 256, size=(n_rows, nb, 32), dtype=np.uint8)
+    return blocks.reshape(n_rows, nb * 34)
+
+
+def random_q6k(rng: np.random.Generator, n_rows: int, n_cols: int) -> np.ndarray:
+    """Random Q6_K rows: random quant bits and int8 scales, fp16 d in [2^-14, 2^-10), as bytes [n_rows, n_cols/256*210]."""
+    nb = n_cols // 256
+    blocks = rng.integers(0, 256, size=(n_rows, nb, 210), dtype=np.uint8)
+    bits = (rng.integers(1, 5, size=(n_rows, nb)) << 10) | rng.integers(0, 1024, size=(n_rows, nb)) | (rng.integers(0, 2, size=(n_rows, nb)) << 15)
+    blocks[:, :, 208] = bits & 0xFF
+    blocks[:, :, 209] = bits >> 8
+    return blocks.reshape(n_rows, nb * 210)

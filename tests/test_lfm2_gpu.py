@@ -122,6 +122,25 @@ def test_greedy_tokens_match(pair, cuda):
     assert seq.n_past() == 104
 
 
+def test_quantised_embedding_matrix(model_path, cuda):
+    """A file whose embedding / output matrix is Q8_0 (quantised checkpoints keep it quantised,
+    lfm2_reference.rs:39) loads and decodes as the checker does."""
+    path = model_path("lfm2-tiny-q8")
+    model, ref = Model.load(path), oracle.Model(path)
+    hp = model.hyperparameters()
+    tokens = prompt_tokens(hp.n_vocab, 30, seed=8)
+    want, want_logits = oracle.greedy(ref, tokens, 24, n_ctx=64)
+    seq = Lfm2Cuda(model, cuda, 64, kv_half=False)
+    logits = np.zeros(hp.n_vocab, dtype=np.float32)
+    seq.prefill(tokens, logits)
+    assert rel_error(logits, want_logits) < HALF_TOLERANCE
+    assert seq.generate(24).tolist() == want
+    steps = Lfm2Cuda(model, cuda, 64, kv_half=False)
+    for tok in tokens:
+        steps.step(int(tok), logits)
+    assert rel_error(logits, want_logits) < STEP_TOLERANCE
+
+
 def test_reset_matches_a_fresh_state(pair, cuda):
     model, _ = pair
     hp = model.hyperparameters()

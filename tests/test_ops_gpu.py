@@ -467,3 +467,53 @@ def test_argmax_readback_slots(cuda):
     with pytest.raises(errors.OutOfBounds):
         cuda.read_readback(rb, 0)
     rb.close()
+
+
+@pytest.mark.parametrize("fmt", ["Q8_0", "Q6_K"])
+def test_byte_layout_formats(cuda, fmt):
+    """Q8_0 and Q6_K (the embedding type of the published Q4_0 files, lfm2_reference.rs:39) through
+    every op that takes a matrix: dequantisation and embedding rows bit for bit
+    (scalar.rs:108-113, :175-202), the decode products in their three forms and the batched product
+    at the matvec tolerance."""
+    from bobcat_b200 import Q6_K, Q8_0
+    from conftest import random_q6k, random_q8_0
+    rng = np.random.default_rng(17)
+    fid, make, type_id = (Q8_0, random_q8_0, 8) if fmt == "Q8_0" else (Q6_K, random_q6k, 14)
+    n_rows, n_cols = 200, 512
+    raw = make(rng, n_rows, n_cols)
+    w = oracle.dequantize(type_id, raw, n_rows * n_cols).reshape(n_rows, n_cols)
+    wb = cuda.upload_matrix(fid, raw, n_rows, n_cols)
+    out = cuda.new_buffer(n_rows * n_cols * 4)
+    cuda.begin(); cuda.expand(fid, wb, out, n_rows, n_cols, out_half=False); cuda.end()
+    got = cuda.read(out, np.zeros((n_rows, n_cols), dtype=np.float32))
+    assert np.array_equal(got.view(np.uint32), w.view(np.uint32))
+    tokens = np.array([0, 199, 17, 17, 123], dtype=np.uint32)
+    tb, eb = cuda.buffer_from(tokens), cuda.new_buffer(tokens.size * n_cols * 4)
+    cuda.begin(); cuda.embed(fid, wb, n_rows, tb, eb, n_cols, tokens.size); cuda.end()
+    assert np.array_equal(cuda.read(eb, np.zeros((tokens.size, n_cols), dtype=np.float32)), w[tokens])
+    # matvec: plain, with a fused norm, accumulating
+    x = rng.uniform(-1, 1, n_cols).astype(np.float32)
+    nw = rng.uniform(0.5, 1.5, n_cols).astype(np.float32)
+    xb, nb, yb = cuda.buffer_from(x), cuda.buffer_from(nw), cuda.new_buffer(n_rows * 4)
+    cuda.begin(); cuda.matvec(fid, wb, n_rows, n_cols, xb, yb); cuda.end()
+    y = cuda.read(yb, np.zeros(n_rows, dtype=np.float32))
+    assert scaled_error(y, oracle.matvec(type_id, raw, x, n_rows), w, x) < 1e-5
+    cuda.begin(); cuda.matvec(fid, wb, n_rows, n_cols, xb, yb, Norm(nb.at(0), 1e-5), accumulate=True); cuda.end()
+    xn = oracle.rms_norm(x, nw, 1e-5)
+    y2 = cuda.read(yb, np.zeros(n_rows, dtype=np.float32))
+    assert scaled_error(y2 - y, oracle.matvec(type_id, raw, xn, n_rows), w, xn) < 1e-5
+    # SwiGLU of a gate / up pair
+    raw_up = make(rng, n_rows, n_cols)
+    ub = cuda.upload_matrix(fid, raw_up, n_rows, n_cols)
+    cuda.begin(); cuda.matvec_swiglu(fid, wb, ub, n_rows, n_cols, xb, Norm(nb.at(0), 1e-5), yb); cuda.end()
+    g, u = oracle.matvec(type_id, raw, xn, n_rows), oracle.matvec(type_id, raw_up, xn, n_rows)
+    want = g / (1 + np.exp(-g.astype(np.float64))) * u
+    assert np.abs(cuda.read(yb, np.zeros(n_rows, dtype=np.float32)) - want).max() < 1e-4 * max(1.0, float(np.abs(want).max()))
+    # batched product
+    xt = rng.uniform(-1, 1, (9, n_cols)).astype(np.float32)
+    xtb, ytb = cuda.buffer_from(xt), cuda.new_buffer(9 * n_rows * 4)
+    cuda.begin(); cuda.matmul(fid, wb, n_rows, n_cols, xtb, ytb, 9, OVERWRITE); cuda.end()
+    yt = cuda.read(ytb, np.zeros((9, n_rows), dtype=np.float32))
+    exact = xt.astype(np.float64) @ w.astype(np.float64).T
+    budget = np.abs(xt.astype(np.float64)) @ np.abs(w.astype(np.float64)).T
+    assert float((np.abs(yt - exact) / np.maximum(budget, 1e-30)).max()) < MATMUL_TOLERANCE

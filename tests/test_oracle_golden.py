@@ -95,3 +95,15 @@ def test_route_picks_top_experts_with_ties_to_lower_ids():
     assert experts[:2].tolist() == [3, 1]
     s3, s1 = 1 / (1 + np.exp(1.0)), 1 / (1 + np.exp(-2.0))
     assert abs(scores[3] - s3 / (s3 + s1 + 1e-6)) < 1e-6
+
+
+def test_byte_layout_formats_match_the_gguf_package():
+    """Q8_0 and Q6_K dequantisation of the checker against the `gguf` package on random blocks, bit for bit."""
+    import gguf
+    from conftest import random_q6k, random_q8_0
+    rng = np.random.default_rng(5)
+    for name, make, qtype, cols in (("Q8_0", random_q8_0, gguf.GGMLQuantizationType.Q8_0, 256), ("Q6_K", random_q6k, gguf.GGMLQuantizationType.Q6_K, 512)):
+        raw = make(rng, 64, cols)
+        want = gguf.quants.dequantize(raw, qtype).astype(np.float32)
+        got = oracle.dequantize(oracle.TYPE_IDS[name], raw, 64 * cols).reshape(64, cols)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), name
