@@ -8,9 +8,9 @@ path: every class here needs the shared library and a CUDA device.
 
 from . import errors
 from .backend import ACCUMULATE, F16, F32, OVERWRITE, Q4_0, Q6_K, Q8_0, SWIGLU, Buffer, Cuda, Norm, View
-from .models import BatchCuda, Checkpoint, Lfm2Cuda, Model, Qwen35Cuda, SeqCuda, Trace
+from .models import BatchCuda, Checkpoint, Engine, Lfm2Cuda, Model, Qwen35Cuda, SeqCuda, Trace
 
 __all__ = [
-    "errors", "Cuda", "Buffer", "View", "Norm", "Model", "Trace", "Checkpoint", "SeqCuda", "Lfm2Cuda", "Qwen35Cuda", "BatchCuda",
+    "errors", "Cuda", "Buffer", "View", "Norm", "Model", "Trace", "Checkpoint", "SeqCuda", "Lfm2Cuda", "Qwen35Cuda", "BatchCuda", "Engine",
     "F32", "F16", "Q4_0", "Q8_0", "Q6_K", "OVERWRITE", "ACCUMULATE", "SWIGLU",
 ]

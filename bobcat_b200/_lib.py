@@ -135,6 +135,12 @@ SIGNATURES = {
     "bc_comm_world": (i32, [vp]),
     "bc_comm_collectives": (u64, [vp]),
     "bc_batch_new_expert_parallel": (i32, [vp, vp, vp, u32, u32, i32, C.POINTER(vp)]),
+    "bc_seq_step_on_device": (i32, [vp, u32]),
+    "bc_engine_new": (i32, [vp, vp, u32, i32, u64, C.POINTER(vp)]),
+    "bc_engine_free": (None, [vp]),
+    "bc_engine_generate": (i32, [vp, vp, sz, C.c_int64, u32, C.POINTER(Sampling), EMIT_FN, vp, vp, sz, C.POINTER(sz), C.POINTER(u32)]),
+    "bc_engine_score": (i32, [vp, vp, vp, sz, vp, vp, vp]),
+    "bc_engine_consumed": (u32, [vp]),
     "bc_seq_launches": (u64, [vp]),
     "bc_seq_set_skip": (i32, [vp, C.c_char_p, u32, u32]),
 }

@@ -373,7 +373,25 @@ void bc_seq_free(bc_seq* seq) { delete seq; }
 uint32_t bc_seq_n_past(const bc_seq* seq) { return seq ? seq->n_past : 0; }
 uint64_t bc_seq_launches(const bc_seq* seq) { return seq ? seq->launches : 0; }
 
+}  // extern "C"
+
+namespace {
+bc_status step_impl(bc_seq* s, uint32_t token, float* logits, size_t logits_len, bc_trace* trace, bool device_logits);
+}
+
+extern "C" {
+
 bc_status bc_seq_step(bc_seq* s, uint32_t token, float* logits, size_t logits_len, bc_trace* trace) {
+    return step_impl(s, token, logits, logits_len, trace, false);
+}
+
+bc_status bc_seq_step_on_device(bc_seq* s, uint32_t token) { return step_impl(s, token, nullptr, 0, nullptr, true); }
+
+}  // extern "C"
+
+namespace {
+
+bc_status step_impl(bc_seq* s, uint32_t token, float* logits, size_t logits_len, bc_trace* trace, bool device_logits) {
     if (!s || !s->backend) return fail(BC_ERR_ARGUMENT, "seq must be non-null and its backend open");
     const bc_hparams& hp = s->hp;
     uint32_t pos = s->n_past;
@@ -389,7 +407,7 @@ bc_status bc_seq_step(bc_seq* s, uint32_t token, float* logits, size_t logits_le
     auto encode_start = Clock::now();
     BC_TRY(timing_begin(s));
     Recorder r(*s);
-    r.step(pos, logits != nullptr, trace != nullptr);
+    r.step(pos, logits != nullptr || device_logits, trace != nullptr);
     double encode = since(encode_start);
     double gpu = 0;
     bc_status finish = timing_end(s, &gpu);
@@ -407,6 +425,10 @@ bc_status bc_seq_step(bc_seq* s, uint32_t token, float* logits, size_t logits_le
     s->last_gpu_seconds = gpu;
     return BC_OK;
 }
+
+}  // namespace
+
+extern "C" {
 
 bc_status bc_seq_prefill(bc_seq* s, const uint32_t* tokens, size_t n_tokens, float* logits, size_t logits_len, float* final_norm,
                          size_t final_norm_len, bc_trace* trace) {

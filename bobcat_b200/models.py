@@ -319,3 +319,62 @@ class BatchCuda:
             self.close()
         except Exception:
             pass
+
+
+
+class Engine:
+    """The token-level half of the reference's ``Engine`` (crates/bobcat-cli/src/engine.rs): a
+    sequence that reuses what earlier requests left on the device, and ``score``."""
+
+    def __init__(self, model: Model, cuda: Cuda, n_ctx: int, kv_half: bool = True, seed: int = 0):
+        self._L = _lib.load()
+        self.model, self.cuda = model, cuda
+        h = C.c_void_p()
+        errors.check(self._L.bc_engine_new(model._h, cuda._h, n_ctx, int(kv_half), seed, C.byref(h)), self._L)
+        self._h = h
+
+    def generate(self, tokens, max_tokens: int, turn: int = -1, sampling=None, emit=None) -> tuple[list[int], int]:
+        """Returns (generated tokens, prompt tokens that were already on the device)."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.uint32)
+        out = np.zeros(max(1, max_tokens), dtype=np.uint32)
+        n, cached = C.c_size_t(), C.c_uint32()
+        failure = []
+
+        def trampoline(token, _user):
+            try:
+                return 1 if emit(int(token)) else 0
+            except Exception as e:
+                failure.append(e)
+                return 0
+
+        cb = _lib.EMIT_FN(trampoline) if emit else C.cast(None, _lib.EMIT_FN)
+        errors.check(self._L.bc_engine_generate(self._h, tokens.ctypes.data_as(C.c_void_p), tokens.size, turn, max_tokens,
+                                                C.byref(sampling) if sampling is not None else None, cb, None,
+                                                out.ctypes.data_as(C.c_void_p), out.size, C.byref(n), C.byref(cached)), self._L)
+        if failure:
+            raise failure[0]
+        return out[: n.value].tolist(), int(cached.value)
+
+    def score(self, prompts, labels) -> list[list[float]]:
+        flat_p = np.concatenate([np.asarray(p, dtype=np.uint32) for p in prompts]) if prompts else np.zeros(0, dtype=np.uint32)
+        flat_l = np.concatenate([np.asarray(l, dtype=np.uint32) for l in labels] + [np.zeros(0, dtype=np.uint32)])
+        off_p = np.cumsum([0] + [len(p) for p in prompts]).astype(np.uint64)
+        off_l = np.cumsum([0] + [len(l) for l in labels]).astype(np.uint64)
+        scores = np.zeros(max(1, flat_l.size), dtype=np.float64)
+        ptr = lambda a: a.ctypes.data_as(C.c_void_p)
+        errors.check(self._L.bc_engine_score(self._h, ptr(flat_p), ptr(off_p), len(prompts), ptr(flat_l), ptr(off_l), ptr(scores)), self._L)
+        return [scores[int(off_l[i]):int(off_l[i + 1])].tolist() for i in range(len(prompts))]
+
+    def consumed(self) -> int:
+        return int(self._L.bc_engine_consumed(self._h))
+
+    def close(self) -> None:
+        if self._h:
+            self._L.bc_engine_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

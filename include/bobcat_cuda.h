@@ -386,6 +386,9 @@ bc_status bc_seq_generate_stream(bc_seq* seq, uint32_t max_tokens, bc_emit_fn em
  * token from the sequence's current logits with bc_op_sample's rules and return it. The caller
  * feeds it to bc_seq_step (with or without logits) to advance. */
 bc_status bc_seq_sample(bc_seq* seq, const bc_sampling* settings, float uniform, const uint32_t* recent, size_t n_recent, uint32_t* token);
+/* step (lfm2_metal.rs:308) whose logits are computed but stay on the device, for a following
+ * bc_seq_sample or bc_seq_greedy_token. */
+bc_status bc_seq_step_on_device(bc_seq* seq, uint32_t token);
 /* reset / checkpoint / restore (lfm2_metal.rs:238-288; qwen35_metal.rs:238-297). */
 bc_status bc_seq_reset(bc_seq* seq);
 bc_status bc_seq_checkpoint(bc_seq* seq, bc_checkpoint** out);
@@ -429,6 +432,37 @@ void bc_prefix_free(bc_prefix* prefix);
 uint32_t bc_prefix_n_past(const bc_prefix* prefix);
 /* last_encode_seconds / last_gpu_seconds (lfm2_metal.rs:223-230). */
 bc_status bc_seq_timings(const bc_seq* seq, double* encode_seconds, double* gpu_seconds);
+
+/* ============================================================================================
+ * Engine: one sequence plus the bookkeeping of the reference's engine that lets a request reuse
+ * what earlier requests left on the device (crates/bobcat-cli/src/engine.rs). Token ids in, token
+ * ids and numbers out: templates, tokenizer, stop strings and tool calls stay with the caller.
+ * ============================================================================================ */
+typedef struct bc_engine bc_engine;
+/* Engine::new's device half: a sequence of n_ctx positions; `seed` starts the stream of draws for
+ * sampled requests. */
+bc_status bc_engine_new(bc_model* model, bc_backend* backend, uint32_t n_ctx, int32_t kv_half, uint64_t seed, bc_engine** out);
+void bc_engine_free(bc_engine* engine);
+/* Engine::generate_inner (engine.rs:510-647) on the rendered prompt `tokens`. Tokens that extend
+ * what the sequence has consumed continue from there; tokens that extend the history recorded at
+ * the previous request's turn restore its checkpoint; anything else starts over. `turn` is the
+ * index of the prompt's last turn-opening token (the reply's turn; the prompt up to it becomes the
+ * next history), or -1. At most max_tokens tokens (and no more than the context holds) are
+ * generated: greedily through the pipelined stream when `sampling` is null or greedy, else picked
+ * on the device by bc_seq_sample's rules with draws from the engine's stream. `emit` (nullable)
+ * sees every token and returns zero to stop. out (capacity out_cap) receives the tokens, n_out
+ * their count, cached_tokens (nullable) how many prompt tokens were already on the device. */
+bc_status bc_engine_generate(bc_engine* engine, const uint32_t* tokens, size_t n_tokens, int64_t turn, uint32_t max_tokens,
+                             const bc_sampling* sampling, bc_emit_fn emit, void* user, uint32_t* out, size_t out_cap, size_t* n_out,
+                             uint32_t* cached_tokens);
+/* Engine::score (engine.rs:372-446): scores[t] = log-probability of label_tokens[t] after prompt i,
+ * for t in [label_offsets[i], label_offsets[i + 1]); prompt i is prompt_tokens[prompt_offsets[i] ..
+ * prompt_offsets[i + 1]). The prompts' longest common prefix runs once; every prompt continues
+ * from its checkpoint. The log-softmax is taken in f64 over the whole vocabulary. */
+bc_status bc_engine_score(bc_engine* engine, const uint32_t* prompt_tokens, const size_t* prompt_offsets, size_t n_prompts,
+                          const uint32_t* label_tokens, const size_t* label_offsets, double* scores);
+/* Tokens the engine's sequence currently holds. */
+uint32_t bc_engine_consumed(const bc_engine* engine);
 
 /* ============================================================================================
  * Batch: n_seqs independent sequences of one model decoding together, one token each per pass,
