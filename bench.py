@@ -336,6 +336,207 @@ def run_batch(args) -> None:
         dist.destroy_process_group()
 
 
+def sharded_blocks(args, cuda, rank, local_rank, world) -> dict:
+    """The two sharded configurations on the same ranks, each as a block beside the replica headline:
+    `ep` - 32 concurrent sequences of the LFM2.5-8B-A1B shape, experts sharded over the ranks
+    (256-token prompts, 128 greedy tokens each); `tp` - one Qwen3.5-9B-shaped sequence tensor-
+    parallel over the ranks (a 2048-token prompt in 512-token chunks, 128 greedy tokens; the
+    60 000-token protocol of that configuration is `--mode prefix`). Both are strong scaling: the
+    work is fixed and the ranks split it. At one GPU the same code runs unsharded, which gives the
+    efficiency its denominator."""
+    import torch
+    import torch.distributed as dist
+
+    from bobcat_b200 import BatchCuda, Model, Qwen35Cuda, replicas
+    from bobcat_b200.sharding import COMM_ID_BYTES, Comm
+
+    def comm_for():
+        if world == 1:
+            return None
+        raw = torch.zeros(COMM_ID_BYTES, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            raw = torch.tensor(list(Comm.unique_id()), dtype=torch.uint8, device="cuda")
+        dist.broadcast(raw, 0)
+        return Comm(cuda, bytes(raw.cpu().tolist()), rank, world)
+
+    def shared_file(config):
+        if rank == 0:
+            model_file(config)
+        if world > 1:
+            dist.barrier()
+        return model_file(config)
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        return [fn() for _ in range(reps)]
+
+    blocks = {}
+    # ---- expert parallel
+    try:
+        n_total, n_prompt, n_decode = 32, 256, 128
+        if n_total % world == 0:
+            model = Model.load(shared_file("lfm2moe-8b-a1b"))
+            hp = model.hyperparameters()
+            comm = comm_for()
+            n_local = n_total // world
+            batch = BatchCuda(model, cuda, n_local, max(n_prompt + n_decode, n_total), True, comm=comm)
+            prompts = [np.random.default_rng(100 + rank * n_local + i).integers(0, hp.n_vocab, n_prompt).astype(np.uint32) for i in range(n_local)]
+
+            def ep_request():
+                for i in range(n_local):
+                    batch.seq(i).reset()
+                    batch.seq(i).prefill(prompts[i])
+                tokens = batch.generate(n_decode)
+                return batch.last_gpu_seconds(), tokens
+
+            rows = timed(ep_request, 2)
+            seconds = replicas.max_over_ranks([float(np.mean([r[0] for r in rows]))], device="cuda")[0]
+            blocks["ep"] = {"config": "lfm2moe-8b-a1b, %d concurrent sequences in all (%d per rank), %d-token prompts, %d greedy tokens each, experts %d per rank" %
+                                      (n_total, n_local, n_prompt, n_decode, hp.n_experts // world),
+                            "scaling": "strong", "n_gpus": world, "tok_s": n_total * n_decode / seconds, "ms_per_pass": 1e3 * seconds / n_decode,
+                            "collectives_per_pass": (comm.collectives() // (3 * n_decode)) if comm else 0,
+                            "token_hash_rank0": replicas.token_hash(rows[-1][1].ravel().tolist())}
+            batch.close()
+            if comm:
+                comm.close()
+            model.close()
+    except Exception as e:  # a block that cannot run must not take the headline with it
+        blocks["ep"] = {"error": "%s: %s" % (type(e).__name__, e)}
+    # ---- tensor parallel
+    try:
+        n_prompt, n_decode, chunk = 2048, 128, 512
+        model = Model.load(shared_file("qwen35-9b"))
+        hp = model.hyperparameters()
+        comm = comm_for()
+        seq = Qwen35Cuda(model, cuda, n_prompt + n_decode, True, comm=comm)
+        prompt = np.random.default_rng(200).integers(0, hp.n_vocab, n_prompt).astype(np.uint32)
+
+        def tp_request():
+            seq.reset()
+            prefill = 0.0
+            for first in range(0, n_prompt, chunk):
+                seq.prefill(prompt[first:first + chunk])
+                prefill += seq.last_gpu_seconds()
+            tokens = seq.generate(n_decode)
+            return prefill, seq.last_gpu_seconds(), tokens
+
+        rows = timed(tp_request, 2)
+        prefill_s, decode_s = replicas.max_over_ranks([float(np.mean([r[0] for r in rows])), float(np.mean([r[1] for r in rows]))], device="cuda")
+        blocks["tp"] = {"config": "qwen35-9b, one sequence, %d-token prompt in chunks of %d, %d greedy tokens" % (n_prompt, chunk, n_decode),
+                        "scaling": "strong", "n_gpus": world, "decode_tok_s": n_decode / decode_s, "prefill_tok_s": n_prompt / prefill_s,
+                        "ms_per_token": 1e3 * decode_s / n_decode, "token_hash_rank0": replicas.token_hash(rows[-1][2].tolist())}
+        seq.close()
+        if comm:
+            comm.close()
+        model.close()
+    except Exception as e:
+        blocks["tp"] = {"error": "%s: %s" % (type(e).__name__, e)}
+    return blocks
+
+
+def run_prefix(args) -> None:
+    """--mode prefix: the long-context protocol with a cached prefix. One shared prefix is prefilled
+    in 512-token chunks and cached; then 8 requests each load it, append their own suffix and decode.
+    Defaults are the Qwen3.5-9B configuration's (60 000 + 8 x (4096 + 256)); --prefix-tokens,
+    --prompt-tokens (the suffix) and --decode-tokens scale it down. One GPU: paged caches, the
+    prefix's full pages mapped, not copied. Several GPUs: the sequence is tensor-parallel and every
+    rank caches its own share. `value` is decode tokens per second over the 8 requests."""
+    import torch
+    import torch.distributed as dist
+
+    from bobcat_b200 import Cuda, Model, Qwen35Cuda, replicas
+    from bobcat_b200.sharding import COMM_ID_BYTES, Comm
+
+    rank, local_rank, world = rank_info()
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    config = args.config if args.config.startswith("qwen") else "qwen35-9b"
+    if rank == 0:
+        model_file(config)
+    if world > 1:
+        dist.barrier()
+    model = Model.load(model_file(config))
+    hp = model.hyperparameters()
+    torch.cuda.set_stream(torch.cuda.Stream())
+    cuda = Cuda.open(local_rank, torch.cuda.current_stream().cuda_stream)
+    comm = None
+    if world > 1:
+        raw = torch.zeros(COMM_ID_BYTES, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            raw = torch.tensor(list(Comm.unique_id()), dtype=torch.uint8, device="cuda")
+        dist.broadcast(raw, 0)
+        comm = Comm(cuda, bytes(raw.cpu().tolist()), rank, world)
+    n_prefix, n_suffix, n_decode, n_requests, chunk = args.prefix_tokens, args.prompt_tokens or 4096, args.decode_tokens or 256, 8, 512
+    n_ctx = n_prefix + n_suffix + n_decode
+    rng = np.random.default_rng(1)
+    prefix_tokens = rng.integers(0, hp.n_vocab, n_prefix).astype(np.uint32)
+    suffixes = [np.random.default_rng(10 + i).integers(0, hp.n_vocab, n_suffix).astype(np.uint32) for i in range(n_requests)]
+
+    def new_seq():
+        return Qwen35Cuda(model, cuda, n_ctx, True, comm=comm, paged=comm is None)
+
+    def prefill(seq, tokens):
+        seconds = 0.0
+        for first in range(0, len(tokens), chunk):
+            seq.prefill(tokens[first:first + chunk])
+            seconds += seq.last_gpu_seconds()
+        return seconds
+
+    source = new_seq()
+    t0 = time.perf_counter()
+    prefix_seconds = prefill(source, prefix_tokens)
+    prefix = source.save_prefix()
+    source.close()
+    seq = new_seq()
+    suffix_seconds = decode_seconds = load_seconds = 0.0
+    hashes = []
+    shared = 0
+    for suffix in suffixes:
+        t1 = time.perf_counter()
+        seq.load_prefix(prefix)
+        load_seconds += time.perf_counter() - t1
+        shared = seq.kv_pages()[2]
+        suffix_seconds += prefill(seq, suffix)
+        tokens = seq.generate(n_decode)
+        decode_seconds += seq.last_gpu_seconds()
+        hashes.append(replicas.token_hash(tokens.tolist()))
+    wall = time.perf_counter() - t0
+    prefix_seconds, suffix_seconds, decode_seconds = replicas.max_over_ranks([prefix_seconds, suffix_seconds, decode_seconds], device="cuda")
+    if rank == 0:
+        peak, _, peak_kind = measured_peaks()
+        value = n_requests * n_decode / decode_seconds
+        kv_row_bytes = hp.n_attention_layers * 2 * hp.n_kv_heads * hp.head_dim * 2
+        token_bytes = model.decode_bytes() + kv_row_bytes * (n_prefix + n_suffix + n_decode / 2) + hp.n_delta_layers * hp.n_v_heads * hp.k_head_dim * hp.v_head_dim * 8
+        line = {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": 1, "warmup": 0, "ms_per_step": 1e3 * wall, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32 activations, Q4_0 weights, f16 KV", "data": "synthetic",
+            "config": {"workload": "%s Q4_0, one %d-token shared prefix prefilled in %d-token chunks and cached, then %d requests of a %d-token suffix and %d greedy "
+                                   "tokens each from the cached prefix; %s" % (config, n_prefix, chunk, n_requests, n_suffix, n_decode,
+                                   "tensor-parallel over %d GPUs" % world if world > 1 else "one GPU, paged KV caches"),
+                       "kv_cache": "f16"},
+            "prefix": {"prefill_tok_s": n_prefix / prefix_seconds, "suffix_prefill_tok_s": n_requests * n_suffix / suffix_seconds, "load_ms_per_request": 1e3 * load_seconds / n_requests,
+                       "kv_pages_shared_per_request": shared, "token_hashes": hashes},
+            "decode": {"tok_s": value, "ms_per_token": 1e3 * decode_seconds / (n_requests * n_decode), "bytes_per_token": token_bytes / world,
+                       "hbm_frac_per_gpu": token_bytes / world * n_requests * n_decode / decode_seconds / 1e9 / peak},
+            "roofline": {"bound": "hbm", "kernel": "whole decode step at the long context", "achieved": token_bytes / world * n_requests * n_decode / decode_seconds / 1e9,
+                         "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": token_bytes / world * n_requests * n_decode / decode_seconds / 1e9 / peak, "traffic": None},
+            "e2e": {"value": n_requests * n_decode / (wall - 0.0), "unit": "tok/s (decode tokens over the whole job's wall time)", "h2d_bytes_per_step": (n_prefix + n_requests * n_suffix) * 4,
+                    "d2h_bytes_per_step": n_requests * n_decode * 4},
+            "gpu_launches": seq.launches(),
+        }
+        print(json.dumps(line))
+    seq.close()
+    if comm:
+        comm.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -430,6 +631,9 @@ def run_ours(args) -> None:
         if not replica_check["identical_on_all_ranks"]:
             raise SystemExit("request 0 decoded to different tokens on different ranks")
 
+    # The sharded configurations ride along as blocks (every rank takes part; rank 0 reports).
+    sharded = {} if args.no_sharded else sharded_blocks(args, cuda, rank, local_rank, world)
+
     if rank == 0:
         peak, tensor_peak, peak_kind = measured_peaks()
         weight_bytes = model.decode_bytes()
@@ -478,6 +682,7 @@ def run_ours(args) -> None:
         }
         if replica_check is not None:
             line["replica_check"] = replica_check
+        line.update(sharded)
         if cpu_rate is not None:
             line["cpu_baseline"] = {"value": cpu_rate, "unit": "tok/s", "cores": 1, "kind": "port",
                                     "sample": "2-token prompt then 4 greedy decode steps of the scalar restatement, single thread (%.1f s)" % cpu_seconds}
@@ -496,9 +701,12 @@ def main() -> None:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--config", default="lfm2-2.6b")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-sharded", action="store_true", help="leave out the expert-parallel and tensor-parallel blocks")
     parser.add_argument("--prompt-tokens", type=int, default=0, help="shorter requests, for profiler captures only (0: the configuration's own)")
     parser.add_argument("--decode-tokens", type=int, default=0)
     parser.add_argument("--prefill-chunk", type=int, default=0)
+    parser.add_argument("--mode", default="request", choices=["request", "prefix"], help="prefix: the long-context protocol with a cached prefix")
+    parser.add_argument("--prefix-tokens", type=int, default=60000)
     parser.add_argument("--seqs", type=int, default=1, help="concurrent sequences per GPU (the multi-sequence decode when > 1)")
     args = parser.parse_args()
     protocol = PROTOCOLS.get(args.config, (512, 128, 512))
@@ -508,6 +716,8 @@ def main() -> None:
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.mode == "prefix":
+        run_prefix(args)
     elif args.seqs > 1:
         run_batch(args)
     else:

@@ -21,6 +21,10 @@ namespace {
 
 constexpr int kChunk = 64;         // positions per chunk of a batch
 constexpr int kDecodeChunk = 16;   // positions per chunk when only a few queries run: more, smaller CTAs fill the device
+// Longer contexts take longer chunks: the chunk count (and with it the partials the combine pass
+// reads back, head_dim + 2 floats per chunk and head) stays a small fraction of the cache traffic,
+// and a replayed step, whose grid covers the whole context, launches a few thousand CTAs at most.
+inline uint32_t decode_chunk(uint32_t n_ctx) { return n_ctx <= 4096 ? (uint32_t)kDecodeChunk : n_ctx <= 32768 ? 64u : 256u; }
 constexpr int kDecodeQueries = 4;  // up to this many queries use the small chunks
 constexpr int kMaxGroup = 8;       // query heads per KV head
 constexpr int kQueryBatch = 64;    // queries per launch, which bounds the scratch
@@ -525,7 +529,7 @@ cudaError_t attention(cudaStream_t stream, const float* q, const void* k_cache, 
     const bool flash_aligned = ((uintptr_t)q | (uintptr_t)out) % 8 == 0 && ((uintptr_t)k_cache | (uintptr_t)v_cache) % 16 == 0;
     if (flash_aligned && attention_flash_supported(kv_half, s)) return attention_flash(stream, q, k_cache, v_cache, out, s);
     const uint32_t group = s.n_heads / s.n_kv_heads;
-    const uint32_t chunk = s.n_queries <= (uint32_t)kDecodeQueries ? kDecodeChunk : kChunk;
+    const uint32_t chunk = s.n_queries <= (uint32_t)kDecodeQueries ? decode_chunk(s.n_ctx) : (uint32_t)kChunk;
     const uint32_t max_chunks = (s.n_ctx + chunk - 1) / chunk;
     const uint32_t n_slices = kChunkThreads / s.head_dim;
     size_t smem = ((size_t)group * s.head_dim + (size_t)group * chunk + (size_t)n_slices * group * s.head_dim) * sizeof(float);
@@ -563,7 +567,7 @@ bool attention_step_supported(const RopeStore& r, const AttentionShape& s) {
 }
 
 cudaError_t attention_step(cudaStream_t stream, const RopeStore& r, float* scratch, float* out, const AttentionShape& s) {
-    const uint32_t chunk = kDecodeChunk, max_chunks = (s.n_ctx + chunk - 1) / chunk;
+    const uint32_t chunk = decode_chunk(s.n_ctx), max_chunks = (s.n_ctx + chunk - 1) / chunk;
     ChunkParams cp{r.q, r.k_cache, r.v_cache, scratch, s.n_heads, s.n_kv_heads, s.head_dim, s.first_pos, s.n_ctx,
                    s.q_stride, s.q_head_stride, 0, max_chunks, s.pos_ptr, chunk, r.k, r.v, r.q_norm, r.k_norm, r.eps, r.theta, r.table};
     dim3 grid(s.n_kv_heads, s.pos_ptr ? max_chunks : s.first_pos / chunk + 1, 1);

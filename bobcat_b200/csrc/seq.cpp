@@ -694,7 +694,7 @@ void bc_checkpoint_free(bc_checkpoint* c) { delete c; }
 bc_status bc_seq_prefix_save(bc_seq* s, bc_prefix** out) {
     if (!s || !s->backend || !out) return fail(BC_ERR_ARGUMENT, "seq and out must be non-null and the backend open");
     if (s->n_past == 0) return fail(BC_ERR_ARGUMENT, "a prefix holds at least one token");
-    if (s->tp) return fail(BC_ERR_UNSUPPORTED, "prefixes of tensor-parallel sequences");
+    // A tensor-parallel rank saves its own share (its heads' rows and state); every rank does the same.
     BC_TRY(s->backend->activate());
     cudaStream_t stream = s->backend->stream;
     const bc_hparams& hp = s->hp;
@@ -748,7 +748,8 @@ bc_status bc_seq_prefix_save(bc_seq* s, bc_prefix** out) {
 
 bc_status bc_seq_prefix_load(bc_seq* s, const bc_prefix* p) {
     if (!s || !s->backend || !p) return fail(BC_ERR_ARGUMENT, "seq and prefix must be non-null and the backend open");
-    if (s->tp) return fail(BC_ERR_UNSUPPORTED, "prefixes of tensor-parallel sequences");
+    if (p->hp.n_kv_heads != s->hp.n_kv_heads || p->hp.n_v_heads != s->hp.n_v_heads)
+        return fail(BC_ERR_ARGUMENT, "the prefix comes from another tensor-parallel split");
     if (p->model != s->model || p->device != s->backend->device || p->kv_half != s->kv_half || p->conv_floats != s->conv_floats ||
         p->delta_floats != s->delta_floats)
         return fail(BC_ERR_ARGUMENT, "the prefix comes from a different model, device or cache type");

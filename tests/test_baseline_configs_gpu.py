@@ -166,6 +166,28 @@ def test_qwen35_2b_request(model_path, cuda):
         seq.close()
 
 
+def test_qwen35_9b_short_request(model_path, cuda):
+    """Config 5's model (hidden 4096, 32 layers, 16 query / 4 KV heads of 256, vocabulary 151 936) at
+    a length the checker finishes in seconds: 8-token prompt on the single-step path, 8 greedy tokens."""
+    path = model_path("qwen35-9b")
+    model, ref = Model.load(path), oracle.Model(path)
+    hp = model.hyperparameters()
+    prompt = np.random.default_rng(1).integers(0, hp.n_vocab, size=8).astype(np.uint32)
+    want_tokens, want_logits, want_layers, _ = checker_run(ref, prompt, 8, want_trace=True)
+    steps = Qwen35Cuda(model, cuda, 32, kv_half=True)
+    logits = np.zeros(hp.n_vocab, dtype=np.float32)
+    worst = 0.0
+    for t, tok in enumerate(prompt):
+        one = model.trace(1)
+        steps.step(int(tok), logits, one)
+        worst = max(worst, max(rel_error(one.layers[il, 0], want_layers[t][il]) for il in range(hp.n_layers)))
+    note(test="qwen35-9b layers, stepped, f16 cache", worst_rel_error=worst)
+    assert worst < LAYER_TOLERANCE
+    assert_logits(logits, want_logits[0], "qwen35-9b stepped prompt")
+    assert_same_tokens(steps.generate(8), want_tokens, want_logits, "qwen35-9b 8+8")
+    steps.close()
+
+
 def test_lfm2moe_8b_a1b_request_and_expert_ids(model_path, cuda):
     """Config 4's model: on the single-step path the expert ids of every mixture-of-experts layer
     equal the checker's for every prompt token; then 40 greedy tokens."""
