@@ -182,6 +182,7 @@ def dominant_kernel(cuda, seq, prompt) -> dict:
     def rows_of(entries, count):
         total = sum(e["seconds"] for e in entries) or 1.0
         return [{"kernel": e["name"], "rows": e["n_rows"], "cols": e["n_cols"], "calls": e["calls"], "us": 1e6 * e["seconds"] / e["calls"],
+                 "bytes_per_launch": e["bytes"] / e["calls"],
                  "gbs": (e["bytes"] / e["seconds"] / 1e9) if e["seconds"] else 0.0, "share": e["seconds"] / total}
                 for e in sorted(entries, key=lambda e: -e["seconds"])[:count]]
 
@@ -652,8 +653,20 @@ def run_ours(args) -> None:
             token_hash = (token_hash * 1000003 + tok) & 0xFFFFFFFFFFFFFFFF
         dom = dominant_kernel(cuda, seq, prompt)
         in_graph = in_graph_costs(seq, prompt, dom["table"], dom["all"])
-        achieved = dom["bytes"] / dom["seconds"] / 1e9
-        top_key = "%s %dx%d" % (dom["top"]["name"], dom["top"]["n_rows"], dom["top"]["n_cols"])
+        # The dominant kernel is the one with the largest share of the replayed step, and its
+        # duration is what a launch of it costs there (launches overlap their neighbours, which a
+        # serialised per-launch timing cannot see); the serialised figure rides along.
+        costed = [r for r in in_graph if r["us"] and r["us"] > 0]
+        top_row = max(costed, key=lambda r: r["us"] * r["calls_per_token"]) if costed else None
+        serial = next((r for r in dom["all"] if top_row and (r["kernel"], r["rows"], r["cols"]) == (top_row["kernel"], top_row["rows"], top_row["cols"])), None)
+        if top_row and serial and serial["bytes_per_launch"]:
+            top_key = "%s %dx%d" % (top_row["kernel"], top_row["rows"], top_row["cols"])
+            launch_bytes, launch_us, serial_us = serial["bytes_per_launch"], top_row["us"], serial["us"]
+            share = top_row["us"] * top_row["calls_per_token"] / sum(r["us"] * r["calls_per_token"] for r in costed)
+        else:
+            top_key = "%s %dx%d" % (dom["top"]["name"], dom["top"]["n_rows"], dom["top"]["n_cols"])
+            launch_bytes, launch_us, serial_us, share = dom["bytes"], 1e6 * dom["seconds"], 1e6 * dom["seconds"], dom["share"]
+        achieved = launch_bytes / (launch_us * 1e-6) / 1e9
         cpu_rate, cpu_seconds = cpu_sample(path, 1, 2, 4) if world == 1 and not args.no_cpu_baseline else (None, None)
         line = {
             "metric": METRIC, "value": decode_tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -670,11 +683,13 @@ def run_ours(args) -> None:
             "prefill": {"tok_s": prefill_tok_s, "ttft_ms": 1e3 * prefill_gpu, "tokens": PROMPT_TOKENS, "tflops": prefill_tflops,
                         "tensor_peak_tflops": tensor_peak, "tensor_frac": prefill_tflops / tensor_peak,
                         "weights_pass_ms": 1e3 * (weight_bytes - hp.n_vocab * hp.n_embd * 4) / (peak * 1e9), "kernels": dom["prefill_table"]},
-            "roofline": {"bound": "hbm", "kernel": "%s %dx%d" % (dom["top"]["name"], dom["top"]["n_rows"], dom["top"]["n_cols"]),
+            "roofline": {"bound": "hbm", "kernel": top_key,
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                         "timing": "duration of one launch inside the replayed decode step: the step re-captured without this kernel, difference in CUDA-event time per token over its launches per token",
                          "traffic": recorded_traffic(top_key), "traffic_source": "ncu summary under profiles/ (recorded, not captured in this run)",
-                         "share_of_decode": dom["share"], "launch_us": 1e6 * dom["seconds"], "bytes_per_launch": dom["bytes"], "kernels": dom["table"],
-                         "in_graph_us": in_graph},
+                         "share_of_decode": share, "launch_us": launch_us, "bytes_per_launch": launch_bytes,
+                         "launch_us_serialised": serial_us, "frac_serialised": launch_bytes / (serial_us * 1e-6) / 1e9 / peak,
+                         "kernels": dom["table"], "in_graph_us": in_graph},
             "e2e": {"value": world * DECODE_TOKENS / decode_wall, "unit": "tok/s", "h2d_bytes_per_step": PROMPT_TOKENS * 4,
                     "d2h_bytes_per_step": DECODE_TOKENS * 4, "prefill_tok_s": world * PROMPT_TOKENS / prefill_wall},
             "gpu_launches": launches,

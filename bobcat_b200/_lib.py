@@ -134,6 +134,7 @@ SIGNATURES = {
     "bc_comm_rank": (i32, [vp]),
     "bc_comm_world": (i32, [vp]),
     "bc_comm_collectives": (u64, [vp]),
+    "bc_comm_peer_reduces": (u64, [vp]),
     "bc_batch_new_expert_parallel": (i32, [vp, vp, vp, u32, u32, i32, C.POINTER(vp)]),
     "bc_seq_step_on_device": (i32, [vp, u32]),
     "bc_engine_new": (i32, [vp, vp, u32, i32, u64, C.POINTER(vp)]),

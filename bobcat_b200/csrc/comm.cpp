@@ -12,8 +12,10 @@
 
 #include <dlfcn.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 using namespace bc;
 
@@ -74,6 +76,71 @@ bc_status nccl_check(Nccl* lib, int result, const char* what) {
     return fail(BC_ERR_EXECUTION, "NCCL error in %s: %s", what, lib->GetErrorString ? lib->GetErrorString(result) : "unknown");
 }
 
+// Every rank allocates a buffer, the ranks exchange its IPC handle (an all-gather of 128 bytes per
+// rank over the new communicator) and map each other's buffers.
+void setup_peer_buffers(bc_comm* c, Nccl* lib) {
+    const char* off = getenv("BOBCAT_NO_PEER_REDUCE");
+    if ((off && off[0] == '1') || c->world > k::kMaxPeers) return;
+    cudaStream_t stream = c->backend->stream;
+    const uint64_t bytes = k::peer_buffer_bytes((uint32_t)c->world);
+    // Every rank takes part in the exchange below whatever happened here, so the collective completes.
+    // The zeroed flags and epoch must be in memory before any peer's first store: the exchange
+    // below orders every rank's first launch after every rank's synchronize here.
+    bool ok = cudaMalloc(&c->peer_local, bytes) == cudaSuccess && cudaMemset(c->peer_local, 0, bytes) == cudaSuccess &&
+              cudaDeviceSynchronize() == cudaSuccess;
+    cudaIpcMemHandle_t handle;
+    std::memset(&handle, 0, sizeof handle);
+    if (ok) ok = cudaIpcGetMemHandle(&handle, c->peer_local) == cudaSuccess;
+    struct Entry {
+        cudaIpcMemHandle_t handle;
+        uint32_t ok;
+        uint32_t pad[15];
+    };
+    static_assert(sizeof(Entry) == 128, "handle entry");
+    Entry mine;
+    std::memset(&mine, 0, sizeof mine);
+    mine.handle = handle;
+    mine.ok = ok ? 1 : 0;
+    Entry* exchange = nullptr;
+    if (cudaMalloc(&exchange, sizeof(Entry) * c->world) != cudaSuccess) return;
+    cudaMemcpyAsync(exchange + c->rank, &mine, sizeof mine, cudaMemcpyHostToDevice, stream);
+    int rc = lib->AllGather(exchange + c->rank, exchange, sizeof(Entry), /*ncclUint8*/ 1, c->nccl, stream);
+    std::vector<Entry> all(c->world);
+    bool gathered = rc == 0 && cudaMemcpyAsync(all.data(), exchange, sizeof(Entry) * c->world, cudaMemcpyDeviceToHost, stream) == cudaSuccess &&
+                    cudaStreamSynchronize(stream) == cudaSuccess;
+    cudaFree(exchange);
+    if (!gathered) return;
+    for (int r = 0; r < c->world; ++r) ok = ok && all[r].ok;
+    if (!ok) return;  // every rank sees the same entries, so every rank decides the same
+    bool mapped = true;
+    for (int r = 0; r < c->world && mapped; ++r) {
+        if (r == c->rank) {
+            c->peer_mapped[r] = c->peer_local;
+            continue;
+        }
+        mapped = cudaIpcOpenMemHandle(&c->peer_mapped[r], all[r].handle, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+        if (!mapped) c->peer_mapped[r] = nullptr;
+    }
+    // The ranks agree on whether everyone mapped everyone: a sum of successes over ranks.
+    float* votes = nullptr;
+    if (cudaMalloc(&votes, 4) != cudaSuccess) return;
+    const float vote = mapped ? 1.f : 0.f;
+    cudaMemcpyAsync(votes, &vote, 4, cudaMemcpyHostToDevice, stream);
+    float total = 0.f;
+    const bool voted = lib->AllReduce(votes, votes, 1, kNcclFloat32, kNcclSum, c->nccl, stream) == 0 &&
+                       cudaMemcpyAsync(&total, votes, 4, cudaMemcpyDeviceToHost, stream) == cudaSuccess && cudaStreamSynchronize(stream) == cudaSuccess;
+    cudaFree(votes);
+    cudaGetLastError();  // a failed mapping must not linger as the thread's last error
+    if (!voted || (int)total != c->world) return;
+    c->peers.world = (uint32_t)c->world;
+    c->peers.rank = (uint32_t)c->rank;
+    c->peers.slot_floats = k::kPeerSlotFloats;
+    c->peers.flags_offset = (uint64_t)2 * c->world * k::kPeerSlotFloats * 4;
+    c->peers.epoch_offset = c->peers.flags_offset + (uint64_t)2 * c->world * 4;
+    for (int r = 0; r < c->world; ++r) c->peers.base[r] = c->peer_mapped[r];
+    c->peer_ready = true;
+}
+
 }  // namespace
 
 namespace bc {
@@ -84,6 +151,23 @@ bc_status comm_all_reduce_sum(bc_comm* c, float* data, size_t count) {
     BC_TRY(nccl_ready(&lib));
     c->collectives += 1;
     return nccl_check(lib, lib->AllReduce(data, data, count, kNcclFloat32, kNcclSum, c->nccl, c->backend->stream), "ncclAllReduce");
+}
+
+bc_status comm_all_reduce_add(bc_comm* c, float* partial, float* y, size_t count) {
+    if (!c || c->world == 1 || count == 0) {
+        if (count && c) BC_CUDA(k::add_floats(c->backend->stream, y, partial, count));
+        return BC_OK;
+    }
+    if (c->peer_ready && count <= k::kPeerSlotFloats && (reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(y)) % 16 == 0) {
+        c->collectives += 1;
+        c->peer_reduces += 1;
+        cudaError_t e = k::peer_all_reduce_add(c->backend->stream, c->peers, partial, y, (uint32_t)count);
+        if (e != cudaSuccess) return cuda_fail(e, "peer_all_reduce_add");
+        return BC_OK;
+    }
+    BC_TRY(comm_all_reduce_sum(c, partial, count));
+    BC_CUDA(k::add_floats(c->backend->stream, y, partial, count));
+    return BC_OK;
 }
 
 bc_status comm_all_gather(bc_comm* c, const float* mine, float* all, size_t count_per_rank) {
@@ -148,6 +232,8 @@ bc_status bc_comm_init(bc_backend* backend, const uint8_t* id, size_t id_len, in
         NcclId nid;
         std::memcpy(nid.bytes, id, BC_COMM_ID_BYTES);
         BC_TRY(nccl_check(lib, lib->CommInitRank(&c->nccl, world, nid, rank), "ncclCommInitRank"));
+        // Failing to set up the peer buffers is not an error: NCCL then carries every collective.
+        setup_peer_buffers(c.get(), lib);
     }
     *out = c.release();
     return BC_OK;
@@ -161,6 +247,19 @@ void bc_comm_free(bc_comm* comm) {
             cudaSetDevice(comm->backend->device);
             cudaStreamSynchronize(comm->backend->stream);
         }
+        // No rank unmaps or frees a buffer a peer may still write: meet first (a one-word sum).
+        if (comm->peer_ready && lib->AllReduce) {
+            float* word = nullptr;
+            if (cudaMalloc(&word, 4) == cudaSuccess) {
+                cudaMemsetAsync(word, 0, 4, comm->backend->stream);
+                lib->AllReduce(word, word, 1, kNcclFloat32, kNcclSum, comm->nccl, comm->backend->stream);
+                cudaStreamSynchronize(comm->backend->stream);
+                cudaFree(word);
+            }
+        }
+        for (int r = 0; r < comm->world && r < k::kMaxPeers; ++r)
+            if (r != comm->rank && comm->peer_mapped[r]) cudaIpcCloseMemHandle(comm->peer_mapped[r]);
+        if (comm->peer_local) cudaFree(comm->peer_local);
         if (lib->CommDestroy) lib->CommDestroy(comm->nccl);
     }
     delete comm;
@@ -169,5 +268,6 @@ void bc_comm_free(bc_comm* comm) {
 int32_t bc_comm_rank(const bc_comm* comm) { return comm ? comm->rank : 0; }
 int32_t bc_comm_world(const bc_comm* comm) { return comm ? comm->world : 1; }
 uint64_t bc_comm_collectives(const bc_comm* comm) { return comm ? comm->collectives : 0; }
+uint64_t bc_comm_peer_reduces(const bc_comm* comm) { return comm ? comm->peer_reduces : 0; }
 
 }  // extern "C"

@@ -162,6 +162,22 @@ cudaError_t attention_flash(cudaStream_t stream, const float* q, const void* k_c
 // a host-mapped word that receives the same value.
 cudaError_t argmax(cudaStream_t stream, const float* x, uint32_t n, uint32_t* out, uint32_t* readback);
 
+// ---- tensor-parallel decode (kernels_comm.cu): y += sum over ranks of `partial`, through buffers
+// every rank has mapped from every other rank (plain peer stores over NVLink; see the kernel).
+constexpr int kMaxPeers = 8;
+constexpr uint32_t kPeerSlotFloats = 16384;
+struct PeerBuffers {
+    void* base[kMaxPeers];   // every rank's buffer as this GPU addresses it (base[rank] is its own)
+    uint32_t world, rank;
+    uint32_t slot_floats;    // floats per slot; slots are [parity 2][world] from the start of a buffer
+    uint64_t flags_offset;   // byte offset of the flags, uint32 [parity 2][world]
+    uint64_t epoch_offset;   // byte offset of the rank's epoch counter
+};
+inline uint64_t peer_buffer_bytes(uint32_t world) { return (uint64_t)2 * world * kPeerSlotFloats * 4 + 2 * world * 4 + 64; }
+cudaError_t peer_all_reduce_add(cudaStream_t stream, const PeerBuffers& peers, const float* partial, float* y, uint32_t count);
+// Nonzero once a rank's flag did not arrive within the wait's limit (1 + that rank). Reading clears it.
+int peer_error_flag();
+
 // ---- sampling (kernels_sample.cu): Sampler::sample of crates/bobcat-cli/src/sampler.rs:45-112.
 struct Sampling {
     float temperature = 0.f;   // <= 0: the most likely token

@@ -72,8 +72,10 @@ struct Recorder {
             return;
         }
         matvec(w, x, s.partial, k::Norm{}, false);
-        run_status([&] { return comm_all_reduce_sum(s.tp, s.partial, w.n_rows); });
-        run("add", 1, w.n_rows, 0, 1, [&] { return k::add_floats(stream, y, s.partial, w.n_rows); });
+        // One kernel over NVLink peer memory when the ranks could map each other's buffers
+        // (kernels_comm.cu), else ncclAllReduce and an add.
+        s.launches += 1;
+        run_status([&] { return comm_all_reduce_add(s.tp, s.partial, y, w.n_rows); });
     }
     void matmul_reduced(const k::Mat& w, const float* x, float* y, uint32_t n) {
         if (!s.tp) {
@@ -81,8 +83,8 @@ struct Recorder {
             return;
         }
         matmul(w, x, s.partial, n, BC_STORE_OVERWRITE);
-        run_status([&] { return comm_all_reduce_sum(s.tp, s.partial, (size_t)n * w.n_rows); });
-        run("add", n, w.n_rows, 0, 1, [&] { return k::add_floats(stream, y, s.partial, (uint64_t)n * w.n_rows); });
+        s.launches += 1;
+        run_status([&] { return comm_all_reduce_add(s.tp, s.partial, y, (size_t)n * w.n_rows); });
     }
     // The logits: on a tensor-parallel rank the output matrix holds the rank's vocabulary rows;
     // every rank ends with all of them.

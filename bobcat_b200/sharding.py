@@ -111,6 +111,10 @@ class Comm:
     def collectives(self) -> int:
         return int(self._L.bc_comm_collectives(self._h))
 
+    def peer_reduces(self) -> int:
+        """Sums over ranks taken by the library's own NVLink peer-memory kernel rather than NCCL."""
+        return int(self._L.bc_comm_peer_reduces(self._h))
+
     def close(self) -> None:
         if self._h:
             self._L.bc_comm_free(self._h)

@@ -511,8 +511,12 @@ bc_status bc_comm_init(bc_backend* backend, const uint8_t* id, size_t id_len, in
 void bc_comm_free(bc_comm* comm);
 int32_t bc_comm_rank(const bc_comm* comm);
 int32_t bc_comm_world(const bc_comm* comm);
-/* Collectives this communicator has recorded so far. */
+/* Collectives this communicator has recorded so far, and how many of them were sums over ranks
+ * taken by this library's own kernel over NVLink peer memory (each rank stores its partial vector
+ * into buffers the ranks mapped from one another at bc_comm_init, then adds the ranks' vectors in
+ * rank order) rather than by NCCL. BOBCAT_NO_PEER_REDUCE=1 leaves every collective to NCCL. */
 uint64_t bc_comm_collectives(const bc_comm* comm);
+uint64_t bc_comm_peer_reduces(const bc_comm* comm);
 
 /* Expert-parallel multi-sequence decode of a mixture-of-experts model (moe_block,
  * crates/bobcat/src/lfm2.rs:413-440, sharded): this rank holds `n_seqs` of the world's sequences

@@ -12,9 +12,10 @@ from conftest import rel_error
 pytestmark = pytest.mark.gpu
 
 
-def _rank_main(rank, world, unique_id, path, prompt, n_ctx, n_decode, kv_half, out):
+def _rank_main(rank, world, unique_id, path, prompt, n_ctx, n_decode, kv_half, peer, out):
     import os
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ["BOBCAT_NO_PEER_REDUCE"] = "0" if peer else "1"
     from bobcat_b200 import Cuda, Model, Qwen35Cuda
     from bobcat_b200.sharding import Comm
 
@@ -35,14 +36,17 @@ def _rank_main(rank, world, unique_id, path, prompt, n_ctx, n_decode, kv_half, o
     tokens = seq.generate(n_decode).tolist()
     seq.restore(ckpt)
     again = seq.generate(n_decode).tolist()
-    out.put((rank, logits, step_logits, tokens, again, comm.collectives()))
+    out.put((rank, logits, step_logits, tokens, again, comm.collectives(), comm.peer_reduces()))
     seq.close()
     comm.close()
     cuda.close()
 
 
+# The sums over ranks of the decode step by the library's own NVLink peer-memory kernel (peer) and
+# by NCCL alone.
+@pytest.mark.parametrize("peer", [True, False], ids=["peer", "nccl"])
 @pytest.mark.parametrize("case", [("qwen35-tiny", False, 30, 20), ("qwen35-tiny", True, 30, 20), ("qwen35-2b", True, 24, 24)])
-def test_two_ranks_decode_what_one_gpu_decodes(model_path, cuda, case):
+def test_two_ranks_decode_what_one_gpu_decodes(model_path, cuda, case, peer):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     from bobcat_b200 import Model, Qwen35Cuda
@@ -68,15 +72,18 @@ def test_two_ranks_decode_what_one_gpu_decodes(model_path, cuda, case):
     unique_id = Comm.unique_id()
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, unique_id, path, prompt, n_ctx, n_decode, kv_half, out)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, unique_id, path, prompt, n_ctx, n_decode, kv_half, peer, out)) for r in range(world)]
     for p in procs:
         p.start()
     results = sorted((out.get(timeout=600) for _ in procs), key=lambda r: r[0])
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    for rank, logits, step_logits, tokens, again, collectives in results:
+    for rank, logits, step_logits, tokens, again, collectives, peer_reduces in results:
         assert collectives > 0
+        # Two GPUs of one machine can map each other's memory, so the peer kernel must have run
+        # when it was allowed to, and must not have when it was switched off.
+        assert (peer_reduces > 0) == peer, (rank, peer_reduces)
         # The batched half runs with half-precision operands on both sides (5e-3 class between two
         # tilings); the stepped half with f32 operands (1e-4, the single-step tolerance).
         assert rel_error(logits, want_logits) < 5e-3, rank
