@@ -296,8 +296,11 @@ cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* packed, f
 // Gate and up of a SwiGLU in one launch: both weight tiles meet the same token tile, two
 // accumulators in tensor memory, y = silu(gate x) * (up x).
 bool matmul_umma_swiglu_supported(const Mat& gate, const Mat& up, uint32_t n_tokens);
+// With `packed_out` the result is written as the packed fp16 input of the product that consumes it
+// (what matmul_pack would make of it, for gate.n_rows columns; gate.n_rows a multiple of 64) and y
+// is not touched.
 cudaError_t matmul_umma_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, const void* packed, float* y, uint32_t n_tokens,
-                               uint32_t y_stride);
+                               uint32_t y_stride, void* packed_out = nullptr);
 // Nonzero once a bounded wait inside the tensor-core prefill kernel gave up (1: producers on a free
 // stage, 2: epilogue on the accumulator, 3: token copy on a free stage, 4: MMA thread on a full stage).
 int matmul_error_flag();

@@ -97,6 +97,9 @@ struct UmmaParams {
     const uint32_t* offsets;
     const uint32_t* entries;
     uint32_t cap_groups;
+    // DUAL == 2 only: when set, silu(gate) * up is written as the fp16 operand of the product that
+    // consumes it (the layout of pack_kernel for n_rows columns and the same tokens) instead of to y.
+    __half* packed_out;
 };
 
 // X [n_tokens][n_cols] f32 -> fp16 operand layout, zero rows up to the padded token count. One
@@ -381,6 +384,31 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.f + expf(-v[j])) * up[j];
                 }
+                if (DUAL == 2 && p.packed_out) {
+                    // The warp's 32 rows are one block of 32 columns of the consuming product, its
+                    // 16 tokens two groups of 8: 4 core-matrix rows of 16 bytes per token. A lane
+                    // holds one column of 16 tokens and the layout wants 8 columns of one token
+                    // per 16 bytes, so the values turn through shared memory (the weight tiles
+                    // are idle by now; 17 rows of 16 bytes per core matrix keep both sides free of
+                    // bank conflicts), and each lane stores two 16-byte rows, 8 lanes to a 128-byte line.
+                    if (row0 + quarter * 32 < p.n_rows) {
+                        __half* turn = reinterpret_cast<__half*>(a_tiles + warp * 1152);
+                        const uint32_t core = (lane & 15) >> 2, e = lane & 3;
+                        const uint32_t at = (lane >> 4) * 4 + (e & 1) * 2 + (e >> 1);  // the column order of pack_kernel
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) turn[(core * 17 + j) * 8 + at] = __float2half_rn(v[j]);
+                        __syncwarp();
+                        const uint32_t tr = lane & 7, mm = lane >> 3;
+                        const uint32_t chunk = (row0 >> 6) + (quarter >> 1), jj = (quarter & 1) * 4 + mm;
+#pragma unroll
+                        for (uint32_t it = 0; it < 2; ++it) {
+                            const uint4 row16 = *reinterpret_cast<const uint4*>(turn + (mm * 17 + it * 8 + tr) * 8);
+                            const uint32_t tg = ((tok0 + u * 16) >> 3) + it;
+                            reinterpret_cast<uint4*>(p.packed_out)[(((uint64_t)chunk * p.token_groups + tg) * kCores + jj) * 8 + tr] = row16;
+                        }
+                    }
+                    continue;
+                }
                 if (out_row < p.n_rows) {
                     // Old values first, all 16 in flight at once, so the read-modify-write stores cost one round trip.
                     float old[16];
@@ -618,7 +646,8 @@ bool matmul_umma_swiglu_supported(const Mat& gate, const Mat& up, uint32_t n_tok
 }
 
 cudaError_t matmul_umma_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, const void* packed, float* y, uint32_t n_tokens,
-                               uint32_t y_stride) {
+                               uint32_t y_stride, void* packed_out) {
+    if (packed_out && (gate.n_rows % kChunkK != 0)) return cudaErrorInvalidValue;
     if (n_tokens == 0 || gate.n_rows == 0) return cudaSuccess;
     cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<2>), Shape<2>::kSmemBytes);
     if (err != cudaSuccess) return err;
@@ -638,6 +667,7 @@ cudaError_t matmul_umma_swiglu(cudaStream_t stream, const Mat& gate, const Mat& 
     p.split = 1;
     p.tile_tokens = choose_tiling(gate.n_rows, gate.n_cols, n_tokens, y_stride, 2, false).tile_tokens;
     p.store = BC_STORE_OVERWRITE;
+    p.packed_out = static_cast<__half*>(packed_out);
     dim3 grid((n_tokens + p.tile_tokens - 1) / p.tile_tokens, (gate.n_rows + kRows - 1) / kRows, 1);
     matmul_umma_kernel<2><<<grid, Shape<2>::kThreads, Shape<2>::kSmemBytes, stream>>>(p);
     return cudaGetLastError();

@@ -240,6 +240,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
 
     // Everything above touched only weights; the input vector (and y, the conv history) belong
     // to earlier launches.
+    // The norm's weights are the model's, not a predecessor's: a thread's share of them is on its
+    // way before the wait, so the input's loads after the wait are the only trip to L2 the
+    // staging waits for (inputs of up to one item per thread; longer inputs load them in the loop).
+    float4 early_wl = make_float4(1.f, 1.f, 1.f, 1.f), early_wh = early_wl;
+    const bool norm_early = p.norm_weight != nullptr && p.n_blocks * 4 <= (uint32_t)kThreads;
+    if (norm_early && (uint32_t)threadIdx.x < p.n_blocks * 4) {
+        const float4* w4e = reinterpret_cast<const float4*>(p.norm_weight);
+        early_wl = __ldg(w4e + (threadIdx.x >> 2) * 8 + (threadIdx.x & 3));
+        early_wh = __ldg(w4e + (threadIdx.x >> 2) * 8 + 4 + (threadIdx.x & 3));
+    }
     if (!p.route) pdl_wait();
 
     // Stage x as the B operand in one pass over global memory: RMSNorm weights applied, every
@@ -264,7 +274,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) matvec_mma_kernel(Params
         if (valid) {
             sumsq += (lo4.x * lo4.x + lo4.y * lo4.y + lo4.z * lo4.z + lo4.w * lo4.w) + (hi4.x * hi4.x + hi4.y * hi4.y + hi4.z * hi4.z + hi4.w * hi4.w);
             if (p.norm_weight) {
-                const float4 wl = __ldg(w4 + b * 8 + t), wh = __ldg(w4 + b * 8 + 4 + t);
+                float4 wl = early_wl, wh = early_wh;
+                if (!norm_early) {
+                    wl = __ldg(w4 + b * 8 + t);
+                    wh = __ldg(w4 + b * 8 + 4 + t);
+                }
                 lo4.x *= wl.x; lo4.y *= wl.y; lo4.z *= wl.z; lo4.w *= wl.w;
                 hi4.x *= wh.x; hi4.y *= wh.y; hi4.z *= wh.z; hi4.w *= wh.w;
             }

@@ -127,6 +127,35 @@ struct Recorder {
             [&] { return k::matmul_umma_swiglu(stream, gate, up, scratch, y, n, gate.n_rows); });
     }
 
+    // hidden += down (silu(gate x^) * (up x^)) over the batch, x^ the normalised rows of hidden
+    // (lfm2.rs:405-411, qwen35.rs:505-516). On the tensor-core path the gate / up launch writes its
+    // result as the packed fp16 input of the down product, so the f32 intermediate and its
+    // packing launch do not exist.
+    void normed_ffn(float* hidden, const float* norm_weight, uint32_t n, const k::Mat& gate, const k::Mat& up, const k::Mat& down) {
+        const bool direct = tensor_products() && k::matmul_umma_swiglu_supported(gate, up, n) && k::matmul_umma_supported(down, n) &&
+                            down.n_cols == gate.n_rows && gate.n_rows % 64 == 0;
+        if (!direct) {
+            normed_swiglu(hidden, norm_weight, n, gate, up, s.ffn);
+            matmul_reduced(down, s.ffn, hidden, n);
+            return;
+        }
+        const uint32_t cols = hp.n_embd;
+        const size_t down_bytes = (k::matmul_scratch_bytes(down, n) + 255) & ~(size_t)255;
+        void* scratch = nullptr;
+        if (status == BC_OK) status = s.backend->pack_scratch(down_bytes + k::matmul_pack_bytes(n, cols), &scratch);
+        void* in_pack = static_cast<char*>(scratch) + down_bytes;
+        run("pack_norm", n, cols, 0, 1, [&] { return k::matmul_pack_norm(stream, hidden, norm(norm_weight), n, cols, in_pack); });
+        run("matmul_swiglu", gate.n_rows, gate.n_cols, 2 * gate.bytes(), 1,
+            [&] { return k::matmul_umma_swiglu(stream, gate, up, in_pack, nullptr, n, gate.n_rows, scratch); });
+        float* target = s.tp ? s.partial : hidden;
+        run("matmul", down.n_rows, down.n_cols, down.bytes(), k::matmul_umma_launches(down, n) - 1,
+            [&] { return k::matmul_umma(stream, down, scratch, target, n, down.n_rows, s.tp ? BC_STORE_OVERWRITE : BC_STORE_ACCUMULATE); });
+        if (s.tp) {
+            s.launches += 1;
+            run_status([&] { return comm_all_reduce_add(s.tp, s.partial, hidden, (size_t)n * down.n_rows); });
+        }
+    }
+
     void normed_matmuls(const float* x, const float* norm_weight, uint32_t n, std::initializer_list<Product> products) {
         const uint32_t cols = hp.n_embd;
         bool fused = true;
@@ -389,8 +418,7 @@ struct Recorder {
                 route_trace = traced ? s.trace_routes + il * (size_t)s.trace_rows * 2 * hp.n_experts_used : nullptr;
                 lfm2_moe(D, n, false);
             } else {
-                normed_swiglu(s.hidden, D.ffn_norm, n, D.gate, D.up, s.ffn);
-                matmul(D.down, s.ffn, s.hidden, n, BC_STORE_ACCUMULATE);
+                normed_ffn(s.hidden, D.ffn_norm, n, D.gate, D.up, D.down);
             }
             if (traced) copy(s.hidden, s.trace_layers + il * trace_stride, (uint64_t)n * n_embd);
         }
@@ -502,8 +530,7 @@ struct Recorder {
                 qwen_delta_tail(D, S.cache_index, n);
                 matmul_reduced(D.ssm_out, s.gdn_out, s.hidden, n);
             }
-            normed_swiglu(s.hidden, D.ffn_norm, n, D.gate, D.up, s.ffn);
-            matmul_reduced(D.down, s.ffn, s.hidden, n);
+            normed_ffn(s.hidden, D.ffn_norm, n, D.gate, D.up, D.down);
             if (traced) copy(s.hidden, s.trace_layers + il * trace_stride, (uint64_t)n * n_embd);
         }
         if (traced)
@@ -546,8 +573,7 @@ struct Recorder {
                 route_trace = nullptr;
                 lfm2_moe(D, n, false);
             } else {
-                normed_swiglu(s.hidden, D.ffn_norm, n, D.gate, D.up, s.ffn);
-                matmul(D.down, s.ffn, s.hidden, n, BC_STORE_ACCUMULATE);
+                normed_ffn(s.hidden, D.ffn_norm, n, D.gate, D.up, D.down);
             }
         }
         // Every row needs its logits, so the output matrix is one batched product too.

@@ -313,11 +313,11 @@ bc_status seq_new(bc_model* model, bc_backend* backend, bc_comm* tp, uint32_t n_
     };
     const char* no_graph = getenv("BOBCAT_NO_GRAPH");
     s->use_graphs = !(no_graph && no_graph[0] == '1');
-    // A tensor-parallel step holds collectives; it is launched kernel by kernel unless
-    // BOBCAT_TP_GRAPH=1 asks for the captured form (NCCL records into a capture as well).
+    // A tensor-parallel step holds collectives (the peer-memory sums and NCCL's gather of the
+    // logits, which records into a capture as well); BOBCAT_TP_GRAPH=0 launches it kernel by kernel.
     if (s->tp) {
         const char* tp_graph = getenv("BOBCAT_TP_GRAPH");
-        s->use_graphs = s->use_graphs && tp_graph && tp_graph[0] == '1';
+        if (tp_graph && tp_graph[0] == '0') s->use_graphs = false;
     }
     // Kernels whose input vector outgrows the default shared-memory limit get their limit raised
     // now, so no launch inside a capture has to.
