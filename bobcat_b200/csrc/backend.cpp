@@ -73,6 +73,20 @@ bc_status bc_backend::pack_scratch(size_t bytes, void** out) {
     return BC_OK;
 }
 
+bc_status bc_backend::partial_scratch(size_t bytes, void** out) {
+    if (bytes > partials_len) {
+        BC_CUDA(cudaStreamSynchronize(stream));
+        if (partials) cudaFree(partials);
+        partials = nullptr;
+        partials_len = 0;
+        size_t want = bytes + bytes / 2;
+        BC_CUDA(cudaMalloc(&partials, want));
+        partials_len = want;
+    }
+    *out = partials;
+    return BC_OK;
+}
+
 namespace {
 
 bc_status need_recording(bc_backend* b) {
@@ -155,6 +169,7 @@ void bc_backend_close(bc_backend* b) {
         buffer->backend = nullptr;
     }
     if (b->pack) cudaFree(b->pack);
+    if (b->partials) cudaFree(b->partials);
     if (b->owns_stream) cudaStreamDestroy(b->stream);
     delete b;
 }

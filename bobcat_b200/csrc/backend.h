@@ -67,6 +67,11 @@ struct bc_backend {
     void* pack = nullptr;
     size_t pack_len = 0;
     bc_status pack_scratch(size_t bytes, void** out);
+    // Partial products of split-K launches, apart from the packed inputs: they may outlive the
+    // launch that wrote them until the next normalisation adds them up.
+    void* partials = nullptr;
+    size_t partials_len = 0;
+    bc_status partial_scratch(size_t bytes, void** out);
 
     bool profiling = false;
     std::map<ProfileKey, ProfileTotals> profile;

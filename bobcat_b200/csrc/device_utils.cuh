@@ -120,5 +120,15 @@ __device__ __forceinline__ float4 ldg_stream(const float4* p) {
     return v;
 }
 
+// Where element (token, col) of a batch lies in the packed fp16 operand layout of the tensor-core
+// prefill kernel (kernels_matmul_umma.cu), counted in halves: chunks of 64 columns, inside a chunk
+// groups of 8 tokens, inside a group 8 core matrices of 8 tokens x 8 columns (16 bytes per token),
+// with the columns of each block of 32 in the order the kernel's weight tiles use.
+__device__ __forceinline__ uint64_t packed_operand_index(uint32_t token, uint32_t col, uint32_t token_groups) {
+    const uint32_t chunk = col >> 6, c = col & 63, w = c & 31, e = w & 3;
+    const uint32_t core = (c >> 5) * 4 + ((w & 15) >> 2), at = (w >> 4) * 4 + (e & 1) * 2 + (e >> 1);
+    return ((((uint64_t)chunk * token_groups + (token >> 3)) * 8 + core) * 8 + (token & 7)) * 8 + at;
+}
+
 }  // namespace k
 }  // namespace bc

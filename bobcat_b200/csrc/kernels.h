@@ -83,8 +83,10 @@ cudaError_t matvec(cudaStream_t stream, const MatvecSegment* segments, int n_seg
 cudaError_t matvec_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, const float* x, Norm norm, float* y);
 cudaError_t matvec_conv(cudaStream_t stream, const Mat& in_proj, const float* x, Norm norm, const float* taps,
                         float* history, float* out, uint32_t n_embd, uint32_t kernel);
+// With `packed` (matmul_pack_bytes(n_tokens, n_embd) bytes; n_embd a multiple of 64) the results go
+// out as the packed fp16 input of the product that consumes them, and `out` is not written.
 cudaError_t short_conv(cudaStream_t stream, const float* bcx, const float* taps, float* history, float* out,
-                       uint32_t n_embd, uint32_t kernel, uint32_t n_tokens);
+                       uint32_t n_embd, uint32_t kernel, uint32_t n_tokens, void* packed = nullptr);
 cudaError_t expand(cudaStream_t stream, const Mat& w, void* out, bool out_half);
 // A position that is either immediate or read from device memory at run time (`*ptr + value`), so
 // one captured launch sequence can be replayed at every position of a decode.
@@ -290,9 +292,29 @@ int matmul_umma_launches(const Mat& w, uint32_t n_tokens);
 cudaError_t matmul_pack(cudaStream_t stream, const float* x, uint32_t n_tokens, uint32_t n_cols, void* packed);
 // RMSNorm fused into the packing: packed = fp16(weight * (x * scale)), so a normalised batch that only feeds
 // tensor-core products never exists in f32.
-cudaError_t matmul_pack_norm(cudaStream_t stream, const float* x, Norm norm, uint32_t n_tokens, uint32_t n_cols, void* packed);
+// The partial products of a split-K launch whose sum into y has not been taken yet: `split`
+// arrays of [n_tokens][n_rows] floats, to be added to y in index order.
+struct Deferred {
+    const float* partial = nullptr;
+    uint32_t split = 0, n_tokens = 0, n_rows = 0;
+};
+// Bytes of partial products matmul_umma writes for this shape (zero when it does not split K).
+uint64_t matmul_partial_bytes(const Mat& w, uint32_t n_tokens);
+// With `add` (for this x: n_tokens rows of n_cols), x += the deferred partial products first, so
+// the sum a split-K product into the residual stream left open costs no launch of its own.
+cudaError_t matmul_pack_norm(cudaStream_t stream, float* x, Norm norm, uint32_t n_tokens, uint32_t n_cols, void* packed,
+                             const Deferred* add = nullptr);
+// `partial`: where a split-K launch puts its partial products (matmul_partial_bytes; by default
+// behind the packed inputs, as matmul_scratch_bytes sizes the scratch). With `defer`, an
+// accumulating split-K product into rows of n_rows floats leaves the sum of the partial products
+// open and describes it there (defer->partial stays null when the launch did not split).
 cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* packed, float* y, uint32_t n_tokens, uint32_t y_stride,
-                        int32_t store);
+                        int32_t store, float* partial = nullptr, Deferred* defer = nullptr);
+// Up to three products that read the same packed inputs, in one launch (q, k and v of an attention
+// layer): ys[i] = ws[i] x for every token, rows of ws[i]->n_rows floats, overwritten.
+cudaError_t matmul_umma_several(cudaStream_t stream, const Mat* const* ws, float* const* ys, int n, const void* packed, uint32_t n_tokens);
+// y += the deferred partial products, in index order.
+cudaError_t matmul_reduce(cudaStream_t stream, const Deferred& d, float* y);
 // Gate and up of a SwiGLU in one launch: both weight tiles meet the same token tile, two
 // accumulators in tensor memory, y = silu(gate x) * (up x).
 bool matmul_umma_swiglu_supported(const Mat& gate, const Mat& up, uint32_t n_tokens);

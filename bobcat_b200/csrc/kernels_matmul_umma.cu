@@ -97,6 +97,14 @@ struct UmmaParams {
     const uint32_t* offsets;
     const uint32_t* entries;
     uint32_t cap_groups;
+    // DUAL == 1 only: further matrices that read the same packed inputs in the same launch (q, k, v).
+    // Row tiles [more_first[i], next) belong to matrix i + 1, which overwrites its own output of
+    // more_rows[i] floats per token. No K split, no grouping.
+    uint32_t n_more;
+    uint32_t more_first[2], more_rows[2];
+    const uint4* more_quants[2];
+    const __half* more_scales[2];
+    float* more_y[2];
     // DUAL == 2 only: when set, silu(gate) * up is written as the fp16 operand of the product that
     // consumes it (the layout of pack_kernel for n_rows columns and the same tokens) instead of to y.
     __half* packed_out;
@@ -172,6 +180,66 @@ __global__ void __launch_bounds__(256) pack_norm_kernel(const float* __restrict_
     }
 }
 
+// pack_norm_kernel for a batch whose rows still lack the sum of a split-K launch's partial
+// products: a token's row first takes the `split` partial rows in index order (like
+// reduce_kernel) and x keeps the sums. One CTA of 16 warps per 4 tokens (half a token group, so
+// the grid is twice as wide), four warps to a token: a row is summed and written by exactly one
+// CTA, which then packs its 4 tokens (64 of a group's 128 bytes per core-matrix row).
+__global__ void __launch_bounds__(512) pack_norm_add_kernel(float* __restrict__ x, const float* __restrict__ weight, float eps,
+                                                            __half* __restrict__ packed, uint32_t n_tokens, uint32_t n_cols, uint32_t token_groups,
+                                                            const float* __restrict__ partial, uint32_t split) {
+    __shared__ float sums[4][4];
+    __shared__ float scales[4];
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, token0 = blockIdx.x * 4;
+    {
+        const uint32_t token = token0 + (warp >> 2), cols4 = n_cols / 4;
+        float sumsq = 0.f;
+        if (token < n_tokens) {
+            float4* row = reinterpret_cast<float4*>(x + (uint64_t)token * n_cols);
+            const uint64_t total4 = (uint64_t)n_tokens * cols4;
+            const float4* part = reinterpret_cast<const float4*>(partial) + (uint64_t)token * cols4;
+#pragma unroll 4
+            for (uint32_t i = (warp & 3) * 32 + lane; i < cols4; i += 128) {
+                float4 sum = __ldcg(part + i);
+                for (uint32_t sp = 1; sp < split; ++sp) {
+                    const float4 o = __ldcg(part + sp * total4 + i);
+                    sum.x += o.x; sum.y += o.y; sum.z += o.z; sum.w += o.w;
+                }
+                float4 v = row[i];
+                v.x += sum.x; v.y += sum.y; v.z += sum.z; v.w += sum.w;
+                row[i] = v;
+                sumsq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+        }
+        sumsq = warp_sum(sumsq);
+        if (lane == 0) sums[warp >> 2][warp & 3] = sumsq;
+    }
+    __syncthreads();
+    if (tid < 4) scales[tid] = rsqrtf(((sums[tid][0] + sums[tid][1]) + (sums[tid][2] + sums[tid][3])) / (float)n_cols + eps);
+    __syncthreads();
+    const uint32_t tr = tid & 3, j = (tid >> 2) & (kCores - 1), sub = tid / (4 * kCores);  // 512 / 32 = 16 chunks per pass
+    const uint32_t token = token0 + tr, n_chunks = n_cols / kChunkK, tg = token0 >> 3, in_group = (token0 & 4) + tr;
+    const float scale = scales[tr];
+    for (uint32_t chunk = sub; chunk < n_chunks; chunk += 512 / (4 * kCores)) {
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (token < n_tokens) {
+            const uint32_t col = chunk * kChunkK + (j >> 2) * 32 + 4 * (j & 3);
+            const float* src = x + (uint64_t)token * n_cols + col;
+            float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 16);
+            const float4 wl = __ldg(reinterpret_cast<const float4*>(weight + col)), wh = __ldg(reinterpret_cast<const float4*>(weight + col + 16));
+            lo.x = wl.x * (lo.x * scale); lo.y = wl.y * (lo.y * scale); lo.z = wl.z * (lo.z * scale); lo.w = wl.w * (lo.w * scale);
+            hi.x = wh.x * (hi.x * scale); hi.y = wh.y * (hi.y * scale); hi.z = wh.z * (hi.z * scale); hi.w = wh.w * (hi.w * scale);
+            __half2 a = __floats2half2_rn(lo.x, lo.z), b = __floats2half2_rn(lo.y, lo.w);
+            __half2 c = __floats2half2_rn(hi.x, hi.z), d = __floats2half2_rn(hi.y, hi.w);
+            out.x = *reinterpret_cast<uint32_t*>(&a);
+            out.y = *reinterpret_cast<uint32_t*>(&b);
+            out.z = *reinterpret_cast<uint32_t*>(&c);
+            out.w = *reinterpret_cast<uint32_t*>(&d);
+        }
+        reinterpret_cast<uint4*>(packed)[(((uint64_t)chunk * token_groups + tg) * kCores + j) * 8 + in_group] = out;
+    }
+}
+
 // Packing for grouped mode: sorted entry i of expert e (offsets[e] <= i < offsets[e + 1]) becomes
 // token i - offsets[e] of the expert's region, which starts at token group e * cap_groups; its row
 // of x is the entry's token (gather: entry / n_used) or the entry itself. One thread per 16-byte
@@ -242,7 +310,24 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
     volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t tok0 = blockIdx.x * p.tile_tokens, row0 = blockIdx.y * kRows;
+    // The matrix this row tile belongs to.
+    uint32_t row_tile = blockIdx.y, w_rows = p.n_rows, w_stride = p.y_stride;
+    const uint4* w_quants = p.quants[0];
+    const __half* w_scales = p.scales[0];
+    float* w_y = p.y;
+    if (DUAL == 1 && p.n_more) {
+        int m = -1;
+        if (row_tile >= p.more_first[0]) m = 0;
+        if (p.n_more > 1 && row_tile >= p.more_first[1]) m = 1;
+        if (m >= 0) {
+            row_tile -= p.more_first[m];
+            w_rows = w_stride = p.more_rows[m];
+            w_quants = p.more_quants[m];
+            w_scales = p.more_scales[m];
+            w_y = p.more_y[m];
+        }
+    }
+    const uint32_t tok0 = blockIdx.x * p.tile_tokens, row0 = row_tile * kRows;
     uint32_t n_tokens = p.n_tokens, group0 = 0;
     uint64_t weight0 = 0;  // first block of this CTA's matrix in the stacked weights
     const uint32_t* out_rows = nullptr;
@@ -283,7 +368,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
         // ---- producers: group `group` takes chunks group, group + kGroups, ...
         const uint32_t row = tid & (kRows - 1), group = tid / kGroupThreads;
         const uint32_t grow = row0 + row;
-        const bool valid = grow < p.n_rows;
+        const bool valid = grow < w_rows;
         const uint64_t first = weight0 + (uint64_t)(valid ? grow : 0) * p.n_blocks + (uint64_t)kc_begin * kChunkBlocks;
         const uint32_t a_off = (row >> 3) * kGroupBytes + (row & 7) * 16;
         // A row's share of a chunk of one matrix. Rows past the matrix keep scale zero, so their tile rows are zero.
@@ -293,8 +378,8 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
         };
         auto fetch = [&](uint32_t i, int m) {
             Share r;
-            const uint4* qsrc = p.quants[m] + first;
-            const unsigned short* ssrc = reinterpret_cast<const unsigned short*>(p.scales[m]) + first;
+            const uint4* qsrc = (m == 0 ? w_quants : p.quants[1]) + first;
+            const unsigned short* ssrc = reinterpret_cast<const unsigned short*>(m == 0 ? w_scales : p.scales[1]) + first;
 #pragma unroll
             for (uint32_t b = 0; b < kChunkBlocks; ++b) {
                 r.q[b] = make_uint4(0, 0, 0, 0);
@@ -372,7 +457,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
             tc_fence_after_sync();
             const uint32_t quarter = warp & 3, part = warp >> 2, units = n_tile / 16;
             const uint32_t out_row = row0 + quarter * 32 + lane;
-            float* out = p.y + (p.split > 1 ? (uint64_t)blockIdx.z * n_tokens * p.y_stride : 0);
+            float* out = w_y + (p.split > 1 ? (uint64_t)blockIdx.z * n_tokens * w_stride : 0);
             for (uint32_t u = part; u < units; u += kGroups) {
                 float v[16];
                 __syncwarp();
@@ -391,7 +476,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
                     // per 16 bytes, so the values turn through shared memory (the weight tiles
                     // are idle by now; 17 rows of 16 bytes per core matrix keep both sides free of
                     // bank conflicts), and each lane stores two 16-byte rows, 8 lanes to a 128-byte line.
-                    if (row0 + quarter * 32 < p.n_rows) {
+                    if (row0 + quarter * 32 < w_rows) {
                         __half* turn = reinterpret_cast<__half*>(a_tiles + warp * 1152);
                         const uint32_t core = (lane & 15) >> 2, e = lane & 3;
                         const uint32_t at = (lane >> 4) * 4 + (e & 1) * 2 + (e >> 1);  // the column order of pack_kernel
@@ -409,7 +494,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
                     }
                     continue;
                 }
-                if (out_row < p.n_rows) {
+                if (out_row < w_rows) {
                     // Old values first, all 16 in flight at once, so the read-modify-write stores cost one round trip.
                     float old[16];
                     // The output row of each token: itself, or in grouped mode the entry it came from.
@@ -421,7 +506,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
                     }
                     if (DUAL == 1 && p.store != BC_STORE_OVERWRITE) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) old[j] = dest[j] != 0xffffffffu ? __ldcg(out + (uint64_t)dest[j] * p.y_stride + out_row) : 0.f;
+                        for (int j = 0; j < 16; ++j) old[j] = dest[j] != 0xffffffffu ? __ldcg(out + (uint64_t)dest[j] * w_stride + out_row) : 0.f;
                     }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -429,7 +514,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
                             float r = my_chunks ? v[j] : 0.f;
                             if (DUAL == 1 && p.store == BC_STORE_ACCUMULATE) r += old[j];
                             else if (DUAL == 1 && p.store == BC_STORE_SWIGLU) r = old[j] / (1.f + expf(-old[j])) * r;
-                            out[(uint64_t)dest[j] * p.y_stride + out_row] = r;
+                            out[(uint64_t)dest[j] * w_stride + out_row] = r;
                         }
                     }
                 }
@@ -579,10 +664,14 @@ bool umma_disabled() {
 
 uint64_t matmul_pack_bytes(uint32_t n_tokens, uint32_t n_cols) { return (uint64_t)((n_tokens + 15u) & ~15u) * n_cols * 2; }
 
+uint64_t matmul_partial_bytes(const Mat& w, uint32_t n_tokens) {
+    uint32_t split = choose_tiling(w.n_rows, w.n_cols, n_tokens, w.n_rows, 1, true).split;
+    return split > 1 ? (uint64_t)split * n_tokens * w.n_rows * 4 : 0;
+}
+
 uint64_t matmul_scratch_bytes(const Mat& w, uint32_t n_tokens) {
     uint64_t pack = (matmul_pack_bytes(n_tokens, w.n_cols) + 255) & ~255ull;
-    uint32_t split = choose_tiling(w.n_rows, w.n_cols, n_tokens, w.n_rows, 1, true).split;
-    return pack + (split > 1 ? (uint64_t)split * n_tokens * w.n_rows * 4 : 0);
+    return pack + matmul_partial_bytes(w, n_tokens);
 }
 
 int matmul_umma_launches(const Mat& w, uint32_t n_tokens) { return choose_tiling(w.n_rows, w.n_cols, n_tokens, w.n_rows, 1, true).split > 1 ? 3 : 2; }
@@ -599,25 +688,41 @@ cudaError_t matmul_pack(cudaStream_t stream, const float* x, uint32_t n_tokens, 
     return cudaGetLastError();
 }
 
-cudaError_t matmul_pack_norm(cudaStream_t stream, const float* x, Norm norm, uint32_t n_tokens, uint32_t n_cols, void* packed) {
+cudaError_t matmul_pack_norm(cudaStream_t stream, float* x, Norm norm, uint32_t n_tokens, uint32_t n_cols, void* packed, const Deferred* add) {
     uint32_t token_groups = ((n_tokens + 15u) & ~15u) / 8;
     if (token_groups == 0 || n_cols == 0) return cudaSuccess;
+    const bool adding = add && add->partial;
+    if (adding && (add->n_tokens != n_tokens || add->n_rows != n_cols || n_cols % 4 != 0)) return cudaErrorInvalidValue;
     const uint32_t shares = token_groups >= 256 ? 1 : token_groups >= 64 ? 4 : 8;
+    if (adding) {
+        pack_norm_add_kernel<<<token_groups * 2, 512, 0, stream>>>(x, norm.weight, norm.eps, static_cast<__half*>(packed), n_tokens, n_cols, token_groups,
+                                                               add->partial, add->split);
+        return cudaGetLastError();
+    }
     pack_norm_kernel<<<dim3(token_groups, shares), 256, 0, stream>>>(x, norm.weight, norm.eps, static_cast<__half*>(packed), n_tokens, n_cols,
                                                                     token_groups);
     return cudaGetLastError();
 }
 
+cudaError_t matmul_reduce(cudaStream_t stream, const Deferred& d, float* y) {
+    if (!d.partial || d.n_tokens == 0) return cudaSuccess;
+    const uint64_t quads = (uint64_t)d.n_tokens * d.n_rows / 4;
+    reduce_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(d.partial, y, d.n_rows, d.n_tokens, d.n_rows, d.split, BC_STORE_ACCUMULATE);
+    return cudaGetLastError();
+}
+
 cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, float* y, uint32_t n_tokens, uint32_t y_stride,
-                        int32_t store) {
+                        int32_t store, float* partial_at, Deferred* defer) {
+    if (defer) *defer = Deferred{};
     if (n_tokens == 0 || w.n_rows == 0) return cudaSuccess;
     cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), Shape<1>::kSmemBytes);
     if (err != cudaSuccess) return err;
     // The split must match matmul_scratch_bytes, which sized the scratch for a dense output.
     const Tiling tiling = choose_tiling(w.n_rows, w.n_cols, n_tokens, y_stride, 1, y_stride == w.n_rows);
     const uint32_t split = tiling.split;
-    float* partial = reinterpret_cast<float*>(static_cast<char*>(const_cast<void*>(scratch)) +
-                                              ((matmul_pack_bytes(n_tokens, w.n_cols) + 255) & ~255ull));
+    float* partial = partial_at ? partial_at
+                                : reinterpret_cast<float*>(static_cast<char*>(const_cast<void*>(scratch)) +
+                                                           ((matmul_pack_bytes(n_tokens, w.n_cols) + 255) & ~255ull));
     UmmaParams p{};
     p.quants[0] = static_cast<const uint4*>(w.data);
     p.scales[0] = w.scales;
@@ -636,8 +741,51 @@ cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, 
     matmul_umma_kernel<1><<<grid, Shape<1>::kThreads, Shape<1>::kSmemBytes, stream>>>(p);
     err = cudaGetLastError();
     if (err != cudaSuccess || split == 1) return err;
+    if (defer && store == BC_STORE_ACCUMULATE && y_stride == w.n_rows) {
+        *defer = Deferred{partial, split, n_tokens, w.n_rows};
+        return cudaSuccess;
+    }
     const uint64_t quads = (uint64_t)n_tokens * w.n_rows / 4;
     reduce_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(partial, y, w.n_rows, n_tokens, y_stride, split, store);
+    return cudaGetLastError();
+}
+
+cudaError_t matmul_umma_several(cudaStream_t stream, const Mat* const* ws, float* const* ys, int n, const void* packed, uint32_t n_tokens) {
+    if (n < 1 || n > 3) return cudaErrorInvalidValue;
+    if (n_tokens == 0) return cudaSuccess;
+    cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), Shape<1>::kSmemBytes);
+    if (err != cudaSuccess) return err;
+    uint32_t total_rows = 0, tiles = 0;
+    for (int i = 0; i < n; ++i) {
+        if (ws[i]->n_cols != ws[0]->n_cols || ws[i]->n_rows == 0) return cudaErrorInvalidValue;
+        total_rows += ws[i]->n_rows;
+    }
+    UmmaParams p{};
+    p.quants[0] = static_cast<const uint4*>(ws[0]->data);
+    p.scales[0] = ws[0]->scales;
+    p.packed = static_cast<const __half*>(packed);
+    p.y = ys[0];
+    p.n_rows = ws[0]->n_rows;
+    p.y_stride = ws[0]->n_rows;
+    tiles = (ws[0]->n_rows + kRows - 1) / kRows;
+    p.n_more = (uint32_t)(n - 1);
+    for (int i = 1; i < n; ++i) {
+        p.more_first[i - 1] = tiles;
+        p.more_rows[i - 1] = ws[i]->n_rows;
+        p.more_quants[i - 1] = static_cast<const uint4*>(ws[i]->data);
+        p.more_scales[i - 1] = ws[i]->scales;
+        p.more_y[i - 1] = ys[i];
+        tiles += (ws[i]->n_rows + kRows - 1) / kRows;
+    }
+    p.n_blocks = ws[0]->n_cols / 32;
+    p.n_chunks = ws[0]->n_cols / kChunkK;
+    p.n_tokens = n_tokens;
+    p.token_groups = ((n_tokens + 15u) & ~15u) / 8;
+    p.split = 1;
+    p.tile_tokens = choose_tiling(total_rows, ws[0]->n_cols, n_tokens, total_rows, 1, false).tile_tokens;
+    p.store = BC_STORE_OVERWRITE;
+    dim3 grid((n_tokens + p.tile_tokens - 1) / p.tile_tokens, tiles, 1);
+    matmul_umma_kernel<1><<<grid, Shape<1>::kThreads, Shape<1>::kSmemBytes, stream>>>(p);
     return cudaGetLastError();
 }
 

@@ -198,9 +198,8 @@ __global__ void norm_rope_kernel(NormRopeParams p) {
 // [kernel - 1][n_embd], oldest first. kernel <= 9. One thread per (token, channel); the sum runs in
 // the order of the token-by-token recurrence, so batches of any split give the same bits. The
 // history is only read here; short_conv_history_kernel rewrites it afterwards.
-__device__ __forceinline__ void short_conv_token(const float* __restrict__ bcx, const float* __restrict__ taps,
-                                                 const float* __restrict__ history, float* __restrict__ out, uint32_t n_embd,
-                                                 uint32_t kernel, uint32_t t, uint32_t ch) {
+__device__ __forceinline__ float short_conv_token(const float* __restrict__ bcx, const float* __restrict__ taps,
+                                                  const float* __restrict__ history, uint32_t n_embd, uint32_t kernel, uint32_t t, uint32_t ch) {
     const float* row = bcx + (uint64_t)t * 3 * n_embd;
     const float b = row[ch], c = row[n_embd + ch], x = row[2 * n_embd + ch];
     float sum = taps[(uint64_t)ch * kernel + kernel - 1] * (b * x);
@@ -216,15 +215,25 @@ __device__ __forceinline__ void short_conv_token(const float* __restrict__ bcx, 
         }
         sum += taps[(uint64_t)ch * kernel + kk] * past;
     }
-    out[(uint64_t)t * n_embd + ch] = c * sum;
+    return c * sum;
 }
 
+// With `packed`, the results go out as the fp16 operand of the product that consumes them
+// (rows up to the next multiple of 16 tokens zero) instead of as f32 rows.
 __global__ void __launch_bounds__(256) short_conv_kernel(const float* __restrict__ bcx, const float* __restrict__ taps,
-                                                         const float* __restrict__ history, float* __restrict__ out, uint32_t n_embd,
-                                                         uint32_t kernel, uint32_t n_tokens) {
+                                                         const float* __restrict__ history, float* __restrict__ out, __half* __restrict__ packed,
+                                                         uint32_t n_embd, uint32_t kernel, uint32_t n_tokens) {
     const uint32_t ch = blockIdx.x * blockDim.x + threadIdx.x;
     if (ch >= n_embd) return;
-    for (uint32_t t = blockIdx.y; t < n_tokens; t += gridDim.y) short_conv_token(bcx, taps, history, out, n_embd, kernel, t, ch);
+    if (packed) {
+        const uint32_t padded = (n_tokens + 15u) & ~15u;
+        for (uint32_t t = blockIdx.y; t < padded; t += gridDim.y) {
+            const float v = t < n_tokens ? short_conv_token(bcx, taps, history, n_embd, kernel, t, ch) : 0.f;
+            packed[packed_operand_index(t, ch, padded / 8)] = __float2half_rn(v);
+        }
+        return;
+    }
+    for (uint32_t t = blockIdx.y; t < n_tokens; t += gridDim.y) out[(uint64_t)t * n_embd + ch] = short_conv_token(bcx, taps, history, n_embd, kernel, t, ch);
 }
 
 // The history after the batch: slot kk holds the product of token n_tokens - (kernel - 1) + kk, or
@@ -493,9 +502,12 @@ cudaError_t silu_mul(cudaStream_t stream, float* x, const float* gate, uint64_t 
 }
 
 cudaError_t short_conv(cudaStream_t stream, const float* bcx, const float* taps, float* history, float* out, uint32_t n_embd,
-                       uint32_t kernel, uint32_t n_tokens) {
+                       uint32_t kernel, uint32_t n_tokens, void* packed) {
     if (n_tokens == 0) return cudaSuccess;
-    short_conv_kernel<<<dim3(blocks_for(n_embd, 256), n_tokens < 65535u ? n_tokens : 65535u), 256, 0, stream>>>(bcx, taps, history, out, n_embd, kernel, n_tokens);
+    if (packed && n_embd % 64 != 0) return cudaErrorInvalidValue;
+    const uint32_t rows = packed ? ((n_tokens + 15u) & ~15u) : n_tokens;
+    short_conv_kernel<<<dim3(blocks_for(n_embd, 256), rows < 65535u ? rows : 65535u), 256, 0, stream>>>(bcx, taps, history, out,
+                                                                                                     static_cast<__half*>(packed), n_embd, kernel, n_tokens);
     short_conv_history_kernel<<<blocks_for(n_embd, 128), 128, 0, stream>>>(bcx, history, n_embd, kernel, n_tokens);
     return cudaGetLastError();
 }

@@ -34,10 +34,25 @@ struct Recorder {
 
     k::Pos at(uint32_t pos) const { return replayed ? k::Pos{s.step_pos, 0} : k::Pos{nullptr, pos}; }
 
+    // A split-K product into the residual stream whose partial products are not added up yet
+    // (in the backend's partial scratch). The normalisation that reads the stream next takes the
+    // sum itself; any other launch that comes first triggers the separate sum.
+    k::Deferred open_sum{};
+    float* open_sum_y = nullptr;
+
+    void close_sum() {
+        if (!open_sum.partial) return;
+        const k::Deferred d = open_sum;
+        open_sum = k::Deferred{};
+        float* y = open_sum_y;
+        run("reduce", d.n_tokens, d.n_rows, 0, 1, [&] { return k::matmul_reduce(stream, d, y); });
+    }
+
     // Launch helper: counts the kernel, keeps the first failure.
     template <typename F>
     void run(const char* name, uint32_t rows, uint32_t cols, uint64_t bytes, int kernels, F&& f) {
         if (status != BC_OK) return;
+        if (open_sum.partial) close_sum();
         // Timing diagnostics: a launch kind left out of the pass (its outputs keep stale values).
         if (!s.skip_name.empty() && s.skip_name == name && (s.skip_rows == 0 || s.skip_rows == rows) && (s.skip_cols == 0 || s.skip_cols == cols)) return;
         s.launches += (uint64_t)kernels;
@@ -48,6 +63,7 @@ struct Recorder {
     template <typename F>
     void run_status(F&& f) {
         if (status != BC_OK) return;
+        if (open_sum.partial) close_sum();
         status = f();
     }
 
@@ -99,9 +115,46 @@ struct Recorder {
     }
 
     void matmul(const k::Mat& w, const float* x, float* y, uint32_t n, int store) {
-        void* pack = nullptr;
-        if (status == BC_OK && tensor_products() && k::matmul_umma_supported(w, n)) status = s.backend->pack_scratch(k::matmul_scratch_bytes(w, n), &pack);
-        run("matmul", w.n_rows, w.n_cols, w.bytes(), pack ? k::matmul_umma_launches(w, n) : 1, [&] { return k::matmul(stream, w, x, y, n, w.n_rows, store, pack); });
+        if (status == BC_OK && tensor_products() && k::matmul_umma_supported(w, n)) {
+            void* pack = nullptr;
+            status = s.backend->pack_scratch(k::matmul_pack_bytes(n, w.n_cols), &pack);
+            run("pack", n, w.n_cols, 0, 1, [&] { return k::matmul_pack(stream, x, n, w.n_cols, pack); });
+            product_of_packed(w, pack, y, n, store);
+            return;
+        }
+        run("matmul", w.n_rows, w.n_cols, w.bytes(), 1, [&] { return k::matmul(stream, w, x, y, n, w.n_rows, store, nullptr); });
+    }
+
+    // The tensor-core product of packed inputs. Split-K shapes put their partial products into the
+    // backend's partial scratch; when the product adds to y, the sum stays open for the next
+    // normalisation of y (open_sum), else it is taken at once.
+    void product_of_packed(const k::Mat& w, const void* packed, float* y, uint32_t n, int store) {
+        close_sum();  // the partial scratch is about to be reused (or regrown)
+        void* partial = nullptr;
+        const uint64_t partial_bytes = k::matmul_partial_bytes(w, n);
+        if (status == BC_OK && partial_bytes) status = s.backend->partial_scratch(partial_bytes, &partial);
+        k::Deferred left{};
+        const bool may_defer = store == BC_STORE_ACCUMULATE;
+        run("matmul", w.n_rows, w.n_cols, w.bytes(), 1, [&] {
+            return k::matmul_umma(stream, w, packed, y, n, w.n_rows, store, static_cast<float*>(partial), may_defer ? &left : nullptr);
+        });
+        if (status != BC_OK) return;
+        if (left.partial) {
+            open_sum = left;
+            open_sum_y = y;
+        } else if (partial_bytes) {
+            s.launches += 1;  // the sum ran inside matmul_umma
+        }
+    }
+
+    // The fused normalisation and packing of x, taking an open sum into x along the way.
+    void pack_normed(float* x, const float* norm_weight, uint32_t n, uint32_t cols, void* packed) {
+        k::Deferred add{};
+        if (open_sum.partial && open_sum_y == x && open_sum.n_tokens == n && open_sum.n_rows == cols) {
+            add = open_sum;
+            open_sum = k::Deferred{};
+        }
+        run("pack_norm", n, cols, 0, 1, [&] { return k::matmul_pack_norm(stream, x, norm(norm_weight), n, cols, packed, &add); });
     }
 
     // RMSNorm of the batch, then products that all read the normalised rows. When every product
@@ -122,7 +175,7 @@ struct Recorder {
         const uint32_t cols = hp.n_embd;
         void* scratch = nullptr;
         if (status == BC_OK) status = s.backend->pack_scratch(k::matmul_pack_bytes(n, cols), &scratch);
-        run("pack_norm", n, cols, 0, 1, [&] { return k::matmul_pack_norm(stream, x, norm(norm_weight), n, cols, scratch); });
+        pack_normed(const_cast<float*>(x), norm_weight, n, cols, scratch);
         run("matmul_swiglu", gate.n_rows, gate.n_cols, 2 * gate.bytes(), 1,
             [&] { return k::matmul_umma_swiglu(stream, gate, up, scratch, y, n, gate.n_rows); });
     }
@@ -140,16 +193,14 @@ struct Recorder {
             return;
         }
         const uint32_t cols = hp.n_embd;
-        const size_t down_bytes = (k::matmul_scratch_bytes(down, n) + 255) & ~(size_t)255;
+        const size_t down_bytes = (k::matmul_pack_bytes(n, down.n_cols) + 255) & ~(size_t)255;
         void* scratch = nullptr;
         if (status == BC_OK) status = s.backend->pack_scratch(down_bytes + k::matmul_pack_bytes(n, cols), &scratch);
         void* in_pack = static_cast<char*>(scratch) + down_bytes;
-        run("pack_norm", n, cols, 0, 1, [&] { return k::matmul_pack_norm(stream, hidden, norm(norm_weight), n, cols, in_pack); });
+        pack_normed(hidden, norm_weight, n, cols, in_pack);
         run("matmul_swiglu", gate.n_rows, gate.n_cols, 2 * gate.bytes(), 1,
             [&] { return k::matmul_umma_swiglu(stream, gate, up, in_pack, nullptr, n, gate.n_rows, scratch); });
-        float* target = s.tp ? s.partial : hidden;
-        run("matmul", down.n_rows, down.n_cols, down.bytes(), k::matmul_umma_launches(down, n) - 1,
-            [&] { return k::matmul_umma(stream, down, scratch, target, n, down.n_rows, s.tp ? BC_STORE_OVERWRITE : BC_STORE_ACCUMULATE); });
+        product_of_packed(down, scratch, s.tp ? s.partial : hidden, n, s.tp ? BC_STORE_OVERWRITE : BC_STORE_ACCUMULATE);
         if (s.tp) {
             s.launches += 1;
             run_status([&] { return comm_all_reduce_add(s.tp, s.partial, hidden, (size_t)n * down.n_rows); });
@@ -171,12 +222,26 @@ struct Recorder {
         }
         void* scratch = nullptr;
         if (status == BC_OK) status = s.backend->pack_scratch(bytes, &scratch);
-        run("pack_norm", n, cols, 0, 1, [&] { return k::matmul_pack_norm(stream, x, norm(norm_weight), n, cols, scratch); });
-        for (const Product& q : products) {
-            const k::Mat& w = *q.w;
-            run("matmul", w.n_rows, w.n_cols, w.bytes(), k::matmul_umma_launches(w, n) - 1,
-                [&] { return k::matmul_umma(stream, w, scratch, q.y, n, w.n_rows, q.store); });
+        pack_normed(const_cast<float*>(x), norm_weight, n, cols, scratch);
+        // Products that only overwrite their outputs (q, k, v) share one launch.
+        bool together = products.size() > 1 && products.size() <= 3;
+        for (const Product& q : products) together = together && q.store == BC_STORE_OVERWRITE;
+        if (together) {
+            const k::Mat* ws[3];
+            float* ys[3];
+            uint32_t rows = 0;
+            uint64_t bytes_read = 0;
+            int count = 0;
+            for (const Product& q : products) {
+                ws[count] = q.w;
+                ys[count++] = q.y;
+                rows += q.w->n_rows;
+                bytes_read += q.w->bytes();
+            }
+            run("matmul", rows, cols, bytes_read, 1, [&] { return k::matmul_umma_several(stream, ws, ys, count, scratch, n); });
+            return;
         }
+        for (const Product& q : products) product_of_packed(*q.w, scratch, q.y, n, q.store);
     }
 
     size_t kv_element_bytes() const { return s.kv_half ? 2 : 4; }
@@ -409,9 +474,18 @@ struct Recorder {
             } else {
                 float* history = s.conv_state + (size_t)S.cache_index * (hp.conv_kernel - 1) * n_embd;
                 normed_matmuls(s.hidden, D.attn_norm, n, {{&D.in_proj, s.bcx, BC_STORE_OVERWRITE}});
-                run("short_conv", n, n_embd, 0, 2,
-                    [&] { return k::short_conv(stream, s.bcx, D.taps, history, s.conv_out, n_embd, hp.conv_kernel, n); });
-                matmul(D.out_proj, s.conv_out, s.hidden, n, BC_STORE_ACCUMULATE);
+                if (tensor_products() && k::matmul_umma_supported(D.out_proj, n) && n_embd % 64 == 0) {
+                    // The convolution writes the packed input of the output projection itself.
+                    void* pack = nullptr;
+                    if (status == BC_OK) status = s.backend->pack_scratch(k::matmul_pack_bytes(n, n_embd), &pack);
+                    run("short_conv", n, n_embd, 0, 2,
+                        [&] { return k::short_conv(stream, s.bcx, D.taps, history, nullptr, n_embd, hp.conv_kernel, n, pack); });
+                    product_of_packed(D.out_proj, pack, s.hidden, n, BC_STORE_ACCUMULATE);
+                } else {
+                    run("short_conv", n, n_embd, 0, 2,
+                        [&] { return k::short_conv(stream, s.bcx, D.taps, history, s.conv_out, n_embd, hp.conv_kernel, n); });
+                    matmul(D.out_proj, s.conv_out, s.hidden, n, BC_STORE_ACCUMULATE);
+                }
             }
             if (S.moe) {
                 run("rms_norm", n, n_embd, 0, 1, [&] { return k::rms_norm(stream, s.hidden, D.ffn_norm, s.normed, n_embd, n, hp.norm_eps); });
@@ -589,6 +663,7 @@ struct Recorder {
     void batch(uint32_t pos, uint32_t n, bool want_logits, bool traced, size_t trace_stride) {
         if (hp.architecture == BC_ARCH_QWEN35) qwen_batch(pos, n, want_logits, traced, trace_stride);
         else lfm2_batch(pos, n, want_logits, traced, trace_stride);
+        close_sum();  // the last layer's product, when no logits were asked for
     }
 
     void argmax(const float* x, uint32_t* out, uint32_t* readback) {
