@@ -176,6 +176,10 @@ bc_status bc_batch_generate(bc_batch* batch, uint32_t* out, size_t n_tokens) {
     bc_seq& rows = *batch->seqs[0];
     uint64_t before = rows.launches;
     Recorder r(rows);
+    // With the sequences spread over ranks, a rank's share runs on the kernels the whole batch
+    // would run on in one process: the tensor-core products when all ranks together hold 16 rows
+    // or more, however few of them are this rank's (they still read every weight).
+    if (batch->ep.comm && batch->ep.comm->world > 1) r.min_tensor_rows = std::max(1u, (16u + (uint32_t)batch->ep.comm->world - 1) / (uint32_t)batch->ep.comm->world);
     k::SeqTable table;
     table.pos = batch->pos;
     table.k_cache = batch->k_ptrs;

@@ -284,7 +284,9 @@ cudaError_t moe_combine(cudaStream_t stream, const float* expert_out, const uint
 cudaError_t matmul(cudaStream_t stream, const Mat& w, const float* x, float* y, uint32_t n_tokens, uint32_t y_stride,
                    int32_t store, void* pack);
 // The tensor-core prefill kernel (kernels_matmul_umma.cu) and its input packing.
-bool matmul_umma_supported(const Mat& w, uint32_t n_tokens);
+// Batches below `min_tokens` rows are left to the f32 tile kernel unless the caller lowers the bound
+// (rows are padded to 16 either way).
+bool matmul_umma_supported(const Mat& w, uint32_t n_tokens, uint32_t min_tokens = 16);
 uint64_t matmul_pack_bytes(uint32_t n_tokens, uint32_t n_cols);
 // Packed inputs plus, for shapes that split K, the partial products.
 uint64_t matmul_scratch_bytes(const Mat& w, uint32_t n_tokens);
@@ -317,7 +319,7 @@ cudaError_t matmul_umma_several(cudaStream_t stream, const Mat* const* ws, float
 cudaError_t matmul_reduce(cudaStream_t stream, const Deferred& d, float* y);
 // Gate and up of a SwiGLU in one launch: both weight tiles meet the same token tile, two
 // accumulators in tensor memory, y = silu(gate x) * (up x).
-bool matmul_umma_swiglu_supported(const Mat& gate, const Mat& up, uint32_t n_tokens);
+bool matmul_umma_swiglu_supported(const Mat& gate, const Mat& up, uint32_t n_tokens, uint32_t min_tokens = 16);
 // With `packed_out` the result is written as the packed fp16 input of the product that consumes it
 // (what matmul_pack would make of it, for gate.n_rows columns; gate.n_rows a multiple of 64) and y
 // is not touched.

@@ -676,8 +676,8 @@ uint64_t matmul_scratch_bytes(const Mat& w, uint32_t n_tokens) {
 
 int matmul_umma_launches(const Mat& w, uint32_t n_tokens) { return choose_tiling(w.n_rows, w.n_cols, n_tokens, w.n_rows, 1, true).split > 1 ? 3 : 2; }
 
-bool matmul_umma_supported(const Mat& w, uint32_t n_tokens) {
-    return !umma_disabled() && w.format == BC_Q4_0 && w.n_cols % kChunkK == 0 && w.n_cols > 0 && n_tokens >= 16;
+bool matmul_umma_supported(const Mat& w, uint32_t n_tokens, uint32_t min_tokens) {
+    return !umma_disabled() && w.format == BC_Q4_0 && w.n_cols % kChunkK == 0 && w.n_cols > 0 && n_tokens >= min_tokens && n_tokens > 0;
 }
 
 cudaError_t matmul_pack(cudaStream_t stream, const float* x, uint32_t n_tokens, uint32_t n_cols, void* packed) {
@@ -789,8 +789,9 @@ cudaError_t matmul_umma_several(cudaStream_t stream, const Mat* const* ws, float
     return cudaGetLastError();
 }
 
-bool matmul_umma_swiglu_supported(const Mat& gate, const Mat& up, uint32_t n_tokens) {
-    return matmul_umma_supported(gate, n_tokens) && matmul_umma_supported(up, n_tokens) && gate.n_rows == up.n_rows && gate.n_cols == up.n_cols;
+bool matmul_umma_swiglu_supported(const Mat& gate, const Mat& up, uint32_t n_tokens, uint32_t min_tokens) {
+    return matmul_umma_supported(gate, n_tokens, min_tokens) && matmul_umma_supported(up, n_tokens, min_tokens) && gate.n_rows == up.n_rows &&
+           gate.n_cols == up.n_cols;
 }
 
 cudaError_t matmul_umma_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, const void* packed, float* y, uint32_t n_tokens,

@@ -29,6 +29,11 @@ struct Recorder {
     bool replayed = false;
     // Traced passes of a mixture-of-experts model: where the next router launch's routes are copied to.
     uint32_t* route_trace = nullptr;
+    // Batches with fewer rows than this multiply on the f32 tile kernels. A prefill's short tail
+    // keeps f32 operands that way; a pass over several sequences lowers it to 1, because its few
+    // rows (a rank's share of the sequences) still read every weight and the tensor-core kernel
+    // reads them faster.
+    uint32_t min_tensor_rows = 16;
 
     explicit Recorder(bc_seq& seq) : s(seq), hp(seq.hp), stream(seq.backend->stream) {}
 
@@ -115,7 +120,7 @@ struct Recorder {
     }
 
     void matmul(const k::Mat& w, const float* x, float* y, uint32_t n, int store) {
-        if (status == BC_OK && tensor_products() && k::matmul_umma_supported(w, n)) {
+        if (status == BC_OK && tensor_products() && k::matmul_umma_supported(w, n, min_tensor_rows)) {
             void* pack = nullptr;
             status = s.backend->pack_scratch(k::matmul_pack_bytes(n, w.n_cols), &pack);
             run("pack", n, w.n_cols, 0, 1, [&] { return k::matmul_pack(stream, x, n, w.n_cols, pack); });
@@ -167,7 +172,7 @@ struct Recorder {
     };
     // ffn = silu(gate x^) * (up x^) over the batch, x^ the normalised rows.
     void normed_swiglu(const float* x, const float* norm_weight, uint32_t n, const k::Mat& gate, const k::Mat& up, float* y) {
-        if (!tensor_products() || !k::matmul_umma_swiglu_supported(gate, up, n)) {
+        if (!tensor_products() || !k::matmul_umma_swiglu_supported(gate, up, n, min_tensor_rows)) {
             // The up projection's store combines with the gate projection already in the buffer.
             normed_matmuls(x, norm_weight, n, {{&gate, y, BC_STORE_OVERWRITE}, {&up, y, BC_STORE_SWIGLU}});
             return;
@@ -185,7 +190,7 @@ struct Recorder {
     // result as the packed fp16 input of the down product, so the f32 intermediate and its
     // packing launch do not exist.
     void normed_ffn(float* hidden, const float* norm_weight, uint32_t n, const k::Mat& gate, const k::Mat& up, const k::Mat& down) {
-        const bool direct = tensor_products() && k::matmul_umma_swiglu_supported(gate, up, n) && k::matmul_umma_supported(down, n) &&
+        const bool direct = tensor_products() && k::matmul_umma_swiglu_supported(gate, up, n, min_tensor_rows) && k::matmul_umma_supported(down, n, min_tensor_rows) &&
                             down.n_cols == gate.n_rows && gate.n_rows % 64 == 0;
         if (!direct) {
             normed_swiglu(hidden, norm_weight, n, gate, up, s.ffn);
@@ -212,7 +217,7 @@ struct Recorder {
         bool fused = true;
         size_t bytes = 0;
         for (const Product& q : products) {
-            fused = fused && tensor_products() && k::matmul_umma_supported(*q.w, n);
+            fused = fused && tensor_products() && k::matmul_umma_supported(*q.w, n, min_tensor_rows);
             bytes = std::max(bytes, (size_t)k::matmul_scratch_bytes(*q.w, n));
         }
         if (!fused) {
@@ -474,7 +479,7 @@ struct Recorder {
             } else {
                 float* history = s.conv_state + (size_t)S.cache_index * (hp.conv_kernel - 1) * n_embd;
                 normed_matmuls(s.hidden, D.attn_norm, n, {{&D.in_proj, s.bcx, BC_STORE_OVERWRITE}});
-                if (tensor_products() && k::matmul_umma_supported(D.out_proj, n) && n_embd % 64 == 0) {
+                if (tensor_products() && k::matmul_umma_supported(D.out_proj, n, min_tensor_rows) && n_embd % 64 == 0) {
                     // The convolution writes the packed input of the output projection itself.
                     void* pack = nullptr;
                     if (status == BC_OK) status = s.backend->pack_scratch(k::matmul_pack_bytes(n, n_embd), &pack);
