@@ -56,7 +56,6 @@ constexpr uint32_t kChunkBlocks = kChunkK / 32;  // Q4_0 blocks per row per stag
 constexpr uint32_t kCores = kChunkK / 8;         // core matrices along K per stage
 constexpr uint32_t kGroupThreads = kRows;  // a producer thread per row of the tile
 constexpr uint32_t kATile = kRows * kChunkK * 2;       // 16 KB
-constexpr uint32_t kBTile = kMaxTokens * kChunkK * 2;  // 32 KB
 constexpr uint32_t kGroupBytes = 8 * kChunkK * 2;      // an 8-row group of a stage: 1 KB
 constexpr uint32_t kCoreBytes = 128;
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -76,7 +75,15 @@ struct Shape {
     static constexpr uint32_t kThreads = kProducers + 64;
     static constexpr uint32_t kStageA = DUAL * kATile;
     static constexpr uint32_t kTmemColumns = DUAL * kMaxTokens;
-    static constexpr size_t kSmemBytes = kStages * (kStageA + kBTile) + (2 * kStages + 1) * 8 + 16;
+    // With two weight matrices the producers take the Q4_0 bytes through shared memory (below), and
+    // the room for that comes from the token tiles: at most 192 tokens instead of 256.
+    static constexpr bool kStaged = DUAL == 2;
+    static constexpr uint32_t kTileTokens = kStaged ? 192 : kMaxTokens;
+    static constexpr uint32_t kStageB = kTileTokens * kChunkK * 2;
+    // Staged form: per group two slots of raw bytes per matrix, 32 bytes of quants and 4 of scales per row.
+    static constexpr uint32_t kRawTile = kGroupThreads * (kChunkBlocks * 18);
+    static constexpr uint32_t kRawBytes = kStaged ? kGroups * 2 * DUAL * kRawTile : 0;
+    static constexpr size_t kSmemBytes = kStages * (kStageA + kStageB) + kRawBytes + (2 * kStages + 1) * 8 + 16;
 };
 
 __device__ int g_matmul_error;
@@ -88,7 +95,7 @@ struct UmmaParams {
     float* y;              // the output, or with split > 1 the partial products [split][n_tokens][n_rows]
     uint32_t n_rows, n_blocks, n_chunks, n_tokens, y_stride, token_groups;
     uint32_t split;        // parts K is divided into (blockIdx.z)
-    uint32_t tile_tokens;  // tokens per CTA, a multiple of 16 up to kMaxTokens
+    uint32_t tile_tokens;  // tokens per CTA, a multiple of 16 up to the shape's kTileTokens
     int store;
     // Grouped mode (mixture of experts), when offsets is set: blockIdx.z is an expert, whose weights
     // are rows [z * n_rows, (z + 1) * n_rows) of the stacked matrices, whose tokens are the entries
@@ -304,8 +311,10 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
     constexpr uint32_t kGroups = Shape<DUAL>::kGroups, kTmaWarp = Shape<DUAL>::kTmaWarp, kMmaWarp = Shape<DUAL>::kMmaWarp;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* a_tiles = smem;
+    constexpr uint32_t kBTile = Shape<DUAL>::kStageB;
     uint8_t* b_tiles = a_tiles + kStages * kStageA;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(b_tiles + kStages * kBTile);
+    uint8_t* raw = b_tiles + kStages * kBTile;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raw + Shape<DUAL>::kRawBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
     volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -391,18 +400,69 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
             }
             return r;
         };
-        // Loads stay in flight in registers: two turns ahead with one matrix, one turn ahead with two.
-        Share cur[DUAL], next[DUAL], after[DUAL];
+        // One matrix: loads stay in flight in registers two turns ahead. Two matrices: a thread's
+        // bytes come through its own two slots of shared memory by cp.async, two turns ahead as
+        // well, and it reads them back itself (no other thread touches them): handing loaded
+        // registers on from turn to turn waits for the youngest load, which with one turn of lead
+        // made a turn as long as a trip to memory.
+        constexpr bool kStaged = Shape<DUAL>::kStaged;
+        constexpr uint32_t kRawTile = Shape<DUAL>::kRawTile;
+        uint8_t* my_raw = raw + (size_t)group * 2 * DUAL * kRawTile;  // [slot][matrix]: quants of the 128 rows, then their scales
+        auto stage_bytes = [&](uint32_t i, uint32_t slot) {
+            if (valid && i < my_chunks) {
 #pragma unroll
-        for (int m = 0; m < DUAL; ++m) {
-            cur[m] = fetch(group, m);
-            next[m] = fetch(group + kGroups, m);
+                for (int m = 0; m < DUAL; ++m) {
+                    const uint4* qsrc = (m == 0 ? w_quants : p.quants[1]) + first + (uint64_t)i * kChunkBlocks;
+                    const unsigned short* ssrc = reinterpret_cast<const unsigned short*>(m == 0 ? w_scales : p.scales[1]) + first + (uint64_t)i * kChunkBlocks;
+                    uint8_t* tile = my_raw + (slot * DUAL + m) * kRawTile;
+#pragma unroll
+                    for (uint32_t b = 0; b < kChunkBlocks; ++b) cp_async_16(smem_u32(tile + row * (16 * kChunkBlocks) + 16 * b), qsrc + b);
+                    cp_async_4(smem_u32(tile + kGroupThreads * (16 * kChunkBlocks) + row * (2 * kChunkBlocks)), ssrc);
+                }
+            }
+            cp_async_commit();
+        };
+        auto staged = [&](uint32_t slot, int m) {
+            Share r;
+            const uint8_t* tile = my_raw + (slot * DUAL + m) * kRawTile;
+#pragma unroll
+            for (uint32_t b = 0; b < kChunkBlocks; ++b) {
+                r.q[b] = make_uint4(0, 0, 0, 0);
+                r.d[b] = 0;
+            }
+            if (valid) {
+#pragma unroll
+                for (uint32_t b = 0; b < kChunkBlocks; ++b) r.q[b] = *reinterpret_cast<const uint4*>(tile + row * (16 * kChunkBlocks) + 16 * b);
+                const uint32_t two = *reinterpret_cast<const uint32_t*>(tile + kGroupThreads * (16 * kChunkBlocks) + row * (2 * kChunkBlocks));
+                r.d[0] = (unsigned short)(two & 0xffffu);
+                r.d[kChunkBlocks - 1] = (unsigned short)(two >> 16);
+            }
+            return r;
+        };
+        static_assert(!kStaged || kChunkBlocks == 2, "the staged form reads a row's two scales as one word");
+        Share cur[DUAL], next[DUAL], after[DUAL];
+        if (kStaged) {
+            stage_bytes(group, 0);
+            stage_bytes(group + kGroups, 1);
+        } else {
+#pragma unroll
+            for (int m = 0; m < DUAL; ++m) {
+                cur[m] = fetch(group, m);
+                next[m] = fetch(group + kGroups, m);
+            }
         }
         bool alive = true;
         const uint32_t stage = group;  // kGroups == kStages
         uint32_t phase = 1;            // the parity a free stage shows
-        for (uint32_t i = group; i < my_chunks; i += kGroups, phase ^= 1) {
-            if (DUAL == 1) after[0] = fetch(i + 2 * kGroups, 0);
+        uint32_t slot = 0;
+        for (uint32_t i = group; i < my_chunks; i += kGroups, phase ^= 1, slot ^= 1) {
+            if (kStaged) {
+                cp_async_wait<1>();  // all but the newest group: this turn's bytes are in
+#pragma unroll
+                for (int m = 0; m < DUAL; ++m) cur[m] = staged(slot, m);
+            } else if (DUAL == 1) {
+                after[0] = fetch(i + 2 * kGroups, 0);
+            }
 #pragma unroll
             for (int m = 0; m < DUAL; ++m) {
                 // Dequantise before waiting for the stage, so only the stores follow the wait.
@@ -438,13 +498,18 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(full0 + 8 * stage);
+            if (kStaged) {
+                stage_bytes(i + 2 * kGroups, slot);  // the slot just read takes the bytes of two turns on
+            } else {
 #pragma unroll
-            for (int m = 0; m < DUAL; ++m) {
-                cur[m] = next[m];
-                if (DUAL == 1) next[m] = after[m];
-                else next[m] = fetch(i + 2 * kGroups, m);
+                for (int m = 0; m < DUAL; ++m) {
+                    cur[m] = next[m];
+                    if (DUAL == 1) next[m] = after[m];
+                    else next[m] = fetch(i + 2 * kGroups, m);
+                }
             }
         }
+        if (kStaged) cp_async_wait<0>();
 
         // ---- epilogue: lanes 32 * (warp % 4).. of tensor memory, a quarter of the columns per warp
         alive = __all_sync(0xffffffffu, alive);
@@ -629,9 +694,10 @@ struct Tiling {
 Tiling choose_tiling(uint32_t n_rows, uint32_t n_cols, uint32_t n_tokens, uint32_t y_stride, int dual, bool may_split) {
     const uint32_t row_tiles = (n_rows + kRows - 1) / kRows, chunks = n_cols / kChunkK, sms = (uint32_t)sm_count();
     const bool can_split = may_split && dual == 1 && n_rows % 4 == 0 && y_stride % 4 == 0;
-    Tiling best{kMaxTokens, 1};
+    const uint32_t widest = dual == 2 ? Shape<2>::kTileTokens : Shape<1>::kTileTokens;
+    Tiling best{widest, 1};
     double best_cost = 1e30;
-    const uint32_t min_tiles = (n_tokens + kMaxTokens - 1) / kMaxTokens;
+    const uint32_t min_tiles = (n_tokens + widest - 1) / widest;
     for (uint32_t token_tiles = min_tiles; token_tiles <= min_tiles + 6; ++token_tiles) {
         uint32_t width = (((n_tokens + token_tiles - 1) / token_tiles) + 15u) & ~15u;
         if (width < 64 && token_tiles > min_tiles) break;
@@ -859,13 +925,13 @@ cudaError_t matmul_experts_umma(cudaStream_t stream, const Mat& w, const Mat* up
     p.y_stride = n_rows;
     p.token_groups = n_experts * cap_groups;
     p.split = 1;
-    p.tile_tokens = kMaxTokens;
+    p.tile_tokens = up ? Shape<2>::kTileTokens : Shape<1>::kTileTokens;
     p.store = BC_STORE_OVERWRITE;
     p.offsets = offsets;
     p.entries = entries;
     p.cap_groups = cap_groups;
     // Any one expert can receive up to n_tokens entries (a token picks an expert at most once).
-    dim3 grid((n_tokens + kMaxTokens - 1) / kMaxTokens, (n_rows + kRows - 1) / kRows, n_experts);
+    dim3 grid((n_tokens + p.tile_tokens - 1) / p.tile_tokens, (n_rows + kRows - 1) / kRows, n_experts);
     if (up) {
         if ((err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<2>), Shape<2>::kSmemBytes)) != cudaSuccess) return err;
         matmul_umma_kernel<2><<<grid, Shape<2>::kThreads, Shape<2>::kSmemBytes, stream>>>(p);
