@@ -229,6 +229,10 @@ cudaError_t gdn_gates(cudaStream_t stream, float* beta, float* alpha, const floa
 // The gated delta rule over n_tokens; state [n_v_heads][k_dim][v_dim]; `normalize` L2-normalises q and k.
 cudaError_t gdn_recurrence(cudaStream_t stream, const float* qkv, const float* beta, const float* decay, float* state, float* out,
                            uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t n_tokens, bool normalize);
+// The q and k heads of qkv ([n_tokens][2 * n_k_heads * k_dim + n_v_heads * v_dim]) L2-normalised in
+// place, q also times 1 / sqrt(k_dim): what gdn_recurrence does per token with `normalize`, done
+// for the whole batch at once, so the recurrence can run without it.
+cudaError_t gdn_qk_norm(cudaStream_t stream, float* qkv, uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t n_tokens);
 // One token through the whole mixer after its projections (conv with history shift, gates, L2
 // norms, delta rule, gated norm) in one launch; gdn_step_supported says whether the shape fits.
 bool gdn_step_supported(uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t kernel);

@@ -4,6 +4,9 @@
 // gdn_qk_norm :181, gdn_recurrence :222, attention_gate :307); the arithmetic they must reproduce is
 // crates/bobcat/src/qwen35.rs:430-516 and :754-778, f32 throughout and in the reference's order.
 
+#include <cstdlib>
+
+#include "async_utils.cuh"
 #include "device_utils.cuh"
 #include "kernels.h"
 
@@ -105,113 +108,168 @@ struct RecurrenceParams {
     int normalize;       // L2-normalise q (times 1/sqrt(k_dim)) and k here, as decode does
 };
 
-// One CTA per value head, one thread per state column, which holds its k_dim state values in
-// registers for the whole run of tokens. Per token (qwen35.rs:483-506): S *= decay;
-// r = sum_i S[i] k_i; delta = (v - r) beta; S[i] += k_i delta; o = sum_i S[i] q_i, each sum as
-// four interleaved partial sums. Value head h reads key head h % n_k_heads.
+// l2_normalize of one head's q or k (qwen35.rs:762-768), element e * 32 + lane in `x[e]`: the sum of
+// squares is taken per run of 32 elements across the warp and the runs are added in order, which
+// is the order gdn_step_kernel takes (there a warp holds one run), so a batch and single steps
+// normalise to the same bits. Returns the factor 1 / sqrt(sum + 1e-6).
+template <int PER>
+__device__ __forceinline__ float l2_factor(const float (&x)[PER]) {
+    float sum = 0.f;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) sum += warp_sum(x[e] * x[e]);
+    return 1.0f / sqrtf(sum + 1e-6f);
+}
+
+// The q and k heads of a batch normalised in place, q also scaled by 1 / sqrt(k_dim): one warp
+// per (token, q or k, key head). Run before the recurrence so that its token loop does not carry
+// the reductions.
 template <int KDIM>
-__global__ void __launch_bounds__(256) gdn_recurrence_kernel(RecurrenceParams p) {
-    // Two copies of the staged q, k and of the reduction scratch, used on alternate tokens, so a
-    // token needs two block barriers and the next token's inputs load while this one computes.
-    __shared__ __align__(16) float qs[2][KDIM], ks[2][KDIM];
-    __shared__ float scratch[2][16];
+__global__ void __launch_bounds__(256) gdn_qk_norm_kernel(float* __restrict__ qkv, uint32_t n_k_heads, uint32_t conv_dim, uint32_t n_tokens) {
+    constexpr int PER = KDIM / 32;
     pdl_launch_dependents();
     pdl_wait();
-    const uint32_t head = blockIdx.x, j = threadIdx.x, vd = p.v_dim;
-    const uint32_t lane = j & 31, warp = j >> 5, n_warps = (blockDim.x + 31) >> 5;
+    const uint32_t lane = threadIdx.x & 31, item = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+    if (item >= n_tokens * 2 * n_k_heads) return;
+    const uint32_t t = item / (2 * n_k_heads), which = (item / n_k_heads) & 1, head = item % n_k_heads;
+    float* x = qkv + (uint64_t)t * conv_dim + (uint64_t)which * n_k_heads * KDIM + head * KDIM;
+    float v[PER];
+#pragma unroll
+    for (int e = 0; e < PER; ++e) v[e] = x[e * 32 + lane];
+    const float factor = l2_factor<PER>(v);
+    const float scale = which == 0 ? (1.0f / sqrtf((float)KDIM)) * factor : factor;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) x[e * 32 + lane] = v[e] * scale;
+}
+
+// The delta rule over a run of tokens. One warp (a CTA of its own) per 8 state columns of a value
+// head; four neighbouring lanes share a column, each holding a quarter of its k_dim state values in
+// registers for the whole run. Per token (qwen35.rs:483-506): S *= decay; r = sum_i S[i] k_i;
+// delta = (v - r) beta; S[i] += k_i delta; o = sum_i S[i] q_i. A lane sums its quarter as two
+// interleaved partial sums and the quarters are added in order - the arithmetic of
+// gdn_step_kernel, so a batch and single steps walk the same values. Value head h reads key head
+// h % n_k_heads. A column's recurrence needs nothing of the other columns, so the warps share no
+// state and meet at no barrier: each stages (and, when asked, normalises) the token's q and k for
+// itself. A head spreads over v_dim / 8 warps, and a token is a chain of k_dim / 4 multiply-adds;
+// the earlier form (a CTA per head, a thread per column with all k_dim values, two block barriers
+// per token) took 1.45 us per token.
+constexpr uint32_t kRecurrenceWarps = 4;  // independent warps per CTA, one per SM partition
+
+template <int KDIM>
+__global__ void __launch_bounds__(32 * kRecurrenceWarps) gdn_recurrence_kernel(RecurrenceParams p) {
+    constexpr int PER = KDIM / 32;   // elements of q and of k a lane brings in
+    constexpr int MINE = KDIM / 4;   // state values of its column a lane holds
+    static_assert(KDIM % 32 == 0 && MINE % 4 == 0, "k_dim");
+    // A token's inputs come through a ring of kAhead + 1 slots of shared memory, copied
+    // (cp.async) kAhead tokens ahead: a token that loaded its successor's inputs into registers
+    // and handed them on lasted one trip to memory, however little it computed.
+    constexpr int kAhead = 7, kSlots = kAhead + 1;
+    // A quarter of q (of k) is followed by four floats of padding, so the four quarters that a
+    // warp's lanes read at once lie in different banks.
+    struct Slot {
+        float q[KDIM + 16], k[KDIM + 16], v[8], beta, decay, pad[2];
+    };
+    auto at = [](uint32_t e) { return e + 4 * (e / MINE); };
+    __shared__ __align__(16) Slot rings[kRecurrenceWarps][kSlots];
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t vd = p.v_dim, groups = (vd + 7) / 8;
+    const uint32_t unit = blockIdx.x * kRecurrenceWarps + (threadIdx.x >> 5);  // (head, group of 8 columns)
+    if (unit >= p.n_v_heads * groups) return;  // whole warps; the warps of a CTA never meet
+    Slot* ring = rings[threadIdx.x >> 5];
+    const uint32_t head = unit / groups, lane = threadIdx.x & 31, part = lane & 3, first_lane = lane & ~3u;
+    const uint32_t column = lane >> 2, j = (unit % groups) * 8 + column;
     const uint32_t key_head = head % p.n_k_heads;
     const uint32_t key_dim = p.n_k_heads * KDIM, conv_dim = 2 * key_dim + p.n_v_heads * vd;
-    float* state = p.state + (uint64_t)head * KDIM * vd;
-    float S[KDIM];
+    float* state = p.state + (uint64_t)head * KDIM * vd + (uint64_t)part * MINE * vd;
+    float S[MINE];
     if (j < vd) {
 #pragma unroll
-        for (int i = 0; i < KDIM; ++i) S[i] = state[(uint64_t)i * vd + j];
+        for (int i = 0; i < MINE; ++i) S[i] = state[(uint64_t)i * vd + j];
     }
-    // This thread's inputs of a token: its element of q and of k, its element of v, the head's gates.
-    struct Inputs {
-        float q, k, v, beta, decay;
-    };
-    auto load = [&](uint32_t t) {
-        Inputs in{0.f, 0.f, 0.f, 0.f, 0.f};
+    // Lane l brings elements e * 32 + l of q and of k; the first lane of a column its v; lanes 1 and 2 the gates.
+    auto bring = [&](uint32_t t) {
         if (t < p.n_tokens) {
+            Slot& slot = ring[t % kSlots];
             const float* row = p.qkv + (uint64_t)t * conv_dim;
-            if (j < KDIM) {
-                in.q = row[key_head * KDIM + j];
-                in.k = row[key_dim + key_head * KDIM + j];
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                async::cp_async_4(async::smem_u32(&slot.q[at(e * 32 + lane)]), row + key_head * KDIM + e * 32 + lane);
+                async::cp_async_4(async::smem_u32(&slot.k[at(e * 32 + lane)]), row + key_dim + key_head * KDIM + e * 32 + lane);
             }
-            if (j < vd) {
-                in.v = row[2 * key_dim + head * vd + j];
-                in.beta = p.beta[(uint64_t)t * p.n_v_heads + head];
-                in.decay = p.decay[(uint64_t)t * p.n_v_heads + head];
-            }
+            if (part == 0 && j < vd) async::cp_async_4(async::smem_u32(&slot.v[column]), row + 2 * key_dim + head * vd + j);
+            if (lane == 1) async::cp_async_4(async::smem_u32(&slot.beta), p.beta + (uint64_t)t * p.n_v_heads + head);
+            if (lane == 2) async::cp_async_4(async::smem_u32(&slot.decay), p.decay + (uint64_t)t * p.n_v_heads + head);
         }
-        return in;
+        async::cp_async_commit();
     };
-    Inputs cur = load(0);
+#pragma unroll
+    for (int t = 0; t < kAhead; ++t) bring((uint32_t)t);
     for (uint32_t t = 0; t < p.n_tokens; ++t) {
-        const Inputs next = load(t + 1);
-        const uint32_t buf = t & 1;
+        __syncwarp();  // every lane is through with the slot the next copy overwrites (the previous token's)
+        bring(t + kAhead);
+        async::cp_async_wait<kAhead>();  // all but the newest kAhead groups: this token's bytes are in
+        __syncwarp();
+        Slot& slot = ring[t % kSlots];
         if (p.normalize) {
-            // l2_normalize (qwen35.rs:762-768): f32 sum of squares, x *= scale / sqrt(sum + 1e-6).
-            float q2 = warp_sum(cur.q * cur.q), k2 = warp_sum(cur.k * cur.k);
-            if (lane == 0) {
-                scratch[buf][warp] = q2;
-                scratch[buf][8 + warp] = k2;
+            float q[PER], k[PER];
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                q[e] = slot.q[at(e * 32 + lane)];
+                k[e] = slot.k[at(e * 32 + lane)];
             }
-            __syncthreads();
-            float qsum = 0.f, ksum = 0.f;
-            for (uint32_t w = 0; w < n_warps; ++w) {
-                qsum += scratch[buf][w];
-                ksum += scratch[buf][8 + w];
+            const float q_scale = (1.0f / sqrtf((float)KDIM)) * l2_factor<PER>(q), k_scale = l2_factor<PER>(k);
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                slot.q[at(e * 32 + lane)] = q[e] * q_scale;
+                slot.k[at(e * 32 + lane)] = k[e] * k_scale;
             }
-            if (j < KDIM) {
-                qs[buf][j] = cur.q * ((1.0f / sqrtf((float)KDIM)) / sqrtf(qsum + 1e-6f));
-                ks[buf][j] = cur.k * (1.0f / sqrtf(ksum + 1e-6f));
-            }
-        } else if (j < KDIM) {
-            qs[buf][j] = cur.q;
-            ks[buf][j] = cur.k;
+            __syncwarp();
         }
-        __syncthreads();
+        const float decay = slot.decay, beta = slot.beta, v = j < vd ? slot.v[column] : 0.f;
+        // Every lane takes part in the shuffles; lanes past the last column carry zeros.
+        const float4* k4 = reinterpret_cast<const float4*>(slot.k + part * (MINE + 4));
+        const float4* q4 = reinterpret_cast<const float4*>(slot.q + part * (MINE + 4));
+        float r0 = 0.f, r1 = 0.f;
         if (j < vd) {
-            // Four partial sums per dot product: a single running sum would make each token a chain
-            // of KDIM dependent adds, which is what bounds this kernel. q and k come four at a time.
-            const float4* k4 = reinterpret_cast<const float4*>(ks[buf]);
-            const float4* q4 = reinterpret_cast<const float4*>(qs[buf]);
-            float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < KDIM / 4; ++i) {
-                const float4 kv = k4[i];
-                S[4 * i] *= cur.decay;
-                S[4 * i + 1] *= cur.decay;
-                S[4 * i + 2] *= cur.decay;
-                S[4 * i + 3] *= cur.decay;
-                r0 += S[4 * i] * kv.x;
-                r1 += S[4 * i + 1] * kv.y;
-                r2 += S[4 * i + 2] * kv.z;
-                r3 += S[4 * i + 3] * kv.w;
+            for (int i = 0; i < MINE / 4; ++i) {
+                const float4 kk = k4[i];
+                S[4 * i] *= decay;
+                S[4 * i + 1] *= decay;
+                S[4 * i + 2] *= decay;
+                S[4 * i + 3] *= decay;
+                r0 += S[4 * i] * kk.x + S[4 * i + 2] * kk.z;
+                r1 += S[4 * i + 1] * kk.y + S[4 * i + 3] * kk.w;
             }
-            const float delta = (cur.v - ((r0 + r1) + (r2 + r3))) * cur.beta;
-            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-#pragma unroll
-            for (int i = 0; i < KDIM / 4; ++i) {
-                const float4 kv = k4[i], qv = q4[i];
-                S[4 * i] += kv.x * delta;
-                S[4 * i + 1] += kv.y * delta;
-                S[4 * i + 2] += kv.z * delta;
-                S[4 * i + 3] += kv.w * delta;
-                o0 += S[4 * i] * qv.x;
-                o1 += S[4 * i + 1] * qv.y;
-                o2 += S[4 * i + 2] * qv.z;
-                o3 += S[4 * i + 3] * qv.w;
-            }
-            p.out[(uint64_t)t * p.n_v_heads * vd + head * vd + j] = (o0 + o1) + (o2 + o3);
         }
-        cur = next;
+        const float r_part = r0 + r1;
+        float r = 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) r += __shfl_sync(0xffffffffu, r_part, first_lane + q);  // the quarters in order
+        const float delta = (v - r) * beta;
+        float o0 = 0.f, o1 = 0.f;
+        if (j < vd) {
+#pragma unroll
+            for (int i = 0; i < MINE / 4; ++i) {
+                const float4 kk = k4[i], qq = q4[i];
+                S[4 * i] += kk.x * delta;
+                S[4 * i + 1] += kk.y * delta;
+                S[4 * i + 2] += kk.z * delta;
+                S[4 * i + 3] += kk.w * delta;
+                o0 += S[4 * i] * qq.x + S[4 * i + 2] * qq.z;
+                o1 += S[4 * i + 1] * qq.y + S[4 * i + 3] * qq.w;
+            }
+        }
+        const float o_part = o0 + o1;
+        float out = 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) out += __shfl_sync(0xffffffffu, o_part, first_lane + q);
+        if (j < vd && part == 0) p.out[(uint64_t)t * p.n_v_heads * vd + head * vd + j] = out;
     }
+    async::cp_async_wait<0>();
     if (j < vd) {
 #pragma unroll
-        for (int i = 0; i < KDIM; ++i) state[(uint64_t)i * vd + j] = S[i];
+        for (int i = 0; i < MINE; ++i) state[(uint64_t)i * vd + j] = S[i];
     }
 }
 
@@ -426,11 +484,21 @@ cudaError_t gdn_recurrence(cudaStream_t stream, const float* qkv, const float* b
     if (n_tokens == 0) return cudaSuccess;
     RecurrenceParams p{qkv, beta, decay, state, out, n_k_heads, n_v_heads, k_dim, v_dim, n_tokens, normalize ? 1 : 0};
     void* args[] = {&p};
-    // One thread per state column, and at least k_dim threads to stage q and k.
-    uint32_t threads = ((v_dim > k_dim ? v_dim : k_dim) + 31) / 32 * 32;
+    // A warp per 8 state columns of a head.
     const void* kernel = k_dim == 32 ? (const void*)gdn_recurrence_kernel<32> : k_dim == 64 ? (const void*)gdn_recurrence_kernel<64>
                        : k_dim == 96 ? (const void*)gdn_recurrence_kernel<96> : (const void*)gdn_recurrence_kernel<128>;
-    return launch_kernel(kernel, dim3(n_v_heads), dim3(threads), 0, stream, args);
+    const uint32_t units = n_v_heads * ((v_dim + 7) / 8);
+    return launch_kernel(kernel, dim3((units + kRecurrenceWarps - 1) / kRecurrenceWarps), dim3(32 * kRecurrenceWarps), 0, stream, args);
+}
+
+cudaError_t gdn_qk_norm(cudaStream_t stream, float* qkv, uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t n_tokens) {
+    if (n_tokens == 0) return cudaSuccess;
+    uint32_t conv_dim = 2 * n_k_heads * k_dim + n_v_heads * v_dim;
+    const uint32_t items = n_tokens * 2 * n_k_heads;
+    void* args[] = {&qkv, &n_k_heads, &conv_dim, &n_tokens};
+    const void* kernel = k_dim == 32 ? (const void*)gdn_qk_norm_kernel<32> : k_dim == 64 ? (const void*)gdn_qk_norm_kernel<64>
+                       : k_dim == 96 ? (const void*)gdn_qk_norm_kernel<96> : (const void*)gdn_qk_norm_kernel<128>;
+    return launch_kernel(kernel, dim3((items + 7) / 8), dim3(256), 0, stream, args);
 }
 
 bool gdn_step_supported(uint32_t n_k_heads, uint32_t n_v_heads, uint32_t k_dim, uint32_t v_dim, uint32_t kernel) {

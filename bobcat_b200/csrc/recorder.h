@@ -529,9 +529,11 @@ struct Recorder {
         run("gdn_conv", n, conv_dim(), 0, k::gdn_conv_launches(n), [&] { return k::gdn_conv(stream, s.gdn_qkv, D.conv1d, history, s.gdn_conv_out, conv_dim(), K, n); });
         run("gdn_gates", n, hp.n_v_heads, 0, 1, [&] { return k::gdn_gates(stream, s.gdn_beta, s.gdn_alpha, D.a, D.dt_bias, hp.n_v_heads, n); });
         uint64_t state_bytes = (uint64_t)hp.n_v_heads * hp.k_head_dim * hp.v_head_dim * 4 * 2;
+        run("gdn_qk_norm", n * 2 * hp.n_k_heads, hp.k_head_dim, 0, 1,
+            [&] { return k::gdn_qk_norm(stream, s.gdn_conv_out, hp.n_k_heads, hp.n_v_heads, hp.k_head_dim, hp.v_head_dim, n); });
         run("gdn_recurrence", n, value_dim(), state_bytes, 1, [&] {
             return k::gdn_recurrence(stream, s.gdn_conv_out, s.gdn_beta, s.gdn_alpha, state, s.gdn_out, hp.n_k_heads, hp.n_v_heads, hp.k_head_dim,
-                                     hp.v_head_dim, n, true);
+                                     hp.v_head_dim, n, false);
         });
         run("gdn_gated_norm", n * hp.n_v_heads, hp.v_head_dim, 0, 1,
             [&] { return k::gdn_gated_norm(stream, s.gdn_out, s.gdn_z, D.ssm_norm, hp.v_head_dim, n * hp.n_v_heads, hp.norm_eps); });

@@ -11,6 +11,7 @@ names the index and the logit gap at that step."""
 
 import json
 import os
+import warnings
 
 import numpy as np
 import pytest
@@ -58,18 +59,31 @@ def checker_run(ref, prompt, n_decode, want_trace=False, want_experts=False):
     return tokens, all_logits, layers, experts
 
 
+# Two candidates whose logits the checker itself separates by less than this fraction of the
+# step's largest logit are a tie: 1e-4 is the agreement the single-step f32 paths are held to, and
+# a sum taken in another order moves a logit by that much. A tie ends the comparison of that run at
+# that index (the sequences differ from there on by construction) and is recorded with its gap.
+TIE = 1e-4
+
+
 def assert_same_tokens(got, want, step_logits, label):
-    """Greedy tokens must be the checker's. On a difference, say where and how close the call was."""
+    """Greedy tokens must be the checker's. On a difference, say where and how close the call was;
+    only a tie by the checker's own logits is let through."""
     got = [int(t) for t in got]
     if got == want:
         note(test=label, tokens=len(want), identical=True)
         return
     i = next(j for j, (a, b) in enumerate(zip(got, want)) if a != b)
     lg = step_logits[i]
-    gap = float(lg[want[i]] - lg[got[i]])
-    note(test=label, tokens=len(want), identical=False, first_divergence=i, logit_gap=gap, logit_scale=float(np.abs(lg).max()))
+    gap, scale = float(lg[want[i]] - lg[got[i]]), float(np.abs(lg).max())
+    tie = 0.0 <= gap <= TIE * scale
+    note(test=label, tokens=len(want), identical=False, first_divergence=i, logit_gap=gap, logit_scale=scale, tie=tie)
+    if tie:
+        warnings.warn("%s: greedy token %d is a tie by the checker's logits (%d against %d, %.3g apart of a largest magnitude %.3g); "
+                      "%d tokens compared" % (label, i, want[i], got[i], gap, scale, i))
+        return
     raise AssertionError("%s: greedy token %d differs (checker %d, GPU %d); the checker's logits separate them by %.3g of a largest magnitude %.3g"
-                         % (label, i, want[i], got[i], gap, float(np.abs(lg).max())))
+                         % (label, i, want[i], got[i], gap, scale))
 
 
 def assert_logits(got, want, label, max_abs_bound=MAX_ABS):
