@@ -65,7 +65,14 @@ def test_two_ranks_decode_what_one_gpu_decodes(model_path, cuda, case, peer):
     single.prefill(prompt[:split], want_logits)
     for tok in prompt[split:]:
         single.step(int(tok), want_step)
-    want_tokens = single.generate(n_decode).tolist()
+    # The one-GPU sequence decodes step by step here, so that the logits behind every token are at
+    # hand: where the ranks' tokens part from it, the logits say whether that was a tie.
+    want_tokens, want_each = [], [want_step.copy()]
+    for _ in range(n_decode):
+        want_tokens.append(int(np.argmax(want_each[-1])))
+        nxt = np.zeros_like(want_logits)
+        single.step(want_tokens[-1], nxt)
+        want_each.append(nxt)
     single.close()
 
     world = 2
@@ -88,7 +95,16 @@ def test_two_ranks_decode_what_one_gpu_decodes(model_path, cuda, case, peer):
         # tilings); the stepped half with f32 operands (1e-4, the single-step tolerance).
         assert rel_error(logits, want_logits) < 5e-3, rank
         assert rel_error(step_logits, want_step) < (5e-3 if kv_half else 1e-4), rank
-        assert tokens == want_tokens, rank
+        if tokens != want_tokens:
+            # Sums over ranks associate differently, so a token may differ where the one-GPU logits
+            # themselves hold a tie: two candidates closer than the agreement this test asks of the
+            # logits (1e-4 of the largest logit with an f32 cache, 5e-3 with an f16 one). Anything
+            # wider is a failure.
+            i = next(j for j, (a, b) in enumerate(zip(tokens, want_tokens)) if a != b)
+            gap = float(want_each[i][want_tokens[i]] - want_each[i][tokens[i]])
+            scale = float(np.abs(want_each[i]).max())
+            assert 0.0 <= gap <= (5e-3 if kv_half else 1e-4) * scale, "rank %d: token %d differs (%d against %d), logits %.3g apart of %.3g" % (
+                rank, i, tokens[i], want_tokens[i], gap, scale)
         assert again == tokens, rank
     # Every rank holds the same logits bit for bit (the gathered vocabulary rows).
     assert np.array_equal(results[0][2], results[1][2])
