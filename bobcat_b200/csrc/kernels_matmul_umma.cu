@@ -121,6 +121,7 @@ struct UmmaParams {
 // thread writes one core-matrix row (16 bytes): 8 halves of one token.
 __global__ void __launch_bounds__(256) pack_kernel(const float* __restrict__ x, __half* __restrict__ packed, uint32_t n_tokens,
                                                    uint32_t n_cols, uint32_t token_groups, uint64_t total) {
+    pdl_launch_dependents();  // the product that reads this packing may set itself up meanwhile
     uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;  // index of the 16-byte output
     if (o >= total) return;
     uint32_t tr = o & 7, j = (o >> 3) & (kCores - 1);
@@ -149,6 +150,7 @@ __global__ void __launch_bounds__(256) pack_kernel(const float* __restrict__ x, 
 __global__ void __launch_bounds__(256) pack_norm_kernel(const float* __restrict__ x, const float* __restrict__ weight, float eps,
                                                         __half* __restrict__ packed, uint32_t n_tokens, uint32_t n_cols, uint32_t token_groups) {
     __shared__ float scales[8];
+    pdl_launch_dependents();
     const uint32_t tg = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     {
         const uint32_t token = tg * 8 + warp;
@@ -197,6 +199,7 @@ __global__ void __launch_bounds__(512) pack_norm_add_kernel(float* __restrict__ 
                                                             const float* __restrict__ partial, uint32_t split) {
     __shared__ float sums[4][4];
     __shared__ float scales[4];
+    pdl_launch_dependents();
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, token0 = blockIdx.x * 4;
     {
         const uint32_t token = token0 + (warp >> 2), cols4 = n_cols / 4;
@@ -255,6 +258,7 @@ __global__ void __launch_bounds__(512) pack_norm_add_kernel(float* __restrict__ 
 __global__ void __launch_bounds__(256) pack_grouped_kernel(const float* __restrict__ x, __half* __restrict__ packed, const uint32_t* __restrict__ offsets,
                                                            const uint32_t* __restrict__ entries, uint32_t n_experts, uint32_t n_used, int gather,
                                                            uint32_t n_cols, uint32_t cap_groups, uint32_t total_entries) {
+    pdl_launch_dependents();
     const uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const uint32_t n_chunks = n_cols / kChunkK;
     if (o >= (uint64_t)total_entries * n_chunks * kCores) return;
@@ -319,6 +323,13 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
     volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // Launched with the programmatic-dependency attribute: a CTA may start while the launch before
+    // it (the packing of this product's inputs, which needs next to no shared memory) still runs.
+    // The weights are nobody's output, so barriers, tensor memory and the producers' first loads
+    // go ahead; whatever reads or writes another launch's data waits first (the token-tile copies,
+    // the epilogue, and in grouped mode everything, since the grouping decides the CTA's work).
+    pdl_launch_dependents();
+    if (p.offsets) pdl_wait();
     // The matrix this row tile belongs to.
     uint32_t row_tile = blockIdx.y, w_rows = p.n_rows, w_stride = p.y_stride;
     const uint4* w_quants = p.quants[0];
@@ -512,6 +523,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
         if (kStaged) cp_async_wait<0>();
 
         // ---- epilogue: lanes 32 * (warp % 4).. of tensor memory, a quarter of the columns per warp
+        pdl_wait();  // y, the partial products and the packed output are other launches' to read or write until now
         alive = __all_sync(0xffffffffu, alive);
         if (alive && !mbar_wait(accum, 0, kSpinLimit, dead)) {
             give_up(dead, 2);
@@ -588,6 +600,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
     } else if (warp == kTmaWarp) {
         // ---- the token tiles: one bulk copy per stage
         if (lane == 0) {
+            pdl_wait();  // the packed inputs are the launch before's
             const uint32_t bytes = n_tile * kChunkK * 2;
             const __half* src = p.packed + (uint64_t)(group0 + tok0 / 8) * (8 * kChunkK);
             uint32_t stage = 0, phase = 1;
@@ -804,7 +817,11 @@ cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, 
     p.tile_tokens = tiling.tile_tokens;
     p.store = split > 1 ? BC_STORE_OVERWRITE : store;
     dim3 grid((n_tokens + tiling.tile_tokens - 1) / tiling.tile_tokens, (w.n_rows + kRows - 1) / kRows, split);
-    matmul_umma_kernel<1><<<grid, Shape<1>::kThreads, Shape<1>::kSmemBytes, stream>>>(p);
+    {
+        void* args[] = {&p};
+        cudaError_t launched = launch_kernel(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), grid, dim3(Shape<1>::kThreads), Shape<1>::kSmemBytes, stream, args);
+        if (launched != cudaSuccess) return launched;
+    }
     err = cudaGetLastError();
     if (err != cudaSuccess || split == 1) return err;
     if (defer && store == BC_STORE_ACCUMULATE && y_stride == w.n_rows) {
@@ -851,7 +868,11 @@ cudaError_t matmul_umma_several(cudaStream_t stream, const Mat* const* ws, float
     p.tile_tokens = choose_tiling(total_rows, ws[0]->n_cols, n_tokens, total_rows, 1, false).tile_tokens;
     p.store = BC_STORE_OVERWRITE;
     dim3 grid((n_tokens + p.tile_tokens - 1) / p.tile_tokens, tiles, 1);
-    matmul_umma_kernel<1><<<grid, Shape<1>::kThreads, Shape<1>::kSmemBytes, stream>>>(p);
+    {
+        void* args[] = {&p};
+        cudaError_t launched = launch_kernel(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), grid, dim3(Shape<1>::kThreads), Shape<1>::kSmemBytes, stream, args);
+        if (launched != cudaSuccess) return launched;
+    }
     return cudaGetLastError();
 }
 
@@ -884,7 +905,11 @@ cudaError_t matmul_umma_swiglu(cudaStream_t stream, const Mat& gate, const Mat& 
     p.store = BC_STORE_OVERWRITE;
     p.packed_out = static_cast<__half*>(packed_out);
     dim3 grid((n_tokens + p.tile_tokens - 1) / p.tile_tokens, (gate.n_rows + kRows - 1) / kRows, 1);
-    matmul_umma_kernel<2><<<grid, Shape<2>::kThreads, Shape<2>::kSmemBytes, stream>>>(p);
+    {
+        void* args[] = {&p};
+        cudaError_t launched = launch_kernel(reinterpret_cast<const void*>(&matmul_umma_kernel<2>), grid, dim3(Shape<2>::kThreads), Shape<2>::kSmemBytes, stream, args);
+        if (launched != cudaSuccess) return launched;
+    }
     return cudaGetLastError();
 }
 
@@ -934,10 +959,18 @@ cudaError_t matmul_experts_umma(cudaStream_t stream, const Mat& w, const Mat* up
     dim3 grid((n_tokens + p.tile_tokens - 1) / p.tile_tokens, (n_rows + kRows - 1) / kRows, n_experts);
     if (up) {
         if ((err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<2>), Shape<2>::kSmemBytes)) != cudaSuccess) return err;
-        matmul_umma_kernel<2><<<grid, Shape<2>::kThreads, Shape<2>::kSmemBytes, stream>>>(p);
+        {
+        void* args[] = {&p};
+        cudaError_t launched = launch_kernel(reinterpret_cast<const void*>(&matmul_umma_kernel<2>), grid, dim3(Shape<2>::kThreads), Shape<2>::kSmemBytes, stream, args);
+        if (launched != cudaSuccess) return launched;
+    }
     } else {
         if ((err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), Shape<1>::kSmemBytes)) != cudaSuccess) return err;
-        matmul_umma_kernel<1><<<grid, Shape<1>::kThreads, Shape<1>::kSmemBytes, stream>>>(p);
+        {
+        void* args[] = {&p};
+        cudaError_t launched = launch_kernel(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), grid, dim3(Shape<1>::kThreads), Shape<1>::kSmemBytes, stream, args);
+        if (launched != cudaSuccess) return launched;
+    }
     }
     return cudaGetLastError();
 }

@@ -223,6 +223,7 @@ __device__ __forceinline__ float short_conv_token(const float* __restrict__ bcx,
 __global__ void __launch_bounds__(256) short_conv_kernel(const float* __restrict__ bcx, const float* __restrict__ taps,
                                                          const float* __restrict__ history, float* __restrict__ out, __half* __restrict__ packed,
                                                          uint32_t n_embd, uint32_t kernel, uint32_t n_tokens) {
+    pdl_launch_dependents();  // the output projection that reads the packed results may set itself up meanwhile
     const uint32_t ch = blockIdx.x * blockDim.x + threadIdx.x;
     if (ch >= n_embd) return;
     if (packed) {
@@ -240,6 +241,7 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const float* __restrict
 // an older slot when the batch is shorter than the history. One thread per channel.
 __global__ void short_conv_history_kernel(const float* __restrict__ bcx, float* __restrict__ history, uint32_t n_embd, uint32_t kernel,
                                           uint32_t n_tokens) {
+    pdl_launch_dependents();
     const uint32_t ch = blockIdx.x * blockDim.x + threadIdx.x;
     if (ch >= n_embd) return;
     float next[8];
