@@ -5,6 +5,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <utility>
+
 #include <cstdint>
 
 namespace bc {
@@ -44,7 +46,24 @@ struct MatvecSegment {
 // may start while the launch before it still runs. Only for kernels that call pdl_wait() before
 // touching memory other launches write. `args` is the usual array of pointers to the arguments.
 cudaError_t launch_kernel(const void* kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, void** args);
+// Whether launches carry the programmatic-dependency attribute (BOBCAT_NO_PDL=1 turns it off).
 bool pdl_enabled();
+// launch_kernel for a kernel given by name, with its arguments as written in a <<<>>> launch. The
+// kernel must call pdl_wait() before it touches what an earlier launch wrote or still reads.
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+}
 // Raise `kernel`'s dynamic shared-memory limit to `smem` bytes on the current device if needed.
 cudaError_t ensure_dynamic_smem(const void* kernel, size_t smem);
 // Number of SMs of the current device.

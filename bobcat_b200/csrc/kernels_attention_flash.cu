@@ -64,6 +64,8 @@ __global__ void __launch_bounds__(kFlashThreads) attention_flash_kernel(FlashPar
     __shared__ __align__(16) __half k_tile[kKeys][kPitch];
     __shared__ __align__(16) __half v_tile[kKeys][kPitch];
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t q0 = blockIdx.x * kQueries, head = blockIdx.y;
@@ -256,7 +258,10 @@ cudaError_t attention_flash(cudaStream_t stream, const float* q, const void* k_c
     FlashParams p{q, static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), out, s.n_heads, s.n_kv_heads,
                   s.first_pos, s.n_queries, s.q_stride, s.q_head_stride};
     dim3 grid((s.n_queries + kQueries - 1) / kQueries, s.n_heads);
-    attention_flash_kernel<<<grid, kFlashThreads, 0, stream>>>(p);
+    {
+        cudaError_t launched = launch_dependent(attention_flash_kernel, grid, dim3(kFlashThreads), 0, stream, p);
+        if (launched != cudaSuccess) return launched;
+    }
     return cudaGetLastError();
 }
 

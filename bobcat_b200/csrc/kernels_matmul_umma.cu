@@ -122,6 +122,7 @@ struct UmmaParams {
 __global__ void __launch_bounds__(256) pack_kernel(const float* __restrict__ x, __half* __restrict__ packed, uint32_t n_tokens,
                                                    uint32_t n_cols, uint32_t token_groups, uint64_t total) {
     pdl_launch_dependents();  // the product that reads this packing may set itself up meanwhile
+    pdl_wait();
     uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;  // index of the 16-byte output
     if (o >= total) return;
     uint32_t tr = o & 7, j = (o >> 3) & (kCores - 1);
@@ -151,6 +152,7 @@ __global__ void __launch_bounds__(256) pack_norm_kernel(const float* __restrict_
                                                         __half* __restrict__ packed, uint32_t n_tokens, uint32_t n_cols, uint32_t token_groups) {
     __shared__ float scales[8];
     pdl_launch_dependents();
+    pdl_wait();
     const uint32_t tg = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     {
         const uint32_t token = tg * 8 + warp;
@@ -200,6 +202,7 @@ __global__ void __launch_bounds__(512) pack_norm_add_kernel(float* __restrict__ 
     __shared__ float sums[4][4];
     __shared__ float scales[4];
     pdl_launch_dependents();
+    pdl_wait();
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, token0 = blockIdx.x * 4;
     {
         const uint32_t token = token0 + (warp >> 2), cols4 = n_cols / 4;
@@ -259,6 +262,7 @@ __global__ void __launch_bounds__(256) pack_grouped_kernel(const float* __restri
                                                            const uint32_t* __restrict__ entries, uint32_t n_experts, uint32_t n_used, int gather,
                                                            uint32_t n_cols, uint32_t cap_groups, uint32_t total_entries) {
     pdl_launch_dependents();
+    pdl_wait();
     const uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const uint32_t n_chunks = n_cols / kChunkK;
     if (o >= (uint64_t)total_entries * n_chunks * kCores) return;
@@ -664,6 +668,8 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
 // y (store) the sum of the `split` partial products, added in index order.
 __global__ void __launch_bounds__(256) reduce_kernel(const float* __restrict__ partial, float* __restrict__ y, uint32_t n_rows,
                                                      uint32_t n_tokens, uint32_t y_stride, uint32_t split, int store) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint64_t total = (uint64_t)n_tokens * n_rows;
     const uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= total) return;  // n_rows is a multiple of 4 here, so a float4 never straddles tokens
@@ -763,8 +769,8 @@ cudaError_t matmul_pack(cudaStream_t stream, const float* x, uint32_t n_tokens, 
     uint32_t token_groups = ((n_tokens + 15u) & ~15u) / 8;
     uint64_t total = (uint64_t)(n_cols / kChunkK) * token_groups * (8 * kCores);
     if (total == 0) return cudaSuccess;
-    pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, static_cast<__half*>(packed), n_tokens, n_cols, token_groups, total);
-    return cudaGetLastError();
+    return launch_dependent(pack_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, static_cast<__half*>(packed), n_tokens, n_cols,
+                            token_groups, total);
 }
 
 cudaError_t matmul_pack_norm(cudaStream_t stream, float* x, Norm norm, uint32_t n_tokens, uint32_t n_cols, void* packed, const Deferred* add) {
@@ -774,20 +780,18 @@ cudaError_t matmul_pack_norm(cudaStream_t stream, float* x, Norm norm, uint32_t 
     if (adding && (add->n_tokens != n_tokens || add->n_rows != n_cols || n_cols % 4 != 0)) return cudaErrorInvalidValue;
     const uint32_t shares = token_groups >= 256 ? 1 : token_groups >= 64 ? 4 : 8;
     if (adding) {
-        pack_norm_add_kernel<<<token_groups * 2, 512, 0, stream>>>(x, norm.weight, norm.eps, static_cast<__half*>(packed), n_tokens, n_cols, token_groups,
-                                                               add->partial, add->split);
-        return cudaGetLastError();
+        return launch_dependent(pack_norm_add_kernel, dim3(token_groups * 2), dim3(512), 0, stream, x, norm.weight, norm.eps, static_cast<__half*>(packed),
+                                n_tokens, n_cols, token_groups, add->partial, add->split);
     }
-    pack_norm_kernel<<<dim3(token_groups, shares), 256, 0, stream>>>(x, norm.weight, norm.eps, static_cast<__half*>(packed), n_tokens, n_cols,
-                                                                    token_groups);
-    return cudaGetLastError();
+    return launch_dependent(pack_norm_kernel, dim3(token_groups, shares), dim3(256), 0, stream, static_cast<const float*>(x), norm.weight, norm.eps,
+                            static_cast<__half*>(packed), n_tokens, n_cols, token_groups);
 }
 
 cudaError_t matmul_reduce(cudaStream_t stream, const Deferred& d, float* y) {
     if (!d.partial || d.n_tokens == 0) return cudaSuccess;
     const uint64_t quads = (uint64_t)d.n_tokens * d.n_rows / 4;
-    reduce_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(d.partial, y, d.n_rows, d.n_tokens, d.n_rows, d.split, BC_STORE_ACCUMULATE);
-    return cudaGetLastError();
+    return launch_dependent(reduce_kernel, dim3((unsigned)((quads + 255) / 256)), dim3(256), 0, stream, d.partial, y, d.n_rows, d.n_tokens, d.n_rows, d.split,
+                            (int)BC_STORE_ACCUMULATE);
 }
 
 cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, float* y, uint32_t n_tokens, uint32_t y_stride,
@@ -829,8 +833,8 @@ cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, 
         return cudaSuccess;
     }
     const uint64_t quads = (uint64_t)n_tokens * w.n_rows / 4;
-    reduce_kernel<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(partial, y, w.n_rows, n_tokens, y_stride, split, store);
-    return cudaGetLastError();
+    return launch_dependent(reduce_kernel, dim3((unsigned)((quads + 255) / 256)), dim3(256), 0, stream, static_cast<const float*>(partial), y, w.n_rows,
+                            n_tokens, y_stride, split, (int)store);
 }
 
 cudaError_t matmul_umma_several(cudaStream_t stream, const Mat* const* ws, float* const* ys, int n, const void* packed, uint32_t n_tokens) {
@@ -930,9 +934,8 @@ cudaError_t matmul_experts_umma(cudaStream_t stream, const Mat& w, const Mat* up
     if (n_tokens == 0 || n_rows == 0) return cudaSuccess;
     const uint32_t cap_groups = ((n_tokens + 15u) & ~15u) / 8, total = n_tokens * n_used;
     const uint64_t outputs = (uint64_t)total * (w.n_cols / kChunkK) * kCores;
-    pack_grouped_kernel<<<(unsigned)((outputs + 255) / 256), 256, 0, stream>>>(x, static_cast<__half*>(scratch), offsets, entries, n_experts, n_used,
-                                                                            gather ? 1 : 0, w.n_cols, cap_groups, total);
-    cudaError_t err = cudaGetLastError();
+    cudaError_t err = launch_dependent(pack_grouped_kernel, dim3((unsigned)((outputs + 255) / 256)), dim3(256), 0, stream, x, static_cast<__half*>(scratch),
+                                       offsets, entries, n_experts, n_used, gather ? 1 : 0, w.n_cols, cap_groups, total);
     if (err != cudaSuccess) return err;
     UmmaParams p{};
     p.quants[0] = static_cast<const uint4*>(w.data);

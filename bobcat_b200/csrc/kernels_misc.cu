@@ -64,6 +64,8 @@ __global__ void expand_q4_0_kernel(const uint4* __restrict__ quants, const __hal
 
 template <typename In, typename Out>
 __global__ void convert_kernel(const In* __restrict__ src, Out* __restrict__ dst, uint64_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[i] = (Out)(float)src[i];
 }
@@ -120,6 +122,8 @@ __global__ void embed_kernel(Mat w, const uint32_t* __restrict__ tokens, Pos pos
 __global__ void __launch_bounds__(kThreads) rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ weight,
                                                              float* __restrict__ out, uint32_t n_cols, float eps) {
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = x + (uint64_t)blockIdx.x * n_cols;
     float* o = out + (uint64_t)blockIdx.x * n_cols;
     float sumsq = 0.f;
@@ -143,6 +147,8 @@ struct NormRopeParams {
 // and angle in f32, as scalar::rope_neox does, crates/bobcat/src/scalar.rs:253-266), then the
 // store as f32 or half. grid (n_heads, n_tokens), 32 threads.
 __global__ void norm_rope_kernel(NormRopeParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x;
     const uint32_t head = blockIdx.x, token = blockIdx.y;
     const float* src = p.src + (uint64_t)token * p.src_stride + (uint64_t)head * p.head_stride;
@@ -224,6 +230,7 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const float* __restrict
                                                          const float* __restrict__ history, float* __restrict__ out, __half* __restrict__ packed,
                                                          uint32_t n_embd, uint32_t kernel, uint32_t n_tokens) {
     pdl_launch_dependents();  // the output projection that reads the packed results may set itself up meanwhile
+    pdl_wait();
     const uint32_t ch = blockIdx.x * blockDim.x + threadIdx.x;
     if (ch >= n_embd) return;
     if (packed) {
@@ -242,6 +249,7 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const float* __restrict
 __global__ void short_conv_history_kernel(const float* __restrict__ bcx, float* __restrict__ history, uint32_t n_embd, uint32_t kernel,
                                           uint32_t n_tokens) {
     pdl_launch_dependents();
+    pdl_wait();
     const uint32_t ch = blockIdx.x * blockDim.x + threadIdx.x;
     if (ch >= n_embd) return;
     float next[8];
@@ -472,7 +480,10 @@ cudaError_t embed(cudaStream_t stream, const Mat& w, const uint32_t* tokens, Pos
 cudaError_t rms_norm(cudaStream_t stream, const float* x, const float* weight, float* out, uint32_t n_cols, uint32_t n_rows,
                      float eps) {
     if (n_rows == 0) return cudaSuccess;
-    rms_norm_kernel<<<n_rows, kThreads, 0, stream>>>(x, weight, out, n_cols, eps);
+    {
+        cudaError_t launched = launch_dependent(rms_norm_kernel, dim3(n_rows), dim3(kThreads), 0, stream, x, weight, out, n_cols, eps);
+        if (launched != cudaSuccess) return launched;
+    }
     return cudaGetLastError();
 }
 
@@ -482,13 +493,19 @@ cudaError_t norm_rope(cudaStream_t stream, const float* src, void* dst, bool dst
     if (n_tokens == 0 || n_heads == 0) return cudaSuccess;
     NormRopeParams p{src, dst, weight, n_heads, head_dim, head_stride, n_rot, first_pos, src_stride, dst_stride, theta, eps, dst_half ? 1 : 0};
     dim3 grid(n_heads, n_tokens);
-    norm_rope_kernel<<<grid, 32, 0, stream>>>(p);
+    {
+        cudaError_t launched = launch_dependent(norm_rope_kernel, grid, dim3(32), 0, stream, p);
+        if (launched != cudaSuccess) return launched;
+    }
     return cudaGetLastError();
 }
 
 cudaError_t convert_half(cudaStream_t stream, const float* src, __half* dst, uint64_t n) {
     if (n == 0) return cudaSuccess;
-    convert_kernel<float, __half><<<blocks_for(n), kThreads, 0, stream>>>(src, dst, n);
+    {
+        cudaError_t launched = launch_dependent(convert_kernel<float, __half>, dim3(blocks_for(n)), dim3(kThreads), 0, stream, src, dst, n);
+        if (launched != cudaSuccess) return launched;
+    }
     return cudaGetLastError();
 }
 
@@ -508,10 +525,10 @@ cudaError_t short_conv(cudaStream_t stream, const float* bcx, const float* taps,
     if (n_tokens == 0) return cudaSuccess;
     if (packed && n_embd % 64 != 0) return cudaErrorInvalidValue;
     const uint32_t rows = packed ? ((n_tokens + 15u) & ~15u) : n_tokens;
-    short_conv_kernel<<<dim3(blocks_for(n_embd, 256), rows < 65535u ? rows : 65535u), 256, 0, stream>>>(bcx, taps, history, out,
-                                                                                                     static_cast<__half*>(packed), n_embd, kernel, n_tokens);
-    short_conv_history_kernel<<<blocks_for(n_embd, 128), 128, 0, stream>>>(bcx, history, n_embd, kernel, n_tokens);
-    return cudaGetLastError();
+    cudaError_t e = launch_dependent(short_conv_kernel, dim3(blocks_for(n_embd, 256), rows < 65535u ? rows : 65535u), dim3(256), 0, stream, bcx, taps,
+                                     static_cast<const float*>(history), out, static_cast<__half*>(packed), n_embd, kernel, n_tokens);
+    if (e != cudaSuccess) return e;
+    return launch_dependent(short_conv_history_kernel, dim3(blocks_for(n_embd, 128)), dim3(128), 0, stream, bcx, history, n_embd, kernel, n_tokens);
 }
 
 cudaError_t argmax(cudaStream_t stream, const float* x, uint32_t n, uint32_t* out, uint32_t* readback) {
