@@ -139,7 +139,9 @@ struct Recorder {
         const uint64_t partial_bytes = k::matmul_partial_bytes(w, n);
         if (status == BC_OK && partial_bytes) status = s.backend->partial_scratch(partial_bytes, &partial);
         k::Deferred left{};
-        const bool may_defer = store == BC_STORE_ACCUMULATE;
+        // The normalisation that would take the sum runs one CTA per 4 tokens: with few rows the
+        // separate, wide sum is quicker.
+        const bool may_defer = store == BC_STORE_ACCUMULATE && n >= 128;
         run("matmul", w.n_rows, w.n_cols, w.bytes(), 1, [&] {
             return k::matmul_umma(stream, w, packed, y, n, w.n_rows, store, static_cast<float*>(partial), may_defer ? &left : nullptr);
         });
