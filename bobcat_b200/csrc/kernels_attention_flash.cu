@@ -1,7 +1,8 @@
-// Prefill attention for heads of 64 elements over an f16 cache: one CTA per (64 queries, head),
-// 64-key tiles, online softmax, the two products on tensor cores. Counterpart of attention_flash
-// (crates/bobcat-metal/src/attention.metal:290-480), which the reference uses under the same
-// conditions (head_dim == 64 and at least 32 queries, backend.rs:2185-2225).
+// Prefill attention for heads of 64, 128 or 256 elements over an f16 cache: one CTA per (64
+// queries, head), 64-key tiles, online softmax, the two products on tensor cores. Counterpart of
+// attention_flash (crates/bobcat-metal/src/attention.metal:290-480), which the reference uses for
+// head_dim == 64 and at least 32 queries (backend.rs:2185-2225); the wider heads (Qwen3.5's
+// attention layers have 256 elements) take the same path here instead of the chunk kernels.
 //
 // Arithmetic. Keys and values are the cache's fp16 values, exactly. The scaled query and the
 // probabilities are each split into two fp16 halves (value = hi + lo, about 22 bits), so neither
@@ -10,7 +11,8 @@
 // f32, as in the chunk kernels.
 //
 // A warp owns 16 queries. Scores S = Q K^T come from mma.m16n8k16 with the query fragments held in
-// registers and key fragments read with ldmatrix from the staged tile; the accumulator layout of S
+// registers (heads of 64; wider heads re-read them from the staged queries at every step, their
+// registers hold the output instead) and key fragments read with ldmatrix from the staged tile; the accumulator layout of S
 // is the A-fragment layout of the second product, so probabilities go from registers straight into
 // P V, whose value fragments are ldmatrix.trans reads of the staged tile.
 
@@ -22,11 +24,14 @@ namespace k {
 
 namespace {
 
-constexpr int kHead = 64;      // head_dim
 constexpr int kQueries = 64;   // queries per CTA: 4 warps x 16
 constexpr int kKeys = 64;      // keys per tile
-constexpr int kPitch = kHead + 8;  // halves per staged row: 144 bytes, so ldmatrix rows fall in distinct banks
 constexpr int kFlashThreads = 128;
+// Halves per staged row: 16 bytes more than the head, so the 8 rows of an ldmatrix fall in distinct banks.
+template <int HD>
+constexpr int flash_pitch() { return HD + 8; }
+template <int HD>
+constexpr size_t flash_smem_bytes() { return (size_t)(2 * kQueries + 2 * kKeys) * flash_pitch<HD>() * 2; }
 
 struct FlashParams {
     const float* q;
@@ -58,11 +63,15 @@ __device__ __forceinline__ void split_half2(float x, float y, uint32_t& hi, uint
     lo = *reinterpret_cast<uint32_t*>(&l);
 }
 
+template <int HD>
 __global__ void __launch_bounds__(kFlashThreads) attention_flash_kernel(FlashParams p) {
-    __shared__ __align__(16) __half q_hi[kQueries][kPitch];
-    __shared__ __align__(16) __half q_lo[kQueries][kPitch];
-    __shared__ __align__(16) __half k_tile[kKeys][kPitch];
-    __shared__ __align__(16) __half v_tile[kKeys][kPitch];
+    constexpr int kHead = HD, kPitch = flash_pitch<HD>();
+    constexpr bool kQueriesInRegisters = HD == 64;
+    extern __shared__ __align__(16) uint8_t flash_smem[];
+    __half (*q_hi)[kPitch] = reinterpret_cast<__half (*)[kPitch]>(flash_smem);
+    __half (*q_lo)[kPitch] = q_hi + kQueries;
+    __half (*k_tile)[kPitch] = q_lo + kQueries;
+    __half (*v_tile)[kPitch] = k_tile + kKeys;
 
     pdl_launch_dependents();
     pdl_wait();
@@ -72,7 +81,7 @@ __global__ void __launch_bounds__(kFlashThreads) attention_flash_kernel(FlashPar
     const uint32_t kv_head = head / (p.n_heads / p.n_kv_heads);
     const uint32_t kv_dim = p.n_kv_heads * kHead;
     const uint32_t kv_len = p.first_pos + p.n_queries;  // cache rows that exist
-    const float scale = 0.125f;                          // 1 / sqrt(64)
+    const float scale = 1.0f / sqrtf((float)kHead);
 
     // Stage the scaled queries as hi + lo halves; rows past the batch are zero.
     for (int i = tid; i < kQueries * (kHead / 2); i += kFlashThreads) {
@@ -89,22 +98,23 @@ __global__ void __launch_bounds__(kFlashThreads) attention_flash_kernel(FlashPar
     }
     __syncthreads();
 
-    // Query fragments: 4 k-steps of 16 elements, hi and lo.
-    uint32_t qa_hi[4][4], qa_lo[4][4];
-    {
+    // Query fragments: k-steps of 16 elements, hi and lo.
+    constexpr int kHeld = kQueriesInRegisters ? kHead / 16 : 1;
+    uint32_t qa_hi[kHeld][4], qa_lo[kHeld][4];
+    auto query_fragments = [&](int ks, uint32_t (&hi)[4], uint32_t (&lo)[4]) {
         const int m = lane >> 3, r = lane & 7;
-        const int row = warp * 16 + (m & 1) * 8 + r;
+        const int row = warp * 16 + (m & 1) * 8 + r, col = ks * 16 + (m >> 1) * 8;
+        ldmatrix_x4(hi, (uint32_t)__cvta_generic_to_shared(&q_hi[row][col]));
+        ldmatrix_x4(lo, (uint32_t)__cvta_generic_to_shared(&q_lo[row][col]));
+    };
+    if (kQueriesInRegisters) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            const int col = ks * 16 + (m >> 1) * 8;
-            ldmatrix_x4(qa_hi[ks], (uint32_t)__cvta_generic_to_shared(&q_hi[row][col]));
-            ldmatrix_x4(qa_lo[ks], (uint32_t)__cvta_generic_to_shared(&q_lo[row][col]));
-        }
+        for (int ks = 0; ks < kHeld; ++ks) query_fragments(ks, qa_hi[ks], qa_lo[ks]);
     }
 
-    float o[8][4];
+    float o[kHead / 8][4];
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int n = 0; n < kHead / 8; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
@@ -145,15 +155,18 @@ __global__ void __launch_bounds__(kFlashThreads) attention_flash_kernel(FlashPar
         {
             const int m = lane >> 3, r = lane & 7;
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
+            for (int ks = 0; ks < kHead / 16; ++ks) {
+                if (!kQueriesInRegisters) query_fragments(ks, qa_hi[0], qa_lo[0]);
+                const uint32_t (&a_hi)[4] = qa_hi[kQueriesInRegisters ? ks : 0];
+                const uint32_t (&a_lo)[4] = qa_lo[kQueriesInRegisters ? ks : 0];
 #pragma unroll
                 for (int np = 0; np < 4; ++np) {  // pairs of key tiles
                     uint32_t b[4];
                     ldmatrix_x4(b, (uint32_t)__cvta_generic_to_shared(&k_tile[np * 16 + (m >> 1) * 8 + r][ks * 16 + (m & 1) * 8]));
-                    mma_f16(s[2 * np], qa_hi[ks], b[0], b[1]);
-                    mma_f16(s[2 * np], qa_lo[ks], b[0], b[1]);
-                    mma_f16(s[2 * np + 1], qa_hi[ks], b[2], b[3]);
-                    mma_f16(s[2 * np + 1], qa_lo[ks], b[2], b[3]);
+                    mma_f16(s[2 * np], a_hi, b[0], b[1]);
+                    mma_f16(s[2 * np], a_lo, b[0], b[1]);
+                    mma_f16(s[2 * np + 1], a_hi, b[2], b[3]);
+                    mma_f16(s[2 * np + 1], a_lo, b[2], b[3]);
                 }
             }
         }
@@ -204,7 +217,7 @@ __global__ void __launch_bounds__(kFlashThreads) attention_flash_kernel(FlashPar
             row_sum[h] = row_sum[h] * correction[h] + tile_sum[h];
         }
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
+        for (int n = 0; n < kHead / 8; ++n) {
             o[n][0] *= correction[0];
             o[n][1] *= correction[0];
             o[n][2] *= correction[1];
@@ -221,7 +234,7 @@ __global__ void __launch_bounds__(kFlashThreads) attention_flash_kernel(FlashPar
                 split_half2(s[2 * kk + 1][0], s[2 * kk + 1][1], pa_hi[2], pa_lo[2]);
                 split_half2(s[2 * kk + 1][2], s[2 * kk + 1][3], pa_hi[3], pa_lo[3]);
 #pragma unroll
-                for (int np = 0; np < 4; ++np) {  // pairs of 8-element output tiles
+                for (int np = 0; np < kHead / 16; ++np) {  // pairs of 8-element output tiles
                     uint32_t b[4];
                     ldmatrix_x4_trans(b, (uint32_t)__cvta_generic_to_shared(&v_tile[kk * 16 + (m & 1) * 8 + r][np * 16 + (m >> 1) * 8]));
                     mma_f16(o[2 * np], pa_hi, b[0], b[1]);
@@ -237,7 +250,7 @@ __global__ void __launch_bounds__(kFlashThreads) attention_flash_kernel(FlashPar
     const uint32_t query_a = q0 + warp * 16 + g, query_b = query_a + 8;
     const float inv_a = 1.f / row_sum[0], inv_b = 1.f / row_sum[1];
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+    for (int n = 0; n < kHead / 8; ++n) {
         const uint32_t col = head * kHead + n * 8 + 2 * t;
         if (query_a < p.n_queries)
             *reinterpret_cast<float2*>(p.out + (uint64_t)query_a * p.n_heads * kHead + col) = make_float2(o[n][0] * inv_a, o[n][1] * inv_a);
@@ -249,8 +262,8 @@ __global__ void __launch_bounds__(kFlashThreads) attention_flash_kernel(FlashPar
 }  // namespace
 
 bool attention_flash_supported(bool kv_half, const AttentionShape& s) {
-    return kv_half && s.head_dim == kHead && s.n_queries >= 32 && s.pos_ptr == nullptr && s.n_kv_heads > 0 && s.n_heads % s.n_kv_heads == 0 &&
-           s.q_stride % 2 == 0 && s.q_head_stride % 2 == 0;
+    return kv_half && (s.head_dim == 64 || s.head_dim == 128 || s.head_dim == 256) && s.n_queries >= 32 && s.pos_ptr == nullptr &&
+           s.n_kv_heads > 0 && s.n_heads % s.n_kv_heads == 0 && s.q_stride % 2 == 0 && s.q_head_stride % 2 == 0;
 }
 
 cudaError_t attention_flash(cudaStream_t stream, const float* q, const void* k_cache, const void* v_cache, float* out,
@@ -258,11 +271,18 @@ cudaError_t attention_flash(cudaStream_t stream, const float* q, const void* k_c
     FlashParams p{q, static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), out, s.n_heads, s.n_kv_heads,
                   s.first_pos, s.n_queries, s.q_stride, s.q_head_stride};
     dim3 grid((s.n_queries + kQueries - 1) / kQueries, s.n_heads);
-    {
-        cudaError_t launched = launch_dependent(attention_flash_kernel, grid, dim3(kFlashThreads), 0, stream, p);
-        if (launched != cudaSuccess) return launched;
+    cudaError_t e;
+    switch (s.head_dim) {
+        case 64:
+            if ((e = ensure_dynamic_smem((const void*)attention_flash_kernel<64>, flash_smem_bytes<64>())) != cudaSuccess) return e;
+            return launch_dependent(attention_flash_kernel<64>, grid, dim3(kFlashThreads), flash_smem_bytes<64>(), stream, p);
+        case 128:
+            if ((e = ensure_dynamic_smem((const void*)attention_flash_kernel<128>, flash_smem_bytes<128>())) != cudaSuccess) return e;
+            return launch_dependent(attention_flash_kernel<128>, grid, dim3(kFlashThreads), flash_smem_bytes<128>(), stream, p);
+        default:
+            if ((e = ensure_dynamic_smem((const void*)attention_flash_kernel<256>, flash_smem_bytes<256>())) != cudaSuccess) return e;
+            return launch_dependent(attention_flash_kernel<256>, grid, dim3(kFlashThreads), flash_smem_bytes<256>(), stream, p);
     }
-    return cudaGetLastError();
 }
 
 }  // namespace k

@@ -179,12 +179,15 @@ def test_norm_rope_matches_scalar(cuda, head_dim, n_rot, dst_half):
 # (first_pos, n_queries, n_heads, n_kv_heads, head_dim): crates/bobcat/tests/metal_attention.rs:19-27
 ATTENTION_CASES = [(0, 1, 4, 2, 64), (5, 1, 4, 2, 64), (63, 3, 8, 2, 64), (100, 70, 4, 4, 32), (0, 130, 4, 1, 64), (37, 2, 2, 1, 256), (700, 1, 32, 8, 64),
                    (0, 512, 8, 2, 64), (100, 70, 8, 2, 64), (3, 33, 4, 2, 64), (61, 200, 4, 4, 64), (45, 1, 8, 1, 128), (130, 4, 16, 4, 128),
-                   (15, 2, 6, 2, 64), (300, 1, 4, 4, 256)]
+                   (15, 2, 6, 2, 64), (300, 1, 4, 4, 256),
+                   # Batches of wide heads on the tensor-core prefill kernel (Qwen3.5's attention layers: 256 elements).
+                   (50, 96, 8, 2, 256), (0, 64, 4, 1, 128), (300, 40, 16, 4, 256), (1000, 33, 2, 1, 256)]
 
 
 def on_flash_kernel(kv_half, n_q, hd):
-    """The shapes attention sends to its tensor-core prefill kernel (the reference's own rule for its flash kernel)."""
-    return kv_half and hd == 64 and n_q >= 32
+    """The shapes attention sends to its tensor-core prefill kernel (the reference's rule for its flash kernel, which
+    knows heads of 64, extended to heads of 128 and 256)."""
+    return kv_half and hd in (64, 128, 256) and n_q >= 32
 
 
 def attention_f64(q, k, v, first_pos, n_heads, n_kv_heads):
