@@ -335,8 +335,8 @@ cudaError_t matmul_pack_norm(cudaStream_t stream, float* x, Norm norm, uint32_t 
 // open and describes it there (defer->partial stays null when the launch did not split).
 cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* packed, float* y, uint32_t n_tokens, uint32_t y_stride,
                         int32_t store, float* partial = nullptr, Deferred* defer = nullptr);
-// Up to three products that read the same packed inputs, in one launch (q, k and v of an attention
-// layer): ys[i] = ws[i] x for every token, rows of ws[i]->n_rows floats, overwritten.
+// Up to four products that read the same packed inputs, in one launch (q, k and v of an attention
+// layer; the projections of a DeltaNet layer): ys[i] = ws[i] x for every token, rows of ws[i]->n_rows floats, overwritten.
 cudaError_t matmul_umma_several(cudaStream_t stream, const Mat* const* ws, float* const* ys, int n, const void* packed, uint32_t n_tokens);
 // y += the deferred partial products, in index order.
 cudaError_t matmul_reduce(cudaStream_t stream, const Deferred& d, float* y);

@@ -104,14 +104,15 @@ struct UmmaParams {
     const uint32_t* offsets;
     const uint32_t* entries;
     uint32_t cap_groups;
-    // DUAL == 1 only: further matrices that read the same packed inputs in the same launch (q, k, v).
+    // DUAL == 1 only: up to three further matrices that read the same packed inputs in the same launch
+    // (q, k, v; the four projections of a DeltaNet layer).
     // Row tiles [more_first[i], next) belong to matrix i + 1, which overwrites its own output of
     // more_rows[i] floats per token. No K split, no grouping.
     uint32_t n_more;
-    uint32_t more_first[2], more_rows[2];
-    const uint4* more_quants[2];
-    const __half* more_scales[2];
-    float* more_y[2];
+    uint32_t more_first[3], more_rows[3];
+    const uint4* more_quants[3];
+    const __half* more_scales[3];
+    float* more_y[3];
     // DUAL == 2 only: when set, silu(gate) * up is written as the fp16 operand of the product that
     // consumes it (the layout of pack_kernel for n_rows columns and the same tokens) instead of to y.
     __half* packed_out;
@@ -343,6 +344,7 @@ __global__ void __launch_bounds__(Shape<DUAL>::kThreads, 1) matmul_umma_kernel(U
         int m = -1;
         if (row_tile >= p.more_first[0]) m = 0;
         if (p.n_more > 1 && row_tile >= p.more_first[1]) m = 1;
+        if (p.n_more > 2 && row_tile >= p.more_first[2]) m = 2;
         if (m >= 0) {
             row_tile -= p.more_first[m];
             w_rows = w_stride = p.more_rows[m];
@@ -838,7 +840,7 @@ cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, 
 }
 
 cudaError_t matmul_umma_several(cudaStream_t stream, const Mat* const* ws, float* const* ys, int n, const void* packed, uint32_t n_tokens) {
-    if (n < 1 || n > 3) return cudaErrorInvalidValue;
+    if (n < 1 || n > 4) return cudaErrorInvalidValue;
     if (n_tokens == 0) return cudaSuccess;
     cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), Shape<1>::kSmemBytes);
     if (err != cudaSuccess) return err;

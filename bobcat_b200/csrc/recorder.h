@@ -230,12 +230,12 @@ struct Recorder {
         void* scratch = nullptr;
         if (status == BC_OK) status = s.backend->pack_scratch(bytes, &scratch);
         pack_normed(const_cast<float*>(x), norm_weight, n, cols, scratch);
-        // Products that only overwrite their outputs (q, k, v) share one launch.
-        bool together = products.size() > 1 && products.size() <= 3;
+        // Products that only overwrite their outputs (q, k, v; a DeltaNet layer's four projections) share one launch.
+        bool together = products.size() > 1 && products.size() <= 4;
         for (const Product& q : products) together = together && q.store == BC_STORE_OVERWRITE;
         if (together) {
-            const k::Mat* ws[3];
-            float* ys[3];
+            const k::Mat* ws[4];
+            float* ys[4];
             uint32_t rows = 0;
             uint64_t bytes_read = 0;
             int count = 0;
