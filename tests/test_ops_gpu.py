@@ -362,6 +362,27 @@ def test_matmul_stores(cuda, fmt, shape):
         b.free()
 
 
+@pytest.mark.parametrize("shape", [(100, 64, 5), (64, 2048, 32), (1000, 96, 17), (129, 32, 1), (4096, 1024, 32)])
+def test_matmul_f32_few_tokens(cuda, shape):
+    """An f32 matrix against at most 32 tokens (the logits of a pass over several sequences) runs on
+    a kernel of its own: ragged row counts, fewer than 32 tokens, and nothing written past the
+    tokens asked for."""
+    n_rows, n_cols, n_tokens = shape
+    rng = np.random.default_rng(sum(shape))
+    raw, w = make_matrix(rng, F32, n_rows, n_cols)
+    x = rng.uniform(-1, 1, (n_tokens, n_cols)).astype(np.float32)
+    y0 = np.full((n_tokens + 1, n_rows), 7.5, dtype=np.float32)
+    wb = cuda.upload_matrix(F32, raw, n_rows, n_cols)
+    xb, yb = cuda.buffer_from(x), cuda.buffer_from(y0)
+    cuda.begin(); cuda.matmul(F32, wb, n_rows, n_cols, xb, yb, n_tokens, OVERWRITE); cuda.end()
+    out = cuda.read(yb, np.zeros_like(y0))
+    exact = x.astype(np.float64) @ w.astype(np.float64).T
+    budget = np.abs(x.astype(np.float64)) @ np.abs(w.astype(np.float64)).T
+    err = np.abs(out[:n_tokens, :n_rows].astype(np.float64) - exact) / np.maximum(budget, 1e-30)
+    assert float(err.max()) < ROUNDED_OPERAND_TOLERANCE
+    assert (out[n_tokens] == 7.5).all()
+
+
 def test_matmul_row_equals_matvec(cuda):
     """One token through the batched multiply equals the decode multiply, the self-consistency the
     reference checks between its prefill and step paths."""
