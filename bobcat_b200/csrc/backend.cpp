@@ -42,6 +42,7 @@ bc_status check_range(const bc_backend* backend, const bc_buffer* buffer, size_t
 bc_status kernel_wait_status() {
     if (int flag = k::matvec_error_flag()) return fail(BC_ERR_EXECUTION, "a decode kernel gave up waiting for its weight stream or its input (code %d)", flag);
     if (int flag = k::matmul_error_flag()) return fail(BC_ERR_EXECUTION, "a prefill kernel gave up waiting on its pipeline (code %d)", flag);
+    if (int flag = k::matmul_few_error_flag()) return fail(BC_ERR_EXECUTION, "a few-token product gave up waiting for its weights (code %d)", flag);
     if (int flag = k::peer_error_flag()) return fail(BC_ERR_EXECUTION, "a sum over ranks gave up waiting for rank %d", flag - 1);
     return BC_OK;
 }

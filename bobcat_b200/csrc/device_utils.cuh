@@ -120,6 +120,27 @@ __device__ __forceinline__ float4 ldg_stream(const float4* p) {
     return v;
 }
 
+// The eight weights of Q4_0 quant word `w` (bytes 4t .. 4t + 3 of a block: weights 4t + e in the low
+// nibbles, 16 + 4t + e in the high ones) times the block scale, as fp16: (e = 0, 2), (1, 3) of the low
+// nibbles, then of the high ones. (q - 8) is exact in fp16 and the product is rounded once.
+__device__ __forceinline__ uint4 dequant_word(uint32_t w, __half2 scale) {
+    const uint32_t magic = 0x64006400u;  // half2(1024, 1024)
+    uint32_t lo02 = (w & 0x000f000fu) | magic;
+    uint32_t hi02 = (w & 0x00f000f0u) | magic;
+    uint32_t w8 = w >> 8;
+    uint32_t lo13 = (w8 & 0x000f000fu) | magic;
+    uint32_t hi13 = (w8 & 0x00f000f0u) | magic;
+    const __half2 bias_lo = __floats2half2_rn(1032.f, 1032.f);
+    const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
+    const __half2 bias_hi = __floats2half2_rn(-72.f, -72.f);  // (1024 + 16 q) / 16 - 72 = q - 8
+    __half2 a = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&lo02), bias_lo), scale);
+    __half2 b = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&lo13), bias_lo), scale);
+    __half2 c = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&hi02), sixteenth, bias_hi), scale);
+    __half2 d = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&hi13), sixteenth, bias_hi), scale);
+    return make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b), *reinterpret_cast<uint32_t*>(&c),
+                      *reinterpret_cast<uint32_t*>(&d));
+}
+
 // Where element (token, col) of a batch lies in the packed fp16 operand layout of the tensor-core
 // prefill kernel (kernels_matmul_umma.cu), counted in halves: chunks of 64 columns, inside a chunk
 // groups of 8 tokens, inside a group 8 core matrices of 8 tokens x 8 columns (16 bytes per token),

@@ -348,6 +348,20 @@ bool matmul_umma_swiglu_supported(const Mat& gate, const Mat& up, uint32_t n_tok
 // is not touched.
 cudaError_t matmul_umma_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, const void* packed, float* y, uint32_t n_tokens,
                                uint32_t y_stride, void* packed_out = nullptr);
+// The same products for at most 32 tokens (kernels_matmul_few.cu): the matrices' decode tiles against
+// the packed inputs on warp-level MMAs, one launch, no split of K left open. matmul_umma,
+// matmul_umma_several, matmul_umma_swiglu and matmul_experts_umma hand over to these whenever the
+// shape allows (BOBCAT_NO_FEW_MATMUL=1 keeps them on the tcgen05 kernel).
+bool matmul_few_supported(const Mat& w, uint32_t n_tokens);
+// Nonzero once a warp of that kernel gave up waiting for its weights.
+int matmul_few_error_flag();
+cudaError_t matmul_few(cudaStream_t stream, const Mat* const* ws, float* const* ys, const uint32_t* strides, int n, const void* packed,
+                       uint32_t n_tokens, int32_t store);
+cudaError_t matmul_few_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, const void* packed, float* y, uint32_t n_tokens, uint32_t y_stride,
+                              void* packed_out);
+bool matmul_few_experts_supported(const Mat& w, const Mat* up, uint32_t n_rows, uint32_t n_experts, uint32_t n_tokens);
+cudaError_t matmul_few_experts(cudaStream_t stream, const Mat& w, const Mat* up, uint32_t n_rows, uint32_t n_experts, const void* packed,
+                               const uint32_t* offsets, const uint32_t* entries, float* y, uint32_t n_tokens, uint32_t n_entries);
 // Nonzero once a bounded wait inside the tensor-core prefill kernel gave up (1: producers on a free
 // stage, 2: epilogue on the accumulator, 3: token copy on a free stage, 4: MMA thread on a full stage).
 int matmul_error_flag();

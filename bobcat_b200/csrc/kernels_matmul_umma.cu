@@ -290,25 +290,6 @@ __global__ void __launch_bounds__(256) pack_grouped_kernel(const float* __restri
     reinterpret_cast<uint4*>(packed)[((chunk * token_groups + tg) * kCores + j) * 8 + (local & 7)] = out;
 }
 
-// The eight weights of quant word `w` times the block scale, as fp16 in the permuted order.
-__device__ __forceinline__ uint4 dequant_word(uint32_t w, __half2 scale) {
-    const uint32_t magic = 0x64006400u;  // half2(1024, 1024)
-    uint32_t lo02 = (w & 0x000f000fu) | magic;
-    uint32_t hi02 = (w & 0x00f000f0u) | magic;
-    uint32_t w8 = w >> 8;
-    uint32_t lo13 = (w8 & 0x000f000fu) | magic;
-    uint32_t hi13 = (w8 & 0x00f000f0u) | magic;
-    const __half2 bias_lo = __floats2half2_rn(1032.f, 1032.f);
-    const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
-    const __half2 bias_hi = __floats2half2_rn(-72.f, -72.f);  // (1024 + 16 q) / 16 - 72 = q - 8
-    __half2 a = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&lo02), bias_lo), scale);
-    __half2 b = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&lo13), bias_lo), scale);
-    __half2 c = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&hi02), sixteenth, bias_hi), scale);
-    __half2 d = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&hi13), sixteenth, bias_hi), scale);
-    return make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b), *reinterpret_cast<uint32_t*>(&c),
-                      *reinterpret_cast<uint32_t*>(&d));
-}
-
 __device__ __forceinline__ void give_up(volatile int* dead, int code) {
     *dead = 1;
     atomicCAS(&g_matmul_error, 0, code);
@@ -761,7 +742,10 @@ uint64_t matmul_scratch_bytes(const Mat& w, uint32_t n_tokens) {
     return pack + matmul_partial_bytes(w, n_tokens);
 }
 
-int matmul_umma_launches(const Mat& w, uint32_t n_tokens) { return choose_tiling(w.n_rows, w.n_cols, n_tokens, w.n_rows, 1, true).split > 1 ? 3 : 2; }
+int matmul_umma_launches(const Mat& w, uint32_t n_tokens) {
+    if (matmul_few_supported(w, n_tokens)) return 2;
+    return choose_tiling(w.n_rows, w.n_cols, n_tokens, w.n_rows, 1, true).split > 1 ? 3 : 2;
+}
 
 bool matmul_umma_supported(const Mat& w, uint32_t n_tokens, uint32_t min_tokens) {
     return !umma_disabled() && w.format == BC_Q4_0 && w.n_cols % kChunkK == 0 && w.n_cols > 0 && n_tokens >= min_tokens && n_tokens > 0;
@@ -800,6 +784,12 @@ cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, 
                         int32_t store, float* partial_at, Deferred* defer) {
     if (defer) *defer = Deferred{};
     if (n_tokens == 0 || w.n_rows == 0) return cudaSuccess;
+    if (matmul_few_supported(w, n_tokens)) {
+        const Mat* ws[1] = {&w};
+        float* ys[1] = {y};
+        const uint32_t strides[1] = {y_stride};
+        return matmul_few(stream, ws, ys, strides, 1, scratch, n_tokens, store);
+    }
     cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), Shape<1>::kSmemBytes);
     if (err != cudaSuccess) return err;
     // The split must match matmul_scratch_bytes, which sized the scratch for a dense output.
@@ -842,6 +832,13 @@ cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, 
 cudaError_t matmul_umma_several(cudaStream_t stream, const Mat* const* ws, float* const* ys, int n, const void* packed, uint32_t n_tokens) {
     if (n < 1 || n > 4) return cudaErrorInvalidValue;
     if (n_tokens == 0) return cudaSuccess;
+    bool few = true;
+    for (int i = 0; i < n; ++i) few = few && matmul_few_supported(*ws[i], n_tokens) && ws[i]->n_cols == ws[0]->n_cols;
+    if (few) {
+        uint32_t strides[4];
+        for (int i = 0; i < n; ++i) strides[i] = ws[i]->n_rows;
+        return matmul_few(stream, ws, ys, strides, n, packed, n_tokens, BC_STORE_OVERWRITE);
+    }
     cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), Shape<1>::kSmemBytes);
     if (err != cudaSuccess) return err;
     uint32_t total_rows = 0, tiles = 0;
@@ -891,6 +888,8 @@ cudaError_t matmul_umma_swiglu(cudaStream_t stream, const Mat& gate, const Mat& 
                                uint32_t y_stride, void* packed_out) {
     if (packed_out && (gate.n_rows % kChunkK != 0)) return cudaErrorInvalidValue;
     if (n_tokens == 0 || gate.n_rows == 0) return cudaSuccess;
+    if (matmul_few_supported(gate, n_tokens) && matmul_few_supported(up, n_tokens))
+        return matmul_few_swiglu(stream, gate, up, packed, y, n_tokens, y_stride, packed_out);
     cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<2>), Shape<2>::kSmemBytes);
     if (err != cudaSuccess) return err;
     UmmaParams p{};
@@ -939,6 +938,8 @@ cudaError_t matmul_experts_umma(cudaStream_t stream, const Mat& w, const Mat* up
     cudaError_t err = launch_dependent(pack_grouped_kernel, dim3((unsigned)((outputs + 255) / 256)), dim3(256), 0, stream, x, static_cast<__half*>(scratch),
                                        offsets, entries, n_experts, n_used, gather ? 1 : 0, w.n_cols, cap_groups, total);
     if (err != cudaSuccess) return err;
+    if (matmul_few_experts_supported(w, up, n_rows, n_experts, n_tokens))
+        return matmul_few_experts(stream, w, up, n_rows, n_experts, scratch, offsets, entries, y, n_tokens, total);
     UmmaParams p{};
     p.quants[0] = static_cast<const uint4*>(w.data);
     p.scales[0] = w.scales;

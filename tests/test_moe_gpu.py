@@ -89,7 +89,8 @@ def test_group_is_a_stable_counting_sort(cuda):
 
 # (n_tokens, n_ff): widths that are multiples of 64 with at least 16 tokens send the grouped product to the
 # tensor-core kernel (fp16 operands, like the reference's Q4_0 prefill kernel); the rest stay on the f32 tile kernel.
-@pytest.mark.parametrize("n_tokens,n_ff,n_embd", [(1, 96, 128), (5, 96, 128), (70, 96, 128), (70, 128, 128), (300, 192, 128), (300, 256, 1024)])
+@pytest.mark.parametrize("n_tokens,n_ff,n_embd", [(1, 96, 128), (5, 96, 128), (70, 96, 128), (70, 128, 128), (300, 192, 128), (300, 256, 1024),
+                                                     (16, 128, 128), (24, 192, 256), (32, 128, 1024), (32, 1792, 2048)])
 def test_expert_paths_match_the_scalar_block(cuda, n_tokens, n_ff, n_embd):
     """Decode (per-token expert matvecs) and prefill (group, grouped matmul, combine) both equal
     lfm2.rs:413-440 computed with the checker's f64 matvec."""

@@ -306,7 +306,9 @@ def test_argmax_ties_go_to_the_lowest_index(cuda):
 
 # Full and partial tiles (crates/bobcat/tests/metal_matmul.rs:226-294): (n_rows, n_cols, n_tokens)
 MATMUL_SHAPES = [(64, 64, 32), (128, 256, 64), (70, 96, 33), (1, 32, 1), (6144, 2048, 128), (2048, 10752, 65), (513, 2048, 512),
-                 (128, 64, 16), (256, 128, 272), (300, 192, 100), (128, 4096, 257)]
+                 (128, 64, 16), (256, 128, 272), (300, 192, 100), (128, 4096, 257),
+                 # at most 32 tokens: the warp-level kernel over the decode tiles (groups of 16, 3, 2 and 1 warps per tile)
+                 (2048, 10752, 32), (6144, 2048, 20), (100, 64, 24), (16, 64, 16), (10752, 2048, 32), (4100, 1088, 17)]
 # Tolerance of the reference's matmul test (metal_matmul.rs), per unit of sum |w x|.
 MATMUL_TOLERANCE = 1e-4
 # The tensor-core kernel rounds weights and inputs to fp16 like the reference's Q4_0 prefill kernel
