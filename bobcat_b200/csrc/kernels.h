@@ -359,6 +359,11 @@ cudaError_t matmul_few(cudaStream_t stream, const Mat* const* ws, float* const* 
                        uint32_t n_tokens, int32_t store);
 cudaError_t matmul_few_swiglu(cudaStream_t stream, const Mat& gate, const Mat& up, const void* packed, float* y, uint32_t n_tokens, uint32_t y_stride,
                               void* packed_out);
+// A matrix too wide for matmul_few (more packed tokens than a CTA keeps): the number of slices of
+// K it is cut into (0: not this kernel's), and the product as that many arrays of
+// [n_tokens][w.n_rows] partial sums, to be added in index order.
+uint32_t matmul_few_slices(const Mat& w, uint32_t n_tokens);
+cudaError_t matmul_few_sliced(cudaStream_t stream, const Mat& w, const void* packed, float* partial, uint32_t n_tokens);
 bool matmul_few_experts_supported(const Mat& w, const Mat* up, uint32_t n_rows, uint32_t n_experts, uint32_t n_tokens);
 cudaError_t matmul_few_experts(cudaStream_t stream, const Mat& w, const Mat* up, uint32_t n_rows, uint32_t n_experts, const void* packed,
                                const uint32_t* offsets, const uint32_t* entries, float* y, uint32_t n_tokens, uint32_t n_entries);

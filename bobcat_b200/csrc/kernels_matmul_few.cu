@@ -79,6 +79,10 @@ struct FewParams {
     // The CTA's warps: groups of `width` warps per matrix (twice that with two matrices) take a
     // tile each, every warp `share` pairs of it.
     uint32_t width, share;
+    // Wide matrices (more tokens than a CTA can keep): K is cut into slices of slice_pairs pairs,
+    // ctas_per_slice CTAs work on a slice (tiles c, c + ctas_per_slice, ...) and keep only its
+    // tokens; slice s writes its sums to y[0] + s * n_tokens * seg_stride[0] for the host to add up.
+    uint32_t slice_pairs, ctas_per_slice;
 };
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -300,9 +304,10 @@ __device__ __forceinline__ void store_tile(const FewParams& p, const Job& j, uin
 // its own slots, [register][lane], once it has read the weights there.
 template <int NT, bool XS>
 __device__ __forceinline__ void do_job(const FewParams& p, const Job& j, uint32_t rank, uint32_t width, uint32_t group_warps, uint32_t group,
-                                       uint32_t lane, uint8_t* slots, uint32_t copiers, Worker<NT, XS>& worker, bool& waited) {
-    const uint32_t pairs = p.n_blocks / 2, stream = rank >= width ? 1 : 0, part = rank - stream * width;
-    const uint32_t first = part * p.share < pairs ? part * p.share : pairs, last = first + p.share < pairs ? first + p.share : pairs;
+                                       uint32_t lane, uint8_t* slots, uint32_t copiers, uint32_t lo, uint32_t hi, Worker<NT, XS>& worker, bool& waited) {
+    // The CTA's pairs are [lo, hi): all of them, or its slice.
+    const uint32_t stream = rank >= width ? 1 : 0, part = rank - stream * width;
+    const uint32_t first = lo + part * p.share < hi ? lo + part * p.share : hi, last = first + p.share < hi ? first + p.share : hi;
     float acc[NT][4], up[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n)
@@ -318,8 +323,8 @@ __device__ __forceinline__ void do_job(const FewParams& p, const Job& j, uint32_
             // The launch's tokens, one contiguous run of the packed operand, into shared memory: the
             // warps that have a job in the first round copy them together, 16 bytes a thread at a
             // time, each core matrix's pieces permuted as the readers expect.
-            const uint4* src = p.packed;
-            const uint32_t n_pieces = p.token_bytes / 16;
+            const uint4* src = p.packed + (uint64_t)lo * p.token_groups * 64;
+            const uint32_t n_pieces = (hi - lo) * p.token_groups * 64, to = worker.tokens + lo * p.token_groups * 64 * 16;  // where pair lo stands
             for (uint32_t q = threadIdx.x; q < n_pieces; q += 4 * copiers) {
                 uint4 v[4];
 #pragma unroll
@@ -329,7 +334,7 @@ __device__ __forceinline__ void do_job(const FewParams& p, const Job& j, uint32_
                 for (int u = 0; u < 4; ++u) {
                     const uint32_t at = q + u * copiers;
                     if (at < n_pieces)
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(worker.tokens + ((at & ~7u) + ((at & 7u) ^ (2 * ((at >> 3) & 3u)))) * 16), "r"(v[u].x),
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(to + ((at & ~7u) + ((at & 7u) ^ (2 * ((at >> 3) & 3u)))) * 16), "r"(v[u].x),
                                      "r"(v[u].y), "r"(v[u].z), "r"(v[u].w)
                                      : "memory");
                 }
@@ -394,21 +399,32 @@ __global__ void __launch_bounds__(kThreads, 1) matmul_few_kernel(FewParams p) {
         __syncthreads();
         n_jobs = n_active * p.n_jobs;
     }
-    const uint32_t my_jobs = n_jobs > blockIdx.x ? (n_jobs - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    uint32_t job0 = blockIdx.x, job_step = gridDim.x, lo = 0, hi = p.n_blocks / 2;
+    uint64_t slice_out = 0;
+    if (p.slice_pairs) {
+        const uint32_t slice = blockIdx.x / p.ctas_per_slice;
+        job0 = blockIdx.x % p.ctas_per_slice, job_step = p.ctas_per_slice;
+        lo = slice * p.slice_pairs;
+        hi = lo + p.slice_pairs < hi ? lo + p.slice_pairs : hi;
+        slice_out = (uint64_t)slice * p.n_tokens * p.seg_stride[0];
+    }
+    const uint32_t my_jobs = n_jobs > job0 ? (n_jobs - job0 + job_step - 1) / job_step : 0;
     if (my_jobs == 0) return;
     const uint32_t width = p.width, streams = p.dual ? 2 : 1;
     const uint32_t group_warps = width * streams, groups = kWarps / group_warps, group = warp / group_warps, rank = warp % group_warps;
     if (group >= groups) return;  // the warps left over when 16 is not a multiple of the group size
     for (uint32_t i = group; i < my_jobs; i += groups) {
-        const Job j = job_of(p, blockIdx.x + i * gridDim.x, active);
+        Job j = job_of(p, job0 + i * job_step, active);
+        j.y += slice_out;
         const uint32_t slot = async::smem_u32(few_smem + warp * (2 * kSlotBytes)), bar = async::smem_u32(&bars[warp][0]);
-        const uint32_t tokens = async::smem_u32(few_smem + kWarps * kSlotBytes);
+        // The address pair 0's tokens would have: a slice's CTA keeps only pairs lo .. hi, from here on.
+        const uint32_t tokens = async::smem_u32(few_smem + kWarps * kSlotBytes) - lo * p.token_groups * 64 * 16;
         const uint32_t copiers = (my_jobs < groups ? my_jobs : groups) * group_warps * 32;  // the threads with a job in the first round
         const uint32_t small = async::smem_u32(few_smem + warp * kSlotBytes);  // slots of half the size when the tokens follow them
 #define BC_FEW_JOB(NT, XS)                                                                                            \
     {                                                                                                                 \
         Worker<NT, XS> worker{XS ? small : slot, bar, XS ? tokens : 0u, issued, taken, 0, 0};                          \
-        do_job<NT, XS>(p, j, rank, width, group_warps, group, lane, few_smem, copiers, worker, waited);                \
+        do_job<NT, XS>(p, j, rank, width, group_warps, group, lane, few_smem, copiers, lo, hi, worker, waited);        \
         issued = worker.issued, taken = worker.taken;                                                                 \
     }
         if (p.token_bytes) {
@@ -439,12 +455,20 @@ cudaError_t launch_few(cudaStream_t stream, FewParams p, uint32_t most_jobs, uin
     cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_few_kernel), kFewSlots / 2 + kMaxTokenBytes);
     const size_t smem = p.token_bytes ? kFewSlots / 2 + p.token_bytes : kFewSlots;
     if (e != cudaSuccess) return e;
-    const uint32_t sms = (uint32_t)sm_count(), ctas = most_jobs < sms ? most_jobs : sms;
+    const uint32_t sms = (uint32_t)sm_count();
+    uint32_t ctas = most_jobs < sms ? most_jobs : sms;
+    if (p.slice_pairs) {
+        const uint32_t slices = (p.n_blocks / 2 + p.slice_pairs - 1) / p.slice_pairs;
+        p.ctas_per_slice = sms / slices > most_jobs ? most_jobs : sms / slices;
+        if (p.ctas_per_slice == 0) return cudaErrorInvalidValue;
+        ctas = p.ctas_per_slice * slices;
+        likely_jobs *= slices;  // jobs per CTA: the tiles over the CTAs of a slice
+    }
     // Warps per job. A group of warps takes a job, `width` of them per matrix, each a share of the
     // pairs; a CTA's jobs go through its groups in rounds. The cost of a choice is rounds x (pairs
     // per warp + a round's fixed cost, about 3 pairs' worth); the narrowest group with the least
     // cost wins.
-    const uint32_t pairs = p.n_blocks / 2, streams = p.dual ? 2 : 1, my_jobs = (likely_jobs + ctas - 1) / ctas;
+    const uint32_t pairs = p.slice_pairs ? p.slice_pairs : p.n_blocks / 2, streams = p.dual ? 2 : 1, my_jobs = (likely_jobs + ctas - 1) / ctas;
     uint32_t best = 0xffffffffu;
     p.width = 1;
     for (uint32_t w = 1; w * streams <= (uint32_t)kWarps && w <= pairs; ++w) {
@@ -493,6 +517,36 @@ cudaError_t matmul_few(cudaStream_t stream, const Mat* const* ws, float* const* 
     p.n_tokens = n_tokens;
     p.token_bytes = few_token_bytes(ws[0]->n_cols, n_tokens);
     p.store = store;
+    if (p.n_jobs == 0) return cudaSuccess;
+    return launch_few(stream, p, p.n_jobs, p.n_jobs);
+}
+
+uint32_t matmul_few_slices(const Mat& w, uint32_t n_tokens) {
+    if (few_disabled() || w.format != BC_Q4_0 || w.tiles == nullptr || n_tokens == 0 || n_tokens > kMaxFewTokens || w.n_cols % 64 != 0 || w.n_cols == 0 || w.n_rows % 4 != 0) return 0;
+    const uint32_t bytes = few_token_bytes(w.n_cols, n_tokens);
+    if (bytes <= kMaxTokenBytes) return 0;  // fits whole: matmul_few
+    const uint32_t slices = (bytes + kMaxTokenBytes - 1) / kMaxTokenBytes;
+    return slices <= 16 ? slices : 0;
+}
+
+cudaError_t matmul_few_sliced(cudaStream_t stream, const Mat& w, const void* packed, float* partial, uint32_t n_tokens) {
+    const uint32_t slices = matmul_few_slices(w, n_tokens);
+    if (slices == 0) return cudaErrorInvalidValue;
+    FewParams p{};
+    p.n_segments = 1;
+    p.tiles[0] = static_cast<const uint8_t*>(w.tiles);
+    p.y[0] = partial;
+    p.seg_tiles[0] = (w.n_rows + 15) / 16;
+    p.seg_rows[0] = w.n_rows;
+    p.seg_stride[0] = w.n_rows;
+    p.n_jobs = p.seg_tiles[0];
+    p.n_blocks = w.n_cols / 32;
+    p.packed = static_cast<const uint4*>(packed);
+    p.token_groups = ((n_tokens + 15u) & ~15u) / 8;
+    p.n_tokens = n_tokens;
+    p.slice_pairs = (p.n_blocks / 2 + slices - 1) / slices;
+    p.token_bytes = p.slice_pairs * p.token_groups * 1024;
+    p.store = BC_STORE_OVERWRITE;
     if (p.n_jobs == 0) return cudaSuccess;
     return launch_few(stream, p, p.n_jobs, p.n_jobs);
 }

@@ -733,6 +733,7 @@ bool umma_disabled() {
 uint64_t matmul_pack_bytes(uint32_t n_tokens, uint32_t n_cols) { return (uint64_t)((n_tokens + 15u) & ~15u) * n_cols * 2; }
 
 uint64_t matmul_partial_bytes(const Mat& w, uint32_t n_tokens) {
+    if (const uint32_t slices = matmul_few_slices(w, n_tokens)) return (uint64_t)slices * n_tokens * w.n_rows * 4;
     uint32_t split = choose_tiling(w.n_rows, w.n_cols, n_tokens, w.n_rows, 1, true).split;
     return split > 1 ? (uint64_t)split * n_tokens * w.n_rows * 4 : 0;
 }
@@ -744,6 +745,7 @@ uint64_t matmul_scratch_bytes(const Mat& w, uint32_t n_tokens) {
 
 int matmul_umma_launches(const Mat& w, uint32_t n_tokens) {
     if (matmul_few_supported(w, n_tokens)) return 2;
+    if (matmul_few_slices(w, n_tokens)) return 3;
     return choose_tiling(w.n_rows, w.n_cols, n_tokens, w.n_rows, 1, true).split > 1 ? 3 : 2;
 }
 
@@ -789,6 +791,21 @@ cudaError_t matmul_umma(cudaStream_t stream, const Mat& w, const void* scratch, 
         float* ys[1] = {y};
         const uint32_t strides[1] = {y_stride};
         return matmul_few(stream, ws, ys, strides, 1, scratch, n_tokens, store);
+    }
+    if (const uint32_t slices = matmul_few_slices(w, n_tokens)) {
+        // A wide matrix against few tokens: slices of K on the few-token kernel, summed in order.
+        float* partial = partial_at ? partial_at
+                                    : reinterpret_cast<float*>(static_cast<char*>(const_cast<void*>(scratch)) +
+                                                               ((matmul_pack_bytes(n_tokens, w.n_cols) + 255) & ~255ull));
+        cudaError_t e = matmul_few_sliced(stream, w, scratch, partial, n_tokens);
+        if (e != cudaSuccess) return e;
+        if (defer && store == BC_STORE_ACCUMULATE && y_stride == w.n_rows) {
+            *defer = Deferred{partial, slices, n_tokens, w.n_rows};
+            return cudaSuccess;
+        }
+        const uint64_t quads = (uint64_t)n_tokens * w.n_rows / 4;
+        return launch_dependent(reduce_kernel, dim3((unsigned)((quads + 255) / 256)), dim3(256), 0, stream, static_cast<const float*>(partial), y, w.n_rows,
+                                n_tokens, y_stride, slices, (int)store);
     }
     cudaError_t err = ensure_dynamic_smem(reinterpret_cast<const void*>(&matmul_umma_kernel<1>), Shape<1>::kSmemBytes);
     if (err != cudaSuccess) return err;
