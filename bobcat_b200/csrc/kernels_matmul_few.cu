@@ -28,7 +28,9 @@
 // core c goes to g ^ 2 (c % 4)): the four t-lanes of a quarter warp read cores 128 bytes apart,
 // which unpermuted is a four-way bank conflict on every read - it, not the weights or the MMAs,
 // set the kernel's time at first (40 us for gate and up of the 2.6B shape, 30 us without it).
-// Otherwise (experts: each has its own few tokens) the pieces come through L1.
+// A wider operand is cut into slices of K that fit: the CTAs are divided among the slices, each
+// keeps its slice's tokens, and slice s leaves its sums in array s of a scratch the host adds up in
+// order (matmul_few_sliced). Experts (each has its own few tokens) read the pieces through L1.
 //
 // Work. A job is a 16-row tile over all of K (for gate/up: the tile of both matrices). A CTA is 16
 // warps on one SM; the CTAs take the jobs in turn, in rounds of as many jobs as the CTA has groups
